@@ -1,0 +1,233 @@
+/*
+ * yule_cuda.h — C ABI of libyule_cuda.so, a B200 (sm_100a) compute backend for Yule.
+ *
+ * The library is the device side of Yule's `ComputeBackend` trait
+ * (yule-gpu/src/lib.rs:21-132).  A Rust shim maps each trait method onto the
+ * entry point of the same name below; `BufferHandle(u64)` (lib.rs:135) crosses
+ * unchanged as `yule_buffer`, `DType` crosses as its GGUF type id
+ * (yule-core/src/dtype.rs:13-58, :155-190), and every failure comes back as a
+ * nonzero status whose text (`yule_cuda_last_error`) the shim wraps in
+ * `YuleError::Gpu(String)` (yule-core/src/error.rs:44).
+ *
+ * Conventions
+ *   - Every entry point returns int32 status; 0 is success.  No exception or
+ *     abort crosses the boundary.
+ *   - All entry points are thread-safe (`ComputeBackend: Send + Sync`, every
+ *     method takes `&self`).  Work is enqueued on one stream per context, so
+ *     ordering between calls is call order; only copy_from_device,
+ *     synchronize, destroy and the runner's logits read-back block the host.
+ *   - Buffers are owned by the context, zero-filled on allocation
+ *     (yule-gpu/src/cuda/memory.rs:26) and addressed only by handle; sizes and
+ *     offsets are checked against the allocation, a bad handle is an error and
+ *     never undefined behaviour.
+ *   - Quantized weights are raw GGUF tensor bytes, unmodified
+ *     (yule-infer/src/gpu_runner.rs:176-181).
+ *   - There is no CPU fallback: without a CUDA device `yule_cuda_create` fails.
+ */
+#ifndef YULE_CUDA_H
+#define YULE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct yule_cuda_ctx yule_cuda_ctx;
+typedef struct yule_cuda_runner yule_cuda_runner;
+typedef uint64_t yule_buffer; /* yule-gpu/src/lib.rs:135 BufferHandle(pub u64) */
+
+/* Status codes (nonzero ⇒ YuleError::Gpu(last_error)). */
+enum {
+    YULE_OK = 0,
+    YULE_ERR_INVALID_ARGUMENT = 1,
+    YULE_ERR_UNKNOWN_BUFFER = 2,   /* cuda/memory.rs "unknown buffer" */
+    YULE_ERR_OUT_OF_BOUNDS = 3,
+    YULE_ERR_UNSUPPORTED_DTYPE = 4, /* cuda/mod.rs:303-307 */
+    YULE_ERR_CUDA = 5,
+    YULE_ERR_OUT_OF_MEMORY = 6,
+    YULE_ERR_DEVICE_STATUS = 7,    /* a bounded device-side wait gave up */
+    YULE_ERR_CONTEXT_LENGTH = 8,   /* gpu_runner.rs:305-307 "context length exceeded" */
+    YULE_ERR_MISSING_TENSOR = 9
+};
+
+/* GGUF type ids accepted where a dtype is asked for (dtype.rs:155-190). */
+enum {
+    YULE_DTYPE_F32 = 0,
+    YULE_DTYPE_F16 = 1,
+    YULE_DTYPE_Q4_0 = 2,
+    YULE_DTYPE_Q8_0 = 8,
+    YULE_DTYPE_Q4_K = 12,
+    YULE_DTYPE_Q6_K = 14
+};
+
+/* Text of the calling thread's most recent failure (UTF-8, NUL-terminated,
+ * valid until that thread's next failing call). */
+const char *yule_cuda_last_error(void);
+
+/* ── lifecycle: CudaBackend::is_available / new / Drop / device_info
+ *    (yule-gpu/src/cuda/mod.rs:20-58, cuda/device.rs:5-77) ─────────────── */
+int32_t yule_cuda_is_available(void); /* 1 when a CUDA device answers, else 0 */
+int32_t yule_cuda_create(int32_t device_ordinal, yule_cuda_ctx **out_ctx);
+int32_t yule_cuda_destroy(yule_cuda_ctx *ctx);
+int32_t yule_cuda_device_info(yule_cuda_ctx *ctx, char *name_buf, size_t name_cap,
+                              uint64_t *memory_bytes, uint32_t *compute_units);
+
+/* ── memory: ComputeBackend::allocate / free / copy_* / synchronize
+ *    (lib.rs:24-25, :69-80; cuda/memory.rs:10-154) ─────────────────────── */
+int32_t yule_cuda_allocate(yule_cuda_ctx *ctx, size_t size_bytes, yule_buffer *out_handle);
+int32_t yule_cuda_free(yule_cuda_ctx *ctx, yule_buffer handle);
+/* Copies min(len, allocation) bytes like the reference's slice semantics. */
+int32_t yule_cuda_copy_to_device(yule_cuda_ctx *ctx, const void *data, size_t len, yule_buffer dst);
+int32_t yule_cuda_copy_from_device(yule_cuda_ctx *ctx, yule_buffer src, void *data, size_t len);
+int32_t yule_cuda_copy_buffer(yule_cuda_ctx *ctx, yule_buffer src, yule_buffer dst, size_t size);
+int32_t yule_cuda_copy_buffer_offset(yule_cuda_ctx *ctx, yule_buffer src, yule_buffer dst,
+                                     size_t src_offset, size_t dst_offset, size_t size);
+int32_t yule_cuda_synchronize(yule_cuda_ctx *ctx);
+
+/* ── compute: the trait's numeric methods with the semantics of the
+ *    reference's own GPU backends (cuda/mod.rs:95-328, vulkan/mod.rs) ───── */
+
+/* lib.rs:26 matmul — kernels/cuda/matmul.cu:4-32: out[row] = dot(A[row,0..k], b)
+ * for row < m; `n` is carried but unused, as in the reference kernel. */
+int32_t yule_cuda_matmul(yule_cuda_ctx *ctx, yule_buffer a, yule_buffer b, yule_buffer out,
+                         uint32_t m, uint32_t n, uint32_t k);
+/* lib.rs:35 softmax — kernels/cuda/softmax.cu:3-45 (max-subtracted). */
+int32_t yule_cuda_softmax(yule_cuda_ctx *ctx, yule_buffer input, yule_buffer output, uint32_t size);
+/* lib.rs:36 rms_norm — kernels/cuda/rms_norm.cu:4-36: x * rsqrt(mean(x^2)+eps) * w. */
+int32_t yule_cuda_rms_norm(yule_cuda_ctx *ctx, yule_buffer input, yule_buffer weight,
+                           yule_buffer output, uint32_t size, float eps);
+/* lib.rs:44 rope — kernels/cuda/rope.cu:3-49: interleaved pairs (2i,2i+1) of
+ * every Q and K head rotated in place by pos * base^(-2i/head_dim). */
+int32_t yule_cuda_rope(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k, uint32_t pos,
+                       uint32_t head_dim, float freq_base, uint32_t n_heads_q, uint32_t n_heads_k);
+/* lib.rs:54 silu — cuda/mod.rs:173-188: output = SiLU(input) * output. */
+int32_t yule_cuda_silu(yule_cuda_ctx *ctx, yule_buffer input, yule_buffer output, uint32_t size);
+/* lib.rs:55 element_mul — cuda/mod.rs:190-208: output = SiLU(a) * b. */
+int32_t yule_cuda_element_mul(yule_cuda_ctx *ctx, yule_buffer a, yule_buffer b, yule_buffer output,
+                              uint32_t size);
+/* lib.rs:62 add — kernels/cuda/add.cu:2-11. */
+int32_t yule_cuda_add(yule_cuda_ctx *ctx, yule_buffer a, yule_buffer b, yule_buffer output,
+                      uint32_t size);
+/* lib.rs:83 attn_score — kernels/cuda/attn_score.cu:3-33: scores[t] =
+ * dot(q[head_offset..+hd], K[t*kv_stride+kv_offset..]) / sqrt(hd); offsets and
+ * strides count floats. */
+int32_t yule_cuda_attn_score(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k_cache,
+                             yule_buffer scores, uint32_t head_dim, uint32_t seq_len,
+                             uint32_t head_offset, uint32_t kv_offset, uint32_t kv_stride);
+/* lib.rs:100 attn_value — kernels/cuda/attn_value.cu:3-33: out[out_offset+d] =
+ * sum_t weights[t] * V[t*kv_stride+kv_offset+d]. */
+int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffer v_cache,
+                             yule_buffer output, uint32_t head_dim, uint32_t seq_len,
+                             uint32_t kv_offset, uint32_t kv_stride, uint32_t out_offset);
+/* lib.rs:119 quantized_matmul — cuda/mod.rs:289-328 + kernels/cuda/qmv_*.cu:
+ * out[row] = sum over blocks of dot(dequant(W[row, block]), x[block]).
+ * gguf_type is 2 (Q4_0), 8 (Q8_0), 12 (Q4_K) or 14 (Q6_K); n_cols must be a
+ * multiple of the format's block size. */
+int32_t yule_cuda_quantized_matmul(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffer input,
+                                   yule_buffer output, uint32_t n_rows, uint32_t n_cols,
+                                   uint32_t gguf_type);
+
+/* ── additive entry points (not trait methods; each equals a sequence of
+ *    trait calls, so the plain trait stays sufficient) ──────────────────── */
+
+/* `batch` activation vectors against one weight read: input is
+ * [batch][x_stride] floats, output [batch][out_stride] floats.  Same per-row
+ * arithmetic as quantized_matmul. */
+int32_t yule_cuda_quantized_matmul_batched(yule_cuda_ctx *ctx, yule_buffer weights,
+                                           yule_buffer input, yule_buffer output, uint32_t n_rows,
+                                           uint32_t n_cols, uint32_t gguf_type, uint32_t batch,
+                                           uint32_t x_stride, uint32_t out_stride);
+/* Same as quantized_matmul but the weight tensor starts `weight_offset` bytes
+ * into its buffer (a multiple of 2; 16 for Q4_K) — what a row-sharded rank or a
+ * ring of tensor copies in one allocation needs. */
+int32_t yule_cuda_quantized_matmul_at(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset,
+                                      yule_buffer input, yule_buffer output, uint32_t n_rows,
+                                      uint32_t n_cols, uint32_t gguf_type);
+/* dequant_block over a whole tensor (yule-core/src/dequant.rs:1232): n_blocks
+ * raw blocks → n_blocks*block_size floats.  Results are bit-identical to
+ * yule-core's scalar dequantisers. */
+int32_t yule_cuda_dequantize(yule_cuda_ctx *ctx, yule_buffer weights, uint32_t gguf_type,
+                             uint64_t n_blocks, yule_buffer out_f32);
+/* The MultiheadAttn dispatch of the GPU runner (gpu_runner.rs:477-499,
+ * shaders/multihead_attn.comp): for every head h, kv head h/(n_heads/n_kv_heads):
+ * scores → softmax → weighted V sum over positions [0, seq_len). */
+int32_t yule_cuda_multihead_attention(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k_cache,
+                                      yule_buffer v_cache, yule_buffer out, uint32_t head_dim,
+                                      uint32_t seq_len, uint32_t n_heads, uint32_t n_kv_heads,
+                                      uint32_t kv_stride);
+/* Embedding row `token` of a [vocab][dim] table of any supported dtype (F32,
+ * F16 or a quantized format) dequantised to `out` — the step the reference GPU
+ * runner does on the CPU (gpu_runner.rs:309-343). */
+int32_t yule_cuda_embed_gather(yule_cuda_ctx *ctx, yule_buffer table, uint32_t gguf_type,
+                               uint32_t dim, uint32_t token, yule_buffer out);
+
+/* Record a sequence of this context's compute/copy_buffer calls once and replay it: between
+ * graph_begin and graph_end the calls are captured into a CUDA graph instead of executed (the
+ * blocking entry points — copy_from_device, synchronize, free, destroy — must not be called
+ * in between).  graph_launch enqueues one replay on the context's stream.  This is the
+ * single-submit batching of the reference's Vulkan runner (begin_batch / submit_batch,
+ * yule-gpu/src/vulkan/mod.rs:108-174) in CUDA terms. */
+int32_t yule_cuda_graph_begin(yule_cuda_ctx *ctx);
+int32_t yule_cuda_graph_end(yule_cuda_ctx *ctx, uint32_t *out_graph_id);
+int32_t yule_cuda_graph_launch(yule_cuda_ctx *ctx, uint32_t graph_id);
+int32_t yule_cuda_graph_destroy(yule_cuda_ctx *ctx, uint32_t graph_id);
+
+/* Stream-ordered timing without any other CUDA binding: record returns an
+ * event id on the context's stream; elapsed gives milliseconds between two
+ * recorded events after waiting for the second. */
+int32_t yule_cuda_event_record(yule_cuda_ctx *ctx, uint32_t *out_event_id);
+int32_t yule_cuda_event_elapsed_ms(yule_cuda_ctx *ctx, uint32_t start_id, uint32_t end_id,
+                                   float *out_ms);
+int32_t yule_cuda_event_reset(yule_cuda_ctx *ctx);
+/* Overwrites a context-owned scratch larger than L2 so that the next kernel
+ * finds its inputs in HBM, not in cache. */
+int32_t yule_cuda_flush_l2(yule_cuda_ctx *ctx);
+/* Number of kernels this library has launched on the context so far. */
+int32_t yule_cuda_launch_count(yule_cuda_ctx *ctx, uint64_t *out_count);
+
+/* ── forward-pass runner: the `ModelRunner` trait
+ *    (yule-infer/src/model_runner.rs:12-17) issued in the op order of
+ *    GpuTransformerRunner::forward (yule-infer/src/gpu_runner.rs:296-695) ── */
+typedef struct {
+    uint32_t dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, ff_dim, max_seq_len;
+    float norm_eps, rope_freq_base;
+    /* 0: one kernel per reference dispatch (RmsNorm, Qmv, Rope, KV copy,
+     *    MultiheadAttn, Add, SiluMul), launched one by one.
+     * 1: fused kernels replayed from a CUDA graph (same arithmetic per row). */
+    uint32_t fused;
+} yule_runner_config;
+
+int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cfg,
+                                yule_cuda_runner **out_runner);
+int32_t yule_cuda_runner_destroy(yule_cuda_runner *runner);
+/* Register an uploaded tensor under its GGUF name ("token_embd.weight",
+ * "blk.%u.attn_q.weight", "output_norm.weight", …; gpu_runner.rs:171-254).
+ * Norm weights are F32 or F16; matrices are Q4_0/Q8_0/Q4_K/Q6_K. */
+int32_t yule_cuda_runner_set_tensor(yule_cuda_runner *runner, const char *name, yule_buffer handle,
+                                    uint32_t gguf_type);
+/* ModelRunner::prefill — token-by-token forward (gpu_runner.rs:703-709);
+ * logits (vocab_size floats, host memory) of the last token. */
+int32_t yule_cuda_runner_prefill(yule_cuda_runner *runner, const uint32_t *tokens, uint32_t n_tokens,
+                                 float *logits_out);
+/* ModelRunner::decode_step (gpu_runner.rs:711-713). */
+int32_t yule_cuda_runner_decode_step(yule_cuda_runner *runner, uint32_t token, float *logits_out);
+/* ModelRunner::reset (gpu_runner.rs:715-719). */
+int32_t yule_cuda_runner_reset(yule_cuda_runner *runner);
+int32_t yule_cuda_runner_position(yule_cuda_runner *runner, uint32_t *out_pos);
+/* Greedy generation with the argmax on the device (ties resolve to the highest
+ * index, yule-infer/src/sampler.rs:150-163): feeds `prompt`, then emits
+ * n_generate tokens into out_tokens.  Only token ids cross the bus. */
+int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *runner, const uint32_t *prompt,
+                                         uint32_t n_prompt, uint32_t n_generate,
+                                         uint32_t *out_tokens);
+/* Device buffers of the runner for layer-by-layer checks: which = 0 hidden,
+ * 1 K cache of `layer`, 2 V cache of `layer`, 3 logits. */
+int32_t yule_cuda_runner_buffer(yule_cuda_runner *runner, uint32_t which, uint32_t layer,
+                                yule_buffer *out_handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YULE_CUDA_H */

@@ -1,0 +1,132 @@
+"""Fused dequant-matvec (ComputeBackend::quantized_matmul, yule-gpu/src/lib.rs:119) against the
+scalar fused dots of yule-core/src/dequant.rs:902-1009 driven by qmv (yule-infer/src/model_runner.rs:152)."""
+
+import numpy as np
+import pytest
+
+from conftest import REL_TOL, guarded_rel_err
+from yule_b200 import DType, YuleGpuError, synth
+
+pytestmark = pytest.mark.gpu
+
+FORMATS = [DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K]
+
+
+def gpu_qmv(backend, dtype, w, x, n_rows, n_cols, batch=1):
+    wh = backend.upload(w)
+    xh = backend.upload(x)
+    oh = backend.allocate(batch * n_rows * 4)
+    if batch == 1:
+        backend.quantized_matmul(wh, xh, oh, n_rows, n_cols, dtype)
+    else:
+        backend.quantized_matmul_batched(wh, xh, oh, n_rows, n_cols, dtype, batch)
+    y = backend.download(oh, batch * n_rows)
+    for h in (wh, xh, oh):
+        backend.free(h)
+    return y
+
+
+def case(dtype, n_rows, n_cols, seed, batch=1):
+    w = synth.random_blocks(dtype, seed, n_rows * (n_cols // dtype.block_size))
+    x = synth.normal(seed + 1, batch * n_cols)
+    return w, x
+
+
+@pytest.mark.parametrize("dtype", FORMATS)
+@pytest.mark.parametrize("n_rows,blocks_per_row", [(1, 1), (7, 2), (129, 22), (5632, 8), (2048, 22), (300, 56)])
+def test_matches_scalar_reference(backend, oracle, dtype, n_rows, blocks_per_row):
+    n_cols = blocks_per_row * 256  # a multiple of every format's block size
+    w, x = case(dtype, n_rows, n_cols, seed=100 + n_rows)
+    y = gpu_qmv(backend, dtype, w, x, n_rows, n_cols)
+    ref = oracle.qmv(int(dtype), w, x, n_rows, n_cols, simd=oracle.SCALAR)
+    assert guarded_rel_err(y, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("dtype", [DType.Q4_0, DType.Q8_0])
+def test_small_block_formats_odd_columns(backend, oracle, dtype):
+    """32-weight blocks with a column count that is not a multiple of 256."""
+    n_rows, n_cols = 33, 32 * 5
+    w, x = case(dtype, n_rows, n_cols, seed=9)
+    y = gpu_qmv(backend, dtype, w, x, n_rows, n_cols)
+    ref = oracle.qmv(int(dtype), w, x, n_rows, n_cols)
+    assert guarded_rel_err(y, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("dtype", FORMATS)
+@pytest.mark.parametrize("batch", [2, 4, 5, 16])
+def test_batched_equals_per_vector(backend, oracle, dtype, batch):
+    n_rows, n_cols = 513, 2048
+    w, x = case(dtype, n_rows, n_cols, seed=77, batch=batch)
+    y = gpu_qmv(backend, dtype, w, x, n_rows, n_cols, batch=batch).reshape(batch, n_rows)
+    for b in range(batch):
+        ref = oracle.qmv(int(dtype), w, x[b * n_cols:(b + 1) * n_cols], n_rows, n_cols)
+        assert guarded_rel_err(y[b], ref) <= REL_TOL
+
+
+def test_config0_shape_quantised_gaussian(backend, oracle):
+    """The TinyLlama FFN-up shape of the headline matvec: 5632 x 2048 Q4_K."""
+    n_rows, n_cols = 5632, 2048
+    w = synth.random_quantized(DType.Q4_K, 5, n_rows * n_cols)
+    x = synth.normal(6, n_cols)
+    y = gpu_qmv(backend, DType.Q4_K, w, x, n_rows, n_cols)
+    ref = oracle.qmv(int(DType.Q4_K), w, x, n_rows, n_cols)
+    assert guarded_rel_err(y, ref) <= REL_TOL
+
+
+def test_q4_0_kat_from_cpu_backend_tests(backend):
+    """yule-gpu/src/cpu.rs:991-1076: two rows of 32 weights that all dequantise to 1.0."""
+    w = np.zeros(36, np.uint8)
+    w[0:2] = (0x00, 0x3C)
+    w[2:18] = 0x99
+    w[18:20] = (0x00, 0x38)
+    w[20:36] = 0xAA
+    y = gpu_qmv(backend, DType.Q4_0, w, np.ones(32, np.float32), 2, 32)
+    assert abs(y[0] - 32.0) < 1e-4 and abs(y[1] - 32.0) < 1e-4
+
+
+def test_linearity_at_full_size(backend):
+    """Size-independent property at a large shape: W(ax + by) = a Wx + b Wy within fp32 noise."""
+    dtype, n_rows, n_cols = DType.Q4_K, 14336, 4096
+    w = synth.random_blocks(dtype, 21, n_rows * (n_cols // 256))
+    x1, x2 = synth.normal(1, n_cols), synth.normal(2, n_cols)
+    y1 = gpu_qmv(backend, dtype, w, x1, n_rows, n_cols)
+    y2 = gpu_qmv(backend, dtype, w, x2, n_rows, n_cols)
+    y3 = gpu_qmv(backend, dtype, w, (2 * x1 - 3 * x2).astype(np.float32), n_rows, n_cols)
+    assert guarded_rel_err(y3, 2 * y1.astype(np.float64) - 3 * y2.astype(np.float64)) <= REL_TOL
+
+
+def test_weight_offset_view(backend, oracle):
+    """A tensor that starts inside a larger buffer (row shard / ring slot)."""
+    dtype, n_rows, n_cols = DType.Q4_K, 64, 512
+    w = synth.random_blocks(dtype, 4, 3 * n_rows * 2)
+    x = synth.normal(8, n_cols)
+    per = n_rows * 2 * 144
+    wh, xh, oh = backend.upload(w), backend.upload(x), backend.allocate(n_rows * 4)
+    backend.quantized_matmul_at(wh, 2 * per, xh, oh, n_rows, n_cols, dtype)
+    y = backend.download(oh, n_rows)
+    ref = oracle.qmv(int(dtype), w[2 * per:], x, n_rows, n_cols)
+    assert guarded_rel_err(y, ref) <= REL_TOL
+    with pytest.raises(YuleGpuError):
+        backend.quantized_matmul_at(wh, 2 * per + 144, xh, oh, n_rows, n_cols, dtype)  # runs off the end
+    for h in (wh, xh, oh):
+        backend.free(h)
+
+
+def test_error_paths(backend):
+    w = backend.allocate(144 * 4)
+    x = backend.allocate(256 * 4)
+    o = backend.allocate(16)
+    with pytest.raises(YuleGpuError) as e:
+        backend.quantized_matmul(w, x, o, 4, 256, 13)  # Q5_K: unsupported dtype for CUDA qmv
+    assert "unsupported dtype" in str(e.value)
+    with pytest.raises(YuleGpuError):
+        backend.quantized_matmul(w, x, o, 4, 200, DType.Q4_K)  # not a block multiple
+    with pytest.raises(YuleGpuError):
+        backend.quantized_matmul(w, x, o, 5, 256, DType.Q4_K)  # weights too small
+    from yule_b200 import BufferHandle
+    with pytest.raises(YuleGpuError) as e:
+        backend.quantized_matmul(BufferHandle(987654), x, o, 4, 256, DType.Q4_K)
+    assert "unknown buffer" in str(e.value)
+    backend.quantized_matmul(w, x, o, 0, 256, DType.Q4_K)  # zero rows: nothing to do
+    for h in (w, x, o):
+        backend.free(h)

@@ -1,0 +1,618 @@
+// api.cu — context, buffer table and the trait-level entry points of libyule_cuda.so.
+//
+// Mirrors CudaBackend (yule-gpu/src/cuda/mod.rs:14-329) and CudaMemoryManager
+// (yule-gpu/src/cuda/memory.rs:10-154): opaque u64 handles, zero-filled allocations, byte-typed
+// copies, every op enqueued on one stream.  Unlike the reference there is no runtime nvcc and no
+// PTX cache (cuda/kernels.rs:145-186): the sm_100a kernels are compiled into this library.
+
+#include <cmath>
+#include <cstring>
+
+#include "internal.h"
+
+namespace yule {
+
+static thread_local char g_err[512] = "";
+
+int32_t fail(int32_t code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int32_t fail_cuda(cudaError_t e, const char *what) {
+    int32_t code = (e == cudaErrorMemoryAllocation) ? YULE_ERR_OUT_OF_MEMORY : YULE_ERR_CUDA;
+    return fail(code, "cuda: %s failed: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+}  // namespace yule
+
+using namespace yule;
+
+bool yule_cuda_ctx::find(yule_buffer h, Buffer *out, const char *what) {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = buffers.find(h);
+    if (it == buffers.end()) {
+        fail(YULE_ERR_UNKNOWN_BUFFER, "unknown buffer %llu (%s)", (unsigned long long)h, what);
+        return false;
+    }
+    *out = it->second;
+    return true;
+}
+
+#define CTX_GUARD(ctx)                                                        \
+    if (!(ctx)) return fail(YULE_ERR_INVALID_ARGUMENT, "null context");       \
+    YULE_CUDA_TRY(cudaSetDevice((ctx)->device))
+
+#define FIND(ctx, handle, var)  \
+    Buffer var;                 \
+    if (!(ctx)->find(handle, &var, #handle)) return YULE_ERR_UNKNOWN_BUFFER
+
+#define NEED_BYTES(buf, bytes, what)                                                              \
+    if ((size_t)(bytes) > (buf).size)                                                             \
+    return fail(YULE_ERR_OUT_OF_BOUNDS, "%s needs %zu bytes but buffer holds %zu", what,          \
+                (size_t)(bytes), (buf).size)
+
+#define LAUNCHED(ctx, call)                                   \
+    do {                                                      \
+        uint64_t _n = 0;                                      \
+        cudaError_t _e = (call);                              \
+        (ctx)->launches.fetch_add(_n);                        \
+        if (_e != cudaSuccess) return fail_cuda(_e, #call);   \
+    } while (0)
+
+extern "C" {
+
+const char *yule_cuda_last_error(void) { return g_err; }
+
+int32_t yule_cuda_is_available(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n > 0 ? 1 : 0;
+}
+
+int32_t yule_cuda_create(int32_t ordinal, yule_cuda_ctx **out_ctx) {
+    if (!out_ctx) return fail(YULE_ERR_INVALID_ARGUMENT, "null out_ctx");
+    *out_ctx = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(YULE_ERR_CUDA, "no CUDA device available (this backend has no CPU fallback)");
+    }
+    if (ordinal < 0 || ordinal >= n)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "device ordinal %d out of range (have %d)", ordinal, n);
+    YULE_CUDA_TRY(cudaSetDevice(ordinal));
+    auto *ctx = new yule_cuda_ctx();
+    ctx->device = ordinal;
+    e = cudaGetDeviceProperties(&ctx->prop, ordinal);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->device_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->device_status, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        delete ctx;
+        return fail_cuda(e, "context setup");
+    }
+    if (ctx->prop.major < 10) {
+        int major = ctx->prop.major, minor = ctx->prop.minor;
+        cudaStreamDestroy(ctx->stream);
+        cudaFree(ctx->device_status);
+        delete ctx;
+        return fail(YULE_ERR_CUDA, "device is sm_%d%d; this library carries sm_100a kernels only", major,
+                    minor);
+    }
+    *out_ctx = ctx;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
+    if (!ctx) return YULE_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto &kv : ctx->buffers) cudaFree(kv.second.ptr);
+    for (auto ev : ctx->events) cudaEventDestroy(ev);
+    for (auto &g : ctx->graphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+    if (ctx->device_status) cudaFree(ctx->device_status);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_device_info(yule_cuda_ctx *ctx, char *name_buf, size_t name_cap, uint64_t *memory_bytes,
+                              uint32_t *compute_units) {
+    CTX_GUARD(ctx);
+    if (name_buf && name_cap) {
+        strncpy(name_buf, ctx->prop.name, name_cap - 1);
+        name_buf[name_cap - 1] = 0;
+    }
+    if (memory_bytes) *memory_bytes = (uint64_t)ctx->prop.totalGlobalMem;
+    if (compute_units) *compute_units = (uint32_t)ctx->prop.multiProcessorCount;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_allocate(yule_cuda_ctx *ctx, size_t size_bytes, yule_buffer *out_handle) {
+    CTX_GUARD(ctx);
+    if (!out_handle) return fail(YULE_ERR_INVALID_ARGUMENT, "null out_handle");
+    Buffer b;
+    b.size = size_bytes;
+    // Rounded up so that a 16-byte vector load starting inside the buffer never leaves it.
+    b.capacity = ((size_bytes + 255) / 256) * 256 + 256;
+    cudaError_t e = cudaMalloc(&b.ptr, b.capacity);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(YULE_ERR_OUT_OF_MEMORY, "cuda allocation of %zu bytes failed: %s", size_bytes,
+                    cudaGetErrorString(e));
+    }
+    YULE_CUDA_TRY(cudaMemsetAsync(b.ptr, 0, b.capacity, ctx->stream));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    uint64_t h = ctx->next_handle++;
+    ctx->buffers[h] = b;
+    *out_handle = h;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_free(yule_cuda_ctx *ctx, yule_buffer handle) {
+    CTX_GUARD(ctx);
+    Buffer b;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        auto it = ctx->buffers.find(handle);
+        if (it == ctx->buffers.end())
+            return fail(YULE_ERR_UNKNOWN_BUFFER, "unknown buffer %llu (free)", (unsigned long long)handle);
+        b = it->second;
+        ctx->buffers.erase(it);
+    }
+    // Work already enqueued may still read the buffer.
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    YULE_CUDA_TRY(cudaFree(b.ptr));
+    return YULE_OK;
+}
+
+static bool is_pinned_host(const void *p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeHost;
+}
+
+int32_t yule_cuda_copy_to_device(yule_cuda_ctx *ctx, const void *data, size_t len, yule_buffer dst) {
+    CTX_GUARD(ctx);
+    FIND(ctx, dst, d);
+    if (len && !data) return fail(YULE_ERR_INVALID_ARGUMENT, "null data");
+    size_t n = len < d.size ? len : d.size;
+    if (n == 0) return YULE_OK;
+    YULE_CUDA_TRY(cudaMemcpyAsync(d.ptr, data, n, cudaMemcpyHostToDevice, ctx->stream));
+    // A pageable source has been staged when the call returns; a pinned one has not, and the
+    // caller's slice is only borrowed for the duration of this call.
+    if (is_pinned_host(data)) YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_copy_from_device(yule_cuda_ctx *ctx, yule_buffer src, void *data, size_t len) {
+    CTX_GUARD(ctx);
+    FIND(ctx, src, s);
+    if (len && !data) return fail(YULE_ERR_INVALID_ARGUMENT, "null data");
+    size_t n = len < s.size ? len : s.size;
+    if (n) YULE_CUDA_TRY(cudaMemcpyAsync(data, s.ptr, n, cudaMemcpyDeviceToHost, ctx->stream));
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_copy_buffer_offset(yule_cuda_ctx *ctx, yule_buffer src, yule_buffer dst, size_t src_offset,
+                                     size_t dst_offset, size_t size) {
+    CTX_GUARD(ctx);
+    FIND(ctx, src, s);
+    FIND(ctx, dst, d);
+    if (src_offset > s.size || size > s.size - src_offset)
+        return fail(YULE_ERR_OUT_OF_BOUNDS, "copy reads [%zu, %zu) of a %zu-byte buffer", src_offset,
+                    src_offset + size, s.size);
+    if (dst_offset > d.size || size > d.size - dst_offset)
+        return fail(YULE_ERR_OUT_OF_BOUNDS, "copy writes [%zu, %zu) of a %zu-byte buffer", dst_offset,
+                    dst_offset + size, d.size);
+    if (size == 0) return YULE_OK;
+    YULE_CUDA_TRY(cudaMemcpyAsync((char *)d.ptr + dst_offset, (const char *)s.ptr + src_offset, size,
+                                  cudaMemcpyDeviceToDevice, ctx->stream));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_copy_buffer(yule_cuda_ctx *ctx, yule_buffer src, yule_buffer dst, size_t size) {
+    return yule_cuda_copy_buffer_offset(ctx, src, dst, 0, 0, size);
+}
+
+int32_t yule_cuda_synchronize(yule_cuda_ctx *ctx) {
+    CTX_GUARD(ctx);
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    int status = 0;
+    YULE_CUDA_TRY(cudaMemcpy(&status, ctx->device_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        cudaMemset(ctx->device_status, 0, sizeof(int));
+        return fail(YULE_ERR_DEVICE_STATUS, "a device-side bounded wait gave up (status word %d)", status);
+    }
+    return YULE_OK;
+}
+
+// ── compute ────────────────────────────────────────────────────────────────────────────────
+
+int32_t yule_cuda_matmul(yule_cuda_ctx *ctx, yule_buffer a, yule_buffer b, yule_buffer out, uint32_t m,
+                         uint32_t n, uint32_t k) {
+    (void)n;
+    CTX_GUARD(ctx);
+    FIND(ctx, a, A);
+    FIND(ctx, b, B);
+    FIND(ctx, out, O);
+    NEED_BYTES(A, (size_t)m * k * 4, "matmul a");
+    NEED_BYTES(B, (size_t)k * 4, "matmul b");
+    NEED_BYTES(O, (size_t)m * 4, "matmul out");
+    if (m == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_matvec_f32((const float *)A.ptr, (const float *)B.ptr, (float *)O.ptr, m, k,
+                                    ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_softmax(yule_cuda_ctx *ctx, yule_buffer input, yule_buffer output, uint32_t size) {
+    CTX_GUARD(ctx);
+    FIND(ctx, input, I);
+    FIND(ctx, output, O);
+    NEED_BYTES(I, (size_t)size * 4, "softmax input");
+    NEED_BYTES(O, (size_t)size * 4, "softmax output");
+    if (size == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_softmax((const float *)I.ptr, (float *)O.ptr, size, ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_rms_norm(yule_cuda_ctx *ctx, yule_buffer input, yule_buffer weight, yule_buffer output,
+                           uint32_t size, float eps) {
+    CTX_GUARD(ctx);
+    FIND(ctx, input, I);
+    FIND(ctx, weight, W);
+    FIND(ctx, output, O);
+    NEED_BYTES(I, (size_t)size * 4, "rms_norm input");
+    NEED_BYTES(W, (size_t)size * 4, "rms_norm weight");
+    NEED_BYTES(O, (size_t)size * 4, "rms_norm output");
+    if (size == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_rms_norm((const float *)I.ptr, (const float *)W.ptr, (float *)O.ptr, size, eps,
+                                  ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_rope(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k, uint32_t pos, uint32_t head_dim,
+                       float freq_base, uint32_t n_heads_q, uint32_t n_heads_k) {
+    CTX_GUARD(ctx);
+    FIND(ctx, q, Q);
+    FIND(ctx, k, K);
+    if (head_dim == 0 || head_dim % 2 || head_dim > 256)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "rope head_dim %u must be even and at most 256", head_dim);
+    NEED_BYTES(Q, (size_t)n_heads_q * head_dim * 4, "rope q");
+    NEED_BYTES(K, (size_t)n_heads_k * head_dim * 4, "rope k");
+    // Angles are evaluated on the host in f32 with the platform libm — the recipe of the CPU
+    // runner's RopeTable (yule-infer/src/model_runner.rs:78-99) — so the rotation matches it bit
+    // for bit; device powf/sinf/cosf differ from libm in the last place.
+    RopeAngles ang;
+    uint32_t half = head_dim / 2;
+    for (uint32_t i = 0; i < half; i++) {
+        float freq = 1.0f / powf(freq_base, 2.0f * (float)i / (float)head_dim);
+        float theta = (float)pos * freq;
+        ang.cos[i] = cosf(theta);
+        ang.sin[i] = sinf(theta);
+    }
+    LAUNCHED(ctx, launch_rope_angles((float *)Q.ptr, (float *)K.ptr, head_dim, n_heads_q, n_heads_k, ang,
+                                     ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_silu(yule_cuda_ctx *ctx, yule_buffer input, yule_buffer output, uint32_t size) {
+    CTX_GUARD(ctx);
+    FIND(ctx, input, I);
+    FIND(ctx, output, O);
+    NEED_BYTES(I, (size_t)size * 4, "silu input");
+    NEED_BYTES(O, (size_t)size * 4, "silu output");
+    if (size == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_silu_mul((const float *)I.ptr, (const float *)O.ptr, (float *)O.ptr, size,
+                                  ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_element_mul(yule_cuda_ctx *ctx, yule_buffer a, yule_buffer b, yule_buffer output,
+                              uint32_t size) {
+    CTX_GUARD(ctx);
+    FIND(ctx, a, A);
+    FIND(ctx, b, B);
+    FIND(ctx, output, O);
+    NEED_BYTES(A, (size_t)size * 4, "element_mul a");
+    NEED_BYTES(B, (size_t)size * 4, "element_mul b");
+    NEED_BYTES(O, (size_t)size * 4, "element_mul output");
+    if (size == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_silu_mul((const float *)A.ptr, (const float *)B.ptr, (float *)O.ptr, size,
+                                  ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_add(yule_cuda_ctx *ctx, yule_buffer a, yule_buffer b, yule_buffer output, uint32_t size) {
+    CTX_GUARD(ctx);
+    FIND(ctx, a, A);
+    FIND(ctx, b, B);
+    FIND(ctx, output, O);
+    NEED_BYTES(A, (size_t)size * 4, "add a");
+    NEED_BYTES(B, (size_t)size * 4, "add b");
+    NEED_BYTES(O, (size_t)size * 4, "add output");
+    if (size == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_add((const float *)A.ptr, (const float *)B.ptr, (float *)O.ptr, size, ctx->stream,
+                             &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_attn_score(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k_cache, yule_buffer scores,
+                             uint32_t head_dim, uint32_t seq_len, uint32_t head_offset, uint32_t kv_offset,
+                             uint32_t kv_stride) {
+    CTX_GUARD(ctx);
+    FIND(ctx, q, Q);
+    FIND(ctx, k_cache, K);
+    FIND(ctx, scores, S);
+    if (seq_len == 0) return YULE_OK;
+    NEED_BYTES(Q, ((size_t)head_offset + head_dim) * 4, "attn_score q");
+    NEED_BYTES(K, ((size_t)(seq_len - 1) * kv_stride + kv_offset + head_dim) * 4, "attn_score k_cache");
+    NEED_BYTES(S, (size_t)seq_len * 4, "attn_score scores");
+    LAUNCHED(ctx, launch_attn_score((const float *)Q.ptr, (const float *)K.ptr, (float *)S.ptr, head_dim,
+                                    seq_len, head_offset, kv_offset, kv_stride, ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffer v_cache, yule_buffer output,
+                             uint32_t head_dim, uint32_t seq_len, uint32_t kv_offset, uint32_t kv_stride,
+                             uint32_t out_offset) {
+    CTX_GUARD(ctx);
+    FIND(ctx, weights, W);
+    FIND(ctx, v_cache, V);
+    FIND(ctx, output, O);
+    NEED_BYTES(W, (size_t)seq_len * 4, "attn_value weights");
+    if (seq_len)
+        NEED_BYTES(V, ((size_t)(seq_len - 1) * kv_stride + kv_offset + head_dim) * 4, "attn_value v_cache");
+    NEED_BYTES(O, ((size_t)out_offset + head_dim) * 4, "attn_value output");
+    if (head_dim == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_attn_value((const float *)W.ptr, (const float *)V.ptr, (float *)O.ptr, head_dim,
+                                    seq_len, kv_offset, kv_stride, out_offset, ctx->stream, &_n));
+    return YULE_OK;
+}
+
+static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset, yule_buffer input,
+                          yule_buffer output, uint32_t n_rows, uint32_t n_cols, uint32_t type, uint32_t batch,
+                          uint32_t x_stride, uint32_t out_stride) {
+    CTX_GUARD(ctx);
+    if (!is_quantized(type))
+        return fail(YULE_ERR_UNSUPPORTED_DTYPE, "unsupported dtype for CUDA qmv: GGUF type %u", type);
+    uint32_t bs = block_size(type);
+    if (n_cols == 0 || n_cols % bs)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "n_cols %u is not a multiple of the block size %u", n_cols, bs);
+    if (batch == 0 || x_stride < n_cols || out_stride < n_rows || x_stride % 4)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "bad batch/stride (batch %u, x_stride %u, out_stride %u)", batch,
+                    x_stride, out_stride);
+    uint32_t align = (type == YULE_DTYPE_Q4_K) ? 16 : 2;
+    if (weight_offset % align)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "weight offset %zu is not a multiple of %u", weight_offset, align);
+    FIND(ctx, weights, W);
+    FIND(ctx, input, X);
+    FIND(ctx, output, O);
+    size_t wbytes = tensor_bytes(type, n_rows, n_cols);
+    if (weight_offset > W.size || wbytes > W.size - weight_offset)
+        return fail(YULE_ERR_OUT_OF_BOUNDS, "quantized_matmul weights need [%zu, %zu) of a %zu-byte buffer",
+                    weight_offset, weight_offset + wbytes, W.size);
+    NEED_BYTES(X, ((size_t)(batch - 1) * x_stride + n_cols) * 4, "quantized_matmul input");
+    NEED_BYTES(O, ((size_t)(batch - 1) * out_stride + n_rows) * 4, "quantized_matmul output");
+    if (n_rows == 0) return YULE_OK;
+    QmvArgs a;
+    a.w = (const uint8_t *)W.ptr + weight_offset;
+    a.x = (const float *)X.ptr;
+    a.out = (float *)O.ptr;
+    a.n_rows = n_rows;
+    a.n_cols = n_cols;
+    a.type = type;
+    a.batch = batch;
+    a.x_stride = x_stride;
+    a.out_stride = out_stride;
+    LAUNCHED(ctx, launch_qmv(a, ctx->prop.multiProcessorCount, ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_quantized_matmul(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffer input,
+                                   yule_buffer output, uint32_t n_rows, uint32_t n_cols, uint32_t gguf_type) {
+    return qmv_common(ctx, weights, 0, input, output, n_rows, n_cols, gguf_type, 1, n_cols, n_rows);
+}
+
+int32_t yule_cuda_quantized_matmul_at(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset,
+                                      yule_buffer input, yule_buffer output, uint32_t n_rows, uint32_t n_cols,
+                                      uint32_t gguf_type) {
+    return qmv_common(ctx, weights, weight_offset, input, output, n_rows, n_cols, gguf_type, 1, n_cols, n_rows);
+}
+
+int32_t yule_cuda_quantized_matmul_batched(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffer input,
+                                           yule_buffer output, uint32_t n_rows, uint32_t n_cols,
+                                           uint32_t gguf_type, uint32_t batch, uint32_t x_stride,
+                                           uint32_t out_stride) {
+    return qmv_common(ctx, weights, 0, input, output, n_rows, n_cols, gguf_type, batch, x_stride, out_stride);
+}
+
+int32_t yule_cuda_dequantize(yule_cuda_ctx *ctx, yule_buffer weights, uint32_t gguf_type, uint64_t n_blocks,
+                             yule_buffer out_f32) {
+    CTX_GUARD(ctx);
+    if (!is_quantized(gguf_type) && gguf_type != YULE_DTYPE_F16 && gguf_type != YULE_DTYPE_F32)
+        return fail(YULE_ERR_UNSUPPORTED_DTYPE, "dequant not implemented for GGUF type %u", gguf_type);
+    FIND(ctx, weights, W);
+    FIND(ctx, out_f32, O);
+    NEED_BYTES(W, n_blocks * block_bytes(gguf_type), "dequantize weights");
+    NEED_BYTES(O, n_blocks * block_size(gguf_type) * 4, "dequantize output");
+    if (n_blocks == 0) return YULE_OK;
+    LAUNCHED(ctx, launch_dequantize((const uint8_t *)W.ptr, gguf_type, n_blocks, (float *)O.ptr, ctx->stream,
+                                    &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_multihead_attention(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k_cache, yule_buffer v_cache,
+                                      yule_buffer out, uint32_t head_dim, uint32_t seq_len, uint32_t n_heads,
+                                      uint32_t n_kv_heads, uint32_t kv_stride) {
+    CTX_GUARD(ctx);
+    if (n_kv_heads == 0 || n_heads == 0 || n_heads % n_kv_heads || head_dim == 0 || seq_len == 0)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "bad attention shape (heads %u, kv heads %u, head_dim %u, seq %u)",
+                    n_heads, n_kv_heads, head_dim, seq_len);
+    if (head_dim > 256) return fail(YULE_ERR_INVALID_ARGUMENT, "head_dim %u above 256", head_dim);
+    FIND(ctx, q, Q);
+    FIND(ctx, k_cache, K);
+    FIND(ctx, v_cache, V);
+    FIND(ctx, out, O);
+    size_t kv_need = ((size_t)(seq_len - 1) * kv_stride + (size_t)n_kv_heads * head_dim) * 4;
+    NEED_BYTES(Q, (size_t)n_heads * head_dim * 4, "attention q");
+    NEED_BYTES(K, kv_need, "attention k_cache");
+    NEED_BYTES(V, kv_need, "attention v_cache");
+    NEED_BYTES(O, (size_t)n_heads * head_dim * 4, "attention out");
+    LAUNCHED(ctx, launch_multihead_attention((const float *)Q.ptr, (const float *)K.ptr, (const float *)V.ptr,
+                                             (float *)O.ptr, head_dim, seq_len, nullptr, seq_len, n_heads,
+                                             n_kv_heads, kv_stride, ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_embed_gather(yule_cuda_ctx *ctx, yule_buffer table, uint32_t gguf_type, uint32_t dim,
+                               uint32_t token, yule_buffer out) {
+    CTX_GUARD(ctx);
+    uint32_t bs = block_size(gguf_type);
+    if (bs == 0) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "embedding dtype %u not supported", gguf_type);
+    if (dim == 0 || dim % bs) return fail(YULE_ERR_INVALID_ARGUMENT, "dim %u not a multiple of block size %u", dim, bs);
+    FIND(ctx, table, T);
+    FIND(ctx, out, O);
+    size_t row_bytes = (size_t)(dim / bs) * block_bytes(gguf_type);
+    NEED_BYTES(T, ((size_t)token + 1) * row_bytes, "embedding table");
+    NEED_BYTES(O, (size_t)dim * 4, "embedding out");
+    LAUNCHED(ctx, launch_embed_gather((const uint8_t *)T.ptr, gguf_type, dim, token, nullptr, (float *)O.ptr,
+                                      ctx->stream, &_n));
+    return YULE_OK;
+}
+
+// ── graph capture / replay ─────────────────────────────────────────────────────────────────
+
+int32_t yule_cuda_graph_begin(yule_cuda_ctx *ctx) {
+    CTX_GUARD(ctx);
+    if (ctx->capturing) return fail(YULE_ERR_INVALID_ARGUMENT, "graph capture already in progress");
+    YULE_CUDA_TRY(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    ctx->capturing = true;
+    ctx->launches_at_capture_begin = ctx->launches.load();
+    return YULE_OK;
+}
+
+int32_t yule_cuda_graph_end(yule_cuda_ctx *ctx, uint32_t *out_graph_id) {
+    CTX_GUARD(ctx);
+    if (!ctx->capturing) return fail(YULE_ERR_INVALID_ARGUMENT, "no graph capture in progress");
+    ctx->capturing = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    // Captured launches did not run; they count each time the graph is replayed.
+    uint64_t captured = ctx->launches.load() - ctx->launches_at_capture_begin;
+    ctx->launches.fetch_sub(captured);
+    if (e != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        return fail_cuda(e, "cudaStreamEndCapture");
+    }
+    if (!out_graph_id) {
+        cudaGraphDestroy(graph);
+        return fail(YULE_ERR_INVALID_ARGUMENT, "null out_graph_id");
+    }
+    yule_cuda_ctx::Graph g;
+    e = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGraphInstantiate");
+    g.kernels = captured;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->graphs.push_back(g);
+    *out_graph_id = (uint32_t)ctx->graphs.size() - 1;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_graph_launch(yule_cuda_ctx *ctx, uint32_t graph_id) {
+    CTX_GUARD(ctx);
+    yule_cuda_ctx::Graph g;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (graph_id >= ctx->graphs.size() || !ctx->graphs[graph_id].exec)
+            return fail(YULE_ERR_INVALID_ARGUMENT, "unknown graph %u", graph_id);
+        g = ctx->graphs[graph_id];
+    }
+    YULE_CUDA_TRY(cudaGraphLaunch(g.exec, ctx->stream));
+    ctx->launches.fetch_add(g.kernels);
+    return YULE_OK;
+}
+
+int32_t yule_cuda_graph_destroy(yule_cuda_ctx *ctx, uint32_t graph_id) {
+    CTX_GUARD(ctx);
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (graph_id >= ctx->graphs.size() || !ctx->graphs[graph_id].exec)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "unknown graph %u", graph_id);
+    cudaGraphExecDestroy(ctx->graphs[graph_id].exec);
+    ctx->graphs[graph_id].exec = nullptr;
+    return YULE_OK;
+}
+
+// ── timing helpers ─────────────────────────────────────────────────────────────────────────
+
+int32_t yule_cuda_event_record(yule_cuda_ctx *ctx, uint32_t *out_event_id) {
+    CTX_GUARD(ctx);
+    if (!out_event_id) return fail(YULE_ERR_INVALID_ARGUMENT, "null out_event_id");
+    cudaEvent_t ev;
+    YULE_CUDA_TRY(cudaEventCreate(&ev));
+    YULE_CUDA_TRY(cudaEventRecord(ev, ctx->stream));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->events.push_back(ev);
+    *out_event_id = (uint32_t)ctx->events.size() - 1;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_event_elapsed_ms(yule_cuda_ctx *ctx, uint32_t start_id, uint32_t end_id, float *out_ms) {
+    CTX_GUARD(ctx);
+    cudaEvent_t a, b;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (start_id >= ctx->events.size() || end_id >= ctx->events.size())
+            return fail(YULE_ERR_INVALID_ARGUMENT, "unknown event id");
+        a = ctx->events[start_id];
+        b = ctx->events[end_id];
+    }
+    YULE_CUDA_TRY(cudaEventSynchronize(b));
+    YULE_CUDA_TRY(cudaEventElapsedTime(out_ms, a, b));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_event_reset(yule_cuda_ctx *ctx) {
+    CTX_GUARD(ctx);
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    for (auto ev : ctx->events) cudaEventDestroy(ev);
+    ctx->events.clear();
+    return YULE_OK;
+}
+
+int32_t yule_cuda_flush_l2(yule_cuda_ctx *ctx) {
+    CTX_GUARD(ctx);
+    if (!ctx->flush_buf) {
+        // Twice the L2 size, so that nothing of an earlier kernel's inputs survives.
+        size_t bytes = (size_t)ctx->prop.l2CacheSize * 2;
+        if (bytes < ((size_t)256 << 20)) bytes = (size_t)256 << 20;
+        YULE_CUDA_TRY(cudaMalloc(&ctx->flush_buf, bytes));
+        ctx->flush_bytes = bytes;
+    }
+    LAUNCHED(ctx, launch_fill_bytes(ctx->flush_buf, ctx->flush_bytes, 0, ctx->stream, &_n));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_launch_count(yule_cuda_ctx *ctx, uint64_t *out_count) {
+    if (!ctx || !out_count) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    *out_count = ctx->launches.load();
+    return YULE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,148 @@
+// internal.h — shared declarations of libyule_cuda.so (context, buffer table, kernel launchers).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/yule_cuda.h"
+
+namespace yule {
+
+struct Buffer {
+    void *ptr = nullptr;
+    size_t size = 0;      // bytes the caller asked for
+    size_t capacity = 0;  // bytes allocated (rounded up, so 16-byte over-reads stay in bounds)
+};
+
+// Sets the calling thread's error text and returns `code`.
+int32_t fail(int32_t code, const char *fmt, ...);
+int32_t fail_cuda(cudaError_t e, const char *what);
+
+#define YULE_CUDA_TRY(expr)                                   \
+    do {                                                      \
+        cudaError_t _e = (expr);                              \
+        if (_e != cudaSuccess) return fail_cuda(_e, #expr);   \
+    } while (0)
+
+}  // namespace yule
+
+struct yule_cuda_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaDeviceProp prop{};
+    std::mutex mu;
+    std::unordered_map<uint64_t, yule::Buffer> buffers;
+    uint64_t next_handle = 1;
+    std::vector<cudaEvent_t> events;
+    struct Graph {
+        cudaGraphExec_t exec = nullptr;
+        uint64_t kernels = 0;
+    };
+    std::vector<Graph> graphs;
+    bool capturing = false;
+    uint64_t launches_at_capture_begin = 0;
+    void *flush_buf = nullptr;
+    size_t flush_bytes = 0;
+    std::atomic<uint64_t> launches{0};
+    // Word the kernels with bounded waits write when they give up; read by synchronize.
+    int *device_status = nullptr;
+
+    // Looks a handle up under the lock; returns false (and sets the error) when unknown.
+    bool find(yule_buffer h, yule::Buffer *out, const char *what);
+};
+
+namespace yule {
+
+inline bool is_quantized(uint32_t t) {
+    return t == YULE_DTYPE_Q4_0 || t == YULE_DTYPE_Q8_0 || t == YULE_DTYPE_Q4_K || t == YULE_DTYPE_Q6_K;
+}
+inline uint32_t block_size(uint32_t t) {  // yule-core/src/dtype.rs:99-118
+    switch (t) {
+        case YULE_DTYPE_F32: case YULE_DTYPE_F16: return 1;
+        case YULE_DTYPE_Q4_0: case YULE_DTYPE_Q8_0: return 32;
+        case YULE_DTYPE_Q4_K: case YULE_DTYPE_Q6_K: return 256;
+        default: return 0;
+    }
+}
+inline uint32_t block_bytes(uint32_t t) {  // yule-core/src/dtype.rs:62-96
+    switch (t) {
+        case YULE_DTYPE_F32: return 4;
+        case YULE_DTYPE_F16: return 2;
+        case YULE_DTYPE_Q4_0: return 18;
+        case YULE_DTYPE_Q8_0: return 34;
+        case YULE_DTYPE_Q4_K: return 144;
+        case YULE_DTYPE_Q6_K: return 210;
+        default: return 0;
+    }
+}
+inline size_t tensor_bytes(uint32_t t, uint64_t n_rows, uint64_t n_cols) {
+    return (size_t)(n_rows * (n_cols / block_size(t)) * block_bytes(t));
+}
+
+// ── kernel launchers (raw device pointers; arguments already validated) ──────────────────────
+// Each returns the cudaError_t of the launch and adds the kernels it launched to *launches.
+
+struct QmvArgs {
+    const uint8_t *w;   // raw GGUF blocks, row-major
+    const float *x;     // [batch][x_stride]
+    float *out;         // [batch][out_stride]
+    uint32_t n_rows, n_cols, type, batch, x_stride, out_stride;
+    // Optional fused prologue/epilogue used by the runner (null when unused):
+    const float *residual = nullptr;  // out[row] = residual[row] + dot   (o-proj / down-proj)
+};
+cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
+
+cudaError_t launch_dequantize(const uint8_t *w, uint32_t type, uint64_t n_blocks, float *out,
+                              cudaStream_t s, uint64_t *launches);
+// Row `*token_ptr` (device) or `token` (when token_ptr is null) of a [vocab][dim] table.
+cudaError_t launch_embed_gather(const uint8_t *table, uint32_t type, uint32_t dim, uint32_t token,
+                                const uint32_t *token_ptr, float *out, cudaStream_t s,
+                                uint64_t *launches);
+
+cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k,
+                              cudaStream_t s, uint64_t *launches);
+cudaError_t launch_softmax(const float *in, float *out, uint32_t n, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_rms_norm(const float *in, const float *w, float *out, uint32_t n, float eps,
+                            cudaStream_t s, uint64_t *launches);
+// cos/sin hold head_dim/2 entries for this position (host-computed), passed by value.
+struct RopeAngles {
+    float cos[128];
+    float sin[128];
+};
+cudaError_t launch_rope_angles(float *q, float *k, uint32_t head_dim, uint32_t n_heads_q,
+                               uint32_t n_heads_k, const RopeAngles &ang, cudaStream_t s,
+                               uint64_t *launches);
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t s,
+                            uint64_t *launches);
+cudaError_t launch_add(const float *a, const float *b, float *out, uint32_t n, cudaStream_t s,
+                       uint64_t *launches);
+cudaError_t launch_attn_score(const float *q, const float *k_cache, float *scores, uint32_t hd,
+                              uint32_t seq_len, uint32_t head_offset, uint32_t kv_offset,
+                              uint32_t kv_stride, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_attn_value(const float *w, const float *v_cache, float *out, uint32_t hd,
+                              uint32_t seq_len, uint32_t kv_offset, uint32_t kv_stride,
+                              uint32_t out_offset, cudaStream_t s, uint64_t *launches);
+// seq_len_ptr (device, value = position; attends to position+1 entries) overrides seq_len when set.
+cudaError_t launch_multihead_attention(const float *q, const float *k_cache, const float *v_cache,
+                                       float *out, uint32_t hd, uint32_t seq_len,
+                                       const uint32_t *pos_ptr, uint32_t max_seq_len, uint32_t n_heads,
+                                       uint32_t n_kv_heads, uint32_t kv_stride, cudaStream_t s,
+                                       uint64_t *launches);
+// Runner kernels that read the position from device memory (graph-replayable).
+cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tmp, float *k_cache,
+                                 float *v_cache, const float *cos_table, const float *sin_table,
+                                 const uint32_t *pos_ptr, uint32_t head_dim, uint32_t n_heads,
+                                 uint32_t n_kv_heads, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *out_token, uint32_t *pos_ptr_to_bump,
+                          cudaStream_t s, uint64_t *launches);
+cudaError_t launch_fill_bytes(void *p, size_t n, int value, cudaStream_t s, uint64_t *launches);
+
+}  // namespace yule

@@ -1,0 +1,536 @@
+// qmv.cu — fused dequantise + dot matvec kernels over raw GGUF blocks, plus the standalone
+// dequantiser and the embedding-row gather.
+//
+// Arithmetic contract (what the CPU code being replaced computes):
+//   Q4_K  yule-core/src/dequant.rs:929-972   sum += (d*sc)*Σ q·x − (dmin*mn)*Σ x   per 32-column sub-block
+//   Q6_K  yule-core/src/dequant.rs:976-1009  sum += d*sc*(q−32)*x                  per weight, 16-column scales
+//   Q4_0  yule-core/src/dequant.rs:902-913   (Σ (nib−8)·x)*d, nibble i in byte i/2 (even=low, odd=high)
+//   Q8_0  yule-core/src/dequant.rs:916-926   (Σ q·x)*d
+// All accumulation is fp32; integer fields are turned into floats exactly (bit-spliced into a
+// float or half whose value is 2^k + n, then one exact subtraction), never rounded.
+//
+// Data layout: weights stay exactly as in the GGUF file — row-major blocks, row r at byte
+// r * (n_cols/block_size) * block_bytes.  The activation vector(s) are staged once per CTA into
+// shared memory together with per-32-column sums (the Σx that every row of a Q4_K matrix shares).
+
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace yule {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t bits) {
+    // cvt.f32.f16 is exact for every finite half, subnormals included.
+    return __half2float(__ushort_as_half((unsigned short)bits));
+}
+
+// Streaming 128-bit load: weights are read exactly once, so keep them out of L1.
+__device__ __forceinline__ uint4 ld_stream_u4(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u16(const uint8_t *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u8(const uint8_t *p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// byte `i` (0..11) of the 12 packed scale bytes held in three little-endian words.
+__device__ __forceinline__ uint32_t scale_byte(uint32_t a, uint32_t b, uint32_t c, int i) {
+    uint32_t w = (i < 4) ? a : ((i < 8) ? b : c);
+    return (w >> (8 * (i & 3))) & 0xFFu;
+}
+// yule-core/src/dequant.rs:176-190 for one sub-block index s.
+__device__ __forceinline__ void q4k_scale_min(uint32_t a, uint32_t b, uint32_t c, int s, uint32_t *sc,
+                                              uint32_t *mn) {
+    if (s < 4) {
+        *sc = scale_byte(a, b, c, s) & 63u;
+        *mn = scale_byte(a, b, c, s + 4) & 63u;
+    } else {
+        uint32_t hi = scale_byte(a, b, c, s + 4);
+        *sc = (hi & 0xFu) | ((scale_byte(a, b, c, s - 4) >> 6) << 4);
+        *mn = (hi >> 4) | ((scale_byte(a, b, c, s) >> 6) << 4);
+    }
+}
+
+// Eight nibbles of one word → exact floats.  Low nibble of byte i → lo[i], high nibble → hi[i].
+// (n | 0x6400) read as a half is 1024+n; (16n | 0x6400) is 1024+16n; one exact half op removes
+// the offset.
+__device__ __forceinline__ void nibbles_to_float(uint32_t w, float lo[4], float hi[4]) {
+    const uint32_t magic = 0x64006400u;
+    uint32_t w8 = w >> 8;
+    uint32_t l02 = (w & 0x000F000Fu) | magic, l13 = (w8 & 0x000F000Fu) | magic;
+    uint32_t h02 = (w & 0x00F000F0u) | magic, h13 = (w8 & 0x00F000F0u) | magic;
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+    const __half2 k16th = __float2half2_rn(0.0625f);
+    const __half2 k64 = __float2half2_rn(-64.0f);
+    float2 a = __half22float2(__hsub2(*reinterpret_cast<__half2 *>(&l02), k1024));
+    float2 b = __half22float2(__hsub2(*reinterpret_cast<__half2 *>(&l13), k1024));
+    float2 c = __half22float2(__hfma2(*reinterpret_cast<__half2 *>(&h02), k16th, k64));
+    float2 d = __half22float2(__hfma2(*reinterpret_cast<__half2 *>(&h13), k16th, k64));
+    lo[0] = a.x; lo[2] = a.y; lo[1] = b.x; lo[3] = b.y;
+    hi[0] = c.x; hi[2] = c.y; hi[1] = d.x; hi[3] = d.y;
+}
+
+// Byte k of `v` (0..255) minus `offset` as an exact float: splice the byte into the mantissa of
+// 2^23, subtract 2^23 + offset.
+template <int K>
+__device__ __forceinline__ float byte_to_float(uint32_t v, float two23_plus_offset) {
+    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440 | K)) - two23_plus_offset;
+}
+
+// ── activation staging ──────────────────────────────────────────────────────────────────────
+// xs: NB vectors of n_cols floats, optionally padded by 4 floats per 32 (PAD) so that lanes
+// that each own one 32-column block hit distinct banks; xsum: NB × n_cols/32 sums.
+template <int NB, bool PAD>
+__device__ __forceinline__ void stage_x(const float *__restrict__ x, uint32_t x_stride, uint32_t n_cols,
+                                        float *xs, float *xsum, bool want_sums) {
+    const uint32_t vstride = PAD ? (n_cols / 32) * 36 : n_cols;
+    for (uint32_t i = threadIdx.x * 4; i < n_cols; i += blockDim.x * 4) {
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            float4 v = *reinterpret_cast<const float4 *>(x + (size_t)b * x_stride + i);
+            uint32_t o = PAD ? (i / 32) * 36 + (i % 32) : i;
+            *reinterpret_cast<float4 *>(xs + b * vstride + o) = v;
+        }
+    }
+    __syncthreads();
+    if (want_sums) {
+        const uint32_t n_sb = n_cols / 32;
+        for (uint32_t s = threadIdx.x; s < n_sb * NB; s += blockDim.x) {
+            uint32_t b = s / n_sb, sb = s % n_sb;
+            const float *p = xs + b * vstride + (PAD ? sb * 36 : sb * 32);
+            float acc = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < 32; i++) acc += p[i];
+            xsum[s] = acc;
+        }
+        __syncthreads();
+    }
+}
+
+// ── Q4_K ────────────────────────────────────────────────────────────────────────────────────
+// Eight lanes share one 144-byte super-block: every lane reads the 16-byte header (one
+// broadcast transaction) and one 16-byte slice of qs — 16 low-nibble columns and the 16
+// high-nibble columns 32 further on.  A warp covers four consecutive super-blocks (576
+// contiguous bytes) per step and walks one row; rows are dealt round-robin to warps.
+template <int NB>
+__global__ void __launch_bounds__(kThreads)
+qmv_q4k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+               uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
+               const float *__restrict__ residual) {
+    extern __shared__ __align__(16) float smem[];
+    float *xs = smem;
+    float *xsum = smem + (size_t)NB * n_cols;
+    stage_x<NB, false>(x, x_stride, n_cols, xs, xsum, true);
+
+    const uint32_t bpr = n_cols / 256;
+    const uint32_t n_sb = n_cols / 32;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane >> 3;  // which of the 4 super-blocks of this step
+    const int j = lane & 7;     // which 16-byte slice of qs
+    const int g = j >> 1;       // group of 64 columns
+    const uint32_t warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t n_warps = gridDim.x * kWarps;
+
+    for (uint32_t row = warp; row < n_rows; row += n_warps) {
+        const uint4 *rowp = reinterpret_cast<const uint4 *>(w + (size_t)row * bpr * 144);
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.f;
+
+        for (uint32_t blk0 = 0; blk0 < bpr; blk0 += 4) {
+            const uint32_t blk = blk0 + sub;
+            if (blk < bpr) {
+                const uint4 *bp = rowp + (size_t)blk * 9;
+                const uint4 hdr = __ldg(bp);
+                const uint4 q = ld_stream_u4(bp + 1 + j);
+                const float d = f16_bits_to_f32(hdr.x & 0xFFFFu);
+                const float dmin = f16_bits_to_f32(hdr.x >> 16);
+                uint32_t sc0, mn0, sc1, mn1;
+                q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * g, &sc0, &mn0);
+                q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * g + 1, &sc1, &mn1);
+                const float s0 = d * (float)sc0, s1 = d * (float)sc1;
+                const float m0 = dmin * (float)mn0, m1 = dmin * (float)mn1;
+
+                float lo[16], hi[16];
+                nibbles_to_float(q.x, lo + 0, hi + 0);
+                nibbles_to_float(q.y, lo + 4, hi + 4);
+                nibbles_to_float(q.z, lo + 8, hi + 8);
+                nibbles_to_float(q.w, lo + 12, hi + 12);
+
+                const uint32_t col = blk * 256 + 64 * g + 16 * (j & 1);
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const float4 *xl = reinterpret_cast<const float4 *>(xs + (size_t)b * n_cols + col);
+                    const float4 *xh = reinterpret_cast<const float4 *>(xs + (size_t)b * n_cols + col + 32);
+                    float dl = 0.f, dh = 0.f;
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        float4 a = xl[v], c = xh[v];
+                        dl = fmaf(lo[4 * v + 0], a.x, dl);
+                        dl = fmaf(lo[4 * v + 1], a.y, dl);
+                        dl = fmaf(lo[4 * v + 2], a.z, dl);
+                        dl = fmaf(lo[4 * v + 3], a.w, dl);
+                        dh = fmaf(hi[4 * v + 0], c.x, dh);
+                        dh = fmaf(hi[4 * v + 1], c.y, dh);
+                        dh = fmaf(hi[4 * v + 2], c.z, dh);
+                        dh = fmaf(hi[4 * v + 3], c.w, dh);
+                    }
+                    float t = fmaf(s0, dl, s1 * dh);
+                    if ((j & 1) == 0) {
+                        // The Σx of a whole 32-column sub-block is charged once, by the even lane.
+                        const float *sx = xsum + (size_t)b * n_sb + blk * 8 + 2 * g;
+                        t -= fmaf(m0, sx[0], m1 * sx[1]);
+                    }
+                    acc[b] += t;
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            float v = warp_sum(acc[b]);
+            if (lane == 0) {
+                if (residual) v += residual[(size_t)b * out_stride + row];
+                out[(size_t)b * out_stride + row] = v;
+            }
+        }
+    }
+}
+
+// ── Q6_K ────────────────────────────────────────────────────────────────────────────────────
+// Sixteen lanes share one 210-byte super-block; lane (h, i) owns columns 128h + 32g + 4i..4i+3
+// for g = 0..3: two 4-byte pieces of ql, one of qh, the four scales of its 16-column groups.
+// Blocks are only 2-byte aligned, so the pieces are fetched as 16-bit halves.
+__device__ __forceinline__ uint32_t ld_u32_as_halves(const uint8_t *p) {
+    return ld_stream_u16(p) | (ld_stream_u16(p + 2) << 16);
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kThreads)
+qmv_q6k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+               uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
+               const float *__restrict__ residual) {
+    extern __shared__ __align__(16) float smem[];
+    float *xs = smem;
+    stage_x<NB, false>(x, x_stride, n_cols, xs, nullptr, false);
+
+    const uint32_t bpr = n_cols / 256;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane >> 4;      // which of the 2 super-blocks of this step
+    const int h = (lane >> 3) & 1;  // half of the super-block (128 columns)
+    const int i = lane & 7;         // columns 4i..4i+3 within each 32-column group
+    const uint32_t warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t n_warps = gridDim.x * kWarps;
+
+    for (uint32_t row = warp; row < n_rows; row += n_warps) {
+        const uint8_t *rowp = w + (size_t)row * bpr * 210;
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.f;
+
+        for (uint32_t blk0 = 0; blk0 < bpr; blk0 += 2) {
+            const uint32_t blk = blk0 + sub;
+            if (blk < bpr) {
+                const uint8_t *bp = rowp + (size_t)blk * 210;
+                const uint32_t ql0 = ld_u32_as_halves(bp + 64 * h + 4 * i);
+                const uint32_t ql1 = ld_u32_as_halves(bp + 64 * h + 32 + 4 * i);
+                const uint32_t qh = ld_u32_as_halves(bp + 128 + 32 * h + 4 * i);
+                const float d = f16_bits_to_f32(ld_stream_u16(bp + 208));
+                const uint8_t *scp = bp + 192 + 8 * h + (i >> 2);
+                float ds[4];
+#pragma unroll
+                for (int g = 0; g < 4; g++) ds[g] = d * (float)(int)(signed char)ld_stream_u8(scp + 2 * g);
+
+                uint32_t qv[4];
+                qv[0] = (ql0 & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
+                qv[1] = (ql1 & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
+                qv[2] = ((ql0 >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
+                qv[3] = ((ql1 >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+
+                const float kOff = 8388608.0f + 32.0f;  // 2^23 + 32: yields q − 32 exactly
+                const uint32_t col = blk * 256 + 128 * h + 4 * i;
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        const float4 a = *reinterpret_cast<const float4 *>(xs + (size_t)b * n_cols + col + 32 * g);
+                        float s = byte_to_float<0>(qv[g], kOff) * a.x;
+                        s = fmaf(byte_to_float<1>(qv[g], kOff), a.y, s);
+                        s = fmaf(byte_to_float<2>(qv[g], kOff), a.z, s);
+                        s = fmaf(byte_to_float<3>(qv[g], kOff), a.w, s);
+                        t = fmaf(ds[g], s, t);
+                    }
+                    acc[b] += t;
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            float v = warp_sum(acc[b]);
+            if (lane == 0) {
+                if (residual) v += residual[(size_t)b * out_stride + row];
+                out[(size_t)b * out_stride + row] = v;
+            }
+        }
+    }
+}
+
+// ── Q8_0 / Q4_0 ─────────────────────────────────────────────────────────────────────────────
+// One lane per 32-weight block (34 or 18 bytes, 2-byte aligned): a warp step covers 32
+// consecutive blocks, i.e. 1088 or 576 contiguous bytes.  Activations sit in shared memory with
+// a 4-float pad after every 32 so the 32 lanes' float4 reads fall into distinct banks.
+template <int NB, bool IS_Q8>
+__global__ void __launch_bounds__(kThreads)
+qmv_q32_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+               uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
+               const float *__restrict__ residual) {
+    extern __shared__ __align__(16) float smem[];
+    float *xs = smem;
+    stage_x<NB, true>(x, x_stride, n_cols, xs, nullptr, false);
+
+    constexpr int BB = IS_Q8 ? 34 : 18;
+    const uint32_t bpr = n_cols / 32;
+    const uint32_t vstride = bpr * 36;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t n_warps = gridDim.x * kWarps;
+
+    for (uint32_t row = warp; row < n_rows; row += n_warps) {
+        const uint8_t *rowp = w + (size_t)row * bpr * BB;
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.f;
+
+        for (uint32_t blk = lane; blk < bpr; blk += 32) {
+            const uint8_t *bp = rowp + (size_t)blk * BB;
+            const float d = f16_bits_to_f32(ld_stream_u16(bp));
+            float s[NB];
+#pragma unroll
+            for (int b = 0; b < NB; b++) s[b] = 0.f;
+            if (IS_Q8) {
+                const float kOff = 8388608.0f + 128.0f;  // (q ^ 0x80) is q + 128 as an unsigned byte
+#pragma unroll
+                for (int v = 0; v < 8; v++) {
+                    uint32_t q4 = (ld_stream_u16(bp + 2 + 4 * v) | (ld_stream_u16(bp + 4 + 4 * v) << 16)) ^ 0x80808080u;
+                    float f0 = byte_to_float<0>(q4, kOff), f1 = byte_to_float<1>(q4, kOff);
+                    float f2 = byte_to_float<2>(q4, kOff), f3 = byte_to_float<3>(q4, kOff);
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        const float4 a = *reinterpret_cast<const float4 *>(xs + b * vstride + blk * 36 + 4 * v);
+                        s[b] = fmaf(f0, a.x, s[b]);
+                        s[b] = fmaf(f1, a.y, s[b]);
+                        s[b] = fmaf(f2, a.z, s[b]);
+                        s[b] = fmaf(f3, a.w, s[b]);
+                    }
+                }
+            } else {
+                const float kOff = 8388608.0f + 8.0f;  // nibble − 8
+#pragma unroll
+                for (int v = 0; v < 8; v++) {
+                    // 16 bits = columns 4v..4v+3 in nibble order (low nibble of a byte comes first)
+                    uint32_t q = ld_stream_u16(bp + 2 + 2 * v);
+                    float f0 = __uint_as_float(0x4B000000u | (q & 0xFu)) - kOff;
+                    float f1 = __uint_as_float(0x4B000000u | ((q >> 4) & 0xFu)) - kOff;
+                    float f2 = __uint_as_float(0x4B000000u | ((q >> 8) & 0xFu)) - kOff;
+                    float f3 = __uint_as_float(0x4B000000u | (q >> 12)) - kOff;
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        const float4 a = *reinterpret_cast<const float4 *>(xs + b * vstride + blk * 36 + 4 * v);
+                        s[b] = fmaf(f0, a.x, s[b]);
+                        s[b] = fmaf(f1, a.y, s[b]);
+                        s[b] = fmaf(f2, a.z, s[b]);
+                        s[b] = fmaf(f3, a.w, s[b]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < NB; b++) acc[b] = fmaf(s[b], d, acc[b]);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            float v = warp_sum(acc[b]);
+            if (lane == 0) {
+                if (residual) v += residual[(size_t)b * out_stride + row];
+                out[(size_t)b * out_stride + row] = v;
+            }
+        }
+    }
+}
+
+// ── launch plumbing ─────────────────────────────────────────────────────────────────────────
+
+using QmvKernel = void (*)(const uint8_t *, const float *, float *, uint32_t, uint32_t, uint32_t, uint32_t,
+                           const float *);
+
+template <int NB>
+QmvKernel pick_kernel(uint32_t type) {
+    switch (type) {
+        case YULE_DTYPE_Q4_K: return qmv_q4k_kernel<NB>;
+        case YULE_DTYPE_Q6_K: return qmv_q6k_kernel<NB>;
+        case YULE_DTYPE_Q8_0: return qmv_q32_kernel<NB, true>;
+        case YULE_DTYPE_Q4_0: return qmv_q32_kernel<NB, false>;
+        default: return nullptr;
+    }
+}
+
+size_t qmv_smem_bytes(uint32_t type, uint32_t n_cols, int nb) {
+    size_t per_vec;
+    if (type == YULE_DTYPE_Q4_K)
+        per_vec = (size_t)n_cols + n_cols / 32;
+    else if (type == YULE_DTYPE_Q6_K)
+        per_vec = n_cols;
+    else
+        per_vec = (size_t)(n_cols / 32) * 36;
+    return per_vec * nb * sizeof(float);
+}
+
+constexpr size_t kMaxSmem = 200 * 1024;
+
+}  // namespace
+
+cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches) {
+    if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;
+    uint32_t done = 0;
+    while (done < a.batch) {
+        int nb = 1;
+        uint32_t left = a.batch - done;
+        if (left >= 4 && qmv_smem_bytes(a.type, a.n_cols, 4) <= kMaxSmem)
+            nb = 4;
+        else if (left >= 2 && qmv_smem_bytes(a.type, a.n_cols, 2) <= kMaxSmem)
+            nb = 2;
+        QmvKernel k = nb == 4 ? pick_kernel<4>(a.type) : nb == 2 ? pick_kernel<2>(a.type) : pick_kernel<1>(a.type);
+        if (!k) return cudaErrorInvalidValue;
+        size_t smem = qmv_smem_bytes(a.type, a.n_cols, nb);
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
+        if (e != cudaSuccess) return e;
+        int occ = 1;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k, kThreads, smem);
+        if (e != cudaSuccess) return e;
+        if (occ < 1) occ = 1;
+        uint32_t max_ctas = (uint32_t)(sm_count * occ);
+        uint32_t want = (a.n_rows + kWarps - 1) / kWarps;
+        uint32_t grid = want < max_ctas ? want : max_ctas;
+        k<<<grid, kThreads, smem, s>>>(a.w, a.x + (size_t)done * a.x_stride, a.out + (size_t)done * a.out_stride,
+                                       a.n_rows, a.n_cols, a.x_stride, a.out_stride,
+                                       a.residual ? a.residual + (size_t)done * a.out_stride : nullptr);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        *launches += 1;
+        done += nb;
+    }
+    return cudaSuccess;
+}
+
+// ── standalone dequantiser (bit-exact with yule-core/src/dequant.rs) ────────────────────────
+namespace {
+
+// Element i of a Q4_K super-block — dequant.rs:260-290.  d*sc, dmin*mn and q*(d*sc) are exact
+// in f32, so the single rounding of the subtraction is the only one, as on the CPU.
+__device__ __forceinline__ float dequant_q4k_elem(const uint8_t *bp, int i) {
+    const float d = f16_bits_to_f32(bp[0] | (bp[1] << 8));
+    const float dmin = f16_bits_to_f32(bp[2] | (bp[3] << 8));
+    const int jg = i >> 6, hi = (i >> 5) & 1, l = i & 31;
+    const int s = 2 * jg + hi;
+    const uint8_t *q = bp + 4;
+    uint32_t sc, mn;
+    if (s < 4) {
+        sc = q[s] & 63;
+        mn = q[s + 4] & 63;
+    } else {
+        sc = (q[s + 4] & 0xF) | ((q[s - 4] >> 6) << 4);
+        mn = (q[s + 4] >> 4) | ((q[s] >> 6) << 4);
+    }
+    const uint32_t nib = (bp[16 + 32 * jg + l] >> (4 * hi)) & 0xF;
+    return __fsub_rn(__fmul_rn((float)nib, __fmul_rn(d, (float)sc)), __fmul_rn(dmin, (float)mn));
+}
+
+// Element i of a Q6_K super-block — dequant.rs:346-372, evaluated (d*sc)*q.
+__device__ __forceinline__ float dequant_q6k_elem(const uint8_t *bp, int i) {
+    const float d = f16_bits_to_f32(bp[208] | (bp[209] << 8));
+    const int h = i >> 7, r = i & 127, g = r >> 5, l = r & 31;
+    const uint32_t low4 = (bp[64 * h + l + 32 * (g & 1)] >> (4 * (g >> 1))) & 0xF;
+    const uint32_t high2 = (bp[128 + 32 * h + l] >> (2 * g)) & 3;
+    const int q = (int)(low4 | (high2 << 4)) - 32;
+    const int sc = (int)(signed char)bp[192 + 8 * h + (l >> 4) + 2 * g];
+    return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+}
+
+// dequant.rs:77-86 (interleaved nibbles) and :142-150.
+__device__ __forceinline__ float dequant_q4_0_elem(const uint8_t *bp, int i) {
+    const float d = f16_bits_to_f32(bp[0] | (bp[1] << 8));
+    const uint32_t byte = bp[2 + (i >> 1)];
+    const uint32_t nib = (i & 1) ? (byte >> 4) : (byte & 0xF);
+    return __fmul_rn(__fsub_rn((float)nib, 8.0f), d);
+}
+__device__ __forceinline__ float dequant_q8_0_elem(const uint8_t *bp, int i) {
+    const float d = f16_bits_to_f32(bp[0] | (bp[1] << 8));
+    return __fmul_rn((float)(int)(signed char)bp[2 + i], d);
+}
+
+__device__ __forceinline__ float dequant_elem(const uint8_t *data, uint32_t type, uint64_t idx) {
+    switch (type) {
+        case YULE_DTYPE_Q4_K: return dequant_q4k_elem(data + (idx >> 8) * 144, (int)(idx & 255));
+        case YULE_DTYPE_Q6_K: return dequant_q6k_elem(data + (idx >> 8) * 210, (int)(idx & 255));
+        case YULE_DTYPE_Q4_0: return dequant_q4_0_elem(data + (idx >> 5) * 18, (int)(idx & 31));
+        case YULE_DTYPE_Q8_0: return dequant_q8_0_elem(data + (idx >> 5) * 34, (int)(idx & 31));
+        case YULE_DTYPE_F16: return f16_bits_to_f32(data[2 * idx] | (data[2 * idx + 1] << 8));
+        default: return reinterpret_cast<const float *>(data)[idx];
+    }
+}
+
+__global__ void dequantize_kernel(const uint8_t *__restrict__ data, uint32_t type, uint64_t n, float *__restrict__ out) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = dequant_elem(data, type, i);
+}
+
+__global__ void embed_gather_kernel(const uint8_t *__restrict__ table, uint32_t type, uint32_t dim, uint32_t token,
+                                    const uint32_t *__restrict__ token_ptr, uint64_t row_bytes,
+                                    float *__restrict__ out) {
+    const uint32_t tok = token_ptr ? *token_ptr : token;
+    const uint8_t *row = table + (uint64_t)tok * row_bytes;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
+        out[i] = dequant_elem(row, type, i);
+}
+
+}  // namespace
+
+cudaError_t launch_dequantize(const uint8_t *w, uint32_t type, uint64_t n_blocks, float *out, cudaStream_t s,
+                              uint64_t *launches) {
+    uint64_t n = n_blocks * block_size(type);
+    uint64_t grid = (n + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    dequantize_kernel<<<(uint32_t)grid, 256, 0, s>>>(w, type, n, out);
+    *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_embed_gather(const uint8_t *table, uint32_t type, uint32_t dim, uint32_t token,
+                                const uint32_t *token_ptr, float *out, cudaStream_t s, uint64_t *launches) {
+    uint64_t row_bytes = (uint64_t)(dim / block_size(type)) * block_bytes(type);
+    embed_gather_kernel<<<(dim + 255) / 256, 256, 0, s>>>(table, type, dim, token, token_ptr, row_bytes, out);
+    *launches += 1;
+    return cudaGetLastError();
+}
+
+}  // namespace yule

@@ -1,0 +1,542 @@
+// runner.cu — forward-pass runner over the C ABI: Yule's `ModelRunner` trait
+// (yule-infer/src/model_runner.rs:12-17) for the Llama-family dense path, issuing the op
+// sequence of GpuTransformerRunner::forward (yule-infer/src/gpu_runner.rs:296-695).
+//
+// Two modes (yule_runner_config::fused):
+//   0  one kernel per reference dispatch, launched one by one with the position passed by value;
+//      the embedding row is dequantised on the device instead of on the CPU (gpu_runner.rs:309-343).
+//   1  the same arithmetic with the RMSNorm/Rope/KV-copy/Add dispatches folded into neighbouring
+//      kernels, position and token read from device memory, and the whole token step replayed
+//      from one CUDA graph.
+
+#include <cmath>
+#include <cstring>
+#include <string>
+
+#include "internal.h"
+
+using namespace yule;
+
+namespace {
+
+struct Tensor {
+    Buffer buf;
+    uint32_t type = 0;
+    bool set = false;
+};
+
+struct Layer {
+    Tensor attn_norm, attn_q, attn_k, attn_v, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down;
+    const float *attn_norm_f32 = nullptr, *ffn_norm_f32 = nullptr;
+    yule_buffer k_cache_h = 0, v_cache_h = 0;
+    float *k_cache = nullptr, *v_cache = nullptr;
+};
+
+}  // namespace
+
+struct yule_cuda_runner {
+    yule_cuda_ctx *ctx = nullptr;
+    yule_runner_config cfg{};
+    std::vector<Layer> layers;
+    Tensor token_embd, output_norm, output;
+    const float *output_norm_f32 = nullptr;
+    std::vector<yule_buffer> owned;  // everything the runner allocated, freed on destroy
+
+    yule_buffer hidden_h = 0, logits_h = 0;
+    float *hidden = nullptr, *residual = nullptr, *normed = nullptr, *q = nullptr, *k_tmp = nullptr,
+          *v_tmp = nullptr, *attn_out = nullptr, *attn_proj = nullptr, *gate = nullptr, *up = nullptr,
+          *ffn_out = nullptr, *logits = nullptr;
+    float *rope_cos = nullptr, *rope_sin = nullptr;  // [max_seq_len][head_dim/2], device
+    uint32_t *d_state = nullptr;    // [0] token, [1] position
+    uint32_t *d_history = nullptr;  // greedy pick made after each position
+    uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
+    size_t h_pinned_cap = 0;
+
+    uint32_t pos = 0;
+    bool fused = false;
+    uint32_t graph_kernels = 0;  // kernels replayed per graph launch
+    bool finalized = false;
+    bool have_next_token = false;  // d_state[0] holds the greedy continuation
+    cudaGraphExec_t graph_exec = nullptr;
+};
+
+namespace {
+
+int32_t alloc_f32(yule_cuda_runner *r, size_t n, float **out, yule_buffer *handle_out = nullptr) {
+    yule_buffer h;
+    int32_t rc = yule_cuda_allocate(r->ctx, n * sizeof(float), &h);
+    if (rc) return rc;
+    Buffer b;
+    if (!r->ctx->find(h, &b, "runner scratch")) return YULE_ERR_UNKNOWN_BUFFER;
+    r->owned.push_back(h);
+    *out = (float *)b.ptr;
+    if (handle_out) *handle_out = h;
+    return YULE_OK;
+}
+
+Tensor *slot_for(yule_cuda_runner *r, const char *name) {
+    if (!strcmp(name, "token_embd.weight")) return &r->token_embd;
+    if (!strcmp(name, "output_norm.weight")) return &r->output_norm;
+    if (!strcmp(name, "output.weight")) return &r->output;
+    unsigned layer = 0;
+    char rest[64];
+    if (sscanf(name, "blk.%u.%63s", &layer, rest) != 2 || layer >= r->cfg.n_layers) return nullptr;
+    Layer &L = r->layers[layer];
+    struct {
+        const char *n;
+        Tensor *t;
+    } slots[] = {{"attn_norm.weight", &L.attn_norm},     {"attn_q.weight", &L.attn_q},
+                 {"attn_k.weight", &L.attn_k},           {"attn_v.weight", &L.attn_v},
+                 {"attn_output.weight", &L.attn_output}, {"ffn_norm.weight", &L.ffn_norm},
+                 {"ffn_gate.weight", &L.ffn_gate},       {"ffn_up.weight", &L.ffn_up},
+                 {"ffn_down.weight", &L.ffn_down}};
+    for (auto &s : slots)
+        if (!strcmp(rest, s.n)) return s.t;
+    return nullptr;
+}
+
+int32_t check_matrix(const Tensor &t, const char *what, uint32_t layer, uint64_t rows, uint64_t cols) {
+    if (!t.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: %s (layer %u)", what, layer);
+    if (!is_quantized(t.type))
+        return fail(YULE_ERR_UNSUPPORTED_DTYPE, "unsupported dtype for GPU qmv: GGUF type %u (%s)", t.type, what);
+    if (cols % block_size(t.type))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "%s: %llu columns is not a multiple of the block size", what,
+                    (unsigned long long)cols);
+    size_t need = tensor_bytes(t.type, rows, cols);
+    if (t.buf.size < need)
+        return fail(YULE_ERR_OUT_OF_BOUNDS, "%s (layer %u) holds %zu bytes, %zu needed", what, layer, t.buf.size, need);
+    return YULE_OK;
+}
+
+// Norm weights arrive as F32 or F16 (gpu_runner.rs:183-211 converts on the host); F16 ones are
+// expanded once on the device.
+int32_t norm_as_f32(yule_cuda_runner *r, const Tensor &t, const char *what, uint32_t layer, const float **out) {
+    const uint32_t dim = r->cfg.dim;
+    if (!t.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: %s (layer %u)", what, layer);
+    if (t.type == YULE_DTYPE_F32) {
+        if (t.buf.size < (size_t)dim * 4) return fail(YULE_ERR_OUT_OF_BOUNDS, "%s too small", what);
+        *out = (const float *)t.buf.ptr;
+        return YULE_OK;
+    }
+    if (t.type != YULE_DTYPE_F16) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "%s must be F32 or F16", what);
+    if (t.buf.size < (size_t)dim * 2) return fail(YULE_ERR_OUT_OF_BOUNDS, "%s too small", what);
+    float *dst;
+    int32_t rc = alloc_f32(r, dim, &dst);
+    if (rc) return rc;
+    uint64_t n = 0;
+    cudaError_t e = launch_dequantize((const uint8_t *)t.buf.ptr, YULE_DTYPE_F16, dim, dst, r->ctx->stream, &n);
+    r->ctx->launches.fetch_add(n);
+    if (e != cudaSuccess) return fail_cuda(e, "norm weight conversion");
+    *out = dst;
+    return YULE_OK;
+}
+
+struct Step {
+    yule_cuda_runner *r;
+    uint64_t n = 0;
+    cudaError_t err = cudaSuccess;
+    void ok(cudaError_t e) {
+        if (err == cudaSuccess && e != cudaSuccess) err = e;
+    }
+    void qmv(const Tensor &w, const float *x, float *out, uint32_t rows, uint32_t cols, const float *residual = nullptr) {
+        QmvArgs a;
+        a.w = (const uint8_t *)w.buf.ptr;
+        a.x = x;
+        a.out = out;
+        a.n_rows = rows;
+        a.n_cols = cols;
+        a.type = w.type;
+        a.batch = 1;
+        a.x_stride = cols;
+        a.out_stride = rows;
+        a.residual = residual;
+        ok(launch_qmv(a, r->ctx->prop.multiProcessorCount, r->ctx->stream, &n));
+    }
+};
+
+// Enqueues one token step.  `by_value` (mode 0): token and position are host values baked into
+// the launches.  Otherwise they are read from d_state, and the greedy pick is written back.
+cudaError_t enqueue_forward(yule_cuda_runner *r, bool by_value, uint32_t token, uint32_t pos, uint64_t *launches) {
+    const yule_runner_config &c = r->cfg;
+    cudaStream_t s = r->ctx->stream;
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    Step st{r};
+    const uint32_t *tok_ptr = by_value ? nullptr : r->d_state;
+    const uint32_t *pos_ptr = by_value ? nullptr : r->d_state + 1;
+
+    st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, token, tok_ptr,
+                              r->hidden, s, &st.n));
+
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        Layer &L = r->layers[l];
+        if (by_value) {
+            st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
+        }
+        st.ok(launch_rms_norm(r->hidden, L.attn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
+        st.qmv(L.attn_q, r->normed, r->q, qdim, dim);
+        st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim, dim);
+        st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim, dim);
+        if (by_value) {
+            RopeAngles ang;
+            const uint32_t half = hd / 2;
+            for (uint32_t i = 0; i < half; i++) {
+                float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)hd);
+                float theta = (float)pos * freq;
+                ang.cos[i] = cosf(theta);
+                ang.sin[i] = sinf(theta);
+            }
+            st.ok(launch_rope_angles(r->q, r->k_tmp, hd, c.n_heads, c.n_kv_heads, ang, s, &st.n));
+            const size_t off = (size_t)pos * kvdim;
+            st.ok(cudaMemcpyAsync(L.k_cache + off, r->k_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
+            st.ok(cudaMemcpyAsync(L.v_cache + off, r->v_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
+            st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, pos + 1, nullptr, pos + 1,
+                                             c.n_heads, c.n_kv_heads, kvdim, s, &st.n));
+            st.qmv(L.attn_output, r->attn_out, r->attn_proj, dim, qdim);
+            st.ok(launch_add(r->residual, r->attn_proj, r->hidden, dim, s, &st.n));
+            st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
+        } else {
+            st.ok(launch_rope_kv_write(r->q, r->k_tmp, r->v_tmp, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin,
+                                       pos_ptr, hd, c.n_heads, c.n_kv_heads, s, &st.n));
+            st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, 0, pos_ptr, c.max_seq_len,
+                                             c.n_heads, c.n_kv_heads, kvdim, s, &st.n));
+            // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
+            st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
+        }
+        st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
+        st.qmv(L.ffn_gate, r->normed, r->gate, ff, dim);
+        st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
+        st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n));
+        if (by_value) {
+            st.qmv(L.ffn_down, r->gate, r->ffn_out, dim, ff);
+            st.ok(launch_add(r->residual, r->ffn_out, r->hidden, dim, s, &st.n));
+        } else {
+            st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
+        }
+    }
+    st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
+    const Tensor &out_w = r->output.set ? r->output : r->token_embd;
+    st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
+    if (!by_value) {
+        // greedy pick → d_history[pos] and d_state[0]; position advances for the next replay
+        st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, nullptr, s, &st.n));
+    }
+    *launches += st.n;
+    return st.err;
+}
+
+__global__ void record_and_advance_kernel(uint32_t *state, uint32_t *history) {
+    const uint32_t pos = state[1];
+    history[pos] = state[0];
+    state[1] = pos + 1;
+}
+
+int32_t finalize(yule_cuda_runner *r) {
+    if (r->finalized) return YULE_OK;
+    const yule_runner_config &c = r->cfg;
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    int32_t rc;
+    if (!r->token_embd.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: token_embd.weight");
+    {
+        uint32_t bs = block_size(r->token_embd.type);
+        if (bs == 0 || dim % bs) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "token_embd dtype %u unsupported", r->token_embd.type);
+        size_t need = (size_t)c.vocab_size * (dim / bs) * block_bytes(r->token_embd.type);
+        if (r->token_embd.buf.size < need) return fail(YULE_ERR_OUT_OF_BOUNDS, "token_embd.weight too small");
+    }
+    if ((rc = norm_as_f32(r, r->output_norm, "output_norm.weight", 0, &r->output_norm_f32))) return rc;
+    if (r->output.set) {
+        if ((rc = check_matrix(r->output, "output.weight", 0, c.vocab_size, dim))) return rc;
+    } else if ((rc = check_matrix(r->token_embd, "token_embd.weight (as output)", 0, c.vocab_size, dim))) {
+        return rc;
+    }
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        Layer &L = r->layers[l];
+        if ((rc = norm_as_f32(r, L.attn_norm, "attn_norm.weight", l, &L.attn_norm_f32))) return rc;
+        if ((rc = norm_as_f32(r, L.ffn_norm, "ffn_norm.weight", l, &L.ffn_norm_f32))) return rc;
+        if ((rc = check_matrix(L.attn_q, "attn_q.weight", l, qdim, dim))) return rc;
+        if ((rc = check_matrix(L.attn_k, "attn_k.weight", l, kvdim, dim))) return rc;
+        if ((rc = check_matrix(L.attn_v, "attn_v.weight", l, kvdim, dim))) return rc;
+        if ((rc = check_matrix(L.attn_output, "attn_output.weight", l, dim, qdim))) return rc;
+        if ((rc = check_matrix(L.ffn_gate, "ffn_gate.weight", l, ff, dim))) return rc;
+        if ((rc = check_matrix(L.ffn_up, "ffn_up.weight", l, ff, dim))) return rc;
+        if ((rc = check_matrix(L.ffn_down, "ffn_down.weight", l, dim, ff))) return rc;
+    }
+    r->finalized = true;
+    return YULE_OK;
+}
+
+int32_t ensure_graph(yule_cuda_runner *r) {
+    if (r->graph_exec) return YULE_OK;
+    cudaStream_t s = r->ctx->stream;
+    cudaGraph_t graph = nullptr;
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    YULE_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
+    uint64_t n = 0;
+    cudaError_t e = enqueue_forward(r, false, 0, 0, &n);
+    if (e == cudaSuccess) {
+        record_and_advance_kernel<<<1, 1, 0, s>>>(r->d_state, r->d_history);
+        e = cudaGetLastError();
+        n += 1;
+    }
+    cudaError_t e2 = cudaStreamEndCapture(s, &graph);
+    if (e != cudaSuccess || e2 != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return fail_cuda(e != cudaSuccess ? e : e2, "graph capture of the token step");
+    }
+    e = cudaGraphInstantiate(&r->graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGraphInstantiate");
+    r->graph_kernels = (uint32_t)n;
+    return YULE_OK;
+}
+
+inline uint32_t graph_kernels(const yule_cuda_runner *r) { return r->graph_kernels; }
+inline bool is_fused(const yule_cuda_runner *r) { return r->fused; }
+
+int32_t ensure_pinned(yule_cuda_runner *r, size_t n_words) {
+    if (r->h_pinned_cap >= n_words) return YULE_OK;
+    if (r->h_pinned) cudaFreeHost(r->h_pinned);
+    r->h_pinned = nullptr;
+    r->h_pinned_cap = 0;
+    size_t cap = n_words < 4096 ? 4096 : n_words;
+    YULE_CUDA_TRY(cudaMallocHost((void **)&r->h_pinned, cap * sizeof(uint32_t)));
+    r->h_pinned_cap = cap;
+    return YULE_OK;
+}
+
+// One token through the model; logits stay on the device.
+int32_t step(yule_cuda_runner *r, uint32_t token, bool token_from_device) {
+    const yule_runner_config &c = r->cfg;
+    if (r->pos >= c.max_seq_len) return fail(YULE_ERR_CONTEXT_LENGTH, "context length exceeded");
+    if (!token_from_device && token >= c.vocab_size)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "token %u outside the vocabulary (%u)", token, c.vocab_size);
+    cudaStream_t s = r->ctx->stream;
+    if (!is_fused(r)) {
+        uint64_t n = 0;
+        cudaError_t e = enqueue_forward(r, true, token, r->pos, &n);
+        r->ctx->launches.fetch_add(n);
+        if (e != cudaSuccess) return fail_cuda(e, "token step");
+    } else {
+        int32_t rc = ensure_graph(r);
+        if (rc) return rc;
+        if (!token_from_device) {
+            // h_pinned[0..1] = {token, pos}: the position is rewritten too, so a reset() or a
+            // failed step cannot leave the device counter out of step with the host's.
+            YULE_CUDA_TRY(cudaStreamSynchronize(s));  // staging words may still be in flight
+            r->h_pinned[0] = token;
+            r->h_pinned[1] = r->pos;
+            YULE_CUDA_TRY(cudaMemcpyAsync(r->d_state, r->h_pinned, 8, cudaMemcpyHostToDevice, s));
+        }
+        YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
+        r->ctx->launches.fetch_add(graph_kernels(r));
+    }
+    r->pos += 1;
+    r->have_next_token = is_fused(r);
+    return YULE_OK;
+}
+
+int32_t read_logits(yule_cuda_runner *r, float *logits_out) {
+    if (!logits_out) return YULE_OK;
+    cudaStream_t s = r->ctx->stream;
+    YULE_CUDA_TRY(cudaMemcpyAsync(logits_out, r->logits, (size_t)r->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, s));
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    return YULE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cfg, yule_cuda_runner **out_runner) {
+    if (!ctx || !cfg || !out_runner) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    *out_runner = nullptr;
+    YULE_CUDA_TRY(cudaSetDevice(ctx->device));
+    const yule_runner_config &c = *cfg;
+    if (!c.dim || !c.n_layers || !c.n_heads || !c.n_kv_heads || !c.head_dim || !c.vocab_size || !c.ff_dim ||
+        !c.max_seq_len)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "runner config has a zero field");
+    if (c.n_heads % c.n_kv_heads) return fail(YULE_ERR_INVALID_ARGUMENT, "n_heads must be a multiple of n_kv_heads");
+    if (c.head_dim % 2 || c.head_dim > 256) return fail(YULE_ERR_INVALID_ARGUMENT, "head_dim must be even and <= 256");
+    if (c.dim % 32 || c.ff_dim % 32 || (c.n_heads * c.head_dim) % 32)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "dim, ff_dim and n_heads*head_dim must be multiples of 32");
+    auto *r = new yule_cuda_runner();
+    r->ctx = ctx;
+    r->cfg = c;
+    r->fused = c.fused != 0;
+    r->layers.resize(c.n_layers);
+    const uint32_t hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd;
+    int32_t rc = YULE_OK;
+    auto A = [&](size_t n, float **p, yule_buffer *h = nullptr) {
+        if (rc == YULE_OK) rc = alloc_f32(r, n, p, h);
+    };
+    A(c.dim, &r->hidden, &r->hidden_h);
+    A(c.dim, &r->residual);
+    A(c.dim, &r->normed);
+    A(qdim, &r->q);
+    A(kvdim, &r->k_tmp);
+    A(kvdim, &r->v_tmp);
+    A(qdim, &r->attn_out);
+    A(c.dim, &r->attn_proj);
+    A(c.ff_dim, &r->gate);
+    A(c.ff_dim, &r->up);
+    A(c.dim, &r->ffn_out);
+    A(c.vocab_size, &r->logits, &r->logits_h);
+    const size_t half = hd / 2;
+    A((size_t)c.max_seq_len * half, &r->rope_cos);
+    A((size_t)c.max_seq_len * half, &r->rope_sin);
+    float *tmp = nullptr;
+    A(2, &tmp);
+    r->d_state = (uint32_t *)tmp;
+    A((size_t)c.max_seq_len + 1, &tmp);
+    r->d_history = (uint32_t *)tmp;
+    for (uint32_t l = 0; l < c.n_layers && rc == YULE_OK; l++) {
+        A((size_t)c.max_seq_len * kvdim, &r->layers[l].k_cache, &r->layers[l].k_cache_h);
+        A((size_t)c.max_seq_len * kvdim, &r->layers[l].v_cache, &r->layers[l].v_cache_h);
+    }
+    if (rc == YULE_OK) rc = ensure_pinned(r, 4096);
+    if (rc == YULE_OK) {
+        // RoPE table with the CPU runner's recipe (model_runner.rs:78-99): f32 powf / sin / cos of
+        // the host libm, so rotations match it bit for bit.
+        std::vector<float> hc((size_t)c.max_seq_len * half), hs((size_t)c.max_seq_len * half);
+        for (size_t p = 0; p < c.max_seq_len; p++)
+            for (size_t i = 0; i < half; i++) {
+                float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)hd);
+                float theta = (float)p * freq;
+                hc[p * half + i] = cosf(theta);
+                hs[p * half + i] = sinf(theta);
+            }
+        cudaError_t e = cudaMemcpyAsync(r->rope_cos, hc.data(), hc.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(r->rope_sin, hs.data(), hs.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = fail_cuda(e, "rope table upload");
+    }
+    if (rc != YULE_OK) {
+        yule_cuda_runner_destroy(r);
+        return rc;
+    }
+    *out_runner = r;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_destroy(yule_cuda_runner *r) {
+    if (!r) return YULE_OK;
+    cudaSetDevice(r->ctx->device);
+    cudaStreamSynchronize(r->ctx->stream);
+    if (r->graph_exec) cudaGraphExecDestroy(r->graph_exec);
+    if (r->h_pinned) cudaFreeHost(r->h_pinned);
+    for (yule_buffer h : r->owned) yule_cuda_free(r->ctx, h);
+    delete r;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_set_tensor(yule_cuda_runner *r, const char *name, yule_buffer handle, uint32_t gguf_type) {
+    if (!r || !name) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    Tensor *t = slot_for(r, name);
+    if (!t) return fail(YULE_ERR_INVALID_ARGUMENT, "tensor name not used by this runner: %s", name);
+    Buffer b;
+    if (!r->ctx->find(handle, &b, name)) return YULE_ERR_UNKNOWN_BUFFER;
+    if (block_size(gguf_type) == 0) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "GGUF type %u not supported (%s)", gguf_type, name);
+    t->buf = b;
+    t->type = gguf_type;
+    t->set = true;
+    r->finalized = false;
+    if (r->graph_exec) {  // pointers are baked into the graph
+        cudaGraphExecDestroy(r->graph_exec);
+        r->graph_exec = nullptr;
+    }
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_prefill(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n_tokens, float *logits_out) {
+    if (!r || (n_tokens && !tokens)) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    for (uint32_t i = 0; i < n_tokens; i++)
+        if ((rc = step(r, tokens[i], false))) return rc;
+    return n_tokens ? read_logits(r, logits_out) : YULE_OK;
+}
+
+int32_t yule_cuda_runner_decode_step(yule_cuda_runner *r, uint32_t token, float *logits_out) {
+    if (!r) return fail(YULE_ERR_INVALID_ARGUMENT, "null runner");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    if ((rc = step(r, token, false))) return rc;
+    return read_logits(r, logits_out);
+}
+
+int32_t yule_cuda_runner_reset(yule_cuda_runner *r) {
+    if (!r) return fail(YULE_ERR_INVALID_ARGUMENT, "null runner");
+    r->pos = 0;
+    r->have_next_token = false;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_position(yule_cuda_runner *r, uint32_t *out_pos) {
+    if (!r || !out_pos) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    *out_pos = r->pos;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *prompt, uint32_t n_prompt,
+                                         uint32_t n_generate, uint32_t *out_tokens) {
+    if (!r || (n_prompt && !prompt) || (n_generate && !out_tokens)) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    if (!is_fused(r)) return fail(YULE_ERR_INVALID_ARGUMENT, "generate_greedy needs a runner created with fused = 1");
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    if ((rc = ensure_graph(r))) return rc;
+    const yule_runner_config &c = r->cfg;
+    if ((uint64_t)r->pos + n_prompt + n_generate > c.max_seq_len)
+        return fail(YULE_ERR_CONTEXT_LENGTH, "context length exceeded");
+    if (n_prompt == 0 && n_generate && !r->have_next_token)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "nothing to continue from: feed a prompt first");
+    cudaStream_t s = r->ctx->stream;
+    if (n_prompt) {
+        for (uint32_t i = 0; i < n_prompt; i++)
+            if (prompt[i] >= c.vocab_size) return fail(YULE_ERR_INVALID_ARGUMENT, "token %u outside the vocabulary", prompt[i]);
+        if ((rc = ensure_pinned(r, 2 * (size_t)n_prompt))) return rc;
+        YULE_CUDA_TRY(cudaStreamSynchronize(s));
+        for (uint32_t i = 0; i < n_prompt; i++) {
+            r->h_pinned[2 * i] = prompt[i];
+            r->h_pinned[2 * i + 1] = r->pos + i;
+        }
+        for (uint32_t i = 0; i < n_prompt; i++) {
+            YULE_CUDA_TRY(cudaMemcpyAsync(r->d_state, r->h_pinned + 2 * i, 8, cudaMemcpyHostToDevice, s));
+            YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
+        }
+        r->ctx->launches.fetch_add((uint64_t)graph_kernels(r) * n_prompt);
+        r->pos += n_prompt;
+        r->have_next_token = true;
+    }
+    if (n_generate) {
+        // Token g is the pick made after position first+g-1, i.e. d_history[first + g - 1]; each
+        // replay consumes the previous pick from d_state[0] without touching the host.
+        const uint32_t first = r->pos;
+        for (uint32_t g = 0; g < n_generate; g++) YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
+        r->ctx->launches.fetch_add((uint64_t)graph_kernels(r) * n_generate);
+        r->pos += n_generate;
+        YULE_CUDA_TRY(cudaMemcpyAsync(out_tokens, r->d_history + first - 1, (size_t)n_generate * 4,
+                                      cudaMemcpyDeviceToHost, s));
+    }
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_buffer(yule_cuda_runner *r, uint32_t which, uint32_t layer, yule_buffer *out_handle) {
+    if (!r || !out_handle) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    switch (which) {
+        case 0: *out_handle = r->hidden_h; return YULE_OK;
+        case 3: *out_handle = r->logits_h; return YULE_OK;
+        case 1:
+        case 2:
+            if (layer >= r->cfg.n_layers) return fail(YULE_ERR_INVALID_ARGUMENT, "layer %u out of range", layer);
+            *out_handle = which == 1 ? r->layers[layer].k_cache_h : r->layers[layer].v_cache_h;
+            return YULE_OK;
+        default: return fail(YULE_ERR_INVALID_ARGUMENT, "unknown buffer selector %u", which);
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,135 @@
+"""Host-side mirror of Yule's GPU forward-pass runner over the C ABI.
+
+``CudaTransformerRunner`` plays the part of ``GpuTransformerRunner`` (yule-infer/src/gpu_runner.rs:72-720)
+behind the ``ModelRunner`` trait (yule-infer/src/model_runner.rs:12-17): it uploads every tensor as raw
+GGUF bytes (gpu_runner.rs:171-254) and exposes ``prefill`` / ``decode_step`` / ``reset``.  The forward
+pass itself runs inside ``libyule_cuda.so``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from .backend import BufferHandle, CudaB200Backend, _check
+from .dtype import DType
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    """The fields of ``GpuConfig`` (yule-infer/src/gpu_runner.rs:13-25) the Llama path uses."""
+    dim: int
+    n_layers: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    vocab_size: int
+    ff_dim: int
+    max_seq_len: int = 4096
+    norm_eps: float = 1e-5
+    rope_freq_base: float = 10000.0
+
+    def tensor_shapes(self) -> dict[str, tuple[int, int]]:
+        """GGUF tensor name → (rows, cols) for every matrix the runner reads (gpu_runner.rs:213-222)."""
+        q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        shapes = {"token_embd.weight": (self.vocab_size, self.dim), "output.weight": (self.vocab_size, self.dim)}
+        for l in range(self.n_layers):
+            p = f"blk.{l}."
+            shapes[p + "attn_q.weight"] = (q, self.dim)
+            shapes[p + "attn_k.weight"] = (kv, self.dim)
+            shapes[p + "attn_v.weight"] = (kv, self.dim)
+            shapes[p + "attn_output.weight"] = (self.dim, q)
+            shapes[p + "ffn_gate.weight"] = (self.ff_dim, self.dim)
+            shapes[p + "ffn_up.weight"] = (self.ff_dim, self.dim)
+            shapes[p + "ffn_down.weight"] = (self.dim, self.ff_dim)
+        return shapes
+
+    def norm_names(self) -> list[str]:
+        names = ["output_norm.weight"]
+        for l in range(self.n_layers):
+            names += [f"blk.{l}.attn_norm.weight", f"blk.{l}.ffn_norm.weight"]
+        return names
+
+
+class CudaTransformerRunner:
+    """``ModelRunner`` over the CUDA backend.
+
+    ``weights`` maps GGUF tensor names to ``(bytes-like or uint8/float array, DType)``.  ``fused=False``
+    issues one kernel per reference dispatch; ``fused=True`` replays fused kernels from a CUDA graph.
+    """
+
+    def __init__(self, backend: CudaB200Backend, config: ModelConfig, weights: dict, fused: bool = True):
+        self.backend = backend
+        self.config = config
+        self._lib = _lib.cuda_lib()
+        cfg = _lib.RunnerConfig(config.dim, config.n_layers, config.n_heads, config.n_kv_heads, config.head_dim,
+                                config.vocab_size, config.ff_dim, config.max_seq_len, config.norm_eps,
+                                config.rope_freq_base, 1 if fused else 0)
+        r = C.c_void_p()
+        _check(self._lib.yule_cuda_runner_create(backend._ctx, C.byref(cfg), C.byref(r)))
+        self._r = r
+        self._handles: dict[str, BufferHandle] = {}
+        self.weight_bytes = 0
+        for name, (data, dtype) in weights.items():
+            arr = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+            h = backend.allocate(arr.nbytes)
+            backend.copy_to_device(arr, h)
+            self._handles[name] = h
+            self.weight_bytes += arr.nbytes
+            _check(self._lib.yule_cuda_runner_set_tensor(self._r, name.encode(), h.id, int(dtype)))
+        backend.synchronize()
+
+    def close(self) -> None:
+        if getattr(self, "_r", None):
+            self._lib.yule_cuda_runner_destroy(self._r)
+            self._r = None
+            for h in self._handles.values():
+                self.backend.free(h)
+            self._handles.clear()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ── ModelRunner ────────────────────────────────────────────────────────────────────────
+    def prefill(self, tokens) -> np.ndarray:
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        logits = np.empty(self.config.vocab_size, np.float32)
+        _check(self._lib.yule_cuda_runner_prefill(self._r, toks.ctypes.data_as(C.POINTER(C.c_uint32)), toks.size,
+                                                  logits.ctypes.data_as(C.POINTER(C.c_float))))
+        return logits
+
+    def decode_step(self, token: int, out: np.ndarray | None = None) -> np.ndarray:
+        logits = out if out is not None else np.empty(self.config.vocab_size, np.float32)
+        _check(self._lib.yule_cuda_runner_decode_step(self._r, int(token), logits.ctypes.data_as(C.POINTER(C.c_float))))
+        return logits
+
+    def reset(self) -> None:
+        _check(self._lib.yule_cuda_runner_reset(self._r))
+
+    # ── additive ───────────────────────────────────────────────────────────────────────────
+    @property
+    def pos(self) -> int:
+        p = C.c_uint32()
+        _check(self._lib.yule_cuda_runner_position(self._r, C.byref(p)))
+        return p.value
+
+    def generate_greedy(self, prompt, n_generate: int) -> np.ndarray:
+        """Feed ``prompt`` (may be empty to continue), then emit ``n_generate`` greedy tokens on the device."""
+        toks = np.ascontiguousarray(prompt, dtype=np.uint32)
+        out = np.empty(max(n_generate, 1), np.uint32)
+        _check(self._lib.yule_cuda_runner_generate_greedy(
+            self._r, toks.ctypes.data_as(C.POINTER(C.c_uint32)), toks.size, n_generate,
+            out.ctypes.data_as(C.POINTER(C.c_uint32))))
+        return out[:n_generate]
+
+    def buffer(self, which: str, layer: int = 0) -> BufferHandle:
+        sel = {"hidden": 0, "k_cache": 1, "v_cache": 2, "logits": 3}[which]
+        h = C.c_uint64()
+        _check(self._lib.yule_cuda_runner_buffer(self._r, sel, layer, C.byref(h)))
+        return BufferHandle(h.value)
