@@ -308,7 +308,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
 
     if rank == 0:
         peaks, peak_kind = measured_peaks()
-        roof = matvec_ring_roofline(backend, peaks, peak_kind)
+        roof = matvec_ring_roofline(backend, peaks, peak_kind, iters=20 if args.small else 1000)
         mid_pos = N_PROMPT + N_GEN // 2
         bpt = decode_bytes_per_token(cfg, weights, mid_pos)
         per_gpu_tok_s = N_GEN * args.steps / (decode_ms * 1e-3)
@@ -351,7 +351,13 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true",
+                    help="profiling-sized run: 4-token prompt + 4 tokens, 20 ring launches, no CPU leg")
     args = ap.parse_args()
+    if args.small:
+        global N_PROMPT, N_GEN
+        N_PROMPT, N_GEN = 4, 4
+        args.no_cpu_baseline = True
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -4,10 +4,20 @@
 import numpy as np
 import pytest
 
-from conftest import REL_TOL, guarded_rel_err
+from conftest import REL_TOL
 from yule_b200 import CudaTransformerRunner, DType, ModelConfig, YuleGpuError, synth
 
 pytestmark = pytest.mark.gpu
+
+
+
+def guarded_rel_err(y, ref):
+    """Logits after a whole forward pass: max |y - ref| relative to the vector's scale max |ref|.  (An
+    element-wise ratio is ill posed here: logits cross zero, and 22 layers of re-ordered fp32 sums leave
+    ~1e-6 of the scale in every entry.)  Single matvecs use the stricter element-wise form."""
+    y, ref = np.asarray(y, np.float64), np.asarray(ref, np.float64)
+    return float(np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30))
+
 
 SMALL = ModelConfig(dim=256, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=32, vocab_size=512, ff_dim=768,
                     max_seq_len=64)
@@ -38,9 +48,10 @@ def greedy_reference(oracle, m, prompt, n_gen):
 
 
 @pytest.mark.parametrize("fused", [False, True])
-@pytest.mark.parametrize("mix", ["q4k_q6k", "q8_0", "q4_0"])
+@pytest.mark.parametrize("mix", ["q4k_q6k", "q4k", "q6k", "q8_0", "q4_0"])
 def test_logits_match_cpu_runner(backend, oracle, fused, mix):
     kw = {"q4k_q6k": dict(linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K),
+          "q4k": dict(linear=DType.Q4_K), "q6k": dict(linear=DType.Q6_K),
           "q8_0": dict(linear=DType.Q8_0), "q4_0": dict(linear=DType.Q4_0)}[mix]
     weights = synth.synthetic_model(SMALL, seed=1, std=0.05, **kw)
     ref = make_oracle_model(oracle, SMALL, weights)

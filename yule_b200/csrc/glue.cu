@@ -78,6 +78,8 @@ __global__ void softmax_kernel(const float *__restrict__ in, float *__restrict__
 // runner's `1.0 / (ss / n + eps).sqrt()` (yule-infer/src/model_runner.rs:254-258).
 __global__ void rms_norm_kernel(const float *__restrict__ in, const float *__restrict__ w, float *__restrict__ out,
                                 uint32_t n, float eps) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     __shared__ float red[32];
     float ss = 0.f;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
@@ -112,6 +114,8 @@ __global__ void rope_kv_write_kernel(float *__restrict__ q, const float *__restr
                                      float *__restrict__ v_cache, const float *__restrict__ cos_table,
                                      const float *__restrict__ sin_table, const uint32_t *__restrict__ pos_ptr,
                                      uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     const uint32_t pos = *pos_ptr;
     const uint32_t half = head_dim / 2;
     const uint32_t kv_stride = n_kv_heads * head_dim;
@@ -143,6 +147,8 @@ __global__ void rope_kv_write_kernel(float *__restrict__ q, const float *__restr
 // kernels/cuda/silu_mul.cu:3-14.
 __global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,
                                 uint32_t n) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = gate[i];
@@ -192,6 +198,8 @@ multihead_attention_kernel(const float *__restrict__ q, const float *__restrict_
                            uint32_t kv_stride) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[32];
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     const uint32_t seq_len = pos_ptr ? (*pos_ptr + 1) : seq_len_arg;
     const uint32_t head = blockIdx.x;
     const uint32_t kv_head = head / (n_heads / n_kv_heads);
@@ -242,10 +250,13 @@ multihead_attention_kernel(const float *__restrict__ q, const float *__restrict_
     }
 }
 
-// Greedy pick with ties to the highest index (yule-infer/src/sampler.rs:150-163), then the
-// position counter is advanced so the next graph replay sees pos+1.
-__global__ void argmax_kernel(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ out_token,
-                              uint32_t *__restrict__ pos_to_bump) {
+// Greedy pick with ties to the highest index (yule-infer/src/sampler.rs:150-163) into state[0];
+// with `history` the pick is also logged at history[position] and the position (state[1]) is
+// advanced, so the next graph replay continues the sequence without the host.
+__global__ void argmax_kernel(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ state,
+                              uint32_t *__restrict__ history) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
     float best = -FLT_MAX;
@@ -288,8 +299,12 @@ __global__ void argmax_kernel(const float *__restrict__ v, uint32_t n, uint32_t 
             }
         }
         if (lane == 0) {
-            *out_token = idx;
-            if (pos_to_bump) *pos_to_bump += 1;
+            state[0] = idx;
+            if (history) {
+                const uint32_t pos = state[1];
+                history[pos] = idx;
+                state[1] = pos + 1;
+            }
         }
     }
 }
@@ -313,10 +328,9 @@ cudaError_t launch_softmax(const float *in, float *out, uint32_t n, cudaStream_t
     return cudaGetLastError();
 }
 cudaError_t launch_rms_norm(const float *in, const float *w, float *out, uint32_t n, float eps, cudaStream_t s,
-                            uint64_t *launches) {
-    rms_norm_kernel<<<1, 1024, 0, s>>>(in, w, out, n, eps);
+                            uint64_t *launches, bool pdl) {
     *launches += 1;
-    return cudaGetLastError();
+    return launch_kernel(rms_norm_kernel, dim3(1), dim3(1024), 0, s, pdl, in, w, out, n, eps);
 }
 cudaError_t launch_rope_angles(float *q, float *k, uint32_t head_dim, uint32_t n_heads_q, uint32_t n_heads_k,
                                const RopeAngles &ang, cudaStream_t s, uint64_t *launches) {
@@ -329,18 +343,16 @@ cudaError_t launch_rope_angles(float *q, float *k, uint32_t head_dim, uint32_t n
 cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tmp, float *k_cache, float *v_cache,
                                  const float *cos_table, const float *sin_table, const uint32_t *pos_ptr,
                                  uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads, cudaStream_t s,
-                                 uint64_t *launches) {
+                                 uint64_t *launches, bool pdl) {
     uint32_t total = (n_heads + n_kv_heads) * (head_dim / 2);
-    rope_kv_write_kernel<<<(total + 255) / 256, 256, 0, s>>>(q, k_tmp, v_tmp, k_cache, v_cache, cos_table, sin_table,
-                                                             pos_ptr, head_dim, n_heads, n_kv_heads);
     *launches += 1;
-    return cudaGetLastError();
+    return launch_kernel(rope_kv_write_kernel, dim3((total + 255) / 256), dim3(256), 0, s, pdl, q, k_tmp, v_tmp, k_cache,
+                         v_cache, cos_table, sin_table, pos_ptr, head_dim, n_heads, n_kv_heads);
 }
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t s,
-                            uint64_t *launches) {
-    silu_mul_kernel<<<(n + 255) / 256, 256, 0, s>>>(gate, up, out, n);
+                            uint64_t *launches, bool pdl) {
     *launches += 1;
-    return cudaGetLastError();
+    return launch_kernel(silu_mul_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, gate, up, out, n);
 }
 cudaError_t launch_add(const float *a, const float *b, float *out, uint32_t n, cudaStream_t s, uint64_t *launches) {
     add_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, b, out, n);
@@ -365,7 +377,7 @@ cudaError_t launch_attn_value(const float *w, const float *v_cache, float *out, 
 cudaError_t launch_multihead_attention(const float *q, const float *k_cache, const float *v_cache, float *out,
                                        uint32_t hd, uint32_t seq_len, const uint32_t *pos_ptr, uint32_t max_seq_len,
                                        uint32_t n_heads, uint32_t n_kv_heads, uint32_t kv_stride, cudaStream_t s,
-                                       uint64_t *launches) {
+                                       uint64_t *launches, bool pdl) {
     uint32_t n_slices = kAttnThreads / hd ? kAttnThreads / hd : 1;
     size_t smem = ((size_t)hd + max_seq_len + (size_t)n_slices * hd) * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
@@ -374,16 +386,14 @@ cudaError_t launch_multihead_attention(const float *q, const float *k_cache, con
                                              (int)smem);
         if (e != cudaSuccess) return e;
     }
-    multihead_attention_kernel<<<n_heads, kAttnThreads, smem, s>>>(q, k_cache, v_cache, out, hd, seq_len, pos_ptr,
-                                                                   n_heads, n_kv_heads, kv_stride);
     *launches += 1;
-    return cudaGetLastError();
+    return launch_kernel(multihead_attention_kernel, dim3(n_heads), dim3(kAttnThreads), smem, s, pdl, q, k_cache,
+                         v_cache, out, hd, seq_len, pos_ptr, n_heads, n_kv_heads, kv_stride);
 }
-cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *out_token, uint32_t *pos_ptr_to_bump, cudaStream_t s,
-                          uint64_t *launches) {
-    argmax_kernel<<<1, 1024, 0, s>>>(v, n, out_token, pos_ptr_to_bump);
+cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *state, uint32_t *history, cudaStream_t s,
+                          uint64_t *launches, bool pdl) {
     *launches += 1;
-    return cudaGetLastError();
+    return launch_kernel(argmax_kernel, dim3(1), dim3(1024), 0, s, pdl, v, n, state, history);
 }
 cudaError_t launch_fill_bytes(void *p, size_t n, int value, cudaStream_t s, uint64_t *launches) {
     uint32_t v = (uint32_t)(value & 0xFF) * 0x01010101u;

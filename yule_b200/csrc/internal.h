@@ -3,6 +3,14 @@
 
 #include <cuda_runtime.h>
 
+#ifdef __CUDACC__
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor drains; everything it reads that the predecessor wrote must come after the wait.
+// Both are no-ops for a normal launch.
+__device__ __forceinline__ void yule_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void yule_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 #include <atomic>
 #include <cstdarg>
 #include <cstdint>
@@ -97,21 +105,57 @@ struct QmvArgs {
     uint32_t n_rows, n_cols, type, batch, x_stride, out_stride;
     // Optional fused prologue/epilogue used by the runner (null when unused):
     const float *residual = nullptr;  // out[row] = residual[row] + dot   (o-proj / down-proj)
+    bool pdl = false;                 // programmatic dependent launch
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
+
+// Q4_K tensor-pipe matvec with the neighbouring ops folded in (qmv_q4k_mma.cu).
+struct Q4kFused {
+    const uint8_t *w[3] = {nullptr, nullptr, nullptr};  // up to three matrices sharing x
+    float *out[3] = {nullptr, nullptr, nullptr};
+    uint32_t rows[3] = {0, 0, 0};
+    uint32_t out_stride[3] = {0, 0, 0};
+    uint32_t n_seg = 1;
+    const float *x = nullptr;  // [batch][x_stride]
+    uint32_t x_stride = 0, n_cols = 0, batch = 1;
+    const float *norm_w = nullptr;    // RMSNorm prologue on x when set
+    float eps = 0.f;
+    const float *residual = nullptr;  // out[0] += residual when set
+    bool swiglu_pair = false;         // w[0], w[1] = gate, up → out[0] = SiLU(gate)·up
+    bool pdl = false;                 // programmatic dependent launch
+};
+bool q4k_mma_supported(uint32_t n_cols, uint32_t batch);
+cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches);
+
+// Launch helper shared by every kernel: optional programmatic-dependent-launch attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 cudaError_t launch_dequantize(const uint8_t *w, uint32_t type, uint64_t n_blocks, float *out,
                               cudaStream_t s, uint64_t *launches);
 // Row `*token_ptr` (device) or `token` (when token_ptr is null) of a [vocab][dim] table.
 cudaError_t launch_embed_gather(const uint8_t *table, uint32_t type, uint32_t dim, uint32_t token,
                                 const uint32_t *token_ptr, float *out, cudaStream_t s,
-                                uint64_t *launches);
+                                uint64_t *launches, bool pdl = false);
 
 cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k,
                               cudaStream_t s, uint64_t *launches);
 cudaError_t launch_softmax(const float *in, float *out, uint32_t n, cudaStream_t s, uint64_t *launches);
 cudaError_t launch_rms_norm(const float *in, const float *w, float *out, uint32_t n, float eps,
-                            cudaStream_t s, uint64_t *launches);
+                            cudaStream_t s, uint64_t *launches, bool pdl = false);
 // cos/sin hold head_dim/2 entries for this position (host-computed), passed by value.
 struct RopeAngles {
     float cos[128];
@@ -121,7 +165,7 @@ cudaError_t launch_rope_angles(float *q, float *k, uint32_t head_dim, uint32_t n
                                uint32_t n_heads_k, const RopeAngles &ang, cudaStream_t s,
                                uint64_t *launches);
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t s,
-                            uint64_t *launches);
+                            uint64_t *launches, bool pdl = false);
 cudaError_t launch_add(const float *a, const float *b, float *out, uint32_t n, cudaStream_t s,
                        uint64_t *launches);
 cudaError_t launch_attn_score(const float *q, const float *k_cache, float *scores, uint32_t hd,
@@ -135,14 +179,16 @@ cudaError_t launch_multihead_attention(const float *q, const float *k_cache, con
                                        float *out, uint32_t hd, uint32_t seq_len,
                                        const uint32_t *pos_ptr, uint32_t max_seq_len, uint32_t n_heads,
                                        uint32_t n_kv_heads, uint32_t kv_stride, cudaStream_t s,
-                                       uint64_t *launches);
+                                       uint64_t *launches, bool pdl = false);
 // Runner kernels that read the position from device memory (graph-replayable).
 cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tmp, float *k_cache,
                                  float *v_cache, const float *cos_table, const float *sin_table,
                                  const uint32_t *pos_ptr, uint32_t head_dim, uint32_t n_heads,
-                                 uint32_t n_kv_heads, cudaStream_t s, uint64_t *launches);
-cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *out_token, uint32_t *pos_ptr_to_bump,
-                          cudaStream_t s, uint64_t *launches);
+                                 uint32_t n_kv_heads, cudaStream_t s, uint64_t *launches, bool pdl = false);
+// Greedy pick (ties to the highest index) into state[0]; when history is set also records it at
+// history[state[1]] and advances state[1].
+cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *state, uint32_t *history, cudaStream_t s,
+                          uint64_t *launches, bool pdl = false);
 cudaError_t launch_fill_bytes(void *p, size_t n, int value, cudaStream_t s, uint64_t *launches);
 
 }  // namespace yule

@@ -115,14 +115,14 @@ __device__ __forceinline__ void stage_x(const float *__restrict__ x, uint32_t x_
     }
     __syncthreads();
     if (want_sums) {
+        // one warp per 32-column group: lane i reads element i (no bank conflicts), shuffle tree
         const uint32_t n_sb = n_cols / 32;
-        for (uint32_t s = threadIdx.x; s < n_sb * NB; s += blockDim.x) {
+        const int lane = threadIdx.x & 31;
+        for (uint32_t s = threadIdx.x >> 5; s < n_sb * NB; s += blockDim.x >> 5) {
             uint32_t b = s / n_sb, sb = s % n_sb;
-            const float *p = xs + b * vstride + (PAD ? sb * 36 : sb * 32);
-            float acc = 0.f;
-#pragma unroll 8
-            for (int i = 0; i < 32; i++) acc += p[i];
-            xsum[s] = acc;
+            float v = xs[b * vstride + (PAD ? sb * 36 : sb * 32) + lane];
+            v = warp_sum(v);
+            if (lane == 0) xsum[s] = v;
         }
         __syncthreads();
     }
@@ -139,6 +139,8 @@ qmv_q4k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
                uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
                const float *__restrict__ residual) {
     extern __shared__ __align__(16) float smem[];
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     float *xs = smem;
     float *xsum = smem + (size_t)NB * n_cols;
     stage_x<NB, false>(x, x_stride, n_cols, xs, xsum, true);
@@ -231,6 +233,8 @@ qmv_q6k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
                uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
                const float *__restrict__ residual) {
     extern __shared__ __align__(16) float smem[];
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     float *xs = smem;
     stage_x<NB, false>(x, x_stride, n_cols, xs, nullptr, false);
 
@@ -306,6 +310,8 @@ qmv_q32_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
                uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
                const float *__restrict__ residual) {
     extern __shared__ __align__(16) float smem[];
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     float *xs = smem;
     stage_x<NB, true>(x, x_stride, n_cols, xs, nullptr, false);
 
@@ -410,6 +416,30 @@ constexpr size_t kMaxSmem = 200 * 1024;
 }  // namespace
 
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches) {
+    if (a.type == YULE_DTYPE_Q4_K && q4k_mma_supported(a.n_cols, 1)) {
+        // tensor-pipe path, up to four activation vectors per pass over the weights
+        uint32_t done = 0;
+        while (done < a.batch) {
+            uint32_t nb = a.batch - done < 4 ? a.batch - done : 4;
+            while (!q4k_mma_supported(a.n_cols, nb)) nb--;
+            Q4kFused f;
+            f.w[0] = a.w;
+            f.out[0] = a.out + (size_t)done * a.out_stride;
+            f.rows[0] = a.n_rows;
+            f.out_stride[0] = a.out_stride;
+            f.n_seg = 1;
+            f.x = a.x + (size_t)done * a.x_stride;
+            f.x_stride = a.x_stride;
+            f.n_cols = a.n_cols;
+            f.batch = nb;
+            f.residual = a.residual ? a.residual + (size_t)done * a.out_stride : nullptr;
+            f.pdl = a.pdl;
+            cudaError_t e = launch_q4k_mma(f, sm_count, s, launches);
+            if (e != cudaSuccess) return e;
+            done += nb;
+        }
+        return cudaSuccess;
+    }
     if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;
     uint32_t done = 0;
     while (done < a.batch) {
@@ -422,19 +452,45 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         QmvKernel k = nb == 4 ? pick_kernel<4>(a.type) : nb == 2 ? pick_kernel<2>(a.type) : pick_kernel<1>(a.type);
         if (!k) return cudaErrorInvalidValue;
         size_t smem = qmv_smem_bytes(a.type, a.n_cols, nb);
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
-        if (e != cudaSuccess) return e;
-        int occ = 1;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k, kThreads, smem);
-        if (e != cudaSuccess) return e;
-        if (occ < 1) occ = 1;
+        // attribute and occupancy are per (kernel, smem): remember the last answer per kernel
+        struct Cached {
+            QmvKernel k = nullptr;
+            size_t smem = 0;
+            int occ = 0;
+        };
+        static Cached cache[16];
+        static std::mutex cache_mu;
+        int occ = 0;
+        {
+            std::lock_guard<std::mutex> lock(cache_mu);
+            Cached *slot = nullptr;
+            for (auto &c : cache)
+                if (c.k == k || c.k == nullptr) {
+                    slot = &c;
+                    break;
+                }
+            if (slot && slot->k == k && slot->smem == smem) {
+                occ = slot->occ;
+            } else {
+                cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
+                if (e != cudaSuccess) return e;
+                e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k, kThreads, smem);
+                if (e != cudaSuccess) return e;
+                if (occ < 1) occ = 1;
+                if (slot) {
+                    slot->k = k;
+                    slot->smem = smem;
+                    slot->occ = occ;
+                }
+            }
+        }
         uint32_t max_ctas = (uint32_t)(sm_count * occ);
         uint32_t want = (a.n_rows + kWarps - 1) / kWarps;
         uint32_t grid = want < max_ctas ? want : max_ctas;
-        k<<<grid, kThreads, smem, s>>>(a.w, a.x + (size_t)done * a.x_stride, a.out + (size_t)done * a.out_stride,
-                                       a.n_rows, a.n_cols, a.x_stride, a.out_stride,
-                                       a.residual ? a.residual + (size_t)done * a.out_stride : nullptr);
-        e = cudaGetLastError();
+        cudaError_t e = launch_kernel(k, dim3(grid), dim3(kThreads), smem, s, a.pdl, a.w,
+                                      a.x + (size_t)done * a.x_stride, a.out + (size_t)done * a.out_stride, a.n_rows,
+                                      a.n_cols, a.x_stride, a.out_stride,
+                                      a.residual ? a.residual + (size_t)done * a.out_stride : (const float *)nullptr);
         if (e != cudaSuccess) return e;
         *launches += 1;
         done += nb;
@@ -507,6 +563,8 @@ __global__ void dequantize_kernel(const uint8_t *__restrict__ data, uint32_t typ
 __global__ void embed_gather_kernel(const uint8_t *__restrict__ table, uint32_t type, uint32_t dim, uint32_t token,
                                     const uint32_t *__restrict__ token_ptr, uint64_t row_bytes,
                                     float *__restrict__ out) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
     const uint32_t tok = token_ptr ? *token_ptr : token;
     const uint8_t *row = table + (uint64_t)tok * row_bytes;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
@@ -526,11 +584,11 @@ cudaError_t launch_dequantize(const uint8_t *w, uint32_t type, uint64_t n_blocks
 }
 
 cudaError_t launch_embed_gather(const uint8_t *table, uint32_t type, uint32_t dim, uint32_t token,
-                                const uint32_t *token_ptr, float *out, cudaStream_t s, uint64_t *launches) {
+                                const uint32_t *token_ptr, float *out, cudaStream_t s, uint64_t *launches, bool pdl) {
     uint64_t row_bytes = (uint64_t)(dim / block_size(type)) * block_bytes(type);
-    embed_gather_kernel<<<(dim + 255) / 256, 256, 0, s>>>(table, type, dim, token, token_ptr, row_bytes, out);
     *launches += 1;
-    return cudaGetLastError();
+    return launch_kernel(embed_gather_kernel, dim3((dim + 255) / 256), dim3(256), 0, s, pdl, table, type, dim, token,
+                         token_ptr, row_bytes, out);
 }
 
 }  // namespace yule

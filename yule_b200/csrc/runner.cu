@@ -10,8 +10,11 @@
 //      from one CUDA graph.
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
+#include <initializer_list>
 #include <string>
+#include <utility>
 
 #include "internal.h"
 
@@ -54,6 +57,7 @@ struct yule_cuda_runner {
 
     uint32_t pos = 0;
     bool fused = false;
+    bool pdl = true;  // programmatic dependent launch between the kernels of the graph
     uint32_t graph_kernels = 0;  // kernels replayed per graph launch
     bool finalized = false;
     bool have_next_token = false;  // d_state[0] holds the greedy continuation
@@ -133,6 +137,7 @@ int32_t norm_as_f32(yule_cuda_runner *r, const Tensor &t, const char *what, uint
 
 struct Step {
     yule_cuda_runner *r;
+    bool pdl = false;
     uint64_t n = 0;
     cudaError_t err = cudaSuccess;
     void ok(cudaError_t e) {
@@ -150,84 +155,144 @@ struct Step {
         a.x_stride = cols;
         a.out_stride = rows;
         a.residual = residual;
+        a.pdl = pdl;
         ok(launch_qmv(a, r->ctx->prop.multiProcessorCount, r->ctx->stream, &n));
     }
 };
 
-// Enqueues one token step.  `by_value` (mode 0): token and position are host values baked into
-// the launches.  Otherwise they are read from d_state, and the greedy pick is written back.
-cudaError_t enqueue_forward(yule_cuda_runner *r, bool by_value, uint32_t token, uint32_t pos, uint64_t *launches) {
+// Mode 0: one kernel per reference dispatch, token and position baked into the launches as host
+// values (gpu_runner.rs:296-695 in order; the embedding row is dequantised on the device).
+cudaError_t enqueue_forward_by_value(yule_cuda_runner *r, uint32_t token, uint32_t pos, uint64_t *launches) {
     const yule_runner_config &c = r->cfg;
     cudaStream_t s = r->ctx->stream;
     const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
     Step st{r};
-    const uint32_t *tok_ptr = by_value ? nullptr : r->d_state;
-    const uint32_t *pos_ptr = by_value ? nullptr : r->d_state + 1;
-
-    st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, token, tok_ptr,
+    st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, token, nullptr,
                               r->hidden, s, &st.n));
-
+    RopeAngles ang;
+    const uint32_t half = hd / 2;
+    for (uint32_t i = 0; i < half; i++) {
+        float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)hd);
+        float theta = (float)pos * freq;
+        ang.cos[i] = cosf(theta);
+        ang.sin[i] = sinf(theta);
+    }
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
-        if (by_value) {
-            st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
-        }
+        st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
         st.ok(launch_rms_norm(r->hidden, L.attn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
         st.qmv(L.attn_q, r->normed, r->q, qdim, dim);
         st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim, dim);
         st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim, dim);
-        if (by_value) {
-            RopeAngles ang;
-            const uint32_t half = hd / 2;
-            for (uint32_t i = 0; i < half; i++) {
-                float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)hd);
-                float theta = (float)pos * freq;
-                ang.cos[i] = cosf(theta);
-                ang.sin[i] = sinf(theta);
-            }
-            st.ok(launch_rope_angles(r->q, r->k_tmp, hd, c.n_heads, c.n_kv_heads, ang, s, &st.n));
-            const size_t off = (size_t)pos * kvdim;
-            st.ok(cudaMemcpyAsync(L.k_cache + off, r->k_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
-            st.ok(cudaMemcpyAsync(L.v_cache + off, r->v_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
-            st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, pos + 1, nullptr, pos + 1,
-                                             c.n_heads, c.n_kv_heads, kvdim, s, &st.n));
-            st.qmv(L.attn_output, r->attn_out, r->attn_proj, dim, qdim);
-            st.ok(launch_add(r->residual, r->attn_proj, r->hidden, dim, s, &st.n));
-            st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
-        } else {
-            st.ok(launch_rope_kv_write(r->q, r->k_tmp, r->v_tmp, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin,
-                                       pos_ptr, hd, c.n_heads, c.n_kv_heads, s, &st.n));
-            st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, 0, pos_ptr, c.max_seq_len,
-                                             c.n_heads, c.n_kv_heads, kvdim, s, &st.n));
-            // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
-            st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
-        }
+        st.ok(launch_rope_angles(r->q, r->k_tmp, hd, c.n_heads, c.n_kv_heads, ang, s, &st.n));
+        const size_t off = (size_t)pos * kvdim;
+        st.ok(cudaMemcpyAsync(L.k_cache + off, r->k_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
+        st.ok(cudaMemcpyAsync(L.v_cache + off, r->v_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
+        st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, pos + 1, nullptr, pos + 1,
+                                         c.n_heads, c.n_kv_heads, kvdim, s, &st.n));
+        st.qmv(L.attn_output, r->attn_out, r->attn_proj, dim, qdim);
+        st.ok(launch_add(r->residual, r->attn_proj, r->hidden, dim, s, &st.n));
+        st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
         st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
         st.qmv(L.ffn_gate, r->normed, r->gate, ff, dim);
         st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
         st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n));
-        if (by_value) {
-            st.qmv(L.ffn_down, r->gate, r->ffn_out, dim, ff);
-            st.ok(launch_add(r->residual, r->ffn_out, r->hidden, dim, s, &st.n));
-        } else {
-            st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
-        }
+        st.qmv(L.ffn_down, r->gate, r->ffn_out, dim, ff);
+        st.ok(launch_add(r->residual, r->ffn_out, r->hidden, dim, s, &st.n));
     }
     st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
-    if (!by_value) {
-        // greedy pick → d_history[pos] and d_state[0]; position advances for the next replay
-        st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, nullptr, s, &st.n));
-    }
     *launches += st.n;
     return st.err;
 }
 
-__global__ void record_and_advance_kernel(uint32_t *state, uint32_t *history) {
-    const uint32_t pos = state[1];
-    history[pos] = state[0];
-    state[1] = pos + 1;
+// Mode 1: the same token step with the small dispatches folded into the matvecs, token and
+// position read from d_state so that one captured graph serves every position, and every launch
+// marked for programmatic dependent launch.
+//   embed → per layer { [RMSNorm + Q/K/V] → [RoPE + KV write] → attention → [o-proj + residual]
+//                       → [RMSNorm + gate/up + SiLU·mul] → [down + residual] }
+//         → [RMSNorm + output] → [argmax + history + position advance]
+// Brackets are single kernels when the matrices involved are Q4_K; other formats fall back to a
+// separate RMSNorm / SiLU·mul kernel around the per-matrix matvec.
+cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
+    const yule_runner_config &c = r->cfg;
+    cudaStream_t s = r->ctx->stream;
+    const int sms = r->ctx->prop.multiProcessorCount;
+    const bool pdl = r->pdl;
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    Step st{r};
+    st.pdl = pdl;
+    const uint32_t *tok_ptr = r->d_state, *pos_ptr = r->d_state + 1;
+    auto all_q4k = [&](std::initializer_list<const Tensor *> ts, uint32_t cols) {
+        for (const Tensor *t : ts)
+            if (t->type != YULE_DTYPE_Q4_K) return false;
+        return q4k_mma_supported(cols, 1);
+    };
+    // x → (optional RMSNorm) → up to three Q4_K matrices in one launch
+    auto fused = [&](std::initializer_list<std::pair<const Tensor *, std::pair<float *, uint32_t>>> segs, const float *x,
+                     uint32_t cols, const float *norm_w, const float *residual, bool pair) {
+        Q4kFused f;
+        uint32_t i = 0;
+        for (auto &sg : segs) {
+            f.w[i] = (const uint8_t *)sg.first->buf.ptr;
+            f.out[i] = sg.second.first;
+            f.rows[i] = sg.second.second;
+            f.out_stride[i] = sg.second.second;
+            i++;
+        }
+        f.n_seg = i;
+        f.x = x;
+        f.x_stride = cols;
+        f.n_cols = cols;
+        f.batch = 1;
+        f.norm_w = norm_w;
+        f.eps = c.norm_eps;
+        f.residual = residual;
+        f.swiglu_pair = pair;
+        f.pdl = pdl;
+        st.ok(launch_q4k_mma(f, sms, s, &st.n));
+    };
+
+    st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, 0, tok_ptr, r->hidden,
+                              s, &st.n, pdl));
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        Layer &L = r->layers[l];
+        if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
+            fused({{&L.attn_q, {r->q, qdim}}, {&L.attn_k, {r->k_tmp, kvdim}}, {&L.attn_v, {r->v_tmp, kvdim}}}, r->hidden,
+                  dim, L.attn_norm_f32, nullptr, false);
+        } else {
+            st.ok(launch_rms_norm(r->hidden, L.attn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
+            st.qmv(L.attn_q, r->normed, r->q, qdim, dim);
+            st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim, dim);
+            st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim, dim);
+        }
+        st.ok(launch_rope_kv_write(r->q, r->k_tmp, r->v_tmp, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin, pos_ptr, hd,
+                                   c.n_heads, c.n_kv_heads, s, &st.n, pdl));
+        st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, 0, pos_ptr, c.max_seq_len,
+                                         c.n_heads, c.n_kv_heads, kvdim, s, &st.n, pdl));
+        // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
+        st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
+        if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
+            fused({{&L.ffn_gate, {r->gate, ff}}, {&L.ffn_up, {r->up, ff}}}, r->hidden, dim, L.ffn_norm_f32, nullptr, true);
+        } else {
+            st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
+            st.qmv(L.ffn_gate, r->normed, r->gate, ff, dim);
+            st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
+            st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n, pdl));
+        }
+        st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
+    }
+    const Tensor &out_w = r->output.set ? r->output : r->token_embd;
+    if (all_q4k({&out_w}, dim)) {
+        fused({{&out_w, {r->logits, c.vocab_size}}}, r->hidden, dim, r->output_norm_f32, nullptr, false);
+    } else {
+        st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
+        st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
+    }
+    st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, r->d_history, s, &st.n, pdl));
+    *launches += st.n;
+    return st.err;
 }
 
 int32_t finalize(yule_cuda_runner *r) {
@@ -271,12 +336,7 @@ int32_t ensure_graph(yule_cuda_runner *r) {
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
     YULE_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
     uint64_t n = 0;
-    cudaError_t e = enqueue_forward(r, false, 0, 0, &n);
-    if (e == cudaSuccess) {
-        record_and_advance_kernel<<<1, 1, 0, s>>>(r->d_state, r->d_history);
-        e = cudaGetLastError();
-        n += 1;
-    }
+    cudaError_t e = enqueue_forward_graph(r, &n);
     cudaError_t e2 = cudaStreamEndCapture(s, &graph);
     if (e != cudaSuccess || e2 != cudaSuccess) {
         if (graph) cudaGraphDestroy(graph);
@@ -313,7 +373,7 @@ int32_t step(yule_cuda_runner *r, uint32_t token, bool token_from_device) {
     cudaStream_t s = r->ctx->stream;
     if (!is_fused(r)) {
         uint64_t n = 0;
-        cudaError_t e = enqueue_forward(r, true, token, r->pos, &n);
+        cudaError_t e = enqueue_forward_by_value(r, token, r->pos, &n);
         r->ctx->launches.fetch_add(n);
         if (e != cudaSuccess) return fail_cuda(e, "token step");
     } else {
@@ -363,6 +423,7 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     r->ctx = ctx;
     r->cfg = c;
     r->fused = c.fused != 0;
+    if (const char *e = getenv("YULE_CUDA_PDL")) r->pdl = atoi(e) != 0;
     r->layers.resize(c.n_layers);
     const uint32_t hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd;
     int32_t rc = YULE_OK;

@@ -1,0 +1,77 @@
+"""Matvec micro-benchmark over the C ABI: one dtype and shape, CUDA-event timed.
+
+    python -m yule_b200.microbench --dtype Q4_K --rows 5632 --cols 2048 [--batch 1] [--iters 200] [--ring]
+
+Without ``--ring`` the weight tensor is read again and again (small tensors stay in L2 — that number is
+labelled ``l2_resident``).  With ``--ring`` the launches rotate over copies of the tensor that together
+exceed twice the L2 capacity, so every launch streams from HBM.  Launches are captured into one CUDA
+graph and replayed; the time per launch is the graph time divided by the launch count.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import numpy as np
+
+from . import CudaB200Backend, DType, matvec_bytes, synth
+
+
+def run(backend, dtype: DType, rows: int, cols: int, batch: int, iters: int, ring: bool, reps: int = 5) -> dict:
+    per = dtype.tensor_bytes(rows, cols)
+    copies = max(1, -(-2 * 2 * 126 * 2 ** 20 // per)) if ring else 1  # ≥ 4 x L2 in total
+    copies = min(copies, max(1, (24 << 30) // per))
+    base = synth.random_blocks(dtype, 1, rows * cols // dtype.block_size)
+    wh = backend.allocate(per * copies)
+    tmp = backend.upload(base)
+    for c in range(copies):
+        backend.copy_buffer_offset(tmp, wh, 0, c * per, per)
+    backend.free(tmp)
+    xh = backend.upload(synth.normal(2, batch * cols))
+    oh = backend.allocate(batch * rows * 4)
+    backend.graph_begin()
+    for i in range(iters):
+        if batch == 1:
+            backend.quantized_matmul_at(wh, (i % copies) * per, xh, oh, rows, cols, dtype)
+        else:
+            backend.quantized_matmul_batched(wh, xh, oh, rows, cols, dtype, batch)
+    graph = backend.graph_end()
+    for _ in range(3):
+        backend.graph_launch(graph)
+    backend.synchronize()
+    times = []
+    for _ in range(reps):
+        backend.event_reset()
+        e0 = backend.event_record()
+        backend.graph_launch(graph)
+        e1 = backend.event_record()
+        times.append(backend.event_elapsed_ms(e0, e1))
+    y = backend.download(oh, batch * rows)
+    backend.graph_destroy(graph)
+    for h in (wh, xh, oh):
+        backend.free(h)
+    us = statistics.median(times) * 1e3 / iters
+    nbytes = matvec_bytes(dtype, rows, cols, batch)
+    return {"dtype": dtype.name, "rows": rows, "cols": cols, "batch": batch, "mode": "hbm_ring" if ring else "l2_resident",
+            "copies": copies, "us_per_launch": round(us, 3), "bytes_per_launch": nbytes,
+            "gbs": round(nbytes / us / 1e3, 1), "nan_outputs": int(np.isnan(y).sum())}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--dtype", default="Q4_K")
+    ap.add_argument("--rows", type=int, default=5632)
+    ap.add_argument("--cols", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--ring", action="store_true")
+    args = ap.parse_args()
+    backend = CudaB200Backend(0)
+    print(json.dumps(run(backend, DType[args.dtype], args.rows, args.cols, args.batch, args.iters, args.ring)))
+    backend.close()
+
+
+if __name__ == "__main__":
+    main()
