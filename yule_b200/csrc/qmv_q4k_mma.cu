@@ -46,7 +46,9 @@ constexpr int kWarps = 8;  // warps per group: one per super-block slot of a til
 
 __device__ __forceinline__ uint4 ld_stream_u4(const uint4 *p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    // L1-allocating on purpose: neighbouring 16-byte pieces share 32-byte sectors, and the second
+    // request then merges with the first in L1 instead of going to L2 again.
+    asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
@@ -150,9 +152,13 @@ __device__ __forceinline__ void word_to_frags(uint32_t w, const RowScales &s, ui
 //          The eight (part, t) combinations a warp reads at once are 128 contiguous bytes.
 //   sb[v]  half2 index (blk*2 + part)*4 + t = 2^-6 · {Σ sub-block 2t, Σ sub-block 2t+1}
 //   inv_scale[v] = 2^-e
+//   sf[v]  float index c/32 = Σ of the 32 columns (scaled by 2^e), for the batch-1 path
+//   zb     64 zeroed uint4: B fragments of lanes that feed an all-zero column
 struct SmemLayout {
     uint4 *xb;
     uint32_t *sb;
+    float *sf;
+    uint4 *zb;
     float *inv_scale;
     float *partial;  // [2 groups][kRoundSlots][kWarps][4 vectors][16 rows]
     float *red;      // reduction scratch, 2 × 32 floats
@@ -163,6 +169,7 @@ constexpr int kRoundSlots = 8;   // (tile, matrix) slots whose partial sums a gr
 
 __host__ __device__ inline size_t xb_bytes(uint32_t n_cols, uint32_t nb) { return (size_t)nb * n_cols * 4; }
 __host__ __device__ inline size_t sb_bytes(uint32_t n_cols, uint32_t nb) { return (size_t)nb * (n_cols / 32) * 4; }
+constexpr size_t kZeroBytes = 64 * sizeof(uint4);
 constexpr size_t kPartialBytes = (size_t)kGroups * kRoundSlots * kWarps * 4 * 16 * sizeof(float);
 
 __device__ __forceinline__ SmemLayout carve(unsigned char *base, uint32_t n_cols, uint32_t nb) {
@@ -172,7 +179,11 @@ __device__ __forceinline__ SmemLayout carve(unsigned char *base, uint32_t n_cols
     off += xb_bytes(n_cols, nb);
     s.sb = reinterpret_cast<uint32_t *>(base + off);
     off += sb_bytes(n_cols, nb);
+    s.sf = reinterpret_cast<float *>(base + off);
+    off += sb_bytes(n_cols, nb);
     off = (off + 15) & ~(size_t)15;
+    s.zb = reinterpret_cast<uint4 *>(base + off);
+    off += kZeroBytes;
     s.inv_scale = reinterpret_cast<float *>(base + off);
     off += 4 * sizeof(float);
     s.partial = reinterpret_cast<float *>(base + off);
@@ -182,9 +193,9 @@ __device__ __forceinline__ SmemLayout carve(unsigned char *base, uint32_t n_cols
 }
 
 size_t smem_bytes(uint32_t n_cols, uint32_t nb) {
-    size_t off = xb_bytes(n_cols, nb) + sb_bytes(n_cols, nb);
+    size_t off = xb_bytes(n_cols, nb) + 2 * sb_bytes(n_cols, nb);
     off = (off + 15) & ~(size_t)15;
-    return off + 4 * sizeof(float) + kPartialBytes + 64 * sizeof(float) + 16;
+    return off + kZeroBytes + 4 * sizeof(float) + kPartialBytes + 64 * sizeof(float) + 16;
 }
 
 constexpr int kThreadsCta = kGroups * kWarps * 32;  // 512
@@ -197,6 +208,7 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
                                                   float eps) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     constexpr int NW = kThreadsCta / 32;
+    if (threadIdx.x < 64) sm.zb[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
     for (uint32_t v = 0; v < nb; v++) {
         const float *xv = x + (size_t)v * x_stride;
         float ss = 0.f, mx = 0.f;
@@ -274,6 +286,7 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
             s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
             s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
             if ((lane & 3) == 0) {
+                sm.sf[(size_t)v * (n_cols / 32) + (c >> 5)] = s8;
                 // 32 values below 2^14 can sum to 2^19: keep Σ·2^-6 (exact) so fp16 cannot overflow;
                 // unpack_scales folds the 2^6 back into dmin
                 s8 *= 0.015625f;
@@ -328,6 +341,84 @@ __device__ __forceinline__ void consume_block(const BlockLoads (&ld)[NR], uint32
         acc[NR - 1][0] = fmaf(-rs[NR - 1].dmin, dm[2], acc[NR - 1][0]);
         acc[NR - 1][1] = fmaf(rs[NR - 1].d, dl[3] + dh[3], acc[NR - 1][1]);
         acc[NR - 1][1] = fmaf(-rs[NR - 1].dmin, dm[3], acc[NR - 1][1]);
+    }
+}
+
+// ── batch-1 path: sub-blocks in the N dimension ─────────────────────────────────────────────
+// B column n = 4·part + t' carries x (part 0 = hi, 1 = lo) only at the k slots that lane t' feeds,
+// zeros elsewhere.  Those slots belong to one sub-block (2t' for the low-nibble MMA, 2t'+1 for the
+// high-nibble one), so D[row][n] is that sub-block's Σ q·x whatever the k order — and the weights
+// go in unscaled: the nibble's bits are used as an fp16 subnormal (q·2^-24, or 16q·2^-24 for a
+// high nibble), one AND per pair of weights.  Lane (g, t) ends up with columns 2t, 2t+1 =
+// groups 2u, 2u+1 (u = t&1) of part t>>1, i.e. sub-blocks 4u..4u+3, and applies their scales.
+struct RowScalesF {
+    float sc[4];  // sc[4u + i] · d · 2^24 (i even: low-nibble MMAs) or · d · 2^20 (i odd)
+    float mn[4];  // mn[4u + i] · dmin, zero in the lanes of the lo part (mins are charged once)
+};
+
+__device__ __forceinline__ RowScalesF unpack_scales_f(const uint4 &hdr, int u, bool charge_mins) {
+    uint32_t sc4, mn4;  // four 6-bit values each, one per byte (dequant.rs:176-190)
+    if (u == 0) {
+        sc4 = hdr.y & 0x3F3F3F3Fu;
+        mn4 = hdr.z & 0x3F3F3F3Fu;
+    } else {
+        sc4 = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+        mn4 = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+    }
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+    const float dmin = charge_mins ? __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16))) : 0.f;
+    const float d24 = d * 16777216.0f, d20 = d * 1048576.0f;
+    const float k23 = 8388608.0f;
+    RowScalesF r;
+    r.sc[0] = (__uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7440)) - k23) * d24;
+    r.sc[1] = (__uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7441)) - k23) * d20;
+    r.sc[2] = (__uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7442)) - k23) * d24;
+    r.sc[3] = (__uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7443)) - k23) * d20;
+    r.mn[0] = (__uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7440)) - k23) * dmin;
+    r.mn[1] = (__uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7441)) - k23) * dmin;
+    r.mn[2] = (__uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7442)) - k23) * dmin;
+    r.mn[3] = (__uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7443)) - k23) * dmin;
+    return r;
+}
+
+template <int NR>
+__device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR], const uint4 *bp, const float *sfp, int u,
+                                                     bool charge_mins, float (&acc)[NR][2]) {
+    float dl[4] = {0.f, 0.f, 0.f, 0.f}, dh[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int wp = 0; wp < 4; wp++) {
+        const uint4 bl = bp[wp * 8], bh = bp[32 + wp * 8];
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int wi = 2 * wp + e;
+            uint32_t lo02[2], lo13[2], hi02[2], hi13[2];
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                const uint32_t w = word_of(ld[r], wi), w8 = w >> 8;
+                lo02[r] = w & 0x000F000Fu;
+                lo13[r] = w8 & 0x000F000Fu;
+                hi02[r] = w & 0x00F000F0u;
+                hi13[r] = w8 & 0x00F000F0u;
+            }
+            if (NR == 1) lo02[1] = lo13[1] = hi02[1] = hi13[1] = 0u;
+            mma_16816(dl, lo02[0], lo02[1], lo13[0], lo13[1], e ? bl.z : bl.x, e ? bl.w : bl.y);
+            mma_16816(dh, hi02[0], hi02[1], hi13[0], hi13[1], e ? bh.z : bh.x, e ? bh.w : bh.y);
+        }
+    }
+    const float4 sx = *reinterpret_cast<const float4 *>(sfp);  // Σx of sub-blocks 4u..4u+3
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+        const RowScalesF rs = unpack_scales_f(ld[r].hdr, u, charge_mins);
+        float a = acc[r][0];
+        a = fmaf(rs.sc[0], dl[2 * r + 0], a);
+        a = fmaf(rs.sc[1], dh[2 * r + 0], a);
+        a = fmaf(rs.sc[2], dl[2 * r + 1], a);
+        a = fmaf(rs.sc[3], dh[2 * r + 1], a);
+        float m = rs.mn[0] * sx.x;
+        m = fmaf(rs.mn[1], sx.y, m);
+        m = fmaf(rs.mn[2], sx.z, m);
+        m = fmaf(rs.mn[3], sx.w, m);
+        acc[r][0] = a - m;
     }
 }
 
@@ -397,7 +488,7 @@ struct UnitCursor {
 // group multiplies super-blocks w, w+8, …; a warp's (tile, matrix, super-block) units form one
 // sequence that is prefetched DEPTH units ahead.  In pair mode a tile is the gate rows followed by
 // the same rows of up.  The activations are staged once per CTA.
-template <int ROWS, int DEPTH>
+template <int ROWS, int DEPTH, bool SUBCOL>
 __global__ void __launch_bounds__(kThreadsCta, 1)
 qmv_q4k_mma_kernel(const Q4kMmaParams p) {
     constexpr int NR = ROWS / 8;
@@ -444,6 +535,13 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
     const uint32_t vec = (uint32_t)(g >> 1) < p.batch ? (g >> 1) : 0;
     const uint4 *xb_lane = sm.xb + (size_t)vec * (p.n_cols / 4) + (g & 1) * 4 + t;
     const uint32_t *sb_lane = sm.sb + (size_t)vec * (p.n_cols / 32) + (g & 1) * 4 + t;
+    // batch-1 path: lane (g, t) feeds column g; that column is live only for g = t (hi part) and
+    // g = t + 4 (lo part), every other lane reads zeros
+    const bool feeds = (g & 3) == t;
+    const uint4 *sub_base = feeds ? sm.xb + (g >> 2) * 4 + t : sm.zb;
+    const uint32_t sub_stride = feeds ? 64u : 0u;
+    const int u = t & 1;
+    const bool charge_mins = t < 2;
 
     // Cross-warp sums of the tiles [k0, k0+kn) of this group, then the epilogue.  Every warp of
     // the group calls this once per round.
@@ -468,7 +566,14 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
             for (uint32_t q = 0; q < nq; q++) {
                 const uint32_t sl = kk * nq + q;
                 float sacc = 0.f;  // fixed order over the warps: deterministic
-                for (uint32_t w2 = 0; w2 < n_warps_used; w2++) sacc += partial[((sl * kWarps + w2) * 4 + v) * 16 + rr];
+                if (SUBCOL) {
+                    // the four t lanes hold (hi, lo) × (sub-blocks 0..3, 4..7): one vector, four addends
+                    for (uint32_t w2 = 0; w2 < n_warps_used; w2++)
+#pragma unroll
+                        for (int tt = 0; tt < 4; tt++) sacc += partial[((sl * kWarps + w2) * 4 + tt) * 16 + rr];
+                } else {
+                    for (uint32_t w2 = 0; w2 < n_warps_used; w2++) sacc += partial[((sl * kWarps + w2) * 4 + v) * 16 + rr];
+                }
                 sums[q] = sacc * inv_scale;
             }
             const size_t o = (size_t)v * p.out_stride[seg] + row;
@@ -500,7 +605,13 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
 #pragma unroll
         for (int i = 0; i < DEPTH; i++) {
             if (base + i < total_units) {
-                consume_block<NR>(buf[i], wid + kWarps * in_slot, t, xb_lane, sb_lane, acc);
+                if (SUBCOL) {
+                    const uint32_t blk = wid + kWarps * in_slot;
+                    consume_block_subcol<NR>(buf[i], sub_base + (size_t)blk * sub_stride, sm.sf + (size_t)blk * 8 + 4 * u, u,
+                                             charge_mins, acc);
+                } else {
+                    consume_block<NR>(buf[i], wid + kWarps * in_slot, t, xb_lane, sb_lane, acc);
+                }
                 if (issued < total_units) {
                     issue_loads<NR>(buf[i], ld_cur.rowp, wid + kWarps * ld_cur.j, t);
                     issued++;
@@ -526,9 +637,9 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
     }
 }
 
-template <int ROWS, int DEPTH>
+template <int ROWS, int DEPTH, bool SUBCOL>
 cudaError_t launch_variant(const Q4kMmaParams &p, int sm_count, size_t smem, bool pdl, cudaStream_t s) {
-    auto kern = qmv_q4k_mma_kernel<ROWS, DEPTH>;
+    auto kern = qmv_q4k_mma_kernel<ROWS, DEPTH, SUBCOL>;
     // per instantiation: the opt-in for large dynamic shared memory
     static bool attr_done = false;
     static std::mutex mu;
@@ -583,8 +694,13 @@ cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint
     p.residual = f.residual;
     if (n_tiles == 0) return cudaSuccess;
     const size_t smem = smem_bytes(f.n_cols, f.batch);
-    cudaError_t e = tile_rows == 8 ? launch_variant<8, 4>(p, sm_count, smem, f.pdl, s)
-                                   : launch_variant<16, 2>(p, sm_count, smem, f.pdl, s);
+    cudaError_t e;
+    if (f.batch == 1)
+        e = tile_rows == 8 ? launch_variant<8, 4, true>(p, sm_count, smem, f.pdl, s)
+                           : launch_variant<16, 2, true>(p, sm_count, smem, f.pdl, s);
+    else
+        e = tile_rows == 8 ? launch_variant<8, 4, false>(p, sm_count, smem, f.pdl, s)
+                           : launch_variant<16, 2, false>(p, sm_count, smem, f.pdl, s);
     if (e != cudaSuccess) return e;
     *launches += 1;
     return cudaSuccess;
