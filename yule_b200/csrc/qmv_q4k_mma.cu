@@ -201,8 +201,11 @@ size_t smem_bytes(uint32_t n_cols, uint32_t nb) {
 constexpr int kThreadsCta = kGroups * kWarps * 32;  // 512
 
 // Stage NB activation vectors: optional RMSNorm, power-of-two normalisation, hi/lo split,
-// fragment order, per-32-column sums.  Two passes over x (it is small and L2-resident).  Each
-// thread handles 8 consecutive columns.
+// fragment order, per-32-column sums.  Each thread owns groups of 8 consecutive columns; the first
+// kCache groups (16 K columns per CTA) stay in registers between the reduction pass and the
+// conversion pass, so x is fetched from L2 only once; longer vectors re-read the remainder.
+constexpr int kCache = 4;
+
 __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const float *__restrict__ x, uint32_t x_stride,
                                                   uint32_t n_cols, uint32_t nb, const float *__restrict__ norm_w,
                                                   float eps) {
@@ -211,18 +214,36 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
     if (threadIdx.x < 64) sm.zb[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
     for (uint32_t v = 0; v < nb; v++) {
         const float *xv = x + (size_t)v * x_stride;
+        float cache[kCache][8];
         float ss = 0.f, mx = 0.f;
-        for (uint32_t c = threadIdx.x * 4; c < n_cols; c += kThreadsCta * 4) {
-            float4 a = *reinterpret_cast<const float4 *>(xv + c);
-            ss = fmaf(a.x, a.x, ss);
-            ss = fmaf(a.y, a.y, ss);
-            ss = fmaf(a.z, a.z, ss);
-            ss = fmaf(a.w, a.w, ss);
+        auto load8 = [&](uint32_t c, float (&a)[8]) {
+            *reinterpret_cast<float4 *>(a) = *reinterpret_cast<const float4 *>(xv + c);
+            *reinterpret_cast<float4 *>(a + 4) = *reinterpret_cast<const float4 *>(xv + c + 4);
+        };
+        auto reduce8 = [&](uint32_t c, const float (&a)[8]) {
+            float gw[8];
             if (norm_w) {
-                const float4 g = *reinterpret_cast<const float4 *>(norm_w + c);
-                a.x *= g.x; a.y *= g.y; a.z *= g.z; a.w *= g.w;
+                *reinterpret_cast<float4 *>(gw) = *reinterpret_cast<const float4 *>(norm_w + c);
+                *reinterpret_cast<float4 *>(gw + 4) = *reinterpret_cast<const float4 *>(norm_w + c + 4);
             }
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                ss = fmaf(a[i], a[i], ss);
+                mx = fmaxf(mx, fabsf(norm_w ? a[i] * gw[i] : a[i]));
+            }
+        };
+#pragma unroll
+        for (int k = 0; k < kCache; k++) {
+            const uint32_t c = (threadIdx.x + k * kThreadsCta) * 8;
+            if (c < n_cols) {
+                load8(c, cache[k]);
+                reduce8(c, cache[k]);
+            }
+        }
+        for (uint32_t c = (threadIdx.x + kCache * kThreadsCta) * 8; c < n_cols; c += kThreadsCta * 8) {
+            float a[8];
+            load8(c, a);
+            reduce8(c, a);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -255,10 +276,8 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
         if (threadIdx.x == 0) sm.inv_scale[v] = inv_scale;
         uint4 *xb = sm.xb + (size_t)v * (n_cols / 4);
         __half *sbh = reinterpret_cast<__half *>(sm.sb + (size_t)v * (n_cols / 32));
-        for (uint32_t c = threadIdx.x * 8; c < n_cols; c += kThreadsCta * 8) {
-            float a[8];
-            *reinterpret_cast<float4 *>(a) = *reinterpret_cast<const float4 *>(xv + c);
-            *reinterpret_cast<float4 *>(a + 4) = *reinterpret_cast<const float4 *>(xv + c + 4);
+        float *sf = sm.sf + (size_t)v * (n_cols / 32);
+        auto convert8 = [&](uint32_t c, float (&a)[8]) {
             if (norm_w) {
                 float gw[8];
                 *reinterpret_cast<float4 *>(gw) = *reinterpret_cast<const float4 *>(norm_w + c);
@@ -268,14 +287,13 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
                 for (int i = 0; i < 8; i++) a[i] = a[i] * inv_rms * gw[i];
             }
             __half hi[8], lo[8];
-            float s8 = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 a[i] *= scale;  // exact (power of two)
                 hi[i] = __float2half_rn(a[i]);
                 lo[i] = __float2half_rn(a[i] - __half2float(hi[i]));
             }
-            s8 = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+            float s8 = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
             const uint32_t blk = c >> 8, t = (c >> 6) & 3, h = (c >> 5) & 1, wp = (c >> 3) & 3;
             const uint32_t idx = ((blk * 2 + h) * 4 + wp) * 8 + t;
             xb[idx] = make_uint4(h2_as_u32(__halves2half2(hi[0], hi[2])), h2_as_u32(__halves2half2(hi[1], hi[3])),
@@ -286,7 +304,7 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
             s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
             s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
             if ((lane & 3) == 0) {
-                sm.sf[(size_t)v * (n_cols / 32) + (c >> 5)] = s8;
+                sf[c >> 5] = s8;
                 // 32 values below 2^14 can sum to 2^19: keep Σ·2^-6 (exact) so fp16 cannot overflow;
                 // unpack_scales folds the 2^6 back into dmin
                 s8 *= 0.015625f;
@@ -296,6 +314,17 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
                 sbh[hidx] = sh;
                 sbh[hidx + 8] = __float2half_rn(s8 - __half2float(sh));  // part 1 sits 4 half2 further on
             }
+        };
+        // n_cols is a multiple of 256, so whole warps are in or out of every step (the shuffles are safe)
+#pragma unroll
+        for (int k = 0; k < kCache; k++) {
+            const uint32_t c = (threadIdx.x + k * kThreadsCta) * 8;
+            if (c < n_cols) convert8(c, cache[k]);
+        }
+        for (uint32_t c = (threadIdx.x + kCache * kThreadsCta) * 8; c < n_cols; c += kThreadsCta * 8) {
+            float a[8];
+            load8(c, a);
+            convert8(c, a);
         }
     }
     __syncthreads();
