@@ -145,6 +145,12 @@ int32_t yule_cuda_quantized_matmul_batched(yule_cuda_ctx *ctx, yule_buffer weigh
 int32_t yule_cuda_quantized_matmul_at(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset,
                                       yule_buffer input, yule_buffer output, uint32_t n_rows,
                                       uint32_t n_cols, uint32_t gguf_type);
+/* Optional, once per weight tensor: lets the library keep a device-side copy of the tensor in the
+ * layout its fastest kernel wants (today: Q6_K regrouped into 16-byte-aligned planes, same byte
+ * count).  Later quantized_matmul calls on the same handle, type and shape use it.  Writing to the
+ * buffer drops the copy.  A no-op for formats that need none.  Results are unchanged. */
+int32_t yule_cuda_prepare_weights(yule_cuda_ctx *ctx, yule_buffer weights, uint32_t gguf_type,
+                                  uint32_t n_rows, uint32_t n_cols);
 /* dequant_block over a whole tensor (yule-core/src/dequant.rs:1232): n_blocks
  * raw blocks → n_blocks*block_size floats.  Results are bit-identical to
  * yule-core's scalar dequantisers. */

@@ -130,3 +130,35 @@ def test_error_paths(backend):
     backend.quantized_matmul(w, x, o, 0, 256, DType.Q4_K)  # zero rows: nothing to do
     for h in (w, x, o):
         backend.free(h)
+
+
+@pytest.mark.parametrize("n_rows,blocks_per_row", [(1, 1), (7, 2), (129, 22), (2048, 22), (300, 56), (4736, 8), (32000, 8)])
+def test_prepared_q6k_matches_scalar_reference(backend, oracle, n_rows, blocks_per_row):
+    """prepare_weights keeps a planar device copy of a Q6_K tensor; the matvec that reads it must
+    give the same numbers as the scalar reference (and as the raw-layout kernel)."""
+    dtype, n_cols = DType.Q6_K, blocks_per_row * 256
+    w, x = case(dtype, n_rows, n_cols, seed=300 + n_rows)
+    wh, xh, oh = backend.upload(w), backend.upload(x), backend.allocate(n_rows * 4)
+    backend.quantized_matmul(wh, xh, oh, n_rows, n_cols, dtype)
+    raw = backend.download(oh, n_rows)
+    backend.prepare_weights(wh, dtype, n_rows, n_cols)
+    backend.quantized_matmul(wh, xh, oh, n_rows, n_cols, dtype)
+    y = backend.download(oh, n_rows)
+    ref = oracle.qmv(int(dtype), w, x, n_rows, n_cols)
+    assert guarded_rel_err(y, ref) <= REL_TOL and guarded_rel_err(raw, ref) <= REL_TOL
+    # writing to the buffer drops the prepared copy: results follow the new bytes
+    w2 = synth.random_blocks(dtype, 999, n_rows * blocks_per_row)
+    backend.copy_to_device(w2, wh)
+    backend.quantized_matmul(wh, xh, oh, n_rows, n_cols, dtype)
+    assert guarded_rel_err(backend.download(oh, n_rows), oracle.qmv(int(dtype), w2, x, n_rows, n_cols)) <= REL_TOL
+    for h in (wh, xh, oh):
+        backend.free(h)
+
+
+def test_prepare_weights_is_a_noop_for_other_formats(backend):
+    for dt in (DType.Q4_K, DType.Q8_0, DType.Q4_0):
+        w = backend.upload(synth.random_blocks(dt, 1, 8 * (256 // dt.block_size)))
+        backend.prepare_weights(w, dt, 8, 256)
+        with pytest.raises(YuleGpuError):
+            backend.prepare_weights(w, dt, 9, 256)  # tensor larger than the buffer
+        backend.free(w)

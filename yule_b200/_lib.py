@@ -48,6 +48,7 @@ _SIGNATURES = {
     "yule_cuda_quantized_matmul": [vp, u64, u64, u64, u32, u32, u32],
     "yule_cuda_quantized_matmul_batched": [vp, u64, u64, u64, u32, u32, u32, u32, u32, u32],
     "yule_cuda_quantized_matmul_at": [vp, u64, size_t, u64, u64, u32, u32, u32],
+    "yule_cuda_prepare_weights": [vp, u64, u32, u32, u32],
     "yule_cuda_dequantize": [vp, u64, u32, u64, u64],
     "yule_cuda_multihead_attention": [vp, u64, u64, u64, u64, u32, u32, u32, u32, u32],
     "yule_cuda_embed_gather": [vp, u64, u32, u32, u32, u64],

@@ -175,6 +175,10 @@ class CudaB200Backend:
         _check(self._lib.yule_cuda_quantized_matmul_at(self._ctx, weights.id, weight_offset, input.id, output.id,
                                                        n_rows, n_cols, int(dtype)))
 
+    def prepare_weights(self, weights: BufferHandle, dtype: DType, n_rows: int, n_cols: int) -> None:
+        """Optional, once per tensor: lets the library keep a device copy in its fastest layout."""
+        _check(self._lib.yule_cuda_prepare_weights(self._ctx, weights.id, int(dtype), n_rows, n_cols))
+
     def dequantize(self, weights: BufferHandle, dtype: DType, n_blocks: int, out_f32: BufferHandle) -> None:
         _check(self._lib.yule_cuda_dequantize(self._ctx, weights.id, int(dtype), n_blocks, out_f32.id))
 

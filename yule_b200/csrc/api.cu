@@ -114,7 +114,10 @@ int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
     if (!ctx) return YULE_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (auto &kv : ctx->buffers) cudaFree(kv.second.ptr);
+    for (auto &kv : ctx->buffers) {
+        cudaFree(kv.second.ptr);
+        if (kv.second.planar) cudaFree(kv.second.planar);
+    }
     for (auto ev : ctx->events) cudaEventDestroy(ev);
     for (auto &g : ctx->graphs)
         if (g.exec) cudaGraphExecDestroy(g.exec);
@@ -172,6 +175,23 @@ int32_t yule_cuda_free(yule_cuda_ctx *ctx, yule_buffer handle) {
     // Work already enqueued may still read the buffer.
     YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     YULE_CUDA_TRY(cudaFree(b.ptr));
+    if (b.planar) YULE_CUDA_TRY(cudaFree(b.planar));
+    return YULE_OK;
+}
+
+// A write to a buffer invalidates the planar copy made from its old contents.
+static int32_t drop_planar(yule_cuda_ctx *ctx, yule_buffer h) {
+    uint8_t *planar = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        auto it = ctx->buffers.find(h);
+        if (it == ctx->buffers.end() || !it->second.planar) return YULE_OK;
+        planar = it->second.planar;
+        it->second.planar = nullptr;
+        it->second.planar_blocks = 0;
+    }
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    YULE_CUDA_TRY(cudaFree(planar));
     return YULE_OK;
 }
 
@@ -190,6 +210,10 @@ int32_t yule_cuda_copy_to_device(yule_cuda_ctx *ctx, const void *data, size_t le
     if (len && !data) return fail(YULE_ERR_INVALID_ARGUMENT, "null data");
     size_t n = len < d.size ? len : d.size;
     if (n == 0) return YULE_OK;
+    if (d.planar) {
+        int32_t rc = drop_planar(ctx, dst);
+        if (rc) return rc;
+    }
     YULE_CUDA_TRY(cudaMemcpyAsync(d.ptr, data, n, cudaMemcpyHostToDevice, ctx->stream));
     // A pageable source has been staged when the call returns; a pinned one has not, and the
     // caller's slice is only borrowed for the duration of this call.
@@ -219,6 +243,10 @@ int32_t yule_cuda_copy_buffer_offset(yule_cuda_ctx *ctx, yule_buffer src, yule_b
         return fail(YULE_ERR_OUT_OF_BOUNDS, "copy writes [%zu, %zu) of a %zu-byte buffer", dst_offset,
                     dst_offset + size, d.size);
     if (size == 0) return YULE_OK;
+    if (d.planar) {
+        int32_t rc = drop_planar(ctx, dst);
+        if (rc) return rc;
+    }
     YULE_CUDA_TRY(cudaMemcpyAsync((char *)d.ptr + dst_offset, (const char *)s.ptr + src_offset, size,
                                   cudaMemcpyDeviceToDevice, ctx->stream));
     return YULE_OK;
@@ -418,6 +446,9 @@ static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight
     a.batch = batch;
     a.x_stride = x_stride;
     a.out_stride = out_stride;
+    if (type == YULE_DTYPE_Q6_K && W.planar && weight_offset == 0 &&
+        W.planar_blocks == (uint64_t)n_rows * (n_cols / 256))
+        a.planar = W.planar;
     LAUNCHED(ctx, launch_qmv(a, ctx->prop.multiProcessorCount, ctx->stream, &_n));
     return YULE_OK;
 }
@@ -438,6 +469,49 @@ int32_t yule_cuda_quantized_matmul_batched(yule_cuda_ctx *ctx, yule_buffer weigh
                                            uint32_t gguf_type, uint32_t batch, uint32_t x_stride,
                                            uint32_t out_stride) {
     return qmv_common(ctx, weights, 0, input, output, n_rows, n_cols, gguf_type, batch, x_stride, out_stride);
+}
+
+int32_t yule_cuda_prepare_weights(yule_cuda_ctx *ctx, yule_buffer weights, uint32_t gguf_type, uint32_t n_rows,
+                                  uint32_t n_cols) {
+    CTX_GUARD(ctx);
+    if (!is_quantized(gguf_type))
+        return fail(YULE_ERR_UNSUPPORTED_DTYPE, "unsupported dtype for CUDA qmv: GGUF type %u", gguf_type);
+    if (n_cols == 0 || n_cols % block_size(gguf_type))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "n_cols %u is not a multiple of the block size", n_cols);
+    FIND(ctx, weights, W);
+    NEED_BYTES(W, tensor_bytes(gguf_type, n_rows, n_cols), "prepare_weights");
+    if (gguf_type != YULE_DTYPE_Q6_K || !q6k_mma_supported(n_cols) || n_rows == 0) return YULE_OK;
+    const uint64_t n_blocks = (uint64_t)n_rows * (n_cols / 256);
+    if (W.planar && W.planar_blocks == n_blocks) return YULE_OK;
+    if (W.planar) {
+        int32_t rc = drop_planar(ctx, weights);
+        if (rc) return rc;
+    }
+    uint8_t *planar = nullptr;
+    cudaError_t e = cudaMalloc((void **)&planar, q6k_planar_bytes(n_blocks));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(YULE_ERR_OUT_OF_MEMORY, "cuda allocation of the planar Q6_K copy (%zu bytes) failed",
+                    q6k_planar_bytes(n_blocks));
+    }
+    {
+        uint64_t _n = 0;
+        e = launch_q6k_repack((const uint8_t *)W.ptr, planar, n_blocks, ctx->stream, &_n);
+        ctx->launches.fetch_add(_n);
+    }
+    if (e != cudaSuccess) {
+        cudaFree(planar);
+        return fail_cuda(e, "Q6_K repack");
+    }
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    auto it = ctx->buffers.find(weights);
+    if (it == ctx->buffers.end()) {
+        cudaFree(planar);
+        return fail(YULE_ERR_UNKNOWN_BUFFER, "buffer freed during prepare_weights");
+    }
+    it->second.planar = planar;
+    it->second.planar_blocks = n_blocks;
+    return YULE_OK;
 }
 
 int32_t yule_cuda_dequantize(yule_cuda_ctx *ctx, yule_buffer weights, uint32_t gguf_type, uint64_t n_blocks,

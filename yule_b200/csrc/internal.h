@@ -28,6 +28,10 @@ struct Buffer {
     void *ptr = nullptr;
     size_t size = 0;      // bytes the caller asked for
     size_t capacity = 0;  // bytes allocated (rounded up, so 16-byte over-reads stay in bounds)
+    // Optional planar device copy of a Q6_K tensor held in this buffer (yule_cuda_prepare_weights);
+    // dropped whenever the buffer is written.
+    uint8_t *planar = nullptr;
+    uint64_t planar_blocks = 0;
 };
 
 // Sets the calling thread's error text and returns `code`.
@@ -106,6 +110,9 @@ struct QmvArgs {
     // Optional fused prologue/epilogue used by the runner (null when unused):
     const float *residual = nullptr;  // out[row] = residual[row] + dot   (o-proj / down-proj)
     bool pdl = false;                 // programmatic dependent launch
+    const uint8_t *planar = nullptr;  // Q6_K: planar copy of the same tensor, when one was prepared
+    const float *norm_w = nullptr;    // RMSNorm prologue (planar Q6_K and Q4_K paths only)
+    float eps = 0.f;
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
 
@@ -126,6 +133,22 @@ struct Q4kFused {
 };
 bool q4k_mma_supported(uint32_t n_cols, uint32_t batch);
 cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches);
+
+// Q6_K tensor-pipe matvec over the planar device copy of a tensor (qmv_q6k_mma.cu).
+struct Q6kPlanar {
+    const uint8_t *planar = nullptr;  // planes ql | qh | scales | d, built by launch_q6k_repack
+    float *out = nullptr;
+    uint32_t n_rows = 0, n_cols = 0;
+    const float *x = nullptr;
+    const float *norm_w = nullptr;    // RMSNorm prologue on x when set
+    float eps = 0.f;
+    const float *residual = nullptr;  // out += residual when set
+    bool pdl = false;
+};
+size_t q6k_planar_bytes(uint64_t n_blocks);
+cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_blocks, cudaStream_t s, uint64_t *launches);
+bool q6k_mma_supported(uint32_t n_cols);
+cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches);
 
 // Launch helper shared by every kernel: optional programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>

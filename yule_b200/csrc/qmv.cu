@@ -433,12 +433,27 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             f.n_cols = a.n_cols;
             f.batch = nb;
             f.residual = a.residual ? a.residual + (size_t)done * a.out_stride : nullptr;
+            f.norm_w = a.norm_w;
+            f.eps = a.eps;
             f.pdl = a.pdl;
             cudaError_t e = launch_q4k_mma(f, sm_count, s, launches);
             if (e != cudaSuccess) return e;
             done += nb;
         }
         return cudaSuccess;
+    }
+    if (a.type == YULE_DTYPE_Q6_K && a.planar && a.batch == 1 && q6k_mma_supported(a.n_cols)) {
+        Q6kPlanar f;
+        f.planar = a.planar;
+        f.out = a.out;
+        f.n_rows = a.n_rows;
+        f.n_cols = a.n_cols;
+        f.x = a.x;
+        f.norm_w = a.norm_w;
+        f.eps = a.eps;
+        f.residual = a.residual;
+        f.pdl = a.pdl;
+        return launch_q6k_mma(f, sm_count, s, launches);
     }
     if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;
     uint32_t done = 0;

@@ -24,6 +24,7 @@ namespace {
 
 struct Tensor {
     Buffer buf;
+    yule_buffer handle = 0;
     uint32_t type = 0;
     bool set = false;
 };
@@ -143,7 +144,9 @@ struct Step {
     void ok(cudaError_t e) {
         if (err == cudaSuccess && e != cudaSuccess) err = e;
     }
-    void qmv(const Tensor &w, const float *x, float *out, uint32_t rows, uint32_t cols, const float *residual = nullptr) {
+    // norm_w set: RMSNorm of x folded into the matvec (only valid when fusable(w, cols) holds)
+    void qmv(const Tensor &w, const float *x, float *out, uint32_t rows, uint32_t cols, const float *residual = nullptr,
+             const float *norm_w = nullptr) {
         QmvArgs a;
         a.w = (const uint8_t *)w.buf.ptr;
         a.x = x;
@@ -156,6 +159,9 @@ struct Step {
         a.out_stride = rows;
         a.residual = residual;
         a.pdl = pdl;
+        a.planar = w.buf.planar;
+        a.norm_w = norm_w;
+        a.eps = r->cfg.norm_eps;
         ok(launch_qmv(a, r->ctx->prop.multiProcessorCount, r->ctx->stream, &n));
     }
 };
@@ -286,6 +292,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     if (all_q4k({&out_w}, dim)) {
         fused({{&out_w, {r->logits, c.vocab_size}}}, r->hidden, dim, r->output_norm_f32, nullptr, false);
+    } else if (out_w.type == YULE_DTYPE_Q6_K && out_w.buf.planar && q6k_mma_supported(dim)) {
+        st.qmv(out_w, r->hidden, r->logits, c.vocab_size, dim, nullptr, r->output_norm_f32);
     } else {
         st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
         st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
@@ -324,6 +332,23 @@ int32_t finalize(yule_cuda_runner *r) {
         if ((rc = check_matrix(L.ffn_gate, "ffn_gate.weight", l, ff, dim))) return rc;
         if ((rc = check_matrix(L.ffn_up, "ffn_up.weight", l, ff, dim))) return rc;
         if ((rc = check_matrix(L.ffn_down, "ffn_down.weight", l, dim, ff))) return rc;
+    }
+    // Device-side planar copies for the formats whose fast kernel wants one (Q6_K).
+    auto prepare = [&](Tensor &t, uint32_t rows, uint32_t cols) -> int32_t {
+        if (!t.set || t.type != YULE_DTYPE_Q6_K) return YULE_OK;
+        int32_t prc = yule_cuda_prepare_weights(r->ctx, t.handle, t.type, rows, cols);
+        if (prc) return prc;
+        if (!r->ctx->find(t.handle, &t.buf, "prepared tensor")) return YULE_ERR_UNKNOWN_BUFFER;
+        return YULE_OK;
+    };
+    if ((rc = prepare(r->output.set ? r->output : r->token_embd, c.vocab_size, dim))) return rc;
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        Layer &L = r->layers[l];
+        if ((rc = prepare(L.attn_q, qdim, dim)) || (rc = prepare(L.attn_k, kvdim, dim)) ||
+            (rc = prepare(L.attn_v, kvdim, dim)) || (rc = prepare(L.attn_output, dim, qdim)) ||
+            (rc = prepare(L.ffn_gate, ff, dim)) || (rc = prepare(L.ffn_up, ff, dim)) ||
+            (rc = prepare(L.ffn_down, dim, ff)))
+            return rc;
     }
     r->finalized = true;
     return YULE_OK;
@@ -499,6 +524,7 @@ int32_t yule_cuda_runner_set_tensor(yule_cuda_runner *r, const char *name, yule_
     if (!r->ctx->find(handle, &b, name)) return YULE_ERR_UNKNOWN_BUFFER;
     if (block_size(gguf_type) == 0) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "GGUF type %u not supported (%s)", gguf_type, name);
     t->buf = b;
+    t->handle = handle;
     t->type = gguf_type;
     t->set = true;
     r->finalized = false;

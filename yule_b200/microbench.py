@@ -19,24 +19,25 @@ import numpy as np
 from . import CudaB200Backend, DType, matvec_bytes, synth
 
 
-def run(backend, dtype: DType, rows: int, cols: int, batch: int, iters: int, ring: bool, reps: int = 5) -> dict:
+def run(backend, dtype: DType, rows: int, cols: int, batch: int, iters: int, ring: bool, reps: int = 5,
+        prepare: bool = True) -> dict:
     per = dtype.tensor_bytes(rows, cols)
     copies = max(1, -(-2 * 2 * 126 * 2 ** 20 // per)) if ring else 1  # ≥ 4 x L2 in total
     copies = min(copies, max(1, (24 << 30) // per))
     base = synth.random_blocks(dtype, 1, rows * cols // dtype.block_size)
-    wh = backend.allocate(per * copies)
-    tmp = backend.upload(base)
-    for c in range(copies):
-        backend.copy_buffer_offset(tmp, wh, 0, c * per, per)
-    backend.free(tmp)
+    # one buffer per copy, so that each can carry its own prepared layout
+    whs = [backend.upload(base) for _ in range(copies)]
+    if prepare:
+        for h in whs:
+            backend.prepare_weights(h, dtype, rows, cols)
     xh = backend.upload(synth.normal(2, batch * cols))
     oh = backend.allocate(batch * rows * 4)
     backend.graph_begin()
     for i in range(iters):
         if batch == 1:
-            backend.quantized_matmul_at(wh, (i % copies) * per, xh, oh, rows, cols, dtype)
+            backend.quantized_matmul(whs[i % copies], xh, oh, rows, cols, dtype)
         else:
-            backend.quantized_matmul_batched(wh, xh, oh, rows, cols, dtype, batch)
+            backend.quantized_matmul_batched(whs[i % copies], xh, oh, rows, cols, dtype, batch)
     graph = backend.graph_end()
     for _ in range(3):
         backend.graph_launch(graph)
@@ -50,12 +51,12 @@ def run(backend, dtype: DType, rows: int, cols: int, batch: int, iters: int, rin
         times.append(backend.event_elapsed_ms(e0, e1))
     y = backend.download(oh, batch * rows)
     backend.graph_destroy(graph)
-    for h in (wh, xh, oh):
+    for h in whs + [xh, oh]:
         backend.free(h)
     us = statistics.median(times) * 1e3 / iters
     nbytes = matvec_bytes(dtype, rows, cols, batch)
     return {"dtype": dtype.name, "rows": rows, "cols": cols, "batch": batch, "mode": "hbm_ring" if ring else "l2_resident",
-            "copies": copies, "us_per_launch": round(us, 3), "bytes_per_launch": nbytes,
+            "copies": copies, "prepared": prepare, "us_per_launch": round(us, 3), "bytes_per_launch": nbytes,
             "gbs": round(nbytes / us / 1e3, 1), "nan_outputs": int(np.isnan(y).sum())}
 
 
@@ -67,9 +68,11 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--ring", action="store_true")
+    ap.add_argument("--raw", action="store_true", help="do not call prepare_weights (raw GGUF layout only)")
     args = ap.parse_args()
     backend = CudaB200Backend(0)
-    print(json.dumps(run(backend, DType[args.dtype], args.rows, args.cols, args.batch, args.iters, args.ring)))
+    print(json.dumps(run(backend, DType[args.dtype], args.rows, args.cols, args.batch, args.iters, args.ring,
+                         prepare=not args.raw)))
     backend.close()
 
 
