@@ -122,6 +122,8 @@ int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
     for (auto &g : ctx->graphs)
         if (g.exec) cudaGraphExecDestroy(g.exec);
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+    if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+    if (ctx->attn_tickets) cudaFree(ctx->attn_tickets);
     if (ctx->device_status) cudaFree(ctx->device_status);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -546,6 +548,42 @@ int32_t yule_cuda_multihead_attention(yule_cuda_ctx *ctx, yule_buffer q, yule_bu
     NEED_BYTES(K, kv_need, "attention k_cache");
     NEED_BYTES(V, kv_need, "attention v_cache");
     NEED_BYTES(O, (size_t)n_heads * head_dim * 4, "attention out");
+    if (attn_decode_supported(head_dim) && kv_stride % 4 == 0) {
+        // split over positions; the partial results live in a context-owned scratch grown on demand
+        AttnDecode a;
+        a.n_splits = attn_pick_splits(n_heads, seq_len, ctx->prop.multiProcessorCount);
+        const size_t need = attn_scratch_floats(n_heads, a.n_splits, head_dim);
+        {
+            std::lock_guard<std::mutex> lock(ctx->mu);
+            if (a.n_splits > 1 && (ctx->attn_scratch_floats < need || ctx->attn_tickets_n < n_heads)) {
+                YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+                if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+                if (ctx->attn_tickets) cudaFree(ctx->attn_tickets);
+                ctx->attn_scratch = nullptr;
+                ctx->attn_tickets = nullptr;
+                ctx->attn_scratch_floats = ctx->attn_tickets_n = 0;
+                YULE_CUDA_TRY(cudaMalloc((void **)&ctx->attn_scratch, need * sizeof(float)));
+                YULE_CUDA_TRY(cudaMalloc((void **)&ctx->attn_tickets, (size_t)n_heads * sizeof(uint32_t)));
+                YULE_CUDA_TRY(cudaMemsetAsync(ctx->attn_tickets, 0, (size_t)n_heads * sizeof(uint32_t), ctx->stream));
+                ctx->attn_scratch_floats = need;
+                ctx->attn_tickets_n = n_heads;
+            }
+            a.scratch = ctx->attn_scratch;
+            a.tickets = ctx->attn_tickets;
+        }
+        a.q = (const float *)Q.ptr;
+        a.k_cache = (float *)K.ptr;
+        a.v_cache = (float *)V.ptr;
+        a.seq_len = seq_len;
+        a.out = (float *)O.ptr;
+        a.hd = head_dim;
+        a.n_heads = n_heads;
+        a.n_kv_heads = n_kv_heads;
+        a.kv_stride = kv_stride;
+        a.max_seq_len = seq_len;
+        LAUNCHED(ctx, launch_attn_decode(a, ctx->stream, &_n));
+        return YULE_OK;
+    }
     LAUNCHED(ctx, launch_multihead_attention((const float *)Q.ptr, (const float *)K.ptr, (const float *)V.ptr,
                                              (float *)O.ptr, head_dim, seq_len, nullptr, seq_len, n_heads,
                                              n_kv_heads, kv_stride, ctx->stream, &_n));

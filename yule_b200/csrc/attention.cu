@@ -1,0 +1,272 @@
+// attention.cu — GQA decode attention over the flat fp32 KV cache, split over positions.
+//
+// What it computes is the per-head loop of yule-infer/src/model_runner.rs:672-758 (equivalently
+// the MultiheadAttn dispatch, yule-gpu/shaders/multihead_attn.comp): for head h with KV head
+// h / (n_heads / n_kv_heads),
+//     s_t = (q_h · K[t]) / sqrt(hd),  p = softmax(s) (max-subtracted),  o_h = Σ_t p_t · V[t].
+// In the runner's graph it also does the work of the Rope dispatch and the two KV-cache copies
+// (yule-infer/src/gpu_runner.rs:422-470): q and the new k row are rotated here with the
+// host-built cos/sin table, and the new K/V rows are written to the caches.
+//
+// Grid (n_heads, n_splits): CTA (h, s) handles positions [s·chunk, (s+1)·chunk).  One thread per
+// position computes a whole score (q is broadcast from shared memory; no shuffles), then the CTA
+// forms its local max / sum-of-exponentials / weighted V sum.  With more than one split the
+// partial triples go to a scratch area and the CTA that arrives last for a head (a ticket from one
+// atomicAdd — nobody waits for anybody) merges them in split order, the standard log-sum-exp
+// merge of yule-gpu/shaders/flash_decode_reduce.comp.
+
+#include <cfloat>
+
+#include "internal.h"
+
+namespace yule {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+struct AttnParams {
+    // inputs
+    const float *q;        // [n_heads][hd]; rotated here when cos_table is set
+    const float *k_new;    // [n_kv][hd] un-rotated K row of the current token (fused mode) or null
+    const float *v_new;    // [n_kv][hd] V row of the current token (fused mode) or null
+    float *k_cache;        // [max_seq][kv_stride]
+    float *v_cache;
+    const float *cos_table, *sin_table;  // [max_seq][hd/2] or null
+    const uint32_t *pos_ptr;             // device position (fused / graph mode) or null
+    uint32_t seq_len;                    // used when pos_ptr is null
+    float *out;                          // [n_heads][hd]
+    float *scratch;                      // [n_heads][n_splits][hd + 2] partial (m, l, acc)
+    uint32_t *tickets;                   // [n_heads], zero between launches
+    uint32_t hd, n_heads, n_kv_heads, kv_stride, n_splits, max_chunk;
+};
+
+__global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[2 * (kThreads / 32)];
+    __shared__ uint32_t s_last;
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
+
+    const uint32_t hd = p.hd, hd4 = hd / 4;
+    const uint32_t head = blockIdx.x, split = blockIdx.y;
+    const uint32_t group = p.n_heads / p.n_kv_heads, kvh = head / group;
+    const uint32_t pos = p.pos_ptr ? *p.pos_ptr : p.seq_len - 1;
+    const uint32_t seq = pos + 1;
+    const bool fused = p.k_new != nullptr;
+    // splits actually used at this sequence length: at least 64 positions each; the rest exit
+    uint32_t eff = (seq + 63) / 64;
+    eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
+    if (split >= eff) return;
+    const uint32_t chunk = (seq + eff - 1) / eff;
+    const uint32_t lo = split * chunk < seq ? split * chunk : seq;
+    const uint32_t hi = lo + chunk < seq ? lo + chunk : seq;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+
+    float *qs = sm;                 // hd: the (rotated) query of this head
+    float *kcur = qs + hd;          // hd: rotated K row of the current token (fused mode)
+    float *scores = kcur + hd;      // max_chunk
+    float *partial = scores + p.max_chunk;  // n_slices × hd
+
+    // q (and the new k row) with RoPE: pairs (2i, 2i+1) rotated by the table entry of this position,
+    // products and sums rounded separately as in apply_rope (model_runner.rs:277-293)
+    for (uint32_t i = threadIdx.x; i < hd / 2; i += kThreads) {
+        float q0 = p.q[(size_t)head * hd + 2 * i], q1 = p.q[(size_t)head * hd + 2 * i + 1];
+        if (p.cos_table) {
+            const float c = p.cos_table[(size_t)pos * (hd / 2) + i], s = p.sin_table[(size_t)pos * (hd / 2) + i];
+            const float r0 = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, s));
+            const float r1 = __fadd_rn(__fmul_rn(q0, s), __fmul_rn(q1, c));
+            q0 = r0;
+            q1 = r1;
+            if (fused) {
+                const float k0 = p.k_new[(size_t)kvh * hd + 2 * i], k1 = p.k_new[(size_t)kvh * hd + 2 * i + 1];
+                kcur[2 * i] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
+                kcur[2 * i + 1] = __fadd_rn(__fmul_rn(k0, s), __fmul_rn(k1, c));
+            }
+        } else if (fused) {
+            kcur[2 * i] = p.k_new[(size_t)kvh * hd + 2 * i];
+            kcur[2 * i + 1] = p.k_new[(size_t)kvh * hd + 2 * i + 1];
+        }
+        qs[2 * i] = q0;
+        qs[2 * i + 1] = q1;
+    }
+    __syncthreads();
+
+    // The first head of each GQA group, in the split that owns the current position, appends the
+    // new K and V rows to the caches (readers of this launch take them from k_new / v_new).
+    if (fused && head % group == 0 && pos >= lo && pos < hi) {
+        for (uint32_t d = threadIdx.x; d < hd; d += kThreads) {
+            p.k_cache[(size_t)pos * p.kv_stride + (size_t)kvh * hd + d] = kcur[d];
+            p.v_cache[(size_t)pos * p.kv_stride + (size_t)kvh * hd + d] = p.v_new[(size_t)kvh * hd + d];
+        }
+    }
+
+    // scores: one thread per position
+    const float scale = 1.0f / sqrtf((float)hd);
+    float mx = -FLT_MAX;
+    for (uint32_t t = lo + threadIdx.x; t < hi; t += kThreads) {
+        const float4 *kp = (fused && t == pos) ? reinterpret_cast<const float4 *>(kcur)
+                                               : reinterpret_cast<const float4 *>(p.k_cache + (size_t)t * p.kv_stride + (size_t)kvh * hd);
+        const float4 *qp = reinterpret_cast<const float4 *>(qs);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (uint32_t i = 0; i < hd4; i++) {
+            const float4 k = kp[i], q = qp[i];
+            a0 = fmaf(q.x, k.x, a0);
+            a1 = fmaf(q.y, k.y, a1);
+            a2 = fmaf(q.z, k.z, a2);
+            a3 = fmaf(q.w, k.w, a3);
+        }
+        const float sc = ((a0 + a1) + (a2 + a3)) * scale;
+        scores[t - lo] = sc;
+        mx = fmaxf(mx, sc);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    mx = -FLT_MAX;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; i++) mx = fmaxf(mx, red[i]);
+
+    float sum = 0.f;
+    for (uint32_t t = lo + threadIdx.x; t < hi; t += kThreads) {
+        const float e = expf(scores[t - lo] - mx);
+        scores[t - lo] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[kThreads / 32 + wid] = sum;
+    __syncthreads();
+    sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; i++) sum += red[kThreads / 32 + i];
+
+    // Σ_t e_t · V[t]: thread (slice, d4) takes positions slice, slice + n_slices, … for 4 dimensions
+    const uint32_t n_slices = kThreads / hd4;
+    const uint32_t d4 = threadIdx.x % hd4, slice = threadIdx.x / hd4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (slice < n_slices) {
+        for (uint32_t t = lo + slice; t < hi; t += n_slices) {
+            const float4 *vp = (fused && t == pos) ? reinterpret_cast<const float4 *>(p.v_new + (size_t)kvh * hd)
+                                                   : reinterpret_cast<const float4 *>(p.v_cache + (size_t)t * p.kv_stride + (size_t)kvh * hd);
+            const float4 v = vp[d4];
+            const float e = scores[t - lo];
+            acc.x = fmaf(e, v.x, acc.x);
+            acc.y = fmaf(e, v.y, acc.y);
+            acc.z = fmaf(e, v.z, acc.z);
+            acc.w = fmaf(e, v.w, acc.w);
+        }
+        reinterpret_cast<float4 *>(partial)[slice * hd4 + d4] = acc;
+    }
+    __syncthreads();
+    float o = 0.f;  // thread d < hd: this split's un-normalised output for dimension d
+    if (threadIdx.x < hd)
+        for (uint32_t s2 = 0; s2 < n_slices; s2++) o += partial[s2 * hd + threadIdx.x];
+
+    if (eff == 1) {
+        if (threadIdx.x < hd) p.out[(size_t)head * hd + threadIdx.x] = o * (1.0f / sum);
+        return;
+    }
+
+    // publish (m, l, acc) of this split, then take a ticket; the last CTA of the head merges
+    float *mine = p.scratch + ((size_t)head * p.n_splits + split) * (hd + 2);
+    if (threadIdx.x < hd) mine[2 + threadIdx.x] = o;
+    if (threadIdx.x == 0) {
+        mine[0] = lo < hi ? mx : -FLT_MAX;
+        mine[1] = lo < hi ? sum : 0.f;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&p.tickets[head], 1u) == eff - 1) ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // __ldcg: these words were written by other SMs; read them from L2, not from a stale L1 line.
+    // All loads are issued before any is used (one L2 round trip, not one per split).
+    const float *all = p.scratch + (size_t)head * p.n_splits * (hd + 2);
+    constexpr int kMaxSplits = 16;
+    float ms[kMaxSplits], ls[kMaxSplits], os[kMaxSplits];
+#pragma unroll
+    for (int s2 = 0; s2 < kMaxSplits; s2++) {
+        const bool live = (uint32_t)s2 < eff;
+        ms[s2] = live ? __ldcg(all + s2 * (hd + 2)) : -FLT_MAX;
+        ls[s2] = live ? __ldcg(all + s2 * (hd + 2) + 1) : 0.f;
+        os[s2] = (live && threadIdx.x < hd) ? __ldcg(all + s2 * (hd + 2) + 2 + threadIdx.x) : 0.f;
+    }
+    float M = -FLT_MAX;
+#pragma unroll
+    for (int s2 = 0; s2 < kMaxSplits; s2++) M = fmaxf(M, ms[s2]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < kMaxSplits; s2++) {
+        const float w = ls[s2] > 0.f ? expf(ms[s2] - M) : 0.f;  // empty split: no weight
+        L = fmaf(ls[s2], w, L);
+        O = fmaf(os[s2], w, O);
+    }
+    if (threadIdx.x < hd) p.out[(size_t)head * hd + threadIdx.x] = O * (1.0f / L);
+    if (threadIdx.x == 0) p.tickets[head] = 0;  // ready for the next launch on this stream
+}
+
+}  // namespace
+
+size_t attn_scratch_floats(uint32_t n_heads, uint32_t n_splits, uint32_t hd) {
+    return (size_t)n_heads * n_splits * (hd + 2);
+}
+
+uint32_t attn_pick_splits(uint32_t n_heads, uint32_t seq_len_hint, int sm_count) {
+    uint32_t s = (2u * (uint32_t)sm_count) / (n_heads ? n_heads : 1);
+    s = s < 1 ? 1 : (s > 16 ? 16 : s);
+    const uint32_t by_len = (seq_len_hint + 63) / 64;  // at least 64 positions per split
+    if (by_len < s) s = by_len < 1 ? 1 : by_len;
+    return s;
+}
+
+bool attn_decode_supported(uint32_t hd) { return hd % 4 == 0 && hd >= 4 && hd <= 256 && kThreads % (hd / 4) == 0; }
+
+cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *launches) {
+    AttnParams p = {};
+    p.q = a.q;
+    p.k_new = a.k_new;
+    p.v_new = a.v_new;
+    p.k_cache = a.k_cache;
+    p.v_cache = a.v_cache;
+    p.cos_table = a.cos_table;
+    p.sin_table = a.sin_table;
+    p.pos_ptr = a.pos_ptr;
+    p.seq_len = a.seq_len;
+    p.out = a.out;
+    p.scratch = a.scratch;
+    p.tickets = a.tickets;
+    p.hd = a.hd;
+    p.n_heads = a.n_heads;
+    p.n_kv_heads = a.n_kv_heads;
+    p.kv_stride = a.kv_stride;
+    p.n_splits = a.n_splits;
+    // A split holds at most max(64, ceil(max_seq / n_splits)) scores (fewer, larger splits are only
+    // used while they stay at 64 positions or less).  A multiple of 4 keeps the float4 area behind
+    // the scores 16-byte aligned.
+    uint32_t mc = (a.max_seq_len + a.n_splits - 1) / a.n_splits;
+    if (mc < 64) mc = 64;
+    p.max_chunk = ((mc + 3) / 4) * 4;
+    const uint32_t n_slices = kThreads / (a.hd / 4);
+    const size_t smem = ((size_t)2 * a.hd + p.max_chunk + (size_t)n_slices * a.hd) * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    *launches += 1;
+    return launch_kernel(attn_decode_kernel, dim3(a.n_heads, a.n_splits), dim3(kThreads), smem, s, a.pdl, p);
+}
+
+}  // namespace yule

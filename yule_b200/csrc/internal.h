@@ -63,6 +63,11 @@ struct yule_cuda_ctx {
     uint64_t launches_at_capture_begin = 0;
     void *flush_buf = nullptr;
     size_t flush_bytes = 0;
+    // scratch of the split-KV attention entry point, grown on demand
+    float *attn_scratch = nullptr;
+    size_t attn_scratch_floats = 0;
+    uint32_t *attn_tickets = nullptr;
+    size_t attn_tickets_n = 0;
     std::atomic<uint64_t> launches{0};
     // Word the kernels with bounded waits write when they give up; read by synchronize.
     int *device_status = nullptr;
@@ -203,6 +208,26 @@ cudaError_t launch_multihead_attention(const float *q, const float *k_cache, con
                                        const uint32_t *pos_ptr, uint32_t max_seq_len, uint32_t n_heads,
                                        uint32_t n_kv_heads, uint32_t kv_stride, cudaStream_t s,
                                        uint64_t *launches, bool pdl = false);
+// Split-KV decode attention, optionally fused with RoPE and the KV-cache append (attention.cu).
+struct AttnDecode {
+    const float *q = nullptr;       // [n_heads][hd]
+    const float *k_new = nullptr;   // fused mode: un-rotated K row of the current token, else null
+    const float *v_new = nullptr;
+    float *k_cache = nullptr, *v_cache = nullptr;
+    const float *cos_table = nullptr, *sin_table = nullptr;  // fused mode: RoPE table [max_seq][hd/2]
+    const uint32_t *pos_ptr = nullptr;  // position in device memory (graph replay), else seq_len is used
+    uint32_t seq_len = 0;
+    float *out = nullptr;
+    float *scratch = nullptr;       // attn_scratch_floats(n_heads, n_splits, hd) floats
+    uint32_t *tickets = nullptr;    // n_heads words, zero before the first launch
+    uint32_t hd = 0, n_heads = 0, n_kv_heads = 0, kv_stride = 0, n_splits = 1, max_seq_len = 0;
+    bool pdl = false;
+};
+size_t attn_scratch_floats(uint32_t n_heads, uint32_t n_splits, uint32_t hd);
+uint32_t attn_pick_splits(uint32_t n_heads, uint32_t seq_len_hint, int sm_count);
+bool attn_decode_supported(uint32_t hd);
+cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *launches);
+
 // Runner kernels that read the position from device memory (graph-replayable).
 cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tmp, float *k_cache,
                                  float *v_cache, const float *cos_table, const float *sin_table,

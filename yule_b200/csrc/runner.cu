@@ -51,6 +51,9 @@ struct yule_cuda_runner {
           *v_tmp = nullptr, *attn_out = nullptr, *attn_proj = nullptr, *gate = nullptr, *up = nullptr,
           *ffn_out = nullptr, *logits = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;  // [max_seq_len][head_dim/2], device
+    float *attn_scratch = nullptr;  // partial results of the split-KV attention
+    uint32_t *attn_tickets = nullptr;
+    uint32_t attn_splits = 1;
     uint32_t *d_state = nullptr;    // [0] token, [1] position
     uint32_t *d_history = nullptr;  // greedy pick made after each position
     uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
@@ -230,6 +233,9 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     Step st{r};
     st.pdl = pdl;
     const uint32_t *tok_ptr = r->d_state, *pos_ptr = r->d_state + 1;
+    // Timing aid: YULE_CUDA_SKIP is a bit mask of kernel classes to leave out of the graph (results
+    // are then meaningless); the time that disappears is that class's cost inside the real step.
+    const unsigned skip = getenv("YULE_CUDA_SKIP") ? (unsigned)strtoul(getenv("YULE_CUDA_SKIP"), nullptr, 0) : 0u;
     auto all_q4k = [&](std::initializer_list<const Tensor *> ts, uint32_t cols) {
         for (const Tensor *t : ts)
             if (t->type != YULE_DTYPE_Q4_K) return false;
@@ -260,11 +266,13 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.ok(launch_q4k_mma(f, sms, s, &st.n));
     };
 
-    st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, 0, tok_ptr, r->hidden,
-                              s, &st.n, pdl));
+    if (!(skip & 256))
+        st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, 0, tok_ptr,
+                                  r->hidden, s, &st.n, pdl));
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
-        if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
+        if (skip & 1) {
+        } else if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
             fused({{&L.attn_q, {r->q, qdim}}, {&L.attn_k, {r->k_tmp, kvdim}}, {&L.attn_v, {r->v_tmp, kvdim}}}, r->hidden,
                   dim, L.attn_norm_f32, nullptr, false);
         } else {
@@ -273,13 +281,40 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim, dim);
             st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim, dim);
         }
-        st.ok(launch_rope_kv_write(r->q, r->k_tmp, r->v_tmp, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin, pos_ptr, hd,
-                                   c.n_heads, c.n_kv_heads, s, &st.n, pdl));
-        st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, 0, pos_ptr, c.max_seq_len,
-                                         c.n_heads, c.n_kv_heads, kvdim, s, &st.n, pdl));
+        if (attn_decode_supported(hd)) {
+            // Rope dispatch + both KV copies + MultiheadAttn in one launch
+            AttnDecode a;
+            a.q = r->q;
+            a.k_new = r->k_tmp;
+            a.v_new = r->v_tmp;
+            a.k_cache = L.k_cache;
+            a.v_cache = L.v_cache;
+            a.cos_table = r->rope_cos;
+            a.sin_table = r->rope_sin;
+            a.pos_ptr = pos_ptr;
+            a.out = r->attn_out;
+            a.scratch = r->attn_scratch;
+            a.tickets = r->attn_tickets;
+            a.hd = hd;
+            a.n_heads = c.n_heads;
+            a.n_kv_heads = c.n_kv_heads;
+            a.kv_stride = kvdim;
+            a.n_splits = r->attn_splits;
+            a.max_seq_len = c.max_seq_len;
+            a.pdl = pdl;
+            if (!(skip & 4)) st.ok(launch_attn_decode(a, s, &st.n));
+        } else {
+            if (!(skip & 2))
+                st.ok(launch_rope_kv_write(r->q, r->k_tmp, r->v_tmp, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin,
+                                           pos_ptr, hd, c.n_heads, c.n_kv_heads, s, &st.n, pdl));
+            if (!(skip & 4))
+                st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, 0, pos_ptr, c.max_seq_len,
+                                                 c.n_heads, c.n_kv_heads, kvdim, s, &st.n, pdl));
+        }
         // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
-        st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
-        if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
+        if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
+        if (skip & 16) {
+        } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
             fused({{&L.ffn_gate, {r->gate, ff}}, {&L.ffn_up, {r->up, ff}}}, r->hidden, dim, L.ffn_norm_f32, nullptr, true);
         } else {
             st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
@@ -287,10 +322,11 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
             st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n, pdl));
         }
-        st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
+        if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
     }
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
-    if (all_q4k({&out_w}, dim)) {
+    if (skip & 64) {
+    } else if (all_q4k({&out_w}, dim)) {
         fused({{&out_w, {r->logits, c.vocab_size}}}, r->hidden, dim, r->output_norm_f32, nullptr, false);
     } else if (out_w.type == YULE_DTYPE_Q6_K && out_w.buf.planar && q6k_mma_supported(dim)) {
         st.qmv(out_w, r->hidden, r->logits, c.vocab_size, dim, nullptr, r->output_norm_f32);
@@ -298,7 +334,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
         st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
     }
-    st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, r->d_history, s, &st.n, pdl));
+    if (!(skip & 128)) st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, r->d_history, s, &st.n, pdl));
     *launches += st.n;
     return st.err;
 }
@@ -471,6 +507,10 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     A((size_t)c.max_seq_len * half, &r->rope_cos);
     A((size_t)c.max_seq_len * half, &r->rope_sin);
     float *tmp = nullptr;
+    r->attn_splits = attn_pick_splits(c.n_heads, c.max_seq_len, ctx->prop.multiProcessorCount);
+    A(attn_scratch_floats(c.n_heads, r->attn_splits, hd) + 4, &r->attn_scratch);
+    A(c.n_heads, &tmp);
+    r->attn_tickets = (uint32_t *)tmp;  // zero-filled by the allocator
     A(2, &tmp);
     r->d_state = (uint32_t *)tmp;
     A((size_t)c.max_seq_len + 1, &tmp);
