@@ -49,7 +49,7 @@ struct AttnParams {
     float *out;                          // [n_heads][hd]
     float *scratch;                      // [n_heads][n_splits][hd + 2] partial (m, l, acc)
     uint32_t *tickets;                   // [n_heads], zero between launches
-    uint32_t hd, n_heads, n_kv_heads, kv_stride, n_splits, max_chunk;
+    uint32_t hd, n_heads, n_kv_heads, kv_stride, n_splits, max_chunk, min_chunk;
 };
 
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
@@ -65,8 +65,9 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     const uint32_t pos = p.pos_ptr ? *p.pos_ptr : p.seq_len - 1;
     const uint32_t seq = pos + 1;
     const bool fused = p.k_new != nullptr;
-    // splits actually used at this sequence length: at least 64 positions each; the rest exit
-    uint32_t eff = (seq + 63) / 64;
+    // splits actually used at this sequence length: at least 256 positions each (one per thread);
+    // the rest exit.  Short sequences therefore take the single-CTA path with no merge step.
+    uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
     eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
     if (split >= eff) return;
     const uint32_t chunk = (seq + eff - 1) / eff;
@@ -226,7 +227,7 @@ size_t attn_scratch_floats(uint32_t n_heads, uint32_t n_splits, uint32_t hd) {
 uint32_t attn_pick_splits(uint32_t n_heads, uint32_t seq_len_hint, int sm_count) {
     uint32_t s = (2u * (uint32_t)sm_count) / (n_heads ? n_heads : 1);
     s = s < 1 ? 1 : (s > 16 ? 16 : s);
-    const uint32_t by_len = (seq_len_hint + 63) / 64;  // at least 64 positions per split
+    const uint32_t by_len = (seq_len_hint + kThreads - 1) / kThreads;  // at least 256 positions per split
     if (by_len < s) s = by_len < 1 ? 1 : by_len;
     return s;
 }
@@ -252,11 +253,12 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
     p.n_kv_heads = a.n_kv_heads;
     p.kv_stride = a.kv_stride;
     p.n_splits = a.n_splits;
-    // A split holds at most max(64, ceil(max_seq / n_splits)) scores (fewer, larger splits are only
-    // used while they stay at 64 positions or less).  A multiple of 4 keeps the float4 area behind
+    // A split holds at most max(256, ceil(max_seq / n_splits)) scores (fewer, larger splits are only
+    // used while they stay at 256 positions or less).  A multiple of 4 keeps the float4 area behind
     // the scores 16-byte aligned.
     uint32_t mc = (a.max_seq_len + a.n_splits - 1) / a.n_splits;
-    if (mc < 64) mc = 64;
+    p.min_chunk = a.min_chunk ? a.min_chunk : kThreads;
+    if (mc < p.min_chunk) mc = p.min_chunk;
     p.max_chunk = ((mc + 3) / 4) * 4;
     const uint32_t n_slices = kThreads / (a.hd / 4);
     const size_t smem = ((size_t)2 * a.hd + p.max_chunk + (size_t)n_slices * a.hd) * sizeof(float);

@@ -3,13 +3,6 @@
 
 #include <cuda_runtime.h>
 
-#ifdef __CUDACC__
-// Programmatic dependent launch: a kernel launched with the attribute may start while its
-// predecessor drains; everything it reads that the predecessor wrote must come after the wait.
-// Both are no-ops for a normal launch.
-__device__ __forceinline__ void yule_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void yule_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-#endif
 
 #include <atomic>
 #include <cstdarg>
@@ -21,6 +14,32 @@ __device__ __forceinline__ void yule_pdl_wait() { asm volatile("griddepcontrol.w
 #include <vector>
 
 #include "../../include/yule_cuda.h"
+
+#ifdef __CUDACC__
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor drains; everything it reads that the predecessor wrote must come after the wait.
+// Both are no-ops for a normal launch.
+__device__ __forceinline__ void yule_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void yule_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Asks L2 to fetch [p, p + bytes) from HBM without waiting for it (p 16-byte aligned, bytes a
+// multiple of 16).  Used by a matvec to pull in the weights of the kernel that runs after it,
+// so HBM keeps streaming across the dependency between the two.
+__device__ __forceinline__ void yule_prefetch_l2(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// Each CTA takes an equal 16-byte-granular slice of [base, base + bytes) and prefetches it in
+// pieces of at most 32 KB from one thread.
+__device__ __forceinline__ void yule_prefetch_l2_slice(const void *base, uint64_t bytes) {
+    if (!base || threadIdx.x != 0) return;
+    const uint64_t per = ((bytes / gridDim.x) + 15) & ~(uint64_t)15;
+    uint64_t lo = (uint64_t)blockIdx.x * per;
+    uint64_t hi = lo + per < bytes ? lo + per : (bytes & ~(uint64_t)15);
+    for (; lo < hi; lo += 32768) {
+        const uint64_t n = hi - lo < 32768 ? hi - lo : 32768;
+        yule_prefetch_l2(reinterpret_cast<const char *>(base) + lo, (uint32_t)n);
+    }
+}
+#endif
 
 namespace yule {
 
@@ -118,6 +137,8 @@ struct QmvArgs {
     const uint8_t *planar = nullptr;  // Q6_K: planar copy of the same tensor, when one was prepared
     const float *norm_w = nullptr;    // RMSNorm prologue (planar Q6_K and Q4_K paths only)
     float eps = 0.f;
+    const void *next_w[2] = {nullptr, nullptr};  // tensor-pipe paths: weights to prefetch into L2
+    uint64_t next_bytes[2] = {0, 0};
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
 
@@ -135,6 +156,8 @@ struct Q4kFused {
     const float *residual = nullptr;  // out[0] += residual when set
     bool swiglu_pair = false;         // w[0], w[1] = gate, up → out[0] = SiLU(gate)·up
     bool pdl = false;                 // programmatic dependent launch
+    const void *next_w[2] = {nullptr, nullptr};  // weights of the kernel(s) that follow: prefetched into L2
+    uint64_t next_bytes[2] = {0, 0};
 };
 bool q4k_mma_supported(uint32_t n_cols, uint32_t batch);
 cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches);
@@ -149,6 +172,8 @@ struct Q6kPlanar {
     float eps = 0.f;
     const float *residual = nullptr;  // out += residual when set
     bool pdl = false;
+    const void *next_w[2] = {nullptr, nullptr};  // weights of the kernel(s) that follow: prefetched into L2
+    uint64_t next_bytes[2] = {0, 0};
 };
 size_t q6k_planar_bytes(uint64_t n_blocks);
 cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_blocks, cudaStream_t s, uint64_t *launches);
@@ -221,6 +246,7 @@ struct AttnDecode {
     float *scratch = nullptr;       // attn_scratch_floats(n_heads, n_splits, hd) floats
     uint32_t *tickets = nullptr;    // n_heads words, zero before the first launch
     uint32_t hd = 0, n_heads = 0, n_kv_heads = 0, kv_stride = 0, n_splits = 1, max_seq_len = 0;
+    uint32_t min_chunk = 0;  // fewest positions a split is worth (0: one per thread of the CTA)
     bool pdl = false;
 };
 size_t attn_scratch_floats(uint32_t n_heads, uint32_t n_splits, uint32_t hd);

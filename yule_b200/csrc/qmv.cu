@@ -436,6 +436,10 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             f.norm_w = a.norm_w;
             f.eps = a.eps;
             f.pdl = a.pdl;
+            for (int i = 0; i < 2; i++) {
+                f.next_w[i] = a.next_w[i];
+                f.next_bytes[i] = a.next_bytes[i];
+            }
             cudaError_t e = launch_q4k_mma(f, sm_count, s, launches);
             if (e != cudaSuccess) return e;
             done += nb;
@@ -453,6 +457,10 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         f.eps = a.eps;
         f.residual = a.residual;
         f.pdl = a.pdl;
+        for (int i = 0; i < 2; i++) {
+            f.next_w[i] = a.next_w[i];
+            f.next_bytes[i] = a.next_bytes[i];
+        }
         return launch_q6k_mma(f, sm_count, s, launches);
     }
     if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;

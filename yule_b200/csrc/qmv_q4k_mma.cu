@@ -465,6 +465,8 @@ struct Q4kMmaParams {
     const float *norm_w;    // RMSNorm weights for the prologue, or null
     float eps;
     const float *residual;  // added to segment 0's output, or null (same layout as out[0])
+    const void *next_w[2];  // weights of the following kernel(s), prefetched into L2
+    uint64_t next_bytes[2];
 };
 
 __device__ __forceinline__ void group_barrier(int group) {
@@ -556,7 +558,10 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
         }
     }
 
-    // Weight loads are in flight; now wait for the kernel that produced the activations.
+    // Own weight loads are in flight; start HBM on the next kernel's weights too, then wait for
+    // the kernel that produced the activations.
+    yule_prefetch_l2_slice(p.next_w[0], p.next_bytes[0]);
+    yule_prefetch_l2_slice(p.next_w[1], p.next_bytes[1]);
     yule_pdl_wait();
     stage_activations(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps);
     // B column n = g: vector n/2, part n%2.  Lanes whose vector does not exist read vector 0;
@@ -721,6 +726,10 @@ cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint
     p.norm_w = f.norm_w;
     p.eps = f.eps;
     p.residual = f.residual;
+    for (int i = 0; i < 2; i++) {
+        p.next_w[i] = f.next_w[i];
+        p.next_bytes[i] = f.next_bytes[i];
+    }
     if (n_tiles == 0) return cudaSuccess;
     const size_t smem = smem_bytes(f.n_cols, f.batch);
     cudaError_t e;

@@ -329,6 +329,8 @@ struct Q6kMmaParams {
     const float *norm_w;
     float eps;
     const float *residual;
+    const void *next_w[2];  // weights of the following kernel(s), prefetched into L2
+    uint64_t next_bytes[2];
 };
 
 __device__ __forceinline__ void group_barrier(int group) {
@@ -392,7 +394,10 @@ qmv_q6k_mma_kernel(const Q6kMmaParams p) {
         }
     }
 
-    yule_pdl_wait();  // weights are in flight; the activations come from the previous kernel
+    // own weights are in flight; start HBM on the next kernel's weights too
+    yule_prefetch_l2_slice(p.next_w[0], p.next_bytes[0]);
+    yule_prefetch_l2_slice(p.next_w[1], p.next_bytes[1]);
+    yule_pdl_wait();  // the activations come from the previous kernel
     stage_activations(sm, p.x, p.n_cols, p.norm_w, p.eps);
 
     // B source of this lane: column n = g is live only for g = t (hi) and g = t + 4 (lo)
@@ -514,6 +519,10 @@ cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uin
     p.norm_w = f.norm_w;
     p.eps = f.eps;
     p.residual = f.residual;
+    for (int i = 0; i < 2; i++) {
+        p.next_w[i] = f.next_w[i];
+        p.next_bytes[i] = f.next_bytes[i];
+    }
     const size_t smem = smem_bytes(f.n_cols);
     cudaError_t e = tile_rows == 8 ? launch_variant<8, 2>(p, sm_count, smem, f.pdl, s)
                                    : launch_variant<16, 2>(p, sm_count, smem, f.pdl, s);

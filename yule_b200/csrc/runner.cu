@@ -147,6 +147,23 @@ struct Step {
     void ok(cudaError_t e) {
         if (err == cudaSuccess && e != cudaSuccess) err = e;
     }
+    // Weights of the kernel(s) that will run next; the tensor-pipe matvecs prefetch them into L2.
+    const void *next_w[2] = {nullptr, nullptr};
+    uint64_t next_bytes[2] = {0, 0};
+    void then(const Tensor *a, const Tensor *b = nullptr) {
+        const Tensor *ts[2] = {a, b};
+        static const bool enabled = !(getenv("YULE_CUDA_PREFETCH") && atoi(getenv("YULE_CUDA_PREFETCH")) == 0);
+        if (!enabled) ts[0] = ts[1] = nullptr;
+        for (int i = 0; i < 2; i++) {
+            const Tensor *t = ts[i];
+            next_w[i] = nullptr;
+            next_bytes[i] = 0;
+            if (!t || !t->set) continue;
+            // the bytes the next kernel will actually read: the planar copy when there is one
+            next_w[i] = t->buf.planar ? (const void *)t->buf.planar : t->buf.ptr;
+            next_bytes[i] = t->buf.planar ? t->buf.planar_blocks * 210 : t->buf.size;
+        }
+    }
     // norm_w set: RMSNorm of x folded into the matvec (only valid when fusable(w, cols) holds)
     void qmv(const Tensor &w, const float *x, float *out, uint32_t rows, uint32_t cols, const float *residual = nullptr,
              const float *norm_w = nullptr) {
@@ -165,6 +182,10 @@ struct Step {
         a.planar = w.buf.planar;
         a.norm_w = norm_w;
         a.eps = r->cfg.norm_eps;
+        for (int i = 0; i < 2; i++) {
+            a.next_w[i] = next_w[i];
+            a.next_bytes[i] = next_bytes[i];
+        }
         ok(launch_qmv(a, r->ctx->prop.multiProcessorCount, r->ctx->stream, &n));
     }
 };
@@ -263,6 +284,10 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         f.residual = residual;
         f.swiglu_pair = pair;
         f.pdl = pdl;
+        for (int k = 0; k < 2; k++) {
+            f.next_w[k] = st.next_w[k];
+            f.next_bytes[k] = st.next_bytes[k];
+        }
         st.ok(launch_q4k_mma(f, sms, s, &st.n));
     };
 
@@ -271,6 +296,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
                                   r->hidden, s, &st.n, pdl));
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
+        const Tensor &out_w_ = r->output.set ? r->output : r->token_embd;
+        st.then(&L.attn_output);  // while Q/K/V and attention run, o-proj's weights come in
         if (skip & 1) {
         } else if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
             fused({{&L.attn_q, {r->q, qdim}}, {&L.attn_k, {r->k_tmp, kvdim}}, {&L.attn_v, {r->v_tmp, kvdim}}}, r->hidden,
@@ -301,6 +328,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             a.kv_stride = kvdim;
             a.n_splits = r->attn_splits;
             a.max_seq_len = c.max_seq_len;
+            a.min_chunk = getenv("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_ATTN_MIN_CHUNK")) : 0;
             a.pdl = pdl;
             if (!(skip & 4)) st.ok(launch_attn_decode(a, s, &st.n));
         } else {
@@ -312,7 +340,9 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
                                                  c.n_heads, c.n_kv_heads, kvdim, s, &st.n, pdl));
         }
         // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
+        st.then(&L.ffn_gate, &L.ffn_up);
         if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
+        st.then(&L.ffn_down);
         if (skip & 16) {
         } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
             fused({{&L.ffn_gate, {r->gate, ff}}, {&L.ffn_up, {r->up, ff}}}, r->hidden, dim, L.ffn_norm_f32, nullptr, true);
@@ -322,8 +352,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
             st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n, pdl));
         }
+        // during down-proj: the next layer's Q and K/V (or the output matrix after the last layer)
+        if (l + 1 < c.n_layers)
+            st.then(&r->layers[l + 1].attn_q, &r->layers[l + 1].attn_k);
+        else
+            st.then(&out_w_);
         if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
     }
+    st.then(nullptr);
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     if (skip & 64) {
     } else if (all_q4k({&out_w}, dim)) {
