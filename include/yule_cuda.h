@@ -163,6 +163,25 @@ int32_t yule_cuda_multihead_attention(yule_cuda_ctx *ctx, yule_buffer q, yule_bu
                                       yule_buffer v_cache, yule_buffer out, uint32_t head_dim,
                                       uint32_t seq_len, uint32_t n_heads, uint32_t n_kv_heads,
                                       uint32_t kv_stride);
+/* multihead_attention for callers that must not allocate device memory when they call: a host that
+ * sealed its process before inference (Yule's sandbox is applied first, and the driver requests
+ * behind cudaMalloc may then be denied), an embedder whose device-memory budget is already handed
+ * out, or a decode loop that may not wait on the allocator's lock.  This entry point has no
+ * counterpart in the reference.  Same arguments and results as yule_cuda_multihead_attention, but
+ * the scratch for the position splits is a fixed array inside the library image (2.02 MiB of
+ * partial sums plus 512 bytes of counters, held by every GPU that loads the library until the
+ * process exits) instead of a buffer the context grows on demand; neither this call nor anything
+ * it calls uses cudaMalloc / cudaFree.
+ *   Limits: at most 128 heads, head_dim <= 256 with 256 % (head_dim / 4) == 0, kv_stride a multiple
+ *   of 4; anything larger is refused with YULE_ERR_INVALID_ARGUMENT and a message naming the limit.
+ *   First use on a device looks up the array's device address; make that first call before you
+ *   open any stream capture.
+ *   All calls share the one array: two calls whose kernels overlap on the GPU (different contexts
+ *   or streams on the same device) race on it — issue them one after the other. */
+int32_t yule_cuda_multihead_attention_static(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k_cache,
+                                             yule_buffer v_cache, yule_buffer out, uint32_t head_dim,
+                                             uint32_t seq_len, uint32_t n_heads, uint32_t n_kv_heads,
+                                             uint32_t kv_stride);
 /* Embedding row `token` of a [vocab][dim] table of any supported dtype (F32,
  * F16 or a quantized format) dequantised to `out` — the step the reference GPU
  * runner does on the CPU (gpu_runner.rs:309-343). */

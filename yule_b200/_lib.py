@@ -51,6 +51,7 @@ _SIGNATURES = {
     "yule_cuda_prepare_weights": [vp, u64, u32, u32, u32],
     "yule_cuda_dequantize": [vp, u64, u32, u64, u64],
     "yule_cuda_multihead_attention": [vp, u64, u64, u64, u64, u32, u32, u32, u32, u32],
+    "yule_cuda_multihead_attention_static": [vp, u64, u64, u64, u64, u32, u32, u32, u32, u32],
     "yule_cuda_embed_gather": [vp, u64, u32, u32, u32, u64],
     "yule_cuda_graph_begin": [vp],
     "yule_cuda_graph_end": [vp, C.POINTER(u32)],

@@ -187,6 +187,15 @@ class CudaB200Backend:
         _check(self._lib.yule_cuda_multihead_attention(self._ctx, q.id, k_cache.id, v_cache.id, out.id, head_dim,
                                                        seq_len, n_heads, n_kv_heads, kv_stride))
 
+    def multihead_attention_static(self, q: BufferHandle, k_cache: BufferHandle, v_cache: BufferHandle,
+                                   out: BufferHandle, head_dim: int, seq_len: int, n_heads: int, n_kv_heads: int,
+                                   kv_stride: int) -> None:
+        """``multihead_attention`` without any device allocation: the split scratch is a fixed array
+        inside the library (at most 128 heads, head_dim <= 256).  For hosts that cannot call the
+        device allocator once inference has started."""
+        _check(self._lib.yule_cuda_multihead_attention_static(self._ctx, q.id, k_cache.id, v_cache.id, out.id,
+                                                              head_dim, seq_len, n_heads, n_kv_heads, kv_stride))
+
     def embed_gather(self, table: BufferHandle, dtype: DType, dim: int, token: int, out: BufferHandle) -> None:
         _check(self._lib.yule_cuda_embed_gather(self._ctx, table.id, int(dtype), dim, token, out.id))
 

@@ -272,3 +272,112 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
 }
 
 }  // namespace yule
+
+// ── allocation-free variant ─────────────────────────────────────────────────────────────────
+// Some hosts cannot allocate device memory at call time: a process that sealed itself before
+// inference (Yule applies a seccomp / Landlock / Job Object sandbox first, and the driver calls
+// behind cudaMalloc may then be refused), an embedder running under a fixed device-memory budget it
+// has already handed out, or a decode loop that may not take the allocator's lock.  For them the
+// split-KV scratch lives in the library image itself: two file-scope __device__ arrays of a fixed,
+// modest size that every GPU which loads the library holds until the process exits.
+
+namespace yule {
+namespace {
+
+constexpr uint32_t kStaticMaxHeads = 128;
+constexpr uint32_t kStaticMaxSplits = 16;
+constexpr uint32_t kStaticMaxHeadDim = 256;
+// 128 heads x 16 splits x (256 + 2) floats = 528 384 floats = 2.02 MiB, plus 512 bytes of tickets
+constexpr size_t kStaticScratchFloats = (size_t)kStaticMaxHeads * kStaticMaxSplits * (kStaticMaxHeadDim + 2);
+
+static __device__ __align__(256) float g_attn_static_scratch[kStaticScratchFloats];
+static __device__ __align__(256) uint32_t g_attn_static_tickets[kStaticMaxHeads];
+
+// In host code the two names above are only stand-ins; the device addresses come from
+// cudaGetSymbolAddress, asked once per device with that device current.
+struct StaticAddrs {
+    float *scratch = nullptr;
+    uint32_t *tickets = nullptr;
+};
+constexpr int kMaxDevices = 64;
+StaticAddrs g_static_addrs[kMaxDevices];
+std::mutex g_static_mu;
+
+cudaError_t static_addresses(int device, StaticAddrs *out) {
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticAddrs &a = g_static_addrs[device];
+    if (!a.scratch) {
+        float *sp = nullptr;
+        uint32_t *tp = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&sp, g_attn_static_scratch);
+        if (e != cudaSuccess) return e;
+        e = cudaGetSymbolAddress((void **)&tp, g_attn_static_tickets);
+        if (e != cudaSuccess) return e;
+        a.scratch = sp;
+        a.tickets = tp;
+    }
+    *out = a;
+    return cudaSuccess;
+}
+
+}  // namespace
+}  // namespace yule
+
+extern "C" int32_t yule_cuda_multihead_attention_static(yule_cuda_ctx *ctx, yule_buffer q, yule_buffer k_cache,
+                                                        yule_buffer v_cache, yule_buffer out, uint32_t head_dim,
+                                                        uint32_t seq_len, uint32_t n_heads, uint32_t n_kv_heads,
+                                                        uint32_t kv_stride) {
+    using namespace yule;
+    if (!ctx) return fail(YULE_ERR_INVALID_ARGUMENT, "null context");
+    YULE_CUDA_TRY(cudaSetDevice(ctx->device));
+    if (n_kv_heads == 0 || n_heads == 0 || n_heads % n_kv_heads || head_dim == 0 || seq_len == 0)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "bad attention shape (heads %u, kv heads %u, head_dim %u, seq %u)", n_heads,
+                    n_kv_heads, head_dim, seq_len);
+    if (!attn_decode_supported(head_dim) || kv_stride % 4)
+        return fail(YULE_ERR_INVALID_ARGUMENT,
+                    "multihead_attention_static needs head_dim with 256 %% (head_dim / 4) == 0 and kv_stride %% 4 == 0 "
+                    "(got head_dim %u, kv_stride %u)", head_dim, kv_stride);
+    const uint32_t n_splits = attn_pick_splits(n_heads, seq_len, ctx->prop.multiProcessorCount);
+    if (n_heads > kStaticMaxHeads || n_splits > kStaticMaxSplits || head_dim > kStaticMaxHeadDim ||
+        attn_scratch_floats(n_heads, n_splits, head_dim) > kStaticScratchFloats)
+        return fail(YULE_ERR_INVALID_ARGUMENT,
+                    "multihead_attention_static: %u heads x head_dim %u exceeds the built-in scratch (at most %u heads, "
+                    "head_dim %u, %zu floats); use yule_cuda_multihead_attention", n_heads, head_dim, kStaticMaxHeads,
+                    kStaticMaxHeadDim, kStaticScratchFloats);
+    Buffer Q, K, V, O;
+    if (!ctx->find(q, &Q, "q") || !ctx->find(k_cache, &K, "k_cache") || !ctx->find(v_cache, &V, "v_cache") ||
+        !ctx->find(out, &O, "out"))
+        return YULE_ERR_UNKNOWN_BUFFER;
+    const size_t kv_need = ((size_t)(seq_len - 1) * kv_stride + (size_t)n_kv_heads * head_dim) * 4;
+    const size_t q_need = (size_t)n_heads * head_dim * 4;
+    if (Q.size < q_need || O.size < q_need || K.size < kv_need || V.size < kv_need)
+        return fail(YULE_ERR_OUT_OF_BOUNDS, "attention buffers too small for %u heads x %u over %u positions", n_heads,
+                    head_dim, seq_len);
+    StaticAddrs addrs;
+    cudaError_t e = static_addresses(ctx->device, &addrs);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress of the built-in attention scratch");
+    // The array keeps whatever the last call left.  Partial results are fully rewritten before they
+    // are read; the tickets must start at zero, so clear them (a failed earlier launch may not have).
+    YULE_CUDA_TRY(cudaMemsetAsync(addrs.tickets, 0, (size_t)n_heads * sizeof(uint32_t), ctx->stream));
+    AttnDecode a;
+    a.q = (const float *)Q.ptr;
+    a.k_cache = (float *)K.ptr;
+    a.v_cache = (float *)V.ptr;
+    a.seq_len = seq_len;
+    a.out = (float *)O.ptr;
+    a.scratch = addrs.scratch;
+    a.tickets = addrs.tickets;
+    a.hd = head_dim;
+    a.n_heads = n_heads;
+    a.n_kv_heads = n_kv_heads;
+    a.kv_stride = kv_stride;
+    a.n_splits = n_splits;
+    a.max_seq_len = seq_len;
+    uint64_t n = 0;
+    e = launch_attn_decode(a, ctx->stream, &n);
+    ctx->launches.fetch_add(n);
+    if (e != cudaSuccess) return fail_cuda(e, "multihead_attention_static launch");
+    return YULE_OK;
+}
+
