@@ -112,6 +112,32 @@ def host_argmax_last(logits: np.ndarray) -> int:
     return int(logits.size - 1 - np.argmax(logits[::-1]))
 
 
+def build_model_70b(rank: int, world: int):
+    """BASELINE configs[4]: Llama-3-70B architecture, every linear Q4_K (~39 GB), row-sharded over `world` ranks.
+    To bound host time the quantised N(0, 0.02) tensors of one layer are generated once and uploaded for all
+    80 layers (distinct device buffers, so HBM traffic is that of 80 different layers)."""
+    from yule_b200 import DType, parallel, synth
+    cfg = synth.LLAMA3_70B
+    one = synth.synthetic_model(ModelConfigOneLayer(cfg), seed=70, linear=DType.Q4_K)
+    weights = {}
+    for name, val in one.items():
+        if name.startswith("blk.0."):
+            for l in range(cfg.n_layers):
+                weights[name.replace("blk.0.", f"blk.{l}.")] = val
+        else:
+            weights[name] = val
+    weights["token_embd.weight"] = weights["output.weight"]  # same bytes: only one row per token is read
+    if world > 1:
+        weights = parallel.shard_model(cfg, weights, rank, world)
+    prompt = synth.tokens(7, N_PROMPT, cfg.vocab_size)
+    return cfg, weights, prompt
+
+
+def ModelConfigOneLayer(cfg):
+    import dataclasses
+    return dataclasses.replace(cfg, n_layers=1)
+
+
 def build_model(rank: int):
     from yule_b200 import DType, synth
     cfg = synth.TINYLLAMA

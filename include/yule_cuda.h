@@ -212,6 +212,19 @@ int32_t yule_cuda_flush_l2(yule_cuda_ctx *ctx);
 /* Number of kernels this library has launched on the context so far. */
 int32_t yule_cuda_launch_count(yule_cuda_ctx *ctx, uint64_t *out_count);
 
+/* ── tensor parallelism over output rows (no counterpart in the reference, which is single-device):
+ *    one process and one context per GPU; rank 0 creates a 128-byte rendezvous id, the caller
+ *    carries it to the other ranks, every rank calls tp_init before creating its runner.  A runner
+ *    created on such a context expects each matrix to hold only this rank's rows
+ *    [rank*n/world, (rank+1)*n/world) (a byte slice of the raw tensor) and all-gathers the
+ *    activations over NCCL.  n_heads, n_kv_heads, dim, ff_dim and vocab_size must be multiples of
+ *    the world size. ── */
+int32_t yule_cuda_tp_unique_id(uint8_t *out_id128);
+int32_t yule_cuda_tp_init(yule_cuda_ctx *ctx, uint32_t rank, uint32_t world, const uint8_t *id128);
+/* In-place all-gather of fp32 on the context's stream: rank r's count_per_rank floats already sit
+ * at offset r*count_per_rank of the buffer; afterwards every rank holds every slice. */
+int32_t yule_cuda_tp_all_gather(yule_cuda_ctx *ctx, yule_buffer buffer, size_t count_per_rank);
+
 /* ── forward-pass runner: the `ModelRunner` trait
  *    (yule-infer/src/model_runner.rs:12-17) issued in the op order of
  *    GpuTransformerRunner::forward (yule-infer/src/gpu_runner.rs:296-695) ── */

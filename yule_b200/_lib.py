@@ -62,6 +62,9 @@ _SIGNATURES = {
     "yule_cuda_event_reset": [vp],
     "yule_cuda_flush_l2": [vp],
     "yule_cuda_launch_count": [vp, C.POINTER(u64)],
+    "yule_cuda_tp_unique_id": [C.POINTER(C.c_uint8)],
+    "yule_cuda_tp_init": [vp, u32, u32, C.POINTER(C.c_uint8)],
+    "yule_cuda_tp_all_gather": [vp, u64, size_t],
     "yule_cuda_runner_create": [vp, C.POINTER(RunnerConfig), C.POINTER(vp)],
     "yule_cuda_runner_destroy": [vp],
     "yule_cuda_runner_set_tensor": [vp, C.c_char_p, u64, u32],

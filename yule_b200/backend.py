@@ -199,6 +199,22 @@ class CudaB200Backend:
     def embed_gather(self, table: BufferHandle, dtype: DType, dim: int, token: int, out: BufferHandle) -> None:
         _check(self._lib.yule_cuda_embed_gather(self._ctx, table.id, int(dtype), dim, token, out.id))
 
+    # ── tensor parallelism (one process per GPU) ───────────────────────────────────────────
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """Rendezvous id created by rank 0; carry it to the other ranks (e.g. torch.distributed broadcast)."""
+        lib = _lib.cuda_lib()
+        buf = (C.c_uint8 * 128)()
+        _check(lib.yule_cuda_tp_unique_id(buf))
+        return bytes(buf)
+
+    def tp_init(self, rank: int, world: int, unique_id: bytes) -> None:
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        _check(self._lib.yule_cuda_tp_init(self._ctx, rank, world, buf))
+
+    def tp_all_gather(self, buffer: BufferHandle, count_per_rank: int) -> None:
+        _check(self._lib.yule_cuda_tp_all_gather(self._ctx, buffer.id, count_per_rank))
+
     # ── graph capture / replay (begin_batch / submit_batch of the Vulkan runner, in CUDA terms) ──
     def graph_begin(self) -> None:
         _check(self._lib.yule_cuda_graph_begin(self._ctx))

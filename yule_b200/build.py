@@ -46,7 +46,7 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
         os.path.join(os.path.dirname(HERE), "include", "yule_cuda.h"), os.path.abspath(__file__)]
     if force or _stale(CUDA_SO, deps):
         flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
-        cmd = [_nvcc()] + flags + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-o", CUDA_SO]
+        cmd = [_nvcc()] + flags + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-ldl", "-o", CUDA_SO]
         subprocess.check_call(cmd)
     return CUDA_SO
 

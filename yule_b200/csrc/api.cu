@@ -114,6 +114,7 @@ int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
     if (!ctx) return YULE_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    tp_destroy(ctx);
     for (auto &kv : ctx->buffers) {
         cudaFree(kv.second.ptr);
         if (kv.second.planar) cudaFree(kv.second.planar);

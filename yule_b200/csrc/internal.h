@@ -82,6 +82,9 @@ struct yule_cuda_ctx {
     uint64_t launches_at_capture_begin = 0;
     void *flush_buf = nullptr;
     size_t flush_bytes = 0;
+    // tensor parallelism (tp.cu): NCCL communicator of this rank, or null when single-GPU
+    void *tp_comm = nullptr;
+    uint32_t tp_rank = 0, tp_world = 1;
     // scratch of the split-KV attention entry point, grown on demand
     float *attn_scratch = nullptr;
     size_t attn_scratch_floats = 0;
@@ -179,6 +182,13 @@ size_t q6k_planar_bytes(uint64_t n_blocks);
 cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_blocks, cudaStream_t s, uint64_t *launches);
 bool q6k_mma_supported(uint32_t n_cols);
 cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches);
+
+// Tensor parallelism (tp.cu).
+struct NcclId {
+    char internal[128];
+};
+cudaError_t tp_all_gather_inplace(yule_cuda_ctx *ctx, float *buf, size_t count_per_rank);
+void tp_destroy(yule_cuda_ctx *ctx);
 
 // Launch helper shared by every kernel: optional programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>

@@ -252,8 +252,17 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     const int sms = r->ctx->prop.multiProcessorCount;
     const bool pdl = r->pdl;
     const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    // Tensor parallelism: this rank computes rows [R*n/N, (R+1)*n/N) of every matrix — its heads, its
+    // slice of the FFN, its slice of the vocabulary — into its slice of the full-size activation
+    // buffers, which are then all-gathered in place.
+    const uint32_t N = r->ctx->tp_world ? r->ctx->tp_world : 1, R = r->ctx->tp_rank;
+    const uint32_t qdim_l = qdim / N, kvdim_l = kvdim / N, ff_l = ff / N, dim_l = dim / N, vocab_l = c.vocab_size / N;
+    const uint32_t heads_l = c.n_heads / N, kvh_l = c.n_kv_heads / N;
     Step st{r};
     st.pdl = pdl;
+    auto gather = [&](float *buf, uint32_t per_rank) {
+        if (N > 1) st.ok(tp_all_gather_inplace(r->ctx, buf, per_rank));
+    };
     const uint32_t *tok_ptr = r->d_state, *pos_ptr = r->d_state + 1;
     // Timing aid: YULE_CUDA_SKIP is a bit mask of kernel classes to leave out of the graph (results
     // are then meaningless); the time that disappears is that class's cost inside the real step.
@@ -301,14 +310,15 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.then(&L.attn_output);  // while Q/K/V and attention run, o-proj's weights come in
         if (skip & 1) {
         } else if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
-            fused({{&L.attn_q, {r->q, qdim}}, {&L.attn_k, {r->k_tmp, kvdim}}, {&L.attn_v, {r->v_tmp, kvdim}}}, r->hidden,
-                  dim, L.attn_norm_f32, nullptr, false);
+            fused({{&L.attn_q, {r->q, qdim_l}}, {&L.attn_k, {r->k_tmp, kvdim_l}}, {&L.attn_v, {r->v_tmp, kvdim_l}}},
+                  r->hidden, dim, L.attn_norm_f32, nullptr, false);
         } else {
             st.ok(launch_rms_norm(r->hidden, L.attn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
-            st.qmv(L.attn_q, r->normed, r->q, qdim, dim);
-            st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim, dim);
-            st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim, dim);
+            st.qmv(L.attn_q, r->normed, r->q, qdim_l, dim);
+            st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim_l, dim);
+            st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim_l, dim);
         }
+        float *attn_out_l = r->attn_out + (size_t)R * qdim_l;
         if (attn_decode_supported(hd)) {
             // Rope dispatch + both KV copies + MultiheadAttn in one launch
             AttnDecode a;
@@ -320,13 +330,13 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             a.cos_table = r->rope_cos;
             a.sin_table = r->rope_sin;
             a.pos_ptr = pos_ptr;
-            a.out = r->attn_out;
+            a.out = attn_out_l;
             a.scratch = r->attn_scratch;
             a.tickets = r->attn_tickets;
             a.hd = hd;
-            a.n_heads = c.n_heads;
-            a.n_kv_heads = c.n_kv_heads;
-            a.kv_stride = kvdim;
+            a.n_heads = heads_l;
+            a.n_kv_heads = kvh_l;
+            a.kv_stride = kvdim_l;
             a.n_splits = r->attn_splits;
             a.max_seq_len = c.max_seq_len;
             a.min_chunk = getenv("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_ATTN_MIN_CHUNK")) : 32;
@@ -335,42 +345,49 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         } else {
             if (!(skip & 2))
                 st.ok(launch_rope_kv_write(r->q, r->k_tmp, r->v_tmp, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin,
-                                           pos_ptr, hd, c.n_heads, c.n_kv_heads, s, &st.n, pdl));
+                                           pos_ptr, hd, heads_l, kvh_l, s, &st.n, pdl));
             if (!(skip & 4))
-                st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, 0, pos_ptr, c.max_seq_len,
-                                                 c.n_heads, c.n_kv_heads, kvdim, s, &st.n, pdl));
+                st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, attn_out_l, hd, 0, pos_ptr, c.max_seq_len,
+                                                 heads_l, kvh_l, kvdim_l, s, &st.n, pdl));
         }
+        gather(r->attn_out, qdim_l);
+        float *hidden_l = r->hidden + (size_t)R * dim_l;
         // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
         st.then(&L.ffn_gate, &L.ffn_up);
-        if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, r->hidden, dim, qdim, r->hidden);
+        if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l);
+        gather(r->hidden, dim_l);
         st.then(&L.ffn_down);
         if (skip & 16) {
         } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
-            fused({{&L.ffn_gate, {r->gate, ff}}, {&L.ffn_up, {r->up, ff}}}, r->hidden, dim, L.ffn_norm_f32, nullptr, true);
+            fused({{&L.ffn_gate, {r->gate + (size_t)R * ff_l, ff_l}}, {&L.ffn_up, {r->up, ff_l}}}, r->hidden, dim,
+                  L.ffn_norm_f32, nullptr, true);
         } else {
             st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
-            st.qmv(L.ffn_gate, r->normed, r->gate, ff, dim);
-            st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
-            st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n, pdl));
+            st.qmv(L.ffn_gate, r->normed, r->gate + (size_t)R * ff_l, ff_l, dim);
+            st.qmv(L.ffn_up, r->normed, r->up, ff_l, dim);
+            st.ok(launch_silu_mul(r->gate + (size_t)R * ff_l, r->up, r->gate + (size_t)R * ff_l, ff_l, s, &st.n, pdl));
         }
+        gather(r->gate, ff_l);
         // during down-proj: the next layer's Q and K/V (or the output matrix after the last layer)
         if (l + 1 < c.n_layers)
             st.then(&r->layers[l + 1].attn_q, &r->layers[l + 1].attn_k);
         else
             st.then(&out_w_);
-        if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, r->hidden, dim, ff, r->hidden);
+        if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l);
+        gather(r->hidden, dim_l);
     }
     st.then(nullptr);
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     if (skip & 64) {
     } else if (all_q4k({&out_w}, dim)) {
-        fused({{&out_w, {r->logits, c.vocab_size}}}, r->hidden, dim, r->output_norm_f32, nullptr, false);
+        fused({{&out_w, {r->logits + (size_t)R * vocab_l, vocab_l}}}, r->hidden, dim, r->output_norm_f32, nullptr, false);
     } else if (out_w.type == YULE_DTYPE_Q6_K && out_w.buf.planar && q6k_mma_supported(dim)) {
-        st.qmv(out_w, r->hidden, r->logits, c.vocab_size, dim, nullptr, r->output_norm_f32);
+        st.qmv(out_w, r->hidden, r->logits + (size_t)R * vocab_l, vocab_l, dim, nullptr, r->output_norm_f32);
     } else {
         st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
-        st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
+        st.qmv(out_w, r->normed, r->logits + (size_t)R * vocab_l, vocab_l, dim);
     }
+    gather(r->logits, vocab_l);
     if (!(skip & 128)) st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, r->d_history, s, &st.n, pdl));
     *launches += st.n;
     return st.err;
@@ -379,8 +396,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
 int32_t finalize(yule_cuda_runner *r) {
     if (r->finalized) return YULE_OK;
     const yule_runner_config &c = r->cfg;
-    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    const uint32_t N = r->ctx->tp_world ? r->ctx->tp_world : 1;
+    // rows this rank holds of each matrix (all of them when single-GPU); input widths stay global
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim_in = c.n_heads * hd, ff_in = c.ff_dim;
+    const uint32_t qdim = qdim_in / N, kvdim = c.n_kv_heads * hd / N, ff = ff_in / N, dim_rows = dim / N,
+                   vocab_rows = c.vocab_size / N;
     int32_t rc;
+    if (N > 1 && !r->output.set)
+        return fail(YULE_ERR_MISSING_TENSOR, "tensor parallelism needs output.weight (a tied embedding cannot be row-sharded)");
     if (!r->token_embd.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: token_embd.weight");
     {
         uint32_t bs = block_size(r->token_embd.type);
@@ -390,7 +413,7 @@ int32_t finalize(yule_cuda_runner *r) {
     }
     if ((rc = norm_as_f32(r, r->output_norm, "output_norm.weight", 0, &r->output_norm_f32))) return rc;
     if (r->output.set) {
-        if ((rc = check_matrix(r->output, "output.weight", 0, c.vocab_size, dim))) return rc;
+        if ((rc = check_matrix(r->output, "output.weight", 0, vocab_rows, dim))) return rc;
     } else if ((rc = check_matrix(r->token_embd, "token_embd.weight (as output)", 0, c.vocab_size, dim))) {
         return rc;
     }
@@ -401,10 +424,10 @@ int32_t finalize(yule_cuda_runner *r) {
         if ((rc = check_matrix(L.attn_q, "attn_q.weight", l, qdim, dim))) return rc;
         if ((rc = check_matrix(L.attn_k, "attn_k.weight", l, kvdim, dim))) return rc;
         if ((rc = check_matrix(L.attn_v, "attn_v.weight", l, kvdim, dim))) return rc;
-        if ((rc = check_matrix(L.attn_output, "attn_output.weight", l, dim, qdim))) return rc;
+        if ((rc = check_matrix(L.attn_output, "attn_output.weight", l, dim_rows, qdim_in))) return rc;
         if ((rc = check_matrix(L.ffn_gate, "ffn_gate.weight", l, ff, dim))) return rc;
         if ((rc = check_matrix(L.ffn_up, "ffn_up.weight", l, ff, dim))) return rc;
-        if ((rc = check_matrix(L.ffn_down, "ffn_down.weight", l, dim, ff))) return rc;
+        if ((rc = check_matrix(L.ffn_down, "ffn_down.weight", l, dim_rows, ff_in))) return rc;
     }
     // Device-side planar copies for the formats whose fast kernel wants one (Q6_K).
     auto prepare = [&](Tensor &t, uint32_t rows, uint32_t cols) -> int32_t {
@@ -414,13 +437,13 @@ int32_t finalize(yule_cuda_runner *r) {
         if (!r->ctx->find(t.handle, &t.buf, "prepared tensor")) return YULE_ERR_UNKNOWN_BUFFER;
         return YULE_OK;
     };
-    if ((rc = prepare(r->output.set ? r->output : r->token_embd, c.vocab_size, dim))) return rc;
+    if ((rc = prepare(r->output.set ? r->output : r->token_embd, vocab_rows, dim))) return rc;
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
         if ((rc = prepare(L.attn_q, qdim, dim)) || (rc = prepare(L.attn_k, kvdim, dim)) ||
-            (rc = prepare(L.attn_v, kvdim, dim)) || (rc = prepare(L.attn_output, dim, qdim)) ||
+            (rc = prepare(L.attn_v, kvdim, dim)) || (rc = prepare(L.attn_output, dim_rows, qdim_in)) ||
             (rc = prepare(L.ffn_gate, ff, dim)) || (rc = prepare(L.ffn_up, ff, dim)) ||
-            (rc = prepare(L.ffn_down, dim, ff)))
+            (rc = prepare(L.ffn_down, dim_rows, ff_in)))
             return rc;
     }
     r->finalized = true;
@@ -517,6 +540,13 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     if (c.head_dim % 2 || c.head_dim > 256) return fail(YULE_ERR_INVALID_ARGUMENT, "head_dim must be even and <= 256");
     if (c.dim % 32 || c.ff_dim % 32 || (c.n_heads * c.head_dim) % 32)
         return fail(YULE_ERR_INVALID_ARGUMENT, "dim, ff_dim and n_heads*head_dim must be multiples of 32");
+    const uint32_t tpw = ctx->tp_world ? ctx->tp_world : 1;
+    if (tpw > 1) {
+        if (!c.fused) return fail(YULE_ERR_INVALID_ARGUMENT, "tensor parallelism needs a runner created with fused = 1");
+        if (c.n_heads % tpw || c.n_kv_heads % tpw || c.dim % tpw || c.ff_dim % tpw || c.vocab_size % tpw ||
+            (c.dim / tpw) % 8 || (c.ff_dim / tpw) % 8 || (c.vocab_size / tpw) % 8)
+            return fail(YULE_ERR_INVALID_ARGUMENT, "model dimensions do not split evenly over %u ranks", tpw);
+    }
     auto *r = new yule_cuda_runner();
     r->ctx = ctx;
     r->cfg = c;
@@ -531,9 +561,10 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     A(c.dim, &r->hidden, &r->hidden_h);
     A(c.dim, &r->residual);
     A(c.dim, &r->normed);
-    A(qdim, &r->q);
-    A(kvdim, &r->k_tmp);
-    A(kvdim, &r->v_tmp);
+    const uint32_t kvdim_l = kvdim / tpw;  // this rank's KV heads
+    A(qdim / tpw, &r->q);
+    A(kvdim_l, &r->k_tmp);
+    A(kvdim_l, &r->v_tmp);
     A(qdim, &r->attn_out);
     A(c.dim, &r->attn_proj);
     A(c.ff_dim, &r->gate);
@@ -553,8 +584,8 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     A((size_t)c.max_seq_len + 1, &tmp);
     r->d_history = (uint32_t *)tmp;
     for (uint32_t l = 0; l < c.n_layers && rc == YULE_OK; l++) {
-        A((size_t)c.max_seq_len * kvdim, &r->layers[l].k_cache, &r->layers[l].k_cache_h);
-        A((size_t)c.max_seq_len * kvdim, &r->layers[l].v_cache, &r->layers[l].v_cache_h);
+        A((size_t)c.max_seq_len * kvdim_l, &r->layers[l].k_cache, &r->layers[l].k_cache_h);
+        A((size_t)c.max_seq_len * kvdim_l, &r->layers[l].v_cache, &r->layers[l].v_cache_h);
     }
     if (rc == YULE_OK) rc = ensure_pinned(r, 4096);
     if (rc == YULE_OK) {
