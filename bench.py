@@ -146,17 +146,16 @@ def build_model(rank: int):
     return cfg, weights, prompt
 
 
-def decode_bytes_per_token(cfg, weights, pos: int) -> int:
-    """Algorithmic HBM bytes of one decode token: every matrix once, the embedding row, and the KV
-    rows of positions [0, pos] for every layer (K and V)."""
-    from yule_b200 import DType
+def decode_bytes_per_token(cfg, weights, pos: int, tp_world: int = 1) -> int:
+    """Algorithmic HBM bytes one GPU reads per decode token: every matrix (shard) once, the embedding row,
+    and this GPU's KV rows of positions [0, pos] for every layer (K and V)."""
     total = 0
     for name, (data, dt) in weights.items():
         if name == "token_embd.weight":
             total += data.size // cfg.vocab_size
         else:
             total += data.size
-    total += 2 * cfg.n_layers * (pos + 1) * cfg.n_kv_heads * cfg.head_dim * 4
+    total += 2 * cfg.n_layers * (pos + 1) * (cfg.n_kv_heads // tp_world) * cfg.head_dim * 4
     return total
 
 
@@ -273,7 +272,15 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         return float(t.item())
 
     backend = CudaB200Backend(local_rank)
-    cfg, weights, prompt = build_model(rank)
+    tp = args.workload == "c4"
+    if tp:
+        if world > 1:
+            ids = [CudaB200Backend.tp_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            backend.tp_init(rank, world, ids[0])
+        cfg, weights, prompt = build_model_70b(rank, world)
+    else:
+        cfg, weights, prompt = build_model(rank)
     runner = CudaTransformerRunner(backend, cfg, weights, fused=True)
 
     def job():
@@ -328,7 +335,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
 
     decode_ms_max = max_over_ranks(decode_ms)
     e2e_ms_max = max_over_ranks(e2e_ms)
-    total_tokens = N_GEN * args.steps * world
+    # replicas: every rank decodes its own sequence; tensor parallelism: all ranks decode one sequence
+    total_tokens = N_GEN * args.steps * (1 if tp else world)
     value = total_tokens / (decode_ms_max * 1e-3)
     e2e_value = total_tokens / (e2e_ms_max * 1e-3)
 
@@ -336,7 +344,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         peaks, peak_kind = measured_peaks()
         roof = matvec_ring_roofline(backend, peaks, peak_kind, iters=20 if args.small else 1000)
         mid_pos = N_PROMPT + N_GEN // 2
-        bpt = decode_bytes_per_token(cfg, weights, mid_pos)
+        bpt = decode_bytes_per_token(cfg, weights, mid_pos, tp_world=world if tp else 1)
         per_gpu_tok_s = N_GEN * args.steps / (decode_ms * 1e-3)
         decode_gbs = bpt * per_gpu_tok_s / 1e9
         cpu = None
@@ -346,11 +354,19 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round((prefill_ms + decode_ms) / args.steps, 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1] TinyLlama-1.1B-arch decode, Q4_K linears, Q6_K output+ffn_down, "
-                                   "fp32 KV, batch 1, 32-token prompt + 128 greedy tokens per step",
-                       "parallelism": f"{world} independent replica(s), one sequence per GPU",
-                       "l2": "weights read per token (664 MB) exceed the 126 MB L2; no flush needed"},
+            "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": ({"workload": "configs[4] Llama-3-70B-arch decode, all linears Q4_K (one layer's tensors "
+                                    f"repeated for the 80 layers), fp32 KV, batch 1, {N_PROMPT}-token prompt + {N_GEN} "
+                                    "greedy tokens per step",
+                        "parallelism": f"tp{world}: output rows of every linear sharded over {world} GPU(s), "
+                                       "NCCL all-gather of activations",
+                        "l2": "weights read per token per GPU (39 GB / N) exceed the 126 MB L2; no flush needed"}
+                       if tp else
+                       {"workload": "configs[1] TinyLlama-1.1B-arch decode, Q4_K linears, Q6_K output+ffn_down, "
+                                    f"fp32 KV, batch 1, {N_PROMPT}-token prompt + {N_GEN} greedy tokens per step",
+                        "parallelism": f"{world} independent replica(s), one sequence per GPU",
+                        "l2": "weights read per token (664 MB) exceed the 126 MB L2; no flush needed"}),
             "decode": {"ms_per_token": round(decode_ms / (N_GEN * args.steps), 4),
                        "prefill_tokens_per_s": round(N_PROMPT * args.steps / (prefill_ms * 1e-3), 1),
                        "hbm_bytes_per_token": bpt, "achieved_gbs": round(decode_gbs, 1),
@@ -376,12 +392,18 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=["c1", "c4"], default="c1",
+                    help="c1: TinyLlama-arch decode, one replica per GPU (default).  c4: Llama-3-70B-arch decode, "
+                         "row-sharded tensor parallelism over the GPUs (512-token prompt + 256 tokens)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized run: 4-token prompt + 4 tokens, 20 ring launches, no CPU leg")
     args = ap.parse_args()
+    global N_PROMPT, N_GEN
+    if args.workload == "c4":
+        N_PROMPT, N_GEN = 512, 256
+        args.no_cpu_baseline = True  # the CPU runner needs minutes per token at this size
     if args.small:
-        global N_PROMPT, N_GEN
         N_PROMPT, N_GEN = 4, 4
         args.no_cpu_baseline = True
     rank = int(os.environ.get("RANK", "0"))
