@@ -47,7 +47,10 @@ def _gpu_count() -> int:
         return 0
 
 
-def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path):
+@pytest.mark.parametrize("collective", ["peer_exchange", "nccl"])
+def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path, collective):
+    """Both forms of the all-gather: stores into the peers' mapped buffers with epoch flags (default), and
+    NCCL's all-gather (YULE_TP_NCCL=1)."""
     if _gpu_count() < 2:
         pytest.skip("needs two GPUs")
     from yule_b200 import CudaTransformerRunner, DType, ModelConfig, synth
@@ -68,7 +71,7 @@ def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path):
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", PORT=str(port), OUT=str(tmp_path), YULE_ROOT=ROOT,
-                   NCCL_NVLS_ENABLE="0")
+                   NCCL_NVLS_ENABLE="0", YULE_TP_NCCL="1" if collective == "nccl" else "0")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env))
     for p in procs:
         assert p.wait(timeout=600) == 0

@@ -304,6 +304,7 @@ __global__ void argmax_kernel(const float *__restrict__ v, uint32_t n, uint32_t 
                 const uint32_t pos = state[1];
                 history[pos] = idx;
                 state[1] = pos + 1;
+                state[2] += 1;  // token counter that reset() never rewinds (epochs of the peer exchange)
             }
         }
     }

@@ -85,6 +85,8 @@ struct yule_cuda_ctx {
     // tensor parallelism (tp.cu): NCCL communicator of this rank, or null when single-GPU
     void *tp_comm = nullptr;
     uint32_t tp_rank = 0, tp_world = 1;
+    float *tp_peer_base[8] = {};  // exchange regions: own allocation at [tp_rank], peers' mappings elsewhere
+    size_t tp_flag_offset = 0, tp_xchg_floats = 0;
     // scratch of the split-KV attention entry point, grown on demand
     float *attn_scratch = nullptr;
     size_t attn_scratch_floats = 0;
@@ -189,6 +191,11 @@ struct NcclId {
 };
 cudaError_t tp_all_gather_inplace(yule_cuda_ctx *ctx, float *buf, size_t count_per_rank);
 void tp_destroy(yule_cuda_ctx *ctx);
+// Peer-memory exchange: the same all-gather as stores into every peer's mapped buffer plus epoch flags.
+int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base);
+bool tp_has_exchange(const yule_cuda_ctx *ctx);
+cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot,
+                        const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches);
 
 // Launch helper shared by every kernel: optional programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>

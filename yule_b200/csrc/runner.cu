@@ -54,7 +54,11 @@ struct yule_cuda_runner {
     float *attn_scratch = nullptr;  // partial results of the split-KV attention
     uint32_t *attn_tickets = nullptr;
     uint32_t attn_splits = 1;
-    uint32_t *d_state = nullptr;    // [0] token, [1] position
+    // tensor parallelism with the peer-memory exchange: offsets (floats) of the gathered buffers inside
+    // the exchange region
+    bool xchg = false;
+    size_t x_attn_out = 0, x_hidden = 0, x_gate = 0, x_logits = 0;
+    uint32_t *d_state = nullptr;    // [0] token, [1] position, [2] tokens processed since creation
     uint32_t *d_history = nullptr;  // greedy pick made after each position
     uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
     size_t h_pinned_cap = 0;
@@ -260,8 +264,16 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     const uint32_t heads_l = c.n_heads / N, kvh_l = c.n_kv_heads / N;
     Step st{r};
     st.pdl = pdl;
-    auto gather = [&](float *buf, uint32_t per_rank) {
-        if (N > 1) st.ok(tp_all_gather_inplace(r->ctx, buf, per_rank));
+    // All-gather number `k` of layer `layer` (k = 4: the logits).  With the peer exchange each gather
+    // has its own flag slot and an epoch derived from the token counter in d_state[2].
+    const uint32_t epochs_per_token = 4 * c.n_layers + 1;
+    auto gather = [&](float *buf, size_t x_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
+        if (N <= 1) return;
+        if (r->xchg)
+            st.ok(tp_exchange(r->ctx, x_off, per_rank, k, r->d_state + 2, epochs_per_token, k == 4 ? 4 * c.n_layers : 4 * layer + k,
+                              pdl, &st.n));
+        else
+            st.ok(tp_all_gather_inplace(r->ctx, buf, per_rank));
     };
     const uint32_t *tok_ptr = r->d_state, *pos_ptr = r->d_state + 1;
     // Timing aid: YULE_CUDA_SKIP is a bit mask of kernel classes to leave out of the graph (results
@@ -350,12 +362,12 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
                 st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, attn_out_l, hd, 0, pos_ptr, c.max_seq_len,
                                                  heads_l, kvh_l, kvdim_l, s, &st.n, pdl));
         }
-        gather(r->attn_out, qdim_l);
+        gather(r->attn_out, r->x_attn_out, qdim_l, l, 0);
         float *hidden_l = r->hidden + (size_t)R * dim_l;
         // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
         st.then(&L.ffn_gate, &L.ffn_up);
         if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l);
-        gather(r->hidden, dim_l);
+        gather(r->hidden, r->x_hidden, dim_l, l, 1);
         st.then(&L.ffn_down);
         if (skip & 16) {
         } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
@@ -367,14 +379,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.qmv(L.ffn_up, r->normed, r->up, ff_l, dim);
             st.ok(launch_silu_mul(r->gate + (size_t)R * ff_l, r->up, r->gate + (size_t)R * ff_l, ff_l, s, &st.n, pdl));
         }
-        gather(r->gate, ff_l);
+        gather(r->gate, r->x_gate, ff_l, l, 2);
         // during down-proj: the next layer's Q and K/V (or the output matrix after the last layer)
         if (l + 1 < c.n_layers)
             st.then(&r->layers[l + 1].attn_q, &r->layers[l + 1].attn_k);
         else
             st.then(&out_w_);
         if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l);
-        gather(r->hidden, dim_l);
+        gather(r->hidden, r->x_hidden, dim_l, l, 3);
     }
     st.then(nullptr);
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
@@ -387,7 +399,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
         st.qmv(out_w, r->normed, r->logits + (size_t)R * vocab_l, vocab_l, dim);
     }
-    gather(r->logits, vocab_l);
+    gather(r->logits, r->x_logits, vocab_l, 0, 4);
     if (!(skip & 128)) st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, r->d_history, s, &st.n, pdl));
     *launches += st.n;
     return st.err;
@@ -521,7 +533,7 @@ int32_t read_logits(yule_cuda_runner *r, float *logits_out) {
     cudaStream_t s = r->ctx->stream;
     YULE_CUDA_TRY(cudaMemcpyAsync(logits_out, r->logits, (size_t)r->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, s));
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
-    return YULE_OK;
+    return r->xchg ? yule_cuda_synchronize(r->ctx) : YULE_OK;  // reports a peer that never arrived
 }
 
 }  // namespace
@@ -558,19 +570,37 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     auto A = [&](size_t n, float **p, yule_buffer *h = nullptr) {
         if (rc == YULE_OK) rc = alloc_f32(r, n, p, h);
     };
-    A(c.dim, &r->hidden, &r->hidden_h);
+    const bool use_xchg = tpw > 1 && !(getenv("YULE_TP_NCCL") && atoi(getenv("YULE_TP_NCCL")) != 0);
+    if (use_xchg) {
+        // gathered activations live in one region that every peer maps
+        r->x_attn_out = 0;
+        r->x_hidden = r->x_attn_out + qdim;
+        r->x_gate = r->x_hidden + c.dim;
+        r->x_logits = r->x_gate + c.ff_dim;
+        float *base = nullptr;
+        rc = tp_setup_exchange(ctx, r->x_logits + c.vocab_size, &base);
+        if (rc == YULE_OK) {
+            r->xchg = true;
+            r->attn_out = base + r->x_attn_out;
+            r->hidden = base + r->x_hidden;
+            r->gate = base + r->x_gate;
+            r->logits = base + r->x_logits;
+        }
+    } else {
+        A(c.dim, &r->hidden, &r->hidden_h);
+    }
     A(c.dim, &r->residual);
     A(c.dim, &r->normed);
     const uint32_t kvdim_l = kvdim / tpw;  // this rank's KV heads
     A(qdim / tpw, &r->q);
     A(kvdim_l, &r->k_tmp);
     A(kvdim_l, &r->v_tmp);
-    A(qdim, &r->attn_out);
+    if (!use_xchg) A(qdim, &r->attn_out);
     A(c.dim, &r->attn_proj);
-    A(c.ff_dim, &r->gate);
+    if (!use_xchg) A(c.ff_dim, &r->gate);
     A(c.ff_dim, &r->up);
     A(c.dim, &r->ffn_out);
-    A(c.vocab_size, &r->logits, &r->logits_h);
+    if (!use_xchg) A(c.vocab_size, &r->logits, &r->logits_h);
     const size_t half = hd / 2;
     A((size_t)c.max_seq_len * half, &r->rope_cos);
     A((size_t)c.max_seq_len * half, &r->rope_sin);
@@ -579,7 +609,7 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     A(attn_scratch_floats(c.n_heads, r->attn_splits, hd) + 4, &r->attn_scratch);
     A(c.n_heads, &tmp);
     r->attn_tickets = (uint32_t *)tmp;  // zero-filled by the allocator
-    A(2, &tmp);
+    A(4, &tmp);
     r->d_state = (uint32_t *)tmp;
     A((size_t)c.max_seq_len + 1, &tmp);
     r->d_history = (uint32_t *)tmp;
@@ -717,14 +747,17 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *pr
                                       cudaMemcpyDeviceToHost, s));
     }
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
-    return YULE_OK;
+    return r->xchg ? yule_cuda_synchronize(r->ctx) : YULE_OK;  // reports a peer that never arrived
 }
 
 int32_t yule_cuda_runner_buffer(yule_cuda_runner *r, uint32_t which, uint32_t layer, yule_buffer *out_handle) {
     if (!r || !out_handle) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
     switch (which) {
-        case 0: *out_handle = r->hidden_h; return YULE_OK;
-        case 3: *out_handle = r->logits_h; return YULE_OK;
+        case 0:
+        case 3:
+            if (r->xchg) return fail(YULE_ERR_INVALID_ARGUMENT, "hidden/logits live in the peer exchange region, not in a buffer");
+            *out_handle = which == 0 ? r->hidden_h : r->logits_h;
+            return YULE_OK;
         case 1:
         case 2:
             if (layer >= r->cfg.n_layers) return fail(YULE_ERR_INVALID_ARGUMENT, "layer %u out of range", layer);

@@ -14,6 +14,7 @@
 #include <dlfcn.h>
 
 #include <cstring>
+#include <vector>
 
 #include "internal.h"
 
@@ -62,6 +63,134 @@ int32_t nccl_fail(int rc, const char *what) {
 
 }  // namespace
 
+// ── peer-memory exchange ────────────────────────────────────────────────────────────────────
+// NCCL's all-gather costs ~20 µs for the few KB a decode step exchanges, 4 times per layer; at batch
+// 1 that is more than the matvecs it separates.  The runner therefore keeps the gathered activation
+// buffers in one "exchange" allocation per rank that every peer maps (cudaIpc, over NVLink), and an
+// all-gather becomes: each rank stores its slice straight into every peer's copy, fences, and
+// publishes an epoch number in the peer's flag word; it then waits — for a bounded time — until its
+// own flag words show the same epoch from every peer.  Plain stores and volatile loads only.
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kFlagSlots = 8;
+constexpr int kXchgThreads = 256;
+
+struct PeerTable {
+    float *base[kMaxRanks];  // peer r's exchange region as mapped into this process (own region for r = rank)
+};
+
+// Flags live at the end of the exchange region: [slot][source rank] epochs, then one CTA counter.
+__device__ __forceinline__ uint32_t *flags_of(float *base, size_t flag_offset_floats) {
+    return reinterpret_cast<uint32_t *>(base + flag_offset_floats);
+}
+
+__global__ void __launch_bounds__(kXchgThreads)
+tp_exchange_kernel(PeerTable peers, size_t buf_offset, uint32_t per_rank, uint32_t rank, uint32_t world,
+                   size_t flag_offset, uint32_t slot, const uint32_t *__restrict__ tick, uint32_t epochs_per_tick,
+                   uint32_t epoch_index, int *__restrict__ status, long long wait_cycles) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
+    // One epoch per (token, exchange): the token counter only changes in another kernel, so every
+    // CTA of every rank computes the same number.
+    const uint32_t epoch = *tick * epochs_per_tick + epoch_index + 1u;
+    float *mine = peers.base[rank] + buf_offset + (size_t)rank * per_rank;
+    // push this rank's slice into every peer's copy of the buffer
+    const uint32_t n4 = per_rank / 4;
+    for (uint32_t p = 0; p < world; p++) {
+        if (p == rank) continue;
+        float4 *dst = reinterpret_cast<float4 *>(peers.base[p] + buf_offset + (size_t)rank * per_rank);
+        const float4 *src = reinterpret_cast<const float4 *>(mine);
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ uint32_t s_last;
+    uint32_t *my_flags = flags_of(peers.base[rank], flag_offset);
+    uint32_t *counter = my_flags + kFlagSlots * kMaxRanks;
+    if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    // every CTA's stores are fenced: publish, then wait for the peers' slices
+    __threadfence_system();
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        volatile uint32_t *theirs = flags_of(peers.base[threadIdx.x], flag_offset) + slot * kMaxRanks + rank;
+        *theirs = epoch;
+    }
+    if (threadIdx.x == 0) *counter = 0;
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        volatile uint32_t *f = my_flags + slot * kMaxRanks + threadIdx.x;
+        const long long t0 = clock64();
+        // bounded: a peer that never arrives leaves a status word for the host instead of a hung GPU
+        while ((int32_t)(*f - epoch) < 0) {
+            if (clock64() - t0 > wait_cycles) {
+                atomicExch(status, 2);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+}
+
+}  // namespace
+
+cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot,
+                        const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches) {
+    PeerTable pt;
+    for (int i = 0; i < kMaxRanks; i++) pt.base[i] = ctx->tp_peer_base[i];
+    uint32_t grid = (per_rank / 4 + kXchgThreads - 1) / kXchgThreads;
+    grid = grid < 1 ? 1 : (grid > 8 ? 8 : grid);
+    // ~2 s at the SM clock: far beyond any real skew between ranks, short enough to report a lost peer
+    const long long wait_cycles = 4000000000LL;
+    *launches += 1;
+    return launch_kernel(tp_exchange_kernel, dim3(grid), dim3(kXchgThreads), 0, ctx->stream, pdl, pt, buf_offset_floats,
+                         per_rank, ctx->tp_rank, ctx->tp_world, ctx->tp_flag_offset, slot, tick, epochs_per_tick,
+                         epoch_index, ctx->device_status, wait_cycles);
+}
+
+// Allocates this rank's exchange region (n_floats of payload + flags), maps every peer's, and
+// returns the local base.  Handles travel through one NCCL all-gather, so no other channel between
+// the processes is needed.
+int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base) {
+    if (ctx->tp_world <= 1 || !ctx->tp_comm) return fail(YULE_ERR_INVALID_ARGUMENT, "tensor parallelism is not initialised");
+    if (ctx->tp_world > (uint32_t)kMaxRanks) return fail(YULE_ERR_INVALID_ARGUMENT, "at most %d ranks", kMaxRanks);
+    if (ctx->tp_peer_base[ctx->tp_rank]) return fail(YULE_ERR_INVALID_ARGUMENT, "exchange region already set up on this context");
+    const size_t payload = (n_floats + 63) & ~(size_t)63;
+    const size_t bytes = payload * sizeof(float) + (kFlagSlots * kMaxRanks + 64) * sizeof(uint32_t);
+    float *base = nullptr;
+    YULE_CUDA_TRY(cudaMalloc((void **)&base, bytes));
+    YULE_CUDA_TRY(cudaMemset(base, 0, bytes));
+    cudaIpcMemHandle_t mine;
+    YULE_CUDA_TRY(cudaIpcGetMemHandle(&mine, base));
+    // all-gather the 64-byte handles on the device
+    unsigned char *d_handles = nullptr;
+    YULE_CUDA_TRY(cudaMalloc((void **)&d_handles, sizeof(mine) * ctx->tp_world));
+    YULE_CUDA_TRY(cudaMemcpy(d_handles + sizeof(mine) * ctx->tp_rank, &mine, sizeof(mine), cudaMemcpyHostToDevice));
+    int rc = g_nccl.AllGather(d_handles + sizeof(mine) * ctx->tp_rank, d_handles, sizeof(mine), /*ncclChar*/ 0, ctx->tp_comm,
+                              ctx->stream);
+    if (rc != 0) return nccl_fail(rc, "ncclAllGather of the exchange handles");
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    std::vector<cudaIpcMemHandle_t> all(ctx->tp_world);
+    YULE_CUDA_TRY(cudaMemcpy(all.data(), d_handles, sizeof(mine) * ctx->tp_world, cudaMemcpyDeviceToHost));
+    YULE_CUDA_TRY(cudaFree(d_handles));
+    for (uint32_t p = 0; p < ctx->tp_world; p++) {
+        if (p == ctx->tp_rank) {
+            ctx->tp_peer_base[p] = base;
+            continue;
+        }
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return fail_cuda(e, "cudaIpcOpenMemHandle of a peer's exchange region");
+        ctx->tp_peer_base[p] = (float *)ptr;
+    }
+    ctx->tp_flag_offset = payload;
+    ctx->tp_xchg_floats = payload;
+    *out_base = base;
+    return YULE_OK;
+}
+
+bool tp_has_exchange(const yule_cuda_ctx *ctx) { return ctx->tp_world > 1 && ctx->tp_peer_base[ctx->tp_rank] != nullptr; }
+
 // In-place all-gather of fp32: every rank's slice of `count` floats already sits at
 // buf + rank*count; afterwards all ranks hold all slices.  Enqueued on the context's stream
 // (capturable into a CUDA graph).
@@ -72,6 +201,14 @@ cudaError_t tp_all_gather_inplace(yule_cuda_ctx *ctx, float *buf, size_t count) 
 }
 
 void tp_destroy(yule_cuda_ctx *ctx) {
+    for (uint32_t p = 0; p < (uint32_t)kMaxRanks; p++) {
+        if (!ctx->tp_peer_base[p]) continue;
+        if (p == ctx->tp_rank)
+            cudaFree(ctx->tp_peer_base[p]);
+        else
+            cudaIpcCloseMemHandle(ctx->tp_peer_base[p]);
+        ctx->tp_peer_base[p] = nullptr;
+    }
     if (ctx->tp_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->tp_comm);
     ctx->tp_comm = nullptr;
 }
