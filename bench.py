@@ -112,13 +112,15 @@ def host_argmax_last(logits: np.ndarray) -> int:
     return int(logits.size - 1 - np.argmax(logits[::-1]))
 
 
-def build_model_70b(rank: int, world: int):
-    """BASELINE configs[4]: Llama-3-70B architecture, every linear Q4_K (~39 GB), row-sharded over `world` ranks.
+def build_model_70b(rank: int, world: int, which: str = "c4"):
+    """BASELINE configs[4]: Llama-3-70B architecture, every linear Q4_K (~39 GB), row-sharded over `world` ranks;
+    configs[3]: Llama-3-8B architecture, Q4_K linears with a Q6_K output matrix.
     To bound host time the quantised N(0, 0.02) tensors of one layer are generated once and uploaded for all
-    80 layers (distinct device buffers, so HBM traffic is that of 80 different layers)."""
+    the layers (distinct device buffers, so HBM traffic is that of different layers)."""
     from yule_b200 import DType, parallel, synth
-    cfg = synth.LLAMA3_70B
-    one = synth.synthetic_model(ModelConfigOneLayer(cfg), seed=70, linear=DType.Q4_K)
+    cfg = synth.LLAMA3_70B if which == "c4" else synth.LLAMA3_8B
+    one = synth.synthetic_model(ModelConfigOneLayer(cfg), seed=70, linear=DType.Q4_K,
+                                output=DType.Q4_K if which == "c4" else DType.Q6_K, token_embd=DType.Q4_K)
     weights = {}
     for name, val in one.items():
         if name.startswith("blk.0."):
@@ -126,7 +128,8 @@ def build_model_70b(rank: int, world: int):
                 weights[name.replace("blk.0.", f"blk.{l}.")] = val
         else:
             weights[name] = val
-    weights["token_embd.weight"] = weights["output.weight"]  # same bytes: only one row per token is read
+    if which == "c4":
+        weights["token_embd.weight"] = weights["output.weight"]  # same bytes: only one row per token is read
     if world > 1:
         weights = parallel.shard_model(cfg, weights, rank, world)
     prompt = synth.tokens(7, N_PROMPT, cfg.vocab_size)
@@ -192,10 +195,13 @@ def matvec_ring_roofline(backend, peaks, peak_kind, iters: int = 1000) -> dict:
     bytes_per_launch = matvec_bytes(dt, n_rows, n_cols)
     achieved = bytes_per_launch * iters / (ms * 1e-3) / 1e9
     peak = float(peaks["hbm_gbs"])
-    return {"bound": "hbm", "kernel": "qmv_q4k_kernel<1>", "workload": "Q4_K 5632x2048 matvec x1000 over an 80-copy ring (519 MB)",
+    return {"bound": "hbm", "kernel": "qmv_q4k_mma_kernel", "workload": "Q4_K 5632x2048 matvec x1000 over an 80-copy ring (519 MB)",
             "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
             "frac": round(achieved / peak, 4), "bytes_per_launch": bytes_per_launch,
-            "us_per_launch": round(ms * 1e3 / iters, 3), "traffic": None}
+            "us_per_launch": round(ms * 1e3 / iters, 3),
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch in the committed ncu capture
+            # (profiles/qmv_q4k_mma_5632x2048.md): nothing is re-read
+            "traffic": 6547456}
 
 
 def cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s: float, max_tokens: int):
@@ -272,13 +278,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         return float(t.item())
 
     backend = CudaB200Backend(local_rank)
-    tp = args.workload == "c4"
+    tp = args.workload in ("c3", "c4")
     if tp:
         if world > 1:
             ids = [CudaB200Backend.tp_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             backend.tp_init(rank, world, ids[0])
-        cfg, weights, prompt = build_model_70b(rank, world)
+        cfg, weights, prompt = build_model_70b(rank, world, args.workload)
     else:
         cfg, weights, prompt = build_model(rank)
     runner = CudaTransformerRunner(backend, cfg, weights, fused=True)
@@ -356,12 +362,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
             "warmup": max(args.warmup, 3), "ms_per_step": round((prefill_ms + decode_ms) / args.steps, 3),
             "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": ({"workload": "configs[4] Llama-3-70B-arch decode, all linears Q4_K (one layer's tensors "
-                                    f"repeated for the 80 layers), fp32 KV, batch 1, {N_PROMPT}-token prompt + {N_GEN} "
-                                    "greedy tokens per step",
+            "config": ({"workload": ("configs[4] Llama-3-70B-arch decode, all linears Q4_K" if args.workload == "c4" else
+                                     "configs[3] Llama-3-8B-arch, Q4_K linears, Q6_K output, prompt fed token by token") +
+                                    f" (one layer's tensors repeated for the {cfg.n_layers} layers), fp32 KV, batch 1, "
+                                    f"{N_PROMPT}-token prompt + {N_GEN} greedy tokens per step",
                         "parallelism": f"tp{world}: output rows of every linear sharded over {world} GPU(s), "
                                        "NCCL all-gather of activations",
-                        "l2": "weights read per token per GPU (39 GB / N) exceed the 126 MB L2; no flush needed"}
+                        "l2": "weights read per token per GPU (GBs) exceed the 126 MB L2; no flush needed"}
                        if tp else
                        {"workload": "configs[1] TinyLlama-1.1B-arch decode, Q4_K linears, Q6_K output+ffn_down, "
                                     f"fp32 KV, batch 1, {N_PROMPT}-token prompt + {N_GEN} greedy tokens per step",
@@ -392,20 +399,27 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["c1", "c4"], default="c1",
-                    help="c1: TinyLlama-arch decode, one replica per GPU (default).  c4: Llama-3-70B-arch decode, "
-                         "row-sharded tensor parallelism over the GPUs (512-token prompt + 256 tokens)")
+    ap.add_argument("--workload", choices=["c1", "c3", "c4"], default="c1",
+                    help="c1: TinyLlama-arch decode, one replica per GPU (default).  c3: Llama-3-8B-arch, 2048-token "
+                         "prompt fed token by token + 256 tokens.  c4: Llama-3-70B-arch decode (512-token prompt + "
+                         "256 tokens).  c3/c4 shard the output rows of every linear over the GPUs (tensor parallelism)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized run: 4-token prompt + 4 tokens, 20 ring launches, no CPU leg")
+    ap.add_argument("--prompt-tokens", type=int, default=0, help="diagnostic: override the workload's prompt length")
+    ap.add_argument("--gen-tokens", type=int, default=0, help="diagnostic: override the workload's generated tokens")
     args = ap.parse_args()
     global N_PROMPT, N_GEN
     if args.workload == "c4":
         N_PROMPT, N_GEN = 512, 256
-        args.no_cpu_baseline = True  # the CPU runner needs minutes per token at this size
+        args.no_cpu_baseline = True  # the CPU runner needs seconds per token at this size
+    if args.workload == "c3":
+        N_PROMPT, N_GEN = 2048, 256
+        args.no_cpu_baseline = True
     if args.small:
         N_PROMPT, N_GEN = 4, 4
         args.no_cpu_baseline = True
+    N_PROMPT, N_GEN = args.prompt_tokens or N_PROMPT, args.gen_tokens or N_GEN
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

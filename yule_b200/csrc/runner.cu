@@ -267,8 +267,9 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     // All-gather number `k` of layer `layer` (k = 4: the logits).  With the peer exchange each gather
     // has its own flag slot and an epoch derived from the token counter in d_state[2].
     const uint32_t epochs_per_token = 4 * c.n_layers + 1;
+    const bool skip_gather = getenv("YULE_CUDA_SKIP") && (strtoul(getenv("YULE_CUDA_SKIP"), nullptr, 0) & 512);
     auto gather = [&](float *buf, size_t x_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
-        if (N <= 1) return;
+        if (N <= 1 || skip_gather) return;
         if (r->xchg)
             st.ok(tp_exchange(r->ctx, x_off, per_rank, k, r->d_state + 2, epochs_per_token, k == 4 ? 4 * c.n_layers : 4 * layer + k,
                               pdl, &st.n));
