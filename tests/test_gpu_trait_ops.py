@@ -134,7 +134,11 @@ def test_attn_score_value_and_manual_pipeline(backend):  # cpu.rs:860-988
 
 
 @pytest.mark.parametrize("n_heads,n_kv,hd,seq", [(2, 1, 2, 2), (32, 4, 64, 1), (32, 4, 64, 160), (32, 8, 128, 777),
-                                                (8, 8, 96, 33)])
+                                                (8, 8, 96, 33),
+                                                # grouped-query kernel (from 512 positions): every group size, both
+                                                # head sizes, a length whose last split is empty (2049 over 64 splits)
+                                                (32, 4, 64, 2049), (64, 8, 128, 1500), (8, 8, 128, 600), (16, 8, 64, 513),
+                                                (16, 4, 128, 4100), (4, 4, 64, 512), (8, 2, 64, 999), (16, 8, 128, 640)])
 def test_multihead_attention_vs_oracle(backend, oracle, n_heads, n_kv, hd, seq):
     """GQA: head h reads kv head h / (n_heads / n_kv) (cpu.rs:1079-1156, gpu_runner.rs:477-499)."""
     kv_stride = n_kv * hd

@@ -552,7 +552,9 @@ int32_t yule_cuda_multihead_attention(yule_cuda_ctx *ctx, yule_buffer q, yule_bu
     if (attn_decode_supported(head_dim) && kv_stride % 4 == 0) {
         // split over positions; the partial results live in a context-owned scratch grown on demand
         AttnDecode a;
-        a.n_splits = attn_pick_splits(n_heads, seq_len, ctx->prop.multiProcessorCount);
+        a.gqa = attn_gqa_supported(head_dim, n_heads, n_kv_heads) && seq_len >= 512;
+        a.n_splits = a.gqa ? attn_gqa_pick_splits(n_kv_heads, seq_len, ctx->prop.multiProcessorCount)
+                           : attn_pick_splits(n_heads, seq_len, ctx->prop.multiProcessorCount);
         const size_t need = attn_scratch_floats(n_heads, a.n_splits, head_dim);
         {
             std::lock_guard<std::mutex> lock(ctx->mu);

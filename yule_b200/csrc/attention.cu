@@ -218,6 +218,338 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     if (threadIdx.x == 0) p.tickets[head] = 0;  // ready for the next launch on this stream
 }
 
+
+// ── grouped-query variant ───────────────────────────────────────────────────────────────────
+// Grid (n_kv_heads, n_splits): CTA (kv, s) serves all GROUP query heads that share KV head kv, so a
+// K or V row leaves HBM once per token instead of once per query head.  Scores: eight lanes per
+// position, each lane reading 16 contiguous bytes per step, so one load instruction of a warp covers
+// four rows in whole 128-byte lines.  Up to 64 splits keep every SM busy at long contexts; the last
+// CTA of a KV head (ticket) merges the splits of its GROUP heads.
+constexpr int kGqaMaxSplits = 64;
+
+template <int GROUP, int HD>
+__global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnParams p) {
+    constexpr int J = HD / 32;                               // 16-byte steps per lane and row
+    constexpr int GH = (GROUP * J > 16) ? (16 / J) : GROUP;  // query heads scored per pass over K
+    constexpr int HD4 = HD / 4;
+    constexpr int NSL = kThreads / HD4;                      // position slices of the V pass
+    constexpr int NOUT = (GROUP * HD + kThreads - 1) / kThreads;
+    extern __shared__ __align__(16) float sm[];
+    __shared__ uint32_t s_last;
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
+
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, head0 = kvh * GROUP;
+    const uint32_t pos = p.pos_ptr ? *p.pos_ptr : p.seq_len - 1;
+    const uint32_t seq = pos + 1;
+    const bool fused = p.k_new != nullptr;
+    uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
+    eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
+    if (split >= eff) return;
+    const uint32_t chunk = (seq + eff - 1) / eff;
+    const uint32_t lo = split * chunk < seq ? split * chunk : seq;
+    const uint32_t hi = lo + chunk < seq ? lo + chunk : seq;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+
+    float *qs = sm;                               // GROUP × HD rotated queries
+    float *kcur = qs + GROUP * HD;                // HD: rotated K row of the current token
+    float *ml = kcur + HD;                        // (max, sum) per head, 16 floats
+    float *scores = ml + 16;                      // GROUP × max_chunk
+    float *partial = scores + (size_t)GROUP * p.max_chunk;  // NSL × GROUP × HD
+    float *mrg = partial + (size_t)NSL * GROUP * HD;        // merge: 2 × GROUP × kGqaMaxSplits
+
+    // The first K tile does not depend on the query: its loads go out before the RoPE prologue.
+    const int qtr = lane >> 3, l8 = lane & 7;
+    auto k_row = [&](uint32_t tb) {
+        const uint32_t t = tb + wid * 4 + qtr;
+        return p.k_cache + (size_t)(t < hi ? t : lo) * p.kv_stride + (size_t)kvh * HD + l8 * 4;
+    };
+    float4 kv_next[J];
+    if (lo < hi) {
+        const float *kp = k_row(lo);
+#pragma unroll
+        for (int j = 0; j < J; j++) kv_next[j] = *reinterpret_cast<const float4 *>(kp + j * 32);
+    }
+
+    // RoPE as in apply_rope (model_runner.rs:277-293): products and sums rounded separately
+    for (uint32_t idx = threadIdx.x; idx < GROUP * (HD / 2); idx += kThreads) {
+        const uint32_t h = idx / (HD / 2), i = idx % (HD / 2);
+        float q0 = p.q[(size_t)(head0 + h) * HD + 2 * i], q1 = p.q[(size_t)(head0 + h) * HD + 2 * i + 1];
+        if (p.cos_table) {
+            const float c = p.cos_table[(size_t)pos * (HD / 2) + i], sn = p.sin_table[(size_t)pos * (HD / 2) + i];
+            const float r0 = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, sn));
+            const float r1 = __fadd_rn(__fmul_rn(q0, sn), __fmul_rn(q1, c));
+            q0 = r0;
+            q1 = r1;
+            if (fused && h == 0) {
+                const float k0 = p.k_new[(size_t)kvh * HD + 2 * i], k1 = p.k_new[(size_t)kvh * HD + 2 * i + 1];
+                kcur[2 * i] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, sn));
+                kcur[2 * i + 1] = __fadd_rn(__fmul_rn(k0, sn), __fmul_rn(k1, c));
+            }
+        } else if (fused && h == 0) {
+            kcur[2 * i] = p.k_new[(size_t)kvh * HD + 2 * i];
+            kcur[2 * i + 1] = p.k_new[(size_t)kvh * HD + 2 * i + 1];
+        }
+        qs[h * HD + 2 * i] = q0;
+        qs[h * HD + 2 * i + 1] = q1;
+    }
+    __syncthreads();
+
+    // the split that owns the current position appends the new K and V rows (readers of this launch
+    // take that row from kcur / v_new, never from the cache)
+    if (fused && pos >= lo && pos < hi) {
+        for (uint32_t d = threadIdx.x; d < HD; d += kThreads) {
+            p.k_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = kcur[d];
+            p.v_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = p.v_new[(size_t)kvh * HD + d];
+        }
+    }
+
+    // scores; the loads of tile i+1 are in flight while tile i is multiplied
+    const float scale = 1.0f / sqrtf((float)HD);
+#pragma unroll 1
+    for (int h0 = 0; h0 < GROUP; h0 += GH) {
+        float4 qr[GH][J];
+#pragma unroll
+        for (int h = 0; h < GH; h++)
+#pragma unroll
+            for (int j = 0; j < J; j++) qr[h][j] = *reinterpret_cast<const float4 *>(qs + (h0 + h) * HD + j * 32 + l8 * 4);
+        if (h0 > 0 && lo < hi) {
+            const float *kp = k_row(lo);
+#pragma unroll
+            for (int j = 0; j < J; j++) kv_next[j] = *reinterpret_cast<const float4 *>(kp + j * 32);
+        }
+        for (uint32_t tb = lo; tb < hi; tb += 32) {
+            const uint32_t t = tb + wid * 4 + qtr;
+            const bool valid = t < hi;
+            float4 kv[J];
+#pragma unroll
+            for (int j = 0; j < J; j++) kv[j] = kv_next[j];
+            if (tb + 32 < hi) {
+                const float *kp = k_row(tb + 32);
+#pragma unroll
+                for (int j = 0; j < J; j++) kv_next[j] = *reinterpret_cast<const float4 *>(kp + j * 32);
+            }
+            if (fused && t == pos) {
+#pragma unroll
+                for (int j = 0; j < J; j++) kv[j] = *reinterpret_cast<const float4 *>(kcur + j * 32 + l8 * 4);
+            }
+            float d[GH];
+#pragma unroll
+            for (int h = 0; h < GH; h++) {
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    a0 = fmaf(qr[h][j].x, kv[j].x, a0);
+                    a1 = fmaf(qr[h][j].y, kv[j].y, a1);
+                    a0 = fmaf(qr[h][j].z, kv[j].z, a0);
+                    a1 = fmaf(qr[h][j].w, kv[j].w, a1);
+                }
+                d[h] = a0 + a1;
+            }
+#pragma unroll
+            for (int h = 0; h < GH; h++) {
+                d[h] += __shfl_xor_sync(0xffffffffu, d[h], 4);
+                d[h] += __shfl_xor_sync(0xffffffffu, d[h], 2);
+                d[h] += __shfl_xor_sync(0xffffffffu, d[h], 1);
+            }
+            if (valid && l8 == 0) {
+#pragma unroll
+                for (int h = 0; h < GH; h++) scores[(size_t)(h0 + h) * p.max_chunk + (t - lo)] = d[h] * scale;
+            }
+        }
+    }
+    __syncthreads();
+
+    // softmax statistics: one warp per head
+    for (int h = wid; h < GROUP; h += kThreads / 32) {
+        float *sc = scores + (size_t)h * p.max_chunk;
+        float mx = -FLT_MAX;
+        for (uint32_t i = lane; i < hi - lo; i += 32) mx = fmaxf(mx, sc[i]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (uint32_t i = lane; i < hi - lo; i += 32) {
+            const float e = expf(sc[i] - mx);
+            sc[i] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            ml[2 * h] = mx;
+            ml[2 * h + 1] = sum;
+        }
+    }
+    __syncthreads();
+
+    // Σ_t e_t · V[t] for all GROUP heads from one read of V
+    const uint32_t d4 = threadIdx.x % HD4, slice = threadIdx.x / HD4;
+    float4 acc[GROUP];
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto v_row = [&](uint32_t t) {
+        return (fused && t == pos) ? reinterpret_cast<const float4 *>(p.v_new + (size_t)kvh * HD) + d4
+                                   : reinterpret_cast<const float4 *>(p.v_cache + (size_t)t * p.kv_stride + (size_t)kvh * HD) + d4;
+    };
+    uint32_t t = lo + slice;
+    for (; t + 3 * NSL < hi; t += 4 * NSL) {  // four rows in flight
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = *v_row(t + u * NSL);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int h = 0; h < GROUP; h++) {
+                const float e = scores[(size_t)h * p.max_chunk + (t + u * NSL - lo)];
+                acc[h].x = fmaf(e, v[u].x, acc[h].x);
+                acc[h].y = fmaf(e, v[u].y, acc[h].y);
+                acc[h].z = fmaf(e, v[u].z, acc[h].z);
+                acc[h].w = fmaf(e, v[u].w, acc[h].w);
+            }
+    }
+    for (; t < hi; t += NSL) {
+        const float4 v = *v_row(t);
+#pragma unroll
+        for (int h = 0; h < GROUP; h++) {
+            const float e = scores[(size_t)h * p.max_chunk + (t - lo)];
+            acc[h].x = fmaf(e, v.x, acc[h].x);
+            acc[h].y = fmaf(e, v.y, acc[h].y);
+            acc[h].z = fmaf(e, v.z, acc[h].z);
+            acc[h].w = fmaf(e, v.w, acc[h].w);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) reinterpret_cast<float4 *>(partial)[((size_t)slice * GROUP + h) * HD4 + d4] = acc[h];
+    __syncthreads();
+    float o[NOUT];
+#pragma unroll
+    for (int k = 0; k < NOUT; k++) {
+        const uint32_t idx = threadIdx.x + k * kThreads;  // (head, dimension)
+        o[k] = 0.f;
+        if (idx < GROUP * HD) {
+            const uint32_t h = idx / HD, dd = idx % HD;
+            for (uint32_t s2 = 0; s2 < NSL; s2++) o[k] += partial[((size_t)s2 * GROUP + h) * HD + dd];
+        }
+    }
+
+    if (eff == 1) {
+#pragma unroll
+        for (int k = 0; k < NOUT; k++) {
+            const uint32_t idx = threadIdx.x + k * kThreads;
+            if (idx < GROUP * HD) p.out[(size_t)head0 * HD + idx] = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
+        }
+        return;
+    }
+
+    // publish (m, l, acc) per head, take a ticket; the last CTA of this KV head merges.
+    // Scratch: accumulators [head][split][HD], then the (m, l) pairs [head][split][2].
+    float *stats = p.scratch + (size_t)p.n_heads * p.n_splits * HD;
+#pragma unroll
+    for (int k = 0; k < NOUT; k++) {
+        const uint32_t idx = threadIdx.x + k * kThreads;
+        if (idx < GROUP * HD) {
+            const uint32_t h = idx / HD, dd = idx % HD;
+            p.scratch[((size_t)(head0 + h) * p.n_splits + split) * HD + dd] = o[k];
+        }
+    }
+    if (threadIdx.x < GROUP) {
+        float *mine = stats + ((size_t)(head0 + threadIdx.x) * p.n_splits + split) * 2;
+        mine[0] = lo < hi ? ml[2 * threadIdx.x] : -FLT_MAX;
+        mine[1] = lo < hi ? ml[2 * threadIdx.x + 1] : 0.f;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&p.tickets[kvh], 1u) == eff - 1) ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // (m, l) of every (head, split): one load per thread, then the weights exp(m - M) in shared memory
+    float *mm = mrg, *ww = mrg + GROUP * kGqaMaxSplits;
+    for (uint32_t i = threadIdx.x; i < GROUP * eff; i += kThreads) {
+        const uint32_t h = i / eff, s2 = i % eff;
+        const float2 st = __ldcg(reinterpret_cast<const float2 *>(stats + ((size_t)(head0 + h) * p.n_splits + s2) * 2));
+        mm[h * kGqaMaxSplits + s2] = st.x;
+        ww[h * kGqaMaxSplits + s2] = st.y;
+    }
+    __syncthreads();
+    if (threadIdx.x < GROUP) {
+        const uint32_t h = threadIdx.x;
+        float M = -FLT_MAX;
+        for (uint32_t s2 = 0; s2 < eff; s2++) M = fmaxf(M, mm[h * kGqaMaxSplits + s2]);
+        float L = 0.f;
+        for (uint32_t s2 = 0; s2 < eff; s2++) {
+            const float l = ww[h * kGqaMaxSplits + s2];
+            const float w = l > 0.f ? expf(mm[h * kGqaMaxSplits + s2] - M) : 0.f;  // empty split: no weight
+            L = fmaf(l, w, L);
+            ww[h * kGqaMaxSplits + s2] = w;
+        }
+        ml[2 * h + 1] = L;
+    }
+    __syncthreads();
+    // Weighted sum of the splits' accumulators: thread (slice, head, d4) takes splits slice,
+    // slice + MS, … as 16-byte loads, sixteen in flight; the slices meet in shared memory.
+    constexpr int NV = GROUP * HD4;                         // float4 outputs of this KV head
+    constexpr int MS = NV >= kThreads ? 1 : kThreads / NV;  // split slices
+    constexpr int NVT = (NV + kThreads - 1) / kThreads;     // outputs per thread when MS == 1
+    float4 *red4 = reinterpret_cast<float4 *>(partial);     // MS × NV float4 (fits: MS·NV ≤ max(NV, 256))
+#pragma unroll
+    for (int k = 0; k < NVT; k++) {
+        const uint32_t vi = (threadIdx.x % (MS > 1 ? NV : kThreads)) + k * kThreads;
+        const uint32_t msl = MS > 1 ? threadIdx.x / NV : 0;
+        if (vi < (uint32_t)NV) {
+            const uint32_t h = vi / HD4, c4 = vi % HD4;
+            const float4 *src = reinterpret_cast<const float4 *>(p.scratch + (size_t)(head0 + h) * p.n_splits * HD) + c4;
+            const float *wh = ww + h * kGqaMaxSplits;
+            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+            uint32_t s2 = msl;
+            for (; s2 + 15 * MS < eff; s2 += 16 * MS) {
+                float4 v[16];
+#pragma unroll
+                for (int u = 0; u < 16; u++) v[u] = __ldcg(src + (size_t)(s2 + u * MS) * HD4);
+#pragma unroll
+                for (int u = 0; u < 16; u++) {
+                    const float w = wh[s2 + u * MS];
+                    O.x = fmaf(v[u].x, w, O.x);
+                    O.y = fmaf(v[u].y, w, O.y);
+                    O.z = fmaf(v[u].z, w, O.z);
+                    O.w = fmaf(v[u].w, w, O.w);
+                }
+            }
+            for (; s2 < eff; s2 += MS) {
+                const float4 v = __ldcg(src + (size_t)s2 * HD4);
+                const float w = wh[s2];
+                O.x = fmaf(v.x, w, O.x);
+                O.y = fmaf(v.y, w, O.y);
+                O.z = fmaf(v.z, w, O.z);
+                O.w = fmaf(v.w, w, O.w);
+            }
+            red4[(size_t)msl * NV + vi] = O;
+        }
+    }
+    __syncthreads();
+    for (uint32_t vi = threadIdx.x; vi < (uint32_t)NV; vi += kThreads) {
+        float4 O = red4[vi];
+        for (int m2 = 1; m2 < MS; m2++) {
+            const float4 v = red4[(size_t)m2 * NV + vi];
+            O.x += v.x;
+            O.y += v.y;
+            O.z += v.z;
+            O.w += v.w;
+        }
+        const float inv = 1.0f / ml[2 * (vi / HD4) + 1];
+        reinterpret_cast<float4 *>(p.out + (size_t)head0 * HD)[vi] = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+    }
+    if (threadIdx.x == 0) p.tickets[kvh] = 0;  // ready for the next launch on this stream
+}
+
+template <int GROUP, int HD>
+cudaError_t launch_gqa_variant(const AttnParams &p, size_t smem, bool pdl, cudaStream_t s) {
+    auto kern = attn_decode_gqa_kernel<GROUP, HD>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_kernel(kern, dim3(p.n_kv_heads, p.n_splits), dim3(kThreads), smem, s, pdl, p);
+}
+
 }  // namespace
 
 size_t attn_scratch_floats(uint32_t n_heads, uint32_t n_splits, uint32_t hd) {
@@ -230,6 +562,21 @@ uint32_t attn_pick_splits(uint32_t n_heads, uint32_t seq_len_hint, int sm_count)
     const uint32_t by_len = (seq_len_hint + kThreads - 1) / kThreads;  // at least 256 positions per split
     if (by_len < s) s = by_len < 1 ? 1 : by_len;
     return s;
+}
+
+bool attn_gqa_supported(uint32_t hd, uint32_t n_heads, uint32_t n_kv_heads) {
+    if (!n_kv_heads || n_heads % n_kv_heads) return false;
+    const uint32_t g = n_heads / n_kv_heads;
+    return (hd == 64 || hd == 128) && (g == 1 || g == 2 || g == 4 || g == 8);
+}
+
+// Splits for the grouped-query kernel: one wave of CTAs, at least 32 positions each at the longest
+// context, at most 64.
+uint32_t attn_gqa_pick_splits(uint32_t n_kv_heads, uint32_t max_seq_len, int sm_count) {
+    uint32_t s = (2u * (uint32_t)sm_count) / (n_kv_heads ? n_kv_heads : 1);  // one wave at two CTAs per SM
+    const uint32_t by_len = (max_seq_len + 31) / 32;
+    if (by_len < s) s = by_len;
+    return s < 1 ? 1 : (s > (uint32_t)kGqaMaxSplits ? (uint32_t)kGqaMaxSplits : s);
 }
 
 bool attn_decode_supported(uint32_t hd) { return hd % 4 == 0 && hd >= 4 && hd <= 256 && kThreads % (hd / 4) == 0; }
@@ -253,6 +600,24 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
     p.n_kv_heads = a.n_kv_heads;
     p.kv_stride = a.kv_stride;
     p.n_splits = a.n_splits;
+    if (a.gqa) {
+        if (!attn_gqa_supported(a.hd, a.n_heads, a.n_kv_heads) || a.n_splits > (uint32_t)kGqaMaxSplits) return cudaErrorInvalidValue;
+        const uint32_t g = a.n_heads / a.n_kv_heads;
+        uint32_t mc = (a.max_seq_len + a.n_splits - 1) / a.n_splits;
+        p.min_chunk = a.min_chunk ? a.min_chunk : 32;
+        if (mc < p.min_chunk) mc = p.min_chunk;
+        p.max_chunk = ((mc + 3) / 4) * 4;
+        const uint32_t nsl = kThreads / (a.hd / 4);
+        const size_t smem = ((size_t)g * a.hd + a.hd + 16 + (size_t)g * p.max_chunk + (size_t)nsl * g * a.hd +
+                             2 * (size_t)g * kGqaMaxSplits) * sizeof(float);
+        if (smem > 200 * 1024) return cudaErrorInvalidValue;
+        *launches += 1;
+#define YULE_GQA_CASE(G, H) if (g == G && a.hd == H) return launch_gqa_variant<G, H>(p, smem, a.pdl, s)
+        YULE_GQA_CASE(1, 64); YULE_GQA_CASE(2, 64); YULE_GQA_CASE(4, 64); YULE_GQA_CASE(8, 64);
+        YULE_GQA_CASE(1, 128); YULE_GQA_CASE(2, 128); YULE_GQA_CASE(4, 128); YULE_GQA_CASE(8, 128);
+#undef YULE_GQA_CASE
+        return cudaErrorInvalidValue;
+    }
     // A split holds at most max(256, ceil(max_seq / n_splits)) scores (fewer, larger splits are only
     // used while they stay at 256 positions or less).  A multiple of 4 keeps the float4 area behind
     // the scores 16-byte aligned.

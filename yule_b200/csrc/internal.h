@@ -265,7 +265,10 @@ struct AttnDecode {
     uint32_t hd = 0, n_heads = 0, n_kv_heads = 0, kv_stride = 0, n_splits = 1, max_seq_len = 0;
     uint32_t min_chunk = 0;  // fewest positions a split is worth (0: one per thread of the CTA)
     bool pdl = false;
+    bool gqa = false;        // grouped-query kernel: one CTA per (KV head, split); n_splits from attn_gqa_pick_splits
 };
+bool attn_gqa_supported(uint32_t hd, uint32_t n_heads, uint32_t n_kv_heads);
+uint32_t attn_gqa_pick_splits(uint32_t n_kv_heads, uint32_t max_seq_len, int sm_count);
 size_t attn_scratch_floats(uint32_t n_heads, uint32_t n_splits, uint32_t hd);
 uint32_t attn_pick_splits(uint32_t n_heads, uint32_t seq_len_hint, int sm_count);
 bool attn_decode_supported(uint32_t hd);

@@ -54,6 +54,7 @@ struct yule_cuda_runner {
     float *attn_scratch = nullptr;  // partial results of the split-KV attention
     uint32_t *attn_tickets = nullptr;
     uint32_t attn_splits = 1;
+    bool attn_gqa = false;
     // tensor parallelism with the peer-memory exchange: offsets (floats) of the gathered buffers inside
     // the exchange region
     bool xchg = false;
@@ -351,6 +352,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             a.n_kv_heads = kvh_l;
             a.kv_stride = kvdim_l;
             a.n_splits = r->attn_splits;
+            a.gqa = r->attn_gqa;
             a.max_seq_len = c.max_seq_len;
             a.min_chunk = getenv("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_ATTN_MIN_CHUNK")) : 32;
             a.pdl = pdl;
@@ -606,7 +608,10 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     A((size_t)c.max_seq_len * half, &r->rope_cos);
     A((size_t)c.max_seq_len * half, &r->rope_sin);
     float *tmp = nullptr;
-    r->attn_splits = attn_pick_splits(c.n_heads, c.max_seq_len, ctx->prop.multiProcessorCount);
+    r->attn_gqa = attn_gqa_supported(hd, c.n_heads, c.n_kv_heads) && !(getenv("YULE_CUDA_ATTN_GQA") && atoi(getenv("YULE_CUDA_ATTN_GQA")) == 0);
+    r->attn_splits = r->attn_gqa ? attn_gqa_pick_splits(c.n_kv_heads / (ctx->tp_world > 1 ? ctx->tp_world : 1), c.max_seq_len,
+                                                        ctx->prop.multiProcessorCount)
+                                 : attn_pick_splits(c.n_heads, c.max_seq_len, ctx->prop.multiProcessorCount);
     A(attn_scratch_floats(c.n_heads, r->attn_splits, hd) + 4, &r->attn_scratch);
     A(c.n_heads, &tmp);
     r->attn_tickets = (uint32_t *)tmp;  // zero-filled by the allocator
