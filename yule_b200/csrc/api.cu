@@ -27,6 +27,26 @@ int32_t fail_cuda(cudaError_t e, const char *what) {
     return fail(code, "cuda: %s failed: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
+// Grows the context's GEMM scratch.  Not while a graph is being captured: allocation is not a
+// stream operation, so the caller must have run one call of this size before capturing.
+int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (ctx->gemm_scratch_bytes >= bytes) return YULE_OK;
+    if (ctx->capturing)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "the GEMM scratch (%zu bytes) cannot grow during graph capture", bytes);
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    ctx->gemm_scratch = nullptr;
+    ctx->gemm_scratch_bytes = 0;
+    cudaError_t e = cudaMalloc(&ctx->gemm_scratch, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(YULE_ERR_OUT_OF_MEMORY, "cuda allocation of %zu bytes of GEMM scratch failed", bytes);
+    }
+    ctx->gemm_scratch_bytes = bytes;
+    return YULE_OK;
+}
+
 }  // namespace yule
 
 using namespace yule;
@@ -126,6 +146,7 @@ int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
     if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
     if (ctx->attn_tickets) cudaFree(ctx->attn_tickets);
     if (ctx->device_status) cudaFree(ctx->device_status);
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return YULE_OK;
@@ -414,6 +435,8 @@ int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffe
     return YULE_OK;
 }
 
+constexpr uint32_t kGemmMinBatch = 8;
+
 static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset, yule_buffer input,
                           yule_buffer output, uint32_t n_rows, uint32_t n_cols, uint32_t type, uint32_t batch,
                           uint32_t x_stride, uint32_t out_stride) {
@@ -452,6 +475,25 @@ static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight
     if (type == YULE_DTYPE_Q6_K && W.planar && weight_offset == 0 &&
         W.planar_blocks == (uint64_t)n_rows * (n_cols / 256))
         a.planar = W.planar;
+    if (batch >= kGemmMinBatch && qgemm_supported(type, n_cols, batch)) {
+        // eight or more activation rows: one pass over the weights on the tcgen05 GEMM
+        int32_t rc = ensure_gemm_scratch(ctx, qgemm_scratch_bytes(batch, n_cols));
+        if (rc) return rc;
+        QGemm g;
+        g.w = a.w;
+        g.type = type;
+        g.x = a.x;
+        g.out = a.out;
+        g.n_rows = n_rows;
+        g.n_cols = n_cols;
+        g.n_tokens = batch;
+        g.x_stride = x_stride;
+        g.out_stride = out_stride;
+        g.scratch = ctx->gemm_scratch;
+        g.status = ctx->device_status;
+        LAUNCHED(ctx, launch_qgemm(g, ctx->prop.multiProcessorCount, ctx->stream, &_n));
+        return YULE_OK;
+    }
     LAUNCHED(ctx, launch_qmv(a, ctx->prop.multiProcessorCount, ctx->stream, &_n));
     return YULE_OK;
 }

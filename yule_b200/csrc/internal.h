@@ -92,6 +92,9 @@ struct yule_cuda_ctx {
     size_t attn_scratch_floats = 0;
     uint32_t *attn_tickets = nullptr;
     size_t attn_tickets_n = 0;
+    // activation tiles of the tensor-core GEMM (qgemm_tc.cu), grown on demand
+    void *gemm_scratch = nullptr;
+    size_t gemm_scratch_bytes = 0;
     std::atomic<uint64_t> launches{0};
     // Word the kernels with bounded waits write when they give up; read by synchronize.
     int *device_status = nullptr;
@@ -146,6 +149,27 @@ struct QmvArgs {
     uint64_t next_bytes[2] = {0, 0};
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
+
+// Quantised GEMM on tcgen05 for eight or more activation rows (qgemm_tc.cu): an activation
+// re-layout kernel followed by the persistent GEMM.  `scratch` holds qgemm_scratch_bytes().
+struct QGemm {
+    const uint8_t *w = nullptr;  // Q4_K blocks, row-major
+    uint32_t type = 0;
+    const float *x = nullptr;    // [n_tokens][x_stride]
+    const float *gate = nullptr;    // prologue: x ← silu(gate) · x (same layout as x), or null
+    const float *norm_w = nullptr;  // prologue: RMSNorm with these weights, or null
+    float eps = 0.f;
+    float *out = nullptr;           // [n_tokens][out_stride]
+    const float *residual = nullptr;  // added to out (same layout), or null
+    uint32_t n_rows = 0, n_cols = 0, n_tokens = 0, x_stride = 0, out_stride = 0;
+    void *scratch = nullptr;
+    int *status = nullptr;  // the context's device status word
+    bool pdl = false;
+};
+int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes);
+bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens);
+size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols);
+cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches);
 
 // Q4_K tensor-pipe matvec with the neighbouring ops folded in (qmv_q4k_mma.cu).
 struct Q4kFused {
