@@ -50,6 +50,7 @@ struct AttnParams {
     float *scratch;                      // [n_heads][n_splits][hd + 2] partial (m, l, acc)
     uint32_t *tickets;                   // [n_heads], zero between launches
     uint32_t hd, n_heads, n_kv_heads, kv_stride, n_splits, max_chunk, min_chunk;
+    uint32_t q_stride, out_stride;       // floats between the q / out rows of consecutive queries (blockIdx.z)
 };
 
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
@@ -240,7 +241,13 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
     yule_pdl_wait();
 
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, head0 = kvh * GROUP;
-    const uint32_t pos = p.pos_ptr ? *p.pos_ptr : p.seq_len - 1;
+    // prefill: query z of the launch sits z positions further on and has its own rows and scratch
+    const uint32_t z = blockIdx.z;
+    const uint32_t pos = p.pos_ptr ? *p.pos_ptr : p.seq_len - 1 + z;
+    const float *q_in = p.q + (size_t)z * p.q_stride;
+    float *out_z = p.out + (size_t)z * p.out_stride;
+    float *scratch_z = p.scratch + (size_t)z * p.n_heads * p.n_splits * (HD + 2);
+    uint32_t *tickets_z = p.tickets + (size_t)z * p.n_heads;
     const uint32_t seq = pos + 1;
     const bool fused = p.k_new != nullptr;
     uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
@@ -274,7 +281,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
     // RoPE as in apply_rope (model_runner.rs:277-293): products and sums rounded separately
     for (uint32_t idx = threadIdx.x; idx < GROUP * (HD / 2); idx += kThreads) {
         const uint32_t h = idx / (HD / 2), i = idx % (HD / 2);
-        float q0 = p.q[(size_t)(head0 + h) * HD + 2 * i], q1 = p.q[(size_t)(head0 + h) * HD + 2 * i + 1];
+        float q0 = q_in[(size_t)(head0 + h) * HD + 2 * i], q1 = q_in[(size_t)(head0 + h) * HD + 2 * i + 1];
         if (p.cos_table) {
             const float c = p.cos_table[(size_t)pos * (HD / 2) + i], sn = p.sin_table[(size_t)pos * (HD / 2) + i];
             const float r0 = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, sn));
@@ -434,20 +441,20 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
 #pragma unroll
         for (int k = 0; k < NOUT; k++) {
             const uint32_t idx = threadIdx.x + k * kThreads;
-            if (idx < GROUP * HD) p.out[(size_t)head0 * HD + idx] = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
+            if (idx < GROUP * HD) out_z[(size_t)head0 * HD + idx] = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
         }
         return;
     }
 
     // publish (m, l, acc) per head, take a ticket; the last CTA of this KV head merges.
     // Scratch: accumulators [head][split][HD], then the (m, l) pairs [head][split][2].
-    float *stats = p.scratch + (size_t)p.n_heads * p.n_splits * HD;
+    float *stats = scratch_z + (size_t)p.n_heads * p.n_splits * HD;
 #pragma unroll
     for (int k = 0; k < NOUT; k++) {
         const uint32_t idx = threadIdx.x + k * kThreads;
         if (idx < GROUP * HD) {
             const uint32_t h = idx / HD, dd = idx % HD;
-            p.scratch[((size_t)(head0 + h) * p.n_splits + split) * HD + dd] = o[k];
+            scratch_z[((size_t)(head0 + h) * p.n_splits + split) * HD + dd] = o[k];
         }
     }
     if (threadIdx.x < GROUP) {
@@ -457,7 +464,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
     }
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(&p.tickets[kvh], 1u) == eff - 1) ? 1u : 0u;
+    if (threadIdx.x == 0) s_last = (atomicAdd(&tickets_z[kvh], 1u) == eff - 1) ? 1u : 0u;
     __syncthreads();
     if (!s_last) return;
     __threadfence();
@@ -496,7 +503,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
         const uint32_t msl = MS > 1 ? threadIdx.x / NV : 0;
         if (vi < (uint32_t)NV) {
             const uint32_t h = vi / HD4, c4 = vi % HD4;
-            const float4 *src = reinterpret_cast<const float4 *>(p.scratch + (size_t)(head0 + h) * p.n_splits * HD) + c4;
+            const float4 *src = reinterpret_cast<const float4 *>(scratch_z + (size_t)(head0 + h) * p.n_splits * HD) + c4;
             const float *wh = ww + h * kGqaMaxSplits;
             float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
             uint32_t s2 = msl;
@@ -535,19 +542,19 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
             O.w += v.w;
         }
         const float inv = 1.0f / ml[2 * (vi / HD4) + 1];
-        reinterpret_cast<float4 *>(p.out + (size_t)head0 * HD)[vi] = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+        reinterpret_cast<float4 *>(out_z + (size_t)head0 * HD)[vi] = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
     }
-    if (threadIdx.x == 0) p.tickets[kvh] = 0;  // ready for the next launch on this stream
+    if (threadIdx.x == 0) tickets_z[kvh] = 0;  // ready for the next launch on this stream
 }
 
 template <int GROUP, int HD>
-cudaError_t launch_gqa_variant(const AttnParams &p, size_t smem, bool pdl, cudaStream_t s) {
+cudaError_t launch_gqa_variant(const AttnParams &p, size_t smem, bool pdl, cudaStream_t s, uint32_t n_tokens = 1) {
     auto kern = attn_decode_gqa_kernel<GROUP, HD>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_kernel(kern, dim3(p.n_kv_heads, p.n_splits), dim3(kThreads), smem, s, pdl, p);
+    return launch_kernel(kern, dim3(p.n_kv_heads, p.n_splits, n_tokens), dim3(kThreads), smem, s, pdl, p);
 }
 
 }  // namespace
@@ -612,7 +619,10 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
                              2 * (size_t)g * kGqaMaxSplits) * sizeof(float);
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         *launches += 1;
-#define YULE_GQA_CASE(G, H) if (g == G && a.hd == H) return launch_gqa_variant<G, H>(p, smem, a.pdl, s)
+        p.q_stride = a.q_stride;
+        p.out_stride = a.out_stride;
+        if (a.n_tokens > 1 && (a.k_new || a.pos_ptr)) return cudaErrorInvalidValue;  // batched queries read the caches only
+#define YULE_GQA_CASE(G, H) if (g == G && a.hd == H) return launch_gqa_variant<G, H>(p, smem, a.pdl, s, a.n_tokens)
         YULE_GQA_CASE(1, 64); YULE_GQA_CASE(2, 64); YULE_GQA_CASE(4, 64); YULE_GQA_CASE(8, 64);
         YULE_GQA_CASE(1, 128); YULE_GQA_CASE(2, 128); YULE_GQA_CASE(4, 128); YULE_GQA_CASE(8, 128);
 #undef YULE_GQA_CASE

@@ -144,6 +144,40 @@ __global__ void rope_kv_write_kernel(float *__restrict__ q, const float *__restr
     }
 }
 
+// Batched form for prefill: token slot z = blockIdx.y sits at position pos0 + z; q[z] is rotated in
+// place, k[z] is rotated into the K cache row of its position and v[z] copied into the V cache.
+__global__ void rope_kv_write_batch_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                           float *__restrict__ k_cache, float *__restrict__ v_cache,
+                                           const float *__restrict__ cos_table, const float *__restrict__ sin_table,
+                                           uint32_t pos0, uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads) {
+    const uint32_t z = blockIdx.y, pos = pos0 + z;
+    const uint32_t half = head_dim / 2;
+    const uint32_t kv_stride = n_kv_heads * head_dim, q_stride = n_heads * head_dim;
+    const uint32_t total_q = n_heads * half, total_k = n_kv_heads * half;
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total_q + total_k) return;
+    const bool is_q = idx < total_q;
+    const uint32_t r = is_q ? idx : idx - total_q;
+    const uint32_t pair = r % half, head = r / half;
+    const float c = cos_table[(size_t)pos * half + pair], sn = sin_table[(size_t)pos * half + pair];
+    const size_t off = (size_t)head * head_dim + 2 * pair;
+    const float *src = is_q ? q + (size_t)z * q_stride + off : k + (size_t)z * kv_stride + off;
+    const float x0 = src[0], x1 = src[1];
+    const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+    const float y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+    if (is_q) {
+        q[(size_t)z * q_stride + off] = y0;
+        q[(size_t)z * q_stride + off + 1] = y1;
+    } else {
+        float *kd = k_cache + (size_t)pos * kv_stride + off;
+        kd[0] = y0;
+        kd[1] = y1;
+        float *vd = v_cache + (size_t)pos * kv_stride + off;
+        vd[0] = v[(size_t)z * kv_stride + off];
+        vd[1] = v[(size_t)z * kv_stride + off + 1];
+    }
+}
+
 // kernels/cuda/silu_mul.cu:3-14.
 __global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,
                                 uint32_t n) {
@@ -349,6 +383,16 @@ cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tm
     *launches += 1;
     return launch_kernel(rope_kv_write_kernel, dim3((total + 255) / 256), dim3(256), 0, s, pdl, q, k_tmp, v_tmp, k_cache,
                          v_cache, cos_table, sin_table, pos_ptr, head_dim, n_heads, n_kv_heads);
+}
+cudaError_t launch_rope_kv_write_batch(float *q, const float *k, const float *v, float *k_cache, float *v_cache,
+                                       const float *cos_table, const float *sin_table, uint32_t pos0, uint32_t n_tokens,
+                                       uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads, cudaStream_t s,
+                                       uint64_t *launches) {
+    uint32_t total = (n_heads + n_kv_heads) * (head_dim / 2);
+    *launches += 1;
+    rope_kv_write_batch_kernel<<<dim3((total + 255) / 256, n_tokens), 256, 0, s>>>(q, k, v, k_cache, v_cache, cos_table, sin_table,
+                                                                                  pos0, head_dim, n_heads, n_kv_heads);
+    return cudaGetLastError();
 }
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t s,
                             uint64_t *launches, bool pdl) {

@@ -170,6 +170,10 @@ int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes);
 bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens);
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols);
 cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches);
+// The two halves of launch_qgemm, for matrices that share their activations (Q/K/V, gate/up):
+// one re-layout, then one GEMM per matrix with the same n_tokens, n_cols and scratch.
+cudaError_t launch_qgemm_xprep(const QGemm &g, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches);
 
 // Q4_K tensor-pipe matvec with the neighbouring ops folded in (qmv_q4k_mma.cu).
 struct Q4kFused {
@@ -245,6 +249,13 @@ cudaError_t launch_embed_gather(const uint8_t *table, uint32_t type, uint32_t di
                                 const uint32_t *token_ptr, float *out, cudaStream_t s,
                                 uint64_t *launches, bool pdl = false);
 
+cudaError_t launch_embed_gather_batch(const uint8_t *table, uint32_t type, uint32_t dim, const uint32_t *tokens,
+                                      uint32_t n_tokens, float *out, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_rope_kv_write_batch(float *q, const float *k, const float *v, float *k_cache, float *v_cache,
+                                       const float *cos_table, const float *sin_table, uint32_t pos0, uint32_t n_tokens,
+                                       uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads, cudaStream_t s,
+                                       uint64_t *launches);
+
 cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k,
                               cudaStream_t s, uint64_t *launches);
 cudaError_t launch_softmax(const float *in, float *out, uint32_t n, cudaStream_t s, uint64_t *launches);
@@ -289,6 +300,9 @@ struct AttnDecode {
     uint32_t hd = 0, n_heads = 0, n_kv_heads = 0, kv_stride = 0, n_splits = 1, max_seq_len = 0;
     uint32_t min_chunk = 0;  // fewest positions a split is worth (0: one per thread of the CTA)
     bool pdl = false;
+    // Prefill: n_tokens > 1 runs one query per blockIdx.z; query z sits at position seq_len - 1 + z,
+    // its q and out rows are q_stride / out_stride floats apart (grouped-query kernel, not fused).
+    uint32_t n_tokens = 1, q_stride = 0, out_stride = 0;
     bool gqa = false;        // grouped-query kernel: one CTA per (KV head, split); n_splits from attn_gqa_pick_splits
 };
 bool attn_gqa_supported(uint32_t hd, uint32_t n_heads, uint32_t n_kv_heads);

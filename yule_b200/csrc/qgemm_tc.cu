@@ -7,32 +7,42 @@
 // prefill as one matvec chain per token (yule-infer/src/gpu_runner.rs:146-160); the arithmetic
 // contract is the same fp32 dot product.
 //
-// Precision.  tcgen05 has no fp32 operand type, so both operands are split into two fp16 terms,
-// v = hi + lo with hi = fp16(v) and lo = fp16(v − hi) (22 significant bits), and three products
-// are accumulated in fp32: W_hi·x_hi + W_hi·x_lo + W_lo·x_hi (the lo·lo term is below 2⁻²² of the
-// result).  Weights are scaled by 2¹⁰ and every activation row by a power of two that puts its
-// largest element in [2¹³, 2¹⁴), so that the lo terms stay in fp16's normal range; the epilogue
-// multiplies the exact inverse back in.
+// Operands.  A Q4_K weight is d·sc·q − dmin·m with a 4-bit q, 6-bit sc and m per 32 columns and
+// fp16 d, dmin per 256.  The tensor core multiplies the exact integers: the W operand of a stage is
+// sc·q (≤ 945, exact in fp16), the 64-column partial sums are drained from TMEM after every stage
+// and multiplied by that row's d in fp32 on the way into register accumulators.  The min term is one
+// more MMA per super-block, (m of the 8 sub-blocks) × (per-sub-block sums of x), drained with −dmin.
+// Activations are fp32, which tcgen05 cannot take: each row is scaled by a power of two that puts
+// its largest element in [2¹³, 2¹⁴) and split into fp16 hi + lo (22 significant bits); two MMAs per
+// 16 columns, W·x_hi and W·x_lo.  The tensor core adds into its fp32 accumulator with truncation, a
+// bias that grows with the chain length; draining after every stage keeps a chain at 8 MMAs and
+// leaves the long sum to ordinary round-to-nearest fp32.  The result matches the fp32 matvec to
+// fp32 rounding.
 //
-// The tensor core adds into its fp32 accumulator with truncation, a bias that grows with the length
-// of the accumulation chain.  So a TMEM accumulator only ever holds one 64-column stage (12 MMAs);
-// the epilogue warps drain it after every stage and keep the running sums in registers, added with
-// ordinary round-to-nearest fp32.
-//
-// One CTA per SM, 18 warps, persistent over (row tile, activation tile) pairs:
+// One CTA per SM, 19 warps, persistent over (row tile, activation tile) pairs:
 //   warps 0-7   drain warps: tcgen05.ld of their 32 TMEM lanes × half of the columns after every
-//               stage, running sums in registers; at the end of a tile scale, residual, store
+//               stage, FMA by d (and −dmin) into registers; at the end of a tile scale, residual, store
 //   warp  8     one thread: bulk copies (TMA engine) of the pre-arranged activation tiles
 //   warp  9     one thread: tcgen05.mma issue; the warp also owns the TMEM allocation
-//   warps 10-17 dequantise Q4_K → fp16 hi/lo straight into the shared-memory operand layout,
-//               with the blocks of the next two super-blocks already on their way from HBM
-// A stage is a 128-row × 64-column slab of W (hi and lo, 32 KB) plus the matching slab of x.
+//   warp  10    one thread: tiled TMA loads (cp.async.bulk.tensor.2d) of the raw Q4_K bytes, one
+//               128-row × 144-byte box per super-block, four boxes in flight; rows past the end of
+//               the matrix arrive as zeros
+//   warps 11-18 unpack Q4_K from that shared-memory copy → fp16 sc·q in the operand layout (about
+//               1.4 instructions per weight)
+// A stage is a 128-row × 64-column slab of W (16 KB) plus the matching hi and lo slabs of x; the last
+// stage of a super-block also carries the 4 KB m slab and the sub-block sums of x.
 // Operands use the no-swizzle K-major core-matrix layout: 8 rows × 16 bytes per core matrix,
-// core matrices of one 8-column step contiguous along the rows.
+// core matrices of one 8-column step contiguous along the rows.  Inside a core-matrix row the eight
+// columns sit in the order 0,2,1,3,4,6,5,7 (the order in which nibble pairs fall out of a 32-bit
+// word); both operands use it, so the products pair up correctly.
 //
 // Every wait is bounded: a pipeline that stops making progress sets the context's status word,
 // raises the CTA's abort flag, lets all roles fall through to the common exit and frees its TMEM.
 
+#include <cstdio>
+#include <cstdlib>
+
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -43,23 +53,31 @@ namespace {
 constexpr int kBM = 128;  // rows of W per tile = TMEM lanes
 constexpr int kBK = 64;   // columns per stage (a quarter of a super-block)
 constexpr int kEpiWarps = 8, kProdWarps = 8;
-constexpr int kLoaderWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kFirstProdWarp = kEpiWarps + 2;
-constexpr int kGemmThreads = (kEpiWarps + 2 + kProdWarps) * 32;  // 576
+constexpr int kLoaderWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kRawWarp = kEpiWarps + 2, kFirstProdWarp = kEpiWarps + 3;
+constexpr int kGemmThreads = (kEpiWarps + 3 + kProdWarps) * 32;  // 608
 constexpr int kMaxStages = 6;
-constexpr uint32_t kAHalfBytes = kBM * kBK * 2;  // one fp16 term of the W slab: 16 KB
-constexpr float kWScale = 1024.f;
+constexpr int kRawSlots = 4;                       // super-blocks of raw Q4_K bytes in flight per CTA
+constexpr uint32_t kRawBytes = kBM * 144;          // one super-block of 128 rows: 18 KB
+constexpr uint32_t kABytes = kBM * kBK * 2;  // the W slab of a stage: 16 KB
+constexpr float kSumScale = 1.0f / 32.0f;     // the sub-block sums of x are stored divided by 32
+constexpr uint32_t kAmBytes = kBM * 16 * 2;  // the m slab of a super-block: 128 rows × 16 columns, 4 KB
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any real stall
 constexpr int kStatusGemmTimeout = 3;
+
+// Cycle counters of CTA 0's roles (YULE_GEMM_PROF=1 prints them after the launch): a timing aid.
+__device__ long long g_gemm_prof[16];
 
 struct GemmParams {
     const uint8_t *w;      // Q4_K blocks, row-major
     const __half *xb;      // activation tiles written by gemm_xprep_kernel
-    const float *oscale;   // per (padded) activation row: 1 / (row scale · kWScale)
+    const float *oscale;   // per (padded) activation row: 1 / row scale
     float *out;            // [n_tokens][out_stride]
     const float *residual; // added to out (same layout) or null
     uint32_t n_rows, n_cols, n_tokens, out_stride;
     uint32_t bn;           // activation rows per tile: 32, 64 or 128
     uint32_t n_mtiles, n_ntiles, stages;
+    uint32_t prof;         // timing aid: record cycle counters of CTA 0
+    uint32_t skip;         // timing aid (YULE_GEMM_SKIP): 1 no unpacking, 2 no MMAs, 4 no draining; results meaningless
     int *status;
 };
 
@@ -138,42 +156,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// 6-bit scale and min of sub-block j from the 12 packed bytes (yule-core/src/dequant.rs:165-176).
-__device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t j, uint32_t *sc, uint32_t *mn) {
-    auto byte_of = [&](uint32_t i) {
-        const uint32_t w = i < 4 ? s0 : (i < 8 ? s1 : s2);
-        return (w >> (8 * (i & 3))) & 0xFFu;
-    };
-    if (j < 4) {
-        *sc = byte_of(j) & 63u;
-        *mn = byte_of(j + 4) & 63u;
-    } else {
-        *sc = (byte_of(j + 4) & 0xFu) | ((byte_of(j - 4) >> 6) << 4);
-        *mn = (byte_of(j + 4) >> 4) | ((byte_of(j) >> 6) << 4);
-    }
+// The eight 6-bit scales and mins of a super-block from its 12 packed bytes
+// (yule-core/src/dequant.rs:165-176), four per word, one byte each.
+struct ScalesMins {
+    uint32_t sc_lo, sc_hi, m_lo, m_hi;  // sub-blocks 0-3 and 4-7
+};
+__device__ __forceinline__ ScalesMins q4k_scales_mins(uint32_t s0, uint32_t s1, uint32_t s2) {
+    ScalesMins r;
+    r.sc_lo = s0 & 0x3F3F3F3Fu;
+    r.m_lo = s1 & 0x3F3F3F3Fu;
+    r.sc_hi = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
+    r.m_hi = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
+    return r;
 }
-
-// Eight weights q·ds − dm (q = the low nibble of each byte of w0, w1) as fp16 hi and lo terms.
-__device__ __forceinline__ void dequant8(uint32_t w0, uint32_t w1, float ds, float dm, uint4 *hi, uint4 *lo) {
-    float v[8];
-#pragma unroll
-    for (int b = 0; b < 4; b++) {
-        // 0x4B000000 | q is the float 2²³ + q: the subtraction is exact
-        v[b] = fmaf(__uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7440 + b)) - 8388608.f, ds, -dm);
-        v[4 + b] = fmaf(__uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7440 + b)) - 8388608.f, ds, -dm);
-    }
-    uint32_t h[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const __half2 hh = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        const float2 back = __half22float2(hh);
-        const __half2 ll = __floats2half2_rn(v[2 * i] - back.x, v[2 * i + 1] - back.y);
-        h[i] = *reinterpret_cast<const uint32_t *>(&hh);
-        l[i] = *reinterpret_cast<const uint32_t *>(&ll);
-    }
-    *hi = make_uint4(h[0], h[1], h[2], h[3]);
-    *lo = make_uint4(l[0], l[1], l[2], l[3]);
-}
+// fp16 pair (1024 + a, 1024 + b) from two bytes: 0x6400 | v is the half 1024 + v for v < 1024
+__device__ __forceinline__ uint32_t biased_pair(uint32_t word, uint32_t selector) { return __byte_perm(word, 0x64646464u, selector); }
+__device__ __forceinline__ __half2 as_half2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
 
 // One row's share of a super-block: the 16-byte header (d, dmin, packed scales) and this thread's
 // 16 of the 32 quant bytes of each of the four 64-column groups.
@@ -183,20 +182,33 @@ struct RowBlock {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const GemmParams p) {
-    constexpr uint32_t NBUF = BN <= 64 ? 4 : 2;            // TMEM accumulators in flight
-    constexpr uint32_t kTmemCols = NBUF * BN;              // 128 or 256: a power of two ≥ 32
-    constexpr uint32_t CW = BN / 2;                        // columns per drain warp
-    constexpr uint32_t kXHalfBytes = BN * kBK * 2;         // one fp16 term of the activation slab
-    constexpr uint32_t kStageBytes = 2 * kAHalfBytes + 2 * kXHalfBytes;
+struct Tile {
+    static constexpr uint32_t NBUF = BN <= 64 ? 4 : 2;       // TMEM accumulator pairs in flight
+    static constexpr uint32_t kTmemCols = NBUF * 2 * BN;     // 256 or 512: main + min accumulator each
+    static constexpr uint32_t CW = BN / 2;                   // columns per drain warp
+    static constexpr uint32_t kXHalfBytes = BN * kBK * 2;    // one fp16 term of the activation slab
+    static constexpr uint32_t kBmBytes = BN * 16 * 2;        // sub-block sums of x: BN rows × (8 hi + 8 lo)
+    // stage: W | m | x_hi | x_lo | sums   (the last three arrive in one bulk copy)
+    static constexpr uint32_t kOffAm = kABytes, kOffX = kABytes + kAmBytes;
+    static constexpr uint32_t kStageBytes = kOffX + 2 * kXHalfBytes + kBmBytes;
+    // activation tiles in global memory, per (activation tile, super-block): four (hi, lo) slabs, then the sums
+    static constexpr uint32_t kSuperBytes = 8 * kXHalfBytes + kBmBytes;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap w_map) {
+    using T = Tile<BN>;
+    constexpr uint32_t NBUF = T::NBUF, CW = T::CW, kXHalfBytes = T::kXHalfBytes, kStageBytes = T::kStageBytes;
     extern __shared__ __align__(128) unsigned char smem[];
     yule_pdl_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *tail = smem + (size_t)p.stages * kStageBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tail);     // full[6] empty[6] acc_full[4] acc_empty[4]
+    unsigned char *raw = tail;                               // kRawSlots boxes of raw Q4_K bytes
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tail + kRawSlots * kRawBytes);  // full[6] empty[6] acc_full[4] acc_empty[4] raw_full[4] raw_empty[4]
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kMaxStages;
     const uint32_t bar_acc_full = bar_empty + 8 * kMaxStages, bar_acc_empty = bar_acc_full + 32;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kMaxStages + 8);
+    const uint32_t bar_raw_full = bar_acc_empty + 32, bar_raw_empty = bar_raw_full + 8 * kRawSlots;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kMaxStages + 8 + 2 * kRawSlots);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     if (threadIdx.x == 0) {
@@ -208,12 +220,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             mbar_init(bar_acc_full + 8 * b, 1);
             mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
         }
+        for (uint32_t b = 0; b < (uint32_t)kRawSlots; b++) {
+            mbar_init(bar_raw_full + 8 * b, 1);            // the loader's expect_tx
+            mbar_init(bar_raw_empty + 8 * b, kProdWarps);  // every producer warp is done with the box
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
     if (warp == kMmaWarp) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(T::kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -233,17 +249,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const uint32_t nt = tile % p.n_ntiles;
-                const unsigned char *src = reinterpret_cast<const unsigned char *>(p.xb) + (size_t)nt * n_kb * 2 * kXHalfBytes;
+                const unsigned char *src = reinterpret_cast<const unsigned char *>(p.xb) + (size_t)nt * bpr * T::kSuperBytes;
                 for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
                     const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes + 2 * kAHalfBytes);
-                    mbar_arrive_expect_tx(bar_full + 8 * s, 2 * kXHalfBytes);
+                    const uint32_t g = kb & 3u;
+                    const uint32_t bytes = 2 * kXHalfBytes + (g == 3 ? T::kBmBytes : 0u);  // the sums ride with the last stage
+                    const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes + T::kOffX);
+                    if (p.skip & 8u) {
+                        mbar_arrive(bar_full + 8 * s);
+                        continue;
+                    }
+                    mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                                 "l"(src + (size_t)kb * 2 * kXHalfBytes), "r"(2 * kXHalfBytes), "r"(bar_full + 8 * s)
+                                 "l"(src + (size_t)(kb >> 2) * T::kSuperBytes + (size_t)g * 2 * kXHalfBytes), "r"(bytes),
+                                 "r"(bar_full + 8 * s)
                                  : "memory");
                 }
             }
@@ -252,33 +275,73 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
         if (lane == 0) {
             // fp16 × fp16 → fp32, both operands K-major, M = 128, N = BN
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-            constexpr uint32_t x_lbo = BN * 16;  // bytes of one 8-column step of the activation slab
+            constexpr uint32_t x_lbo = BN * 16;  // bytes of one 8-column step of an activation slab
             uint32_t it = 0;
             bool ok = true;
+            long long tw0 = 0, tw1 = 0, ti = 0, tc = 0;
+            const long long tstart = p.prof ? clock64() : 0;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
                     const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
                     const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
-                    if (!mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status) ||
-                        !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) {
+                    const long long c0 = p.prof ? clock64() : 0;
+                    if (!(p.skip & 16u) && !mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
+                    const long long c1 = p.prof ? clock64() : 0;
+                    if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const long long c2 = p.prof ? clock64() : 0;
+                    tw0 += c1 - c0;
+                    tw1 += c2 - c1;
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + buf * BN;
-                    const uint32_t a_hi = smem_u32(smem + (size_t)s * kStageBytes), a_lo = a_hi + kAHalfBytes;
-                    const uint32_t x_hi = a_lo + kAHalfBytes, x_lo = x_hi + kXHalfBytes;
+                    const uint32_t d_main = tmem_base + buf * 2 * BN, d_min = d_main + BN;
+                    const uint32_t a = smem_u32(smem + (size_t)s * kStageBytes);
+                    const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
 #pragma unroll
                     for (uint32_t k16 = 0; k16 < kBK / 16; k16++) {
-                        const uint64_t da_hi = smem_desc(a_hi + k16 * 4096, 2048, 128), da_lo = smem_desc(a_lo + k16 * 4096, 2048, 128);
-                        const uint64_t dx_hi = smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), dx_lo = smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128);
-                        umma_f16(d_tmem, da_hi, dx_hi, idesc, k16 != 0u);  // every stage starts a fresh accumulator
-                        umma_f16(d_tmem, da_hi, dx_lo, idesc, 1u);
-                        umma_f16(d_tmem, da_lo, dx_hi, idesc, 1u);
+                        if (p.skip & 2u) break;
+                        const uint64_t da = smem_desc(a + k16 * 4096, 2048, 128);
+                        umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // fresh per stage
+                        umma_f16(d_main, da, smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
                     }
+                    if ((kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
+                        umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(x_lo + kXHalfBytes, x_lbo, 128), idesc, 0u);
+                    const long long c3 = p.prof ? clock64() : 0;
                     umma_commit(bar_empty + 8 * s);       // the slabs may be overwritten once these MMAs are done
-                    umma_commit(bar_acc_full + 8 * buf);  // and the accumulator may be drained
+                    if (!(p.skip & 32u)) umma_commit(bar_acc_full + 8 * buf);  // and the accumulators may be drained
+                    const long long c4 = p.prof ? clock64() : 0;
+                    ti += c3 - c2;
+                    tc += c4 - c3;
                 }
+            }
+            if (p.prof && blockIdx.x == 0) {
+                g_gemm_prof[0] = clock64() - tstart;
+                g_gemm_prof[1] = tw0;
+                g_gemm_prof[2] = tw1;
+                g_gemm_prof[3] = ti;
+                g_gemm_prof[4] = tc;
+                g_gemm_prof[5] = it;
+            }
+        }
+    } else if (warp == kRawWarp) {
+        if (lane == 0) {
+            const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const uint32_t n_units = my_tiles * bpr;
+            for (uint32_t u = 0; u < n_units; u++) {
+                const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
+                if (!mbar_wait(bar_raw_empty + 8 * slot, ph ^ 1u, abort_flag, p.status)) break;
+                const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x, sb = u % bpr;
+                const uint32_t x = sb * 144u, y = (tile / p.n_ntiles) * kBM;  // byte column (a multiple of 16), first row
+                mbar_arrive_expect_tx(bar_raw_full + 8 * slot, kRawBytes);
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                        smem_u32(raw + (size_t)slot * kRawBytes)),
+                    "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar_raw_full + 8 * slot), "r"(x), "r"(y)
+                    : "memory");
             }
         }
     } else if (warp >= kFirstProdWarp) {
@@ -286,58 +349,90 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
         const uint32_t r = ptid & 127u, hf = ptid >> 7;           // row of the tile, which 16 bytes of the 32
         const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t n_units = my_tiles * bpr;  // (tile, super-block) pairs of this CTA, in order
-        auto load_block = [&](uint32_t u, RowBlock &b) {
-            if (u >= n_units) return;
-            const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x, sb = u % bpr;
-            uint32_t row = (tile / p.n_ntiles) * kBM + r;
-            row = row < p.n_rows ? row : p.n_rows - 1;  // clamp: stays in bounds, the result is dropped
-            const uint8_t *bp = p.w + ((size_t)row * bpr + sb) * 144;
-            b.hdr = __ldg(reinterpret_cast<const uint4 *>(bp));
-#pragma unroll
-            for (int g = 0; g < 4; g++) b.q[g] = __ldg(reinterpret_cast<const uint4 *>(bp + 16 + g * 32 + hf * 16));
-        };
-        RowBlock cur, nxt, nxt2;
-        load_block(0, cur);
-        load_block(1, nxt);
         uint32_t it = 0;
         bool ok = true;
         const uint32_t in_core = (r >> 3) * 128 + (r & 7u) * 16;
-        for (uint32_t u = 0; u < n_units && ok; u++) {
-            load_block(u + 2, nxt2);
-            const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&cur.hdr.x));
+        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400)), kneg1024 = __half2half2(__ushort_as_half(0xE400));
+        long long pw = 0, pk = 0, pf = 0;
+        const long long pstart = p.prof ? clock64() : 0;
+        // the four stages of one super-block
+        auto unpack_block = [&](const RowBlock &cur) {
+            const ScalesMins sm = q4k_scales_mins(cur.hdr.y, cur.hdr.z, cur.hdr.w);
 #pragma unroll
             for (uint32_t g = 0; g < 4; g++, it++) {
                 const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
-                uint32_t sc0, mn0, sc1, mn1;
-                q4k_scale_min(cur.hdr.y, cur.hdr.z, cur.hdr.w, 2 * g, &sc0, &mn0);
-                q4k_scale_min(cur.hdr.y, cur.hdr.z, cur.hdr.w, 2 * g + 1, &sc1, &mn1);
-                const float ds0 = dd.x * (float)sc0 * kWScale, dm0 = dd.y * (float)mn0 * kWScale;
-                const float ds1 = dd.x * (float)sc1 * kWScale, dm1 = dd.y * (float)mn1 * kWScale;
+                // scales of sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles) as fp16 pairs (sc, sc)
+                const uint32_t scw = g < 2 ? sm.sc_lo : sm.sc_hi, j0 = (2 * g) & 3u;
+                const __half2 sc0 = __hsub2(as_half2(biased_pair(scw, 0x4040u + j0 * 0x0101u)), k1024);
+                const __half2 sc1 = __hsub2(as_half2(biased_pair(scw, 0x4040u + (j0 + 1) * 0x0101u)), k1024);
+                const __half2 nb0 = __hmul2(sc0, kneg1024), nb1 = __hmul2(sc1, kneg1024);  // −1024·sc ≥ −64512: exact
+                const long long c0 = p.prof ? clock64() : 0;
                 if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                     ok = false;
-                    break;
+                    return;
                 }
-                unsigned char *a_hi = smem + (size_t)s * kStageBytes, *a_lo = a_hi + kAHalfBytes;
+                const long long c1 = p.prof ? clock64() : 0;
+                pw += c1 - c0;
+                unsigned char *a = smem + (size_t)s * kStageBytes;
                 // byte b of the 32 holds column b (low nibble, sub-block 2g) and column 32 + b (high nibble)
                 const uint32_t qw[4] = {cur.q[g].x, cur.q[g].y, cur.q[g].z, cur.q[g].w};
 #pragma unroll
                 for (int half8 = 0; half8 < 2; half8++) {
+                    if (p.skip & 1u) break;
                     const uint32_t w0 = qw[2 * half8], w1 = qw[2 * half8 + 1];
-                    uint4 hi, lo;
                     const uint32_t kc_lo = hf * 2 + half8;  // 8-column step of the low-nibble columns
-                    dequant8(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, ds0, dm0, &hi, &lo);
-                    *reinterpret_cast<uint4 *>(a_hi + kc_lo * 2048 + in_core) = hi;
-                    *reinterpret_cast<uint4 *>(a_lo + kc_lo * 2048 + in_core) = lo;
-                    dequant8((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, ds1, dm1, &hi, &lo);
-                    *reinterpret_cast<uint4 *>(a_hi + (4 + kc_lo) * 2048 + in_core) = hi;
-                    *reinterpret_cast<uint4 *>(a_lo + (4 + kc_lo) * 2048 + in_core) = lo;
+                    // (1024 + q)·sc − 1024·sc = q·sc, exact; pairs are bytes (0, 2) and (1, 3) of a word
+                    auto mul = [&](uint32_t nib_pair, __half2 sc, __half2 nb) {
+                        return as_u32(__hfma2(as_half2((nib_pair & 0x000F000Fu) | 0x64006400u), sc, nb));
+                    };
+                    uint4 lo, hi;
+                    lo.x = mul(w0, sc0, nb0);
+                    lo.y = mul(w0 >> 8, sc0, nb0);
+                    lo.z = mul(w1, sc0, nb0);
+                    lo.w = mul(w1 >> 8, sc0, nb0);
+                    hi.x = mul(w0 >> 4, sc1, nb1);
+                    hi.y = mul(w0 >> 12, sc1, nb1);
+                    hi.z = mul(w1 >> 4, sc1, nb1);
+                    hi.w = mul(w1 >> 12, sc1, nb1);
+                    *reinterpret_cast<uint4 *>(a + kc_lo * 2048 + in_core) = lo;
+                    *reinterpret_cast<uint4 *>(a + (4 + kc_lo) * 2048 + in_core) = hi;
                 }
+                if (g == 3) {
+                    // the eight mins of the super-block, twice: columns 0-7 meet the hi sums, 8-15 the lo sums
+                    uint4 m;
+                    m.x = as_u32(__hsub2(as_half2(biased_pair(sm.m_lo, 0x5140u)), k1024));
+                    m.y = as_u32(__hsub2(as_half2(biased_pair(sm.m_lo, 0x5342u)), k1024));
+                    m.z = as_u32(__hsub2(as_half2(biased_pair(sm.m_hi, 0x5140u)), k1024));
+                    m.w = as_u32(__hsub2(as_half2(biased_pair(sm.m_hi, 0x5342u)), k1024));
+                    *reinterpret_cast<uint4 *>(a + T::kOffAm + hf * 2048 + in_core) = m;
+                }
+                const long long c2 = p.prof ? clock64() : 0;
                 fence_async_smem();  // generic-proxy stores → visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                const long long c3 = p.prof ? clock64() : 0;
+                pk += c2 - c1;
+                pf += c3 - c2;
             }
-            cur = nxt;
-            nxt = nxt2;
+        };
+        for (uint32_t u = 0; u < n_units && ok; u++) {
+            const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
+            if (!mbar_wait(bar_raw_full + 8 * slot, ph, abort_flag, p.status)) break;
+            // row r of the box: 144 bytes; rows are 36 words apart, so eight lanes cover all 32 banks
+            const unsigned char *bp = raw + (size_t)slot * kRawBytes + r * 144u;
+            RowBlock cur;
+            cur.hdr = *reinterpret_cast<const uint4 *>(bp);
+#pragma unroll
+            for (int g = 0; g < 4; g++) cur.q[g] = *reinterpret_cast<const uint4 *>(bp + 16 + g * 32 + hf * 16);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_raw_empty + 8 * slot);  // this warp's share of the box is in registers
+            unpack_block(cur);
+        }
+        if (p.prof && blockIdx.x == 0 && ptid == 0) {
+            g_gemm_prof[6] = clock64() - pstart;
+            g_gemm_prof[7] = pw;
+            g_gemm_prof[8] = pk;
+            g_gemm_prof[9] = pf;
         }
     } else {
         // drain warp: TMEM lanes [32·(warp % 4), +32) = rows of the tile, columns [CW·(warp / 4), +CW)
@@ -345,31 +440,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
         const uint32_t lane_base = (warp & 3u) * 32u, col_base = (warp >> 2) * CW;
         uint32_t it = 0;
         bool ok = true;
+        long long dw = 0;
+        const long long dstart = p.prof ? clock64() : 0;
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const uint32_t mt = tile / p.n_ntiles, nt = tile % p.n_ntiles;
+            const uint32_t row = mt * kBM + lane_base + lane;
+            const uint8_t *rowp = p.w + (size_t)(row < p.n_rows ? row : p.n_rows - 1) * bpr * 144;
             float acc[CW];
 #pragma unroll
             for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
+            uint32_t dd_cur = 0, dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp));  // (d, dmin) of super-block 0
             for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
+                if (p.skip & 32u) break;
                 const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
+                if ((kb & 3u) == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
+                    dd_cur = dd_next;
+                    if (kb + 4 < n_kb) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)((kb >> 2) + 1) * 144));
+                }
+                const float2 dd = __half22float2(as_half2(dd_cur));
+                const long long c0 = p.prof ? clock64() : 0;
                 if (!mbar_wait(bar_acc_full + 8 * buf, aph, abort_flag, p.status)) {
                     ok = false;
                     break;
                 }
+                if (p.prof) dw += clock64() - c0;
                 tc_fence_after();
+                const uint32_t t_main = tmem_base + (lane_base << 16) + buf * 2 * BN + col_base;
 #pragma unroll
                 for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
+                    if (p.skip & 4u) break;
                     uint32_t v[16];
-                    tmem_ld16(tmem_base + (lane_base << 16) + buf * BN + col_base + c0, v);
+                    tmem_ld16(t_main + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) acc[c0 + j] += __uint_as_float(v[j]);
+                    for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(dd.x, __uint_as_float(v[j]), acc[c0 + j]);
+                }
+                if ((kb & 3u) == 3u) {
+#pragma unroll
+                    for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(t_main + BN + c0, v);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(-dd.y * (1.0f / kSumScale), __uint_as_float(v[j]), acc[c0 + j]);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
             }
             if (!ok) break;
-            const uint32_t row = mt * kBM + lane_base + lane;
             const uint32_t n0 = nt * BN + col_base;
 #pragma unroll
             for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
@@ -387,8 +505,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                 }
             }
         }
+        if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
+            g_gemm_prof[10] = clock64() - dstart;
+            g_gemm_prof[11] = dw;
+        }
     }
 
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) g_gemm_prof[15] = 1;
     // common exit: nothing of this CTA may still be in flight when its TMEM and shared memory go
     tc_fence_before();
     __syncthreads();
@@ -401,20 +524,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
         __syncthreads();
     }
     if (warp == kMmaWarp) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T::kTmemCols) : "memory");
     }
 }
 
-// Activation rows → fp16 hi/lo tiles in the operand layout of the GEMM, one CTA per (padded) row.
-// Optional prologues: RMSNorm (out = x · inv · w as in yule-infer/src/model_runner.rs:254-263) or
-// SwiGLU (silu(gate) · x, kernels/cuda/silu_mul.cu:3-14).
+// Activation rows → the GEMM's operand tiles, one CTA per (padded) row: power-of-two row scale,
+// fp16 hi/lo split, the column order of the W operand inside every group of eight, and the
+// per-32-column sums for the min term.  Optional prologues: RMSNorm (out = x · inv · w as in
+// yule-infer/src/model_runner.rs:254-263) or SwiGLU (silu(gate) · x, kernels/cuda/silu_mul.cu:3-14).
 struct XprepParams {
     const float *x;
     const float *gate;    // when set: y = silu(gate) · x
     const float *norm_w;  // when set: y = x · inv_rms · norm_w
     float eps;
     uint32_t x_stride, n_tokens, n_cols, bn;
-    __half *xb;
+    unsigned char *xb;
     float *oscale;
 };
 
@@ -423,15 +547,27 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
     yule_pdl_wait();
     __shared__ float red[32];
     const uint32_t n = blockIdx.x, nt = n / p.bn, r = n % p.bn;
-    const uint32_t n_kb = p.n_cols / kBK;
-    const size_t half_elems = (size_t)p.bn * kBK;  // halves per fp16 term of one slab
-    auto slab = [&](uint32_t kb, uint32_t term) { return p.xb + ((size_t)(nt * n_kb + kb) * 2 + term) * half_elems; };
-    auto in_slab = [&](uint32_t kk) { return ((kk >> 3) * (p.bn / 8) + (r >> 3)) * 64 + (r & 7u) * 8; };
+    const uint32_t bpr = p.n_cols / 256;
+    const uint32_t x_half_bytes = p.bn * kBK * 2, bm_bytes = p.bn * 32, super_bytes = 8 * x_half_bytes + bm_bytes;
+    const uint32_t core = ((r >> 3) * 64 + (r & 7u) * 8) * 2;  // byte offset of this row inside an 8-column step
+    // 16 bytes of columns [k0, k0 + 8): term 0 = hi, 1 = lo
+    auto slab16 = [&](uint32_t k0, uint32_t term) {
+        const uint32_t sb = k0 >> 8, g = (k0 >> 6) & 3u, kc = (k0 >> 3) & 7u;
+        return p.xb + ((size_t)nt * bpr + sb) * super_bytes + (size_t)(2 * g + term) * x_half_bytes + kc * (p.bn * 16) + core;
+    };
+    // the two bytes of sub-block s (of super-block sb) in the sums slab: column s (hi) or 8 + s (lo)
+    auto sum_slot = [&](uint32_t sb, uint32_t s, uint32_t term) {
+        return reinterpret_cast<__half *>(p.xb + ((size_t)nt * bpr + sb) * super_bytes + 8 * (size_t)x_half_bytes +
+                                          term * (p.bn * 16) + core) + s;
+    };
     if (n >= p.n_tokens) {  // padding row of the last tile
         for (uint32_t k0 = threadIdx.x * 8; k0 < p.n_cols; k0 += 256 * 8) {
-            const uint32_t kb = k0 / kBK, off = in_slab(k0 % kBK);
-            *reinterpret_cast<uint4 *>(slab(kb, 0) + off) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4 *>(slab(kb, 1) + off) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(slab16(k0, 0)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(slab16(k0, 1)) = make_uint4(0, 0, 0, 0);
+            if ((k0 & 31u) == 0) {
+                *sum_slot(k0 >> 8, (k0 >> 5) & 7u, 0) = __ushort_as_half(0);
+                *sum_slot(k0 >> 8, (k0 >> 5) & 7u, 1) = __ushort_as_half(0);
+            }
         }
         if (threadIdx.x == 0) p.oscale[n] = 0.f;
         return;
@@ -476,22 +612,67 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
         frexpf(amax, &ex);  // amax = m · 2^ex, m in [0.5, 1)
         scale = ldexpf(1.f, 14 - ex);
     }
-    if (threadIdx.x == 0) p.oscale[n] = (1.0f / scale) / kWScale;
+    if (threadIdx.x == 0) p.oscale[n] = 1.0f / scale;
     for (uint32_t k0 = threadIdx.x * 8; k0 < p.n_cols; k0 += 256 * 8) {
+        float v[8];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            v[i] = value(k0 + i) * scale;
+            sum += v[i];
+        }
+        // positions 0..7 of the 16 bytes hold columns 0,2,1,3,4,6,5,7
+        const float o[8] = {v[0], v[2], v[1], v[3], v[4], v[6], v[5], v[7]};
         uint32_t h[4], l[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float v0 = value(k0 + 2 * i) * scale, v1 = value(k0 + 2 * i + 1) * scale;
-            const __half2 hh = __floats2half2_rn(v0, v1);
+            const __half2 hh = __floats2half2_rn(o[2 * i], o[2 * i + 1]);
             const float2 back = __half22float2(hh);
-            const __half2 ll = __floats2half2_rn(v0 - back.x, v1 - back.y);
-            h[i] = *reinterpret_cast<const uint32_t *>(&hh);
-            l[i] = *reinterpret_cast<const uint32_t *>(&ll);
+            h[i] = as_u32(hh);
+            l[i] = as_u32(__floats2half2_rn(o[2 * i] - back.x, o[2 * i + 1] - back.y));
         }
-        const uint32_t kb = k0 / kBK, off = in_slab(k0 % kBK);
-        *reinterpret_cast<uint4 *>(slab(kb, 0) + off) = make_uint4(h[0], h[1], h[2], h[3]);
-        *reinterpret_cast<uint4 *>(slab(kb, 1) + off) = make_uint4(l[0], l[1], l[2], l[3]);
+        *reinterpret_cast<uint4 *>(slab16(k0, 0)) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4 *>(slab16(k0, 1)) = make_uint4(l[0], l[1], l[2], l[3]);
+        // four consecutive threads cover one 32-column sub-block
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((threadIdx.x & 3u) == 0) {
+            sum *= kSumScale;  // 32 elements of up to 2^14 each: keep the sum inside fp16's range
+            const __half sh = __float2half_rn(sum);
+            *sum_slot(k0 >> 8, (k0 >> 5) & 7u, 0) = sh;
+            *sum_slot(k0 >> 8, (k0 >> 5) & 7u, 1) = __float2half_rn(sum - __half2float(sh));
+        }
     }
+}
+
+// 2-D view of a Q4_K matrix for the TMA engine: bytes along a row, rows; box = one super-block
+// (144 bytes) of 128 rows.  Rows past the end read as zeros (a block of zeros dequantises to 0).
+cudaError_t encode_weight_map(const uint8_t *w, uint32_t n_rows, uint32_t n_cols, CUtensorMap *out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!encode) {
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+            if (e != cudaSuccess) return e;
+            if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+            encode = reinterpret_cast<EncodeFn>(fn);
+        }
+    }
+    const cuuint64_t row_bytes = (cuuint64_t)(n_cols / 256) * 144;
+    const cuuint64_t dims[2] = {row_bytes, n_rows};
+    const cuuint64_t strides[1] = {row_bytes};  // bytes between rows (a multiple of 16)
+    const cuuint32_t box[2] = {144, kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 64 ? 64 : 128); }
@@ -505,15 +686,16 @@ bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens) {
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols) {
     const uint32_t bn = pick_bn(n_tokens);
     const size_t padded = (size_t)((n_tokens + bn - 1) / bn) * bn;
-    return padded * n_cols * 4 + padded * sizeof(float) + 256;
+    return padded * n_cols * 4 + padded * (n_cols / 256) * 32 + padded * sizeof(float) + 512;
 }
 
-cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches) {
-    if (!qgemm_supported(g.type, g.n_cols, g.n_tokens) || g.n_rows == 0) return cudaErrorInvalidValue;
+cudaError_t launch_qgemm_xprep(const QGemm &g, cudaStream_t s, uint64_t *launches) {
+    if (!qgemm_supported(g.type, g.n_cols, g.n_tokens)) return cudaErrorInvalidValue;
     const uint32_t bn = pick_bn(g.n_tokens);
     const uint32_t n_ntiles = (g.n_tokens + bn - 1) / bn, padded = n_ntiles * bn;
-    __half *xb = reinterpret_cast<__half *>(g.scratch);
-    float *oscale = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(g.scratch) + (((size_t)padded * g.n_cols * 4 + 255) & ~(size_t)255));
+    unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch);
+    const size_t tiles_bytes = (size_t)padded * g.n_cols * 4 + (size_t)padded * (g.n_cols / 256) * 32;
+    float *oscale = reinterpret_cast<float *>(xb + ((tiles_bytes + 255) & ~(size_t)255));
 
     XprepParams xp = {};
     xp.x = g.x;
@@ -529,10 +711,20 @@ cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t 
     cudaError_t e = launch_kernel(gemm_xprep_kernel, dim3(padded), dim3(256), 0, s, g.pdl, xp);
     if (e != cudaSuccess) return e;
     *launches += 1;
+    return cudaSuccess;
+}
 
+cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches) {
+    if (!qgemm_supported(g.type, g.n_cols, g.n_tokens) || g.n_rows == 0) return cudaErrorInvalidValue;
+    const uint32_t bn = pick_bn(g.n_tokens);
+    const uint32_t n_ntiles = (g.n_tokens + bn - 1) / bn, padded = n_ntiles * bn;
+    unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch);
+    const size_t tiles_bytes = (size_t)padded * g.n_cols * 4 + (size_t)padded * (g.n_cols / 256) * 32;
+    float *oscale = reinterpret_cast<float *>(xb + ((tiles_bytes + 255) & ~(size_t)255));
+    cudaError_t e;
     GemmParams p = {};
     p.w = g.w;
-    p.xb = xb;
+    p.xb = reinterpret_cast<const __half *>(xb);
     p.oscale = oscale;
     p.out = g.out;
     p.residual = g.residual;
@@ -543,22 +735,47 @@ cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t 
     p.bn = bn;
     p.n_mtiles = (g.n_rows + kBM - 1) / kBM;
     p.n_ntiles = n_ntiles;
-    const uint32_t stage_bytes = 2 * kAHalfBytes + 2 * bn * kBK * 2;
-    uint32_t stages = (200u * 1024u) / stage_bytes;
+    const uint32_t stage_bytes = kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
+    uint32_t stages = (uint32_t)((220u * 1024u - (kRawSlots * kRawBytes + 512u)) / stage_bytes);
     p.stages = stages > (uint32_t)kMaxStages ? (uint32_t)kMaxStages : stages;
     p.status = g.status;
-    const size_t smem = (size_t)p.stages * stage_bytes + (2 * kMaxStages + 8) * 8 + 16;
+    p.prof = getenv("YULE_GEMM_PROF") ? 1u : 0u;
+    p.skip = getenv("YULE_GEMM_SKIP") ? (uint32_t)atoi(getenv("YULE_GEMM_SKIP")) : 0u;
+    const size_t tail_bytes = (size_t)kRawSlots * kRawBytes + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 16;
+    const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
+    CUtensorMap w_map;
+    e = encode_weight_map(g.w, g.n_rows, g.n_cols, &w_map);
+    if (e != cudaSuccess) return e;
     uint32_t grid = p.n_mtiles * p.n_ntiles;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
     auto launch = [&](auto kern) {
-        cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+        cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024);
         if (e2 != cudaSuccess) return e2;
-        return launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, s, g.pdl, p);
+        return launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, s, g.pdl, p, w_map);
     };
     e = bn == 32 ? launch(qgemm_q4k_tc_kernel<32>) : (bn == 64 ? launch(qgemm_q4k_tc_kernel<64>) : launch(qgemm_q4k_tc_kernel<128>));
     if (e != cudaSuccess) return e;
     *launches += 1;
+    if (p.prof) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(s, &cs);
+        if (cs == cudaStreamCaptureStatusNone && cudaStreamSynchronize(s) == cudaSuccess) {
+            long long h[16];
+            if (cudaMemcpyFromSymbol(h, g_gemm_prof, sizeof(h)) == cudaSuccess)
+                fprintf(stderr,
+                        "[qgemm prof, CTA 0, cycles] mma: total %lld wait_acc_empty %lld wait_full %lld issue %lld commit %lld stages %lld | "
+                        "producer: total %lld wait_empty %lld unpack %lld fence+arrive %lld | drain: total %lld wait_acc_full %lld\n",
+                        h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], h[10], h[11]);
+        }
+    }
     return cudaSuccess;
+}
+
+cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches) {
+    if (g.n_rows == 0) return cudaErrorInvalidValue;
+    cudaError_t e = launch_qgemm_xprep(g, s, launches);
+    if (e != cudaSuccess) return e;
+    return launch_qgemm_mm(g, sm_count, s, launches);
 }
 
 }  // namespace yule

@@ -594,7 +594,23 @@ __global__ void embed_gather_kernel(const uint8_t *__restrict__ table, uint32_t 
         out[i] = dequant_elem(row, type, i);
 }
 
+// Rows tokens[0..n) of a [vocab][dim] table into out[n][dim]; blockIdx.y is the token slot.
+__global__ void embed_gather_batch_kernel(const uint8_t *__restrict__ table, uint32_t type, uint32_t dim,
+                                          const uint32_t *__restrict__ tokens, uint64_t row_bytes, float *__restrict__ out) {
+    const uint8_t *row = table + (uint64_t)tokens[blockIdx.y] * row_bytes;
+    float *o = out + (size_t)blockIdx.y * dim;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x) o[i] = dequant_elem(row, type, i);
+}
+
 }  // namespace
+
+cudaError_t launch_embed_gather_batch(const uint8_t *table, uint32_t type, uint32_t dim, const uint32_t *tokens,
+                                      uint32_t n_tokens, float *out, cudaStream_t s, uint64_t *launches) {
+    uint64_t row_bytes = (uint64_t)(dim / block_size(type)) * block_bytes(type);
+    *launches += 1;
+    embed_gather_batch_kernel<<<dim3((dim + 255) / 256, n_tokens), 256, 0, s>>>(table, type, dim, tokens, row_bytes, out);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_dequantize(const uint8_t *w, uint32_t type, uint64_t n_blocks, float *out, cudaStream_t s,
                               uint64_t *launches) {

@@ -64,6 +64,12 @@ struct yule_cuda_runner {
     uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
     size_t h_pinned_cap = 0;
 
+    // Batched prefill on the tensor-core GEMM: chunk buffers, allocated on first use
+    uint32_t pf_chunk = 0, pf_splits = 1;
+    float *pf_x = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_att = nullptr, *pf_gate = nullptr,
+          *pf_up = nullptr, *pf_attn_scratch = nullptr;
+    uint32_t *pf_tokens = nullptr, *pf_tickets = nullptr;
+
     uint32_t pos = 0;
     bool fused = false;
     bool pdl = true;  // programmatic dependent launch between the kernels of the graph
@@ -500,6 +506,157 @@ int32_t ensure_pinned(yule_cuda_runner *r, size_t n_words) {
     return YULE_OK;
 }
 
+// ── batched prefill ─────────────────────────────────────────────────────────────────────────
+// The reference feeds a prompt one token at a time through the decode path
+// (yule-infer/src/gpu_runner.rs:146-160).  Here the prompt goes through the layers in chunks of up
+// to 512 tokens: every linear is one tensor-core GEMM over the chunk, so the weights cross HBM once
+// per chunk instead of once per token.  It fills the KV caches only; the caller runs the last prompt
+// token through the ordinary token step, which produces the logits and the greedy pick.
+
+constexpr uint32_t kPrefillChunk = 512, kPrefillMinTokens = 16, kPrefillMinChunk = 256;
+
+uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
+    uint32_t c = getenv("YULE_CUDA_PREFILL_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_PREFILL_CHUNK")) : kPrefillChunk;
+    c = c < 8 ? 8 : c;
+    return c < r->cfg.max_seq_len ? c : r->cfg.max_seq_len;
+}
+
+// Single GPU, graph mode, grouped-query attention kernel available, every linear of every layer
+// Q4_K with a column count the GEMM takes, and a context short enough for the attention kernel's
+// score buffer at eight splits.
+bool prefill_batched_ok(const yule_cuda_runner *r) {
+    const yule_runner_config &c = r->cfg;
+    if (getenv("YULE_CUDA_BATCH_PREFILL") && atoi(getenv("YULE_CUDA_BATCH_PREFILL")) == 0) return false;
+    if (!r->fused || r->ctx->tp_world > 1 || !r->attn_gqa) return false;
+    if (!qgemm_supported(YULE_DTYPE_Q4_K, c.dim, 8) || !qgemm_supported(YULE_DTYPE_Q4_K, c.ff_dim, 8) ||
+        !qgemm_supported(YULE_DTYPE_Q4_K, c.n_heads * c.head_dim, 8))
+        return false;
+    for (const Layer &L : r->layers)
+        for (const Tensor *t : {&L.attn_q, &L.attn_k, &L.attn_v, &L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down})
+            if (t->type != YULE_DTYPE_Q4_K) return false;
+    const uint32_t splits = c.max_seq_len / 1024 < 1 ? 1 : (c.max_seq_len / 1024 > 8 ? 8 : c.max_seq_len / 1024);
+    const size_t score_bytes = (size_t)(c.n_heads / c.n_kv_heads) * ((c.max_seq_len + splits - 1) / splits + 4) * 4;
+    return score_bytes <= 96 * 1024;
+}
+
+int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n) {
+    const yule_runner_config &c = r->cfg;
+    yule_cuda_ctx *ctx = r->ctx;
+    cudaStream_t s = ctx->stream;
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    const int sms = ctx->prop.multiProcessorCount;
+    int32_t rc;
+    if (!r->pf_chunk) {
+        const uint32_t C = prefill_chunk_size(r);
+        r->pf_splits = c.max_seq_len / 1024 < 1 ? 1 : (c.max_seq_len / 1024 > 8 ? 8 : c.max_seq_len / 1024);
+        float *tok_f = nullptr, *tick_f = nullptr;
+        if ((rc = alloc_f32(r, (size_t)C * dim, &r->pf_x)) || (rc = alloc_f32(r, (size_t)C * qdim, &r->pf_q)) ||
+            (rc = alloc_f32(r, (size_t)C * kvdim, &r->pf_k)) || (rc = alloc_f32(r, (size_t)C * kvdim, &r->pf_v)) ||
+            (rc = alloc_f32(r, (size_t)C * qdim, &r->pf_att)) || (rc = alloc_f32(r, (size_t)C * ff, &r->pf_gate)) ||
+            (rc = alloc_f32(r, (size_t)C * ff, &r->pf_up)) || (rc = alloc_f32(r, C, &tok_f)) ||
+            (rc = alloc_f32(r, (size_t)C * c.n_heads, &tick_f)) ||
+            (rc = alloc_f32(r, (size_t)C * attn_scratch_floats(c.n_heads, r->pf_splits, hd) + 4, &r->pf_attn_scratch)))
+            return rc;
+        r->pf_tokens = (uint32_t *)tok_f;
+        r->pf_tickets = (uint32_t *)tick_f;  // zero-filled by the allocator; the kernel leaves them at zero
+        r->pf_chunk = C;
+    }
+    const uint32_t C = r->pf_chunk;
+    const uint32_t widest = ff > qdim ? (ff > dim ? ff : dim) : (qdim > dim ? qdim : dim);
+    if ((rc = ensure_gemm_scratch(ctx, qgemm_scratch_bytes(C, widest)))) return rc;
+    if ((rc = ensure_pinned(r, C))) return rc;
+    uint64_t launches = 0;
+    struct Guard {
+        yule_cuda_ctx *ctx;
+        uint64_t *n;
+        ~Guard() { ctx->launches.fetch_add(*n); }
+    } guard{ctx, &launches};
+
+    auto xprep = [&](const float *x, uint32_t cols, uint32_t m, const float *norm_w, const float *gate) {
+        QGemm g;
+        g.type = YULE_DTYPE_Q4_K;
+        g.x = x;
+        g.gate = gate;
+        g.norm_w = norm_w;
+        g.eps = c.norm_eps;
+        g.x_stride = cols;
+        g.n_cols = cols;
+        g.n_tokens = m;
+        g.scratch = ctx->gemm_scratch;
+        return launch_qgemm_xprep(g, s, &launches);
+    };
+    auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, uint32_t m, float *out, const float *residual) {
+        QGemm g;
+        g.w = (const uint8_t *)t.buf.ptr;
+        g.type = YULE_DTYPE_Q4_K;
+        g.out = out;
+        g.residual = residual;
+        g.n_rows = rows;
+        g.n_cols = cols;
+        g.n_tokens = m;
+        g.out_stride = rows;
+        g.scratch = ctx->gemm_scratch;
+        g.status = ctx->device_status;
+        return launch_qgemm_mm(g, sms, s, &launches);
+    };
+#define PF_TRY(expr)                                              \
+    do {                                                          \
+        cudaError_t _e = (expr);                                  \
+        if (_e != cudaSuccess) return fail_cuda(_e, "batched prefill: " #expr); \
+    } while (0)
+
+    for (uint32_t c0 = 0; c0 < n; c0 += C) {
+        const uint32_t m = n - c0 < C ? n - c0 : C, pos0 = r->pos + c0;
+        YULE_CUDA_TRY(cudaStreamSynchronize(s));  // the staging words of the previous chunk may still be in flight
+        for (uint32_t i = 0; i < m; i++) r->h_pinned[i] = tokens[c0 + i];
+        YULE_CUDA_TRY(cudaMemcpyAsync(r->pf_tokens, r->h_pinned, (size_t)m * 4, cudaMemcpyHostToDevice, s));
+        PF_TRY(launch_embed_gather_batch((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, r->pf_tokens, m, r->pf_x,
+                                         s, &launches));
+        for (uint32_t l = 0; l < c.n_layers; l++) {
+            Layer &L = r->layers[l];
+            // attention block: RMSNorm folded into the re-layout, Q/K/V share it
+            PF_TRY(xprep(r->pf_x, dim, m, L.attn_norm_f32, nullptr));
+            PF_TRY(mm(L.attn_q, qdim, dim, m, r->pf_q, nullptr));
+            PF_TRY(mm(L.attn_k, kvdim, dim, m, r->pf_k, nullptr));
+            PF_TRY(mm(L.attn_v, kvdim, dim, m, r->pf_v, nullptr));
+            PF_TRY(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin, pos0, m, hd,
+                                              c.n_heads, c.n_kv_heads, s, &launches));
+            AttnDecode a;
+            a.q = r->pf_q;
+            a.k_cache = L.k_cache;
+            a.v_cache = L.v_cache;
+            a.seq_len = pos0 + 1;  // query z attends to positions [0, pos0 + z]
+            a.out = r->pf_att;
+            a.scratch = r->pf_attn_scratch;
+            a.tickets = r->pf_tickets;
+            a.hd = hd;
+            a.n_heads = c.n_heads;
+            a.n_kv_heads = c.n_kv_heads;
+            a.kv_stride = kvdim;
+            a.n_splits = r->pf_splits;
+            a.max_seq_len = c.max_seq_len;
+            a.min_chunk = kPrefillMinChunk;
+            a.gqa = true;
+            a.n_tokens = m;
+            a.q_stride = qdim;
+            a.out_stride = qdim;
+            PF_TRY(launch_attn_decode(a, s, &launches));
+            PF_TRY(xprep(r->pf_att, qdim, m, nullptr, nullptr));
+            PF_TRY(mm(L.attn_output, dim, qdim, m, r->pf_x, r->pf_x));  // x += Wo · attention
+            // feed-forward block: RMSNorm folded in, gate/up share the re-layout, SwiGLU folded into the next one
+            PF_TRY(xprep(r->pf_x, dim, m, L.ffn_norm_f32, nullptr));
+            PF_TRY(mm(L.ffn_gate, ff, dim, m, r->pf_gate, nullptr));
+            PF_TRY(mm(L.ffn_up, ff, dim, m, r->pf_up, nullptr));
+            PF_TRY(xprep(r->pf_up, ff, m, nullptr, r->pf_gate));
+            PF_TRY(mm(L.ffn_down, dim, ff, m, r->pf_x, r->pf_x));  // x += Wdown · (silu(gate) · up)
+        }
+    }
+#undef PF_TRY
+    r->pos += n;
+    r->have_next_token = false;
+    return YULE_OK;
+}
+
 // One token through the model; logits stay on the device.
 int32_t step(yule_cuda_runner *r, uint32_t token, bool token_from_device) {
     const yule_runner_config &c = r->cfg;
@@ -684,7 +841,17 @@ int32_t yule_cuda_runner_prefill(yule_cuda_runner *r, const uint32_t *tokens, ui
     YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
     int32_t rc = finalize(r);
     if (rc) return rc;
-    for (uint32_t i = 0; i < n_tokens; i++)
+    if ((uint64_t)r->pos + n_tokens > r->cfg.max_seq_len) return fail(YULE_ERR_CONTEXT_LENGTH, "context length exceeded");
+    uint32_t first = 0;
+    if (n_tokens >= kPrefillMinTokens && prefill_batched_ok(r)) {
+        for (uint32_t i = 0; i < n_tokens; i++)
+            if (tokens[i] >= r->cfg.vocab_size)
+                return fail(YULE_ERR_INVALID_ARGUMENT, "token %u outside the vocabulary (%u)", tokens[i], r->cfg.vocab_size);
+        // all but the last token in chunks on the GEMM path; the last one yields the logits
+        if ((rc = prefill_batched(r, tokens, n_tokens - 1))) return rc;
+        first = n_tokens - 1;
+    }
+    for (uint32_t i = first; i < n_tokens; i++)
         if ((rc = step(r, tokens[i], false))) return rc;
     return n_tokens ? read_logits(r, logits_out) : YULE_OK;
 }
@@ -728,18 +895,25 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *pr
     if (n_prompt) {
         for (uint32_t i = 0; i < n_prompt; i++)
             if (prompt[i] >= c.vocab_size) return fail(YULE_ERR_INVALID_ARGUMENT, "token %u outside the vocabulary", prompt[i]);
-        if ((rc = ensure_pinned(r, 2 * (size_t)n_prompt))) return rc;
+        uint32_t first = 0;
+        if (n_prompt >= kPrefillMinTokens && prefill_batched_ok(r)) {
+            // all but the last prompt token in chunks on the GEMM path (KV caches only)
+            if ((rc = prefill_batched(r, prompt, n_prompt - 1))) return rc;
+            first = n_prompt - 1;
+        }
+        const uint32_t rest = n_prompt - first;
+        if ((rc = ensure_pinned(r, 2 * (size_t)rest))) return rc;
         YULE_CUDA_TRY(cudaStreamSynchronize(s));
-        for (uint32_t i = 0; i < n_prompt; i++) {
-            r->h_pinned[2 * i] = prompt[i];
+        for (uint32_t i = 0; i < rest; i++) {
+            r->h_pinned[2 * i] = prompt[first + i];
             r->h_pinned[2 * i + 1] = r->pos + i;
         }
-        for (uint32_t i = 0; i < n_prompt; i++) {
+        for (uint32_t i = 0; i < rest; i++) {
             YULE_CUDA_TRY(cudaMemcpyAsync(r->d_state, r->h_pinned + 2 * i, 8, cudaMemcpyHostToDevice, s));
             YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
         }
-        r->ctx->launches.fetch_add((uint64_t)graph_kernels(r) * n_prompt);
-        r->pos += n_prompt;
+        r->ctx->launches.fetch_add((uint64_t)graph_kernels(r) * rest);
+        r->pos += rest;
         r->have_next_token = true;
     }
     if (n_generate) {
