@@ -424,9 +424,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             cur.hdr = *reinterpret_cast<const uint4 *>(bp);
 #pragma unroll
             for (int g = 0; g < 4; g++) cur.q[g] = *reinterpret_cast<const uint4 *>(bp + 16 + g * 32 + hf * 16);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_raw_empty + 8 * slot);  // this warp's share of the box is in registers
             unpack_block(cur);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_raw_empty + 8 * slot);  // this warp is done with the box
         }
         if (p.prof && blockIdx.x == 0 && ptid == 0) {
             g_gemm_prof[6] = clock64() - pstart;
