@@ -19,15 +19,17 @@
 // leaves the long sum to ordinary round-to-nearest fp32.  The result matches the fp32 matvec to
 // fp32 rounding.
 //
-// One CTA per SM, 19 warps, persistent over (row tile, activation tile) pairs:
+// One CTA per SM, 20 warps, persistent over (row tile, activation tile) pairs:
 //   warps 0-7   drain warps: tcgen05.ld of their 32 TMEM lanes × half of the columns after every
 //               stage, FMA by d (and −dmin) into registers; at the end of a tile scale, residual, store
 //   warp  8     one thread: bulk copies (TMA engine) of the pre-arranged activation tiles
-//   warp  9     one thread: tcgen05.mma issue; the warp also owns the TMEM allocation
+//   warps 9, 11 one thread each: tcgen05.mma issue, even stages from one, odd stages from the other
+//               (a single thread issues about one MMA per 63 cycles, less than the tensor core
+//               takes); warp 9 also owns the TMEM allocation
 //   warp  10    one thread: tiled TMA loads (cp.async.bulk.tensor.2d) of the raw Q4_K bytes, one
 //               128-row × 144-byte box per super-block, four boxes in flight; rows past the end of
 //               the matrix arrive as zeros
-//   warps 11-18 unpack Q4_K from that shared-memory copy → fp16 sc·q in the operand layout (about
+//   warps 12-19 unpack Q4_K from that shared-memory copy → fp16 sc·q in the operand layout (about
 //               1.4 instructions per weight)
 // A stage is a 128-row × 64-column slab of W (16 KB) plus the matching hi and lo slabs of x; the last
 // stage of a super-block also carries the 4 KB m slab and the sub-block sums of x.
@@ -53,8 +55,9 @@ namespace {
 constexpr int kBM = 128;  // rows of W per tile = TMEM lanes
 constexpr int kBK = 64;   // columns per stage (a quarter of a super-block)
 constexpr int kEpiWarps = 8, kProdWarps = 8;
-constexpr int kLoaderWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kRawWarp = kEpiWarps + 2, kFirstProdWarp = kEpiWarps + 3;
-constexpr int kGemmThreads = (kEpiWarps + 3 + kProdWarps) * 32;  // 608
+constexpr int kLoaderWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kRawWarp = kEpiWarps + 2, kMmaWarp2 = kEpiWarps + 3,
+              kFirstProdWarp = kEpiWarps + 4;
+constexpr int kGemmThreads = (kEpiWarps + 4 + kProdWarps) * 32;  // 640
 constexpr int kMaxStages = 6;
 constexpr int kRawSlots = 4;                       // super-blocks of raw Q4_K bytes in flight per CTA
 constexpr uint32_t kRawBytes = kBM * 144;          // one super-block of 128 rows: 18 KB
@@ -210,6 +213,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
     const uint32_t bar_raw_full = bar_acc_empty + 32, bar_raw_empty = bar_raw_full + 8 * kRawSlots;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kMaxStages + 8 + 2 * kRawSlots);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile uint32_t *mma_progress = reinterpret_cast<volatile uint32_t *>(tmem_slot + 2);  // per MMA thread: stages seen full
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; s++) {
@@ -225,6 +229,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             mbar_init(bar_raw_empty + 8 * b, kProdWarps);  // every producer warp is done with the box
         }
         *abort_flag = 0;
+        mma_progress[0] = mma_progress[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
@@ -271,8 +276,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                 }
             }
         }
-    } else if (warp == kMmaWarp) {
+    } else if (warp == kMmaWarp || warp == kMmaWarp2) {
         if (lane == 0) {
+            const uint32_t parity_of_mine = warp == kMmaWarp ? 0u : 1u;  // this thread issues the stages with it % 2 == parity
             // fp16 × fp16 → fp32, both operands K-major, M = 128, N = BN
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
             constexpr uint32_t x_lbo = BN * 16;  // bytes of one 8-column step of an activation slab
@@ -282,18 +288,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             const long long tstart = p.prof ? clock64() : 0;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
+                    const bool mine = (it & 1u) == parity_of_mine;  // the threads alternate stages
                     const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
                     const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
                     const long long c0 = p.prof ? clock64() : 0;
-                    if (!(p.skip & 16u) && !mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status)) {
+                    if (mine && !(p.skip & 16u) && !mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
+                    if (!mine) continue;
                     const long long c1 = p.prof ? clock64() : 0;
+                    // A parity wait only tells phase k of a barrier from phase k - 1.  The previous use of this
+                    // stage may belong to the other thread: wait until it has seen that phase complete, so that
+                    // this thread never asks for a phase two ahead of the barrier's.
+                    if (it >= p.stages && ((it - p.stages) & 1u) != parity_of_mine) {
+                        const long long t0 = clock64();
+                        while (mma_progress[parity_of_mine ^ 1u] < it - p.stages + 1) {
+                            if (*abort_flag || clock64() - t0 > kWaitCycles) {
+                                *abort_flag = 1;
+                                atomicExch(p.status, kStatusGemmTimeout);
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!ok) break;
+                    }
                     if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
+                    mma_progress[parity_of_mine] = it + 1;
                     const long long c2 = p.prof ? clock64() : 0;
                     tw0 += c1 - c0;
                     tw1 += c2 - c1;
@@ -305,7 +329,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                     for (uint32_t k16 = 0; k16 < kBK / 16; k16++) {
                         if (p.skip & 2u) break;
                         const uint64_t da = smem_desc(a + k16 * 4096, 2048, 128);
-                        umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // fresh per stage
+                        umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // every stage starts a fresh accumulator
                         umma_f16(d_main, da, smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
                     }
                     if ((kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
@@ -318,7 +342,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                     tc += c4 - c3;
                 }
             }
-            if (p.prof && blockIdx.x == 0) {
+            if (p.prof && blockIdx.x == 0 && warp == kMmaWarp) {
                 g_gemm_prof[0] = clock64() - tstart;
                 g_gemm_prof[1] = tw0;
                 g_gemm_prof[2] = tw1;
@@ -474,7 +498,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
 #pragma unroll
                     for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(dd.x, __uint_as_float(v[j]), acc[c0 + j]);
                 }
-                if ((kb & 3u) == 3u) {
+                if ((kb & 3u) == 3u) {  // the stage that ends a super-block carries the min term
 #pragma unroll
                     for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                         uint32_t v[16];
