@@ -177,6 +177,18 @@ __device__ __forceinline__ uint32_t biased_pair(uint32_t word, uint32_t selector
 __device__ __forceinline__ __half2 as_half2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
 __device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
 
+// Position in the stage ring without a runtime division (an integer division runs on the same
+// slow pipe as the half conversions): slot and phase parity, advanced once per stage.
+struct RingPos {
+    uint32_t s = 0, ph = 0;
+    __device__ __forceinline__ void advance(uint32_t stages) {
+        if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+        }
+    }
+};
+
 // One row's share of a super-block: the 16-byte header (d, dmin, packed scales) and this thread's
 // 16 of the 32 quant bytes of each of the four 64-column groups.
 struct RowBlock {
@@ -251,12 +263,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
         if (lane == 0) {
             yule_pdl_wait();  // the activation tiles come from the kernel before this one
             uint32_t it = 0;
+            RingPos ring;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const uint32_t nt = tile % p.n_ntiles;
                 const unsigned char *src = reinterpret_cast<const unsigned char *>(p.xb) + (size_t)nt * bpr * T::kSuperBytes;
-                for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
-                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                for (uint32_t kb = 0; kb < n_kb; kb++, it++, ring.advance(p.stages)) {
+                    const uint32_t s = ring.s, ph = ring.ph;
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
@@ -284,12 +297,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             constexpr uint32_t x_lbo = BN * 16;  // bytes of one 8-column step of an activation slab
             uint32_t it = 0;
             bool ok = true;
+            RingPos ring;
             long long tw0 = 0, tw1 = 0, ti = 0, tc = 0;
             const long long tstart = p.prof ? clock64() : 0;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
+                for (uint32_t kb = 0; kb < n_kb; kb++, it++, ring.advance(p.stages)) {
                     const bool mine = (it & 1u) == parity_of_mine;  // the threads alternate stages
-                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    const uint32_t s = ring.s, ph = ring.ph;
                     const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
                     const long long c0 = p.prof ? clock64() : 0;
                     if (mine && !(p.skip & 16u) && !mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status)) {
@@ -377,14 +391,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
         bool ok = true;
         const uint32_t in_core = (r >> 3) * 128 + (r & 7u) * 16;
         const __half2 k1024 = __half2half2(__ushort_as_half(0x6400)), kneg1024 = __half2half2(__ushort_as_half(0xE400));
+        RingPos ring;
         long long pw = 0, pk = 0, pf = 0;
         const long long pstart = p.prof ? clock64() : 0;
         // the four stages of one super-block
         auto unpack_block = [&](const RowBlock &cur) {
             const ScalesMins sm = q4k_scales_mins(cur.hdr.y, cur.hdr.z, cur.hdr.w);
 #pragma unroll
-            for (uint32_t g = 0; g < 4; g++, it++) {
-                const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+            for (uint32_t g = 0; g < 4; g++, it++, ring.advance(p.stages)) {
+                const uint32_t s = ring.s, ph = ring.ph;
                 // scales of sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles) as fp16 pairs (sc, sc)
                 const uint32_t scw = g < 2 ? sm.sc_lo : sm.sc_hi, j0 = (2 * g) & 3u;
                 const __half2 sc0 = __hsub2(as_half2(biased_pair(scw, 0x4040u + j0 * 0x0101u)), k1024);
