@@ -363,7 +363,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
             "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": ({"workload": ("configs[4] Llama-3-70B-arch decode, all linears Q4_K" if args.workload == "c4" else
-                                     "configs[3] Llama-3-8B-arch, Q4_K linears, Q6_K output, prompt fed token by token") +
+                                     "configs[3] Llama-3-8B-arch, Q4_K linears, Q6_K output, prompt through the chunked GEMM prefill on one GPU") +
                                     f" (one layer's tensors repeated for the {cfg.n_layers} layers), fp32 KV, batch 1, "
                                     f"{N_PROMPT}-token prompt + {N_GEN} greedy tokens per step",
                         "parallelism": f"tp{world}: output rows of every linear sharded over {world} GPU(s), "
@@ -401,7 +401,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["c1", "c3", "c4"], default="c1",
                     help="c1: TinyLlama-arch decode, one replica per GPU (default).  c3: Llama-3-8B-arch, 2048-token "
-                         "prompt fed token by token + 256 tokens.  c4: Llama-3-70B-arch decode (512-token prompt + "
+                         "prompt + 256 tokens.  c4: Llama-3-70B-arch decode (512-token prompt + "
                          "256 tokens).  c3/c4 shard the output rows of every linear over the GPUs (tensor parallelism)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true",
