@@ -49,7 +49,9 @@ enum {
     YULE_ERR_OUT_OF_MEMORY = 6,
     YULE_ERR_DEVICE_STATUS = 7,    /* a bounded device-side wait gave up */
     YULE_ERR_CONTEXT_LENGTH = 8,   /* gpu_runner.rs:305-307 "context length exceeded" */
-    YULE_ERR_MISSING_TENSOR = 9
+    YULE_ERR_MISSING_TENSOR = 9,
+    YULE_ERR_PARSE = 10            /* a model file was rejected (yule-core/src/error.rs: InvalidMagic, UnsupportedVersion,
+                                      Parse, InvalidTensorShape, TensorOutOfBounds); the message names which */
 };
 
 /* GGUF type ids accepted where a dtype is asked for (dtype.rs:155-190). */
@@ -269,6 +271,51 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *runner, const uint32_
  * 1 K cache of `layer`, 2 V cache of `layer`, 3 logits. */
 int32_t yule_cuda_runner_buffer(yule_cuda_runner *runner, uint32_t which, uint32_t layer,
                                 yule_buffer *out_handle);
+
+/* ── GGUF v3 files (yule-core/src/gguf.rs:271-431, yule-infer/src/weight_loader.rs:19-38,
+ *    yule-infer/src/gpu_runner.rs:171-254) ─────────────────────────────────
+ * The reader needs no GPU.  It applies the reference's checks: magic, version 3
+ * only, at most 100 000 tensors and key-value pairs, strings up to 1 MiB, arrays
+ * up to 10 M elements, at most 8 dimensions, shape overflow, every tensor inside
+ * the file, no two tensors overlapping; the data section starts at the next
+ * multiple of general.alignment (32 when absent).  Any violation is
+ * YULE_ERR_PARSE with a message. */
+typedef struct yule_gguf yule_gguf;
+
+typedef struct yule_gguf_tensor_info {
+    const char *name;       /* owned by the yule_gguf */
+    uint32_t n_dims;
+    uint64_t shape[8];      /* GGUF order: shape[0] is the row length, shape[1] the row count */
+    uint32_t gguf_type;
+    uint64_t offset;        /* from the start of the data section */
+    uint64_t size_bytes;
+    const uint8_t *data;    /* the tensor's bytes inside the mapped (or caller-owned) file image */
+} yule_gguf_tensor_info;
+
+/* Maps the file read-only and parses it (GgufParser::parse_file). */
+int32_t yule_gguf_open(const char *path, yule_gguf **out);
+/* Parses an image the caller keeps alive until yule_gguf_close (GgufParser::parse_bytes). */
+int32_t yule_gguf_parse(const void *data, size_t size, yule_gguf **out);
+int32_t yule_gguf_close(yule_gguf *g);
+/* Any out pointer may be null. */
+int32_t yule_gguf_summary(const yule_gguf *g, uint32_t *version, uint64_t *n_tensors, uint64_t *n_kv,
+                          uint64_t *data_offset, uint64_t *alignment);
+int32_t yule_gguf_tensor(const yule_gguf *g, uint64_t index, yule_gguf_tensor_info *out);
+int32_t yule_gguf_find_tensor(const yule_gguf *g, const char *name, uint64_t *index);
+/* Metadata with the widening rules of GgufValue::as_u32 / as_f64 / as_str. */
+int32_t yule_gguf_meta_u32(const yule_gguf *g, const char *key, uint32_t *out);
+int32_t yule_gguf_meta_f64(const yule_gguf *g, const char *key, double *out);
+int32_t yule_gguf_meta_str(const yule_gguf *g, const char *key, const char **out);
+/* The runner configuration of the model in the file: GgufFile::to_loaded_model
+ * (gguf.rs:493-586) plus the derivations of GpuTransformerRunner::new
+ * (gpu_runner.rs:86-122).  max_seq_len = min(context_length, max_seq_len_cap)
+ * when the cap is non-zero.  Llama-family architectures only. */
+int32_t yule_gguf_runner_config(const yule_gguf *g, uint32_t max_seq_len_cap, yule_runner_config *cfg);
+/* Creates a runner and uploads every tensor it needs from the file image through
+ * pinned staging buffers and asynchronous copies (upload_weights,
+ * gpu_runner.rs:171-254).  The runner owns the device buffers. */
+int32_t yule_cuda_runner_load_gguf(yule_cuda_ctx *ctx, const yule_gguf *g, uint32_t max_seq_len_cap, uint32_t fused,
+                                   yule_cuda_runner **out_runner);
 
 #ifdef __cplusplus
 }

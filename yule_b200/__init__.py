@@ -7,3 +7,4 @@ mirror of Yule's ``ComputeBackend`` trait and ``ModelRunner`` for tests, benchma
 from .dtype import DType, matvec_bytes  # noqa: F401
 from .backend import BufferHandle, CudaB200Backend, YuleGpuError, is_available  # noqa: F401
 from .runner import CudaTransformerRunner, ModelConfig  # noqa: F401
+from .gguf import GgufFile, GgufTensor, load_runner  # noqa: F401

@@ -23,6 +23,12 @@ class RunnerConfig(C.Structure):
                 ("rope_freq_base", f32), ("fused", u32)]
 
 
+class GgufTensorInfo(C.Structure):
+    """``yule_gguf_tensor_info`` of include/yule_cuda.h."""
+    _fields_ = [("name", C.c_char_p), ("n_dims", u32), ("shape", u64 * 8), ("gguf_type", u32), ("offset", u64),
+                ("size_bytes", u64), ("data", vp)]
+
+
 # name → argtypes; every entry returns int32 status unless listed in _RESTYPES.
 _SIGNATURES = {
     "yule_cuda_is_available": [],
@@ -74,6 +80,17 @@ _SIGNATURES = {
     "yule_cuda_runner_position": [vp, C.POINTER(u32)],
     "yule_cuda_runner_generate_greedy": [vp, C.POINTER(u32), u32, u32, C.POINTER(u32)],
     "yule_cuda_runner_buffer": [vp, u32, u32, C.POINTER(u64)],
+    "yule_gguf_open": [C.c_char_p, C.POINTER(vp)],
+    "yule_gguf_parse": [vp, size_t, C.POINTER(vp)],
+    "yule_gguf_close": [vp],
+    "yule_gguf_summary": [vp, C.POINTER(u32), C.POINTER(u64), C.POINTER(u64), C.POINTER(u64), C.POINTER(u64)],
+    "yule_gguf_tensor": [vp, u64, C.POINTER(GgufTensorInfo)],
+    "yule_gguf_find_tensor": [vp, C.c_char_p, C.POINTER(u64)],
+    "yule_gguf_meta_u32": [vp, C.c_char_p, C.POINTER(u32)],
+    "yule_gguf_meta_f64": [vp, C.c_char_p, C.POINTER(C.c_double)],
+    "yule_gguf_meta_str": [vp, C.c_char_p, C.POINTER(C.c_char_p)],
+    "yule_gguf_runner_config": [vp, u32, C.POINTER(RunnerConfig)],
+    "yule_cuda_runner_load_gguf": [vp, vp, u32, u32, C.POINTER(vp)],
 }
 _RESTYPES = {"yule_cuda_last_error": C.c_char_p}
 

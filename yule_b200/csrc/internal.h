@@ -167,6 +167,8 @@ struct QGemm {
     bool pdl = false;
 };
 int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes);
+// Adds a buffer to the set the runner frees when it is destroyed (runner.cu).
+void runner_adopt_buffer(yule_cuda_runner *r, yule_buffer h);
 bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens);
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols);
 cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches);

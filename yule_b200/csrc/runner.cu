@@ -79,6 +79,10 @@ struct yule_cuda_runner {
     cudaGraphExec_t graph_exec = nullptr;
 };
 
+namespace yule {
+void runner_adopt_buffer(yule_cuda_runner *r, yule_buffer h) { r->owned.push_back(h); }
+}  // namespace yule
+
 namespace {
 
 int32_t alloc_f32(yule_cuda_runner *r, size_t n, float **out, yule_buffer *handle_out = nullptr) {

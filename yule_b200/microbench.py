@@ -72,8 +72,20 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--ring", action="store_true")
     ap.add_argument("--raw", action="store_true", help="do not call prepare_weights (raw GGUF layout only)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="the format x shape x batch grid of the matvec sweep (4 formats, 5 shapes, batch 1/4/16), "
+                         "weights streamed from HBM; prints one JSON line per case")
     args = ap.parse_args()
     backend = CudaB200Backend(0)
+    if args.sweep:
+        shapes = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]
+        for dt in (DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K):
+            for rows, cols in shapes:
+                for batch in (1, 4, 16):
+                    iters = 20 if rows * cols > 10 ** 8 else 100
+                    print(json.dumps(run(backend, dt, rows, cols, batch, iters, True, reps=3)), flush=True)
+        backend.close()
+        return
     print(json.dumps(run(backend, DType[args.dtype], args.rows, args.cols, args.batch, args.iters, args.ring,
                          prepare=not args.raw)))
     backend.close()
