@@ -11,14 +11,14 @@ from conftest import REL_TOL, guarded_rel_err
 pytestmark = pytest.mark.gpu
 
 
-def run(backend, w, x, n_rows, n_cols, batch, x_stride=None, out_stride=None):
+def run(backend, w, x, n_rows, n_cols, batch, x_stride=None, out_stride=None, dtype=DType.Q4_K):
     x_stride = x_stride or n_cols
     out_stride = out_stride or n_rows
     xs = np.zeros((batch, x_stride), np.float32)
     xs[:, :n_cols] = x.reshape(batch, n_cols)
     wh, xh = backend.upload(w), backend.upload(xs.reshape(-1))
     oh = backend.upload(np.full(batch * out_stride, 7.0, np.float32))
-    backend.quantized_matmul_batched(wh, xh, oh, n_rows, n_cols, DType.Q4_K, batch, x_stride, out_stride)
+    backend.quantized_matmul_batched(wh, xh, oh, n_rows, n_cols, dtype, batch, x_stride, out_stride)
     backend.synchronize()
     y = backend.download(oh, batch * out_stride).reshape(batch, out_stride)
     for h in (wh, xh, oh):
@@ -88,3 +88,21 @@ def test_gemm_equals_matvec_path(backend):
     y4 = np.concatenate([run(backend, w, x[:4 * n_cols], n_rows, n_cols, 4),
                          run(backend, w, x[4 * n_cols:], n_rows, n_cols, 4)])
     assert guarded_rel_err(y8.reshape(-1), y4.reshape(-1)) <= REL_TOL
+
+
+@pytest.mark.parametrize("dtype", [DType.Q6_K, DType.Q8_0, DType.Q4_0, DType.Q4_K])
+@pytest.mark.parametrize("n_rows,n_cols,batch", [(200, 512, 9), (513, 2048, 64), (1024, 1024, 200)])
+def test_generic_format_gemm(backend, oracle, monkeypatch, dtype, n_rows, n_cols, batch):
+    """Q6_K, Q8_0 and Q4_0 (and Q4_K when forced) go through the kernel whose producers dequantise with the
+    bit-exact per-element routine and split the weight into fp16 hi + lo."""
+    monkeypatch.setenv("YULE_GEMM_GENERIC", "1")
+    w = synth.random_blocks(dtype, 500 + n_rows, n_rows * (n_cols // dtype.block_size))
+    x = synth.normal(501 + batch, batch * n_cols)
+    y = run(backend, w, x, n_rows, n_cols, batch, dtype=dtype)
+    W = oracle.dequant(int(dtype), w).astype(np.float64).reshape(n_rows, n_cols)
+    X = x.astype(np.float64).reshape(batch, n_cols)
+    scale = np.sqrt((X ** 2).sum(1))[:, None] * np.sqrt((W ** 2).sum(1))[None, :]
+    assert (np.abs(y - X @ W.T) / scale).max() <= 4e-6
+    for b in range(0, batch, max(1, batch // 8)):
+        ref = oracle.qmv(int(dtype), w, x[b * n_cols:(b + 1) * n_cols], n_rows, n_cols)
+        assert guarded_rel_err(y[b], ref) <= REL_TOL

@@ -157,9 +157,12 @@ PREFILL_CFG = ModelConfig(dim=256, n_layers=3, n_heads=4, n_kv_heads=2, head_dim
                           max_seq_len=160)
 
 
-@pytest.mark.parametrize("chunk,n_prompt", [(None, 40), ("16", 45), ("8", 17), (None, 150)])
-def test_batched_prefill_matches_cpu_runner_and_token_path(backend, oracle, monkeypatch, chunk, n_prompt):
-    weights = synth.synthetic_model(PREFILL_CFG, seed=11, std=0.05, linear=DType.Q4_K)
+@pytest.mark.parametrize("chunk,n_prompt,mix", [(None, 40, "q4k"), ("16", 45, "q4k"), ("8", 17, "q4k"), (None, 150, "q4k"),
+                                                 (None, 40, "q4k_q6k"), ("16", 45, "q8_0"), (None, 33, "q4_0"), (None, 24, "q6k")])
+def test_batched_prefill_matches_cpu_runner_and_token_path(backend, oracle, monkeypatch, chunk, n_prompt, mix):
+    kw = {"q4k": dict(linear=DType.Q4_K), "q4k_q6k": dict(linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K),
+          "q8_0": dict(linear=DType.Q8_0), "q4_0": dict(linear=DType.Q4_0), "q6k": dict(linear=DType.Q6_K)}[mix]
+    weights = synth.synthetic_model(PREFILL_CFG, seed=11, std=0.05, **kw)
     ref = make_oracle_model(oracle, PREFILL_CFG, weights)
     prompt = synth.tokens(12, n_prompt, PREFILL_CFG.vocab_size)
     want = ref.prefill(prompt)

@@ -43,10 +43,12 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include "dequant_device.cuh"
 #include "internal.h"
 
 namespace yule {
@@ -59,10 +61,14 @@ constexpr int kLoaderWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kRawWarp = kEpi
               kFirstProdWarp = kEpiWarps + 4;
 constexpr int kGemmThreads = (kEpiWarps + 4 + kProdWarps) * 32;  // 640
 constexpr int kMaxStages = 6;
-constexpr int kRawSlots = 4;                       // super-blocks of raw Q4_K bytes in flight per CTA
+#ifndef YULE_GEMM_RAW_SLOTS
+#define YULE_GEMM_RAW_SLOTS 4
+#endif
+constexpr int kRawSlots = YULE_GEMM_RAW_SLOTS;                       // super-blocks of raw Q4_K bytes in flight per CTA
 constexpr uint32_t kRawBytes = kBM * 144;          // one super-block of 128 rows: 18 KB
 constexpr uint32_t kABytes = kBM * kBK * 2;  // the W slab of a stage: 16 KB
 constexpr float kSumScale = 1.0f / 32.0f;     // the sub-block sums of x are stored divided by 32
+constexpr float kGenericWScale = 1024.f;      // generic kernel: weights are scaled by 2^10 before the fp16 hi/lo split
 constexpr uint32_t kAmBytes = kBM * 16 * 2;  // the m slab of a super-block: 128 rows × 16 columns, 4 KB
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any real stall
 constexpr int kStatusGemmTimeout = 3;
@@ -79,6 +85,9 @@ struct GemmParams {
     uint32_t n_rows, n_cols, n_tokens, out_stride;
     uint32_t bn;           // activation rows per tile: 32, 64 or 128
     uint32_t n_mtiles, n_ntiles, stages;
+    uint32_t type;         // GGUF type id of the weights (generic kernel)
+    uint64_t w_row_bytes;  // bytes of one row of the weight tensor
+    float out_scale;       // generic kernel: 1 / kGenericWScale; exact kernel: 1
     uint32_t prof;         // timing aid: record cycle counters of CTA 0
     uint32_t skip;         // timing aid (YULE_GEMM_SKIP): 1 no unpacking, 2 no MMAs, 4 no draining; results meaningless
     int *status;
@@ -196,30 +205,35 @@ struct RowBlock {
     uint4 q[4];
 };
 
-template <int BN>
+// GENERIC = false: the Q4_K kernel with exact integer operands.  GENERIC = true: any block format;
+// the producers dequantise to fp32 exactly as the CPU code does and split the value, scaled by 2^10,
+// into fp16 hi + lo; three MMAs per 16 columns (W_hi·x_hi, W_hi·x_lo, W_lo·x_hi); no raw-block ring.
+template <int BN, bool GENERIC>
 struct Tile {
     static constexpr uint32_t NBUF = BN <= 64 ? 4 : 2;       // TMEM accumulator pairs in flight
     static constexpr uint32_t kTmemCols = NBUF * 2 * BN;     // 256 or 512: main + min accumulator each
     static constexpr uint32_t CW = BN / 2;                   // columns per drain warp
     static constexpr uint32_t kXHalfBytes = BN * kBK * 2;    // one fp16 term of the activation slab
     static constexpr uint32_t kBmBytes = BN * 16 * 2;        // sub-block sums of x: BN rows × (8 hi + 8 lo)
-    // stage: W | m | x_hi | x_lo | sums   (the last three arrive in one bulk copy)
-    static constexpr uint32_t kOffAm = kABytes, kOffX = kABytes + kAmBytes;
-    static constexpr uint32_t kStageBytes = kOffX + 2 * kXHalfBytes + kBmBytes;
+    // stage (exact):   W | m | x_hi | x_lo | sums   (the last three arrive in one bulk copy)
+    // stage (generic): W_hi | W_lo | x_hi | x_lo
+    static constexpr uint32_t kOffAm = kABytes, kOffX = GENERIC ? 2 * kABytes : kABytes + kAmBytes;
+    static constexpr uint32_t kStageBytes = kOffX + 2 * kXHalfBytes + (GENERIC ? 0u : kBmBytes);
+    static constexpr uint32_t kRawRingBytes = GENERIC ? 0u : kRawSlots * kRawBytes;
     // activation tiles in global memory, per (activation tile, super-block): four (hi, lo) slabs, then the sums
     static constexpr uint32_t kSuperBytes = 8 * kXHalfBytes + kBmBytes;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap w_map) {
-    using T = Tile<BN>;
+template <int BN, bool GENERIC>
+__global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap w_map) {
+    using T = Tile<BN, GENERIC>;
     constexpr uint32_t NBUF = T::NBUF, CW = T::CW, kXHalfBytes = T::kXHalfBytes, kStageBytes = T::kStageBytes;
     extern __shared__ __align__(128) unsigned char smem[];
     yule_pdl_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *tail = smem + (size_t)p.stages * kStageBytes;
     unsigned char *raw = tail;                               // kRawSlots boxes of raw Q4_K bytes
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tail + kRawSlots * kRawBytes);  // full[6] empty[6] acc_full[4] acc_empty[4] raw_full[4] raw_empty[4]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tail + T::kRawRingBytes);  // full[6] empty[6] acc_full[4] acc_empty[4] raw_full[4] raw_empty[4]
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kMaxStages;
     const uint32_t bar_acc_full = bar_empty + 8 * kMaxStages, bar_acc_empty = bar_acc_full + 32;
     const uint32_t bar_raw_full = bar_acc_empty + 32, bar_raw_empty = bar_raw_full + 8 * kRawSlots;
@@ -275,7 +289,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                         break;
                     }
                     const uint32_t g = kb & 3u;
-                    const uint32_t bytes = 2 * kXHalfBytes + (g == 3 ? T::kBmBytes : 0u);  // the sums ride with the last stage
+                    const uint32_t bytes = 2 * kXHalfBytes + ((!GENERIC && g == 3) ? T::kBmBytes : 0u);  // the sums ride with the last stage
                     const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes + T::kOffX);
                     if (p.skip & 8u) {
                         mbar_arrive(bar_full + 8 * s);
@@ -336,7 +350,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                     tw0 += c1 - c0;
                     tw1 += c2 - c1;
                     tc_fence_after();
-                    const uint32_t d_main = tmem_base + buf * 2 * BN, d_min = d_main + BN;
+                    const uint32_t d_main = tmem_base + buf * 2 * BN;
+                    [[maybe_unused]] const uint32_t d_min = d_main + BN;
                     const uint32_t a = smem_u32(smem + (size_t)s * kStageBytes);
                     const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
 #pragma unroll
@@ -345,8 +360,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                         const uint64_t da = smem_desc(a + k16 * 4096, 2048, 128);
                         umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // every stage starts a fresh accumulator
                         umma_f16(d_main, da, smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
+                        if (GENERIC)  // the lo term of the weights against the hi term of the activations
+                            umma_f16(d_main, smem_desc(a + kABytes + k16 * 4096, 2048, 128), smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
                     }
-                    if ((kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
+                    if (!GENERIC && (kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
                         umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(x_lo + kXHalfBytes, x_lbo, 128), idesc, 0u);
                     const long long c3 = p.prof ? clock64() : 0;
                     umma_commit(bar_empty + 8 * s);       // the slabs may be overwritten once these MMAs are done
@@ -366,7 +383,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             }
         }
     } else if (warp == kRawWarp) {
-        if (lane == 0) {
+        if (!GENERIC && lane == 0) {
             const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
             const uint32_t n_units = my_tiles * bpr;
             for (uint32_t u = 0; u < n_units; u++) {
@@ -385,6 +402,51 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
     } else if (warp >= kFirstProdWarp) {
         const uint32_t ptid = threadIdx.x - kFirstProdWarp * 32;  // 0..255
         const uint32_t r = ptid & 127u, hf = ptid >> 7;           // row of the tile, which 16 bytes of the 32
+        if (GENERIC) {
+            // Any block format: thread (r, hf) dequantises columns [32·hf, 32·hf + 32) of the stage for row r with
+            // the bit-exact per-element routine, scales by 2^10 and splits into fp16 hi + lo.
+            const uint32_t in_core = (r >> 3) * 128 + (r & 7u) * 16;
+            const uint64_t row_bytes = p.w_row_bytes;
+            uint32_t it = 0;
+            RingPos ring;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                uint32_t row = (tile / p.n_ntiles) * kBM + r;
+                const bool live = row < p.n_rows;
+                row = live ? row : p.n_rows - 1;
+                const uint8_t *rowp = p.w + (size_t)row * row_bytes;
+                for (uint32_t kb = 0; kb < n_kb && ok; kb++, it++, ring.advance(p.stages)) {
+                    if (!mbar_wait(bar_empty + 8 * ring.s, ring.ph ^ 1u, abort_flag, p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    unsigned char *a_hi = smem + (size_t)ring.s * kStageBytes, *a_lo = a_hi + kABytes;
+#pragma unroll 1
+                    for (uint32_t c8 = 0; c8 < 4; c8++) {
+                        const uint32_t col0 = kb * kBK + hf * 32 + c8 * 8;
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) v[i] = live ? dequant_elem(rowp, p.type, col0 + i) * kGenericWScale : 0.f;
+                        // positions 0..7 of the 16 bytes hold columns 0,2,1,3,4,6,5,7 (the order of the activation tiles)
+                        const float o[8] = {v[0], v[2], v[1], v[3], v[4], v[6], v[5], v[7]};
+                        uint32_t h[4], l[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const __half2 hh = __floats2half2_rn(o[2 * i], o[2 * i + 1]);
+                            const float2 back = __half22float2(hh);
+                            h[i] = as_u32(hh);
+                            l[i] = as_u32(__floats2half2_rn(o[2 * i] - back.x, o[2 * i + 1] - back.y));
+                        }
+                        const uint32_t kc = hf * 4 + c8;
+                        *reinterpret_cast<uint4 *>(a_hi + kc * 2048 + in_core) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4 *>(a_lo + kc * 2048 + in_core) = make_uint4(l[0], l[1], l[2], l[3]);
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * ring.s);
+                }
+            }
+        } else {
         const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t n_units = my_tiles * bpr;  // (tile, super-block) pairs of this CTA, in order
         uint32_t it = 0;
@@ -473,6 +535,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             g_gemm_prof[8] = pk;
             g_gemm_prof[9] = pf;
         }
+        }  // exact Q4_K producer
     } else {
         // drain warp: TMEM lanes [32·(warp % 4), +32) = rows of the tile, columns [CW·(warp / 4), +CW)
         yule_pdl_wait();
@@ -488,15 +551,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
             float acc[CW];
 #pragma unroll
             for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
-            uint32_t dd_cur = 0, dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp));  // (d, dmin) of super-block 0
+            uint32_t dd_cur = 0, dd_next = GENERIC ? 0u : __ldg(reinterpret_cast<const uint32_t *>(rowp));  // (d, dmin) of super-block 0
             for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
                 if (p.skip & 32u) break;
                 const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
-                if ((kb & 3u) == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
+                if (!GENERIC && (kb & 3u) == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
                     dd_cur = dd_next;
                     if (kb + 4 < n_kb) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)((kb >> 2) + 1) * 144));
                 }
-                const float2 dd = __half22float2(as_half2(dd_cur));
+                const float2 dd = GENERIC ? make_float2(1.f, 0.f) : __half22float2(as_half2(dd_cur));
                 const long long c0 = p.prof ? clock64() : 0;
                 if (!mbar_wait(bar_acc_full + 8 * buf, aph, abort_flag, p.status)) {
                     ok = false;
@@ -513,7 +576,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
 #pragma unroll
                     for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(dd.x, __uint_as_float(v[j]), acc[c0 + j]);
                 }
-                if ((kb & 3u) == 3u) {  // the stage that ends a super-block carries the min term
+                if (!GENERIC && (kb & 3u) == 3u) {  // the stage that ends a super-block carries the min term
 #pragma unroll
                     for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                         uint32_t v[16];
@@ -536,7 +599,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_q4k_tc_kernel(const Gem
                     const float sc = __shfl_sync(0xffffffffu, osc, j);
                     const uint32_t n = n0 + c0 + j;
                     if (row < p.n_rows && n < p.n_tokens) {
-                        float val = acc[c0 + j] * sc;
+                        float val = acc[c0 + j] * sc * p.out_scale;
                         const size_t o = (size_t)n * p.out_stride + row;
                         if (p.residual) val += p.residual[o];
                         p.out[o] = val;
@@ -718,8 +781,10 @@ uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 
 
 }  // namespace
 
+// Q4_K runs on the exact-integer kernel; Q6_K, Q8_0 and Q4_0 on the generic one (YULE_GEMM_GENERIC=1
+// sends Q4_K there too, for comparison).  The activation tiles are laid out per 256 columns.
 bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens) {
-    return type == YULE_DTYPE_Q4_K && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
+    return is_quantized(type) && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
 }
 
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols) {
@@ -774,17 +839,25 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.bn = bn;
     p.n_mtiles = (g.n_rows + kBM - 1) / kBM;
     p.n_ntiles = n_ntiles;
-    const uint32_t stage_bytes = kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
-    uint32_t stages = (uint32_t)((220u * 1024u - (kRawSlots * kRawBytes + 512u)) / stage_bytes);
+    const bool generic = g.type != YULE_DTYPE_Q4_K || (getenv("YULE_GEMM_GENERIC") && atoi(getenv("YULE_GEMM_GENERIC")));
+    const uint32_t stage_bytes = generic ? 2 * kABytes + 2 * bn * kBK * 2 : kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
+    const size_t raw_ring = generic ? 0 : (size_t)kRawSlots * kRawBytes;
+    uint32_t stages = (uint32_t)((220u * 1024u - (raw_ring + 512u)) / stage_bytes);
     p.stages = stages > (uint32_t)kMaxStages ? (uint32_t)kMaxStages : stages;
+    p.type = g.type;
+    p.w_row_bytes = (uint64_t)(g.n_cols / block_size(g.type)) * block_bytes(g.type);
+    p.out_scale = generic ? 1.0f / kGenericWScale : 1.0f;
     p.status = g.status;
     p.prof = getenv("YULE_GEMM_PROF") ? 1u : 0u;
     p.skip = getenv("YULE_GEMM_SKIP") ? (uint32_t)atoi(getenv("YULE_GEMM_SKIP")) : 0u;
-    const size_t tail_bytes = (size_t)kRawSlots * kRawBytes + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 16;
+    const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 16;
     const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
     CUtensorMap w_map;
-    e = encode_weight_map(g.w, g.n_rows, g.n_cols, &w_map);
-    if (e != cudaSuccess) return e;
+    memset(&w_map, 0, sizeof(w_map));
+    if (!generic) {
+        e = encode_weight_map(g.w, g.n_rows, g.n_cols, &w_map);
+        if (e != cudaSuccess) return e;
+    }
     uint32_t grid = p.n_mtiles * p.n_ntiles;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
     auto launch = [&](auto kern) {
@@ -792,7 +865,10 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
         if (e2 != cudaSuccess) return e2;
         return launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, s, g.pdl, p, w_map);
     };
-    e = bn == 32 ? launch(qgemm_q4k_tc_kernel<32>) : (bn == 64 ? launch(qgemm_q4k_tc_kernel<64>) : launch(qgemm_q4k_tc_kernel<128>));
+    if (generic)
+        e = bn == 32 ? launch(qgemm_tc_kernel<32, true>) : (bn == 64 ? launch(qgemm_tc_kernel<64, true>) : launch(qgemm_tc_kernel<128, true>));
+    else
+        e = bn == 32 ? launch(qgemm_tc_kernel<32, false>) : (bn == 64 ? launch(qgemm_tc_kernel<64, false>) : launch(qgemm_tc_kernel<128, false>));
     if (e != cudaSuccess) return e;
     *launches += 1;
     if (p.prof) {

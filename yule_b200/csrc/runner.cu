@@ -525,9 +525,9 @@ uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
     return c < r->cfg.max_seq_len ? c : r->cfg.max_seq_len;
 }
 
-// Single GPU, graph mode, grouped-query attention kernel available, every linear of every layer
-// Q4_K with a column count the GEMM takes, and a context short enough for the attention kernel's
-// score buffer at eight splits.
+// Single GPU, graph mode, grouped-query attention kernel available, every linear of every layer in a
+// block format with a column count the GEMM takes (multiples of 256), and a context short enough
+// for the attention kernel's score buffer at eight splits.
 bool prefill_batched_ok(const yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
     if (getenv("YULE_CUDA_BATCH_PREFILL") && atoi(getenv("YULE_CUDA_BATCH_PREFILL")) == 0) return false;
@@ -537,7 +537,7 @@ bool prefill_batched_ok(const yule_cuda_runner *r) {
         return false;
     for (const Layer &L : r->layers)
         for (const Tensor *t : {&L.attn_q, &L.attn_k, &L.attn_v, &L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down})
-            if (t->type != YULE_DTYPE_Q4_K) return false;
+            if (!is_quantized(t->type)) return false;
     const uint32_t splits = c.max_seq_len / 1024 < 1 ? 1 : (c.max_seq_len / 1024 > 8 ? 8 : c.max_seq_len / 1024);
     const size_t score_bytes = (size_t)(c.n_heads / c.n_kv_heads) * ((c.max_seq_len + splits - 1) / splits + 4) * 4;
     return score_bytes <= 96 * 1024;
@@ -592,7 +592,7 @@ int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n)
     auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, uint32_t m, float *out, const float *residual) {
         QGemm g;
         g.w = (const uint8_t *)t.buf.ptr;
-        g.type = YULE_DTYPE_Q4_K;
+        g.type = t.type;
         g.out = out;
         g.residual = residual;
         g.n_rows = rows;
