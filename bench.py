@@ -204,6 +204,26 @@ def matvec_ring_roofline(backend, peaks, peak_kind, iters: int = 1000) -> dict:
             "traffic": 6547456}
 
 
+def large_shape_rooflines(backend, peaks) -> dict:
+    """The same matvec kernels on shapes large enough to be bandwidth-bound (BASELINE configs[2]'s 128256x4096,
+    Q4_K and Q6_K, batch 1) and the tcgen05 GEMM on a prefill-sized problem: what the kernels do when launch
+    and dependency latency do not dominate.  Weights stream from HBM over a ring of copies."""
+    from yule_b200 import DType, microbench
+    out = {}
+    peak = float(peaks["hbm_gbs"])
+    for dt in (DType.Q4_K, DType.Q6_K):
+        r = microbench.run(backend, dt, 128256, 4096, 1, 20, True, reps=3)
+        out[f"{dt.name}_128256x4096_batch1"] = {"bound": "hbm", "achieved": r["gbs"], "peak": peak, "unit": "GB/s",
+                                                "frac": round(r["gbs"] / peak, 4), "us_per_launch": r["us_per_launch"]}
+    r = microbench.run(backend, DType.Q4_K, 4096, 14336, 512, 10, True, reps=3)
+    tpeak = float(peaks.get("bf16_tflops", 0) or 0)
+    out["Q4_K_gemm_4096x14336_x512"] = {"bound": "tensor", "achieved": r["tflops"], "peak": tpeak, "unit": "TFLOP/s",
+                                        "frac": round(r["tflops"] / tpeak, 4) if tpeak else None,
+                                        "us_per_launch": r["us_per_launch"],
+                                        "note": "useful FLOPs; the kernel issues two MMAs per product (fp16 hi/lo activations)"}
+    return out
+
+
 def cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s: float, max_tokens: int):
     """Decode tokens/s of the CPU runner restated in the oracle, all host threads, on a bounded sample:
     a 4-token prompt, then greedy decode steps until `budget_s` seconds or `max_tokens` tokens."""
@@ -349,6 +369,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         roof = matvec_ring_roofline(backend, peaks, peak_kind, iters=20 if args.small else 1000)
+        roof_large = None if (args.small or world > 1 or args.workload != "c1") else large_shape_rooflines(backend, peaks)
         mid_pos = N_PROMPT + N_GEN // 2
         bpt = decode_bytes_per_token(cfg, weights, mid_pos, tp_world=world if tp else 1)
         per_gpu_tok_s = N_GEN * args.steps / (decode_ms * 1e-3)
@@ -382,7 +403,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": 8 * N_GEN,
                     "d2h_bytes_per_step": 4 * cfg.vocab_size * N_GEN,
                     "path": "ModelRunner prefill/decode_step over the C ABI, host logits + host argmax"},
-            "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
+            "gpu_launches": int(launches), "roofline": roof, "roofline_large_shapes": roof_large, "cpu_baseline": cpu,
+            "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     runner.close()

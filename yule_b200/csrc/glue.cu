@@ -296,12 +296,22 @@ __global__ void argmax_kernel(const float *__restrict__ v, uint32_t n, uint32_t 
     float best = -FLT_MAX;
     uint32_t idx = 0;
     bool any = false;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        float x = v[i];
-        if (!any || x >= best) {
-            best = x;
-            idx = i;
-            any = true;
+    // eight loads in flight per thread (the logits sit in L2; one load at a time is all latency)
+    for (uint32_t base = threadIdx.x; base < n; base += blockDim.x * 8) {
+        float x[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const uint32_t i = base + k * blockDim.x;
+            x[k] = i < n ? v[i] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const uint32_t i = base + k * blockDim.x;
+            if (i < n && (!any || x[k] >= best)) {
+                best = x[k];
+                idx = i;
+                any = true;
+            }
         }
     }
     if (!any) best = -FLT_MAX;

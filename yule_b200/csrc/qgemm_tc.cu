@@ -87,6 +87,10 @@ struct GemmParams {
     uint32_t n_mtiles, n_ntiles, stages;
     uint32_t type;         // GGUF type id of the weights (generic kernel)
     uint64_t w_row_bytes;  // bytes of one row of the weight tensor
+    uint32_t unit_bytes;   // generic kernel: bytes of 256 columns of one row
+    uint32_t raw_stride;   // generic kernel: shared-memory row stride of the raw copy (an odd multiple of 16 bytes)
+    uint32_t raw_chunks;   // generic kernel: 16-byte chunks copied per row and unit
+    uint32_t raw_ring_bytes;  // generic kernel: two slots of 128 rows
     float out_scale;       // generic kernel: 1 / kGenericWScale; exact kernel: 1
     uint32_t prof;         // timing aid: record cycle counters of CTA 0
     uint32_t skip;         // timing aid (YULE_GEMM_SKIP): 1 no unpacking, 2 no MMAs, 4 no draining; results meaningless
@@ -186,6 +190,49 @@ __device__ __forceinline__ uint32_t biased_pair(uint32_t word, uint32_t selector
 __device__ __forceinline__ __half2 as_half2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
 __device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
 
+// Eight consecutive weights (columns col0 .. col0+7 of a 256-column unit, col0 a multiple of 8) from a
+// 2-byte-aligned copy of the unit's blocks, with the arithmetic of the per-element routines
+// (dequant_device.cuh): one header decode per call instead of one per weight.
+__device__ __forceinline__ void dequant8_unit(const unsigned char *unit, uint32_t type, uint32_t col0, float (&v)[8]) {
+    auto u16_at = [&](uint32_t byte_off) { return (uint32_t) * reinterpret_cast<const unsigned short *>(unit + byte_off); };
+    if (type == YULE_DTYPE_Q8_0) {
+        const uint32_t b = (col0 >> 5) * 34, i0 = col0 & 31u;
+        const float d = f16_bits_to_f32(u16_at(b));
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t w = u16_at(b + 2 + i0 + 2 * k);
+            v[2 * k] = __fmul_rn((float)(int)(signed char)(w & 0xFFu), d);
+            v[2 * k + 1] = __fmul_rn((float)(int)(signed char)(w >> 8), d);
+        }
+    } else if (type == YULE_DTYPE_Q4_0) {
+        const uint32_t b = (col0 >> 5) * 18, i0 = col0 & 31u;
+        const float d = f16_bits_to_f32(u16_at(b));
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const uint32_t w = u16_at(b + 2 + i0 / 2 + 2 * k);  // two bytes = four weights: low nibble first
+#pragma unroll
+            for (int q = 0; q < 4; q++) v[4 * k + q] = __fmul_rn(__fsub_rn((float)((w >> (4 * q)) & 0xFu), 8.0f), d);
+        }
+    } else if (type == YULE_DTYPE_Q6_K) {
+        const uint32_t h = col0 >> 7, r = col0 & 127u, g = r >> 5, l0 = r & 31u;
+        const float d = f16_bits_to_f32(u16_at(208));
+        const uint32_t scw = u16_at(192 + 8 * h + 2 * g);  // the two scales of this 32-column group
+        const float ds = __fmul_rn(d, (float)(int)(signed char)((l0 >> 4) ? (scw >> 8) : (scw & 0xFFu)));
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t ql = u16_at(64 * h + 32 * (g & 1u) + l0 + 2 * k) >> (4 * (g >> 1));
+            const uint32_t qh = u16_at(128 + 32 * h + l0 + 2 * k) >> (2 * g);
+            const int q0 = (int)((ql & 0xFu) | ((qh & 3u) << 4)) - 32;
+            const int q1 = (int)(((ql >> 8) & 0xFu) | (((qh >> 8) & 3u) << 4)) - 32;
+            v[2 * k] = __fmul_rn(ds, (float)q0);
+            v[2 * k + 1] = __fmul_rn(ds, (float)q1);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = dequant_elem(unit, type, col0 + i);
+    }
+}
+
 // Position in the stage ring without a runtime division (an integer division runs on the same
 // slow pipe as the half conversions): slot and phase parity, advanced once per stage.
 struct RingPos {
@@ -219,7 +266,7 @@ struct Tile {
     // stage (generic): W_hi | W_lo | x_hi | x_lo
     static constexpr uint32_t kOffAm = kABytes, kOffX = GENERIC ? 2 * kABytes : kABytes + kAmBytes;
     static constexpr uint32_t kStageBytes = kOffX + 2 * kXHalfBytes + (GENERIC ? 0u : kBmBytes);
-    static constexpr uint32_t kRawRingBytes = GENERIC ? 0u : kRawSlots * kRawBytes;
+    static constexpr uint32_t kRawRingBytes = GENERIC ? 0u : kRawSlots * kRawBytes;  // generic: sized at launch
     // activation tiles in global memory, per (activation tile, super-block): four (hi, lo) slabs, then the sums
     static constexpr uint32_t kSuperBytes = 8 * kXHalfBytes + kBmBytes;
 };
@@ -233,7 +280,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *tail = smem + (size_t)p.stages * kStageBytes;
     unsigned char *raw = tail;                               // kRawSlots boxes of raw Q4_K bytes
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tail + T::kRawRingBytes);  // full[6] empty[6] acc_full[4] acc_empty[4] raw_full[4] raw_empty[4]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tail + (GENERIC ? p.raw_ring_bytes : T::kRawRingBytes));  // full[6] empty[6] acc_full[4] acc_empty[4] raw_full[4] raw_empty[4]
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kMaxStages;
     const uint32_t bar_acc_full = bar_empty + 8 * kMaxStages, bar_acc_empty = bar_acc_full + 32;
     const uint32_t bar_raw_full = bar_acc_empty + 32, bar_raw_empty = bar_raw_full + 8 * kRawSlots;
@@ -403,19 +450,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         const uint32_t ptid = threadIdx.x - kFirstProdWarp * 32;  // 0..255
         const uint32_t r = ptid & 127u, hf = ptid >> 7;           // row of the tile, which 16 bytes of the 32
         if (GENERIC) {
-            // Any block format: thread (r, hf) dequantises columns [32·hf, 32·hf + 32) of the stage for row r with
-            // the bit-exact per-element routine, scales by 2^10 and splits into fp16 hi + lo.
+            // Any block format.  The eight producer warps copy a 256-column unit of the raw bytes of the tile's 128
+            // rows into one of two shared-memory slots with 16-byte cp.async from the aligned address at or below
+            // each row's unit start (the blocks themselves are only 2-byte aligned), always one unit ahead of the
+            // one being unpacked; thread (r, hf) then dequantises columns [32·hf, 32·hf + 32) of every stage for
+            // row r from that copy with the arithmetic of the bit-exact per-element routines, scales by 2^10 and
+            // splits into fp16 hi + lo.
             const uint32_t in_core = (r >> 3) * 128 + (r & 7u) * 16;
-            const uint64_t row_bytes = p.w_row_bytes;
-            uint32_t it = 0;
+            const uint32_t ub = p.unit_bytes, rstride = p.raw_stride, c16 = p.raw_chunks;
+            const uint32_t slot_bytes = kBM * rstride;
+            const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const uint32_t n_units = my_tiles * bpr;
+            auto unit_start = [&](uint32_t u, uint32_t tile_row) {  // address of row `tile_row`'s bytes of unit u
+                const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x, sb = u % bpr;
+                uint32_t grow = (tile / p.n_ntiles) * kBM + tile_row;
+                grow = grow < p.n_rows ? grow : p.n_rows - 1;
+                return reinterpret_cast<uintptr_t>(p.w) + (size_t)grow * p.w_row_bytes + (size_t)sb * ub;
+            };
+            auto copy_unit = [&](uint32_t u) {
+                if (u < n_units) {
+                    const uint32_t dst0 = smem_u32(raw + (size_t)(u & 1u) * slot_bytes);
+                    uint32_t row = 0, c = ptid;
+                    while (c >= c16) {
+                        c -= c16;
+                        row++;
+                    }
+                    for (uint32_t e = ptid; e < kBM * c16; e += 256) {
+                        const uintptr_t src = (unit_start(u, row) & ~(uintptr_t)15) + (size_t)c * 16;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + row * rstride + c * 16), "l"(src) : "memory");
+                        c += 256;
+                        while (c >= c16) {
+                            c -= c16;
+                            row++;
+                        }
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");  // one group per unit, empty past the end
+            };
             RingPos ring;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                uint32_t row = (tile / p.n_ntiles) * kBM + r;
-                const bool live = row < p.n_rows;
-                row = live ? row : p.n_rows - 1;
-                const uint8_t *rowp = p.w + (size_t)row * row_bytes;
-                for (uint32_t kb = 0; kb < n_kb && ok; kb++, it++, ring.advance(p.stages)) {
+            copy_unit(0);
+            for (uint32_t u = 0; u < n_units && ok; u++) {
+                copy_unit(u + 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of unit u have landed
+                asm volatile("bar.sync 2, 256;" ::: "memory");         // and everyone else's
+                const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x;
+                const bool live = (tile / p.n_ntiles) * kBM + r < p.n_rows;
+                const unsigned char *rawrow = raw + (size_t)(u & 1u) * slot_bytes + (size_t)r * rstride + (unit_start(u, r) & 15u);
+                for (uint32_t g = 0; g < 4 && ok; g++, ring.advance(p.stages)) {
                     if (!mbar_wait(bar_empty + 8 * ring.s, ring.ph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
@@ -423,10 +505,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     unsigned char *a_hi = smem + (size_t)ring.s * kStageBytes, *a_lo = a_hi + kABytes;
 #pragma unroll 1
                     for (uint32_t c8 = 0; c8 < 4; c8++) {
-                        const uint32_t col0 = kb * kBK + hf * 32 + c8 * 8;
+                        const uint32_t col0 = g * kBK + hf * 32 + c8 * 8;  // column inside the unit
                         float v[8];
+                        dequant8_unit(rawrow, p.type, col0, v);
 #pragma unroll
-                        for (int i = 0; i < 8; i++) v[i] = live ? dequant_elem(rowp, p.type, col0 + i) * kGenericWScale : 0.f;
+                        for (int i = 0; i < 8; i++) v[i] = live ? v[i] * kGenericWScale : 0.f;
                         // positions 0..7 of the 16 bytes hold columns 0,2,1,3,4,6,5,7 (the order of the activation tiles)
                         const float o[8] = {v[0], v[2], v[1], v[3], v[4], v[6], v[5], v[7]};
                         uint32_t h[4], l[4];
@@ -445,7 +528,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_full + 8 * ring.s);
                 }
+                asm volatile("bar.sync 2, 256;" ::: "memory");  // the slot may be overwritten by unit u + 2
             }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         } else {
         const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t n_units = my_tiles * bpr;  // (tile, super-block) pairs of this CTA, in order
@@ -841,8 +926,13 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.n_ntiles = n_ntiles;
     const bool generic = g.type != YULE_DTYPE_Q4_K || (getenv("YULE_GEMM_GENERIC") && atoi(getenv("YULE_GEMM_GENERIC")));
     const uint32_t stage_bytes = generic ? 2 * kABytes + 2 * bn * kBK * 2 : kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
-    const size_t raw_ring = generic ? 0 : (size_t)kRawSlots * kRawBytes;
+    p.unit_bytes = 256 / block_size(g.type) * block_bytes(g.type);
+    p.raw_chunks = (p.unit_bytes + 14 + 15) / 16;      // covers the unit from any 2-byte-aligned start
+    p.raw_stride = (p.raw_chunks | 1u) * 16;            // an odd multiple of 16 bytes
+    p.raw_ring_bytes = (2 * kBM * p.raw_stride + 127u) & ~127u;
+    const size_t raw_ring = generic ? p.raw_ring_bytes : (size_t)kRawSlots * kRawBytes;
     uint32_t stages = (uint32_t)((220u * 1024u - (raw_ring + 512u)) / stage_bytes);
+    if (stages < 2) return cudaErrorInvalidValue;
     p.stages = stages > (uint32_t)kMaxStages ? (uint32_t)kMaxStages : stages;
     p.type = g.type;
     p.w_row_bytes = (uint64_t)(g.n_cols / block_size(g.type)) * block_bytes(g.type);
@@ -850,7 +940,7 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.status = g.status;
     p.prof = getenv("YULE_GEMM_PROF") ? 1u : 0u;
     p.skip = getenv("YULE_GEMM_SKIP") ? (uint32_t)atoi(getenv("YULE_GEMM_SKIP")) : 0u;
-    const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 16;
+    const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 32;
     const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
     CUtensorMap w_map;
     memset(&w_map, 0, sizeof(w_map));
