@@ -34,6 +34,8 @@
 // Programmatic dependent launch: weights do not depend on the previous kernel, so their loads are
 // issued before `griddepcontrol.wait`; only the activation read waits.
 
+#include <cstdlib>
+
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -706,7 +708,12 @@ cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint
     // 16-row tiles use the whole MMA; 8-row tiles (half of each MMA idle) only when 16-row tiles
     // would leave warp groups without work.
     const uint32_t rows_for_grid = pair ? 2 * f.rows[0] : total_rows;
-    const int tile_rows = (rows_for_grid / 16 >= (uint32_t)kGroups * (uint32_t)sm_count) ? 16 : 8;
+    // Tile height.  16-row tiles use the whole MMA and half the instructions per byte of 8-row tiles; they win
+    // as soon as they keep about 60 % of the warp groups busy (measured: 4096 rows, 256 tiles for 296 groups,
+    // 10-25 % faster with 16; 2048 rows, 128 tiles, faster with 8).  YULE_QMV_ROWS forces one (timing aid).
+    const uint32_t n_groups = (uint32_t)kGroups * (uint32_t)sm_count;
+    int tile_rows = ((rows_for_grid / 16) * 10 >= n_groups * 6) ? 16 : 8;
+    if (const char *force = getenv("YULE_QMV_ROWS")) tile_rows = atoi(force) == 8 ? 8 : (atoi(force) == 16 ? 16 : tile_rows);
     uint32_t n_tiles = 0;
     for (uint32_t i = 0; i < f.n_seg; i++) {
         p.w[i] = f.w[i];

@@ -20,6 +20,8 @@
 // Lane (g, t): rows g and g+8; t = (h, u) owns l ∈ [16u, 16u+16) of half h, i.e. columns
 // 128h + 32j + 16u + [0,16) for j = 0..3: 16 bytes of ql for j ∈ {0,2}, 16 for j ∈ {1,3}, 16 of qh.
 
+#include <cstdlib>
+
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -508,7 +510,12 @@ bool q6k_mma_supported(uint32_t n_cols) { return n_cols % 256 == 0 && smem_bytes
 cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches) {
     if (f.n_rows == 0) return cudaSuccess;
     Q6kMmaParams p = {};
-    const int tile_rows = (f.n_rows / 16 >= (uint32_t)kGroups * (uint32_t)sm_count) ? 16 : 8;
+    // Tile height.  16-row tiles use the whole MMA and half the instructions per byte of 8-row tiles; they win
+    // as soon as they keep about 60 % of the warp groups busy (measured: 4096 rows, 256 tiles for 296 groups,
+    // 10-25 % faster with 16; 2048 rows, 128 tiles, faster with 8).  YULE_QMV_ROWS forces one (timing aid).
+    const uint32_t n_groups = (uint32_t)kGroups * (uint32_t)sm_count;
+    int tile_rows = ((f.n_rows / 16) * 10 >= n_groups * 6) ? 16 : 8;
+    if (const char *force = getenv("YULE_QMV_ROWS")) tile_rows = atoi(force) == 8 ? 8 : (atoi(force) == 16 ? 16 : tile_rows);
     p.planar = f.planar;
     p.n_blocks = (uint64_t)f.n_rows * (f.n_cols / 256);
     p.out = f.out;
