@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE configs[1]): TinyLlama-1.1B-architecture decode — 22 layers, hidden 2048, 32 query /
+Workload (BASELINE.json configs[1]): TinyLlama-1.1B-architecture decode — 22 layers, hidden 2048, 32 query /
 4 KV heads (head_dim 64), SwiGLU FFN 5632, vocab 32000; random-init N(0, 0.02) weights quantised to
 Q4_K (output and ffn_down Q6_K), fp32 KV cache, batch 1, 32-token random prompt, 128 greedy tokens.
 One *step* is one such job.  The metric is decode tokens per second (the 128 generated tokens; the
@@ -13,7 +13,7 @@ prompt pass is timed separately).
 `e2e`    — the same job through the reference-facing ModelRunner calls (prefill / decode_step) with
            host buffers: every step uploads the token and position and downloads the vocab-sized logits, and the
            argmax runs on the host.
-`roofline` — the Q4_K dequant-matvec kernel at the TinyLlama FFN-up shape (BASELINE configs[0]:
+`roofline` — the Q4_K dequant-matvec kernel at the TinyLlama FFN-up shape (BASELINE.json configs[0]:
            5632x2048, 1000 launches) over a ring of weight copies larger than L2, replayed from a
            CUDA graph and timed with CUDA events; achieved = algorithmic bytes per launch / average
            launch duration, peak = measured copy bandwidth of this pool's B200s.
@@ -113,7 +113,7 @@ def host_argmax_last(logits: np.ndarray) -> int:
 
 
 def build_model_70b(rank: int, world: int, which: str = "c4"):
-    """BASELINE configs[4]: Llama-3-70B architecture, every linear Q4_K (~39 GB), row-sharded over `world` ranks;
+    """BASELINE.json configs[4]: Llama-3-70B architecture, every linear Q4_K (~39 GB), row-sharded over `world` ranks;
     configs[3]: Llama-3-8B architecture, Q4_K linears with a Q6_K output matrix.
     To bound host time the quantised N(0, 0.02) tensors of one layer are generated once and uploaded for all
     the layers (distinct device buffers, so HBM traffic is that of different layers)."""
@@ -205,7 +205,7 @@ def matvec_ring_roofline(backend, peaks, peak_kind, iters: int = 1000) -> dict:
 
 
 def large_shape_rooflines(backend, peaks) -> dict:
-    """The same matvec kernels on shapes large enough to be bandwidth-bound (BASELINE configs[2]'s 128256x4096,
+    """The same matvec kernels on shapes large enough to be bandwidth-bound (BASELINE.json configs[2]'s 128256x4096,
     Q4_K and Q6_K, batch 1) and the tcgen05 GEMM on a prefill-sized problem: what the kernels do when launch
     and dependency latency do not dominate.  Weights stream from HBM over a ring of copies."""
     from yule_b200 import DType, microbench

@@ -134,7 +134,7 @@ def test_missing_tensor_is_reported(backend):
 
 
 def test_tinyllama_config_greedy_identical(backend, oracle):
-    """BASELINE configs[1]: TinyLlama-1.1B architecture, Q4_K linears, Q6_K output and ffn_down, fp32 KV,
+    """BASELINE.json configs[1]: TinyLlama-1.1B architecture, Q4_K linears, Q6_K output and ffn_down, fp32 KV,
     32-token random prompt, 128 greedy tokens — the stream must equal the CPU runner's."""
     cfg = synth.TINYLLAMA
     weights = synth.synthetic_model(cfg, seed=2024, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)

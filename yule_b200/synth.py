@@ -18,7 +18,7 @@ from .runner import ModelConfig
 _u8p = C.POINTER(C.c_uint8)
 _f32p = C.POINTER(C.c_float)
 
-# BASELINE configs: Llama-architecture shapes only; weights are random.
+# Shapes of the configs in BASELINE.json: Llama-architecture shapes only; weights are random.
 TINYLLAMA = ModelConfig(dim=2048, n_layers=22, n_heads=32, n_kv_heads=4, head_dim=64, vocab_size=32000,
                         ff_dim=5632, max_seq_len=4096, norm_eps=1e-5, rope_freq_base=10000.0)
 LLAMA3_8B = ModelConfig(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, head_dim=128, vocab_size=128256,
