@@ -22,7 +22,8 @@ from yule_b200 import CudaB200Backend, CudaTransformerRunner, DType, ModelConfig
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=rank, world_size=world)
 cfg = ModelConfig(dim=512, n_layers=3, n_heads=8, n_kv_heads=4, head_dim=64, vocab_size=1024, ff_dim=1536, max_seq_len=64)
-weights = synth.synthetic_model(cfg, seed=3, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
+mix = dict(ffn_down=DType.Q6_K, output=DType.Q6_K) if os.environ["MIX"] == "q4k_q6k" else {}
+weights = synth.synthetic_model(cfg, seed=3, std=0.05, linear=DType.Q4_K, **mix)
 b = CudaB200Backend(rank)
 ids = [CudaB200Backend.tp_unique_id() if rank == 0 else None]
 dist.broadcast_object_list(ids, src=0)
@@ -47,15 +48,18 @@ def _gpu_count() -> int:
         return 0
 
 
-@pytest.mark.parametrize("collective", ["peer_exchange", "nccl"])
-def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path, collective):
-    """Both forms of the all-gather: stores into the peers' mapped buffers with epoch flags (default), and
-    NCCL's all-gather (YULE_TP_NCCL=1)."""
+@pytest.mark.parametrize("collective,mix", [("peer_exchange", "q4k_q6k"), ("nccl", "q4k_q6k"), ("peer_exchange", "q4k"),
+                                            ("peer_exchange_unfolded", "q4k")])
+def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path, collective, mix):
+    """Every form of the all-gather: stores into the peers' mapped buffers with epoch flags, either from a
+    separate exchange kernel or folded into the Q4_K matvecs on both sides (the default where producer and
+    consumer are that kernel: the all-Q4_K model), and NCCL's all-gather (YULE_TP_NCCL=1)."""
     if _gpu_count() < 2:
         pytest.skip("needs two GPUs")
     from yule_b200 import CudaTransformerRunner, DType, ModelConfig, synth
     cfg = ModelConfig(dim=512, n_layers=3, n_heads=8, n_kv_heads=4, head_dim=64, vocab_size=1024, ff_dim=1536, max_seq_len=64)
-    weights = synth.synthetic_model(cfg, seed=3, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
+    kw = dict(ffn_down=DType.Q6_K, output=DType.Q6_K) if mix == "q4k_q6k" else {}
+    weights = synth.synthetic_model(cfg, seed=3, std=0.05, linear=DType.Q4_K, **kw)
     prompt = synth.tokens(5, 7, cfg.vocab_size)
     single = CudaTransformerRunner(backend, cfg, weights, fused=True)
     want_logits = single.prefill(prompt)
@@ -71,7 +75,8 @@ def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path, collecti
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", PORT=str(port), OUT=str(tmp_path), YULE_ROOT=ROOT,
-                   NCCL_NVLS_ENABLE="0", YULE_TP_NCCL="1" if collective == "nccl" else "0")
+                   NCCL_NVLS_ENABLE="0", YULE_TP_NCCL="1" if collective == "nccl" else "0", MIX=mix,
+                   YULE_TP_FUSE="0" if collective == "peer_exchange_unfolded" else "1")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env))
     for p in procs:
         assert p.wait(timeout=600) == 0

@@ -134,6 +134,26 @@ inline size_t tensor_bytes(uint32_t t, uint64_t n_rows, uint64_t n_cols) {
 // ── kernel launchers (raw device pointers; arguments already validated) ──────────────────────
 // Each returns the cudaError_t of the launch and adds the kernels it launched to *launches.
 
+// Tensor parallelism folded into a matvec (set-up in tp.cu).  Producer side: the kernel also stores
+// its output rows into every peer's copy of the gathered buffer; its last CTA publishes an epoch
+// number in the peers' flag words.  Consumer side: a kernel that reads a gathered vector first waits
+// — for a bounded time, reporting through `status` — until its own flag words show that epoch from
+// every peer.  One exchange = one (slot, epoch) pair; epoch = *tick · epochs_per_tick + index + 1.
+struct TpFuse {
+    uint32_t world = 1, rank = 0;
+    const uint32_t *tick = nullptr;
+    uint32_t epochs_per_tick = 0;
+    int *status = nullptr;
+    bool push = false;               // producer
+    uint32_t push_index = 0;
+    float *peer_out[8] = {};         // peer p's address of this rank's slice (null for this rank)
+    uint32_t *peer_flag[8] = {};     // peer p's flag word for (slot, this rank)
+    uint32_t *counter = nullptr;     // ticket of the CTAs of this launch (zero between launches)
+    bool wait = false;               // consumer
+    uint32_t wait_index = 0;
+    const uint32_t *my_flag[8] = {}; // this rank's flag word for (slot, peer p)
+};
+
 struct QmvArgs {
     const uint8_t *w;   // raw GGUF blocks, row-major
     const float *x;     // [batch][x_stride]
@@ -147,6 +167,7 @@ struct QmvArgs {
     float eps = 0.f;
     const void *next_w[2] = {nullptr, nullptr};  // tensor-pipe paths: weights to prefetch into L2
     uint64_t next_bytes[2] = {0, 0};
+    TpFuse tp;                        // Q4_K tensor-pipe path only
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
 
@@ -193,6 +214,7 @@ struct Q4kFused {
     bool pdl = false;                 // programmatic dependent launch
     const void *next_w[2] = {nullptr, nullptr};  // weights of the kernel(s) that follow: prefetched into L2
     uint64_t next_bytes[2] = {0, 0};
+    TpFuse tp;                        // pushes out[0] to the peers / waits for a gathered x
 };
 bool q4k_mma_supported(uint32_t n_cols, uint32_t batch);
 cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches);
@@ -224,6 +246,12 @@ void tp_destroy(yule_cuda_ctx *ctx);
 // Peer-memory exchange: the same all-gather as stores into every peer's mapped buffer plus epoch flags.
 int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base);
 bool tp_has_exchange(const yule_cuda_ctx *ctx);
+// Fill the producer / consumer half of a TpFuse for the exchange (slot, index) of the buffer slice at
+// buf_offset_floats + rank·per_rank inside the exchange region.
+void tp_fuse_push(const yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot, const uint32_t *tick,
+                  uint32_t epochs_per_tick, uint32_t index, TpFuse *f);
+void tp_fuse_wait(const yule_cuda_ctx *ctx, uint32_t slot, const uint32_t *tick, uint32_t epochs_per_tick, uint32_t index,
+                  TpFuse *f);
 cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot,
                         const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches);
 

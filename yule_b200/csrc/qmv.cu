@@ -433,6 +433,7 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             f.norm_w = a.norm_w;
             f.eps = a.eps;
             f.pdl = a.pdl;
+            f.tp = a.tp;
             for (int i = 0; i < 2; i++) {
                 f.next_w[i] = a.next_w[i];
                 f.next_bytes[i] = a.next_bytes[i];

@@ -453,6 +453,35 @@ __device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR],
     }
 }
 
+// Kept out of line: the tensor-parallel paths must not cost the single-GPU kernels registers.
+__device__ __noinline__ void tp_push_value(const TpFuse &tp, size_t o, float v) {
+    for (uint32_t pp = 0; pp < tp.world; pp++)
+        if (tp.peer_out[pp]) tp.peer_out[pp][o] = v;
+}
+__device__ __noinline__ void tp_wait_flags(const TpFuse &tp) {
+    if (threadIdx.x < tp.world && threadIdx.x != tp.rank) {
+        const uint32_t epoch = *tp.tick * tp.epochs_per_tick + tp.wait_index + 1u;
+        const volatile uint32_t *f = tp.my_flag[threadIdx.x];
+        const long long t0 = clock64();
+        while ((int32_t)(*f - epoch) < 0) {
+            if (clock64() - t0 > 4000000000LL) {  // ~2 s: a lost peer becomes a status word, not a hung GPU
+                atomicExch(tp.status, 2);
+                break;
+            }
+        }
+    }
+    __threadfence();
+}
+__device__ __noinline__ void tp_publish(const TpFuse &tp) {
+    if (threadIdx.x == 0 && atomicAdd(tp.counter, 1u) == gridDim.x - 1) {
+        *tp.counter = 0;
+        __threadfence_system();
+        const uint32_t epoch = *tp.tick * tp.epochs_per_tick + tp.push_index + 1u;
+        for (uint32_t pp = 0; pp < tp.world; pp++)
+            if (tp.peer_flag[pp]) *reinterpret_cast<volatile uint32_t *>(tp.peer_flag[pp]) = epoch;
+    }
+}
+
 struct Q4kMmaParams {
     const uint8_t *w[3];    // segment weight tensors (raw Q4_K blocks)
     float *out[3];          // segment outputs, [batch][out_stride[s]]
@@ -469,6 +498,7 @@ struct Q4kMmaParams {
     const float *residual;  // added to segment 0's output, or null (same layout as out[0])
     const void *next_w[2];  // weights of the following kernel(s), prefetched into L2
     uint64_t next_bytes[2];
+    TpFuse tp;              // tensor parallelism: push out[0] to the peers / wait for the gathered x
 };
 
 __device__ __forceinline__ void group_barrier(int group) {
@@ -523,7 +553,7 @@ struct UnitCursor {
 // the same rows of up.  The activations are staged once per CTA.
 template <int ROWS, int DEPTH, bool SUBCOL>
 __global__ void __launch_bounds__(kThreadsCta, 1)
-qmv_q4k_mma_kernel(const Q4kMmaParams p) {
+qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     constexpr int NR = ROWS / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     yule_pdl_launch_dependents();
@@ -565,6 +595,12 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
     yule_prefetch_l2_slice(p.next_w[0], p.next_bytes[0]);
     yule_prefetch_l2_slice(p.next_w[1], p.next_bytes[1]);
     yule_pdl_wait();
+    if (p.tp.wait) {
+        // x was gathered by stores from the peers: wait for their flags of that exchange (bounded), before the
+        // first load of x (nothing of x is in this SM's L1 yet, and the flags are read past it)
+        tp_wait_flags(p.tp);
+        __syncthreads();
+    }
     stage_activations(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps);
     // B column n = g: vector n/2, part n%2.  Lanes whose vector does not exist read vector 0;
     // their output columns are never looked at.
@@ -615,11 +651,12 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
             const size_t o = (size_t)v * p.out_stride[seg] + row;
             if (p.pair) {
                 // silu_mul.cu: x / (1 + exp(−x)) * up
-                p.out[0][o] = (sums[0] / (1.0f + expf(-sums[0]))) * sums[1];
-            } else {
-                if (seg == 0 && p.residual) sums[0] += p.residual[o];
-                p.out[seg][o] = sums[0];
+                sums[0] = (sums[0] / (1.0f + expf(-sums[0]))) * sums[1];
+            } else if (seg == 0 && p.residual) {
+                sums[0] += p.residual[o];
             }
+            p.out[seg][o] = sums[0];
+            if (p.tp.push && seg == 0) tp_push_value(p.tp, o, sums[0]);  // the same row into every peer's copy
         }
         group_barrier(group);
     };
@@ -628,8 +665,7 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
         // more warps than super-blocks per row: this warp only helps with the reductions
         for (uint32_t k0 = 0; k0 < my_tiles; k0 += tiles_per_round)
             finish_round(k0, (my_tiles - k0) < tiles_per_round ? (my_tiles - k0) : tiles_per_round);
-        return;
-    }
+    } else {
 
     float acc[NR][2];
 #pragma unroll
@@ -670,6 +706,14 @@ qmv_q4k_mma_kernel(const Q4kMmaParams p) {
                 }
             }
         }
+    }
+    }  // nbw != 0
+
+    if (p.tp.push) {
+        // every CTA's remote stores are fenced before it takes a ticket; the last one publishes the epoch
+        __threadfence_system();
+        __syncthreads();
+        tp_publish(p.tp);
     }
 }
 
@@ -733,6 +777,7 @@ cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint
     p.norm_w = f.norm_w;
     p.eps = f.eps;
     p.residual = f.residual;
+    p.tp = f.tp;
     for (int i = 0; i < 2; i++) {
         p.next_w[i] = f.next_w[i];
         p.next_bytes[i] = f.next_bytes[i];

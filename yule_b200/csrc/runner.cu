@@ -182,8 +182,9 @@ struct Step {
     }
     // norm_w set: RMSNorm of x folded into the matvec (only valid when fusable(w, cols) holds)
     void qmv(const Tensor &w, const float *x, float *out, uint32_t rows, uint32_t cols, const float *residual = nullptr,
-             const float *norm_w = nullptr) {
+             const float *norm_w = nullptr, const TpFuse *tp = nullptr) {
         QmvArgs a;
+        if (tp) a.tp = *tp;
         a.w = (const uint8_t *)w.buf.ptr;
         a.x = x;
         a.out = out;
@@ -296,10 +297,44 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             if (t->type != YULE_DTYPE_Q4_K) return false;
         return q4k_mma_supported(cols, 1);
     };
+    // Tensor parallelism folded into the Q4_K matvecs: when both the kernel that produces a gathered vector
+    // and the one that consumes it are the Q4_K tensor-pipe kernel, the producer stores its rows straight into
+    // the peers' buffers and the consumer waits for the peers' flags: no separate exchange launch.
+    // YULE_TP_FUSE=0 keeps the separate exchange kernel everywhere.
+    const bool tp_fuse = N > 1 && r->xchg && !skip_gather && !(getenv("YULE_TP_FUSE") && atoi(getenv("YULE_TP_FUSE")) == 0);
+    auto is_q4k_mma = [&](const Tensor &t, uint32_t cols) { return t.type == YULE_DTYPE_Q4_K && q4k_mma_supported(cols, 1); };
+    auto epoch_index = [&](uint32_t layer, uint32_t k) { return k == 4 ? 4 * c.n_layers : 4 * layer + k; };
+    auto push_of = [&](size_t x_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
+        TpFuse f;
+        tp_fuse_push(r->ctx, x_off, per_rank, k, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
+        return f;
+    };
+    auto add_wait = [&](TpFuse &f, uint32_t layer, uint32_t k) {
+        tp_fuse_wait(r->ctx, k, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
+    };
+    // which gathers are folded: 1 after o-proj (consumer gate/up), 2 after gate/up (consumer down),
+    // 3 after down (consumer: next layer's Q/K/V, or the output matrix after the last layer)
+    auto folded = [&](uint32_t layer, uint32_t k) {
+        if (!tp_fuse) return false;
+        const Layer &L = r->layers[layer];
+        const Tensor &ow = r->output.set ? r->output : r->token_embd;
+        if (k == 1) return is_q4k_mma(L.attn_output, qdim) && all_q4k({&L.ffn_gate, &L.ffn_up}, dim);
+        if (k == 2) return all_q4k({&L.ffn_gate, &L.ffn_up}, dim) && is_q4k_mma(L.ffn_down, ff);
+        if (k == 3) {
+            if (!is_q4k_mma(L.ffn_down, ff)) return false;
+            if (layer + 1 < c.n_layers) {
+                const Layer &Nx = r->layers[layer + 1];
+                return all_q4k({&Nx.attn_q, &Nx.attn_k, &Nx.attn_v}, dim);
+            }
+            return all_q4k({&ow}, dim);
+        }
+        return false;
+    };
     // x → (optional RMSNorm) → up to three Q4_K matrices in one launch
     auto fused = [&](std::initializer_list<std::pair<const Tensor *, std::pair<float *, uint32_t>>> segs, const float *x,
-                     uint32_t cols, const float *norm_w, const float *residual, bool pair) {
+                     uint32_t cols, const float *norm_w, const float *residual, bool pair, const TpFuse *tp = nullptr) {
         Q4kFused f;
+        if (tp) f.tp = *tp;
         uint32_t i = 0;
         for (auto &sg : segs) {
             f.w[i] = (const uint8_t *)sg.first->buf.ptr;
@@ -334,8 +369,10 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.then(&L.attn_output);  // while Q/K/V and attention run, o-proj's weights come in
         if (skip & 1) {
         } else if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
+            TpFuse tq;
+            if (l > 0 && folded(l - 1, 3)) add_wait(tq, l - 1, 3);
             fused({{&L.attn_q, {r->q, qdim_l}}, {&L.attn_k, {r->k_tmp, kvdim_l}}, {&L.attn_v, {r->v_tmp, kvdim_l}}},
-                  r->hidden, dim, L.attn_norm_f32, nullptr, false);
+                  r->hidden, dim, L.attn_norm_f32, nullptr, false, &tq);
         } else {
             st.ok(launch_rms_norm(r->hidden, L.attn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
             st.qmv(L.attn_q, r->normed, r->q, qdim_l, dim);
@@ -379,33 +416,47 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         float *hidden_l = r->hidden + (size_t)R * dim_l;
         // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
         st.then(&L.ffn_gate, &L.ffn_up);
-        if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l);
-        gather(r->hidden, r->x_hidden, dim_l, l, 1);
+        {
+            TpFuse to;
+            if (folded(l, 1)) to = push_of(r->x_hidden, dim_l, l, 1);
+            if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l, nullptr, &to);
+        }
+        if (!folded(l, 1)) gather(r->hidden, r->x_hidden, dim_l, l, 1);
         st.then(&L.ffn_down);
         if (skip & 16) {
         } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
+            TpFuse tg;
+            if (folded(l, 2)) tg = push_of(r->x_gate, ff_l, l, 2);
+            if (folded(l, 1)) add_wait(tg, l, 1);
             fused({{&L.ffn_gate, {r->gate + (size_t)R * ff_l, ff_l}}, {&L.ffn_up, {r->up, ff_l}}}, r->hidden, dim,
-                  L.ffn_norm_f32, nullptr, true);
+                  L.ffn_norm_f32, nullptr, true, &tg);
         } else {
             st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
             st.qmv(L.ffn_gate, r->normed, r->gate + (size_t)R * ff_l, ff_l, dim);
             st.qmv(L.ffn_up, r->normed, r->up, ff_l, dim);
             st.ok(launch_silu_mul(r->gate + (size_t)R * ff_l, r->up, r->gate + (size_t)R * ff_l, ff_l, s, &st.n, pdl));
         }
-        gather(r->gate, r->x_gate, ff_l, l, 2);
+        if (!folded(l, 2)) gather(r->gate, r->x_gate, ff_l, l, 2);
         // during down-proj: the next layer's Q and K/V (or the output matrix after the last layer)
         if (l + 1 < c.n_layers)
             st.then(&r->layers[l + 1].attn_q, &r->layers[l + 1].attn_k);
         else
             st.then(&out_w_);
-        if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l);
-        gather(r->hidden, r->x_hidden, dim_l, l, 3);
+        {
+            TpFuse td;
+            if (folded(l, 3)) td = push_of(r->x_hidden, dim_l, l, 3);
+            if (folded(l, 2)) add_wait(td, l, 2);
+            if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l, nullptr, &td);
+        }
+        if (!folded(l, 3)) gather(r->hidden, r->x_hidden, dim_l, l, 3);
     }
     st.then(nullptr);
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     if (skip & 64) {
     } else if (all_q4k({&out_w}, dim)) {
-        fused({{&out_w, {r->logits + (size_t)R * vocab_l, vocab_l}}}, r->hidden, dim, r->output_norm_f32, nullptr, false);
+        TpFuse tw;
+        if (c.n_layers && folded(c.n_layers - 1, 3)) add_wait(tw, c.n_layers - 1, 3);
+        fused({{&out_w, {r->logits + (size_t)R * vocab_l, vocab_l}}}, r->hidden, dim, r->output_norm_f32, nullptr, false, &tw);
     } else if (out_w.type == YULE_DTYPE_Q6_K && out_w.buf.planar && q6k_mma_supported(dim)) {
         st.qmv(out_w, r->hidden, r->logits + (size_t)R * vocab_l, vocab_l, dim, nullptr, r->output_norm_f32);
     } else {
