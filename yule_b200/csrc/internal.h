@@ -134,11 +134,13 @@ inline size_t tensor_bytes(uint32_t t, uint64_t n_rows, uint64_t n_cols) {
 // ── kernel launchers (raw device pointers; arguments already validated) ──────────────────────
 // Each returns the cudaError_t of the launch and adds the kernels it launched to *launches.
 
-// Tensor parallelism folded into a matvec (set-up in tp.cu).  Producer side: the kernel also stores
-// its output rows into every peer's copy of the gathered buffer; its last CTA publishes an epoch
-// number in the peers' flag words.  Consumer side: a kernel that reads a gathered vector first waits
-// — for a bounded time, reporting through `status` — until its own flag words show that epoch from
-// every peer.  One exchange = one (slot, epoch) pair; epoch = *tick · epochs_per_tick + index + 1.
+// Tensor parallelism folded into a matvec (set-up in tp.cu), flag-in-data form.  A gathered vector has, next
+// to its plain copy, a copy of (value, epoch) pairs in every rank's exchange region.  Producer side: as each
+// output row is reduced the kernel stores the pair, one 8-byte store, into every rank's pair buffer (its own
+// included).  Consumer side: the kernel that reads the gathered vector reads the pairs and polls — for a
+// bounded time, reporting through `status` — until every pair it needs carries the epoch of that exchange.
+// No fence, no flag word, no ticket: an exchange costs one NVLink store latency.
+// epoch = *tick · epochs_per_tick + index + 1 (never 0: the buffers start zeroed).
 struct TpFuse {
     uint32_t world = 1, rank = 0;
     const uint32_t *tick = nullptr;
@@ -146,12 +148,10 @@ struct TpFuse {
     int *status = nullptr;
     bool push = false;               // producer
     uint32_t push_index = 0;
-    float *peer_out[8] = {};         // peer p's address of this rank's slice (null for this rank)
-    uint32_t *peer_flag[8] = {};     // peer p's flag word for (slot, this rank)
-    uint32_t *counter = nullptr;     // ticket of the CTAs of this launch (zero between launches)
+    uint2 *pair_out[8] = {};         // rank p's pair buffer at this rank's slice (every rank, this one too)
     bool wait = false;               // consumer
     uint32_t wait_index = 0;
-    const uint32_t *my_flag[8] = {}; // this rank's flag word for (slot, peer p)
+    const uint2 *pair_in = nullptr;  // this rank's pair buffer of the whole gathered vector
 };
 
 struct QmvArgs {
@@ -246,12 +246,13 @@ void tp_destroy(yule_cuda_ctx *ctx);
 // Peer-memory exchange: the same all-gather as stores into every peer's mapped buffer plus epoch flags.
 int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base);
 bool tp_has_exchange(const yule_cuda_ctx *ctx);
-// Fill the producer / consumer half of a TpFuse for the exchange (slot, index) of the buffer slice at
-// buf_offset_floats + rank·per_rank inside the exchange region.
-void tp_fuse_push(const yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot, const uint32_t *tick,
+// Fill the producer / consumer half of a TpFuse for exchange `index` of a gathered vector whose pair buffer
+// starts at pair_offset_floats inside the exchange region (2 floats per element, rank r's slice at element
+// r·per_rank).
+void tp_fuse_push(const yule_cuda_ctx *ctx, size_t pair_offset_floats, uint32_t per_rank, const uint32_t *tick,
                   uint32_t epochs_per_tick, uint32_t index, TpFuse *f);
-void tp_fuse_wait(const yule_cuda_ctx *ctx, uint32_t slot, const uint32_t *tick, uint32_t epochs_per_tick, uint32_t index,
-                  TpFuse *f);
+void tp_fuse_wait(const yule_cuda_ctx *ctx, size_t pair_offset_floats, const uint32_t *tick, uint32_t epochs_per_tick,
+                  uint32_t index, TpFuse *f);
 cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot,
                         const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches);
 

@@ -202,6 +202,42 @@ size_t smem_bytes(uint32_t n_cols, uint32_t nb) {
 
 constexpr int kThreadsCta = kGroups * kWarps * 32;  // 512
 
+// Kept out of line: the tensor-parallel path must not cost the single-GPU kernels registers.
+__device__ __noinline__ void tp_push_value(const TpFuse &tp, size_t o, float v) {
+    const uint2 pair = make_uint2(__float_as_uint(v), *tp.tick * tp.epochs_per_tick + tp.push_index + 1u);
+    for (uint32_t pp = 0; pp < tp.world; pp++)  // one 8-byte store each
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(tp.pair_out[pp] + o), "r"(pair.x), "r"(pair.y) : "memory");
+}
+// Eight consecutive elements of a gathered vector from its (value, epoch) pairs: polls until all eight
+// carry `epoch` (bounded: a lost peer becomes a status word, not a hung GPU).
+__device__ __forceinline__ void tp_load8(const uint2 *pairs, uint32_t epoch, int *status, float (&a)[8]) {
+    long long t0 = 0;
+    for (uint32_t it = 0;; it++) {
+        uint4 q[4];
+        // one 16-byte load per two pairs: value and epoch of a pair must come from the same access
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w)
+                         : "l"(pairs + 2 * i)
+                         : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < 4; i++) ok = ok && q[i].y == epoch && q[i].w == epoch;
+        if (!ok) {
+            if (it == 0) t0 = clock64();
+            if ((it & 63u) != 63u || clock64() - t0 < 4000000000LL) continue;
+            atomicExch(status, 2);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            a[2 * i] = __uint_as_float(q[i].x);
+            a[2 * i + 1] = __uint_as_float(q[i].z);
+        }
+        return;
+    }
+}
+
 // Stage NB activation vectors: optional RMSNorm, power-of-two normalisation, hi/lo split,
 // fragment order, per-32-column sums.  Each thread owns groups of 8 consecutive columns; the first
 // kCache groups (16 K columns per CTA) stay in registers between the reduction pass and the
@@ -210,7 +246,8 @@ constexpr int kCache = 4;
 
 __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const float *__restrict__ x, uint32_t x_stride,
                                                   uint32_t n_cols, uint32_t nb, const float *__restrict__ norm_w,
-                                                  float eps) {
+                                                  float eps, const uint2 *pairs = nullptr, uint32_t pair_epoch = 0,
+                                                  int *status = nullptr) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     constexpr int NW = kThreadsCta / 32;
     if (threadIdx.x < 64) sm.zb[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
@@ -219,6 +256,10 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
         float cache[kCache][8];
         float ss = 0.f, mx = 0.f;
         auto load8 = [&](uint32_t c, float (&a)[8]) {
+            if (pairs) {  // tensor parallelism: the vector arrives as (value, epoch) pairs stored by all ranks
+                tp_load8(pairs + c, pair_epoch, status, a);
+                return;
+            }
             *reinterpret_cast<float4 *>(a) = *reinterpret_cast<const float4 *>(xv + c);
             *reinterpret_cast<float4 *>(a + 4) = *reinterpret_cast<const float4 *>(xv + c + 4);
         };
@@ -453,35 +494,6 @@ __device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR],
     }
 }
 
-// Kept out of line: the tensor-parallel paths must not cost the single-GPU kernels registers.
-__device__ __noinline__ void tp_push_value(const TpFuse &tp, size_t o, float v) {
-    for (uint32_t pp = 0; pp < tp.world; pp++)
-        if (tp.peer_out[pp]) tp.peer_out[pp][o] = v;
-}
-__device__ __noinline__ void tp_wait_flags(const TpFuse &tp) {
-    if (threadIdx.x < tp.world && threadIdx.x != tp.rank) {
-        const uint32_t epoch = *tp.tick * tp.epochs_per_tick + tp.wait_index + 1u;
-        const volatile uint32_t *f = tp.my_flag[threadIdx.x];
-        const long long t0 = clock64();
-        while ((int32_t)(*f - epoch) < 0) {
-            if (clock64() - t0 > 4000000000LL) {  // ~2 s: a lost peer becomes a status word, not a hung GPU
-                atomicExch(tp.status, 2);
-                break;
-            }
-        }
-    }
-    __threadfence();
-}
-__device__ __noinline__ void tp_publish(const TpFuse &tp) {
-    if (threadIdx.x == 0 && atomicAdd(tp.counter, 1u) == gridDim.x - 1) {
-        *tp.counter = 0;
-        __threadfence_system();
-        const uint32_t epoch = *tp.tick * tp.epochs_per_tick + tp.push_index + 1u;
-        for (uint32_t pp = 0; pp < tp.world; pp++)
-            if (tp.peer_flag[pp]) *reinterpret_cast<volatile uint32_t *>(tp.peer_flag[pp]) = epoch;
-    }
-}
-
 struct Q4kMmaParams {
     const uint8_t *w[3];    // segment weight tensors (raw Q4_K blocks)
     float *out[3];          // segment outputs, [batch][out_stride[s]]
@@ -595,13 +607,9 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     yule_prefetch_l2_slice(p.next_w[0], p.next_bytes[0]);
     yule_prefetch_l2_slice(p.next_w[1], p.next_bytes[1]);
     yule_pdl_wait();
-    if (p.tp.wait) {
-        // x was gathered by stores from the peers: wait for their flags of that exchange (bounded), before the
-        // first load of x (nothing of x is in this SM's L1 yet, and the flags are read past it)
-        tp_wait_flags(p.tp);
-        __syncthreads();
-    }
-    stage_activations(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps);
+    // tensor parallelism: x may arrive as (value, epoch) pairs stored by all ranks
+    stage_activations(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps, p.tp.wait ? p.tp.pair_in : nullptr,
+                      p.tp.wait ? *p.tp.tick * p.tp.epochs_per_tick + p.tp.wait_index + 1u : 0u, p.tp.status);
     // B column n = g: vector n/2, part n%2.  Lanes whose vector does not exist read vector 0;
     // their output columns are never looked at.
     const uint32_t vec = (uint32_t)(g >> 1) < p.batch ? (g >> 1) : 0;
@@ -709,12 +717,6 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     }
     }  // nbw != 0
 
-    if (p.tp.push) {
-        // every CTA's remote stores are fenced before it takes a ticket; the last one publishes the epoch
-        __threadfence_system();
-        __syncthreads();
-        tp_publish(p.tp);
-    }
 }
 
 template <int ROWS, int DEPTH, bool SUBCOL>

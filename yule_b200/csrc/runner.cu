@@ -59,6 +59,7 @@ struct yule_cuda_runner {
     // the exchange region
     bool xchg = false;
     size_t x_attn_out = 0, x_hidden = 0, x_gate = 0, x_logits = 0;
+    size_t x_pair_hidden = 0, x_pair_gate = 0;  // (value, epoch) pair copies of hidden and gate (2 floats per element)
     uint32_t *d_state = nullptr;    // [0] token, [1] position, [2] tokens processed since creation
     uint32_t *d_history = nullptr;  // greedy pick made after each position
     uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
@@ -298,19 +299,19 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         return q4k_mma_supported(cols, 1);
     };
     // Tensor parallelism folded into the Q4_K matvecs: when both the kernel that produces a gathered vector
-    // and the one that consumes it are the Q4_K tensor-pipe kernel, the producer stores its rows straight into
-    // the peers' buffers and the consumer waits for the peers' flags: no separate exchange launch.
-    // YULE_TP_FUSE=0 keeps the separate exchange kernel everywhere.
+    // and the one that consumes it are the Q4_K tensor-pipe kernel, the producer stores (value, epoch) pairs
+    // straight into every rank's pair buffer as its rows are reduced and the consumer polls the pairs while it
+    // stages x: no exchange launch, no fence, no flag.  YULE_TP_FUSE=0 keeps the exchange kernel everywhere.
     const bool tp_fuse = N > 1 && r->xchg && !skip_gather && !(getenv("YULE_TP_FUSE") && atoi(getenv("YULE_TP_FUSE")) == 0);
     auto is_q4k_mma = [&](const Tensor &t, uint32_t cols) { return t.type == YULE_DTYPE_Q4_K && q4k_mma_supported(cols, 1); };
     auto epoch_index = [&](uint32_t layer, uint32_t k) { return k == 4 ? 4 * c.n_layers : 4 * layer + k; };
-    auto push_of = [&](size_t x_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
+    auto push_of = [&](size_t pair_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
         TpFuse f;
-        tp_fuse_push(r->ctx, x_off, per_rank, k, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
+        tp_fuse_push(r->ctx, pair_off, per_rank, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
         return f;
     };
-    auto add_wait = [&](TpFuse &f, uint32_t layer, uint32_t k) {
-        tp_fuse_wait(r->ctx, k, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
+    auto add_wait = [&](TpFuse &f, size_t pair_off, uint32_t layer, uint32_t k) {
+        tp_fuse_wait(r->ctx, pair_off, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
     };
     // which gathers are folded: 1 after o-proj (consumer gate/up), 2 after gate/up (consumer down),
     // 3 after down (consumer: next layer's Q/K/V, or the output matrix after the last layer)
@@ -370,7 +371,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         if (skip & 1) {
         } else if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
             TpFuse tq;
-            if (l > 0 && folded(l - 1, 3)) add_wait(tq, l - 1, 3);
+            if (l > 0 && folded(l - 1, 3)) add_wait(tq, r->x_pair_hidden, l - 1, 3);
             fused({{&L.attn_q, {r->q, qdim_l}}, {&L.attn_k, {r->k_tmp, kvdim_l}}, {&L.attn_v, {r->v_tmp, kvdim_l}}},
                   r->hidden, dim, L.attn_norm_f32, nullptr, false, &tq);
         } else {
@@ -418,7 +419,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.then(&L.ffn_gate, &L.ffn_up);
         {
             TpFuse to;
-            if (folded(l, 1)) to = push_of(r->x_hidden, dim_l, l, 1);
+            if (folded(l, 1)) to = push_of(r->x_pair_hidden, dim_l, l, 1);
             if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l, nullptr, &to);
         }
         if (!folded(l, 1)) gather(r->hidden, r->x_hidden, dim_l, l, 1);
@@ -426,8 +427,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         if (skip & 16) {
         } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
             TpFuse tg;
-            if (folded(l, 2)) tg = push_of(r->x_gate, ff_l, l, 2);
-            if (folded(l, 1)) add_wait(tg, l, 1);
+            if (folded(l, 2)) tg = push_of(r->x_pair_gate, ff_l, l, 2);
+            if (folded(l, 1)) add_wait(tg, r->x_pair_hidden, l, 1);
             fused({{&L.ffn_gate, {r->gate + (size_t)R * ff_l, ff_l}}, {&L.ffn_up, {r->up, ff_l}}}, r->hidden, dim,
                   L.ffn_norm_f32, nullptr, true, &tg);
         } else {
@@ -444,8 +445,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.then(&out_w_);
         {
             TpFuse td;
-            if (folded(l, 3)) td = push_of(r->x_hidden, dim_l, l, 3);
-            if (folded(l, 2)) add_wait(td, l, 2);
+            if (folded(l, 3)) td = push_of(r->x_pair_hidden, dim_l, l, 3);
+            if (folded(l, 2)) add_wait(td, r->x_pair_gate, l, 2);
             if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l, nullptr, &td);
         }
         if (!folded(l, 3)) gather(r->hidden, r->x_hidden, dim_l, l, 3);
@@ -455,7 +456,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     if (skip & 64) {
     } else if (all_q4k({&out_w}, dim)) {
         TpFuse tw;
-        if (c.n_layers && folded(c.n_layers - 1, 3)) add_wait(tw, c.n_layers - 1, 3);
+        if (c.n_layers && folded(c.n_layers - 1, 3)) add_wait(tw, r->x_pair_hidden, c.n_layers - 1, 3);
         fused({{&out_w, {r->logits + (size_t)R * vocab_l, vocab_l}}}, r->hidden, dim, r->output_norm_f32, nullptr, false, &tw);
     } else if (out_w.type == YULE_DTYPE_Q6_K && out_w.buf.planar && q6k_mma_supported(dim)) {
         st.qmv(out_w, r->hidden, r->logits + (size_t)R * vocab_l, vocab_l, dim, nullptr, r->output_norm_f32);
@@ -792,8 +793,10 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         r->x_hidden = r->x_attn_out + qdim;
         r->x_gate = r->x_hidden + c.dim;
         r->x_logits = r->x_gate + c.ff_dim;
+        r->x_pair_hidden = (r->x_logits + c.vocab_size + 3) & ~(size_t)3;  // 16-byte aligned
+        r->x_pair_gate = r->x_pair_hidden + 2 * (size_t)c.dim;
         float *base = nullptr;
-        rc = tp_setup_exchange(ctx, r->x_logits + c.vocab_size, &base);
+        rc = tp_setup_exchange(ctx, r->x_pair_gate + 2 * (size_t)c.ff_dim, &base);
         if (rc == YULE_OK) {
             r->xchg = true;
             r->attn_out = base + r->x_attn_out;

@@ -189,7 +189,7 @@ int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base)
     return YULE_OK;
 }
 
-void tp_fuse_push(const yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot, const uint32_t *tick,
+void tp_fuse_push(const yule_cuda_ctx *ctx, size_t pair_offset_floats, uint32_t per_rank, const uint32_t *tick,
                   uint32_t epochs_per_tick, uint32_t index, TpFuse *f) {
     f->world = ctx->tp_world;
     f->rank = ctx->tp_rank;
@@ -198,18 +198,14 @@ void tp_fuse_push(const yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t p
     f->status = ctx->device_status;
     f->push = true;
     f->push_index = index;
-    for (uint32_t p = 0; p < (uint32_t)kMaxRanks; p++) {
-        const bool peer = p < ctx->tp_world && p != ctx->tp_rank;
-        f->peer_out[p] = peer ? ctx->tp_peer_base[p] + buf_offset_floats + (size_t)ctx->tp_rank * per_rank : nullptr;
-        f->peer_flag[p] = peer ? reinterpret_cast<uint32_t *>(ctx->tp_peer_base[p] + ctx->tp_flag_offset) + slot * kMaxRanks + ctx->tp_rank
-                               : nullptr;
-    }
-    // one ticket word per slot, behind the flag words and the exchange kernel's own counter
-    f->counter = reinterpret_cast<uint32_t *>(ctx->tp_peer_base[ctx->tp_rank] + ctx->tp_flag_offset) + kFlagSlots * kMaxRanks + 1 + slot;
+    for (uint32_t p = 0; p < (uint32_t)kMaxRanks; p++)
+        f->pair_out[p] = p < ctx->tp_world
+                             ? reinterpret_cast<uint2 *>(ctx->tp_peer_base[p] + pair_offset_floats) + (size_t)ctx->tp_rank * per_rank
+                             : nullptr;
 }
 
-void tp_fuse_wait(const yule_cuda_ctx *ctx, uint32_t slot, const uint32_t *tick, uint32_t epochs_per_tick, uint32_t index,
-                  TpFuse *f) {
+void tp_fuse_wait(const yule_cuda_ctx *ctx, size_t pair_offset_floats, const uint32_t *tick, uint32_t epochs_per_tick,
+                  uint32_t index, TpFuse *f) {
     f->world = ctx->tp_world;
     f->rank = ctx->tp_rank;
     f->tick = tick;
@@ -217,10 +213,7 @@ void tp_fuse_wait(const yule_cuda_ctx *ctx, uint32_t slot, const uint32_t *tick,
     f->status = ctx->device_status;
     f->wait = true;
     f->wait_index = index;
-    for (uint32_t p = 0; p < (uint32_t)kMaxRanks; p++)
-        f->my_flag[p] = (p < ctx->tp_world && p != ctx->tp_rank)
-                            ? reinterpret_cast<const uint32_t *>(ctx->tp_peer_base[ctx->tp_rank] + ctx->tp_flag_offset) + slot * kMaxRanks + p
-                            : nullptr;
+    f->pair_in = reinterpret_cast<const uint2 *>(ctx->tp_peer_base[ctx->tp_rank] + pair_offset_floats);
 }
 
 bool tp_has_exchange(const yule_cuda_ctx *ctx) { return ctx->tp_world > 1 && ctx->tp_peer_base[ctx->tp_rank] != nullptr; }
