@@ -51,6 +51,7 @@ struct AttnParams {
     uint32_t *tickets;                   // [n_heads], zero between launches
     uint32_t hd, n_heads, n_kv_heads, kv_stride, n_splits, max_chunk, min_chunk;
     uint32_t q_stride, out_stride;       // floats between the q / out rows of consecutive queries (blockIdx.z)
+    TpFuse tp;                           // tensor parallelism: the output also goes out as (value, epoch) pairs
 };
 
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
@@ -228,8 +229,16 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
 // CTA of a KV head (ticket) merges the splits of its GROUP heads.
 constexpr int kGqaMaxSplits = 64;
 
+// Tensor parallelism: element o of this rank's slice of the attention output as a (value, epoch) pair into
+// every rank's pair buffer, one 8-byte store each (the reader polls the pairs; see TpFuse).
+__device__ __noinline__ void tp_push_value(const TpFuse &tp, size_t o, float v) {
+    const uint32_t epoch = *tp.tick * tp.epochs_per_tick + tp.push_index + 1u;
+    for (uint32_t pp = 0; pp < tp.world; pp++)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(tp.pair_out[pp] + o), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+}
+
 template <int GROUP, int HD>
-__global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_constant__ AttnParams p) {
     constexpr int J = HD / 32;                               // 16-byte steps per lane and row
     constexpr int GH = (GROUP * J > 16) ? (16 / J) : GROUP;  // query heads scored per pass over K
     constexpr int HD4 = HD / 4;
@@ -441,7 +450,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
 #pragma unroll
         for (int k = 0; k < NOUT; k++) {
             const uint32_t idx = threadIdx.x + k * kThreads;
-            if (idx < GROUP * HD) out_z[(size_t)head0 * HD + idx] = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
+            if (idx < GROUP * HD) {
+                const float val = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
+                out_z[(size_t)head0 * HD + idx] = val;
+                if (p.tp.push) tp_push_value(p.tp, (size_t)head0 * HD + idx, val);
+            }
         }
         return;
     }
@@ -542,7 +555,15 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const AttnPar
             O.w += v.w;
         }
         const float inv = 1.0f / ml[2 * (vi / HD4) + 1];
-        reinterpret_cast<float4 *>(out_z + (size_t)head0 * HD)[vi] = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+        const float4 res = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+        reinterpret_cast<float4 *>(out_z + (size_t)head0 * HD)[vi] = res;
+        if (p.tp.push) {
+            const size_t o0 = (size_t)head0 * HD + 4 * (size_t)vi;
+            tp_push_value(p.tp, o0, res.x);
+            tp_push_value(p.tp, o0 + 1, res.y);
+            tp_push_value(p.tp, o0 + 2, res.z);
+            tp_push_value(p.tp, o0 + 3, res.w);
+        }
     }
     if (threadIdx.x == 0) tickets_z[kvh] = 0;  // ready for the next launch on this stream
 }
@@ -621,6 +642,7 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
         *launches += 1;
         p.q_stride = a.q_stride;
         p.out_stride = a.out_stride;
+        p.tp = a.tp;
         if (a.n_tokens > 1 && (a.k_new || a.pos_ptr)) return cudaErrorInvalidValue;  // batched queries read the caches only
 #define YULE_GQA_CASE(G, H) if (g == G && a.hd == H) return launch_gqa_variant<G, H>(p, smem, a.pdl, s, a.n_tokens)
         YULE_GQA_CASE(1, 64); YULE_GQA_CASE(2, 64); YULE_GQA_CASE(4, 64); YULE_GQA_CASE(8, 64);

@@ -334,6 +334,7 @@ struct AttnDecode {
     // Prefill: n_tokens > 1 runs one query per blockIdx.z; query z sits at position seq_len - 1 + z,
     // its q and out rows are q_stride / out_stride floats apart (grouped-query kernel, not fused).
     uint32_t n_tokens = 1, q_stride = 0, out_stride = 0;
+    TpFuse tp;               // grouped-query kernel: tensor parallelism, output pushed as (value, epoch) pairs
     bool gqa = false;        // grouped-query kernel: one CTA per (KV head, split); n_splits from attn_gqa_pick_splits
 };
 bool attn_gqa_supported(uint32_t hd, uint32_t n_heads, uint32_t n_kv_heads);

@@ -59,7 +59,7 @@ struct yule_cuda_runner {
     // the exchange region
     bool xchg = false;
     size_t x_attn_out = 0, x_hidden = 0, x_gate = 0, x_logits = 0;
-    size_t x_pair_hidden = 0, x_pair_gate = 0;  // (value, epoch) pair copies of hidden and gate (2 floats per element)
+    size_t x_pair_hidden = 0, x_pair_gate = 0, x_pair_attn = 0;  // (value, epoch) pair copies (2 floats per element)
     uint32_t *d_state = nullptr;    // [0] token, [1] position, [2] tokens processed since creation
     uint32_t *d_history = nullptr;  // greedy pick made after each position
     uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
@@ -313,12 +313,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     auto add_wait = [&](TpFuse &f, size_t pair_off, uint32_t layer, uint32_t k) {
         tp_fuse_wait(r->ctx, pair_off, r->d_state + 2, epochs_per_token, epoch_index(layer, k), &f);
     };
-    // which gathers are folded: 1 after o-proj (consumer gate/up), 2 after gate/up (consumer down),
+    // which gathers are folded: 0 after attention (grouped-query kernel, consumer o-proj),
+    // 1 after o-proj (consumer gate/up), 2 after gate/up (consumer down),
     // 3 after down (consumer: next layer's Q/K/V, or the output matrix after the last layer)
     auto folded = [&](uint32_t layer, uint32_t k) {
         if (!tp_fuse) return false;
         const Layer &L = r->layers[layer];
         const Tensor &ow = r->output.set ? r->output : r->token_embd;
+        if (k == 0) return r->attn_gqa && attn_decode_supported(hd) && is_q4k_mma(L.attn_output, qdim);
         if (k == 1) return is_q4k_mma(L.attn_output, qdim) && all_q4k({&L.ffn_gate, &L.ffn_up}, dim);
         if (k == 2) return all_q4k({&L.ffn_gate, &L.ffn_up}, dim) && is_q4k_mma(L.ffn_down, ff);
         if (k == 3) {
@@ -404,6 +406,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             a.max_seq_len = c.max_seq_len;
             a.min_chunk = getenv("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_ATTN_MIN_CHUNK")) : 32;
             a.pdl = pdl;
+            if (folded(l, 0)) a.tp = push_of(r->x_pair_attn, qdim_l, l, 0);
             if (!(skip & 4)) st.ok(launch_attn_decode(a, s, &st.n));
         } else {
             if (!(skip & 2))
@@ -413,13 +416,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
                 st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, attn_out_l, hd, 0, pos_ptr, c.max_seq_len,
                                                  heads_l, kvh_l, kvdim_l, s, &st.n, pdl));
         }
-        gather(r->attn_out, r->x_attn_out, qdim_l, l, 0);
+        if (!folded(l, 0)) gather(r->attn_out, r->x_attn_out, qdim_l, l, 0);
         float *hidden_l = r->hidden + (size_t)R * dim_l;
         // hidden = hidden + W_o · attn_out (the Add dispatch folded into the matvec epilogue)
         st.then(&L.ffn_gate, &L.ffn_up);
         {
             TpFuse to;
             if (folded(l, 1)) to = push_of(r->x_pair_hidden, dim_l, l, 1);
+            if (folded(l, 0)) add_wait(to, r->x_pair_attn, l, 0);
             if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l, nullptr, &to);
         }
         if (!folded(l, 1)) gather(r->hidden, r->x_hidden, dim_l, l, 1);
@@ -795,8 +799,9 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         r->x_logits = r->x_gate + c.ff_dim;
         r->x_pair_hidden = (r->x_logits + c.vocab_size + 3) & ~(size_t)3;  // 16-byte aligned
         r->x_pair_gate = r->x_pair_hidden + 2 * (size_t)c.dim;
+        r->x_pair_attn = r->x_pair_gate + 2 * (size_t)c.ff_dim;
         float *base = nullptr;
-        rc = tp_setup_exchange(ctx, r->x_pair_gate + 2 * (size_t)c.ff_dim, &base);
+        rc = tp_setup_exchange(ctx, r->x_pair_attn + 2 * (size_t)qdim, &base);
         if (rc == YULE_OK) {
             r->xchg = true;
             r->attn_out = base + r->x_attn_out;
