@@ -237,7 +237,8 @@ __device__ __noinline__ void tp_push_value(const TpFuse &tp, size_t o, float v) 
         asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(tp.pair_out[pp] + o), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
 }
 
-template <int GROUP, int HD>
+// TP = true only for launches of a tensor-parallel runner that also push (value, epoch) pairs.
+template <int GROUP, int HD, bool TP>
 __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_constant__ AttnParams p) {
     constexpr int J = HD / 32;                               // 16-byte steps per lane and row
     constexpr int GH = (GROUP * J > 16) ? (16 / J) : GROUP;  // query heads scored per pass over K
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
             if (idx < GROUP * HD) {
                 const float val = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
                 out_z[(size_t)head0 * HD + idx] = val;
-                if (p.tp.push) tp_push_value(p.tp, (size_t)head0 * HD + idx, val);
+                if (TP && p.tp.push) tp_push_value(p.tp, (size_t)head0 * HD + idx, val);
             }
         }
         return;
@@ -557,7 +558,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
         const float inv = 1.0f / ml[2 * (vi / HD4) + 1];
         const float4 res = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
         reinterpret_cast<float4 *>(out_z + (size_t)head0 * HD)[vi] = res;
-        if (p.tp.push) {
+        if (TP && p.tp.push) {
             const size_t o0 = (size_t)head0 * HD + 4 * (size_t)vi;
             tp_push_value(p.tp, o0, res.x);
             tp_push_value(p.tp, o0 + 1, res.y);
@@ -570,7 +571,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
 
 template <int GROUP, int HD>
 cudaError_t launch_gqa_variant(const AttnParams &p, size_t smem, bool pdl, cudaStream_t s, uint32_t n_tokens = 1) {
-    auto kern = attn_decode_gqa_kernel<GROUP, HD>;
+    auto kern = p.tp.push ? attn_decode_gqa_kernel<GROUP, HD, true> : attn_decode_gqa_kernel<GROUP, HD, false>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;

@@ -244,6 +244,7 @@ __device__ __forceinline__ void tp_load8(const uint2 *pairs, uint32_t epoch, int
 // conversion pass, so x is fetched from L2 only once; longer vectors re-read the remainder.
 constexpr int kCache = 4;
 
+template <bool TP>
 __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const float *__restrict__ x, uint32_t x_stride,
                                                   uint32_t n_cols, uint32_t nb, const float *__restrict__ norm_w,
                                                   float eps, const uint2 *pairs = nullptr, uint32_t pair_epoch = 0,
@@ -256,7 +257,7 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
         float cache[kCache][8];
         float ss = 0.f, mx = 0.f;
         auto load8 = [&](uint32_t c, float (&a)[8]) {
-            if (pairs) {  // tensor parallelism: the vector arrives as (value, epoch) pairs stored by all ranks
+            if (TP && pairs) {  // tensor parallelism: the vector arrives as (value, epoch) pairs stored by all ranks
                 tp_load8(pairs + c, pair_epoch, status, a);
                 return;
             }
@@ -563,7 +564,9 @@ struct UnitCursor {
 // group multiplies super-blocks w, w+8, …; a warp's (tile, matrix, super-block) units form one
 // sequence that is prefetched DEPTH units ahead.  In pair mode a tile is the gate rows followed by
 // the same rows of up.  The activations are staged once per CTA.
-template <int ROWS, int DEPTH, bool SUBCOL>
+// TP = true only for launches of a tensor-parallel runner that push or poll (value, epoch) pairs: the
+// single-GPU instantiations carry none of that code.
+template <int ROWS, int DEPTH, bool SUBCOL, bool TP>
 __global__ void __launch_bounds__(kThreadsCta, 1)
 qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     constexpr int NR = ROWS / 8;
@@ -608,8 +611,11 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     yule_prefetch_l2_slice(p.next_w[1], p.next_bytes[1]);
     yule_pdl_wait();
     // tensor parallelism: x may arrive as (value, epoch) pairs stored by all ranks
-    stage_activations(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps, p.tp.wait ? p.tp.pair_in : nullptr,
-                      p.tp.wait ? *p.tp.tick * p.tp.epochs_per_tick + p.tp.wait_index + 1u : 0u, p.tp.status);
+    if (TP)
+        stage_activations<true>(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps, p.tp.wait ? p.tp.pair_in : nullptr,
+                                p.tp.wait ? *p.tp.tick * p.tp.epochs_per_tick + p.tp.wait_index + 1u : 0u, p.tp.status);
+    else
+        stage_activations<false>(sm, p.x, p.x_stride, p.n_cols, p.batch, p.norm_w, p.eps);
     // B column n = g: vector n/2, part n%2.  Lanes whose vector does not exist read vector 0;
     // their output columns are never looked at.
     const uint32_t vec = (uint32_t)(g >> 1) < p.batch ? (g >> 1) : 0;
@@ -664,7 +670,7 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
                 sums[0] += p.residual[o];
             }
             p.out[seg][o] = sums[0];
-            if (p.tp.push && seg == 0) tp_push_value(p.tp, o, sums[0]);  // the same row into every peer's copy
+            if (TP && p.tp.push && seg == 0) tp_push_value(p.tp, o, sums[0]);  // the same row into every peer's copy
         }
         group_barrier(group);
     };
@@ -719,9 +725,10 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
 
 }
 
-template <int ROWS, int DEPTH, bool SUBCOL>
+template <int ROWS, int DEPTH, bool SUBCOL, bool TP = false>
 cudaError_t launch_variant(const Q4kMmaParams &p, int sm_count, size_t smem, bool pdl, cudaStream_t s) {
-    auto kern = qmv_q4k_mma_kernel<ROWS, DEPTH, SUBCOL>;
+    if (!TP && (p.tp.push || p.tp.wait)) return launch_variant<ROWS, DEPTH, SUBCOL, true>(p, sm_count, smem, pdl, s);
+    auto kern = qmv_q4k_mma_kernel<ROWS, DEPTH, SUBCOL, TP>;
     // per instantiation: the opt-in for large dynamic shared memory
     static bool attr_done = false;
     static std::mutex mu;
