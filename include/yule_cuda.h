@@ -136,12 +136,12 @@ int32_t yule_cuda_quantized_matmul(yule_cuda_ctx *ctx, yule_buffer weights, yule
 
 /* `batch` activation vectors against one weight read: input is
  * [batch][x_stride] floats, output [batch][out_stride] floats.  Same per-row
- * arithmetic as quantized_matmul.  Up to 7 vectors go through the matvec
- * kernels four at a time; 8 or more Q4_K vectors (n_cols a multiple of 256)
- * go through the tcgen05 GEMM in one pass over the weights.  The GEMM keeps its
- * activation tiles in a scratch owned by the context, grown on demand; growing
- * is not possible while a graph is being captured, so run one call of the
- * largest batch before yule_cuda_graph_begin. */
+ * arithmetic as quantized_matmul.  Small batches go through the matvec kernels
+ * four vectors at a time; from 16 vectors of Q4_K, or 32 of Q6_K / Q8_0 / Q4_0
+ * (n_cols a multiple of 256), the tcgen05 GEMM takes one pass over the weights.
+ * The GEMM keeps its activation tiles in a scratch owned by the context, grown
+ * on demand; growing is not possible while a graph is being captured, so run
+ * one call of the largest batch before yule_cuda_graph_begin. */
 int32_t yule_cuda_quantized_matmul_batched(yule_cuda_ctx *ctx, yule_buffer weights,
                                            yule_buffer input, yule_buffer output, uint32_t n_rows,
                                            uint32_t n_cols, uint32_t gguf_type, uint32_t batch,

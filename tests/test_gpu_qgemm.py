@@ -11,6 +11,13 @@ from conftest import REL_TOL, guarded_rel_err
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def gemm_for_small_batches(monkeypatch):
+    """By default the GEMM takes over from 16 (Q4_K) or 32 (other formats) activation rows; these tests
+    want it from 8, its smallest tile."""
+    monkeypatch.setenv("YULE_GEMM_MIN_BATCH", "8")
+
+
 def run(backend, w, x, n_rows, n_cols, batch, x_stride=None, out_stride=None, dtype=DType.Q4_K):
     x_stride = x_stride or n_cols
     out_stride = out_stride or n_rows

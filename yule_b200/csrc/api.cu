@@ -8,6 +8,8 @@
 #include <cmath>
 #include <cstring>
 
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace yule {
@@ -435,7 +437,16 @@ int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffe
     return YULE_OK;
 }
 
-constexpr uint32_t kGemmMinBatch = 8;
+// From how many activation rows the tcgen05 GEMM beats ceil(batch / 4) passes of the matvec kernels
+// (measured on 4096x4096 .. 128256x4096): the exact Q4_K kernel from 16, the generic kernel of the
+// other formats from 32.  YULE_GEMM_MIN_BATCH overrides both (at least 8).
+static uint32_t gemm_min_batch(uint32_t type) {
+    if (const char *e = getenv("YULE_GEMM_MIN_BATCH")) {
+        const int v = atoi(e);
+        return v < 8 ? 8u : (uint32_t)v;
+    }
+    return type == YULE_DTYPE_Q4_K ? 16u : 32u;
+}
 
 static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset, yule_buffer input,
                           yule_buffer output, uint32_t n_rows, uint32_t n_cols, uint32_t type, uint32_t batch,
@@ -475,8 +486,8 @@ static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight
     if (type == YULE_DTYPE_Q6_K && W.planar && weight_offset == 0 &&
         W.planar_blocks == (uint64_t)n_rows * (n_cols / 256))
         a.planar = W.planar;
-    if (batch >= kGemmMinBatch && qgemm_supported(type, n_cols, batch)) {
-        // eight or more activation rows: one pass over the weights on the tcgen05 GEMM
+    if (batch >= gemm_min_batch(type) && qgemm_supported(type, n_cols, batch)) {
+        // enough activation rows: one pass over the weights on the tcgen05 GEMM
         int32_t rc = ensure_gemm_scratch(ctx, qgemm_scratch_bytes(batch, n_cols));
         if (rc) return rc;
         QGemm g;
