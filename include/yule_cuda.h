@@ -59,8 +59,15 @@ enum {
     YULE_DTYPE_F32 = 0,
     YULE_DTYPE_F16 = 1,
     YULE_DTYPE_Q4_0 = 2,
+    YULE_DTYPE_Q4_1 = 3,
+    YULE_DTYPE_Q5_0 = 6,
+    YULE_DTYPE_Q5_1 = 7,
     YULE_DTYPE_Q8_0 = 8,
+    YULE_DTYPE_Q8_1 = 9,
+    YULE_DTYPE_Q2_K = 10,
+    YULE_DTYPE_Q3_K = 11,
     YULE_DTYPE_Q4_K = 12,
+    YULE_DTYPE_Q5_K = 13,
     YULE_DTYPE_Q6_K = 14
 };
 

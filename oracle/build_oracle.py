@@ -44,13 +44,14 @@ def _stale(target: str, sources: list[str]) -> bool:
 
 
 def build_oracle(force: bool = False) -> str:
-    srcs = [os.path.join(HERE, "yule_oracle.c"), os.path.join(HERE, "yule_oracle_avx2.c")]
+    srcs = [os.path.join(HERE, "yule_oracle.c"), os.path.join(HERE, "yule_oracle_ext.c"),
+            os.path.join(HERE, "yule_oracle_avx2.c")]
     deps = srcs + [os.path.join(HERE, "yule_oracle.h"), os.path.abspath(__file__)]
     if force or _stale(ORACLE_SO, deps):
-        # The scalar file is built without any -m flag so nothing can be contracted or widened;
+        # The scalar files are built without any -m flag so nothing can be contracted or widened;
         # the AVX2 file needs -mavx2 -mfma for its intrinsics.
         objs = []
-        for src, extra in ((srcs[0], []), (srcs[1], ["-mavx2", "-mfma"])):
+        for src, extra in ((srcs[0], []), (srcs[1], []), (srcs[2], ["-mavx2", "-mfma"])):
             obj = src[:-2] + ".o"
             subprocess.check_call(["gcc", "-c", src, "-o", obj] +
                                   [f for f in _CFLAGS if f != "-shared"] + extra)

@@ -36,7 +36,7 @@ def _load() -> C.CDLL:
     lib = C.CDLL(so)
     lib.yo_f16_to_f32.restype = C.c_float
     lib.yo_f16_to_f32.argtypes = [C.c_uint16]
-    for name in ("q4_0", "q8_0", "q4_k", "q6_k"):
+    for name in ("q4_0", "q8_0", "q4_k", "q6_k", "q4_1", "q5_0", "q5_1", "q8_1", "q2_k", "q3_k", "q5_k"):
         f = getattr(lib, "yo_vec_dot_" + name)
         f.restype = C.c_float
         f.argtypes = [_u8p, _f32p]

@@ -24,9 +24,16 @@ int yo_block_size(int type) {
     case YO_F16:
         return 1;
     case YO_Q4_0:
+    case YO_Q4_1:
+    case YO_Q5_0:
+    case YO_Q5_1:
     case YO_Q8_0:
+    case YO_Q8_1:
         return 32;
+    case YO_Q2_K:
+    case YO_Q3_K:
     case YO_Q4_K:
+    case YO_Q5_K:
     case YO_Q6_K:
         return 256;
     default:
@@ -49,6 +56,20 @@ int yo_block_bytes(int type) {
         return 144;
     case YO_Q6_K:
         return 210;
+    case YO_Q4_1:
+        return 20;
+    case YO_Q5_0:
+        return 22;
+    case YO_Q5_1:
+        return 24;
+    case YO_Q8_1:
+        return 36;
+    case YO_Q2_K:
+        return 84;
+    case YO_Q3_K:
+        return 110;
+    case YO_Q5_K:
+        return 176;
     default:
         return 0;
     }
@@ -191,7 +212,7 @@ int yo_dequant_block(int type, const uint8_t *block, float *out) {
         memcpy(out, block, 4);
         return 0;
     default:
-        return -1;
+        return yo_ext_dequant_block(type, block, out);
     }
 }
 
@@ -330,7 +351,7 @@ int yo_vec_dot_block(int type, const uint8_t *block, const float *act, int simd,
         *out = yo_vec_dot_q6_k(block, act);
         return 0;
     default:
-        return -1;
+        return yo_ext_vec_dot_block(type, block, act, out);
     }
 }
 
@@ -391,7 +412,7 @@ static void *qmv_thread(void *p) {
 int yo_qmv(int type, const uint8_t *w, const float *x, float *out, size_t n_rows, size_t n_cols,
            int n_threads, int simd) {
     int bs = yo_block_size(type), bb = yo_block_bytes(type);
-    if (type != YO_Q4_0 && type != YO_Q8_0 && type != YO_Q4_K && type != YO_Q6_K)
+    if (bs <= 1)
         return -1;
     if (n_threads <= 0)
         n_threads = yo_hardware_threads();

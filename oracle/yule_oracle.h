@@ -32,8 +32,15 @@ enum {
     YO_F32 = 0,
     YO_F16 = 1,
     YO_Q4_0 = 2,
+    YO_Q4_1 = 3,
+    YO_Q5_0 = 6,
+    YO_Q5_1 = 7,
     YO_Q8_0 = 8,
+    YO_Q8_1 = 9,
+    YO_Q2_K = 10,
+    YO_Q3_K = 11,
     YO_Q4_K = 12,
+    YO_Q5_K = 13,
     YO_Q6_K = 14,
 };
 
@@ -54,6 +61,23 @@ void yo_dequant_q8_0(const uint8_t *block, float *out);                   /* deq
 void yo_dequant_q4_k(const uint8_t *block, float *out);                   /* dequant.rs:260-290 */
 void yo_dequant_q6_k(const uint8_t *block, float *out);                   /* dequant.rs:346-372 */
 int yo_dequant_block(int type, const uint8_t *block, float *out);         /* dequant.rs:1232    */
+/* yule_oracle_ext.c: the formats the reference's GPU backends reject but its CPU runner handles. */
+void yo_dequant_q4_1(const uint8_t *block, float *out); /* dequant.rs:91-101  */
+void yo_dequant_q5_0(const uint8_t *block, float *out); /* dequant.rs:106-119 */
+void yo_dequant_q5_1(const uint8_t *block, float *out); /* dequant.rs:124-138 */
+void yo_dequant_q8_1(const uint8_t *block, float *out); /* dequant.rs:156-165 */
+void yo_dequant_q2_k(const uint8_t *block, float *out); /* dequant.rs:196-214 */
+void yo_dequant_q3_k(const uint8_t *block, float *out); /* dequant.rs:219-251 */
+void yo_dequant_q5_k(const uint8_t *block, float *out); /* dequant.rs:297-338 */
+float yo_vec_dot_q4_1(const uint8_t *block, const float *act); /* dequant.rs:1143-1157 */
+float yo_vec_dot_q5_0(const uint8_t *block, const float *act); /* dequant.rs:1160-1174 */
+float yo_vec_dot_q5_1(const uint8_t *block, const float *act); /* dequant.rs:1177-1194 */
+float yo_vec_dot_q8_1(const uint8_t *block, const float *act); /* dequant.rs:1197-1207 */
+float yo_vec_dot_q2_k(const uint8_t *block, const float *act); /* dequant.rs:1013-1041 */
+float yo_vec_dot_q3_k(const uint8_t *block, const float *act); /* dequant.rs:1045-1084 */
+float yo_vec_dot_q5_k(const uint8_t *block, const float *act); /* dequant.rs:1088-1140 */
+int yo_ext_dequant_block(int type, const uint8_t *block, float *out);
+int yo_ext_vec_dot_block(int type, const uint8_t *block, const float *act, float *out);
 int yo_dequant_tensor(int type, const uint8_t *data, size_t n_blocks, float *out);
 
 float yo_vec_dot_q4_0(const uint8_t *block, const float *act); /* dequant.rs:902-913  */

@@ -1,14 +1,16 @@
 """Dequantised weights must be bit-identical to yule-core's scalar dequantisers
-(yule-core/src/dequant.rs:77-86, :142-150, :260-290, :346-372), checked through the C ABI."""
+(yule-core/src/dequant.rs:77-165, :196-372), checked through the C ABI."""
 
 import numpy as np
 import pytest
 
 from yule_b200 import DType, synth
+from yule_b200.dtype import EXTRA_QUANTIZED
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = [DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K]
+FORMATS = [DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K] + list(EXTRA_QUANTIZED)
+QUANTISABLE = [d for d in FORMATS if d not in (DType.Q8_1, DType.Q2_K, DType.Q3_K)]
 
 
 def gpu_dequant(backend, dtype, data):
@@ -30,7 +32,7 @@ def test_random_field_blocks_bit_exact(backend, oracle, dtype):
     assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), "f32 bit mismatch"
 
 
-@pytest.mark.parametrize("dtype", FORMATS)
+@pytest.mark.parametrize("dtype", QUANTISABLE)
 def test_quantised_gaussian_bit_exact(backend, oracle, dtype):
     data = synth.random_quantized(dtype, seed=3, n_weights=256 * 2048, std=0.02)
     got = gpu_dequant(backend, dtype, data)
@@ -73,6 +75,39 @@ def test_reference_kats(backend):
     assert out[0] == 127.0 and out[1] == -128.0
 
 
+def test_reference_kats_other_formats(backend):
+    """The hand-built blocks of yule-core's tests for Q4_1, Q5_0, Q3_K, Q5_K and Q8_1
+    (dequant.rs:1405-1426, :1444-1474, :1490-1527, :1530-1563, :1598-1611)."""
+    b = np.zeros(20, np.uint8)
+    b[1] = b[3] = 0x3C
+    b[4] = 0xF0
+    out = gpu_dequant(backend, DType.Q4_1, b)
+    assert out[0] == 1.0 and out[1] == 16.0 and out[2] == 1.0
+    b = np.zeros(22, np.uint8)
+    b[1] = 0x3C
+    b[2] = 0x02
+    b[6] = 0x5A
+    out = gpu_dequant(backend, DType.Q5_0, b)
+    assert out[0] == -6.0 and out[1] == 5.0
+    b = np.zeros(110, np.uint8)
+    b[109] = 0x3C
+    b[96], b[104], b[32] = 0x01, 0x02, 0x01
+    assert gpu_dequant(backend, DType.Q3_K, b)[0] == -3.0
+    b[0] = 0x01
+    assert gpu_dequant(backend, DType.Q3_K, b)[0] == 1.0
+    b = np.zeros(176, np.uint8)
+    b[1] = 0x3C
+    b[4], b[48] = 0x01, 0x05
+    assert gpu_dequant(backend, DType.Q5_K, b)[0] == 5.0
+    b[16] = 0x01
+    assert gpu_dequant(backend, DType.Q5_K, b)[0] == 21.0
+    b = np.zeros(36, np.uint8)
+    b[1] = 0x3C
+    b[4], b[5] = 42, 0x80
+    out = gpu_dequant(backend, DType.Q8_1, b)
+    assert out[0] == 42.0 and out[1] == -128.0
+
+
 def test_empty_and_errors(backend):
     from yule_b200 import YuleGpuError
     w = backend.allocate(144)
@@ -81,6 +116,6 @@ def test_empty_and_errors(backend):
     with pytest.raises(YuleGpuError):
         backend.dequantize(w, DType.Q4_K, 2, out)  # reads past the weight buffer
     with pytest.raises(YuleGpuError):
-        backend.dequantize(w, 13, 1, out)  # Q5_K is not on this path
+        backend.dequantize(w, 16, 1, out)  # IQ2_XXS: no kernel reads it
     backend.free(w)
     backend.free(out)

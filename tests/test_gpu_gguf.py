@@ -48,11 +48,11 @@ def test_missing_tensor_and_unsupported_format_are_refused(backend, tmp_path):
     with pytest.raises(YuleGpuError) as e:
         load_runner(backend, g)
     assert "tensor not found: blk.1.ffn_up.weight" in str(e.value)
-    # a K-quant the kernels do not read yet (Q5_K, id 13): parsed, but refused at load with the reference's words
+    # a format the kernels do not read (IQ2_XXS, id 16, 66 bytes per 256): parsed, but refused at load with the reference's words
     shapes = CFG.tensor_shapes()
     tensors = {n: (d, int(t), (shapes[n][1], shapes[n][0]) if n in shapes else (CFG.dim,)) for n, (d, t) in weights.items()}
     rows, cols = shapes["blk.0.attn_q.weight"]
-    tensors["blk.0.attn_q.weight"] = (np.zeros(rows * cols // 256 * 176, np.uint8), 13, (cols, rows))
+    tensors["blk.0.attn_q.weight"] = (np.zeros(rows * cols // 256 * 66, np.uint8), 16, (cols, rows))
     g2 = GgufFile.parse(gw.build(gw.llama_metadata(CFG), tensors))
     with pytest.raises(YuleGpuError) as e:
         load_runner(backend, g2)

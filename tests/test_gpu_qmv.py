@@ -1,15 +1,16 @@
 """Fused dequant-matvec (ComputeBackend::quantized_matmul, yule-gpu/src/lib.rs:119) against the
-scalar fused dots of yule-core/src/dequant.rs:902-1009 driven by qmv (yule-infer/src/model_runner.rs:152)."""
+scalar fused dots of yule-core/src/dequant.rs:902-1207 driven by qmv (yule-infer/src/model_runner.rs:152)."""
 
 import numpy as np
 import pytest
 
 from conftest import REL_TOL, guarded_rel_err
 from yule_b200 import DType, YuleGpuError, synth
+from yule_b200.dtype import EXTRA_QUANTIZED
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = [DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K]
+FORMATS = [DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K] + list(EXTRA_QUANTIZED)
 
 
 def gpu_qmv(backend, dtype, w, x, n_rows, n_cols, batch=1):
@@ -42,7 +43,7 @@ def test_matches_scalar_reference(backend, oracle, dtype, n_rows, blocks_per_row
     assert guarded_rel_err(y, ref) <= REL_TOL
 
 
-@pytest.mark.parametrize("dtype", [DType.Q4_0, DType.Q8_0])
+@pytest.mark.parametrize("dtype", [DType.Q4_0, DType.Q8_0, DType.Q4_1, DType.Q5_0, DType.Q5_1, DType.Q8_1])
 def test_small_block_formats_odd_columns(backend, oracle, dtype):
     """32-weight blocks with a column count that is not a multiple of 256."""
     n_rows, n_cols = 33, 32 * 5
@@ -117,7 +118,7 @@ def test_error_paths(backend):
     x = backend.allocate(256 * 4)
     o = backend.allocate(16)
     with pytest.raises(YuleGpuError) as e:
-        backend.quantized_matmul(w, x, o, 4, 256, 13)  # Q5_K: unsupported dtype for CUDA qmv
+        backend.quantized_matmul(w, x, o, 4, 256, 16)  # IQ2_XXS: unsupported dtype for CUDA qmv
     assert "unsupported dtype" in str(e.value)
     with pytest.raises(YuleGpuError):
         backend.quantized_matmul(w, x, o, 4, 200, DType.Q4_K)  # not a block multiple

@@ -48,11 +48,12 @@ def greedy_reference(oracle, m, prompt, n_gen):
 
 
 @pytest.mark.parametrize("fused", [False, True])
-@pytest.mark.parametrize("mix", ["q4k_q6k", "q4k", "q6k", "q8_0", "q4_0"])
+@pytest.mark.parametrize("mix", ["q4k_q6k", "q4k", "q6k", "q8_0", "q4_0", "q5k", "q5_0", "q4_1_q5_1"])
 def test_logits_match_cpu_runner(backend, oracle, fused, mix):
     kw = {"q4k_q6k": dict(linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K),
           "q4k": dict(linear=DType.Q4_K), "q6k": dict(linear=DType.Q6_K),
-          "q8_0": dict(linear=DType.Q8_0), "q4_0": dict(linear=DType.Q4_0)}[mix]
+          "q8_0": dict(linear=DType.Q8_0), "q4_0": dict(linear=DType.Q4_0), "q5k": dict(linear=DType.Q5_K),
+          "q5_0": dict(linear=DType.Q5_0), "q4_1_q5_1": dict(linear=DType.Q4_1, ffn_down=DType.Q5_1)}[mix]
     weights = synth.synthetic_model(SMALL, seed=1, std=0.05, **kw)
     ref = make_oracle_model(oracle, SMALL, weights)
     run = CudaTransformerRunner(backend, SMALL, weights, fused=fused)

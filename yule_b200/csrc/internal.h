@@ -105,14 +105,26 @@ struct yule_cuda_ctx {
 
 namespace yule {
 
-inline bool is_quantized(uint32_t t) {
+// The four formats with tuned matvec and tensor-core GEMM kernels.
+inline bool is_tuned_format(uint32_t t) {
     return t == YULE_DTYPE_Q4_0 || t == YULE_DTYPE_Q8_0 || t == YULE_DTYPE_Q4_K || t == YULE_DTYPE_Q6_K;
+}
+// Every block format the kernels can read: the tuned four plus the formats that run through the
+// element-wise matvec (Yule's own GPU backends reject those, yule-gpu/src/cuda/mod.rs:303-307).
+inline bool is_quantized(uint32_t t) {
+    switch (t) {
+        case YULE_DTYPE_Q4_1: case YULE_DTYPE_Q5_0: case YULE_DTYPE_Q5_1: case YULE_DTYPE_Q8_1:
+        case YULE_DTYPE_Q2_K: case YULE_DTYPE_Q3_K: case YULE_DTYPE_Q5_K: return true;
+        default: return is_tuned_format(t);
+    }
 }
 inline uint32_t block_size(uint32_t t) {  // yule-core/src/dtype.rs:99-118
     switch (t) {
         case YULE_DTYPE_F32: case YULE_DTYPE_F16: return 1;
-        case YULE_DTYPE_Q4_0: case YULE_DTYPE_Q8_0: return 32;
-        case YULE_DTYPE_Q4_K: case YULE_DTYPE_Q6_K: return 256;
+        case YULE_DTYPE_Q4_0: case YULE_DTYPE_Q8_0: case YULE_DTYPE_Q4_1: case YULE_DTYPE_Q5_0:
+        case YULE_DTYPE_Q5_1: case YULE_DTYPE_Q8_1: return 32;
+        case YULE_DTYPE_Q4_K: case YULE_DTYPE_Q6_K: case YULE_DTYPE_Q2_K: case YULE_DTYPE_Q3_K:
+        case YULE_DTYPE_Q5_K: return 256;
         default: return 0;
     }
 }
@@ -124,6 +136,13 @@ inline uint32_t block_bytes(uint32_t t) {  // yule-core/src/dtype.rs:62-96
         case YULE_DTYPE_Q8_0: return 34;
         case YULE_DTYPE_Q4_K: return 144;
         case YULE_DTYPE_Q6_K: return 210;
+        case YULE_DTYPE_Q4_1: return 20;
+        case YULE_DTYPE_Q5_0: return 22;
+        case YULE_DTYPE_Q5_1: return 24;
+        case YULE_DTYPE_Q8_1: return 36;
+        case YULE_DTYPE_Q2_K: return 84;
+        case YULE_DTYPE_Q3_K: return 110;
+        case YULE_DTYPE_Q5_K: return 176;
         default: return 0;
     }
 }

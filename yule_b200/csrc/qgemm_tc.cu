@@ -869,7 +869,7 @@ uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 
 // Q4_K runs on the exact-integer kernel; Q6_K, Q8_0 and Q4_0 on the generic one (YULE_GEMM_GENERIC=1
 // sends Q4_K there too, for comparison).  The activation tiles are laid out per 256 columns.
 bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens) {
-    return is_quantized(type) && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
+    return is_tuned_format(type) && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
 }
 
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols) {

@@ -381,6 +381,67 @@ qmv_q32_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
     }
 }
 
+// ── formats without a tuned kernel ──────────────────────────────────────────────────────────
+// One warp per row, a lane per run of 8 consecutive columns (inside one sub-block of every
+// format, so the scale decode is shared by the 8 weights); the weights are dequantised with the
+// per-element functions and accumulated in f32.  Correct for any row length that is a multiple
+// of the block size; not tuned: the byte-wise loads keep it far below the HBM roofline.
+template <int NB, uint32_t TYPE>
+__global__ void __launch_bounds__(kThreads)
+qmv_elem_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+                uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
+                const float *__restrict__ residual) {
+    extern __shared__ __align__(16) float smem[];
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
+    float *xs = smem;
+    stage_x<NB, false>(x, x_stride, n_cols, xs, nullptr, false);
+
+    constexpr uint32_t BS = (TYPE == YULE_DTYPE_Q2_K || TYPE == YULE_DTYPE_Q3_K || TYPE == YULE_DTYPE_Q5_K) ? 256 : 32;
+    constexpr uint32_t BB = TYPE == YULE_DTYPE_Q4_1 ? 20 : TYPE == YULE_DTYPE_Q5_0 ? 22 : TYPE == YULE_DTYPE_Q5_1 ? 24
+                          : TYPE == YULE_DTYPE_Q8_1 ? 36 : TYPE == YULE_DTYPE_Q2_K ? 84 : TYPE == YULE_DTYPE_Q3_K ? 110 : 176;
+    const size_t row_bytes = (size_t)(n_cols / BS) * BB;
+    const uint32_t n_runs = n_cols / 8;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t n_warps = gridDim.x * kWarps;
+
+    for (uint32_t row = warp; row < n_rows; row += n_warps) {
+        const uint8_t *rowp = w + (size_t)row * row_bytes;
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.f;
+        for (uint32_t run = lane; run < n_runs; run += 32) {
+            float wv[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) wv[k] = dequant_row_elem<TYPE>(rowp, run * 8 + k);
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const float4 a0 = *reinterpret_cast<const float4 *>(xs + (size_t)b * n_cols + run * 8);
+                const float4 a1 = *reinterpret_cast<const float4 *>(xs + (size_t)b * n_cols + run * 8 + 4);
+                float s = acc[b];
+                s = fmaf(wv[0], a0.x, s);
+                s = fmaf(wv[1], a0.y, s);
+                s = fmaf(wv[2], a0.z, s);
+                s = fmaf(wv[3], a0.w, s);
+                s = fmaf(wv[4], a1.x, s);
+                s = fmaf(wv[5], a1.y, s);
+                s = fmaf(wv[6], a1.z, s);
+                s = fmaf(wv[7], a1.w, s);
+                acc[b] = s;
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            float v = warp_sum(acc[b]);
+            if (lane == 0) {
+                if (residual) v += residual[(size_t)b * out_stride + row];
+                out[(size_t)b * out_stride + row] = v;
+            }
+        }
+    }
+}
+
 // ── launch plumbing ─────────────────────────────────────────────────────────────────────────
 
 using QmvKernel = void (*)(const uint8_t *, const float *, float *, uint32_t, uint32_t, uint32_t, uint32_t,
@@ -393,6 +454,13 @@ QmvKernel pick_kernel(uint32_t type) {
         case YULE_DTYPE_Q6_K: return qmv_q6k_kernel<NB>;
         case YULE_DTYPE_Q8_0: return qmv_q32_kernel<NB, true>;
         case YULE_DTYPE_Q4_0: return qmv_q32_kernel<NB, false>;
+        case YULE_DTYPE_Q4_1: return qmv_elem_kernel<NB, YULE_DTYPE_Q4_1>;
+        case YULE_DTYPE_Q5_0: return qmv_elem_kernel<NB, YULE_DTYPE_Q5_0>;
+        case YULE_DTYPE_Q5_1: return qmv_elem_kernel<NB, YULE_DTYPE_Q5_1>;
+        case YULE_DTYPE_Q8_1: return qmv_elem_kernel<NB, YULE_DTYPE_Q8_1>;
+        case YULE_DTYPE_Q2_K: return qmv_elem_kernel<NB, YULE_DTYPE_Q2_K>;
+        case YULE_DTYPE_Q3_K: return qmv_elem_kernel<NB, YULE_DTYPE_Q3_K>;
+        case YULE_DTYPE_Q5_K: return qmv_elem_kernel<NB, YULE_DTYPE_Q5_K>;
         default: return nullptr;
     }
 }
@@ -401,7 +469,7 @@ size_t qmv_smem_bytes(uint32_t type, uint32_t n_cols, int nb) {
     size_t per_vec;
     if (type == YULE_DTYPE_Q4_K)
         per_vec = (size_t)n_cols + n_cols / 32;
-    else if (type == YULE_DTYPE_Q6_K)
+    else if (type == YULE_DTYPE_Q6_K || !is_tuned_format(type))
         per_vec = n_cols;
     else
         per_vec = (size_t)(n_cols / 32) * 36;
@@ -479,7 +547,7 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             size_t smem = 0;
             int occ = 0;
         };
-        static Cached cache[16];
+        static Cached cache[48];
         static std::mutex cache_mu;
         int occ = 0;
         {

@@ -82,8 +82,29 @@ inline void put_f16(uint8_t *p, uint16_t h) {
     p[1] = (uint8_t)(h >> 8);
 }
 
-int block_size(int t) { return (t == 2 || t == 8) ? 32 : ((t == 12 || t == 14) ? 256 : 0); }
-int block_bytes(int t) { return t == 2 ? 18 : t == 8 ? 34 : t == 12 ? 144 : t == 14 ? 210 : 0; }
+int block_size(int t) {
+    switch (t) {
+        case 2: case 3: case 6: case 7: case 8: case 9: return 32;
+        case 10: case 11: case 12: case 13: case 14: return 256;
+        default: return 0;
+    }
+}
+int block_bytes(int t) {
+    switch (t) {
+        case 2: return 18;
+        case 3: return 20;
+        case 6: return 22;
+        case 7: return 24;
+        case 8: return 34;
+        case 9: return 36;
+        case 10: return 84;
+        case 11: return 110;
+        case 12: return 144;
+        case 13: return 176;
+        case 14: return 210;
+        default: return 0;
+    }
+}
 
 template <class F>
 void parallel_for(uint64_t n, int n_threads, F fn) {
@@ -114,10 +135,15 @@ void random_block(int type, uint64_t seed, uint64_t blk, float scale_std, uint8_
     uint16_t d = f32_to_f16(std::fabs(normal(seed, 2 * blk)) * scale_std);
     uint16_t dm = f32_to_f16(std::fabs(normal(seed, 2 * blk + 1)) * scale_std);
     switch (type) {
-        case 12:
+        case 3: case 7: case 9: case 12: case 13:  // d then m / s / dmin
             put_f16(out, d);
             put_f16(out + 2, dm);
             break;
+        case 10:
+            put_f16(out + 80, d);
+            put_f16(out + 82, dm);
+            break;
+        case 11: put_f16(out + 108, d); break;
         case 14: put_f16(out + 208, d); break;
         default: put_f16(out, d); break;
     }
@@ -149,7 +175,8 @@ void quantize_q4_0(const float *x, uint8_t *out) {
     }
 }
 
-void quantize_q4_k(const float *x, uint8_t *out) {
+// Q4_K (levels 15) and Q5_K (levels 31): same scales, Q5_K keeps bit 4 of weight (s, l) in bit s of qh[l].
+void quantize_q45_k(const float *x, uint8_t *out, int levels) {
     float scale[8], mn[8], max_scale = 0.f, max_min = 0.f;
     for (int s = 0; s < 8; s++) {
         float lo = x[32 * s], hi = x[32 * s];
@@ -158,7 +185,7 @@ void quantize_q4_k(const float *x, uint8_t *out) {
             hi = std::max(hi, x[32 * s + i]);
         }
         mn[s] = std::max(0.f, -lo);
-        scale[s] = (hi + mn[s]) / 15.0f;
+        scale[s] = (hi + mn[s]) / (float)levels;
         max_scale = std::max(max_scale, scale[s]);
         max_min = std::max(max_min, mn[s]);
     }
@@ -184,10 +211,49 @@ void quantize_q4_k(const float *x, uint8_t *out) {
             for (int h = 0; h < 2; h++) {
                 int s = 2 * g + h;
                 float ds = d * (float)sc[s], ms = dmin * (float)m[s];
-                qs[h] = ds > 0 ? std::clamp(nearest((x[64 * g + 32 * h + l] + ms) / ds), 0, 15) : 0;
+                qs[h] = ds > 0 ? std::clamp(nearest((x[64 * g + 32 * h + l] + ms) / ds), 0, levels) : 0;
             }
-            out[16 + 32 * g + l] = (uint8_t)(qs[0] | (qs[1] << 4));
+            if (levels == 15) {
+                out[16 + 32 * g + l] = (uint8_t)(qs[0] | (qs[1] << 4));
+            } else {
+                if (g == 0) out[16 + l] = 0;
+                out[16 + l] |= (uint8_t)(((qs[0] >> 4) << (2 * g)) | ((qs[1] >> 4) << (2 * g + 1)));
+                out[48 + 32 * g + l] = (uint8_t)((qs[0] & 15) | ((qs[1] & 15) << 4));
+            }
         }
+    }
+}
+
+// Legacy 5-bit and asymmetric formats (dequant.rs:91-138): qh bit i is bit 4 of weight i.
+void quantize_q5_0(const float *x, uint8_t *out) {
+    float amax = 0.f;
+    for (int i = 0; i < 32; i++) amax = std::max(amax, std::fabs(x[i]));
+    uint16_t dh = f32_to_f16(amax / 15.0f);
+    float d = f16_to_f32(dh), id = d > 0 ? 1.0f / d : 0.f;
+    put_f16(out, dh);
+    std::memset(out + 2, 0, 20);
+    for (int i = 0; i < 32; i++) {
+        int q = std::clamp(nearest(x[i] * id) + 16, 0, 31);
+        out[2 + i / 8] |= (uint8_t)((q >> 4) << (i & 7));
+        out[6 + i / 2] |= (uint8_t)((q & 15) << (4 * (i & 1)));
+    }
+}
+void quantize_q45_1(const float *x, uint8_t *out, int levels) {
+    float lo = x[0], hi = x[0];
+    for (int i = 1; i < 32; i++) {
+        lo = std::min(lo, x[i]);
+        hi = std::max(hi, x[i]);
+    }
+    uint16_t dh = f32_to_f16((hi - lo) / (float)levels), mh = f32_to_f16(lo);
+    float d = f16_to_f32(dh), m = f16_to_f32(mh), id = d > 0 ? 1.0f / d : 0.f;
+    put_f16(out, dh);
+    put_f16(out + 2, mh);
+    const int qs_off = levels == 15 ? 4 : 8;
+    std::memset(out + 4, 0, levels == 15 ? 16 : 20);
+    for (int i = 0; i < 32; i++) {
+        int q = std::clamp(nearest((x[i] - m) * id), 0, levels);
+        if (levels == 31) out[4 + i / 8] |= (uint8_t)((q >> 4) << (i & 7));
+        out[qs_off + i / 2] |= (uint8_t)((q & 15) << (4 * (i & 1)));
     }
 }
 
@@ -220,10 +286,16 @@ void quantize_block(int type, const float *x, uint8_t *out) {
     switch (type) {
         case 2: quantize_q4_0(x, out); break;
         case 8: quantize_q8_0(x, out); break;
-        case 12: quantize_q4_k(x, out); break;
+        case 3: quantize_q45_1(x, out, 15); break;
+        case 6: quantize_q5_0(x, out); break;
+        case 7: quantize_q45_1(x, out, 31); break;
+        case 12: quantize_q45_k(x, out, 15); break;
+        case 13: quantize_q45_k(x, out, 31); break;
         case 14: quantize_q6_k(x, out); break;
     }
 }
+
+bool has_quantizer(int t) { return t == 2 || t == 3 || t == 6 || t == 7 || t == 8 || t == 12 || t == 13 || t == 14; }
 
 }  // namespace
 
@@ -254,7 +326,7 @@ int ys_random_blocks(int type, uint64_t seed, float scale_std, uint8_t *out, uin
 // Quantise n floats (a multiple of the block size) into blocks.
 int ys_quantize(int type, const float *x, uint64_t n, uint8_t *out, int n_threads) {
     const int bs = block_size(type), bb = block_bytes(type);
-    if (!bs || n % (uint64_t)bs) return -1;
+    if (!bs || !has_quantizer(type) || n % (uint64_t)bs) return -1;
     parallel_for(n / bs, n_threads, [=](uint64_t b, uint64_t e) {
         for (uint64_t i = b; i < e; i++) quantize_block(type, x + i * (uint64_t)bs, out + i * (uint64_t)bb);
     });
@@ -264,7 +336,7 @@ int ys_quantize(int type, const float *x, uint64_t n, uint8_t *out, int n_thread
 // N(0, std) weights generated and quantised block by block without an f32 copy of the tensor.
 int ys_random_quantized(int type, uint64_t seed, float std_, uint8_t *out, uint64_t n_weights, int n_threads) {
     const int bs = block_size(type), bb = block_bytes(type);
-    if (!bs || n_weights % (uint64_t)bs) return -1;
+    if (!bs || !has_quantizer(type) || n_weights % (uint64_t)bs) return -1;
     parallel_for(n_weights / bs, n_threads, [=](uint64_t b, uint64_t e) {
         float tmp[256];
         for (uint64_t i = b; i < e; i++) {
