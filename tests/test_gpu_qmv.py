@@ -113,6 +113,21 @@ def test_weight_offset_view(backend, oracle):
         backend.free(h)
 
 
+@pytest.mark.parametrize("shift", [0, 6])
+def test_q5k_any_two_byte_offset(backend, oracle, shift):
+    """Q5_K at a 16-byte-aligned offset (vectorised kernel) and at an odd one (element-wise kernel)."""
+    dtype, n_rows, n_cols = DType.Q5_K, 70, 1024
+    blocks = synth.random_blocks(dtype, 21, n_rows * 4)
+    w = np.concatenate([np.zeros(176 + shift, np.uint8), blocks])
+    x = synth.normal(8, n_cols)
+    wh, xh, oh = backend.upload(w), backend.upload(x), backend.allocate(n_rows * 4)
+    backend.quantized_matmul_at(wh, 176 + shift, xh, oh, n_rows, n_cols, dtype)
+    y = backend.download(oh, n_rows)
+    assert guarded_rel_err(y, oracle.qmv(int(dtype), blocks, x, n_rows, n_cols)) <= REL_TOL
+    for h in (wh, xh, oh):
+        backend.free(h)
+
+
 def test_error_paths(backend):
     w = backend.allocate(144 * 4)
     x = backend.allocate(256 * 4)

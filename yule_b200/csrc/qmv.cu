@@ -72,11 +72,16 @@ __device__ __forceinline__ void q4k_scale_min(uint32_t a, uint32_t b, uint32_t c
 // Eight nibbles of one word → exact floats.  Low nibble of byte i → lo[i], high nibble → hi[i].
 // (n | 0x6400) read as a half is 1024+n; (16n | 0x6400) is 1024+16n; one exact half op removes
 // the offset.
-__device__ __forceinline__ void nibbles_to_float(uint32_t w, float lo[4], float hi[4]) {
+// `bit_lo` / `bit_hi` carry a fifth bit per byte (bit 0 of each byte, Q5_K): +16 on the low-nibble
+// value is mantissa bit 4 of 1024+n, +16 on the high-nibble value is bit 8 of 1024+16n.
+__device__ __forceinline__ void nibbles_to_float(uint32_t w, float lo[4], float hi[4], uint32_t bit_lo = 0,
+                                                 uint32_t bit_hi = 0) {
     const uint32_t magic = 0x64006400u;
     uint32_t w8 = w >> 8;
-    uint32_t l02 = (w & 0x000F000Fu) | magic, l13 = (w8 & 0x000F000Fu) | magic;
-    uint32_t h02 = (w & 0x00F000F0u) | magic, h13 = (w8 & 0x00F000F0u) | magic;
+    uint32_t l02 = (w & 0x000F000Fu) | magic | ((bit_lo & 0x00010001u) << 4);
+    uint32_t l13 = (w8 & 0x000F000Fu) | magic | (((bit_lo >> 8) & 0x00010001u) << 4);
+    uint32_t h02 = (w & 0x00F000F0u) | magic | ((bit_hi & 0x00010001u) << 8);
+    uint32_t h13 = (w8 & 0x00F000F0u) | magic | (((bit_hi >> 8) & 0x00010001u) << 8);
     const __half2 k1024 = __float2half2_rn(1024.0f);
     const __half2 k16th = __float2half2_rn(0.0625f);
     const __half2 k64 = __float2half2_rn(-64.0f);
@@ -130,7 +135,9 @@ __device__ __forceinline__ void stage_x(const float *__restrict__ x, uint32_t x_
 // broadcast transaction) and one 16-byte slice of qs — 16 low-nibble columns and the 16
 // high-nibble columns 32 further on.  A warp covers four consecutive super-blocks (576
 // contiguous bytes) per step and walks one row; rows are dealt round-robin to warps.
-template <int NB>
+// Q5: the 176-byte Q5_K super-block (dequant.rs:297-338) — same header, then 32 bytes of fifth
+// bits (bit s of qh[l] belongs to sub-block s, column l) before the 128 bytes of nibbles.
+template <int NB, bool Q5 = false>
 __global__ void __launch_bounds__(kThreads)
 qmv_q4k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
                uint32_t n_rows, uint32_t n_cols, uint32_t x_stride, uint32_t out_stride,
@@ -152,7 +159,8 @@ qmv_q4k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
     const uint32_t n_warps = gridDim.x * kWarps;
 
     for (uint32_t row = warp; row < n_rows; row += n_warps) {
-        const uint4 *rowp = reinterpret_cast<const uint4 *>(w + (size_t)row * bpr * 144);
+        constexpr int kU4 = Q5 ? 11 : 9;  // 16-byte words per super-block
+        const uint4 *rowp = reinterpret_cast<const uint4 *>(w + (size_t)row * bpr * (kU4 * 16));
         float acc[NB];
 #pragma unroll
         for (int b = 0; b < NB; b++) acc[b] = 0.f;
@@ -160,9 +168,11 @@ qmv_q4k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
         for (uint32_t blk0 = 0; blk0 < bpr; blk0 += 4) {
             const uint32_t blk = blk0 + sub;
             if (blk < bpr) {
-                const uint4 *bp = rowp + (size_t)blk * 9;
+                const uint4 *bp = rowp + (size_t)blk * kU4;
                 const uint4 hdr = __ldg(bp);
-                const uint4 q = ld_stream_u4(bp + 1 + j);
+                const uint4 q = ld_stream_u4(bp + (Q5 ? 3 : 1) + j);
+                uint4 fifth = make_uint4(0, 0, 0, 0);
+                if (Q5) fifth = __ldg(bp + 1 + (j & 1));
                 const float d = f16_bits_to_f32(hdr.x & 0xFFFFu);
                 const float dmin = f16_bits_to_f32(hdr.x >> 16);
                 uint32_t sc0, mn0, sc1, mn1;
@@ -172,10 +182,11 @@ qmv_q4k_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
                 const float m0 = dmin * (float)mn0, m1 = dmin * (float)mn1;
 
                 float lo[16], hi[16];
-                nibbles_to_float(q.x, lo + 0, hi + 0);
-                nibbles_to_float(q.y, lo + 4, hi + 4);
-                nibbles_to_float(q.z, lo + 8, hi + 8);
-                nibbles_to_float(q.w, lo + 12, hi + 12);
+                const int sh = 2 * g;
+                nibbles_to_float(q.x, lo + 0, hi + 0, fifth.x >> sh, fifth.x >> (sh + 1));
+                nibbles_to_float(q.y, lo + 4, hi + 4, fifth.y >> sh, fifth.y >> (sh + 1));
+                nibbles_to_float(q.z, lo + 8, hi + 8, fifth.z >> sh, fifth.z >> (sh + 1));
+                nibbles_to_float(q.w, lo + 12, hi + 12, fifth.w >> sh, fifth.w >> (sh + 1));
 
                 const uint32_t col = blk * 256 + 64 * g + 16 * (j & 1);
 #pragma unroll
@@ -447,8 +458,10 @@ qmv_elem_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, floa
 using QmvKernel = void (*)(const uint8_t *, const float *, float *, uint32_t, uint32_t, uint32_t, uint32_t,
                            const float *);
 
+// `aligned`: the weights start on a 16-byte boundary (the Q5_K kernel reads 16-byte words).
 template <int NB>
-QmvKernel pick_kernel(uint32_t type) {
+QmvKernel pick_kernel(uint32_t type, bool aligned) {
+    if (type == YULE_DTYPE_Q5_K && aligned) return qmv_q4k_kernel<NB, true>;
     switch (type) {
         case YULE_DTYPE_Q4_K: return qmv_q4k_kernel<NB>;
         case YULE_DTYPE_Q6_K: return qmv_q6k_kernel<NB>;
@@ -467,7 +480,7 @@ QmvKernel pick_kernel(uint32_t type) {
 
 size_t qmv_smem_bytes(uint32_t type, uint32_t n_cols, int nb) {
     size_t per_vec;
-    if (type == YULE_DTYPE_Q4_K)
+    if (type == YULE_DTYPE_Q4_K || type == YULE_DTYPE_Q5_K)
         per_vec = (size_t)n_cols + n_cols / 32;
     else if (type == YULE_DTYPE_Q6_K || !is_tuned_format(type))
         per_vec = n_cols;
@@ -538,7 +551,9 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             nb = 4;
         else if (left >= 2 && qmv_smem_bytes(a.type, a.n_cols, 2) <= kMaxSmem)
             nb = 2;
-        QmvKernel k = nb == 4 ? pick_kernel<4>(a.type) : nb == 2 ? pick_kernel<2>(a.type) : pick_kernel<1>(a.type);
+        const bool aligned = (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
+        QmvKernel k = nb == 4 ? pick_kernel<4>(a.type, aligned) : nb == 2 ? pick_kernel<2>(a.type, aligned)
+                                                                           : pick_kernel<1>(a.type, aligned);
         if (!k) return cudaErrorInvalidValue;
         size_t smem = qmv_smem_bytes(a.type, a.n_cols, nb);
         // attribute and occupancy are per (kernel, smem): remember the last answer per kernel
