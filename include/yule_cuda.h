@@ -54,7 +54,9 @@ enum {
                                       Parse, InvalidTensorShape, TensorOutOfBounds); the message names which */
 };
 
-/* GGUF type ids accepted where a dtype is asked for (dtype.rs:155-190). */
+/* GGUF type ids accepted where a dtype is asked for (dtype.rs:155-190).  Q4_0, Q8_0, Q4_K and
+ * Q6_K have tuned matvec and GEMM kernels; the other block formats (which Yule's own GPU backends
+ * refuse, yule-gpu/src/cuda/mod.rs:303-307) dequantise bit-exactly and run through slower matvecs. */
 enum {
     YULE_DTYPE_F32 = 0,
     YULE_DTYPE_F16 = 1,
