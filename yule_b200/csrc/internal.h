@@ -230,6 +230,7 @@ struct Q4kFused {
     float eps = 0.f;
     const float *residual = nullptr;  // out[0] += residual when set
     bool swiglu_pair = false;         // w[0], w[1] = gate, up → out[0] = SiLU(gate)·up
+    bool q5 = false;                  // the matrices are Q5_K (176-byte super-blocks), 16-byte aligned
     bool pdl = false;                 // programmatic dependent launch
     const void *next_w[2] = {nullptr, nullptr};  // weights of the kernel(s) that follow: prefetched into L2
     uint64_t next_bytes[2] = {0, 0};

@@ -494,7 +494,8 @@ constexpr size_t kMaxSmem = 200 * 1024;
 }  // namespace
 
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches) {
-    if (a.type == YULE_DTYPE_Q4_K && q4k_mma_supported(a.n_cols, 1)) {
+    const bool q5_mma = a.type == YULE_DTYPE_Q5_K && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0 && !a.tp.push && !a.tp.wait;
+    if ((a.type == YULE_DTYPE_Q4_K || q5_mma) && q4k_mma_supported(a.n_cols, 1)) {
         // tensor-pipe path, up to four activation vectors per pass over the weights
         uint32_t done = 0;
         while (done < a.batch) {
@@ -506,6 +507,7 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             f.rows[0] = a.n_rows;
             f.out_stride[0] = a.out_stride;
             f.n_seg = 1;
+            f.q5 = q5_mma;
             f.x = a.x + (size_t)done * a.x_stride;
             f.x_stride = a.x_stride;
             f.n_cols = a.n_cols;

@@ -55,6 +55,11 @@ __device__ __forceinline__ uint4 ld_stream_u4(const uint4 *p) {
                  : "l"(p));
     return v;
 }
+__device__ __forceinline__ uint2 ld_stream_u2(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::evict_first.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -68,19 +73,35 @@ __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_c
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
 // The three 16-byte pieces one lane needs from one super-block of one row.
+// Q5_K (dequant.rs:297-338) adds the 32 bytes of fifth bits that sit between header and nibbles:
+// bit s of byte l belongs to sub-block s, column l.  All four lanes of a row need all 32 bytes;
+// each keeps a quarter (bytes 8t..8t+7) and hands words out by shuffle when the block is used.
 struct BlockLoads {
     uint4 hdr, qa, qb;
+    uint2 f;  // Q5_K only
 };
 
-template <int NR>  // rows per lane: 2 (ROWS = 16) or 1 (ROWS = 8)
+template <int NR, bool Q5>  // rows per lane: 2 (ROWS = 16) or 1 (ROWS = 8)
 __device__ __forceinline__ void issue_loads(BlockLoads (&ld)[NR], const uint4 *const (&rowp)[NR], uint32_t blk, int t) {
 #pragma unroll
     for (int r = 0; r < NR; r++) {
-        const uint4 *bp = rowp[r] + (size_t)blk * 9;
+        const uint4 *bp = rowp[r] + (size_t)blk * (Q5 ? 11 : 9);
         ld[r].hdr = ld_stream_u4(bp);
-        ld[r].qa = ld_stream_u4(bp + 1 + 2 * t);
-        ld[r].qb = ld_stream_u4(bp + 2 + 2 * t);
+        if (Q5) ld[r].f = ld_stream_u2(reinterpret_cast<const uint2 *>(bp + 1) + t);
+        ld[r].qa = ld_stream_u4(bp + (Q5 ? 3 : 1) + 2 * t);
+        ld[r].qb = ld_stream_u4(bp + (Q5 ? 4 : 2) + 2 * t);
     }
+}
+
+// Fifth bits of the four columns of word wi for this lane's group t, moved to bit 0 of each byte:
+// `.x` for the low-nibble sub-block 2t, `.y` for the high-nibble sub-block 2t+1.
+template <bool Q5>
+__device__ __forceinline__ uint2 fifth_of(const BlockLoads &b, int wi, int t) {
+    if (!Q5) return make_uint2(0u, 0u);
+    // word wi lives in lane (wi >> 1) of this row's quad; every lane of the warp takes part
+    uint32_t f = __shfl_sync(0xFFFFFFFFu, (wi & 1) ? b.f.y : b.f.x, wi >> 1, 4);
+    f >>= 2 * t;
+    return make_uint2(f & 0x01010101u, (f >> 1) & 0x01010101u);
 }
 
 // Word wi (0..7) of the lane's 32 bytes of qs; wi is a compile-time constant after unrolling.
@@ -136,14 +157,17 @@ __device__ __forceinline__ RowScales unpack_scales(const uint4 &hdr, int t) {
 
 // One word = 4 bytes = 4 low-nibble weights (columns c..c+3) + 4 high-nibble weights (c+32..).
 // Fragment halves pair bytes (0,2) and (1,3); B is laid out to match.
-__device__ __forceinline__ void word_to_frags(uint32_t w, const RowScales &s, uint32_t &lo02, uint32_t &lo13,
+// A fifth bit (Q5_K) is +16: mantissa bit 4 of 1024+q, bit 8 of 1024+16q; 31·63 < 2048 stays exact.
+__device__ __forceinline__ void word_to_frags(uint32_t w, const RowScales &s, uint2 fifth, uint32_t &lo02, uint32_t &lo13,
                                               uint32_t &hi02, uint32_t &hi13) {
     const uint32_t magic = 0x64006400u;
     const uint32_t w8 = w >> 8;
-    lo02 = h2_as_u32(__hfma2(u32_as_h2((w & 0x000F000Fu) | magic), s.sc_lo, s.c_lo));
-    lo13 = h2_as_u32(__hfma2(u32_as_h2((w8 & 0x000F000Fu) | magic), s.sc_lo, s.c_lo));
-    hi02 = h2_as_u32(__hfma2(u32_as_h2((w & 0x00F000F0u) | magic), s.sc_hi, s.c_hi));
-    hi13 = h2_as_u32(__hfma2(u32_as_h2((w8 & 0x00F000F0u) | magic), s.sc_hi, s.c_hi));
+    const uint32_t f_lo02 = (fifth.x & 0x00010001u) << 4, f_lo13 = ((fifth.x >> 8) & 0x00010001u) << 4;
+    const uint32_t f_hi02 = (fifth.y & 0x00010001u) << 8, f_hi13 = ((fifth.y >> 8) & 0x00010001u) << 8;
+    lo02 = h2_as_u32(__hfma2(u32_as_h2((w & 0x000F000Fu) | magic | f_lo02), s.sc_lo, s.c_lo));
+    lo13 = h2_as_u32(__hfma2(u32_as_h2((w8 & 0x000F000Fu) | magic | f_lo13), s.sc_lo, s.c_lo));
+    hi02 = h2_as_u32(__hfma2(u32_as_h2((w & 0x00F000F0u) | magic | f_hi02), s.sc_hi, s.c_hi));
+    hi13 = h2_as_u32(__hfma2(u32_as_h2((w8 & 0x00F000F0u) | magic | f_hi13), s.sc_hi, s.c_hi));
 }
 
 // Shared-memory image of the activations for one CTA.  Per vector v:
@@ -375,7 +399,7 @@ __device__ __forceinline__ void stage_activations(const SmemLayout &sm, const fl
 }
 
 // Multiply one super-block (this lane's rows × 64-column group) into the running sums.
-template <int NR>
+template <int NR, bool Q5>
 __device__ __forceinline__ void consume_block(const BlockLoads (&ld)[NR], uint32_t blk, int t, const uint4 *xb_lane,
                                               const uint32_t *sb_lane, float (&acc)[NR][2]) {
     RowScales rs[NR];
@@ -395,7 +419,7 @@ __device__ __forceinline__ void consume_block(const BlockLoads (&ld)[NR], uint32
 #pragma unroll
             for (int r = 0; r < NR; r++) {
                 const uint32_t w = word_of(ld[r], wi);
-                word_to_frags(w, rs[r], lo02[r], lo13[r], hi02[r], hi13[r]);
+                word_to_frags(w, rs[r], fifth_of<Q5>(ld[r], wi, t), lo02[r], lo13[r], hi02[r], hi13[r]);
             }
             if (NR == 1) lo02[1] = lo13[1] = hi02[1] = hi13[1] = 0u;
             mma_16816(dl, lo02[0], lo02[1], lo13[0], lo13[1], e ? bl.z : bl.x, e ? bl.w : bl.y);
@@ -454,9 +478,9 @@ __device__ __forceinline__ RowScalesF unpack_scales_f(const uint4 &hdr, int u, b
     return r;
 }
 
-template <int NR>
+template <int NR, bool Q5>
 __device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR], const uint4 *bp, const float *sfp, int u,
-                                                     bool charge_mins, float (&acc)[NR][2]) {
+                                                     int t, bool charge_mins, float (&acc)[NR][2]) {
     float dl[4] = {0.f, 0.f, 0.f, 0.f}, dh[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int wp = 0; wp < 4; wp++) {
@@ -472,6 +496,14 @@ __device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR],
                 lo13[r] = w8 & 0x000F000Fu;
                 hi02[r] = w & 0x00F000F0u;
                 hi13[r] = w8 & 0x00F000F0u;
+                if (Q5) {
+                    // the fifth bit extends the subnormal: bit 4 of q·2^-24, bit 8 of 16q·2^-24
+                    const uint2 f = fifth_of<Q5>(ld[r], wi, t);
+                    lo02[r] |= (f.x & 0x00010001u) << 4;
+                    lo13[r] |= ((f.x >> 8) & 0x00010001u) << 4;
+                    hi02[r] |= (f.y & 0x00010001u) << 8;
+                    hi13[r] |= ((f.y >> 8) & 0x00010001u) << 8;
+                }
             }
             if (NR == 1) lo02[1] = lo13[1] = hi02[1] = hi13[1] = 0u;
             mma_16816(dl, lo02[0], lo02[1], lo13[0], lo13[1], e ? bl.z : bl.x, e ? bl.w : bl.y);
@@ -520,7 +552,7 @@ __device__ __forceinline__ void group_barrier(int group) {
 
 // Walks one warp's units in order: tile index k (of its group), matrix q (pair mode), super-block
 // slot j; the row pointers are recomputed only when the tile or matrix changes.
-template <int ROWS>
+template <int ROWS, bool Q5>
 struct UnitCursor {
     static constexpr int NR = ROWS / 8;
     uint32_t k, q, j;
@@ -542,7 +574,7 @@ struct UnitCursor {
         for (int r = 0; r < NR; r++) {
             uint32_t row = tile * ROWS + g + 8 * r;
             row = row < n_rows ? row : n_rows - 1;  // clamp: the load stays in bounds, the result is dropped
-            rowp[r] = reinterpret_cast<const uint4 *>(p.w[seg] + (size_t)row * bpr * 144);
+            rowp[r] = reinterpret_cast<const uint4 *>(p.w[seg] + (size_t)row * bpr * (Q5 ? 176 : 144));
         }
     }
     __device__ __forceinline__ void advance(const Q4kMmaParams &p, uint32_t first_tile, uint32_t tile_stride, uint32_t bpr,
@@ -566,7 +598,7 @@ struct UnitCursor {
 // the same rows of up.  The activations are staged once per CTA.
 // TP = true only for launches of a tensor-parallel runner that push or poll (value, epoch) pairs: the
 // single-GPU instantiations carry none of that code.
-template <int ROWS, int DEPTH, bool SUBCOL, bool TP>
+template <int ROWS, int DEPTH, bool SUBCOL, bool TP, bool Q5>
 __global__ void __launch_bounds__(kThreadsCta, 1)
 qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     constexpr int NR = ROWS / 8;
@@ -588,7 +620,7 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
     const SmemLayout sm = carve(smem_raw, p.n_cols, p.batch);
     float *partial = sm.partial + (size_t)group * kRoundSlots * kWarps * 4 * 16;
 
-    UnitCursor<ROWS> ld_cur;
+    UnitCursor<ROWS, Q5> ld_cur;
     ld_cur.k = ld_cur.q = ld_cur.j = 0;
     const uint32_t total_units = my_tiles * nq * nbw;
     uint32_t issued = 0;
@@ -598,7 +630,7 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
 #pragma unroll
         for (int i = 0; i < DEPTH; i++) {
             if (issued < total_units) {
-                issue_loads<NR>(buf[i], ld_cur.rowp, wid + kWarps * ld_cur.j, t);
+                issue_loads<NR, Q5>(buf[i], ld_cur.rowp, wid + kWarps * ld_cur.j, t);
                 issued++;
                 if (issued < total_units) ld_cur.advance(p, first_tile, tile_stride, bpr, g, nbw, nq);
             }
@@ -693,13 +725,13 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
             if (base + i < total_units) {
                 if (SUBCOL) {
                     const uint32_t blk = wid + kWarps * in_slot;
-                    consume_block_subcol<NR>(buf[i], sub_base + (size_t)blk * sub_stride, sm.sf + (size_t)blk * 8 + 4 * u, u,
-                                             charge_mins, acc);
+                    consume_block_subcol<NR, Q5>(buf[i], sub_base + (size_t)blk * sub_stride, sm.sf + (size_t)blk * 8 + 4 * u,
+                                                 u, t, charge_mins, acc);
                 } else {
-                    consume_block<NR>(buf[i], wid + kWarps * in_slot, t, xb_lane, sb_lane, acc);
+                    consume_block<NR, Q5>(buf[i], wid + kWarps * in_slot, t, xb_lane, sb_lane, acc);
                 }
                 if (issued < total_units) {
-                    issue_loads<NR>(buf[i], ld_cur.rowp, wid + kWarps * ld_cur.j, t);
+                    issue_loads<NR, Q5>(buf[i], ld_cur.rowp, wid + kWarps * ld_cur.j, t);
                     issued++;
                     if (issued < total_units) ld_cur.advance(p, first_tile, tile_stride, bpr, g, nbw, nq);
                 }
@@ -725,10 +757,11 @@ qmv_q4k_mma_kernel(const __grid_constant__ Q4kMmaParams p) {
 
 }
 
-template <int ROWS, int DEPTH, bool SUBCOL, bool TP = false>
+template <int ROWS, int DEPTH, bool SUBCOL, bool Q5 = false, bool TP = false>
 cudaError_t launch_variant(const Q4kMmaParams &p, int sm_count, size_t smem, bool pdl, cudaStream_t s) {
-    if (!TP && (p.tp.push || p.tp.wait)) return launch_variant<ROWS, DEPTH, SUBCOL, true>(p, sm_count, smem, pdl, s);
-    auto kern = qmv_q4k_mma_kernel<ROWS, DEPTH, SUBCOL, TP>;
+    if (!TP && !Q5 && (p.tp.push || p.tp.wait))
+        return launch_variant<ROWS, DEPTH, SUBCOL, false, true>(p, sm_count, smem, pdl, s);
+    auto kern = qmv_q4k_mma_kernel<ROWS, DEPTH, SUBCOL, TP, Q5>;
     // per instantiation: the opt-in for large dynamic shared memory
     static bool attr_done = false;
     static std::mutex mu;
@@ -794,7 +827,14 @@ cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint
     if (n_tiles == 0) return cudaSuccess;
     const size_t smem = smem_bytes(f.n_cols, f.batch);
     cudaError_t e;
-    if (f.batch == 1)
+    if (f.q5 && (f.tp.push || f.tp.wait)) return cudaErrorInvalidValue;  // the exchange is built for Q4_K only
+    if (f.q5 && f.batch == 1)
+        e = tile_rows == 8 ? launch_variant<8, 4, true, true>(p, sm_count, smem, f.pdl, s)
+                           : launch_variant<16, 2, true, true>(p, sm_count, smem, f.pdl, s);
+    else if (f.q5)
+        e = tile_rows == 8 ? launch_variant<8, 4, false, true>(p, sm_count, smem, f.pdl, s)
+                           : launch_variant<16, 2, false, true>(p, sm_count, smem, f.pdl, s);
+    else if (f.batch == 1)
         e = tile_rows == 8 ? launch_variant<8, 4, true>(p, sm_count, smem, f.pdl, s)
                            : launch_variant<16, 2, true>(p, sm_count, smem, f.pdl, s);
     else
