@@ -146,8 +146,9 @@ int32_t yule_cuda_quantized_matmul(yule_cuda_ctx *ctx, yule_buffer weights, yule
 /* `batch` activation vectors against one weight read: input is
  * [batch][x_stride] floats, output [batch][out_stride] floats.  Same per-row
  * arithmetic as quantized_matmul.  Small batches go through the matvec kernels
- * four vectors at a time; from 16 vectors of Q4_K, or 32 of Q6_K / Q8_0 / Q4_0
- * (n_cols a multiple of 256), the tcgen05 GEMM takes one pass over the weights.
+ * four vectors at a time; from 16 vectors of Q4_K, 32 of Q6_K / Q8_0 / Q4_0, or
+ * 64 of the other block formats (n_cols a multiple of 256), the tcgen05 GEMM
+ * takes one pass over the weights.
  * The GEMM keeps its activation tiles in a scratch owned by the context, grown
  * on demand; growing is not possible while a graph is being captured, so run
  * one call of the largest batch before yule_cuda_graph_begin. */
@@ -258,7 +259,7 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
 int32_t yule_cuda_runner_destroy(yule_cuda_runner *runner);
 /* Register an uploaded tensor under its GGUF name ("token_embd.weight",
  * "blk.%u.attn_q.weight", "output_norm.weight", …; gpu_runner.rs:171-254).
- * Norm weights are F32 or F16; matrices are Q4_0/Q8_0/Q4_K/Q6_K. */
+ * Norm weights are F32 or F16; matrices are any block format of the enum above. */
 int32_t yule_cuda_runner_set_tensor(yule_cuda_runner *runner, const char *name, yule_buffer handle,
                                     uint32_t gguf_type);
 /* ModelRunner::prefill — token-by-token forward (gpu_runner.rs:703-709);

@@ -97,10 +97,11 @@ def test_gemm_equals_matvec_path(backend):
     assert guarded_rel_err(y8.reshape(-1), y4.reshape(-1)) <= REL_TOL
 
 
-@pytest.mark.parametrize("dtype", [DType.Q6_K, DType.Q8_0, DType.Q4_0, DType.Q4_K])
+@pytest.mark.parametrize("dtype", [DType.Q6_K, DType.Q8_0, DType.Q4_0, DType.Q4_K, DType.Q5_K, DType.Q5_0, DType.Q4_1, DType.Q5_1,
+                                   DType.Q8_1, DType.Q3_K, DType.Q2_K])
 @pytest.mark.parametrize("n_rows,n_cols,batch", [(200, 512, 9), (513, 2048, 64), (1024, 1024, 200)])
 def test_generic_format_gemm(backend, oracle, monkeypatch, dtype, n_rows, n_cols, batch):
-    """Q6_K, Q8_0 and Q4_0 (and Q4_K when forced) go through the kernel whose producers dequantise with the
+    """Every format but Q4_K (and Q4_K when forced) goes through the kernel whose producers dequantise with the
     bit-exact per-element routine and split the weight into fp16 hi + lo."""
     monkeypatch.setenv("YULE_GEMM_GENERIC", "1")
     w = synth.random_blocks(dtype, 500 + n_rows, n_rows * (n_cols // dtype.block_size))

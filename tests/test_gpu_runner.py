@@ -159,10 +159,12 @@ PREFILL_CFG = ModelConfig(dim=256, n_layers=3, n_heads=4, n_kv_heads=2, head_dim
 
 
 @pytest.mark.parametrize("chunk,n_prompt,mix", [(None, 40, "q4k"), ("16", 45, "q4k"), ("8", 17, "q4k"), (None, 150, "q4k"),
-                                                 (None, 40, "q4k_q6k"), ("16", 45, "q8_0"), (None, 33, "q4_0"), (None, 24, "q6k")])
+                                                 (None, 40, "q4k_q6k"), ("16", 45, "q8_0"), (None, 33, "q4_0"), (None, 24, "q6k"),
+                                                 (None, 40, "q5k"), ("16", 37, "q5_0_q4_1")])
 def test_batched_prefill_matches_cpu_runner_and_token_path(backend, oracle, monkeypatch, chunk, n_prompt, mix):
     kw = {"q4k": dict(linear=DType.Q4_K), "q4k_q6k": dict(linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K),
-          "q8_0": dict(linear=DType.Q8_0), "q4_0": dict(linear=DType.Q4_0), "q6k": dict(linear=DType.Q6_K)}[mix]
+          "q8_0": dict(linear=DType.Q8_0), "q4_0": dict(linear=DType.Q4_0), "q6k": dict(linear=DType.Q6_K),
+          "q5k": dict(linear=DType.Q5_K), "q5_0_q4_1": dict(linear=DType.Q5_0, ffn_down=DType.Q4_1)}[mix]
     weights = synth.synthetic_model(PREFILL_CFG, seed=11, std=0.05, **kw)
     ref = make_oracle_model(oracle, PREFILL_CFG, weights)
     prompt = synth.tokens(12, n_prompt, PREFILL_CFG.vocab_size)

@@ -227,7 +227,29 @@ __device__ __forceinline__ void dequant8_unit(const unsigned char *unit, uint32_
             v[2 * k] = __fmul_rn(ds, (float)q0);
             v[2 * k + 1] = __fmul_rn(ds, (float)q1);
         }
+    } else if (type == YULE_DTYPE_Q5_K) {
+        // dequant.rs:297-338: eight columns of sub-block s; nibbles of group s/2, fifth bits in bit s of qh
+        const uint32_t s = col0 >> 5, l0 = col0 & 31u;
+        uint32_t sc, mn;
+        if (s < 4) {
+            sc = unit[4 + s] & 63u;
+            mn = unit[8 + s] & 63u;
+        } else {
+            sc = (unit[8 + s] & 0xFu) | ((unit[s] >> 6) << 4);
+            mn = (unit[8 + s] >> 4) | ((unit[4 + s] >> 6) << 4);
+        }
+        const float ds = __fmul_rn(f16_bits_to_f32(u16_at(0)), (float)sc);
+        const float dm = __fmul_rn(f16_bits_to_f32(u16_at(2)), (float)mn);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t ql = u16_at(48 + 32 * (s >> 1) + l0 + 2 * k) >> (4 * (s & 1u));
+            const uint32_t qh = u16_at(16 + l0 + 2 * k) >> s;
+            const uint32_t q0 = (ql & 0xFu) | ((qh & 1u) << 4), q1 = ((ql >> 8) & 0xFu) | (((qh >> 8) & 1u) << 4);
+            v[2 * k] = __fsub_rn(__fmul_rn((float)q0, ds), dm);
+            v[2 * k + 1] = __fsub_rn(__fmul_rn((float)q1, ds), dm);
+        }
     } else {
+        // the remaining formats: the per-element decoders (block index from the column)
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = dequant_elem(unit, type, col0 + i);
     }
@@ -869,7 +891,7 @@ uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 
 // Q4_K runs on the exact-integer kernel; Q6_K, Q8_0 and Q4_0 on the generic one (YULE_GEMM_GENERIC=1
 // sends Q4_K there too, for comparison).  The activation tiles are laid out per 256 columns.
 bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens) {
-    return is_tuned_format(type) && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
+    return is_quantized(type) && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
 }
 
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols) {
