@@ -141,10 +141,10 @@ def ModelConfigOneLayer(cfg):
     return dataclasses.replace(cfg, n_layers=1)
 
 
-def build_model(rank: int):
+def build_model(rank: int, linear: str = "Q4_K"):
     from yule_b200 import DType, synth
     cfg = synth.TINYLLAMA
-    weights = synth.synthetic_model(cfg, seed=2024, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
+    weights = synth.synthetic_model(cfg, seed=2024, linear=DType[linear], ffn_down=DType.Q6_K, output=DType.Q6_K)
     prompt = synth.tokens(99 + rank, N_PROMPT, cfg.vocab_size)
     return cfg, weights, prompt
 
@@ -306,7 +306,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
             backend.tp_init(rank, world, ids[0])
         cfg, weights, prompt = build_model_70b(rank, world, args.workload)
     else:
-        cfg, weights, prompt = build_model(rank)
+        cfg, weights, prompt = build_model(rank, args.linear)
     runner = CudaTransformerRunner(backend, cfg, weights, fused=True)
 
     def job():
@@ -391,10 +391,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
                                        "NCCL all-gather of activations",
                         "l2": "weights read per token per GPU (GBs) exceed the 126 MB L2; no flush needed"}
                        if tp else
-                       {"workload": "configs[1] TinyLlama-1.1B-arch decode, Q4_K linears, Q6_K output+ffn_down, "
+                       {"workload": f"configs[1] TinyLlama-1.1B-arch decode, {args.linear} linears, Q6_K output+ffn_down, "
                                     f"fp32 KV, batch 1, {N_PROMPT}-token prompt + {N_GEN} greedy tokens per step",
                         "parallelism": f"{world} independent replica(s), one sequence per GPU",
-                        "l2": "weights read per token (664 MB) exceed the 126 MB L2; no flush needed"}),
+                        "l2": f"weights read per token ({bpt / 1e6:.0f} MB) exceed the 126 MB L2; no flush needed"}),
             "decode": {"ms_per_token": round(decode_ms / (N_GEN * args.steps), 4),
                        "prefill_tokens_per_s": round(N_PROMPT * args.steps / (prefill_ms * 1e-3), 1),
                        "hbm_bytes_per_token": bpt, "achieved_gbs": round(decode_gbs, 1),
@@ -428,6 +428,8 @@ def main() -> int:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized run: 4-token prompt + 4 tokens, 20 ring launches, no CPU leg")
+    ap.add_argument("--linear", default="Q4_K", choices=["Q4_K", "Q5_K", "Q8_0", "Q4_0", "Q5_0"],
+                    help="diagnostic: block format of the c1 workload's linears (the metric is quoted on Q4_K)")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="diagnostic: override the workload's prompt length")
     ap.add_argument("--gen-tokens", type=int, default=0, help="diagnostic: override the workload's generated tokens")
     args = ap.parse_args()

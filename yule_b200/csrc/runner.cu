@@ -298,6 +298,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             if (t->type != YULE_DTYPE_Q4_K) return false;
         return q4k_mma_supported(cols, 1);
     };
+    // Matrices that can share one launch of the tensor-pipe kernel: all Q4_K, or (single GPU) all Q5_K.
+    auto all_mma = [&](std::initializer_list<const Tensor *> ts, uint32_t cols) {
+        if (all_q4k(ts, cols)) return true;
+        if (N > 1) return false;
+        for (const Tensor *t : ts)
+            if (t->type != YULE_DTYPE_Q5_K || (reinterpret_cast<uintptr_t>(t->buf.ptr) & 15)) return false;
+        return q4k_mma_supported(cols, 1);
+    };
     // Tensor parallelism folded into the Q4_K matvecs: when both the kernel that produces a gathered vector
     // and the one that consumes it are the Q4_K tensor-pipe kernel, the producer stores (value, epoch) pairs
     // straight into every rank's pair buffer as its rows are reduced and the consumer polls the pairs while it
@@ -339,6 +347,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         Q4kFused f;
         if (tp) f.tp = *tp;
         uint32_t i = 0;
+        f.q5 = segs.begin()->first->type == YULE_DTYPE_Q5_K;
         for (auto &sg : segs) {
             f.w[i] = (const uint8_t *)sg.first->buf.ptr;
             f.out[i] = sg.second.first;
@@ -371,7 +380,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         const Tensor &out_w_ = r->output.set ? r->output : r->token_embd;
         st.then(&L.attn_output);  // while Q/K/V and attention run, o-proj's weights come in
         if (skip & 1) {
-        } else if (all_q4k({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
+        } else if (all_mma({&L.attn_q, &L.attn_k, &L.attn_v}, dim)) {
             TpFuse tq;
             if (l > 0 && folded(l - 1, 3)) add_wait(tq, r->x_pair_hidden, l - 1, 3);
             fused({{&L.attn_q, {r->q, qdim_l}}, {&L.attn_k, {r->k_tmp, kvdim_l}}, {&L.attn_v, {r->v_tmp, kvdim_l}}},
@@ -429,7 +438,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         if (!folded(l, 1)) gather(r->hidden, r->x_hidden, dim_l, l, 1);
         st.then(&L.ffn_down);
         if (skip & 16) {
-        } else if (all_q4k({&L.ffn_gate, &L.ffn_up}, dim)) {
+        } else if (all_mma({&L.ffn_gate, &L.ffn_up}, dim)) {
             TpFuse tg;
             if (folded(l, 2)) tg = push_of(r->x_pair_gate, ff_l, l, 2);
             if (folded(l, 1)) add_wait(tg, r->x_pair_hidden, l, 1);
@@ -458,7 +467,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     st.then(nullptr);
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     if (skip & 64) {
-    } else if (all_q4k({&out_w}, dim)) {
+    } else if (all_mma({&out_w}, dim)) {
         TpFuse tw;
         if (c.n_layers && folded(c.n_layers - 1, 3)) add_wait(tw, r->x_pair_hidden, c.n_layers - 1, 3);
         fused({{&out_w, {r->logits + (size_t)R * vocab_l, vocab_l}}}, r->hidden, dim, r->output_norm_f32, nullptr, false, &tw);
