@@ -15,11 +15,15 @@ pytestmark = pytest.mark.gpu
 CFG = ModelConfig(dim=256, n_layers=3, n_heads=4, n_kv_heads=2, head_dim=64, vocab_size=512, ff_dim=768, max_seq_len=96)
 
 
-@pytest.mark.parametrize("mix", ["q4k_q6k_f16norm", "q8_0_tied"])
+@pytest.mark.parametrize("mix", ["q4k_q6k_f16norm", "q8_0_tied", "q5k_q6k", "q5_0_q4_1"])
 def test_loaded_runner_equals_hand_built_runner(backend, oracle, tmp_path, mix):
     if mix == "q4k_q6k_f16norm":
         weights = synth.synthetic_model(CFG, seed=21, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K,
                                         norm_dtype=DType.F16)
+    elif mix == "q5k_q6k":  # the layout of a Q5_K_M file: formats Yule's own GPU backends refuse
+        weights = synth.synthetic_model(CFG, seed=25, std=0.05, linear=DType.Q5_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
+    elif mix == "q5_0_q4_1":
+        weights = synth.synthetic_model(CFG, seed=26, std=0.05, linear=DType.Q5_0, ffn_down=DType.Q4_1, token_embd=DType.Q5_1)
     else:
         weights = synth.synthetic_model(CFG, seed=22, std=0.05, linear=DType.Q8_0)
         del weights["output.weight"]  # tied embedding: the loader falls back to token_embd (gpu_runner.rs:209-210)

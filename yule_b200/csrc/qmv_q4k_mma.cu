@@ -95,12 +95,17 @@ __device__ __forceinline__ void issue_loads(BlockLoads (&ld)[NR], const uint4 *c
 
 // Fifth bits of the four columns of word wi for this lane's group t, moved to bit 0 of each byte:
 // `.x` for the low-nibble sub-block 2t, `.y` for the high-nibble sub-block 2t+1.
+// Word wi of the 32 bytes of fifth bits: it lives in lane (wi >> 1) of this row's quad; every lane of
+// the warp takes part in the shuffle.
+template <bool Q5>
+__device__ __forceinline__ uint32_t fifth_word(const BlockLoads &b, int wi) {
+    if (!Q5) return 0u;
+    return __shfl_sync(0xFFFFFFFFu, (wi & 1) ? b.f.y : b.f.x, wi >> 1, 4);
+}
 template <bool Q5>
 __device__ __forceinline__ uint2 fifth_of(const BlockLoads &b, int wi, int t) {
     if (!Q5) return make_uint2(0u, 0u);
-    // word wi lives in lane (wi >> 1) of this row's quad; every lane of the warp takes part
-    uint32_t f = __shfl_sync(0xFFFFFFFFu, (wi & 1) ? b.f.y : b.f.x, wi >> 1, 4);
-    f >>= 2 * t;
+    const uint32_t f = fifth_word<Q5>(b, wi) >> (2 * t);
     return make_uint2(f & 0x01010101u, (f >> 1) & 0x01010101u);
 }
 
@@ -453,6 +458,7 @@ struct RowScalesF {
     float mn[4];  // mn[4u + i] · dmin, zero in the lanes of the lo part (mins are charged once)
 };
 
+template <bool Q5>
 __device__ __forceinline__ RowScalesF unpack_scales_f(const uint4 &hdr, int u, bool charge_mins) {
     uint32_t sc4, mn4;  // four 6-bit values each, one per byte (dequant.rs:176-190)
     if (u == 0) {
@@ -464,7 +470,8 @@ __device__ __forceinline__ RowScalesF unpack_scales_f(const uint4 &hdr, int u, b
     }
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
     const float dmin = charge_mins ? __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16))) : 0.f;
-    const float d24 = d * 16777216.0f, d20 = d * 1048576.0f;
+    // Q5_K operands carry q·2^-24 in both halves; Q4_K's high nibbles stay in place (16q·2^-24)
+    const float d24 = d * 16777216.0f, d20 = Q5 ? d24 : d * 1048576.0f;
     const float k23 = 8388608.0f;
     RowScalesF r;
     r.sc[0] = (__uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7440)) - k23) * d24;
@@ -492,17 +499,22 @@ __device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR],
 #pragma unroll
             for (int r = 0; r < NR; r++) {
                 const uint32_t w = word_of(ld[r], wi), w8 = w >> 8;
-                lo02[r] = w & 0x000F000Fu;
-                lo13[r] = w8 & 0x000F000Fu;
-                hi02[r] = w & 0x00F000F0u;
-                hi13[r] = w8 & 0x00F000F0u;
                 if (Q5) {
-                    // the fifth bit extends the subnormal: bit 4 of q·2^-24, bit 8 of 16q·2^-24
-                    const uint2 f = fifth_of<Q5>(ld[r], wi, t);
-                    lo02[r] |= (f.x & 0x00010001u) << 4;
-                    lo13[r] |= ((f.x >> 8) & 0x00010001u) << 4;
-                    hi02[r] |= (f.y & 0x00010001u) << 8;
-                    hi13[r] |= ((f.y >> 8) & 0x00010001u) << 8;
+                    // four 5-bit values per register first (nibble | fifth bit << 4), then one byte
+                    // permute per operand: both halves of the word are q·2^-24 (no factor 16 on the
+                    // high nibbles, see unpack_scales_f)
+                    const uint32_t f = fifth_word<Q5>(ld[r], wi) >> (2 * t);
+                    const uint32_t cl = (w & 0x0F0F0F0Fu) | ((f << 4) & 0x10101010u);
+                    const uint32_t ch = ((w >> 4) & 0x0F0F0F0Fu) | ((f << 3) & 0x10101010u);
+                    lo02[r] = __byte_perm(cl, 0u, 0x4240);
+                    lo13[r] = __byte_perm(cl, 0u, 0x4341);
+                    hi02[r] = __byte_perm(ch, 0u, 0x4240);
+                    hi13[r] = __byte_perm(ch, 0u, 0x4341);
+                } else {
+                    lo02[r] = w & 0x000F000Fu;
+                    lo13[r] = w8 & 0x000F000Fu;
+                    hi02[r] = w & 0x00F000F0u;
+                    hi13[r] = w8 & 0x00F000F0u;
                 }
             }
             if (NR == 1) lo02[1] = lo13[1] = hi02[1] = hi13[1] = 0u;
@@ -513,7 +525,7 @@ __device__ __forceinline__ void consume_block_subcol(const BlockLoads (&ld)[NR],
     const float4 sx = *reinterpret_cast<const float4 *>(sfp);  // Σx of sub-blocks 4u..4u+3
 #pragma unroll
     for (int r = 0; r < NR; r++) {
-        const RowScalesF rs = unpack_scales_f(ld[r].hdr, u, charge_mins);
+        const RowScalesF rs = unpack_scales_f<Q5>(ld[r].hdr, u, charge_mins);
         float a = acc[r][0];
         a = fmaf(rs.sc[0], dl[2 * r + 0], a);
         a = fmaf(rs.sc[1], dh[2 * r + 0], a);
