@@ -393,10 +393,65 @@ qmv_q32_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float
 }
 
 // ── formats without a tuned kernel ──────────────────────────────────────────────────────────
+// Eight consecutive weights of a row (columns 8·run .. 8·run+7, inside one sub-block of every
+// format) with 16-bit loads: one header decode per call.  Rows start 2-byte aligned and every block
+// size is even, so the 16-bit loads are aligned.  Same arithmetic as the per-element decoders.
+template <uint32_t TYPE>
+__device__ __forceinline__ void dequant8_row(const uint8_t *rowp, uint32_t run, float (&v)[8]) {
+    if (TYPE == YULE_DTYPE_Q8_1) {
+        const uint8_t *bp = rowp + (size_t)(run >> 2) * 36;
+        const float d = f16_bits_to_f32(ld_stream_u16(bp));
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t w = ld_stream_u16(bp + 4 + (run & 3u) * 8 + 2 * k);
+            v[2 * k] = (float)(int)(signed char)(w & 0xFFu) * d;
+            v[2 * k + 1] = (float)(int)(signed char)(w >> 8) * d;
+        }
+    } else if (TYPE == YULE_DTYPE_Q4_1 || TYPE == YULE_DTYPE_Q5_0 || TYPE == YULE_DTYPE_Q5_1) {
+        constexpr uint32_t BB = TYPE == YULE_DTYPE_Q4_1 ? 20 : TYPE == YULE_DTYPE_Q5_0 ? 22 : 24;
+        constexpr bool HAS_M = TYPE != YULE_DTYPE_Q5_0, HAS_QH = TYPE != YULE_DTYPE_Q4_1;
+        constexpr uint32_t QH = HAS_M ? 4 : 2, QS = QH + (HAS_QH ? 4 : 0);
+        const uint8_t *bp = rowp + (size_t)(run >> 2) * BB;
+        const uint32_t part = run & 3u;  // which 8 of the block's 32 weights
+        const float d = f16_bits_to_f32(ld_stream_u16(bp));
+        const float m = HAS_M ? f16_bits_to_f32(ld_stream_u16(bp + 2)) : 0.f;
+        const uint32_t qh = HAS_QH ? ld_stream_u8(bp + QH + part) : 0u;
+        const uint32_t qs = ld_stream_u16(bp + QS + part * 4) | (ld_stream_u16(bp + QS + part * 4 + 2) << 16);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const float q = (float)(((qs >> (4 * k)) & 0xFu) | (((qh >> k) & 1u) << 4));
+            v[k] = HAS_M ? fmaf(q, d, m) : (q - 16.0f) * d;
+        }
+    } else if (TYPE == YULE_DTYPE_Q2_K) {
+        const uint8_t *bp = rowp + (size_t)(run >> 5) * 84;
+        const uint32_t i0 = (run & 31u) * 8;
+        const uint32_t sm = ld_stream_u8(bp + (i0 >> 4));
+        const float ds = f16_bits_to_f32(ld_stream_u16(bp + 80)) * (float)(sm & 0xFu);
+        const float dm = f16_bits_to_f32(ld_stream_u16(bp + 82)) * (float)(sm >> 4);
+        const uint32_t qs = ld_stream_u16(bp + 16 + (i0 >> 2));
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = fmaf(ds, (float)((qs >> (2 * k)) & 3u), -dm);
+    } else if (TYPE == YULE_DTYPE_Q3_K) {
+        const uint8_t *bp = rowp + (size_t)(run >> 5) * 110;
+        const uint32_t i0 = (run & 31u) * 8, j = i0 >> 4;
+        const uint32_t lo4 = j < 8 ? (ld_stream_u8(bp + 96 + j) & 0xFu) : (ld_stream_u8(bp + 88 + j) >> 4);
+        const uint32_t hi2 = (ld_stream_u8(bp + 104 + (j >> 2)) >> (2 * (j & 3u))) & 3u;
+        const float ds = f16_bits_to_f32(ld_stream_u16(bp + 108)) * (float)((int)(lo4 | (hi2 << 4)) - 32);
+        const uint32_t qs = ld_stream_u16(bp + 32 + (i0 >> 2));
+        const uint32_t hm = ld_stream_u8(bp + (i0 >> 3));
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            v[k] = ds * (float)((int)(((qs >> (2 * k)) & 3u) | (((hm >> k) & 1u) << 2)) - 4);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = dequant_row_elem<TYPE>(rowp, run * 8 + k);
+    }
+}
+
 // One warp per row, a lane per run of 8 consecutive columns (inside one sub-block of every
-// format, so the scale decode is shared by the 8 weights); the weights are dequantised with the
-// per-element functions and accumulated in f32.  Correct for any row length that is a multiple
-// of the block size; not tuned: the byte-wise loads keep it far below the HBM roofline.
+// format, so the scale decode is shared by the 8 weights), accumulated in f32.  Correct for any
+// row length that is a multiple of the block size; not tuned: narrow loads and a scalar decode
+// keep it far below the HBM roofline.
 template <int NB, uint32_t TYPE>
 __global__ void __launch_bounds__(kThreads)
 qmv_elem_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
@@ -424,8 +479,7 @@ qmv_elem_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x, floa
         for (int b = 0; b < NB; b++) acc[b] = 0.f;
         for (uint32_t run = lane; run < n_runs; run += 32) {
             float wv[8];
-#pragma unroll
-            for (int k = 0; k < 8; k++) wv[k] = dequant_row_elem<TYPE>(rowp, run * 8 + k);
+            dequant8_row<TYPE>(rowp, run, wv);
 #pragma unroll
             for (int b = 0; b < NB; b++) {
                 const float4 a0 = *reinterpret_cast<const float4 *>(xs + (size_t)b * n_cols + run * 8);
