@@ -75,11 +75,12 @@ def main() -> None:
     ap.add_argument("--sweep", action="store_true",
                     help="the format x shape x batch grid of the matvec sweep (4 formats, 5 shapes, batch 1/4/16), "
                          "weights streamed from HBM; prints one JSON line per case")
+    ap.add_argument("--formats", default="Q4_0,Q8_0,Q4_K,Q6_K", help="comma-separated formats of --sweep")
     args = ap.parse_args()
     backend = CudaB200Backend(0)
     if args.sweep:
         shapes = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]
-        for dt in (DType.Q4_0, DType.Q8_0, DType.Q4_K, DType.Q6_K):
+        for dt in [DType[n] for n in args.formats.split(",")]:
             for rows, cols in shapes:
                 for batch in (1, 4, 16):
                     iters = 20 if rows * cols > 10 ** 8 else 100
