@@ -439,14 +439,14 @@ int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffe
 
 // From how many activation rows the tcgen05 GEMM beats ceil(batch / 4) passes of the matvec kernels
 // (measured on 4096x4096 .. 128256x4096): the exact Q4_K kernel from 16, the generic kernel of the
-// Q6_K / Q8_0 / Q4_0 from 32, the formats whose GEMM producers decode element by element (and Q5_K) from 64.
+// other formats from 32, except Q5_K (tensor-pipe matvec at 3.5 us per row against a 195 us GEMM) from 64.
 // YULE_GEMM_MIN_BATCH overrides all three (at least 8).
 static uint32_t gemm_min_batch(uint32_t type) {
     if (const char *e = getenv("YULE_GEMM_MIN_BATCH")) {
         const int v = atoi(e);
         return v < 8 ? 8u : (uint32_t)v;
     }
-    return type == YULE_DTYPE_Q4_K ? 16u : is_tuned_format(type) ? 32u : 64u;
+    return type == YULE_DTYPE_Q4_K ? 16u : type == YULE_DTYPE_Q5_K ? 64u : 32u;
 }
 
 static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset, yule_buffer input,

@@ -248,8 +248,49 @@ __device__ __forceinline__ void dequant8_unit(const unsigned char *unit, uint32_
             v[2 * k] = __fsub_rn(__fmul_rn((float)q0, ds), dm);
             v[2 * k + 1] = __fsub_rn(__fmul_rn((float)q1, ds), dm);
         }
+    } else if (type == YULE_DTYPE_Q2_K) {
+        // dequant.rs:196-214: (d*scale)*q - dmin*min, sub-blocks of 16
+        const uint32_t sm = unit[col0 >> 4];
+        const float ds = __fmul_rn(f16_bits_to_f32(u16_at(80)), (float)(sm & 0xFu));
+        const float dm = __fmul_rn(f16_bits_to_f32(u16_at(82)), (float)(sm >> 4));
+        const uint32_t qs = u16_at(16 + (col0 >> 2));
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = __fsub_rn(__fmul_rn(ds, (float)((qs >> (2 * k)) & 3u)), dm);
+    } else if (type == YULE_DTYPE_Q3_K) {
+        // dequant.rs:219-251: 6-bit scale centred at 32, 3-bit weight centred at 4
+        const uint32_t j = col0 >> 4;
+        const uint32_t lo4 = j < 8 ? (unit[96 + j] & 0xFu) : (unit[88 + j] >> 4);
+        const uint32_t hi2 = (unit[104 + (j >> 2)] >> (2 * (j & 3u))) & 3u;
+        const float ds = __fmul_rn(f16_bits_to_f32(u16_at(108)), (float)((int)(lo4 | (hi2 << 4)) - 32));
+        const uint32_t qs = u16_at(32 + (col0 >> 2)), hm = unit[col0 >> 3];
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            v[k] = __fmul_rn(ds, (float)((int)(((qs >> (2 * k)) & 3u) | (((hm >> k) & 1u) << 2)) - 4));
+    } else if (type == YULE_DTYPE_Q8_1) {
+        const uint32_t b = (col0 >> 5) * 36, i0 = col0 & 31u;
+        const float d = f16_bits_to_f32(u16_at(b));
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t w = u16_at(b + 4 + i0 + 2 * k);
+            v[2 * k] = __fmul_rn((float)(int)(signed char)(w & 0xFFu), d);
+            v[2 * k + 1] = __fmul_rn((float)(int)(signed char)(w >> 8), d);
+        }
+    } else if (type == YULE_DTYPE_Q4_1 || type == YULE_DTYPE_Q5_0 || type == YULE_DTYPE_Q5_1) {
+        // dequant.rs:91-138: optional minimum m after d, optional 32 fifth bits before the nibbles
+        const bool has_m = type != YULE_DTYPE_Q5_0, has_qh = type != YULE_DTYPE_Q4_1;
+        const uint32_t bb = type == YULE_DTYPE_Q4_1 ? 20u : type == YULE_DTYPE_Q5_0 ? 22u : 24u;
+        const uint32_t b = (col0 >> 5) * bb, i0 = col0 & 31u;
+        const uint32_t qh_off = has_m ? 4u : 2u, qs_off = qh_off + (has_qh ? 4u : 0u);
+        const float d = f16_bits_to_f32(u16_at(b));
+        const float m = has_m ? f16_bits_to_f32(u16_at(b + 2)) : 0.f;
+        const uint32_t qh = has_qh ? unit[b + qh_off + (i0 >> 3)] : 0u;
+        const uint32_t qs = u16_at(b + qs_off + (i0 >> 1)) | (u16_at(b + qs_off + (i0 >> 1) + 2) << 16);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const float q = (float)(((qs >> (4 * k)) & 0xFu) | (((qh >> k) & 1u) << 4));
+            v[k] = has_m ? __fadd_rn(__fmul_rn(q, d), m) : __fmul_rn(__fsub_rn(q, 16.0f), d);
+        }
     } else {
-        // the remaining formats: the per-element decoders (block index from the column)
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = dequant_elem(unit, type, col0 + i);
     }
