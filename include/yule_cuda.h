@@ -96,6 +96,22 @@ int32_t yule_cuda_copy_buffer(yule_cuda_ctx *ctx, yule_buffer src, yule_buffer d
 int32_t yule_cuda_copy_buffer_offset(yule_cuda_ctx *ctx, yule_buffer src, yule_buffer dst,
                                      size_t src_offset, size_t dst_offset, size_t size);
 int32_t yule_cuda_synchronize(yule_cuda_ctx *ctx);
+/* Budget, in SM clock cycles, of every bounded device-side wait launched from this
+ * context afterwards (peer pairs and flags of the tensor-parallel exchange, the
+ * shared-memory ring of the matvec, the GEMM pipeline).  A wait that runs out
+ * writes the context's status word; every later wait of the same context returns
+ * at once, and the next synchronize / runner call returns YULE_ERR_DEVICE_STATUS.
+ * 0 restores the default (about one second).  No counterpart in the reference,
+ * which has no device-side waits (cuda/mod.rs synchronises on the host). */
+int32_t yule_cuda_set_wait_budget(yule_cuda_ctx *ctx, uint64_t cycles);
+/* Self-test of the give-up path: runs one kernel whose bounded wait cannot be
+ * satisfied (which = 0: the Q4_K matvec polling for a gathered vector's pairs;
+ * 1: the exchange kernel polling for a peer's flag; the "peer" is memory of this
+ * GPU that nothing writes), with a budget of budget_cycles (0: the context's).
+ * The kernel returns normally; the call returns YULE_ERR_DEVICE_STATUS, which is
+ * the expected result, and the context stays usable.  No counterpart in the
+ * reference. */
+int32_t yule_cuda_selftest_bounded_wait(yule_cuda_ctx *ctx, uint32_t which, uint64_t budget_cycles);
 
 /* ── compute: the trait's numeric methods with the semantics of the
  *    reference's own GPU backends (cuda/mod.rs:95-328, vulkan/mod.rs) ───── */
@@ -134,8 +150,10 @@ int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffe
                              uint32_t kv_offset, uint32_t kv_stride, uint32_t out_offset);
 /* lib.rs:119 quantized_matmul — cuda/mod.rs:289-328 + kernels/cuda/qmv_*.cu:
  * out[row] = sum over blocks of dot(dequant(W[row, block]), x[block]).
- * gguf_type is 2 (Q4_0), 8 (Q8_0), 12 (Q4_K) or 14 (Q6_K); n_cols must be a
- * multiple of the format's block size. */
+ * gguf_type is any block format of the YULE_DTYPE_* list above: the reference's
+ * GPU backends take 2 (Q4_0), 8 (Q8_0), 12 (Q4_K) and 14 (Q6_K) and reject the
+ * rest (cuda/mod.rs:303-307); here Q4_1, Q5_0, Q5_1, Q8_1, Q2_K, Q3_K and Q5_K
+ * are accepted too.  n_cols must be a multiple of the format's block size. */
 int32_t yule_cuda_quantized_matmul(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffer input,
                                    yule_buffer output, uint32_t n_rows, uint32_t n_cols,
                                    uint32_t gguf_type);

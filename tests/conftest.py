@@ -9,6 +9,10 @@ import sys
 import numpy as np
 import pytest
 
+# The library reads its tuning knobs (YULE_GEMM_*, YULE_TP_*, YULE_CUDA_*) only in a process started with this
+# switch; some tests select a kernel route through them.
+os.environ.setdefault("YULE_CUDA_DEBUG", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

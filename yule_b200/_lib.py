@@ -42,6 +42,8 @@ _SIGNATURES = {
     "yule_cuda_copy_buffer": [vp, u64, u64, size_t],
     "yule_cuda_copy_buffer_offset": [vp, u64, u64, size_t, size_t, size_t],
     "yule_cuda_synchronize": [vp],
+    "yule_cuda_set_wait_budget": [vp, u64],
+    "yule_cuda_selftest_bounded_wait": [vp, u32, u64],
     "yule_cuda_matmul": [vp, u64, u64, u64, u32, u32, u32],
     "yule_cuda_softmax": [vp, u64, u64, u32],
     "yule_cuda_rms_norm": [vp, u64, u64, u64, u32, f32],

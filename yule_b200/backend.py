@@ -147,6 +147,15 @@ class CudaB200Backend:
     def synchronize(self) -> None:
         _check(self._lib.yule_cuda_synchronize(self._ctx))
 
+    def set_wait_budget(self, cycles: int) -> None:
+        """Budget (SM clock cycles) of the bounded device-side waits launched afterwards; 0 = default."""
+        _check(self._lib.yule_cuda_set_wait_budget(self._ctx, cycles))
+
+    def selftest_bounded_wait(self, which: int, budget_cycles: int) -> None:
+        """Runs a kernel whose wait cannot be satisfied; raises ``YuleGpuError`` (code 7, device status) when the
+        give-up path works, which is the expected outcome."""
+        _check(self._lib.yule_cuda_selftest_bounded_wait(self._ctx, which, budget_cycles))
+
     def attn_score(self, q: BufferHandle, k_cache: BufferHandle, scores: BufferHandle, head_dim: int, seq_len: int,
                    head_offset: int, kv_offset: int, kv_stride: int) -> None:
         _check(self._lib.yule_cuda_attn_score(self._ctx, q.id, k_cache.id, scores.id, head_dim, seq_len,

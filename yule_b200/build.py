@@ -41,13 +41,26 @@ def _stale(target: str, sources: list[str]) -> bool:
 
 
 def build_cuda(force: bool = False, verbose: bool = False) -> str:
+    """One nvcc process per source file (in parallel), objects under ``csrc/build/``, then one link."""
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    deps = srcs + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + [
+    common = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + [
         os.path.join(os.path.dirname(HERE), "include", "yule_cuda.h"), os.path.abspath(__file__)]
-    if force or _stale(CUDA_SO, deps):
-        flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
-        cmd = [_nvcc()] + flags + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-ldl", "-o", CUDA_SO]
-        subprocess.check_call(cmd)
+    objdir = os.path.join(CSRC, "build")
+    os.makedirs(objdir, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f not in ("--use_fast_math=false", "-shared")]
+    jobs = []
+    for src in srcs:
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        if force or _stale(obj, [src] + common):
+            jobs.append([_nvcc()] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj])
+    if jobs:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+            list(pool.map(subprocess.check_call, jobs))
+    objs = [os.path.join(objdir, os.path.basename(s)[:-3] + ".o") for s in srcs]
+    if force or jobs or _stale(CUDA_SO, objs):
+        subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC"] + objs +
+                              ["-ldl", "-o", CUDA_SO])
     return CUDA_SO
 
 

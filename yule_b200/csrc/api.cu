@@ -16,6 +16,14 @@ namespace yule {
 
 static thread_local char g_err[512] = "";
 
+const char *knob(const char *name) {
+    static const bool debug = [] {
+        const char *d = getenv("YULE_CUDA_DEBUG");
+        return d && atoi(d) != 0;
+    }();
+    return debug ? getenv(name) : nullptr;
+}
+
 int32_t fail(int32_t code, const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -64,8 +72,15 @@ bool yule_cuda_ctx::find(yule_buffer h, Buffer *out, const char *what) {
     return true;
 }
 
+// Also ends the chain of programmatic dependent launches: only qmv_common re-arms it, after a matvec.
 #define CTX_GUARD(ctx)                                                        \
     if (!(ctx)) return fail(YULE_ERR_INVALID_ARGUMENT, "null context");       \
+    const bool _pdl_chain = (ctx)->pdl_chain;                                 \
+    (void)_pdl_chain;                                                         \
+    (ctx)->pdl_chain = false;                                                 \
+    const int _chain_n = (ctx)->chain_n;                                      \
+    (void)_chain_n;                                                           \
+    (ctx)->chain_n = 0;                                                       \
     YULE_CUDA_TRY(cudaSetDevice((ctx)->device))
 
 #define FIND(ctx, handle, var)  \
@@ -215,6 +230,7 @@ static int32_t drop_planar(yule_cuda_ctx *ctx, yule_buffer h) {
         planar = it->second.planar;
         it->second.planar = nullptr;
         it->second.planar_blocks = 0;
+        it->second.planar_cols = 0;
     }
     YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     YULE_CUDA_TRY(cudaFree(planar));
@@ -291,6 +307,12 @@ int32_t yule_cuda_synchronize(yule_cuda_ctx *ctx) {
         cudaMemset(ctx->device_status, 0, sizeof(int));
         return fail(YULE_ERR_DEVICE_STATUS, "a device-side bounded wait gave up (status word %d)", status);
     }
+    return YULE_OK;
+}
+
+int32_t yule_cuda_set_wait_budget(yule_cuda_ctx *ctx, uint64_t cycles) {
+    CTX_GUARD(ctx);
+    ctx->wait_cycles = cycles ? (long long)(cycles > (1ull << 62) ? (1ull << 62) : cycles) : kDefaultWaitCycles;
     return YULE_OK;
 }
 
@@ -442,7 +464,7 @@ int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffe
 // other formats from 32, except Q5_K (tensor-pipe matvec at 3.5 us per row against a 195 us GEMM) from 64.
 // YULE_GEMM_MIN_BATCH overrides all three (at least 8).
 static uint32_t gemm_min_batch(uint32_t type) {
-    if (const char *e = getenv("YULE_GEMM_MIN_BATCH")) {
+    if (const char *e = knob("YULE_GEMM_MIN_BATCH")) {
         const int v = atoi(e);
         return v < 8 ? 8u : (uint32_t)v;
     }
@@ -484,7 +506,7 @@ static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight
     a.batch = batch;
     a.x_stride = x_stride;
     a.out_stride = out_stride;
-    if (type == YULE_DTYPE_Q6_K && W.planar && weight_offset == 0 &&
+    if (type == YULE_DTYPE_Q6_K && W.planar && weight_offset == 0 && W.planar_cols == n_cols &&
         W.planar_blocks == (uint64_t)n_rows * (n_cols / 256))
         a.planar = W.planar;
     if (batch >= gemm_min_batch(type) && qgemm_supported(type, n_cols, batch)) {
@@ -506,7 +528,34 @@ static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight
         LAUNCHED(ctx, launch_qgemm(g, ctx->prop.multiProcessorCount, ctx->stream, &_n));
         return YULE_OK;
     }
+    // Consecutive matvec calls overlap through programmatic dependent launch.  The kernels read their weights
+    // before the dependency wait, so the chain is used only when the previous call on this context was a matvec
+    // too and no call that may still be running writes what this one reads as weights.  When its activations
+    // are not such an output either (Q, K and V from one normed vector; gate and up), nothing this kernel reads
+    // depends on its predecessors: only its stores are ordered behind them (late wait).
+    const char *w_lo = (const char *)a.w, *w_hi = w_lo + wbytes;
+    const char *x_lo = (const char *)X.ptr, *x_hi = x_lo + ((size_t)(batch - 1) * x_stride + n_cols) * 4;
+    const char *o_lo = (const char *)O.ptr, *o_hi = o_lo + ((size_t)(batch - 1) * out_stride + n_rows) * 4;
+    bool w_hazard = false, x_hazard = false;
+    ctx->chain_n = _chain_n;  // (the guard above ended the chain for every other entry point)
+    for (int i = 0; i < ctx->chain_n; i++) {
+        w_hazard = w_hazard || (w_lo < ctx->chain_hi[i] && ctx->chain_lo[i] < w_hi);
+        x_hazard = x_hazard || (x_lo < ctx->chain_hi[i] && ctx->chain_lo[i] < x_hi);
+    }
+    a.pdl = _pdl_chain && !w_hazard;
+    a.late_wait = a.pdl && !x_hazard && ctx->chain_n < yule_cuda_ctx::kChainRanges;
+    a.status = ctx->device_status;
+    a.wait_cycles = ctx->wait_cycles;
     LAUNCHED(ctx, launch_qmv(a, ctx->prop.multiProcessorCount, ctx->stream, &_n));
+    ctx->pdl_chain = true;
+    if (!a.late_wait) ctx->chain_n = 0;  // this kernel waits for all its predecessors before it reads or writes
+    bool listed = false;
+    for (int i = 0; i < ctx->chain_n; i++) listed = listed || (ctx->chain_lo[i] <= o_lo && o_hi <= ctx->chain_hi[i]);
+    if (!listed) {
+        ctx->chain_lo[ctx->chain_n] = o_lo;
+        ctx->chain_hi[ctx->chain_n] = o_hi;
+        ctx->chain_n++;
+    }
     return YULE_OK;
 }
 
@@ -539,21 +588,21 @@ int32_t yule_cuda_prepare_weights(yule_cuda_ctx *ctx, yule_buffer weights, uint3
     NEED_BYTES(W, tensor_bytes(gguf_type, n_rows, n_cols), "prepare_weights");
     if (gguf_type != YULE_DTYPE_Q6_K || !q6k_mma_supported(n_cols) || n_rows == 0) return YULE_OK;
     const uint64_t n_blocks = (uint64_t)n_rows * (n_cols / 256);
-    if (W.planar && W.planar_blocks == n_blocks) return YULE_OK;
+    if (W.planar && W.planar_blocks == n_blocks && W.planar_cols == n_cols) return YULE_OK;
     if (W.planar) {
         int32_t rc = drop_planar(ctx, weights);
         if (rc) return rc;
     }
     uint8_t *planar = nullptr;
-    cudaError_t e = cudaMalloc((void **)&planar, q6k_planar_bytes(n_blocks));
+    cudaError_t e = cudaMalloc((void **)&planar, q6k_planar_bytes(n_rows, n_cols));
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(YULE_ERR_OUT_OF_MEMORY, "cuda allocation of the planar Q6_K copy (%zu bytes) failed",
-                    q6k_planar_bytes(n_blocks));
+                    q6k_planar_bytes(n_rows, n_cols));
     }
     {
         uint64_t _n = 0;
-        e = launch_q6k_repack((const uint8_t *)W.ptr, planar, n_blocks, ctx->stream, &_n);
+        e = launch_q6k_repack((const uint8_t *)W.ptr, planar, n_rows, n_cols, ctx->stream, &_n);
         ctx->launches.fetch_add(_n);
     }
     if (e != cudaSuccess) {
@@ -568,6 +617,7 @@ int32_t yule_cuda_prepare_weights(yule_cuda_ctx *ctx, yule_buffer weights, uint3
     }
     it->second.planar = planar;
     it->second.planar_blocks = n_blocks;
+    it->second.planar_cols = n_cols;
     return YULE_OK;
 }
 

@@ -43,15 +43,29 @@ __device__ __forceinline__ void yule_prefetch_l2_slice(const void *base, uint64_
 
 namespace yule {
 
+// Values of the device status word (yule_cuda_ctx::device_status): which bounded wait gave up.
+constexpr int kStatusPeerTimeout = 2;   // tensor parallelism: a peer's (value, epoch) pairs or flag never arrived
+constexpr int kStatusGemmTimeout = 3;   // tcgen05 GEMM: an mbarrier of its pipeline never completed
+constexpr int kStatusRingTimeout = 4;   // matvec: a bulk copy into the shared-memory ring never completed
+// Default budget of a bounded wait, in SM clock cycles (~1 s): far beyond any real skew between ranks,
+// short enough to report a lost peer.  yule_cuda_set_wait_budget changes it per context.
+constexpr long long kDefaultWaitCycles = 2000000000LL;
+
 struct Buffer {
     void *ptr = nullptr;
     size_t size = 0;      // bytes the caller asked for
     size_t capacity = 0;  // bytes allocated (rounded up, so 16-byte over-reads stay in bounds)
-    // Optional planar device copy of a Q6_K tensor held in this buffer (yule_cuda_prepare_weights);
+    // Optional row-planar device copy of a Q6_K tensor held in this buffer (yule_cuda_prepare_weights);
     // dropped whenever the buffer is written.
     uint8_t *planar = nullptr;
     uint64_t planar_blocks = 0;
+    uint32_t planar_cols = 0;  // the copy is laid out row by row, so it belongs to one (rows, cols) shape
 };
+
+// Tuning and timing knobs (YULE_QMV_*, YULE_GEMM_*, YULE_CUDA_*, YULE_TP_*) are read from the environment only
+// when the process runs with YULE_CUDA_DEBUG=1; a production process ignores them, so no environment
+// variable can change routing or results.  Returns the variable's value or null.
+const char *knob(const char *name);
 
 // Sets the calling thread's error text and returns `code`.
 int32_t fail(int32_t code, const char *fmt, ...);
@@ -98,6 +112,17 @@ struct yule_cuda_ctx {
     std::atomic<uint64_t> launches{0};
     // Word the kernels with bounded waits write when they give up; read by synchronize.
     int *device_status = nullptr;
+    long long wait_cycles = yule::kDefaultWaitCycles;  // budget of every bounded device-side wait
+    // Programmatic dependent launch between consecutive matvec calls of the trait API: allowed only when the
+    // previous operation enqueued on the stream was one of this library's kernels, and its output does not
+    // overlap the weights of the call being launched (weights are read before the dependency wait).
+    bool pdl_chain = false;
+    // Outputs of the matvec calls of the current chain that may still be running when the next one starts:
+    // a kernel that waits for its predecessor before reading anything settles everything before it, a kernel
+    // whose stores alone wait (late wait) does not.
+    static constexpr int kChainRanges = 8;
+    const char *chain_lo[kChainRanges] = {}, *chain_hi[kChainRanges] = {};
+    int chain_n = 0;
 
     // Looks a handle up under the lock; returns false (and sets the error) when unknown.
     bool find(yule_buffer h, yule::Buffer *out, const char *what);
@@ -165,6 +190,7 @@ struct TpFuse {
     const uint32_t *tick = nullptr;
     uint32_t epochs_per_tick = 0;
     int *status = nullptr;
+    long long wait_cycles = kDefaultWaitCycles;  // budget of the consumer's polling
     bool push = false;               // producer
     uint32_t push_index = 0;
     uint2 *pair_out[8] = {};         // rank p's pair buffer at this rank's slice (every rank, this one too)
@@ -181,12 +207,17 @@ struct QmvArgs {
     // Optional fused prologue/epilogue used by the runner (null when unused):
     const float *residual = nullptr;  // out[row] = residual[row] + dot   (o-proj / down-proj)
     bool pdl = false;                 // programmatic dependent launch
+    // With pdl: none of this call's inputs (x, residual) is written by the previous kernel of the stream, so
+    // only this kernel's stores have to wait for it (Q4_K / Q6_K tensor-pipe kernels; ignored elsewhere).
+    bool late_wait = false;
     const uint8_t *planar = nullptr;  // Q6_K: planar copy of the same tensor, when one was prepared
     const float *norm_w = nullptr;    // RMSNorm prologue (planar Q6_K and Q4_K paths only)
     float eps = 0.f;
     const void *next_w[2] = {nullptr, nullptr};  // tensor-pipe paths: weights to prefetch into L2
     uint64_t next_bytes[2] = {0, 0};
     TpFuse tp;                        // Q4_K tensor-pipe path only
+    int *status = nullptr;            // device status word for bounded waits inside the kernels, or null
+    long long wait_cycles = kDefaultWaitCycles;
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
 
@@ -232,16 +263,23 @@ struct Q4kFused {
     bool swiglu_pair = false;         // w[0], w[1] = gate, up → out[0] = SiLU(gate)·up
     bool q5 = false;                  // the matrices are Q5_K (176-byte super-blocks), 16-byte aligned
     bool pdl = false;                 // programmatic dependent launch
+    bool late_wait = false;           // with pdl: inputs do not come from the previous kernel; only the stores wait for it
     const void *next_w[2] = {nullptr, nullptr};  // weights of the kernel(s) that follow: prefetched into L2
     uint64_t next_bytes[2] = {0, 0};
     TpFuse tp;                        // pushes out[0] to the peers / waits for a gathered x
+    int *status = nullptr;            // device status word for the kernel's own bounded waits, or null
+    long long wait_cycles = kDefaultWaitCycles;
 };
 bool q4k_mma_supported(uint32_t n_cols, uint32_t batch);
+// Routes to the shared-memory-ring kernel (qmv_q4k_ring.cu) when it takes the case, else to the
+// register-streaming kernel of qmv_q4k_mma.cu.
 cudaError_t launch_q4k_mma(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches);
+bool q4k_ring_supported(const Q4kFused &f);
+cudaError_t launch_q4k_ring(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches);
 
-// Q6_K tensor-pipe matvec over the planar device copy of a tensor (qmv_q6k_mma.cu).
+// Q6_K tensor-pipe matvec over the row-planar device copy of a tensor (qmv_q6k_ring.cu).
 struct Q6kPlanar {
-    const uint8_t *planar = nullptr;  // planes ql | qh | scales | d, built by launch_q6k_repack
+    const uint8_t *planar = nullptr;  // per row: ql | qh | scales | d of all its blocks, built by launch_q6k_repack
     float *out = nullptr;
     uint32_t n_rows = 0, n_cols = 0;
     const float *x = nullptr;
@@ -249,13 +287,22 @@ struct Q6kPlanar {
     float eps = 0.f;
     const float *residual = nullptr;  // out += residual when set
     bool pdl = false;
-    const void *next_w[2] = {nullptr, nullptr};  // weights of the kernel(s) that follow: prefetched into L2
+    bool late_wait = false;           // with pdl: inputs do not come from the previous kernel; only the stores wait for it
+    const void *next_w[2] = {nullptr, nullptr};  // unused by the ring kernel (its successor fetches its own weights early)
     uint64_t next_bytes[2] = {0, 0};
+    int *status = nullptr;            // device status word for the kernel's bounded waits, or null
+    long long wait_cycles = kDefaultWaitCycles;
 };
-size_t q6k_planar_bytes(uint64_t n_blocks);
-cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_blocks, cudaStream_t s, uint64_t *launches);
+size_t q6k_planar_bytes(uint64_t n_rows, uint32_t n_cols);
+cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_rows, uint32_t n_cols, cudaStream_t s,
+                              uint64_t *launches);
 bool q6k_mma_supported(uint32_t n_cols);
+// Shared-memory-ring kernel (qmv_q6k_ring.cu): the kernel of calls whose inputs do not depend on the previous
+// kernel (late wait), which overlap with it on the same SMs.
 cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches);
+// Register-streaming kernel (qmv_q6k_mma.cu): the kernel of dependent chains.
+bool q6k_stream_supported(uint32_t n_cols);
+cudaError_t launch_q6k_stream(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches);
 
 // Tensor parallelism (tp.cu).
 struct NcclId {

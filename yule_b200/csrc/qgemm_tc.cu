@@ -71,7 +71,6 @@ constexpr float kSumScale = 1.0f / 32.0f;     // the sub-block sums of x are sto
 constexpr float kGenericWScale = 1024.f;      // generic kernel: weights are scaled by 2^10 before the fp16 hi/lo split
 constexpr uint32_t kAmBytes = kBM * 16 * 2;  // the m slab of a super-block: 128 rows × 16 columns, 4 KB
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any real stall
-constexpr int kStatusGemmTimeout = 3;
 
 // Cycle counters of CTA 0's roles (YULE_GEMM_PROF=1 prints them after the launch): a timing aid.
 __device__ long long g_gemm_prof[16];
@@ -987,7 +986,7 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.bn = bn;
     p.n_mtiles = (g.n_rows + kBM - 1) / kBM;
     p.n_ntiles = n_ntiles;
-    const bool generic = g.type != YULE_DTYPE_Q4_K || (getenv("YULE_GEMM_GENERIC") && atoi(getenv("YULE_GEMM_GENERIC")));
+    const bool generic = g.type != YULE_DTYPE_Q4_K || (knob("YULE_GEMM_GENERIC") && atoi(knob("YULE_GEMM_GENERIC")));
     const uint32_t stage_bytes = generic ? 2 * kABytes + 2 * bn * kBK * 2 : kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
     p.unit_bytes = 256 / block_size(g.type) * block_bytes(g.type);
     p.raw_chunks = (p.unit_bytes + 14 + 15) / 16;      // covers the unit from any 2-byte-aligned start
@@ -1001,8 +1000,8 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.w_row_bytes = (uint64_t)(g.n_cols / block_size(g.type)) * block_bytes(g.type);
     p.out_scale = generic ? 1.0f / kGenericWScale : 1.0f;
     p.status = g.status;
-    p.prof = getenv("YULE_GEMM_PROF") ? 1u : 0u;
-    p.skip = getenv("YULE_GEMM_SKIP") ? (uint32_t)atoi(getenv("YULE_GEMM_SKIP")) : 0u;
+    p.prof = knob("YULE_GEMM_PROF") ? 1u : 0u;
+    p.skip = knob("YULE_GEMM_SKIP") ? (uint32_t)atoi(knob("YULE_GEMM_SKIP")) : 0u;
     const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 32;
     const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
     CUtensorMap w_map;

@@ -570,7 +570,10 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
             f.norm_w = a.norm_w;
             f.eps = a.eps;
             f.pdl = a.pdl;
+            f.late_wait = a.late_wait;
             f.tp = a.tp;
+            f.status = a.status;
+            f.wait_cycles = a.wait_cycles;
             for (int i = 0; i < 2; i++) {
                 f.next_w[i] = a.next_w[i];
                 f.next_bytes[i] = a.next_bytes[i];
@@ -581,7 +584,7 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         }
         return cudaSuccess;
     }
-    if (a.type == YULE_DTYPE_Q6_K && a.planar && a.batch == 1 && q6k_mma_supported(a.n_cols)) {
+    if (a.type == YULE_DTYPE_Q6_K && a.planar && a.batch == 1 && q6k_mma_supported(a.n_cols) && q6k_stream_supported(a.n_cols)) {
         Q6kPlanar f;
         f.planar = a.planar;
         f.out = a.out;
@@ -592,11 +595,13 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         f.eps = a.eps;
         f.residual = a.residual;
         f.pdl = a.pdl;
-        for (int i = 0; i < 2; i++) {
-            f.next_w[i] = a.next_w[i];
-            f.next_bytes[i] = a.next_bytes[i];
-        }
-        return launch_q6k_mma(f, sm_count, s, launches);
+        f.late_wait = a.late_wait;
+        f.status = a.status;
+        f.wait_cycles = a.wait_cycles;
+        // independent call → ring kernel (overlaps with its predecessor); dependent chain or long matrix → streaming kernel
+        bool ring = a.pdl && a.late_wait && (a.n_rows + 15) / 16 <= 8u * (uint32_t)sm_count;
+        if (const char *k = knob("YULE_QMV_RING")) ring = atoi(k) != 0;
+        return ring ? launch_q6k_mma(f, sm_count, s, launches) : launch_q6k_stream(f, sm_count, s, launches);
     }
     if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;
     uint32_t done = 0;

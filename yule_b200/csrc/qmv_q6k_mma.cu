@@ -1,14 +1,13 @@
-// qmv_q6k_mma.cu — Q6_K fused dequantise + matvec on the tensor pipe, from a planar copy of the
-// tensor, plus the kernel that builds that copy.
+// qmv_q6k_mma.cu — Q6_K fused dequantise + matvec on the tensor pipe, weights streamed through registers
+// from the row-planar copy of the tensor (built by qmv_q6k_ring.cu, which also describes the layout).
+// This is the kernel of dependent chains (the token step of the runner): it keeps the first super-blocks of
+// every warp in registers across the dependency wait.  qmv_q6k_ring.cu is the kernel of independent calls.
 //
 // Contract: yule-core/src/dequant.rs:976-1009 — sum += d * sc[8h + l/16 + 2j] * (q − 32) * x for the
 // weight at column 128h + 32j + l, q assembled from a nibble of ql and two bits of qh.
 //
-// Planar copy.  A Q6_K super-block is 210 bytes (ql[128] qh[64] scales[16] d[2]) and only 2-byte
-// aligned in the GGUF stream, which rules out wide loads.  The device keeps, next to the raw
-// tensor, the same bytes regrouped into four planes — every block's ql, then every block's qh,
-// then the scales, then d — so that each piece a lane needs is one aligned 16-byte load.  Same
-// byte count (210 per block), same values; built once per tensor by repack_q6k_kernel.
+// Row-planar copy: per row, every block's ql, then every block's qh, then the scales, then the d values — each
+// piece a lane needs is one aligned 16-byte load.
 //
 // Tensor-core formulation (same ideas as qmv_q4k_mma.cu, batch 1):
 //   A  the 6-bit q as an fp16 subnormal (q·2^-24, exact), assembled byte-parallel from ql/qh and
@@ -58,33 +57,8 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 
-// Planes of a tensor of n_blocks super-blocks.
-struct Planes {
-    const uint8_t *ql, *qh, *sc, *d;
-};
-__host__ __device__ inline Planes planes_of(const uint8_t *base, uint64_t n_blocks) {
-    Planes p;
-    p.ql = base;
-    p.qh = base + n_blocks * 128;
-    p.sc = base + n_blocks * 192;
-    p.d = base + n_blocks * 208;
-    return p;
-}
-
-__global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ planar, uint64_t n_blocks) {
-    const Planes p = planes_of(planar, n_blocks);
-    const uint64_t total = n_blocks * 105;  // 16-bit pieces: blocks are 2-byte aligned
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t b = i / 105;
-        const uint32_t o = (uint32_t)(i - b * 105) * 2;
-        const unsigned short v = *reinterpret_cast<const unsigned short *>(raw + b * 210 + o);
-        uint8_t *dst = o < 128 ? const_cast<uint8_t *>(p.ql) + b * 128 + o
-                     : o < 192 ? const_cast<uint8_t *>(p.qh) + b * 64 + (o - 128)
-                     : o < 208 ? const_cast<uint8_t *>(p.sc) + b * 16 + (o - 192)
-                               : const_cast<uint8_t *>(p.d) + b * 2;
-        *reinterpret_cast<unsigned short *>(dst) = v;
-    }
-}
+// Row record of the row-planar copy (same arithmetic as qmv_q6k_ring.cu).
+__host__ __device__ inline size_t row_record_bytes(uint32_t bpr) { return (size_t)bpr * 208 + ((bpr * 2 + 15) & ~15u); }
 
 // What one lane needs from one super-block of one row.
 struct BlockLoads {
@@ -93,16 +67,16 @@ struct BlockLoads {
 };
 
 template <int NR>
-__device__ __forceinline__ void issue_loads(BlockLoads (&ld)[NR], const Planes &pl, const uint64_t (&rowblk)[NR],
-                                            uint32_t blk, int h, int u) {
+__device__ __forceinline__ void issue_loads(BlockLoads (&ld)[NR], const uint8_t *const (&rec)[NR], uint32_t bpr, uint32_t blk,
+                                            int h, int u) {
 #pragma unroll
     for (int r = 0; r < NR; r++) {
-        const uint64_t b = rowblk[r] + blk;
-        ld[r].qa = ld_stream_u4(pl.ql + b * 128 + 64 * h + 16 * u);
-        ld[r].qb = ld_stream_u4(pl.ql + b * 128 + 64 * h + 32 + 16 * u);
-        ld[r].qh = ld_stream_u4(pl.qh + b * 64 + 32 * h + 16 * u);
-        ld[r].sc = ld_stream_u4(pl.sc + b * 16);
-        ld[r].d = ld_stream_u16(pl.d + b * 2);
+        const uint8_t *ql = rec[r] + (size_t)blk * 128, *qh = rec[r] + (size_t)bpr * 128 + (size_t)blk * 64;
+        ld[r].qa = ld_stream_u4(ql + 64 * h + 16 * u);
+        ld[r].qb = ld_stream_u4(ql + 64 * h + 32 + 16 * u);
+        ld[r].qh = ld_stream_u4(qh + 32 * h + 16 * u);
+        ld[r].sc = ld_stream_u4(rec[r] + (size_t)bpr * 192 + (size_t)blk * 16);
+        ld[r].d = ld_stream_u16(rec[r] + (size_t)bpr * 208 + (size_t)blk * 2);
     }
 }
 
@@ -324,7 +298,6 @@ __device__ __forceinline__ void consume_block(const BlockLoads (&ld)[NR], const 
 
 struct Q6kMmaParams {
     const uint8_t *planar;
-    uint64_t n_blocks;
     float *out;
     uint32_t n_rows, n_cols, n_tiles;
     const float *x;
@@ -357,21 +330,21 @@ qmv_q6k_mma_kernel(const Q6kMmaParams p) {
     const uint32_t G = gridDim.x;
     const uint32_t first_tile = blockIdx.x + group * G, tile_stride = kGroups * G;
     const uint32_t my_tiles = p.n_tiles > first_tile ? (p.n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
-    const Planes pl = planes_of(p.planar, p.n_blocks);
+    const size_t rec_bytes = row_record_bytes(bpr);
 
     const SmemLayout sm = carve(smem_raw, p.n_cols);
     float *partial = sm.partial + (size_t)group * kRoundSlots * kWarps * 4 * 16;
 
     // load cursor: tile k, super-block slot j
     uint32_t lk = 0, lj = 0;
-    uint64_t rowblk[NR];
+    const uint8_t *rowrec[NR];
     auto locate = [&]() {
         const uint32_t tile = first_tile + lk * tile_stride;
 #pragma unroll
         for (int r = 0; r < NR; r++) {
             uint32_t row = tile * ROWS + g + 8 * r;
             row = row < p.n_rows ? row : p.n_rows - 1;  // clamp: the load stays in bounds, the result is dropped
-            rowblk[r] = (uint64_t)row * bpr;
+            rowrec[r] = p.planar + (size_t)row * rec_bytes;
         }
     };
     auto advance = [&]() {
@@ -389,7 +362,7 @@ qmv_q6k_mma_kernel(const Q6kMmaParams p) {
 #pragma unroll
         for (int i = 0; i < DEPTH; i++) {
             if (issued < total_units) {
-                issue_loads<NR>(buf[i], pl, rowblk, wid + kWarps * lj, h, u);
+                issue_loads<NR>(buf[i], rowrec, bpr, wid + kWarps * lj, h, u);
                 issued++;
                 if (issued < total_units) advance();
             }
@@ -452,7 +425,7 @@ qmv_q6k_mma_kernel(const Q6kMmaParams p) {
                 consume_block<NR>(buf[i], bx_base + (size_t)blk * blk_stride, j_stride, s32_base + (size_t)blk * s32_stride, u2,
                                   acc);
                 if (issued < total_units) {
-                    issue_loads<NR>(buf[i], pl, rowblk, wid + kWarps * lj, h, u);
+                    issue_loads<NR>(buf[i], rowrec, bpr, wid + kWarps * lj, h, u);
                     issued++;
                     if (issued < total_units) advance();
                 }
@@ -478,14 +451,18 @@ qmv_q6k_mma_kernel(const Q6kMmaParams p) {
 template <int ROWS, int DEPTH>
 cudaError_t launch_variant(const Q6kMmaParams &p, int sm_count, size_t smem, bool pdl, cudaStream_t s) {
     auto kern = qmv_q6k_mma_kernel<ROWS, DEPTH>;
-    static bool attr_done = false;
+    // the attribute belongs to the device, not the process: one flag per device ordinal
+    static bool attr_done[64] = {};
     static std::mutex mu;
     {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
         std::lock_guard<std::mutex> lock(mu);
-        if (!attr_done) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             if (e != cudaSuccess) return e;
-            attr_done = true;
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
     uint32_t grid = (uint32_t)sm_count;
@@ -496,18 +473,9 @@ cudaError_t launch_variant(const Q6kMmaParams &p, int sm_count, size_t smem, boo
 
 }  // namespace
 
-size_t q6k_planar_bytes(uint64_t n_blocks) { return (size_t)n_blocks * 210 + 256; }
+bool q6k_stream_supported(uint32_t n_cols) { return n_cols % 256 == 0 && smem_bytes(n_cols) <= 200 * 1024; }
 
-cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_blocks, cudaStream_t s, uint64_t *launches) {
-    if (n_blocks == 0) return cudaSuccess;
-    repack_q6k_kernel<<<148 * 8, 256, 0, s>>>(raw, planar, n_blocks);
-    *launches += 1;
-    return cudaGetLastError();
-}
-
-bool q6k_mma_supported(uint32_t n_cols) { return n_cols % 256 == 0 && smem_bytes(n_cols) <= 200 * 1024; }
-
-cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches) {
+cudaError_t launch_q6k_stream(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches) {
     if (f.n_rows == 0) return cudaSuccess;
     Q6kMmaParams p = {};
     // Tile height.  16-row tiles use the whole MMA and half the instructions per byte of 8-row tiles; they win
@@ -515,9 +483,8 @@ cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uin
     // 10-25 % faster with 16; 2048 rows, 128 tiles, faster with 8).  YULE_QMV_ROWS forces one (timing aid).
     const uint32_t n_groups = (uint32_t)kGroups * (uint32_t)sm_count;
     int tile_rows = ((f.n_rows / 16) * 10 >= n_groups * 6) ? 16 : 8;
-    if (const char *force = getenv("YULE_QMV_ROWS")) tile_rows = atoi(force) == 8 ? 8 : (atoi(force) == 16 ? 16 : tile_rows);
+    if (const char *force = knob("YULE_QMV_ROWS")) tile_rows = atoi(force) == 8 ? 8 : (atoi(force) == 16 ? 16 : tile_rows);
     p.planar = f.planar;
-    p.n_blocks = (uint64_t)f.n_rows * (f.n_cols / 256);
     p.out = f.out;
     p.n_rows = f.n_rows;
     p.n_cols = f.n_cols;

@@ -1,0 +1,601 @@
+// qmv_q6k_ring.cu — Q6_K fused dequantise + matvec on the tensor pipe, weights staged through a
+// shared-memory ring by bulk copies from a row-planar copy of the tensor, plus the kernel that builds
+// that copy.
+//
+// Contract: yule-core/src/dequant.rs:976-1009 — sum += d * sc[8h + l/16 + 2j] * (q − 32) * x for the
+// weight at column 128h + 32j + l, q assembled from a nibble of ql and two bits of qh.
+//
+// Row-planar copy.  A Q6_K super-block is 210 bytes (ql[128] qh[64] scales[16] d[2]) and only 2-byte
+// aligned in the GGUF stream, which rules out both wide loads and bulk copies (16-byte granular).  The
+// device keeps, next to the raw tensor, the same bytes regrouped row by row: every block's ql of the
+// row, then every block's qh, then the scales, then the d values (padded to a multiple of 16 bytes).
+// Any run of blocks that starts at a multiple of eight is then four 16-byte-aligned contiguous pieces.
+// Same values, 210 bytes per block plus at most 14 bytes per row; built once per tensor.
+//
+// Tensor-core formulation (batch 1):
+//   A  the 6-bit q as an fp16 subnormal (q·2^-24, exact), assembled byte-parallel from ql/qh and
+//      spread to 16-bit lanes with one PRMT per pair;
+//   B  x·2^e split into hi/lo halves; column n = 4·part + t' carries x only at the k slots lane
+//      t' feeds, so D[row][n] is the Σ q·x of one 16-column scale group whatever the k order;
+//   −32 offset: Σ (q−32)·x = Σ q·x − 32·Σx, with the per-16-column Σx staged once per CTA;
+//   scales and d applied in fp32.  Only the order of fp32 additions differs from the CPU code.
+// Lane (g, t): rows g and g+8; t = (h, u) owns l ∈ [16u, 16u+16) of half h, i.e. columns
+// 128h + 32j + 16u + [0,16) for j = 0..3: 16 bytes of ql for j ∈ {0,2}, 16 for j ∈ {1,3}, 16 of qh.
+//
+// Schedule: that of qmv_q4k_ring.cu — two groups of 8 warps per CTA, 16-row tiles dealt round-robin,
+// a stage is 16 rows × up to 8 super-blocks (four planes in shared memory, each with a row pitch that
+// keeps the 16-byte fragment reads of a quarter warp in distinct banks), copies issued before
+// `griddepcontrol.wait`, slots refilled by the warp that releases them last, bounded waits.
+
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace yule {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kGroups = 2;
+constexpr int kThreadsCta = kGroups * kWarps * 32;
+constexpr int kStageRows = 16;
+constexpr int kStageBlocks = kWarps;
+constexpr int kMaxStages = 4;  // per group
+// planes of a stage: row pitches ≡ 32, 64, 16, 16 (mod 128) for the 16-byte reads at 64h+16u, 32h+16u, 0, 0
+constexpr uint32_t kQlPitch = kStageBlocks * 128 + 32, kQhPitch = kStageBlocks * 64 + 64, kScPitch = kStageBlocks * 16 + 16,
+                   kDPitch = 16;
+constexpr uint32_t kQlOff = 0, kQhOff = kQlOff + kStageRows * kQlPitch, kScOff = kQhOff + kStageRows * kQhPitch,
+                   kDOff = kScOff + kStageRows * kScPitch, kStageBytes = kDOff + kStageRows * kDPitch;  // 28 672
+static_assert(kStageBytes % 128 == 0, "stages stay 128-byte aligned");
+constexpr size_t kFullSmSmem = 227 * 1024;
+constexpr size_t kPreferredSmem = 140 * 1024;  // leaves room for a small neighbour kernel on the same SM
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+// Row record of the row-planar copy.
+__host__ __device__ inline uint32_t d_section_bytes(uint32_t bpr) { return (bpr * 2 + 15) & ~15u; }
+__host__ __device__ inline size_t row_record_bytes(uint32_t bpr) { return (size_t)bpr * 208 + d_section_bytes(bpr); }
+
+__global__ void repack_q6k_rows_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ planar, uint64_t n_rows, uint32_t bpr) {
+    const size_t rec = row_record_bytes(bpr);
+    const uint32_t dsec = d_section_bytes(bpr);
+    const uint64_t per_row = (uint64_t)bpr * 104 + dsec / 2;  // 16-bit pieces of a row record (blocks are 2-byte aligned)
+    const uint64_t total = n_rows * per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = i / per_row;
+        const uint32_t o = (uint32_t)(i - row * per_row) * 2;  // byte offset inside the record
+        const uint8_t *src_row = raw + row * bpr * 210;
+        unsigned short v = 0;
+        if (o < bpr * 128) {
+            v = *reinterpret_cast<const unsigned short *>(src_row + (size_t)(o / 128) * 210 + (o % 128));
+        } else if (o < bpr * 192) {
+            const uint32_t q = o - bpr * 128;
+            v = *reinterpret_cast<const unsigned short *>(src_row + (size_t)(q / 64) * 210 + 128 + (q % 64));
+        } else if (o < bpr * 208) {
+            const uint32_t q = o - bpr * 192;
+            v = *reinterpret_cast<const unsigned short *>(src_row + (size_t)(q / 16) * 210 + 192 + (q % 16));
+        } else {
+            const uint32_t q = (o - bpr * 208) / 2;  // block index; the tail of the section is padding
+            if (q < bpr) v = *reinterpret_cast<const unsigned short *>(src_row + (size_t)q * 210 + 208);
+        }
+        *reinterpret_cast<unsigned short *>(planar + row * rec + o) = v;
+    }
+}
+
+// Shared-memory image of the activation vector:
+//   xh, xl   fp16 hi / lo of x·2^e in column order, 8 halves of padding after every 128 columns;
+//            xl starts 64 bytes (mod 128) after xh, so the eight live lanes of a B load fall into
+//            distinct banks;
+//   s32      −32 · Σx over each 16-column scale group (fp32);
+//   zb       zeros for lanes that feed an all-zero B column (and for the lanes that must not
+//            charge the −32 term a second time).
+struct XImage {
+    __half *xh, *xl;
+    float *s32;
+    uint4 *zb;
+    float *inv_scale;
+    float *red;
+};
+struct RingSmem {
+    unsigned char *ring;
+    XImage x;
+    float *partial;  // [group][buffer][warp][row]
+    uint64_t *bars;
+    uint32_t *cnt;
+};
+__host__ __device__ inline uint32_t padded_cols(uint32_t n_cols) { return n_cols + 8 * (n_cols / 128); }
+__host__ __device__ inline size_t x_plane_bytes(uint32_t n_cols) { return (((size_t)padded_cols(n_cols) * 2 + 127) / 128) * 128; }
+constexpr size_t kPartialBytes = (size_t)kGroups * 2 * kWarps * 16 * sizeof(float);
+
+__host__ __device__ inline size_t ring_fixed_bytes(uint32_t n_cols) {
+    size_t off = 2 * (x_plane_bytes(n_cols) + 64) + (size_t)(n_cols / 16) * 4;
+    off = (off + 15) & ~(size_t)15;
+    off += 64 + 16 + 64 * sizeof(float) + kPartialBytes + (size_t)kGroups * kMaxStages * (8 + 4);
+    return (off + 127) & ~(size_t)127;
+}
+__host__ __device__ inline size_t ring_smem_bytes(uint32_t n_cols, uint32_t stages) {
+    return (size_t)kGroups * stages * kStageBytes + ring_fixed_bytes(n_cols);
+}
+__device__ __forceinline__ RingSmem carve(unsigned char *base, uint32_t n_cols, uint32_t stages) {
+    RingSmem s;
+    s.ring = base;
+    size_t off = (size_t)kGroups * stages * kStageBytes;
+    s.x.xh = reinterpret_cast<__half *>(base + off);
+    off += x_plane_bytes(n_cols) + 64;
+    s.x.xl = reinterpret_cast<__half *>(base + off);
+    off += x_plane_bytes(n_cols) + 64;
+    s.x.s32 = reinterpret_cast<float *>(base + off);
+    off += (size_t)(n_cols / 16) * 4;
+    off = (off + 15) & ~(size_t)15;
+    s.x.zb = reinterpret_cast<uint4 *>(base + off);
+    off += 64;
+    s.x.inv_scale = reinterpret_cast<float *>(base + off);
+    off += 16;
+    s.x.red = reinterpret_cast<float *>(base + off);
+    off += 64 * sizeof(float);
+    s.partial = reinterpret_cast<float *>(base + off);
+    off += kPartialBytes;
+    s.bars = reinterpret_cast<uint64_t *>(base + off);
+    off += (size_t)kGroups * kMaxStages * 8;
+    s.cnt = reinterpret_cast<uint32_t *>(base + off);
+    return s;
+}
+
+// RMSNorm (optional), power-of-two normalisation, fp16 hi/lo split and per-16-column sums of x, by the
+// whole CTA.  Each thread keeps its first kCache groups of 8 columns in registers between the reduction
+// pass and the conversion pass; longer vectors re-read the remainder from L2.
+__device__ __forceinline__ void stage_activations(const XImage &sm, const float *__restrict__ x, uint32_t n_cols,
+                                                  const float *__restrict__ norm_w, float eps) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr int NW = kThreadsCta / 32;
+    constexpr int kCache = 2;
+    if (threadIdx.x < 4) sm.zb[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+    float cache[kCache][8];
+    float ss = 0.f, mx = 0.f;
+    auto load8 = [&](uint32_t c, float (&a)[8]) {
+        *reinterpret_cast<float4 *>(a) = *reinterpret_cast<const float4 *>(x + c);
+        *reinterpret_cast<float4 *>(a + 4) = *reinterpret_cast<const float4 *>(x + c + 4);
+    };
+    auto reduce8 = [&](uint32_t c, const float (&a)[8]) {
+        float gw[8];
+        if (norm_w) {
+            *reinterpret_cast<float4 *>(gw) = *reinterpret_cast<const float4 *>(norm_w + c);
+            *reinterpret_cast<float4 *>(gw + 4) = *reinterpret_cast<const float4 *>(norm_w + c + 4);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            ss = fmaf(a[i], a[i], ss);
+            mx = fmaxf(mx, fabsf(norm_w ? a[i] * gw[i] : a[i]));
+        }
+    };
+#pragma unroll
+    for (int k = 0; k < kCache; k++) {
+        const uint32_t c = (threadIdx.x + k * kThreadsCta) * 8;
+        if (c < n_cols) {
+            load8(c, cache[k]);
+            reduce8(c, cache[k]);
+        }
+    }
+    for (uint32_t c = (threadIdx.x + kCache * kThreadsCta) * 8; c < n_cols; c += kThreadsCta * 8) {
+        float a[8];
+        load8(c, a);
+        reduce8(c, a);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if (lane == 0) {
+        sm.red[wid] = ss;
+        sm.red[32 + wid] = mx;
+    }
+    __syncthreads();
+    ss = 0.f;
+    mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < NW; i++) {
+        ss += sm.red[i];
+        mx = fmaxf(mx, sm.red[32 + i]);
+    }
+    // RMSNorm scale as the CPU runner forms it: 1 / sqrt(ss / n + eps) (yule-infer/src/model_runner.rs:254-258)
+    const float inv_rms = norm_w ? 1.0f / sqrtf(ss / (float)n_cols + eps) : 1.0f;
+    mx *= inv_rms;
+    int eb = (int)((__float_as_uint(mx) >> 23) & 0xFFu);
+    if (mx == 0.f || eb == 0xFF) eb = 127 + 13;
+    int se = 127 + 13 - (eb - 127);
+    se = se < 1 ? 1 : (se > 253 ? 253 : se);
+    const float scale = __uint_as_float((uint32_t)se << 23);
+    if (threadIdx.x == 0) sm.inv_scale[0] = __uint_as_float((uint32_t)(254 - se) << 23);
+    auto convert8 = [&](uint32_t c, float (&a)[8]) {
+        if (norm_w) {
+            float gw[8];
+            *reinterpret_cast<float4 *>(gw) = *reinterpret_cast<const float4 *>(norm_w + c);
+            *reinterpret_cast<float4 *>(gw + 4) = *reinterpret_cast<const float4 *>(norm_w + c + 4);
+#pragma unroll
+            for (int i = 0; i < 8; i++) a[i] = a[i] * inv_rms * gw[i];
+        }
+        __half hi[8], lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            a[i] *= scale;
+            hi[i] = __float2half_rn(a[i]);
+            lo[i] = __float2half_rn(a[i] - __half2float(hi[i]));
+        }
+        const uint32_t pc = c + 8 * (c >> 7);
+        *reinterpret_cast<uint4 *>(sm.xh + pc) =
+            make_uint4(h2_as_u32(__halves2half2(hi[0], hi[1])), h2_as_u32(__halves2half2(hi[2], hi[3])),
+                       h2_as_u32(__halves2half2(hi[4], hi[5])), h2_as_u32(__halves2half2(hi[6], hi[7])));
+        *reinterpret_cast<uint4 *>(sm.xl + pc) =
+            make_uint4(h2_as_u32(__halves2half2(lo[0], lo[1])), h2_as_u32(__halves2half2(lo[2], lo[3])),
+                       h2_as_u32(__halves2half2(lo[4], lo[5])), h2_as_u32(__halves2half2(lo[6], lo[7])));
+        float s8 = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+        s8 += __shfl_xor_sync(0xffffffffu, s8, 1);  // two consecutive threads hold one 16-column group
+        if ((lane & 1) == 0) sm.s32[c >> 4] = -32.0f * s8;
+    };
+#pragma unroll
+    for (int k = 0; k < kCache; k++) {
+        const uint32_t c = (threadIdx.x + k * kThreadsCta) * 8;
+        if (c < n_cols) convert8(c, cache[k]);
+    }
+    for (uint32_t c = (threadIdx.x + kCache * kThreadsCta) * 8; c < n_cols; c += kThreadsCta * 8) {
+        float a[8];
+        load8(c, a);
+        convert8(c, a);
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ uint32_t word4(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// One super-block of rows g and g+8 from the stage (`st`: stage base, `rb`: this lane's first row and the
+// block slot already folded into the plane offsets) times this lane's 16 l-values of all four column groups.
+//   bx   this lane's B source for the block: xh/xl + padded column of (blk, h, u), or the zero region
+//   s32  −32·Σx of the eight scale groups this lane applies (or zeros)
+__device__ __forceinline__ void consume_block_smem(const unsigned char *ql0, const unsigned char *qh0, const unsigned char *sc0,
+                                                   const unsigned char *d0, const __half *bx, uint32_t j_stride, const float *s32,
+                                                   int u2, float &acc0, float &acc1) {
+    float dj[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) dj[j][0] = dj[j][1] = dj[j][2] = dj[j][3] = 0.f;
+    {
+        // rows g (index 0) and g + 8 (index 1) sit 8 row pitches apart in every plane
+        const uint4 qa0 = *reinterpret_cast<const uint4 *>(ql0), qa1 = *reinterpret_cast<const uint4 *>(ql0 + 8 * kQlPitch);
+        const uint4 qb0 = *reinterpret_cast<const uint4 *>(ql0 + 32), qb1 = *reinterpret_cast<const uint4 *>(ql0 + 8 * kQlPitch + 32);
+        const uint4 h0 = *reinterpret_cast<const uint4 *>(qh0), h1 = *reinterpret_cast<const uint4 *>(qh0 + 8 * kQhPitch);
+#pragma unroll
+        for (int i4 = 0; i4 < 4; i4++) {
+            // 6-bit values of the four column groups, four weights per word, one per byte
+            uint32_t v[2][4];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint32_t qa = word4(r ? qa1 : qa0, i4), qb = word4(r ? qb1 : qb0, i4), qh = word4(r ? h1 : h0, i4);
+                v[r][0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
+                v[r][1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
+                v[r][2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
+                v[r][3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint2 b = *reinterpret_cast<const uint2 *>(bx + j * j_stride + 4 * i4);
+                // bytes → 16-bit lanes: {b0, b1} and {b2, b3}; the value is q·2^-24 as an fp16 subnormal
+                mma_16816(dj[j], __byte_perm(v[0][j], 0u, 0x4140), __byte_perm(v[1][j], 0u, 0x4140),
+                          __byte_perm(v[0][j], 0u, 0x4342), __byte_perm(v[1][j], 0u, 0x4342), b.x, b.y);
+            }
+        }
+    }
+    const float4 sa = *reinterpret_cast<const float4 *>(s32), sb = *reinterpret_cast<const float4 *>(s32 + 4);
+    const float sg[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};  // index 2j + {0,1}
+    const float k24 = 16777216.0f;
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        // the eight scales this lane applies: sc[8·u2 + 2j + {0,1}], signed bytes → float
+        const uint2 scw = *reinterpret_cast<const uint2 *>(sc0 + r * 8 * kScPitch + 8 * u2);
+        const uint32_t w0 = scw.x ^ 0x80808080u, w1 = scw.y ^ 0x80808080u;
+        const float k = 8388608.0f + 128.0f;
+        float scf[8];
+        scf[0] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7440)) - k;
+        scf[1] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7441)) - k;
+        scf[2] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7442)) - k;
+        scf[3] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7443)) - k;
+        scf[4] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7440)) - k;
+        scf[5] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7441)) - k;
+        scf[6] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7442)) - k;
+        scf[7] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7443)) - k;
+        float tmp = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // columns 2t and 2t+1 of D are scale groups (h = u2, u = 0) and (h = u2, u = 1) of group j
+            tmp = fmaf(scf[2 * j], fmaf(dj[j][2 * r], k24, sg[2 * j]), tmp);
+            tmp = fmaf(scf[2 * j + 1], fmaf(dj[j][2 * r + 1], k24, sg[2 * j + 1]), tmp);
+        }
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(d0 + r * 8 * kDPitch)));
+        if (r)
+            acc1 = fmaf(d, tmp, acc1);
+        else
+            acc0 = fmaf(d, tmp, acc0);
+    }
+}
+
+struct Q6kRingParams {
+    const uint8_t *planar;  // row-planar copy
+    float *out;
+    uint32_t n_rows, n_cols, n_tiles;
+    const float *x;
+    const float *norm_w;
+    float eps;
+    const float *residual;
+    uint32_t stages, chunks;
+    int *status;
+    long long wait_cycles;
+    uint32_t late_wait;  // inputs are not written by the previous kernel: only the stores wait for it
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, int *status, long long budget) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; it++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0u && clock64() - t0 > budget) {
+            if (status) atomicCAS(status, 0, kStatusRingTimeout);
+            return false;
+        }
+    }
+}
+// 1-D bulk copy global → shared memory of this CTA (16-byte aligned, this GPU's own memory).
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Copies of stage (tile, chunk): lane l < 16 fetches row l's ql and qh pieces, lane 16 + l its scales and d.
+__device__ __forceinline__ void issue_stage(const Q6kRingParams &p, uint32_t tile, uint32_t chunk, uint32_t bpr, uint32_t dst,
+                                            uint32_t bar, int lane) {
+    const uint32_t row0 = tile * kStageRows;
+    const uint32_t left = p.n_rows - row0;
+    const uint32_t rows = left < (uint32_t)kStageRows ? left : (uint32_t)kStageRows;
+    const uint32_t blk0 = chunk * kStageBlocks;
+    const uint32_t nblk = bpr - blk0 < (uint32_t)kStageBlocks ? bpr - blk0 : (uint32_t)kStageBlocks;
+    if (lane == 0) mbar_arrive_expect_tx(bar, rows * (nblk * 208u + 16u));
+    __syncwarp();
+    const uint32_t r = (uint32_t)lane & 15u;
+    if (r < rows) {
+        const uint8_t *rec = p.planar + (size_t)(row0 + r) * row_record_bytes(bpr);
+        if (lane < 16) {
+            bulk_g2s(dst + kQlOff + r * kQlPitch, rec + (size_t)blk0 * 128, nblk * 128u, bar);
+            bulk_g2s(dst + kQhOff + r * kQhPitch, rec + (size_t)bpr * 128 + (size_t)blk0 * 64, nblk * 64u, bar);
+        } else {
+            bulk_g2s(dst + kScOff + r * kScPitch, rec + (size_t)bpr * 192 + (size_t)blk0 * 16, nblk * 16u, bar);
+            bulk_g2s(dst + kDOff + r * kDPitch, rec + (size_t)bpr * 208 + (size_t)blk0 * 2, 16u, bar);
+        }
+    }
+}
+
+__device__ __forceinline__ void ring_group_barrier(int group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(kWarps * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreadsCta, 2)
+qmv_q6k_ring_kernel(const __grid_constant__ Q6kRingParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    yule_pdl_launch_dependents();
+
+    const int lane = threadIdx.x & 31;
+    const int group = threadIdx.x >> 8, wid = (threadIdx.x >> 5) & (kWarps - 1);
+    const int g = lane >> 2, t = lane & 3;
+    const int h = t >> 1, u = t & 1;
+    const uint32_t bpr = p.n_cols / 256;
+    const uint32_t G = gridDim.x;
+    const uint32_t first_tile = blockIdx.x + group * G, tile_stride = kGroups * G;
+    const uint32_t my_tiles = p.n_tiles > first_tile ? (p.n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+    const uint32_t S = p.stages, chunks = p.chunks;
+    const uint32_t total = my_tiles * chunks;
+
+    const RingSmem sm = carve(smem_raw, p.n_cols, S);
+    unsigned char *ring = sm.ring + (size_t)group * S * kStageBytes;
+    const uint32_t ring_u32 = smem_u32(ring);
+    const uint32_t bar0 = smem_u32(sm.bars + group * kMaxStages);
+    uint32_t *cnt = sm.cnt + group * kMaxStages;
+
+    if (wid == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < kMaxStages; i++) {
+                mbar_init(bar0 + 8 * i, 1);
+                cnt[i] = 0;
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        uint32_t k = 0, c = 0;
+        for (uint32_t n = 0; n < S && n < total; n++) {
+            issue_stage(p, first_tile + k * tile_stride, c, bpr, ring_u32 + n * kStageBytes, bar0 + 8 * n, lane);
+            if (++c == chunks) {
+                c = 0;
+                k++;
+            }
+        }
+    }
+
+    if (!p.late_wait) yule_pdl_wait();  // the activations (and the residual) come from the previous kernel
+    stage_activations(sm.x, p.x, p.n_cols, p.norm_w, p.eps);
+    if (total == 0) return;
+
+    // B source of this lane: column n = g is live only for g = t (hi) and g = t + 4 (lo)
+    const bool feeds = (g & 3) == t;
+    const __half *bx_base = feeds ? ((g >> 2) ? sm.x.xl : sm.x.xh) + (128 + 8) * h + 16 * u : reinterpret_cast<const __half *>(sm.x.zb);
+    const uint32_t blk_stride = feeds ? 2 * (128 + 8) : 0u;  // halves per super-block (two padded 128-column runs)
+    const uint32_t j_stride = feeds ? 32u : 0u;
+    // −32·Σx: charged once, by the lanes whose output columns belong to the hi part (t < 2)
+    const int u2 = t & 1;
+    const bool charge = t < 2;
+    const float *s32_base = charge ? sm.x.s32 + 8 * u2 : reinterpret_cast<const float *>(sm.x.zb);
+    const uint32_t s32_stride = charge ? 16u : 0u;
+    const uint32_t n_warps_used = bpr < (uint32_t)kWarps ? bpr : (uint32_t)kWarps;
+    float *part_base = sm.partial + (size_t)group * (2 * kWarps * 16);
+
+    uint32_t ck = 0, cc = 0;  // job and chunk of stage n
+    float acc0 = 0.f, acc1 = 0.f;
+    uint32_t slot = 0, phase = 0;
+    for (uint32_t n = 0; n < total; n++) {
+        const uint32_t bar = bar0 + 8 * slot;
+        if (!ring_wait(bar, phase, p.status, p.wait_cycles)) return;  // all eight warps of the group wait on the same copy
+        const uint32_t blk0 = cc * kStageBlocks;
+        const uint32_t nblk = bpr - blk0 < (uint32_t)kStageBlocks ? bpr - blk0 : (uint32_t)kStageBlocks;
+        if ((uint32_t)wid < nblk) {
+            const unsigned char *st = ring + (size_t)slot * kStageBytes;
+            const uint32_t blk = blk0 + wid;
+            consume_block_smem(st + kQlOff + (uint32_t)g * kQlPitch + (uint32_t)wid * 128u + 64u * h + 16u * u,
+                               st + kQhOff + (uint32_t)g * kQhPitch + (uint32_t)wid * 64u + 32u * h + 16u * u,
+                               st + kScOff + (uint32_t)g * kScPitch + (uint32_t)wid * 16u, st + kDOff + (uint32_t)g * kDPitch + (uint32_t)wid * 2u,
+                               bx_base + (size_t)blk * blk_stride, j_stride, s32_base + (size_t)blk * s32_stride, u2, acc0, acc1);
+        }
+        __syncwarp();
+        uint32_t last = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            last = ((atomicAdd(&cnt[slot], 1u) & (kWarps - 1)) == kWarps - 1) ? 1u : 0u;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last && n + S < total) {
+            uint32_t nk = ck, nc = cc + S;
+            while (nc >= chunks) {
+                nc -= chunks;
+                nk++;
+            }
+            issue_stage(p, first_tile + nk * tile_stride, nc, bpr, ring_u32 + slot * kStageBytes, bar, lane);
+        }
+        if (cc + 1 == chunks) {
+            float v0 = acc0, v1 = acc1;
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            float *part = part_base + (size_t)(ck & 1u) * (kWarps * 16);
+            if (t == 0) {
+                part[wid * 16 + g] = v0;
+                part[wid * 16 + g + 8] = v1;
+            }
+            acc0 = acc1 = 0.f;
+            if (p.late_wait) yule_pdl_wait();  // the previous kernel is settled before our stores
+            ring_group_barrier(group);
+            const uint32_t tid = threadIdx.x & (kWarps * 32 - 1);
+            if (tid < (uint32_t)kStageRows) {
+                const uint32_t row = (first_tile + ck * tile_stride) * kStageRows + tid;
+                if (row < p.n_rows) {
+                    float sacc = 0.f;  // fixed order over the warps: deterministic
+                    for (uint32_t w2 = 0; w2 < n_warps_used; w2++) sacc += part[w2 * 16 + tid];
+                    sacc *= sm.x.inv_scale[0];
+                    if (p.residual) sacc += p.residual[row];
+                    p.out[row] = sacc;
+                }
+            }
+            cc = 0;
+            ck++;
+        } else {
+            cc++;
+        }
+        if (++slot == S) {
+            slot = 0;
+            phase ^= 1u;
+        }
+    }
+}
+
+}  // namespace
+
+size_t q6k_planar_bytes(uint64_t n_rows, uint32_t n_cols) { return (size_t)n_rows * row_record_bytes(n_cols / 256) + 256; }
+
+cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planar, uint64_t n_rows, uint32_t n_cols, cudaStream_t s,
+                              uint64_t *launches) {
+    if (n_rows == 0) return cudaSuccess;
+    repack_q6k_rows_kernel<<<148 * 8, 256, 0, s>>>(raw, planar, n_rows, n_cols / 256);
+    *launches += 1;
+    return cudaGetLastError();
+}
+
+bool q6k_mma_supported(uint32_t n_cols) { return n_cols != 0 && n_cols % 256 == 0 && ring_smem_bytes(n_cols, 1) <= kFullSmSmem; }
+
+cudaError_t launch_q6k_mma(const Q6kPlanar &f, int sm_count, cudaStream_t s, uint64_t *launches) {
+    if (f.n_rows == 0) return cudaSuccess;
+    Q6kRingParams p = {};
+    p.planar = f.planar;
+    p.out = f.out;
+    p.n_rows = f.n_rows;
+    p.n_cols = f.n_cols;
+    p.n_tiles = (f.n_rows + kStageRows - 1) / kStageRows;
+    p.x = f.x;
+    p.norm_w = f.norm_w;
+    p.eps = f.eps;
+    p.residual = f.residual;
+    p.status = f.status;
+    p.wait_cycles = f.wait_cycles;
+    p.late_wait = (f.pdl && f.late_wait) ? 1u : 0u;
+    const uint32_t bpr = f.n_cols / 256;
+    p.chunks = (bpr + kStageBlocks - 1) / kStageBlocks;
+    uint32_t max_ctas = (uint32_t)sm_count;  // one CTA per SM: the other half of the SM is for the neighbouring launches
+    if (const char *k = knob("YULE_QMV_RING_CTAS")) max_ctas = (uint32_t)atoi(k) > 0 ? (uint32_t)atoi(k) : max_ctas;
+    uint32_t grid = (p.n_tiles + kGroups - 1) / kGroups;
+    if (grid > max_ctas) grid = max_ctas;
+    // Ring depth: two stages per group when they fit next to the activation image without taking the whole SM,
+    // more only up to what a group will consume; a very long x leaves room for one.
+    const size_t fixed = ring_fixed_bytes(f.n_cols);
+    uint32_t stages = fixed + 2 * (size_t)kGroups * kStageBytes <= kPreferredSmem
+                          ? (uint32_t)((kPreferredSmem - fixed) / ((size_t)kGroups * kStageBytes))
+                          : (uint32_t)((kFullSmSmem - fixed) / ((size_t)kGroups * kStageBytes));
+    if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
+    const uint32_t jobs_per_group = (p.n_tiles + kGroups * grid - 1) / (kGroups * grid);
+    const uint32_t need = jobs_per_group * p.chunks;
+    if (stages > need) stages = need;
+    if (stages < 1) return cudaErrorInvalidValue;
+    p.stages = stages;
+    const size_t smem = ring_smem_bytes(f.n_cols, stages);
+    auto kern = qmv_q6k_ring_kernel;
+    // the opt-in for large dynamic shared memory is a per-device attribute
+    static bool attr_done[64] = {};
+    static std::mutex mu;
+    {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFullSmSmem);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kThreadsCta), smem, s, f.pdl, p);
+    if (e != cudaSuccess) return e;
+    *launches += 1;
+    return cudaSuccess;
+}
+
+}  // namespace yule

@@ -169,7 +169,7 @@ struct Step {
     void then(const Tensor *a, const Tensor *b = nullptr) {
         const Tensor *ts[2] = {a, b};
         // measured neutral-to-slightly-negative on the TinyLlama-size step, so off unless asked for
-        static const bool enabled = getenv("YULE_CUDA_PREFETCH") && atoi(getenv("YULE_CUDA_PREFETCH")) != 0;
+        static const bool enabled = knob("YULE_CUDA_PREFETCH") && atoi(knob("YULE_CUDA_PREFETCH")) != 0;
         if (!enabled) ts[0] = ts[1] = nullptr;
         for (int i = 0; i < 2; i++) {
             const Tensor *t = ts[i];
@@ -178,7 +178,7 @@ struct Step {
             if (!t || !t->set) continue;
             // the bytes the next kernel will actually read: the planar copy when there is one
             next_w[i] = t->buf.planar ? (const void *)t->buf.planar : t->buf.ptr;
-            next_bytes[i] = t->buf.planar ? t->buf.planar_blocks * 210 : t->buf.size;
+            next_bytes[i] = t->buf.planar ? q6k_planar_bytes(t->buf.planar_blocks / (t->buf.planar_cols / 256), t->buf.planar_cols) - 256 : t->buf.size;
         }
     }
     // norm_w set: RMSNorm of x folded into the matvec (only valid when fusable(w, cols) holds)
@@ -200,6 +200,8 @@ struct Step {
         a.planar = w.buf.planar;
         a.norm_w = norm_w;
         a.eps = r->cfg.norm_eps;
+        a.status = r->ctx->device_status;
+        a.wait_cycles = r->ctx->wait_cycles;
         for (int i = 0; i < 2; i++) {
             a.next_w[i] = next_w[i];
             a.next_bytes[i] = next_bytes[i];
@@ -280,7 +282,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     // All-gather number `k` of layer `layer` (k = 4: the logits).  With the peer exchange each gather
     // has its own flag slot and an epoch derived from the token counter in d_state[2].
     const uint32_t epochs_per_token = 4 * c.n_layers + 1;
-    const bool skip_gather = getenv("YULE_CUDA_SKIP") && (strtoul(getenv("YULE_CUDA_SKIP"), nullptr, 0) & 512);
+    const bool skip_gather = knob("YULE_CUDA_SKIP") && (strtoul(knob("YULE_CUDA_SKIP"), nullptr, 0) & 512);
     auto gather = [&](float *buf, size_t x_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
         if (N <= 1 || skip_gather) return;
         if (r->xchg)
@@ -292,7 +294,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     const uint32_t *tok_ptr = r->d_state, *pos_ptr = r->d_state + 1;
     // Timing aid: YULE_CUDA_SKIP is a bit mask of kernel classes to leave out of the graph (results
     // are then meaningless); the time that disappears is that class's cost inside the real step.
-    const unsigned skip = getenv("YULE_CUDA_SKIP") ? (unsigned)strtoul(getenv("YULE_CUDA_SKIP"), nullptr, 0) : 0u;
+    const unsigned skip = knob("YULE_CUDA_SKIP") ? (unsigned)strtoul(knob("YULE_CUDA_SKIP"), nullptr, 0) : 0u;
     auto all_q4k = [&](std::initializer_list<const Tensor *> ts, uint32_t cols) {
         for (const Tensor *t : ts)
             if (t->type != YULE_DTYPE_Q4_K) return false;
@@ -310,7 +312,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     // and the one that consumes it are the Q4_K tensor-pipe kernel, the producer stores (value, epoch) pairs
     // straight into every rank's pair buffer as its rows are reduced and the consumer polls the pairs while it
     // stages x: no exchange launch, no fence, no flag.  YULE_TP_FUSE=0 keeps the exchange kernel everywhere.
-    const bool tp_fuse = N > 1 && r->xchg && !skip_gather && !(getenv("YULE_TP_FUSE") && atoi(getenv("YULE_TP_FUSE")) == 0);
+    const bool tp_fuse = N > 1 && r->xchg && !skip_gather && !(knob("YULE_TP_FUSE") && atoi(knob("YULE_TP_FUSE")) == 0);
     auto is_q4k_mma = [&](const Tensor &t, uint32_t cols) { return t.type == YULE_DTYPE_Q4_K && q4k_mma_supported(cols, 1); };
     auto epoch_index = [&](uint32_t layer, uint32_t k) { return k == 4 ? 4 * c.n_layers : 4 * layer + k; };
     auto push_of = [&](size_t pair_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
@@ -365,6 +367,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         f.residual = residual;
         f.swiglu_pair = pair;
         f.pdl = pdl;
+        f.status = r->ctx->device_status;
+        f.wait_cycles = r->ctx->wait_cycles;
         for (int k = 0; k < 2; k++) {
             f.next_w[k] = st.next_w[k];
             f.next_bytes[k] = st.next_bytes[k];
@@ -413,7 +417,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             a.n_splits = r->attn_splits;
             a.gqa = r->attn_gqa;
             a.max_seq_len = c.max_seq_len;
-            a.min_chunk = getenv("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_ATTN_MIN_CHUNK")) : 32;
+            a.min_chunk = knob("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(knob("YULE_CUDA_ATTN_MIN_CHUNK")) : 32;
             a.pdl = pdl;
             if (folded(l, 0)) a.tp = push_of(r->x_pair_attn, qdim_l, l, 0);
             if (!(skip & 4)) st.ok(launch_attn_decode(a, s, &st.n));
@@ -582,10 +586,13 @@ int32_t ensure_pinned(yule_cuda_runner *r, size_t n_words) {
 // per chunk instead of once per token.  It fills the KV caches only; the caller runs the last prompt
 // token through the ordinary token step, which produces the logits and the greedy pick.
 
+// Tensor-parallel runs read the device status word every this many tokens and stop enqueuing once a bounded
+// wait has given up (the waits themselves return at once after the first failure).
+constexpr uint32_t kStatusCheckTokens = 32;
 constexpr uint32_t kPrefillChunk = 512, kPrefillMinTokens = 16, kPrefillMinChunk = 256;
 
 uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
-    uint32_t c = getenv("YULE_CUDA_PREFILL_CHUNK") ? (uint32_t)atoi(getenv("YULE_CUDA_PREFILL_CHUNK")) : kPrefillChunk;
+    uint32_t c = knob("YULE_CUDA_PREFILL_CHUNK") ? (uint32_t)atoi(knob("YULE_CUDA_PREFILL_CHUNK")) : kPrefillChunk;
     c = c < 8 ? 8 : c;
     return c < r->cfg.max_seq_len ? c : r->cfg.max_seq_len;
 }
@@ -595,7 +602,7 @@ uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
 // for the attention kernel's score buffer at eight splits.
 bool prefill_batched_ok(const yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
-    if (getenv("YULE_CUDA_BATCH_PREFILL") && atoi(getenv("YULE_CUDA_BATCH_PREFILL")) == 0) return false;
+    if (knob("YULE_CUDA_BATCH_PREFILL") && atoi(knob("YULE_CUDA_BATCH_PREFILL")) == 0) return false;
     if (!r->fused || r->ctx->tp_world > 1 || !r->attn_gqa) return false;
     if (!qgemm_supported(YULE_DTYPE_Q4_K, c.dim, 8) || !qgemm_supported(YULE_DTYPE_Q4_K, c.ff_dim, 8) ||
         !qgemm_supported(YULE_DTYPE_Q4_K, c.n_heads * c.head_dim, 8))
@@ -792,14 +799,14 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     r->ctx = ctx;
     r->cfg = c;
     r->fused = c.fused != 0;
-    if (const char *e = getenv("YULE_CUDA_PDL")) r->pdl = atoi(e) != 0;
+    if (const char *e = knob("YULE_CUDA_PDL")) r->pdl = atoi(e) != 0;
     r->layers.resize(c.n_layers);
     const uint32_t hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd;
     int32_t rc = YULE_OK;
     auto A = [&](size_t n, float **p, yule_buffer *h = nullptr) {
         if (rc == YULE_OK) rc = alloc_f32(r, n, p, h);
     };
-    const bool use_xchg = tpw > 1 && !(getenv("YULE_TP_NCCL") && atoi(getenv("YULE_TP_NCCL")) != 0);
+    const bool use_xchg = tpw > 1 && !(knob("YULE_TP_NCCL") && atoi(knob("YULE_TP_NCCL")) != 0);
     if (use_xchg) {
         // gathered activations live in one region that every peer maps
         r->x_attn_out = 0;
@@ -837,7 +844,7 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     A((size_t)c.max_seq_len * half, &r->rope_cos);
     A((size_t)c.max_seq_len * half, &r->rope_sin);
     float *tmp = nullptr;
-    r->attn_gqa = attn_gqa_supported(hd, c.n_heads, c.n_kv_heads) && !(getenv("YULE_CUDA_ATTN_GQA") && atoi(getenv("YULE_CUDA_ATTN_GQA")) == 0);
+    r->attn_gqa = attn_gqa_supported(hd, c.n_heads, c.n_kv_heads) && !(knob("YULE_CUDA_ATTN_GQA") && atoi(knob("YULE_CUDA_ATTN_GQA")) == 0);
     r->attn_splits = r->attn_gqa ? attn_gqa_pick_splits(c.n_kv_heads / (ctx->tp_world > 1 ? ctx->tp_world : 1), c.max_seq_len,
                                                         ctx->prop.multiProcessorCount)
                                  : attn_pick_splits(c.n_heads, c.max_seq_len, ctx->prop.multiProcessorCount);
@@ -983,6 +990,8 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *pr
         for (uint32_t i = 0; i < rest; i++) {
             YULE_CUDA_TRY(cudaMemcpyAsync(r->d_state, r->h_pinned + 2 * i, 8, cudaMemcpyHostToDevice, s));
             YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
+            // tensor parallelism: a peer that stopped answering is noticed here, not after the whole prompt
+            if (r->xchg && (i % kStatusCheckTokens) == kStatusCheckTokens - 1 && (rc = yule_cuda_synchronize(r->ctx))) return rc;
         }
         r->ctx->launches.fetch_add((uint64_t)graph_kernels(r) * rest);
         r->pos += rest;
@@ -992,7 +1001,10 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *pr
         // Token g is the pick made after position first+g-1, i.e. d_history[first + g - 1]; each
         // replay consumes the previous pick from d_state[0] without touching the host.
         const uint32_t first = r->pos;
-        for (uint32_t g = 0; g < n_generate; g++) YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
+        for (uint32_t g = 0; g < n_generate; g++) {
+            YULE_CUDA_TRY(cudaGraphLaunch(r->graph_exec, s));
+            if (r->xchg && (g % kStatusCheckTokens) == kStatusCheckTokens - 1 && (rc = yule_cuda_synchronize(r->ctx))) return rc;
+        }
         r->ctx->launches.fetch_add((uint64_t)graph_kernels(r) * n_generate);
         r->pos += n_generate;
         YULE_CUDA_TRY(cudaMemcpyAsync(out_tokens, r->d_history + first - 1, (size_t)n_generate * 4,

@@ -121,10 +121,12 @@ tp_exchange_kernel(PeerTable peers, size_t buf_offset, uint32_t per_rank, uint32
     if (threadIdx.x < world && threadIdx.x != rank) {
         volatile uint32_t *f = my_flags + slot * kMaxRanks + threadIdx.x;
         const long long t0 = clock64();
-        // bounded: a peer that never arrives leaves a status word for the host instead of a hung GPU
+        // bounded: a peer that never arrives leaves a status word for the host instead of a hung GPU; once any
+        // wait of this context has given up, later ones return at once
         while ((int32_t)(*f - epoch) < 0) {
+            if (*reinterpret_cast<volatile int *>(status) != 0) break;
             if (clock64() - t0 > wait_cycles) {
-                atomicExch(status, 2);
+                atomicCAS(status, 0, kStatusPeerTimeout);
                 break;
             }
         }
@@ -140,8 +142,7 @@ cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t p
     for (int i = 0; i < kMaxRanks; i++) pt.base[i] = ctx->tp_peer_base[i];
     uint32_t grid = (per_rank / 4 + kXchgThreads - 1) / kXchgThreads;
     grid = grid < 1 ? 1 : (grid > 8 ? 8 : grid);
-    // ~2 s at the SM clock: far beyond any real skew between ranks, short enough to report a lost peer
-    const long long wait_cycles = 4000000000LL;
+    const long long wait_cycles = ctx->wait_cycles;
     *launches += 1;
     return launch_kernel(tp_exchange_kernel, dim3(grid), dim3(kXchgThreads), 0, ctx->stream, pdl, pt, buf_offset_floats,
                          per_rank, ctx->tp_rank, ctx->tp_world, ctx->tp_flag_offset, slot, tick, epochs_per_tick,
@@ -196,6 +197,7 @@ void tp_fuse_push(const yule_cuda_ctx *ctx, size_t pair_offset_floats, uint32_t 
     f->tick = tick;
     f->epochs_per_tick = epochs_per_tick;
     f->status = ctx->device_status;
+    f->wait_cycles = ctx->wait_cycles;
     f->push = true;
     f->push_index = index;
     for (uint32_t p = 0; p < (uint32_t)kMaxRanks; p++)
@@ -211,6 +213,7 @@ void tp_fuse_wait(const yule_cuda_ctx *ctx, size_t pair_offset_floats, const uin
     f->tick = tick;
     f->epochs_per_tick = epochs_per_tick;
     f->status = ctx->device_status;
+    f->wait_cycles = ctx->wait_cycles;
     f->wait = true;
     f->wait_index = index;
     f->pair_in = reinterpret_cast<const uint2 *>(ctx->tp_peer_base[ctx->tp_rank] + pair_offset_floats);
@@ -288,6 +291,71 @@ int32_t yule_cuda_tp_all_gather(yule_cuda_ctx *ctx, yule_buffer buffer, size_t c
     cudaError_t e = tp_all_gather_inplace(ctx, (float *)b.ptr, count_per_rank);
     if (e != cudaSuccess) return fail(YULE_ERR_CUDA, "nccl: ncclAllGather failed");
     return YULE_OK;
+}
+
+// Makes one bounded device-side wait run out on purpose, without a peer and without a fault: the waiting
+// kernel polls memory that nothing ever writes, gives up after `budget_cycles`, records the status word and
+// returns normally, and the synchronize at the end reports YULE_ERR_DEVICE_STATUS.  Single GPU.
+//   which = 0  the Q4_K matvec as consumer of a gathered vector: its (value, epoch) pairs never arrive
+//   which = 1  the exchange kernel: the stand-in peer (a second buffer on this GPU) never publishes its flag
+int32_t yule_cuda_selftest_bounded_wait(yule_cuda_ctx *ctx, uint32_t which, uint64_t budget_cycles) {
+    if (!ctx) return fail(YULE_ERR_INVALID_ARGUMENT, "null context");
+    if (which > 1) return fail(YULE_ERR_INVALID_ARGUMENT, "unknown wait selector %u", which);
+    if (ctx->tp_world > 1) return fail(YULE_ERR_INVALID_ARGUMENT, "the self-test runs on a context without tensor parallelism");
+    YULE_CUDA_TRY(cudaSetDevice(ctx->device));
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    const uint32_t n_rows = 16, n_cols = 256, per_rank = 128;
+    const size_t payload = 1024;  // floats: pairs of the 256-element vector, or the two 128-float slices
+    const size_t region_bytes = payload * sizeof(float) + (kFlagSlots * kMaxRanks + 64) * sizeof(uint32_t);
+    char *mem = nullptr;
+    const size_t w_bytes = (size_t)n_rows * 144, total = 2 * region_bytes + w_bytes + 4096;
+    YULE_CUDA_TRY(cudaMalloc((void **)&mem, total));
+    cudaError_t e = cudaMemset(mem, 0, total);
+    float *region_a = (float *)mem, *region_b = (float *)(mem + region_bytes);
+    uint8_t *w = (uint8_t *)(mem + 2 * region_bytes);
+    float *x = (float *)(mem + 2 * region_bytes + w_bytes), *out = x + n_cols;
+    const uint32_t *tick = (const uint32_t *)(out + n_rows);  // stays 0: the awaited epoch is 1
+    const long long budget = budget_cycles ? (long long)budget_cycles : ctx->wait_cycles;
+    uint64_t launches = 0;
+    if (e == cudaSuccess && which == 0) {
+        Q4kFused f;
+        f.w[0] = w;
+        f.out[0] = out;
+        f.rows[0] = n_rows;
+        f.out_stride[0] = n_rows;
+        f.x = x;
+        f.x_stride = n_cols;
+        f.n_cols = n_cols;
+        f.status = ctx->device_status;
+        f.wait_cycles = budget;
+        f.tp.world = 2;
+        f.tp.tick = tick;
+        f.tp.epochs_per_tick = 1;
+        f.tp.status = ctx->device_status;
+        f.tp.wait_cycles = budget;
+        f.tp.wait = true;
+        f.tp.wait_index = 0;
+        f.tp.pair_in = reinterpret_cast<const uint2 *>(region_a);
+        e = launch_q4k_mma(f, ctx->prop.multiProcessorCount, ctx->stream, &launches);
+    } else if (e == cudaSuccess) {
+        const long long saved_budget = ctx->wait_cycles;
+        ctx->tp_peer_base[0] = region_a;
+        ctx->tp_peer_base[1] = region_b;
+        ctx->tp_rank = 0;
+        ctx->tp_world = 2;
+        ctx->tp_flag_offset = payload;
+        ctx->wait_cycles = budget;
+        e = tp_exchange(ctx, 0, per_rank, 0, tick, 1, 0, false, &launches);
+        ctx->tp_peer_base[0] = ctx->tp_peer_base[1] = nullptr;
+        ctx->tp_world = 1;
+        ctx->tp_flag_offset = 0;
+        ctx->wait_cycles = saved_budget;
+    }
+    ctx->launches.fetch_add(launches);
+    int32_t rc = e == cudaSuccess ? yule_cuda_synchronize(ctx) : fail_cuda(e, "bounded-wait self-test launch");
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(mem);
+    return rc;
 }
 
 }  // extern "C"
