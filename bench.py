@@ -23,6 +23,15 @@ prompt pass is timed separately).
 With --gpus N > 1 (launched under torchrun, one rank per GPU) every rank decodes its own independent
 sequence with its own replica of the model — batch-1 decode of a model that fits one GPU has no
 exchange step — and `value` is the sum over ranks divided by the slowest rank's time (weak scaling).
+
+`tp` — measured in the same run at every N: batch-1 decode of the Llama-3-70B-architecture model
+       (BASELINE.json configs[4], every linear Q4_K, ~39 GB) with the output rows of every linear sharded over
+       the N GPUs and the activations exchanged over NVLink peer memory (strong scaling: one sequence, N GPUs).
+       Carries ms/token, tokens/s, the per-GPU fraction of the HBM roofline, and `tp_check`: a two-layer model
+       of the same layer shapes run on N GPUs and on one, logits compared bit for bit and greedy tokens compared.
+
+`--impl reference` — the CPU runner (the oracle's restatement of the reference, its own Q4_K assembly kernel
+       where built) on the same job: the same 32-token prompt, then greedy tokens until 128 or a time budget.
 """
 
 from __future__ import annotations
@@ -43,6 +52,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 N_PROMPT, N_GEN = 32, 128
+# DRAM bytes of one 5632x2048 launch of the ring kernel, from the ncu capture summarised in the named file
+RING_TRAFFIC_BYTES = None
+RING_TRAFFIC_SOURCE = "profiles/qmv_q4k_ring_5632x2048.md (ncu capture of one launch; null until captured for this kernel)"
 METRIC = "batch-1 decode tokens/s; Q4_K matvec achieved HBM GB/s vs B200 peak"
 UNIT = "tokens/s"
 
@@ -195,13 +207,15 @@ def matvec_ring_roofline(backend, peaks, peak_kind, iters: int = 1000) -> dict:
     bytes_per_launch = matvec_bytes(dt, n_rows, n_cols)
     achieved = bytes_per_launch * iters / (ms * 1e-3) / 1e9
     peak = float(peaks["hbm_gbs"])
-    return {"bound": "hbm", "kernel": "qmv_q4k_mma_kernel", "workload": "Q4_K 5632x2048 matvec x1000 over an 80-copy ring (519 MB)",
+    return {"bound": "hbm", "kernel": "qmv_q4k_ring_kernel",
+            "workload": "Q4_K 5632x2048 matvec x1000 over an 80-copy ring (519 MB); the launches are independent calls of the "
+                        "trait method (same input vector), so each overlaps with its predecessor and only its stores wait for it",
             "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
             "frac": round(achieved / peak, 4), "bytes_per_launch": bytes_per_launch,
             "us_per_launch": round(ms * 1e3 / iters, 3),
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch in the committed ncu capture
-            # (profiles/qmv_q4k_mma_5632x2048.md): nothing is re-read
-            "traffic": 6547456}
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch in the committed ncu capture: not measured
+            # in this run
+            "traffic": RING_TRAFFIC_BYTES, "traffic_source": RING_TRAFFIC_SOURCE}
 
 
 def large_shape_rooflines(backend, peaks) -> dict:
@@ -225,8 +239,9 @@ def large_shape_rooflines(backend, peaks) -> dict:
 
 
 def cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s: float, max_tokens: int):
-    """Decode tokens/s of the CPU runner restated in the oracle, all host threads, on a bounded sample:
-    a 4-token prompt, then greedy decode steps until `budget_s` seconds or `max_tokens` tokens."""
+    """Decode tokens/s of the CPU runner restated in the oracle, all host threads, on a bounded sample of the
+    same job: the same prompt token by token (untimed, as the prompt pass of the GPU arm), then greedy decode
+    steps until `budget_s` seconds or `max_tokens` tokens."""
     from oracle import oracle as o
     have_asm = o.load_reference_asm()
     simd = o.AVX2_ASM if have_asm else (o.AVX2 if o.lib.yo_have_avx2() else o.SCALAR)
@@ -235,7 +250,7 @@ def cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s: float, max_tokens: 
                 norm_eps=cfg.norm_eps, rope_freq_base=cfg.rope_freq_base, simd=simd, n_threads=0)
     for name, (data, dt) in weights.items():
         m.set_tensor(name, data, int(dt))
-    logits = m.prefill(prompt[:4])
+    logits = m.prefill(prompt)
     n, t0 = 0, time.perf_counter()
     while n < max_tokens and (time.perf_counter() - t0) < budget_s:
         logits = m.decode_step(o.argmax(logits))
@@ -243,34 +258,154 @@ def cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s: float, max_tokens: 
     dt_s = time.perf_counter() - t0
     cores = o.lib.yo_hardware_threads()
     kind = "port"
-    sample = (f"{n} greedy decode tokens after a 4-token prompt, TinyLlama-arch Q4_K/Q6_K, "
-              f"{'reference q4k_gemv_avx2.S for Q4_K blocks, ' if have_asm else ''}"
+    sample = (f"{n} of the {max_tokens} greedy decode tokens after the same {len(prompt)}-token prompt (time-bounded), "
+              f"TinyLlama-arch Q4_K/Q6_K, {'reference q4k_gemv_avx2.S for Q4_K blocks, ' if have_asm else ''}"
               f"{'AVX2' if simd != o.SCALAR else 'scalar'} fused dots, one thread per row chunk per matvec")
     return n / dt_s, cores, kind, sample, n, dt_s
+
+
+WORKLOAD_C1 = ("configs[1] TinyLlama-1.1B-arch decode, {linear} linears, Q6_K output+ffn_down, fp32 KV, batch 1, "
+               "{n_prompt}-token prompt + {n_gen} greedy tokens per step")
 
 
 def run_reference(args, rank: int, world: int) -> int:
     if rank != 0:
         return 0
     cfg, weights, prompt = build_model(0)
-    vals, total_tokens, total_s = [], 0, 0.0
+    total_tokens, total_s = 0, 0.0
+    cores = kind = sample = None
     for _ in range(args.warmup):
-        cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s=1.0, max_tokens=2)
+        cpu_forward_tokens_per_s(cfg, weights, prompt[:2], budget_s=0.5, max_tokens=2)
     for _ in range(args.steps):
-        tps, cores, kind, sample, n, dt_s = cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s=6.0, max_tokens=16)
-        vals.append(tps)
+        tps, cores, kind, sample, n, dt_s = cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s=4.0, max_tokens=N_GEN)
         total_tokens += n
         total_s += dt_s
     value = total_tokens / total_s
     line = {"impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * total_s / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1] TinyLlama-1.1B-arch decode, Q4_K linears, Q6_K output+ffn_down, batch 1"},
+            "config": {"workload": WORKLOAD_C1.format(linear="Q4_K", n_prompt=N_PROMPT, n_gen=N_GEN),
+                       "parallelism": "host cores of rank 0 (the reference has no multi-device path)",
+                       "sample": sample},
             "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
     return 0
+
+
+def measure_tp(args, rank: int, world: int, local_rank: int, dist, peaks) -> dict | None:
+    """configs[4] at world size N: batch-1 decode of the Llama-3-70B-architecture model, output rows of every
+    linear sharded over the N GPUs (one layer's tensors generated once and uploaded for all 80 layers, each
+    rank generating only its own rows).  Before the timing, a two-layer model of the same layer shapes is run
+    on N GPUs and (on rank 0) on one GPU: logits compared bit for bit, greedy tokens compared."""
+    import dataclasses
+    from yule_b200 import CudaB200Backend, CudaTransformerRunner, DType, YuleGpuError, synth
+
+    def gather_max(v: float) -> float:
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n_prompt, n_gen = (8, 8) if args.small else (args.tp_prompt, args.tp_gen)
+    full = synth.LLAMA3_70B
+    out = {"workload": f"configs[4] Llama-3-70B-arch decode, all linears Q4_K (one layer's tensors repeated for the "
+                       f"{full.n_layers} layers), fp32 KV, batch 1, {n_prompt}-token prompt + {n_gen} greedy tokens",
+           "world": world, "scaling": "strong",
+           "exchange": ("none (one GPU)" if world == 1 else
+                        "(value, epoch) pairs stored into every rank's peer-mapped buffer from the producer's epilogue, "
+                        "polled by the consumer; logits through the exchange kernel; NVLS/multimem not used")}
+    tpb = CudaB200Backend(local_rank)
+    try:
+        if world > 1:
+            ids = [CudaB200Backend.tp_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            tpb.tp_init(rank, world, ids[0])
+            tpb.set_wait_budget(600_000_000)  # ~0.3 s: a lost peer ends the step quickly with a status, not a stall
+        # ── parity: two layers, N GPUs against one ────────────────────────────────────────────────
+        small = dataclasses.replace(full, n_layers=2, vocab_size=8192, max_seq_len=64)
+        w_loc = synth.synthetic_model(small, seed=71, linear=DType.Q4_K, rank=rank, world=world)
+        prompt = synth.tokens(11, 6, small.vocab_size)
+        run = CudaTransformerRunner(tpb, small, w_loc, fused=True)
+        logits_tp = run.prefill(prompt).copy()
+        run.reset()
+        toks_tp = run.generate_greedy(prompt, 12)
+        run.close()
+        if world > 1 and rank == 0:
+            one = CudaB200Backend(local_rank)
+            w_all = synth.synthetic_model(small, seed=71, linear=DType.Q4_K)
+            run1 = CudaTransformerRunner(one, small, w_all, fused=True)
+            logits_1 = run1.prefill(prompt).copy()
+            run1.reset()
+            toks_1 = run1.generate_greedy(prompt, 12)
+            run1.close()
+            one.close()
+            scale = float(np.abs(logits_1).max())
+            out["tp_check"] = {"world": world, "layers": 2,
+                               "logits_bit_identical": bool(np.array_equal(logits_tp.view(np.uint32), logits_1.view(np.uint32))),
+                               "logits_max_rel_diff": float(np.abs(logits_tp - logits_1).max() / max(scale, 1e-30)),
+                               "greedy_identical": bool(np.array_equal(toks_tp, toks_1))}
+        elif world == 1:
+            out["tp_check"] = {"world": 1, "note": "the one-GPU run is the reference of the check"}
+        del w_loc
+        # ── timing: the 80-layer model ────────────────────────────────────────────────────────────
+        cfg = full if not args.small else dataclasses.replace(full, n_layers=4)
+        one_layer = synth.synthetic_model(dataclasses.replace(cfg, n_layers=1), seed=70, linear=DType.Q4_K, rank=rank, world=world)
+        weights = {}
+        for name, val in one_layer.items():
+            if name.startswith("blk.0."):
+                for l in range(cfg.n_layers):
+                    weights[name.replace("blk.0.", f"blk.{l}.")] = val
+            elif name != "token_embd.weight":
+                weights[name] = val
+        # the embedding table is replicated and only one row per token is read: a sixteenth of it is generated
+        # and repeated (rows are self-contained runs of blocks)
+        part = synth.random_quantized(DType.Q4_K, synth.tensor_seed(70, "token_embd.weight"), cfg.vocab_size // 16 * cfg.dim)
+        weights["token_embd.weight"] = (np.tile(part, 16), DType.Q4_K)
+        prompt = synth.tokens(7, n_prompt, cfg.vocab_size)
+        run = CudaTransformerRunner(tpb, cfg, weights, fused=True)
+
+        def job():
+            run.reset()
+            e0 = tpb.event_record()
+            run.generate_greedy(prompt, 0)
+            e1 = tpb.event_record()
+            toks = run.generate_greedy([], n_gen)
+            e2 = tpb.event_record()
+            return tpb.event_elapsed_ms(e0, e1), tpb.event_elapsed_ms(e1, e2), toks
+
+        job()
+        tpb.synchronize()
+        tpb.event_reset()
+        if dist is not None:
+            dist.barrier()
+        reps = 1 if args.small else 2
+        pre_ms = dec_ms = 0.0
+        for _ in range(reps):
+            p_ms, d_ms, _ = job()
+            pre_ms += p_ms
+            dec_ms += d_ms
+        tpb.synchronize()
+        dec_ms = gather_max(dec_ms)
+        pre_ms = gather_max(pre_ms)
+        bpt = decode_bytes_per_token(cfg, weights, n_prompt + n_gen // 2, tp_world=world)
+        ms_tok = dec_ms / (reps * n_gen)
+        gbs = bpt / (ms_tok * 1e-3) / 1e9
+        out.update({"ms_per_token": round(ms_tok, 4), "tokens_per_s": round(1e3 / ms_tok, 2),
+                    "prefill_tokens_per_s": round(n_prompt * reps / (pre_ms * 1e-3), 1),
+                    "hbm_bytes_per_token_per_gpu": bpt, "achieved_gbs_per_gpu": round(gbs, 1),
+                    "frac_of_peak_per_gpu": round(gbs / float(peaks["hbm_gbs"]), 4),
+                    "dominant_kernel": "qmv_q4k_mma_kernel (Q4_K matvec, about 95 % of the token step; attention and the "
+                                       "logits exchange are the rest)"})
+        run.close()
+    except YuleGpuError as e:
+        out["error"] = f"{e.code}: {e.message}"
+    finally:
+        tpb.close()
+    return out if rank == 0 else None
 
 
 def run_ours(args, rank: int, world: int, local_rank: int) -> int:
@@ -366,8 +501,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
     value = total_tokens / (decode_ms_max * 1e-3)
     e2e_value = total_tokens / (e2e_ms_max * 1e-3)
 
+    peaks, peak_kind = measured_peaks()
+    tp_obj = None
+    if not tp and not args.no_tp:
+        tp_obj = measure_tp(args, rank, world, local_rank, dist, peaks)
+
     if rank == 0:
-        peaks, peak_kind = measured_peaks()
         roof = matvec_ring_roofline(backend, peaks, peak_kind, iters=20 if args.small else 1000)
         roof_large = None if (args.small or world > 1 or args.workload != "c1") else large_shape_rooflines(backend, peaks)
         mid_pos = N_PROMPT + N_GEN // 2
@@ -376,11 +515,11 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         decode_gbs = bpt * per_gpu_tok_s / 1e9
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            tps, cores, kind, sample, _, _ = cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s=12.0, max_tokens=48)
+            tps, cores, kind, sample, _, _ = cpu_forward_tokens_per_s(cfg, weights, prompt, budget_s=10.0, max_tokens=N_GEN)
             cpu = {"value": round(tps, 3), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round((prefill_ms + decode_ms) / args.steps, 3),
+            "warmup": max(args.warmup, 3), "warmup_requested": args.warmup, "ms_per_step": round((prefill_ms + decode_ms) / args.steps, 3),
             "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": ({"workload": ("configs[4] Llama-3-70B-arch decode, all linears Q4_K" if args.workload == "c4" else
@@ -391,8 +530,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
                                        "NCCL all-gather of activations",
                         "l2": "weights read per token per GPU (GBs) exceed the 126 MB L2; no flush needed"}
                        if tp else
-                       {"workload": f"configs[1] TinyLlama-1.1B-arch decode, {args.linear} linears, Q6_K output+ffn_down, "
-                                    f"fp32 KV, batch 1, {N_PROMPT}-token prompt + {N_GEN} greedy tokens per step",
+                       {"workload": WORKLOAD_C1.format(linear=args.linear, n_prompt=N_PROMPT, n_gen=N_GEN),
                         "parallelism": f"{world} independent replica(s), one sequence per GPU",
                         "l2": f"weights read per token ({bpt / 1e6:.0f} MB) exceed the 126 MB L2; no flush needed"}),
             "decode": {"ms_per_token": round(decode_ms / (N_GEN * args.steps), 4),
@@ -404,7 +542,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
                     "d2h_bytes_per_step": 4 * cfg.vocab_size * N_GEN,
                     "path": "ModelRunner prefill/decode_step over the C ABI, host logits + host argmax"},
             "gpu_launches": int(launches), "roofline": roof, "roofline_large_shapes": roof_large, "cpu_baseline": cpu,
-            "clocks": clocks,
+            "clocks": clocks, "tp": tp_obj,
         }
         print(json.dumps(line), flush=True)
     runner.close()
@@ -426,6 +564,9 @@ def main() -> int:
                          "prompt + 256 tokens.  c4: Llama-3-70B-arch decode (512-token prompt + "
                          "256 tokens).  c3/c4 shard the output rows of every linear over the GPUs (tensor parallelism)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp", action="store_true", help="leave out the `tp` object (the 70B-arch tensor-parallel decode)")
+    ap.add_argument("--tp-prompt", type=int, default=64, help="prompt tokens of the `tp` measurement")
+    ap.add_argument("--tp-gen", type=int, default=128, help="generated tokens of the `tp` measurement")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized run: 4-token prompt + 4 tokens, 20 ring launches, no CPU leg")
     ap.add_argument("--linear", default="Q4_K", choices=["Q4_K", "Q5_K", "Q8_0", "Q4_0", "Q5_0"],

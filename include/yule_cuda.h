@@ -270,6 +270,17 @@ typedef struct {
      *    MultiheadAttn, Add, SiluMul), launched one by one.
      * 1: fused kernels replayed from a CUDA graph (same arithmetic per row). */
     uint32_t fused;
+    /* Architecture variants of the dense path, as RunnerConfig derives them from the file
+     * (yule-infer/src/model_runner.rs:417-460); all zero = the Llama default.  The reference's GPU runner drops
+     * them (gpu_runner.rs implements the Llama path only); its CPU runner is the contract.
+     * Optional tensors go with them: "blk.N.attn_{q,k,v}.bias" (F32 / F16; :640-651) and Gemma2's
+     * "blk.N.attn_post_norm.weight" / "blk.N.ffn_post_norm.weight" (:764-779, :985-999). */
+    uint32_t rotary_dim;         /* partial RoPE: rotated prefix of every head (:430-434); 0 or >= head_dim = all of it */
+    uint32_t sliding_window;     /* attention sees positions >= pos - window (:688-696); 0 = none */
+    float attn_logit_softcap;    /* score = cap * tanh(score / cap) before the softmax (:716-721); 0 = none */
+    float logit_softcap;         /* the same on the final logits (:1027-1032); 0 = none */
+    float norm_weight_offset;    /* Gemma: norms use (w + offset), embeddings are scaled by sqrt(dim) (:246-275, :568-574) */
+    uint32_t geglu;              /* Gemma: gelu(gate) * up instead of SiLU(gate) * up (:974-978) */
 } yule_runner_config;
 
 int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cfg,
@@ -295,6 +306,19 @@ int32_t yule_cuda_runner_position(yule_cuda_runner *runner, uint32_t *out_pos);
 int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *runner, const uint32_t *prompt,
                                          uint32_t n_prompt, uint32_t n_generate,
                                          uint32_t *out_tokens);
+/* Batched decode: `batch` independent sequences, one new token each per call, every sequence with its own
+ * KV caches and position (all start at 0; reset_batch rewinds them).  Per sequence the result is that of
+ * decode_step on a runner of its own (the reference serves one sequence per ModelRunner,
+ * yule-infer/src/lib.rs:169-216); across the batch every linear is one GEMM, so the weights are read once
+ * per step.  Single GPU, fused = 1, Llama op sequence, n_cols in multiples of 256; the first call fixes the
+ * batch size of the runner.  logits_out: [batch][vocab_size] floats or null. */
+int32_t yule_cuda_runner_decode_batch(yule_cuda_runner *runner, const uint32_t *tokens, uint32_t batch, float *logits_out);
+int32_t yule_cuda_runner_reset_batch(yule_cuda_runner *runner);
+/* Greedy generation for a batch, picks made on the device: prompts is [batch][n_prompt] (equal lengths),
+ * out_tokens [batch][n_generate]; token g of a sequence is the pick made after its position
+ * n_prompt - 1 + g (ties to the highest index, sampler.rs:150-163). */
+int32_t yule_cuda_runner_generate_greedy_batch(yule_cuda_runner *runner, const uint32_t *prompts, uint32_t batch,
+                                               uint32_t n_prompt, uint32_t n_generate, uint32_t *out_tokens);
 /* Device buffers of the runner for layer-by-layer checks: which = 0 hidden,
  * 1 K cache of `layer`, 2 V cache of `layer`, 3 logits. */
 int32_t yule_cuda_runner_buffer(yule_cuda_runner *runner, uint32_t which, uint32_t layer,

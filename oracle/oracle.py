@@ -28,6 +28,8 @@ class ModelConfig(C.Structure):
         ("ff_dim", C.c_uint32), ("max_seq_len", C.c_uint32),
         ("norm_eps", C.c_float), ("rope_freq_base", C.c_float),
         ("mod_enabled", C.c_int32), ("simd", C.c_int32), ("n_threads", C.c_int32),
+        ("rotary_dim", C.c_uint32), ("sliding_window", C.c_uint32), ("attn_logit_softcap", C.c_float),
+        ("logit_softcap", C.c_float), ("norm_weight_offset", C.c_float), ("geglu", C.c_int32),
     ]
 
 
@@ -62,6 +64,10 @@ def _load() -> C.CDLL:
     lib.yo_softmax.restype = None
     lib.yo_attention.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p] + [C.c_size_t] * 4
     lib.yo_attention.restype = None
+    lib.yo_attention_ex.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p] + [C.c_size_t] * 5 + [C.c_float]
+    lib.yo_attention_ex.restype = None
+    lib.yo_gelu.argtypes = [C.c_float]
+    lib.yo_gelu.restype = C.c_float
     lib.yo_swiglu.argtypes = [_f32p, _f32p, C.c_size_t]
     lib.yo_swiglu.restype = None
     lib.yo_argmax.argtypes = [_f32p, C.c_size_t]
@@ -193,9 +199,11 @@ def rope_table(max_seq_len: int, rotary_dim: int, freq_base: float):
     return cos, sin
 
 
-def apply_rope(vec: np.ndarray, pos: int, head_dim: int, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+def apply_rope(vec: np.ndarray, pos: int, head_dim: int, cos: np.ndarray, sin: np.ndarray,
+               rotary_dim: int = 0) -> np.ndarray:
+    """``rotary_dim`` (0 = head_dim) is the dimension the table was built for: only that prefix of each head turns."""
     out = np.array(vec, dtype=np.float32, copy=True)
-    lib.yo_apply_rope(_f32(out), out.size, pos, head_dim, head_dim // 2, _f32(cos), _f32(sin))
+    lib.yo_apply_rope(_f32(out), out.size, pos, head_dim, (rotary_dim or head_dim) // 2, _f32(cos), _f32(sin))
     return out
 
 
@@ -205,15 +213,20 @@ def softmax(s: np.ndarray) -> np.ndarray:
     return out
 
 
-def attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len) -> np.ndarray:
+def attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len, sliding_window: int = 0,
+              softcap: float = 0.0) -> np.ndarray:
     q = np.ascontiguousarray(q, np.float32)
     k_cache = np.ascontiguousarray(k_cache, np.float32)
     v_cache = np.ascontiguousarray(v_cache, np.float32)
     out = np.zeros(n_heads * head_dim, np.float32)
     scratch = np.zeros(max(seq_len, 1), np.float32)
-    lib.yo_attention(_f32(q), _f32(k_cache), _f32(v_cache), _f32(out), _f32(scratch), n_heads,
-                     n_kv_heads, head_dim, seq_len)
+    lib.yo_attention_ex(_f32(q), _f32(k_cache), _f32(v_cache), _f32(out), _f32(scratch), n_heads,
+                        n_kv_heads, head_dim, seq_len, sliding_window, softcap)
     return out
+
+
+def gelu(x: float) -> float:
+    return float(lib.yo_gelu(x))
 
 
 def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
@@ -233,12 +246,15 @@ class Model:
 
     def __init__(self, *, dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, ff_dim,
                  max_seq_len, norm_eps=1e-5, rope_freq_base=10000.0, mod_enabled=-1, simd=SCALAR,
-                 n_threads=0):
+                 n_threads=0, rotary_dim=0, sliding_window=0, attn_logit_softcap=0.0, logit_softcap=0.0,
+                 norm_weight_offset=0.0, geglu=False):
         if simd == AVX2_ASM and not load_reference_asm():
             simd = AVX2
         self.simd = simd
         self.cfg = ModelConfig(dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, ff_dim,
-                               max_seq_len, norm_eps, rope_freq_base, mod_enabled, simd, n_threads)
+                               max_seq_len, norm_eps, rope_freq_base, mod_enabled, simd, n_threads,
+                               rotary_dim, sliding_window, attn_logit_softcap, logit_softcap, norm_weight_offset,
+                               1 if geglu else 0)
         self._m = lib.yo_model_create(C.byref(self.cfg))
         self._keep = {}
 

@@ -496,23 +496,33 @@ void yo_softmax(float *s, size_t n) {
         s[i] *= inv;
 }
 
-/* model_runner.rs:672-758 without sliding window / softcap / streaming. */
-void yo_attention(const float *q, const float *k_cache, const float *v_cache, float *attn_out,
-                  float *scores, size_t n_heads, size_t n_kv_heads, size_t hd, size_t seq_len) {
+/* model_runner.rs:672-758, flat cache (no streaming cache).  A masked score is -inf, so it contributes
+ * exp(-inf) = 0 to the softmax and 0 * v to the output, exactly as in the reference. */
+void yo_attention_ex(const float *q, const float *k_cache, const float *v_cache, float *attn_out,
+                     float *scores, size_t n_heads, size_t n_kv_heads, size_t hd, size_t seq_len,
+                     size_t sliding_window, float softcap) {
     size_t group = n_heads / n_kv_heads;
     size_t kv_stride = n_kv_heads * hd;
+    size_t pos = seq_len - 1;
     float scale = 1.0f / sqrtf((float)hd);
     memset(attn_out, 0, n_heads * hd * sizeof(float));
     for (size_t h = 0; h < n_heads; h++) {
         size_t kv_h = h / group;
         const float *qh = q + h * hd;
         for (size_t t = 0; t < seq_len; t++) {
+            if (sliding_window && pos >= sliding_window && t < pos - sliding_window) {
+                scores[t] = -INFINITY;
+                continue;
+            }
             const float *kh = k_cache + t * kv_stride + kv_h * hd;
             float dot = 0.0f;
             for (size_t d = 0; d < hd; d++)
                 dot += qh[d] * kh[d];
             scores[t] = dot * scale;
         }
+        if (softcap != 0.0f)
+            for (size_t t = 0; t < seq_len; t++)
+                scores[t] = softcap * tanhf(scores[t] / softcap);
         yo_softmax(scores, seq_len);
         float *oh = attn_out + h * hd;
         for (size_t t = 0; t < seq_len; t++) {
@@ -522,6 +532,11 @@ void yo_attention(const float *q, const float *k_cache, const float *v_cache, fl
                 oh[d] += w * vh[d];
         }
     }
+}
+
+void yo_attention(const float *q, const float *k_cache, const float *v_cache, float *attn_out,
+                  float *scores, size_t n_heads, size_t n_kv_heads, size_t hd, size_t seq_len) {
+    yo_attention_ex(q, k_cache, v_cache, attn_out, scores, n_heads, n_kv_heads, hd, seq_len, 0, 0.0f);
 }
 
 /* model_runner.rs:968-972 */
@@ -561,6 +576,8 @@ typedef struct {
 
 typedef struct {
     yo_tensor attn_norm, attn_q, attn_k, attn_v, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down;
+    /* optional (weight_loader.rs:203-218): Qwen2 Q/K/V biases, Gemma2 post-norms */
+    yo_tensor attn_q_bias, attn_k_bias, attn_v_bias, attn_post_norm, ffn_post_norm;
 } yo_layer;
 
 struct yo_model {
@@ -570,7 +587,7 @@ struct yo_model {
     yo_layer *layers;
     float **k_cache, **v_cache;
     float *hidden, *residual, *normed, *q, *k, *v, *attn_out, *attn_proj, *scores, *gate, *up,
-        *ffn_out, *normw;
+        *ffn_out, *normw, *post_tmp;
     float *rope_cos, *rope_sin;
     uint32_t pos;
     /* Mixture-of-Depths bookkeeping (mixture_of_depths.rs:28-67) */
@@ -598,6 +615,7 @@ yo_model *yo_model_create(const yo_model_config *cfg) {
     m->residual = falloc(dim);
     m->normed = falloc(dim);
     m->normw = falloc(dim);
+    m->post_tmp = falloc(dim);
     m->q = falloc((size_t)cfg->n_heads * hd);
     m->k = falloc((size_t)cfg->n_kv_heads * hd);
     m->v = falloc((size_t)cfg->n_kv_heads * hd);
@@ -607,10 +625,12 @@ yo_model *yo_model_create(const yo_model_config *cfg) {
     m->gate = falloc(cfg->ff_dim);
     m->up = falloc(cfg->ff_dim);
     m->ffn_out = falloc(dim);
-    size_t half = hd / 2;
+    /* model_runner.rs:430-434: a rotary dimension below head_dim rotates only that prefix of every head */
+    size_t rot = (cfg->rotary_dim && cfg->rotary_dim < hd) ? cfg->rotary_dim : hd;
+    size_t half = rot / 2;
     m->rope_cos = falloc((size_t)cfg->max_seq_len * half);
     m->rope_sin = falloc((size_t)cfg->max_seq_len * half);
-    yo_rope_table(cfg->max_seq_len, hd, cfg->rope_freq_base, m->rope_cos, m->rope_sin);
+    yo_rope_table(cfg->max_seq_len, rot, cfg->rope_freq_base, m->rope_cos, m->rope_sin);
     m->mod_layer_computed = (uint8_t *)malloc(L ? L : 1);
     memset(m->mod_layer_computed, 1, L ? L : 1);
     return m;
@@ -630,6 +650,7 @@ void yo_model_destroy(yo_model *m) {
     free(m->residual);
     free(m->normed);
     free(m->normw);
+    free(m->post_tmp);
     free(m->q);
     free(m->k);
     free(m->v);
@@ -671,7 +692,10 @@ int yo_model_set_tensor(yo_model *m, const char *name, const uint8_t *data, size
                      {"attn_k.weight", &l->attn_k},           {"attn_v.weight", &l->attn_v},
                      {"attn_output.weight", &l->attn_output}, {"ffn_norm.weight", &l->ffn_norm},
                      {"ffn_gate.weight", &l->ffn_gate},       {"ffn_up.weight", &l->ffn_up},
-                     {"ffn_down.weight", &l->ffn_down}};
+                     {"ffn_down.weight", &l->ffn_down},       {"attn_q.bias", &l->attn_q_bias},
+                     {"attn_k.bias", &l->attn_k_bias},        {"attn_v.bias", &l->attn_v_bias},
+                     {"attn_post_norm.weight", &l->attn_post_norm},
+                     {"ffn_post_norm.weight", &l->ffn_post_norm}};
         for (size_t i = 0; i < sizeof(slots) / sizeof(slots[0]); i++)
             if (!strcmp(rest, slots[i].n)) {
                 *slots[i].t = t;
@@ -700,6 +724,24 @@ static int model_qmv(const yo_model *m, const yo_tensor *t, const float *x, size
     return yo_qmv(t->type, t->data, x, out, n_rows, n_cols, m->cfg.n_threads, m->cfg.simd);
 }
 
+/* model_runner.rs:295-310: F32 or F16 bias added element by element. */
+static void add_bias(float *v, size_t n, const yo_tensor *b) {
+    for (size_t i = 0; i < n; i++) {
+        float x;
+        if (b->type == YO_F32)
+            memcpy(&x, b->data + 4 * i, 4);
+        else
+            x = rd_f16(b->data, 2 * i);
+        v[i] += x;
+    }
+}
+
+/* model_runner.rs:312-314 */
+static float gelu_tanh(float x) {
+    return x * 0.5f * (1.0f + tanhf(0.7978846f * (x + 0.044715f * x * x * x)));
+}
+float yo_gelu(float x) { return gelu_tanh(x); }
+
 /* mixture_of_depths.rs:113-117 */
 static float activation_norm(const float *h, size_t n) {
     float ss = 0.0f;
@@ -723,8 +765,8 @@ static int should_skip_layer(const float *hidden, size_t dim, size_t layer, size
     return activation_norm(hidden, dim) < skip_threshold;
 }
 
-/* model_runner.rs:533-1036, Llama-family dense path (no bias, no MoE, no
- * Gemma post-norms/softcaps, flat KV cache). */
+/* model_runner.rs:533-1036, dense path with its architecture variants (Q/K/V bias, partial RoPE, sliding
+ * window, Gemma norm offset / embedding scale / GeGLU / post-norms / softcaps); no MoE, flat KV cache. */
 int yo_model_forward(yo_model *m, uint32_t token, float *logits) {
     const yo_model_config *c = &m->cfg;
     size_t dim = c->dim, hd = c->head_dim, n_heads = c->n_heads, n_kv = c->n_kv_heads;
@@ -745,6 +787,15 @@ int yo_model_forward(yo_model *m, uint32_t token, float *logits) {
             if (yo_dequant_block(m->token_embd.type, tok + b * (size_t)bb, m->hidden + b * (size_t)bs))
                 return -1;
     }
+
+    /* Gemma: embeddings scaled by sqrt(dim) (:568-574) */
+    const float norm_off = c->norm_weight_offset;
+    if (norm_off > 0.0f) {
+        float sc = sqrtf((float)dim);
+        for (size_t i = 0; i < dim; i++)
+            m->hidden[i] *= sc;
+    }
+    size_t rot = (c->rotary_dim && c->rotary_dim < hd) ? c->rotary_dim : hd;
 
     size_t seq_len = pos + 1;
     if (m->mod_on)
@@ -770,49 +821,79 @@ int yo_model_forward(yo_model *m, uint32_t token, float *logits) {
 
         if (norm_weights(&L->attn_norm, dim, m->normw))
             return -1;
-        yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, 0.0f, m->normed);
+        yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, norm_off, m->normed);
 
         if (model_qmv(m, &L->attn_q, m->normed, dim, m->q, n_heads * hd) ||
             model_qmv(m, &L->attn_k, m->normed, dim, m->k, kv_stride) ||
             model_qmv(m, &L->attn_v, m->normed, dim, m->v, kv_stride))
             return -1;
+        /* Q/K/V bias (:640-651) */
+        if (L->attn_q_bias.data)
+            add_bias(m->q, n_heads * hd, &L->attn_q_bias);
+        if (L->attn_k_bias.data)
+            add_bias(m->k, kv_stride, &L->attn_k_bias);
+        if (L->attn_v_bias.data)
+            add_bias(m->v, kv_stride, &L->attn_v_bias);
 
-        yo_apply_rope(m->q, n_heads * hd, pos, hd, hd / 2, m->rope_cos, m->rope_sin);
-        yo_apply_rope(m->k, kv_stride, pos, hd, hd / 2, m->rope_cos, m->rope_sin);
+        yo_apply_rope(m->q, n_heads * hd, pos, hd, rot / 2, m->rope_cos, m->rope_sin);
+        yo_apply_rope(m->k, kv_stride, pos, hd, rot / 2, m->rope_cos, m->rope_sin);
 
         memcpy(m->k_cache[layer] + pos * kv_stride, m->k, kv_stride * 4);
         memcpy(m->v_cache[layer] + pos * kv_stride, m->v, kv_stride * 4);
 
-        yo_attention(m->q, m->k_cache[layer], m->v_cache[layer], m->attn_out, m->scores, n_heads,
-                     n_kv, hd, seq_len);
+        yo_attention_ex(m->q, m->k_cache[layer], m->v_cache[layer], m->attn_out, m->scores, n_heads,
+                        n_kv, hd, seq_len, c->sliding_window, c->attn_logit_softcap);
 
         if (model_qmv(m, &L->attn_output, m->attn_out, n_heads * hd, m->attn_proj, dim))
             return -1;
+        /* post-attention norm (Gemma2, :764-779) */
+        if (L->attn_post_norm.data) {
+            memcpy(m->post_tmp, m->attn_proj, dim * 4);
+            if (norm_weights(&L->attn_post_norm, dim, m->normw))
+                return -1;
+            yo_rms_norm(m->post_tmp, m->normw, dim, c->norm_eps, norm_off, m->attn_proj);
+        }
         for (size_t i = 0; i < dim; i++)
             m->hidden[i] = m->residual[i] + m->attn_proj[i];
 
         memcpy(m->residual, m->hidden, dim * 4);
         if (norm_weights(&L->ffn_norm, dim, m->normw))
             return -1;
-        yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, 0.0f, m->normed);
+        yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, norm_off, m->normed);
 
         if (model_qmv(m, &L->ffn_gate, m->normed, dim, m->gate, ff) ||
             model_qmv(m, &L->ffn_up, m->normed, dim, m->up, ff))
             return -1;
-        yo_swiglu(m->gate, m->up, ff);
+        if (c->geglu) { /* :974-978 */
+            for (size_t i = 0; i < ff; i++)
+                m->gate[i] = gelu_tanh(m->gate[i]) * m->up[i];
+        } else {
+            yo_swiglu(m->gate, m->up, ff);
+        }
         if (model_qmv(m, &L->ffn_down, m->gate, ff, m->ffn_out, dim))
             return -1;
+        /* post-FFN norm (Gemma2, :985-999) */
+        if (L->ffn_post_norm.data) {
+            memcpy(m->post_tmp, m->ffn_out, dim * 4);
+            if (norm_weights(&L->ffn_post_norm, dim, m->normw))
+                return -1;
+            yo_rms_norm(m->post_tmp, m->normw, dim, c->norm_eps, norm_off, m->ffn_out);
+        }
         for (size_t i = 0; i < dim; i++)
             m->hidden[i] = m->residual[i] + m->ffn_out[i];
     }
 
     if (norm_weights(&m->output_norm, dim, m->normw))
         return -1;
-    yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, 0.0f, m->normed);
+    yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, norm_off, m->normed);
     /* gpu_runner.rs:214-215 and weight_loader: output falls back to token_embd */
     const yo_tensor *out_t = m->output.data ? &m->output : &m->token_embd;
     if (model_qmv(m, out_t, m->normed, dim, logits, c->vocab_size))
         return -1;
+    /* final logit softcap (Gemma2, :1027-1032) */
+    if (c->logit_softcap != 0.0f)
+        for (size_t i = 0; i < c->vocab_size; i++)
+            logits[i] = c->logit_softcap * tanhf(logits[i] / c->logit_softcap);
     m->pos += 1;
     return 0;
 }

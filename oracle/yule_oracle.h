@@ -121,8 +121,15 @@ void yo_softmax(float *s, size_t n);
 void yo_attention(const float *q, const float *k_cache, const float *v_cache, float *attn_out,
                   float *scores_scratch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
                   size_t seq_len);
+/* The same with the sliding-window mask (:688-696; window 0 = none) and the attention logit softcap
+ * (:716-721; cap 0 = none). */
+void yo_attention_ex(const float *q, const float *k_cache, const float *v_cache, float *attn_out,
+                     float *scores_scratch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                     size_t seq_len, size_t sliding_window, float softcap);
 /* model_runner.rs:968-972: gate[i] = gate[i]*sigmoid(gate[i])*up[i]. */
 void yo_swiglu(float *gate, const float *up, size_t n);
+/* model_runner.rs:312-314: the tanh form of GELU used by GeGLU. */
+float yo_gelu(float x);
 /* yule-infer/src/sampler.rs:150-163 — argmax with `>=`, so ties go to the
  * highest index. */
 uint32_t yo_argmax(const float *v, size_t n);
@@ -134,6 +141,13 @@ typedef struct {
     int32_t mod_enabled; /* -1: as the reference (n_layers >= 32, model_runner.rs:463); 0/1 force */
     int32_t simd;        /* YO_SCALAR / YO_AVX2 / YO_AVX2_ASM */
     int32_t n_threads;   /* <= 0: all hardware threads */
+    /* Architecture variants of the dense path (RunnerConfig, model_runner.rs:25-58); zero = the Llama default. */
+    uint32_t rotary_dim;       /* partial RoPE: rotated prefix of each head (model_runner.rs:430-434, :502); 0 = head_dim */
+    uint32_t sliding_window;   /* attention sees positions t >= pos - w once pos >= w (:688-696); 0 = none */
+    float attn_logit_softcap;  /* scores = cap * tanh(scores / cap) before the softmax (:716-721); 0 = none */
+    float logit_softcap;       /* the same on the final logits (:1027-1032); 0 = none */
+    float norm_weight_offset;  /* Gemma: norm weights are (w + 1) and embeddings are scaled by sqrt(dim) (:246-275, :568-574) */
+    int32_t geglu;             /* Gemma: gelu(gate) * up instead of SiLU (:312-314, :974-978) */
 } yo_model_config;
 
 typedef struct yo_model yo_model;

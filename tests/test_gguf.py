@@ -138,9 +138,40 @@ def test_model_description(native_libs):
     tensors = {n: (d, int(t), (shapes[n][1], shapes[n][0]) if n in shapes else (256,)) for n, (d, t) in w2.items()}
     got2 = GgufFile.parse(gw.build(meta, tensors)).model_config()
     assert dataclasses.replace(got2, norm_eps=cfg2.norm_eps) == cfg2 and got2.norm_eps == pytest.approx(1e-5, rel=1e-6)
-    # an architecture outside the Llama-family path is refused, not mis-run
-    with pytest.raises(YuleGpuError):
-        GgufFile.parse(gw.model_file(cfg, weights, arch="gemma")).model_config()
+    # architectures outside the dense transformer path are refused, not mis-run
+    for arch in ("mamba", "rwkv6", "mixtral", "bert"):
+        with pytest.raises(YuleGpuError):
+            GgufFile.parse(gw.model_file(cfg, weights, arch=arch)).model_config()
+
+
+def test_architecture_variants_from_metadata(native_libs):
+    """The variant fields RunnerConfig derives (yule-infer/src/model_runner.rs:417-460, gguf.rs:553-560)."""
+    cfg = ModelConfig(dim=256, n_layers=1, n_heads=8, n_kv_heads=2, head_dim=32, vocab_size=64, ff_dim=256, max_seq_len=64,
+                      norm_eps=1e-6)
+    weights = synth.synthetic_model(cfg, seed=6)
+
+    def parsed(arch, extra):
+        shapes = cfg.tensor_shapes()
+        tensors = {n: (d, int(t), (shapes[n][1], shapes[n][0]) if n in shapes else (cfg.dim,)) for n, (d, t) in weights.items()}
+        meta = gw.llama_metadata(cfg, arch)
+        meta.update(extra)
+        return GgufFile.parse(gw.build(meta, tensors)).model_config()
+
+    got = parsed("mistral", {"mistral.attention.sliding_window": 16})
+    assert got.sliding_window == 16 and got.rotary_dim == 0 and not got.geglu and got.norm_weight_offset == 0.0
+    got = parsed("phi3", {"phi3.rope.dimension_count": 16})
+    assert got.rotary_dim == 16
+    assert parsed("phi3", {"phi3.rope.dimension_count": 32}).rotary_dim == 0  # the whole head: no partial rotation
+    got = parsed("gemma2", {"gemma2.attn_logit_softcapping": (gw.F64, 30.0), "gemma2.attention.attn_logit_softcapping": (gw.F64, 50.0)})
+    assert got.geglu and got.norm_weight_offset == 1.0 and got.logit_softcap == 30.0 and got.attn_logit_softcap == 50.0
+    # mixture of experts: refused (expert routing, model_runner.rs:813-958, is not computed by this backend)
+    with pytest.raises(YuleGpuError, match="experts"):
+        parsed("llama", {"llama.expert_count": 8, "llama.expert_used_count": 2})
+    # default epsilon of Qwen / Phi / Gemma files that carry none: 1e-6 (model_runner.rs:414-417)
+    shapes = cfg.tensor_shapes()
+    tensors = {n: (d, int(t), (shapes[n][1], shapes[n][0]) if n in shapes else (cfg.dim,)) for n, (d, t) in weights.items()}
+    meta = {k: v for k, v in gw.llama_metadata(cfg, "qwen2").items() if not k.endswith("layer_norm_rms_epsilon")}
+    assert GgufFile.parse(gw.build(meta, tensors)).model_config().norm_eps == pytest.approx(1e-6, rel=1e-6)
 
 
 def test_open_maps_a_file(native_libs, tmp_path):

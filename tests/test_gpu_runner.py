@@ -27,7 +27,9 @@ def make_oracle_model(oracle, cfg, weights, simd=None):
     m = oracle.Model(dim=cfg.dim, n_layers=cfg.n_layers, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
                      head_dim=cfg.head_dim, vocab_size=cfg.vocab_size, ff_dim=cfg.ff_dim,
                      max_seq_len=cfg.max_seq_len, norm_eps=cfg.norm_eps, rope_freq_base=cfg.rope_freq_base,
-                     simd=oracle.SCALAR if simd is None else simd)
+                     simd=oracle.SCALAR if simd is None else simd, rotary_dim=cfg.rotary_dim,
+                     sliding_window=cfg.sliding_window, attn_logit_softcap=cfg.attn_logit_softcap,
+                     logit_softcap=cfg.logit_softcap, norm_weight_offset=cfg.norm_weight_offset, geglu=cfg.geglu)
     for name, (data, dt) in weights.items():
         m.set_tensor(name, data, int(dt))
     return m

@@ -20,7 +20,8 @@ class RunnerConfig(C.Structure):
     """``yule_runner_config`` of include/yule_cuda.h."""
     _fields_ = [("dim", u32), ("n_layers", u32), ("n_heads", u32), ("n_kv_heads", u32), ("head_dim", u32),
                 ("vocab_size", u32), ("ff_dim", u32), ("max_seq_len", u32), ("norm_eps", f32),
-                ("rope_freq_base", f32), ("fused", u32)]
+                ("rope_freq_base", f32), ("fused", u32), ("rotary_dim", u32), ("sliding_window", u32),
+                ("attn_logit_softcap", f32), ("logit_softcap", f32), ("norm_weight_offset", f32), ("geglu", u32)]
 
 
 class GgufTensorInfo(C.Structure):
@@ -82,6 +83,9 @@ _SIGNATURES = {
     "yule_cuda_runner_position": [vp, C.POINTER(u32)],
     "yule_cuda_runner_generate_greedy": [vp, C.POINTER(u32), u32, u32, C.POINTER(u32)],
     "yule_cuda_runner_buffer": [vp, u32, u32, C.POINTER(u64)],
+    "yule_cuda_runner_decode_batch": [vp, C.POINTER(u32), u32, C.POINTER(f32)],
+    "yule_cuda_runner_reset_batch": [vp],
+    "yule_cuda_runner_generate_greedy_batch": [vp, C.POINTER(u32), u32, u32, u32, C.POINTER(u32)],
     "yule_gguf_open": [C.c_char_p, C.POINTER(vp)],
     "yule_gguf_parse": [vp, size_t, C.POINTER(vp)],
     "yule_gguf_close": [vp],
@@ -131,6 +135,7 @@ def synth_lib() -> C.CDLL:
         lib.ys_random_blocks.argtypes = [C.c_int, u64, f32, C.POINTER(C.c_uint8), u64, C.c_int]
         lib.ys_quantize.argtypes = [C.c_int, C.POINTER(f32), u64, C.POINTER(C.c_uint8), C.c_int]
         lib.ys_random_quantized.argtypes = [C.c_int, u64, f32, C.POINTER(C.c_uint8), u64, C.c_int]
+        lib.ys_random_quantized_at.argtypes = [C.c_int, u64, f32, C.POINTER(C.c_uint8), u64, u64, C.c_int]
         lib.ys_f32_to_f16.argtypes = [f32]
         lib.ys_f32_to_f16.restype = C.c_uint16
         _synth = lib

@@ -45,7 +45,7 @@ int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes) {
     if (ctx->capturing)
         return fail(YULE_ERR_INVALID_ARGUMENT, "the GEMM scratch (%zu bytes) cannot grow during graph capture", bytes);
     YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    if (ctx->gemm_scratch) ctx->retired_scratch.push_back(ctx->gemm_scratch);  // graphs captured earlier may still use it
     ctx->gemm_scratch = nullptr;
     ctx->gemm_scratch_bytes = 0;
     cudaError_t e = cudaMalloc(&ctx->gemm_scratch, bytes);
@@ -164,6 +164,7 @@ int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
     if (ctx->attn_tickets) cudaFree(ctx->attn_tickets);
     if (ctx->device_status) cudaFree(ctx->device_status);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    for (void *p : ctx->retired_scratch) cudaFree(p);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return YULE_OK;
@@ -664,8 +665,11 @@ int32_t yule_cuda_multihead_attention(yule_cuda_ctx *ctx, yule_buffer q, yule_bu
             std::lock_guard<std::mutex> lock(ctx->mu);
             if (a.n_splits > 1 && (ctx->attn_scratch_floats < need || ctx->attn_tickets_n < n_heads)) {
                 YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-                if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
-                if (ctx->attn_tickets) cudaFree(ctx->attn_tickets);
+                if (ctx->capturing)
+                    return fail(YULE_ERR_INVALID_ARGUMENT, "the attention scratch cannot grow during graph capture: run the call once outside the capture first");
+                // graphs captured earlier may still replay into the old blocks: retire them, do not free them
+                if (ctx->attn_scratch) ctx->retired_scratch.push_back(ctx->attn_scratch);
+                if (ctx->attn_tickets) ctx->retired_scratch.push_back(ctx->attn_tickets);
                 ctx->attn_scratch = nullptr;
                 ctx->attn_tickets = nullptr;
                 ctx->attn_scratch_floats = ctx->attn_tickets_n = 0;

@@ -51,6 +51,10 @@ struct AttnParams {
     uint32_t *tickets;                   // [n_heads], zero between launches
     uint32_t hd, n_heads, n_kv_heads, kv_stride, n_splits, max_chunk, min_chunk;
     uint32_t q_stride, out_stride;       // floats between the q / out rows of consecutive queries (blockIdx.z)
+    uint32_t pos_per_query;              // batched decode: query z sits at pos_ptr[z] of its own caches
+    size_t kv_batch_stride;              // floats between the caches of consecutive queries (batched decode)
+    uint32_t window;                     // sliding window (model_runner.rs:688-696), 0 = none
+    float softcap;                       // attention logit softcap (model_runner.rs:716-721), 0 = none
     TpFuse tp;                           // tensor parallelism: the output also goes out as (value, epoch) pairs
 };
 
@@ -69,11 +73,18 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     const bool fused = p.k_new != nullptr;
     // splits actually used at this sequence length: at least 256 positions each (one per thread);
     // the rest exit.  Short sequences therefore take the single-CTA path with no merge step.
-    uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
+    // Sliding window: the reference masks positions t < pos − window to −inf once pos >= window; they then carry
+    // no weight, so the splits simply cover [begin, seq) instead of [0, seq).  With an attention softcap as well
+    // the reference caps after masking (model_runner.rs:688-721), and cap·tanh(−inf / cap) is −cap, a finite
+    // score: masked positions then keep a (small) weight, so they are visited and given exactly that score.
+    const uint32_t first_visible = (p.window && pos >= p.window) ? pos - p.window : 0;
+    const uint32_t begin = p.softcap != 0.f ? 0u : first_visible;
+    const uint32_t span = seq - begin;
+    uint32_t eff = (span + p.min_chunk - 1) / p.min_chunk;
     eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
     if (split >= eff) return;
-    const uint32_t chunk = (seq + eff - 1) / eff;
-    const uint32_t lo = split * chunk < seq ? split * chunk : seq;
+    const uint32_t chunk = (span + eff - 1) / eff;
+    const uint32_t lo = begin + (split * chunk < span ? split * chunk : span);
     const uint32_t hi = lo + chunk < seq ? lo + chunk : seq;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 
@@ -130,7 +141,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
             a2 = fmaf(q.z, k.z, a2);
             a3 = fmaf(q.w, k.w, a3);
         }
-        const float sc = ((a0 + a1) + (a2 + a3)) * scale;
+        float sc = ((a0 + a1) + (a2 + a3)) * scale;
+        if (p.softcap != 0.f) sc = t < first_visible ? -p.softcap : p.softcap * tanhf(sc / p.softcap);
         scores[t - lo] = sc;
         mx = fmaxf(mx, sc);
     }
@@ -253,18 +265,27 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, head0 = kvh * GROUP;
     // prefill: query z of the launch sits z positions further on and has its own rows and scratch
     const uint32_t z = blockIdx.z;
-    const uint32_t pos = p.pos_ptr ? *p.pos_ptr : p.seq_len - 1 + z;
+    const uint32_t pos = p.pos_ptr ? (p.pos_per_query ? p.pos_ptr[z] : *p.pos_ptr) : p.seq_len - 1 + z;
+    float *const k_cache = p.k_cache + (size_t)z * p.kv_batch_stride;
+    float *const v_cache = p.v_cache + (size_t)z * p.kv_batch_stride;
     const float *q_in = p.q + (size_t)z * p.q_stride;
     float *out_z = p.out + (size_t)z * p.out_stride;
     float *scratch_z = p.scratch + (size_t)z * p.n_heads * p.n_splits * (HD + 2);
     uint32_t *tickets_z = p.tickets + (size_t)z * p.n_heads;
     const uint32_t seq = pos + 1;
     const bool fused = p.k_new != nullptr;
-    uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
+    // Sliding window: the reference masks positions t < pos − window to −inf once pos >= window; they then carry
+    // no weight, so the splits simply cover [begin, seq) instead of [0, seq).  With an attention softcap as well
+    // the reference caps after masking (model_runner.rs:688-721), and cap·tanh(−inf / cap) is −cap, a finite
+    // score: masked positions then keep a (small) weight, so they are visited and given exactly that score.
+    const uint32_t first_visible = (p.window && pos >= p.window) ? pos - p.window : 0;
+    const uint32_t begin = p.softcap != 0.f ? 0u : first_visible;
+    const uint32_t span = seq - begin;
+    uint32_t eff = (span + p.min_chunk - 1) / p.min_chunk;
     eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
     if (split >= eff) return;
-    const uint32_t chunk = (seq + eff - 1) / eff;
-    const uint32_t lo = split * chunk < seq ? split * chunk : seq;
+    const uint32_t chunk = (span + eff - 1) / eff;
+    const uint32_t lo = begin + (split * chunk < span ? split * chunk : span);
     const uint32_t hi = lo + chunk < seq ? lo + chunk : seq;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 
@@ -279,7 +300,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
     const int qtr = lane >> 3, l8 = lane & 7;
     auto k_row = [&](uint32_t tb) {
         const uint32_t t = tb + wid * 4 + qtr;
-        return p.k_cache + (size_t)(t < hi ? t : lo) * p.kv_stride + (size_t)kvh * HD + l8 * 4;
+        return k_cache + (size_t)(t < hi ? t : lo) * p.kv_stride + (size_t)kvh * HD + l8 * 4;
     };
     float4 kv_next[J];
     if (lo < hi) {
@@ -316,8 +337,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
     // take that row from kcur / v_new, never from the cache)
     if (fused && pos >= lo && pos < hi) {
         for (uint32_t d = threadIdx.x; d < HD; d += kThreads) {
-            p.k_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = kcur[d];
-            p.v_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = p.v_new[(size_t)kvh * HD + d];
+            k_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = kcur[d];
+            v_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = p.v_new[(size_t)kvh * HD + d];
         }
     }
 
@@ -371,7 +392,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
             }
             if (valid && l8 == 0) {
 #pragma unroll
-                for (int h = 0; h < GH; h++) scores[(size_t)(h0 + h) * p.max_chunk + (t - lo)] = d[h] * scale;
+                for (int h = 0; h < GH; h++) {
+                    float sc = d[h] * scale;
+                    if (p.softcap != 0.f) sc = t < first_visible ? -p.softcap : p.softcap * tanhf(sc / p.softcap);
+                    scores[(size_t)(h0 + h) * p.max_chunk + (t - lo)] = sc;
+                }
             }
         }
     }
@@ -404,7 +429,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
     for (int h = 0; h < GROUP; h++) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
     auto v_row = [&](uint32_t t) {
         return (fused && t == pos) ? reinterpret_cast<const float4 *>(p.v_new + (size_t)kvh * HD) + d4
-                                   : reinterpret_cast<const float4 *>(p.v_cache + (size_t)t * p.kv_stride + (size_t)kvh * HD) + d4;
+                                   : reinterpret_cast<const float4 *>(v_cache + (size_t)t * p.kv_stride + (size_t)kvh * HD) + d4;
     };
     uint32_t t = lo + slice;
     for (; t + 3 * NSL < hi; t += 4 * NSL) {  // four rows in flight
@@ -629,6 +654,11 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
     p.n_kv_heads = a.n_kv_heads;
     p.kv_stride = a.kv_stride;
     p.n_splits = a.n_splits;
+    p.window = a.window;
+    p.softcap = a.softcap;
+    p.pos_per_query = a.pos_per_query ? 1u : 0u;
+    p.kv_batch_stride = a.kv_batch_stride;
+    if ((a.pos_per_query || a.kv_batch_stride) && !a.gqa) return cudaErrorInvalidValue;
     if (a.gqa) {
         if (!attn_gqa_supported(a.hd, a.n_heads, a.n_kv_heads) || a.n_splits > (uint32_t)kGqaMaxSplits) return cudaErrorInvalidValue;
         const uint32_t g = a.n_heads / a.n_kv_heads;
@@ -644,7 +674,8 @@ cudaError_t launch_attn_decode(const AttnDecode &a, cudaStream_t s, uint64_t *la
         p.q_stride = a.q_stride;
         p.out_stride = a.out_stride;
         p.tp = a.tp;
-        if (a.n_tokens > 1 && (a.k_new || a.pos_ptr)) return cudaErrorInvalidValue;  // batched queries read the caches only
+        // several queries per launch read the caches only; a device position is one per query then (batched decode)
+        if (a.n_tokens > 1 && (a.k_new || (a.pos_ptr && !a.pos_per_query))) return cudaErrorInvalidValue;
 #define YULE_GQA_CASE(G, H) if (g == G && a.hd == H) return launch_gqa_variant<G, H>(p, smem, a.pdl, s, a.n_tokens)
         YULE_GQA_CASE(1, 64); YULE_GQA_CASE(2, 64); YULE_GQA_CASE(4, 64); YULE_GQA_CASE(8, 64);
         YULE_GQA_CASE(1, 128); YULE_GQA_CASE(2, 128); YULE_GQA_CASE(4, 128); YULE_GQA_CASE(8, 128);

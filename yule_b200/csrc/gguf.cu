@@ -381,8 +381,22 @@ int32_t yule_gguf_runner_config(const yule_gguf *g, uint32_t max_seq_len_cap, yu
     if (!g || !cfg) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
     const char *arch = g->get_str("general.architecture");
     const std::string prefix = arch ? arch : "unknown";
-    if (prefix != "llama" && prefix != "mistral" && prefix != "qwen" && prefix != "qwen2")
-        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: architecture '%s' is outside the Llama-family decode path of this backend", prefix.c_str());
+    // The dense transformer path of yule-infer/src/model_runner.rs with its variants: Llama / Mistral (sliding
+    // window), Phi (partial RoPE), Qwen (Q/K/V bias), Gemma (norm offset, embedding scale, GeGLU, post-norms,
+    // softcaps).  Mixture-of-experts files (model_runner.rs:813-958) and the non-transformer architectures are
+    // refused rather than mis-computed.
+    const bool is_gemma = prefix == "gemma" || prefix == "gemma2";
+    const bool is_phi = prefix == "phi" || prefix == "phi2" || prefix == "phi3";
+    const bool is_qwen = prefix == "qwen" || prefix == "qwen2";
+    if (prefix != "llama" && prefix != "mistral" && !is_qwen && !is_gemma && !is_phi)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: architecture '%s' is outside the dense decode path of this backend", prefix.c_str());
+    uint32_t experts = 0;
+    if (g->get_u32(prefix + ".expert_count", &experts) && experts > 0)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: mixture-of-experts model (%u experts): expert routing is not implemented in this backend", experts);
+    if (g->find_tensor("blk.0.ffn_gate_exps.weight") || g->find_tensor("blk.0.ffn_gate.0.weight"))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: mixture-of-experts tensors present: expert routing is not implemented in this backend");
+    if (is_phi && !g->find_tensor("blk.0.attn_q.weight"))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: this file has a packed attn_qkv tensor; the runner reads separate attn_q / attn_k / attn_v");
     memset(cfg, 0, sizeof(*cfg));
     uint32_t ctx = 4096, heads = 0, kv = 0;
     g->get_u32(prefix + ".context_length", &ctx);
@@ -407,13 +421,29 @@ int32_t yule_gguf_runner_config(const yule_gguf *g, uint32_t max_seq_len_cap, yu
     cfg->head_dim = cfg->dim / heads;
     const TensorEntry *gate = g->find_tensor("blk.0.ffn_gate.weight");
     cfg->ff_dim = (gate && gate->n_dims == 2) ? (uint32_t)gate->shape[1] : (uint32_t)(std::ceil(cfg->dim * 8.0 / 3.0 / 256.0) * 256);
-    double eps = 1e-5, theta = 10000.0;
+    // model_runner.rs:414-417: 1e-6 for Phi / Qwen / Gemma, 1e-5 otherwise, when the file has no epsilon
+    double eps = (is_phi || is_qwen || is_gemma) ? 1e-6 : 1e-5, theta = 10000.0;
     g->get_f64(prefix + ".attention.layer_norm_rms_epsilon", &eps);
     g->get_f64(prefix + ".rope.freq_base", &theta);
     cfg->norm_eps = (float)eps;
     cfg->rope_freq_base = (float)theta;
     cfg->max_seq_len = (max_seq_len_cap && max_seq_len_cap < ctx) ? max_seq_len_cap : ctx;
     cfg->fused = 1;
+    // variants (gguf.rs:553-560, model_runner.rs:417-460)
+    uint32_t v = 0;
+    if (g->get_u32(prefix + ".attention.sliding_window", &v)) cfg->sliding_window = v;
+    if (g->get_u32(prefix + ".rope.dimension_count", &v) && v < cfg->head_dim) cfg->rotary_dim = v;
+    double cap = 0.0;
+    if (g->get_f64(prefix + ".attn_logit_softcapping", &cap)) cfg->logit_softcap = (float)cap;
+    if (g->get_f64(prefix + ".attention.attn_logit_softcapping", &cap)) cfg->attn_logit_softcap = (float)cap;
+    if (is_gemma) {
+        cfg->norm_weight_offset = 1.0f;
+        cfg->geglu = 1;
+    }
+    if (cfg->rotary_dim % 2) return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: odd rope.dimension_count %u", cfg->rotary_dim);
+    // The CPU runner switches to a streaming KV cache (sink tokens + half-context window) from 8192 positions
+    // (model_runner.rs:458, :468-481); this backend keeps the flat cache, so longer contexts are capped there.
+    if (cfg->max_seq_len >= 8192) cfg->max_seq_len = 8191;
     return YULE_OK;
 }
 
@@ -474,12 +504,19 @@ int32_t yule_cuda_runner_load_gguf(yule_cuda_ctx *ctx, const yule_gguf *g, uint3
         return cleanup(rc);
     static const char *per_layer[] = {"attn_norm.weight", "attn_q.weight",   "attn_k.weight",  "attn_v.weight",   "attn_output.weight",
                                       "ffn_norm.weight",  "ffn_gate.weight", "ffn_up.weight",  "ffn_down.weight"};
-    for (uint32_t l = 0; l < cfg.n_layers; l++)
+    // optional tensors of the variants (weight_loader.rs:203-218)
+    static const char *per_layer_optional[] = {"attn_q.bias", "attn_k.bias", "attn_v.bias", "attn_post_norm.weight", "ffn_post_norm.weight"};
+    for (uint32_t l = 0; l < cfg.n_layers; l++) {
+        char name[96];
         for (const char *suffix : per_layer) {
-            char name[96];
             snprintf(name, sizeof(name), "blk.%u.%s", l, suffix);
             if ((rc = upload(name, true))) return cleanup(rc);
         }
+        for (const char *suffix : per_layer_optional) {
+            snprintf(name, sizeof(name), "blk.%u.%s", l, suffix);
+            if ((rc = upload(name, false))) return cleanup(rc);
+        }
+    }
     rc = cleanup(YULE_OK);
     *out_runner = r;
     return rc;

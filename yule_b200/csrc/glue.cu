@@ -146,11 +146,18 @@ __global__ void rope_kv_write_kernel(float *__restrict__ q, const float *__restr
 
 // Batched form for prefill: token slot z = blockIdx.y sits at position pos0 + z; q[z] is rotated in
 // place, k[z] is rotated into the K cache row of its position and v[z] copied into the V cache.
+// Batched decode uses the same kernel with `row_pos` set: slot z is then the current token of sequence z, at
+// position row_pos[z] of that sequence's own cache (caches `cache_stride` floats apart).
 __global__ void rope_kv_write_batch_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                            float *__restrict__ k_cache, float *__restrict__ v_cache,
                                            const float *__restrict__ cos_table, const float *__restrict__ sin_table,
-                                           uint32_t pos0, uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads) {
-    const uint32_t z = blockIdx.y, pos = pos0 + z;
+                                           uint32_t pos0, uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads,
+                                           const uint32_t *__restrict__ row_pos, size_t cache_stride) {
+    const uint32_t z = blockIdx.y, pos = row_pos ? row_pos[z] : pos0 + z;
+    if (row_pos) {
+        k_cache += (size_t)z * cache_stride;
+        v_cache += (size_t)z * cache_stride;
+    }
     const uint32_t half = head_dim / 2;
     const uint32_t kv_stride = n_kv_heads * head_dim, q_stride = n_heads * head_dim;
     const uint32_t total_q = n_heads * half, total_k = n_kv_heads * half;
@@ -187,6 +194,36 @@ __global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__r
     if (i >= n) return;
     const float x = gate[i];
     out[i] = (x / (1.0f + expf(-x))) * up[i];
+}
+
+// Element-wise pieces of the architecture variants of yule-infer/src/model_runner.rs: out[i] = f(a[i], b[i], v).
+//   kAddScalar   a + v                      norm weights with Gemma's offset (:246-275: w[i] + offset)
+//   kScale       a * v                      Gemma's embedding scale sqrt(dim) (:568-574)
+//   kSoftcap     v * tanh(a / v)            final logit softcap (:1027-1032)
+//   kGeluMul     gelu(a) * b                GeGLU (:312-314, :974-978), gelu in its tanh form
+//   kAddVec      a + b                      Q/K/V bias (:295-310), residual after a post-norm (:781-783)
+enum ElemOp { kAddScalar, kScale, kSoftcap, kGeluMul, kAddVec };
+template <int OP>
+__global__ void elementwise_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, uint32_t n,
+                                   float v) {
+    yule_pdl_launch_dependents();
+    yule_pdl_wait();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float x = a[i];
+    float r;
+    if (OP == kAddScalar) {
+        r = x + v;
+    } else if (OP == kScale) {
+        r = x * v;
+    } else if (OP == kSoftcap) {
+        r = v * tanhf(x / v);
+    } else if (OP == kGeluMul) {
+        r = (x * 0.5f * (1.0f + tanhf(0.7978846f * (x + 0.044715f * x * x * x)))) * b[i];
+    } else {
+        r = x + b[i];
+    }
+    out[i] = r;
 }
 
 // kernels/cuda/add.cu:2-11.
@@ -229,7 +266,7 @@ __global__ void __launch_bounds__(kAttnThreads)
 multihead_attention_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
                            const float *__restrict__ v_cache, float *__restrict__ out, uint32_t hd, uint32_t seq_len_arg,
                            const uint32_t *__restrict__ pos_ptr, uint32_t n_heads, uint32_t n_kv_heads,
-                           uint32_t kv_stride) {
+                           uint32_t kv_stride, uint32_t window, float softcap) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[32];
     yule_pdl_launch_dependents();
@@ -242,24 +279,32 @@ multihead_attention_kernel(const float *__restrict__ q, const float *__restrict_
     float *partial = scores + seq_len;  // (kAttnThreads / hd_lanes) × hd floats, see below
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const float scale = 1.0f / sqrtf((float)hd);
+    // sliding window (yule-infer/src/model_runner.rs:688-696): positions before pos − window are masked to −inf
+    // there, i.e. carry no weight; here they are simply not visited
+    // With a softcap as well the reference caps after masking, and cap·tanh(−inf / cap) = −cap is a finite score:
+    // masked positions then keep a small weight, so they are visited and given exactly that score.
+    const uint32_t pos = seq_len - 1;
+    const uint32_t first_visible = (window && pos >= window) ? pos - window : 0;
+    const uint32_t begin = softcap != 0.f ? 0u : first_visible;
 
     for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = q[(size_t)head * hd + d];
     __syncthreads();
 
     // scores: one warp per position, lanes across head_dim (coalesced K rows)
     float mx = -FLT_MAX;
-    for (uint32_t t = wid; t < seq_len; t += kAttnThreads / 32) {
+    for (uint32_t t = begin + wid; t < seq_len; t += kAttnThreads / 32) {
         const float *kp = k_cache + (size_t)t * kv_stride + (size_t)kv_head * hd;
         float acc = 0.f;
         for (uint32_t d = lane; d < hd; d += 32) acc = fmaf(qs[d], kp[d], acc);
         acc = warp_sum(acc) * scale;
+        if (softcap != 0.f) acc = t < first_visible ? -softcap : softcap * tanhf(acc / softcap);  // attention logit softcap (:716-721)
         if (lane == 0) scores[t] = acc;
         mx = fmaxf(mx, acc);
     }
     mx = block_max(mx, red);  // also orders the score writes before the reads below
 
     float sum = 0.f;
-    for (uint32_t t = threadIdx.x; t < seq_len; t += blockDim.x) {
+    for (uint32_t t = begin + threadIdx.x; t < seq_len; t += blockDim.x) {
         float e = expf(scores[t] - mx);
         scores[t] = e;
         sum += e;
@@ -272,7 +317,7 @@ multihead_attention_kernel(const float *__restrict__ q, const float *__restrict_
     const uint32_t d = threadIdx.x % hd, slice = threadIdx.x / hd;
     float acc = 0.f;
     if (slice < n_slices && threadIdx.x < n_slices * hd) {
-        for (uint32_t t = slice; t < seq_len; t += n_slices)
+        for (uint32_t t = begin + slice; t < seq_len; t += n_slices)
             acc = fmaf(scores[t] * inv, v_cache[(size_t)t * kv_stride + (size_t)kv_head * hd + d], acc);
         partial[slice * hd + d] = acc;
     }
@@ -354,6 +399,65 @@ __global__ void argmax_kernel(const float *__restrict__ v, uint32_t n, uint32_t 
     }
 }
 
+// Batched decode: row b = blockIdx.x of [batch][n] logits → tokens[b] (ties to the highest index, as above),
+// logged at history[b * history_stride + step[0]]; block 0 advances every sequence's position and the step.
+__global__ void argmax_rows_kernel(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ tokens, uint32_t *__restrict__ pos,
+                                   uint32_t *__restrict__ step, uint32_t *__restrict__ history, uint32_t history_stride) {
+    __shared__ float bv[32];
+    __shared__ uint32_t bi[32];
+    const float *row = v + (size_t)blockIdx.x * n;
+    float best = -FLT_MAX;
+    uint32_t idx = 0;
+    bool any = false;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float x = row[i];
+        if (!any || x >= best) {
+            best = x;
+            idx = i;
+            any = true;
+        }
+    }
+    if (!any) best = -FLT_MAX;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ob > best || (ob == best && oi > idx)) {
+            best = ob;
+            idx = oi;
+        }
+    }
+    if (lane == 0) {
+        bv[wid] = best;
+        bi[wid] = idx;
+    }
+    __syncthreads();
+    if (wid == 0) {
+        best = lane < nw ? bv[lane] : -FLT_MAX;
+        idx = lane < nw ? bi[lane] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ob > best || (ob == best && oi > idx)) {
+                best = ob;
+                idx = oi;
+            }
+        }
+        if (lane == 0) {
+            tokens[blockIdx.x] = idx;
+            if (history) history[(size_t)blockIdx.x * history_stride + step[0]] = idx;
+        }
+    }
+}
+// After the picks of a step: every sequence moves one position on.
+__global__ void advance_rows_kernel(uint32_t *__restrict__ pos, uint32_t *__restrict__ step, uint32_t batch) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < batch) pos[i] += 1;
+    if (i == 0) step[0] += 1;
+}
+
 __global__ void fill_bytes_kernel(uint4 *__restrict__ p, size_t n16, uint32_t v) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
         p[i] = make_uint4(v, v, v, v);
@@ -397,11 +501,12 @@ cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tm
 cudaError_t launch_rope_kv_write_batch(float *q, const float *k, const float *v, float *k_cache, float *v_cache,
                                        const float *cos_table, const float *sin_table, uint32_t pos0, uint32_t n_tokens,
                                        uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads, cudaStream_t s,
-                                       uint64_t *launches) {
+                                       uint64_t *launches, const uint32_t *row_pos, size_t cache_stride) {
     uint32_t total = (n_heads + n_kv_heads) * (head_dim / 2);
     *launches += 1;
     rope_kv_write_batch_kernel<<<dim3((total + 255) / 256, n_tokens), 256, 0, s>>>(q, k, v, k_cache, v_cache, cos_table, sin_table,
-                                                                                  pos0, head_dim, n_heads, n_kv_heads);
+                                                                                  pos0, head_dim, n_heads, n_kv_heads, row_pos,
+                                                                                  cache_stride);
     return cudaGetLastError();
 }
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t s,
@@ -432,7 +537,7 @@ cudaError_t launch_attn_value(const float *w, const float *v_cache, float *out, 
 cudaError_t launch_multihead_attention(const float *q, const float *k_cache, const float *v_cache, float *out,
                                        uint32_t hd, uint32_t seq_len, const uint32_t *pos_ptr, uint32_t max_seq_len,
                                        uint32_t n_heads, uint32_t n_kv_heads, uint32_t kv_stride, cudaStream_t s,
-                                       uint64_t *launches, bool pdl) {
+                                       uint64_t *launches, bool pdl, uint32_t window, float softcap) {
     uint32_t n_slices = kAttnThreads / hd ? kAttnThreads / hd : 1;
     size_t smem = ((size_t)hd + max_seq_len + (size_t)n_slices * hd) * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
@@ -443,12 +548,36 @@ cudaError_t launch_multihead_attention(const float *q, const float *k_cache, con
     }
     *launches += 1;
     return launch_kernel(multihead_attention_kernel, dim3(n_heads), dim3(kAttnThreads), smem, s, pdl, q, k_cache,
-                         v_cache, out, hd, seq_len, pos_ptr, n_heads, n_kv_heads, kv_stride);
+                         v_cache, out, hd, seq_len, pos_ptr, n_heads, n_kv_heads, kv_stride, window, softcap);
+}
+cudaError_t launch_elementwise(int op, const float *a, const float *b, float *out, uint32_t n, float v, cudaStream_t s,
+                               uint64_t *launches, bool pdl) {
+    if (n == 0) return cudaSuccess;
+    *launches += 1;
+    const dim3 grid((n + 255) / 256), block(256);
+    switch (op) {
+        case kAddScalar: return launch_kernel(elementwise_kernel<kAddScalar>, grid, block, 0, s, pdl, a, b, out, n, v);
+        case kScale: return launch_kernel(elementwise_kernel<kScale>, grid, block, 0, s, pdl, a, b, out, n, v);
+        case kSoftcap: return launch_kernel(elementwise_kernel<kSoftcap>, grid, block, 0, s, pdl, a, b, out, n, v);
+        case kGeluMul: return launch_kernel(elementwise_kernel<kGeluMul>, grid, block, 0, s, pdl, a, b, out, n, v);
+        default: return launch_kernel(elementwise_kernel<kAddVec>, grid, block, 0, s, pdl, a, b, out, n, v);
+    }
 }
 cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *state, uint32_t *history, cudaStream_t s,
                           uint64_t *launches, bool pdl) {
     *launches += 1;
     return launch_kernel(argmax_kernel, dim3(1), dim3(1024), 0, s, pdl, v, n, state, history);
+}
+cudaError_t launch_argmax_rows(const float *v, uint32_t n, uint32_t batch, uint32_t *tokens, uint32_t *pos, uint32_t *step,
+                               uint32_t *history, uint32_t history_stride, cudaStream_t s, uint64_t *launches) {
+    argmax_rows_kernel<<<batch, 1024, 0, s>>>(v, n, tokens, pos, step, history, history_stride);
+    *launches += 1;
+    return cudaGetLastError();
+}
+cudaError_t launch_advance_rows(uint32_t *pos, uint32_t *step, uint32_t batch, cudaStream_t s, uint64_t *launches) {
+    advance_rows_kernel<<<(batch + 255) / 256, 256, 0, s>>>(pos, step, batch);
+    *launches += 1;
+    return cudaGetLastError();
 }
 cudaError_t launch_fill_bytes(void *p, size_t n, int value, cudaStream_t s, uint64_t *launches) {
     uint32_t v = (uint32_t)(value & 0xFF) * 0x01010101u;

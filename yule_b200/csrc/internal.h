@@ -109,6 +109,9 @@ struct yule_cuda_ctx {
     // activation tiles of the tensor-core GEMM (qgemm_tc.cu), grown on demand
     void *gemm_scratch = nullptr;
     size_t gemm_scratch_bytes = 0;
+    // Scratch blocks that were outgrown.  A CUDA graph captured earlier (the runner's steps, a caller's batch)
+    // may still replay into them, so they are kept until the context is destroyed instead of being freed.
+    std::vector<void *> retired_scratch;
     std::atomic<uint64_t> launches{0};
     // Word the kernels with bounded waits write when they give up; read by synchronize.
     int *device_status = nullptr;
@@ -352,7 +355,12 @@ cudaError_t launch_embed_gather_batch(const uint8_t *table, uint32_t type, uint3
 cudaError_t launch_rope_kv_write_batch(float *q, const float *k, const float *v, float *k_cache, float *v_cache,
                                        const float *cos_table, const float *sin_table, uint32_t pos0, uint32_t n_tokens,
                                        uint32_t head_dim, uint32_t n_heads, uint32_t n_kv_heads, cudaStream_t s,
-                                       uint64_t *launches);
+                                       uint64_t *launches, const uint32_t *row_pos = nullptr, size_t cache_stride = 0);
+// Batched decode: greedy pick per row of [batch][n] logits (ties to the highest index) into tokens[b] and
+// history[b * history_stride + step[0]]; then every position and the step counter move on by one.
+cudaError_t launch_argmax_rows(const float *v, uint32_t n, uint32_t batch, uint32_t *tokens, uint32_t *pos, uint32_t *step,
+                               uint32_t *history, uint32_t history_stride, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_advance_rows(uint32_t *pos, uint32_t *step, uint32_t batch, cudaStream_t s, uint64_t *launches);
 
 cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k,
                               cudaStream_t s, uint64_t *launches);
@@ -382,7 +390,12 @@ cudaError_t launch_multihead_attention(const float *q, const float *k_cache, con
                                        float *out, uint32_t hd, uint32_t seq_len,
                                        const uint32_t *pos_ptr, uint32_t max_seq_len, uint32_t n_heads,
                                        uint32_t n_kv_heads, uint32_t kv_stride, cudaStream_t s,
-                                       uint64_t *launches, bool pdl = false);
+                                       uint64_t *launches, bool pdl = false, uint32_t window = 0, float softcap = 0.f);
+// Element-wise pieces of the architecture variants (glue.cu): out[i] = f(a[i], b[i], v); b may be null for the
+// one-input ops.
+enum { kElemAddScalar = 0, kElemScale = 1, kElemSoftcap = 2, kElemGeluMul = 3, kElemAddVec = 4 };
+cudaError_t launch_elementwise(int op, const float *a, const float *b, float *out, uint32_t n, float v, cudaStream_t s,
+                               uint64_t *launches, bool pdl = false);
 // Split-KV decode attention, optionally fused with RoPE and the KV-cache append (attention.cu).
 struct AttnDecode {
     const float *q = nullptr;       // [n_heads][hd]
@@ -401,7 +414,13 @@ struct AttnDecode {
     // Prefill: n_tokens > 1 runs one query per blockIdx.z; query z sits at position seq_len - 1 + z,
     // its q and out rows are q_stride / out_stride floats apart (grouped-query kernel, not fused).
     uint32_t n_tokens = 1, q_stride = 0, out_stride = 0;
+    // Batched decode: query z is the current token of sequence z — its position is pos_ptr[z] and its caches lie
+    // z * kv_batch_stride floats after k_cache / v_cache (grouped-query kernel, not fused).
+    bool pos_per_query = false;
+    size_t kv_batch_stride = 0;
     TpFuse tp;               // grouped-query kernel: tensor parallelism, output pushed as (value, epoch) pairs
+    uint32_t window = 0;     // sliding window (yule-infer/src/model_runner.rs:688-696): positions < pos − window are not attended; 0 = none
+    float softcap = 0.f;     // attention logit softcap (:716-721): score = cap · tanh(score / cap); 0 = none
     bool gqa = false;        // grouped-query kernel: one CTA per (KV head, split); n_splits from attn_gqa_pick_splits
 };
 bool attn_gqa_supported(uint32_t hd, uint32_t n_heads, uint32_t n_kv_heads);

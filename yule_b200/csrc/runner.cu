@@ -31,7 +31,11 @@ struct Tensor {
 
 struct Layer {
     Tensor attn_norm, attn_q, attn_k, attn_v, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down;
+    // optional tensors of the architecture variants (yule-infer/src/weight_loader.rs:203-218)
+    Tensor q_bias, k_bias, v_bias, attn_post_norm, ffn_post_norm;
     const float *attn_norm_f32 = nullptr, *ffn_norm_f32 = nullptr;
+    const float *q_bias_f32 = nullptr, *k_bias_f32 = nullptr, *v_bias_f32 = nullptr;
+    const float *attn_post_norm_f32 = nullptr, *ffn_post_norm_f32 = nullptr;
     yule_buffer k_cache_h = 0, v_cache_h = 0;
     float *k_cache = nullptr, *v_cache = nullptr;
 };
@@ -70,6 +74,18 @@ struct yule_cuda_runner {
     float *pf_x = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_att = nullptr, *pf_gate = nullptr,
           *pf_up = nullptr, *pf_attn_scratch = nullptr;
     uint32_t *pf_tokens = nullptr, *pf_tickets = nullptr;
+
+    // Batched decode: `bd_batch` independent sequences advancing one token per step, each with its own KV
+    // caches and position; every linear is one GEMM over the batch (the chunk buffers above hold the rows).
+    uint32_t bd_batch = 0, bd_rows = 0;  // sequences; rows the GEMMs run over (at least 8)
+    std::vector<float *> bd_k, bd_v;     // per layer [batch][max_seq_len][kv_dim]
+    float *bd_logits = nullptr;          // [bd_rows][vocab]
+    uint32_t *bd_tokens = nullptr, *bd_pos = nullptr, *bd_step = nullptr, *bd_history = nullptr, *bd_prompts = nullptr;
+    size_t bd_prompts_cap = 0;
+    std::vector<uint32_t> bd_host_pos;
+    uint32_t bd_host_step = 0;
+    cudaGraphExec_t bd_graph = nullptr;
+    uint32_t bd_graph_kernels = 0;
 
     uint32_t pos = 0;
     bool fused = false;
@@ -113,7 +129,9 @@ Tensor *slot_for(yule_cuda_runner *r, const char *name) {
                  {"attn_k.weight", &L.attn_k},           {"attn_v.weight", &L.attn_v},
                  {"attn_output.weight", &L.attn_output}, {"ffn_norm.weight", &L.ffn_norm},
                  {"ffn_gate.weight", &L.ffn_gate},       {"ffn_up.weight", &L.ffn_up},
-                 {"ffn_down.weight", &L.ffn_down}};
+                 {"ffn_down.weight", &L.ffn_down},       {"attn_q.bias", &L.q_bias},
+                 {"attn_k.bias", &L.k_bias},             {"attn_v.bias", &L.v_bias},
+                 {"attn_post_norm.weight", &L.attn_post_norm}, {"ffn_post_norm.weight", &L.ffn_post_norm}};
     for (auto &s : slots)
         if (!strcmp(rest, s.n)) return s.t;
     return nullptr;
@@ -132,27 +150,54 @@ int32_t check_matrix(const Tensor &t, const char *what, uint32_t layer, uint64_t
     return YULE_OK;
 }
 
-// Norm weights arrive as F32 or F16 (gpu_runner.rs:183-211 converts on the host); F16 ones are
-// expanded once on the device.
-int32_t norm_as_f32(yule_cuda_runner *r, const Tensor &t, const char *what, uint32_t layer, const float **out) {
-    const uint32_t dim = r->cfg.dim;
+// Norm weights and biases arrive as F32 or F16 (gpu_runner.rs:183-211 converts on the host; model_runner.rs:259-273,
+// :295-310 read both); F16 ones are expanded once on the device.  `offset` is Gemma's norm weight offset
+// (model_runner.rs:273: w[i] + offset, formed in f32 exactly as there).
+int32_t vector_as_f32(yule_cuda_runner *r, const Tensor &t, const char *what, uint32_t layer, uint32_t n, float offset,
+                      const float **out) {
     if (!t.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: %s (layer %u)", what, layer);
-    if (t.type == YULE_DTYPE_F32) {
-        if (t.buf.size < (size_t)dim * 4) return fail(YULE_ERR_OUT_OF_BOUNDS, "%s too small", what);
+    if (t.type != YULE_DTYPE_F32 && t.type != YULE_DTYPE_F16) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "%s must be F32 or F16", what);
+    if (t.buf.size < (size_t)n * (t.type == YULE_DTYPE_F32 ? 4 : 2)) return fail(YULE_ERR_OUT_OF_BOUNDS, "%s too small", what);
+    if (t.type == YULE_DTYPE_F32 && offset == 0.f) {
         *out = (const float *)t.buf.ptr;
         return YULE_OK;
     }
-    if (t.type != YULE_DTYPE_F16) return fail(YULE_ERR_UNSUPPORTED_DTYPE, "%s must be F32 or F16", what);
-    if (t.buf.size < (size_t)dim * 2) return fail(YULE_ERR_OUT_OF_BOUNDS, "%s too small", what);
     float *dst;
-    int32_t rc = alloc_f32(r, dim, &dst);
+    int32_t rc = alloc_f32(r, n, &dst);
     if (rc) return rc;
-    uint64_t n = 0;
-    cudaError_t e = launch_dequantize((const uint8_t *)t.buf.ptr, YULE_DTYPE_F16, dim, dst, r->ctx->stream, &n);
-    r->ctx->launches.fetch_add(n);
-    if (e != cudaSuccess) return fail_cuda(e, "norm weight conversion");
+    uint64_t cnt = 0;
+    cudaError_t e = cudaSuccess;
+    const float *src = (const float *)t.buf.ptr;
+    if (t.type == YULE_DTYPE_F16) {
+        e = launch_dequantize((const uint8_t *)t.buf.ptr, YULE_DTYPE_F16, n, dst, r->ctx->stream, &cnt);
+        src = dst;
+    }
+    if (e == cudaSuccess && offset != 0.f) e = launch_elementwise(kElemAddScalar, src, nullptr, dst, n, offset, r->ctx->stream, &cnt);
+    r->ctx->launches.fetch_add(cnt);
+    if (e != cudaSuccess) return fail_cuda(e, "norm / bias weight conversion");
     *out = dst;
     return YULE_OK;
+}
+int32_t norm_as_f32(yule_cuda_runner *r, const Tensor &t, const char *what, uint32_t layer, const float **out) {
+    return vector_as_f32(r, t, what, layer, r->cfg.dim, r->cfg.norm_weight_offset, out);
+}
+
+// Any architecture variant that changes the op sequence (everything except partial RoPE, which lives in the
+// RoPE table, and the norm offset, which lives in the converted norm weights).
+bool has_bias(const yule_cuda_runner *r) {
+    for (const Layer &L : r->layers)
+        if (L.q_bias.set || L.k_bias.set || L.v_bias.set) return true;
+    return false;
+}
+bool has_post_norms(const yule_cuda_runner *r) {
+    for (const Layer &L : r->layers)
+        if (L.attn_post_norm.set || L.ffn_post_norm.set) return true;
+    return false;
+}
+bool is_variant(const yule_cuda_runner *r) {
+    const yule_runner_config &c = r->cfg;
+    return c.sliding_window || c.attn_logit_softcap != 0.f || c.logit_softcap != 0.f || c.norm_weight_offset != 0.f || c.geglu ||
+           has_bias(r) || has_post_norms(r);
 }
 
 struct Step {
@@ -219,13 +264,21 @@ cudaError_t enqueue_forward_by_value(yule_cuda_runner *r, uint32_t token, uint32
     Step st{r};
     st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, token, nullptr,
                               r->hidden, s, &st.n));
+    // Gemma: embeddings scaled by sqrt(dim) (model_runner.rs:568-574)
+    if (c.norm_weight_offset > 0.f) st.ok(launch_elementwise(kElemScale, r->hidden, nullptr, r->hidden, dim, sqrtf((float)dim), s, &st.n));
+    // RoPE angles of this position; with partial RoPE only the first rotary_dim/2 pairs turn (cos 1, sin 0 beyond)
     RopeAngles ang;
-    const uint32_t half = hd / 2;
+    const uint32_t half = hd / 2, rot = (c.rotary_dim && c.rotary_dim < hd) ? c.rotary_dim : hd;
     for (uint32_t i = 0; i < half; i++) {
-        float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)hd);
-        float theta = (float)pos * freq;
-        ang.cos[i] = cosf(theta);
-        ang.sin[i] = sinf(theta);
+        if (i < rot / 2) {
+            float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)rot);
+            float theta = (float)pos * freq;
+            ang.cos[i] = cosf(theta);
+            ang.sin[i] = sinf(theta);
+        } else {
+            ang.cos[i] = 1.0f;
+            ang.sin[i] = 0.0f;
+        }
     }
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
@@ -234,25 +287,46 @@ cudaError_t enqueue_forward_by_value(yule_cuda_runner *r, uint32_t token, uint32
         st.qmv(L.attn_q, r->normed, r->q, qdim, dim);
         st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim, dim);
         st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim, dim);
+        // Q/K/V bias (model_runner.rs:640-651)
+        if (L.q_bias_f32) st.ok(launch_elementwise(kElemAddVec, r->q, L.q_bias_f32, r->q, qdim, 0.f, s, &st.n));
+        if (L.k_bias_f32) st.ok(launch_elementwise(kElemAddVec, r->k_tmp, L.k_bias_f32, r->k_tmp, kvdim, 0.f, s, &st.n));
+        if (L.v_bias_f32) st.ok(launch_elementwise(kElemAddVec, r->v_tmp, L.v_bias_f32, r->v_tmp, kvdim, 0.f, s, &st.n));
         st.ok(launch_rope_angles(r->q, r->k_tmp, hd, c.n_heads, c.n_kv_heads, ang, s, &st.n));
         const size_t off = (size_t)pos * kvdim;
         st.ok(cudaMemcpyAsync(L.k_cache + off, r->k_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
         st.ok(cudaMemcpyAsync(L.v_cache + off, r->v_tmp, (size_t)kvdim * 4, cudaMemcpyDeviceToDevice, s));
         st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, r->attn_out, hd, pos + 1, nullptr, pos + 1,
-                                         c.n_heads, c.n_kv_heads, kvdim, s, &st.n));
+                                         c.n_heads, c.n_kv_heads, kvdim, s, &st.n, false, c.sliding_window, c.attn_logit_softcap));
         st.qmv(L.attn_output, r->attn_out, r->attn_proj, dim, qdim);
-        st.ok(launch_add(r->residual, r->attn_proj, r->hidden, dim, s, &st.n));
+        // post-attention norm (Gemma2, model_runner.rs:764-779)
+        if (L.attn_post_norm_f32) {
+            st.ok(launch_rms_norm(r->attn_proj, L.attn_post_norm_f32, r->ffn_out, dim, c.norm_eps, s, &st.n));
+            st.ok(launch_add(r->residual, r->ffn_out, r->hidden, dim, s, &st.n));
+        } else {
+            st.ok(launch_add(r->residual, r->attn_proj, r->hidden, dim, s, &st.n));
+        }
         st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
         st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
         st.qmv(L.ffn_gate, r->normed, r->gate, ff, dim);
         st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
-        st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n));
+        if (c.geglu)  // model_runner.rs:974-978
+            st.ok(launch_elementwise(kElemGeluMul, r->gate, r->up, r->gate, ff, 0.f, s, &st.n));
+        else
+            st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n));
         st.qmv(L.ffn_down, r->gate, r->ffn_out, dim, ff);
-        st.ok(launch_add(r->residual, r->ffn_out, r->hidden, dim, s, &st.n));
+        // post-FFN norm (Gemma2, model_runner.rs:985-999)
+        if (L.ffn_post_norm_f32) {
+            st.ok(launch_rms_norm(r->ffn_out, L.ffn_post_norm_f32, r->attn_proj, dim, c.norm_eps, s, &st.n));
+            st.ok(launch_add(r->residual, r->attn_proj, r->hidden, dim, s, &st.n));
+        } else {
+            st.ok(launch_add(r->residual, r->ffn_out, r->hidden, dim, s, &st.n));
+        }
     }
     st.ok(launch_rms_norm(r->hidden, r->output_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
     const Tensor &out_w = r->output.set ? r->output : r->token_embd;
     st.qmv(out_w, r->normed, r->logits, c.vocab_size, dim);
+    // final logit softcap (Gemma2, model_runner.rs:1027-1032)
+    if (c.logit_softcap != 0.f) st.ok(launch_elementwise(kElemSoftcap, r->logits, nullptr, r->logits, c.vocab_size, c.logit_softcap, s, &st.n));
     *launches += st.n;
     return st.err;
 }
@@ -312,7 +386,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     // and the one that consumes it are the Q4_K tensor-pipe kernel, the producer stores (value, epoch) pairs
     // straight into every rank's pair buffer as its rows are reduced and the consumer polls the pairs while it
     // stages x: no exchange launch, no fence, no flag.  YULE_TP_FUSE=0 keeps the exchange kernel everywhere.
-    const bool tp_fuse = N > 1 && r->xchg && !skip_gather && !(knob("YULE_TP_FUSE") && atoi(knob("YULE_TP_FUSE")) == 0);
+    // (the folded exchange assumes the Llama op sequence: a variant model takes the exchange kernel everywhere)
+    const bool tp_fuse = N > 1 && r->xchg && !skip_gather && !is_variant(r) && !(knob("YULE_TP_FUSE") && atoi(knob("YULE_TP_FUSE")) == 0);
     auto is_q4k_mma = [&](const Tensor &t, uint32_t cols) { return t.type == YULE_DTYPE_Q4_K && q4k_mma_supported(cols, 1); };
     auto epoch_index = [&](uint32_t layer, uint32_t k) { return k == 4 ? 4 * c.n_layers : 4 * layer + k; };
     auto push_of = [&](size_t pair_off, uint32_t per_rank, uint32_t layer, uint32_t k) {
@@ -379,6 +454,9 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
     if (!(skip & 256))
         st.ok(launch_embed_gather((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, 0, tok_ptr,
                                   r->hidden, s, &st.n, pdl));
+    // Gemma: embeddings scaled by sqrt(dim) (model_runner.rs:568-574)
+    if (c.norm_weight_offset > 0.f)
+        st.ok(launch_elementwise(kElemScale, r->hidden, nullptr, r->hidden, dim, sqrtf((float)dim), s, &st.n, pdl));
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
         const Tensor &out_w_ = r->output.set ? r->output : r->token_embd;
@@ -395,6 +473,10 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.qmv(L.attn_k, r->normed, r->k_tmp, kvdim_l, dim);
             st.qmv(L.attn_v, r->normed, r->v_tmp, kvdim_l, dim);
         }
+        // Q/K/V bias (model_runner.rs:640-651); tensor parallelism: this rank's rows of each
+        if (L.q_bias_f32) st.ok(launch_elementwise(kElemAddVec, r->q, L.q_bias_f32 + (size_t)R * qdim_l, r->q, qdim_l, 0.f, s, &st.n, pdl));
+        if (L.k_bias_f32) st.ok(launch_elementwise(kElemAddVec, r->k_tmp, L.k_bias_f32 + (size_t)R * kvdim_l, r->k_tmp, kvdim_l, 0.f, s, &st.n, pdl));
+        if (L.v_bias_f32) st.ok(launch_elementwise(kElemAddVec, r->v_tmp, L.v_bias_f32 + (size_t)R * kvdim_l, r->v_tmp, kvdim_l, 0.f, s, &st.n, pdl));
         float *attn_out_l = r->attn_out + (size_t)R * qdim_l;
         if (attn_decode_supported(hd)) {
             // Rope dispatch + both KV copies + MultiheadAttn in one launch
@@ -419,6 +501,8 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             a.max_seq_len = c.max_seq_len;
             a.min_chunk = knob("YULE_CUDA_ATTN_MIN_CHUNK") ? (uint32_t)atoi(knob("YULE_CUDA_ATTN_MIN_CHUNK")) : 32;
             a.pdl = pdl;
+            a.window = c.sliding_window;
+            a.softcap = c.attn_logit_softcap;
             if (folded(l, 0)) a.tp = push_of(r->x_pair_attn, qdim_l, l, 0);
             if (!(skip & 4)) st.ok(launch_attn_decode(a, s, &st.n));
         } else {
@@ -427,7 +511,7 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
                                            pos_ptr, hd, heads_l, kvh_l, s, &st.n, pdl));
             if (!(skip & 4))
                 st.ok(launch_multihead_attention(r->q, L.k_cache, L.v_cache, attn_out_l, hd, 0, pos_ptr, c.max_seq_len,
-                                                 heads_l, kvh_l, kvdim_l, s, &st.n, pdl));
+                                                 heads_l, kvh_l, kvdim_l, s, &st.n, pdl, c.sliding_window, c.attn_logit_softcap));
         }
         if (!folded(l, 0)) gather(r->attn_out, r->x_attn_out, qdim_l, l, 0);
         float *hidden_l = r->hidden + (size_t)R * dim_l;
@@ -437,12 +521,19 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             TpFuse to;
             if (folded(l, 1)) to = push_of(r->x_pair_hidden, dim_l, l, 1);
             if (folded(l, 0)) add_wait(to, r->x_pair_attn, l, 0);
-            if (!(skip & 8)) st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l, nullptr, &to);
+            if (L.attn_post_norm_f32) {
+                // post-attention norm (Gemma2, model_runner.rs:764-779): project, normalise, then add the residual
+                st.qmv(L.attn_output, r->attn_out, r->attn_proj, dim, qdim);
+                st.ok(launch_rms_norm(r->attn_proj, L.attn_post_norm_f32, r->ffn_out, dim, c.norm_eps, s, &st.n, pdl));
+                st.ok(launch_elementwise(kElemAddVec, r->hidden, r->ffn_out, r->hidden, dim, 0.f, s, &st.n, pdl));
+            } else if (!(skip & 8)) {
+                st.qmv(L.attn_output, r->attn_out, hidden_l, dim_l, qdim, hidden_l, nullptr, &to);
+            }
         }
         if (!folded(l, 1)) gather(r->hidden, r->x_hidden, dim_l, l, 1);
         st.then(&L.ffn_down);
         if (skip & 16) {
-        } else if (all_mma({&L.ffn_gate, &L.ffn_up}, dim)) {
+        } else if (!c.geglu && all_mma({&L.ffn_gate, &L.ffn_up}, dim)) {
             TpFuse tg;
             if (folded(l, 2)) tg = push_of(r->x_pair_gate, ff_l, l, 2);
             if (folded(l, 1)) add_wait(tg, r->x_pair_hidden, l, 1);
@@ -452,7 +543,10 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n, pdl));
             st.qmv(L.ffn_gate, r->normed, r->gate + (size_t)R * ff_l, ff_l, dim);
             st.qmv(L.ffn_up, r->normed, r->up, ff_l, dim);
-            st.ok(launch_silu_mul(r->gate + (size_t)R * ff_l, r->up, r->gate + (size_t)R * ff_l, ff_l, s, &st.n, pdl));
+            if (c.geglu)  // model_runner.rs:974-978
+                st.ok(launch_elementwise(kElemGeluMul, r->gate + (size_t)R * ff_l, r->up, r->gate + (size_t)R * ff_l, ff_l, 0.f, s, &st.n, pdl));
+            else
+                st.ok(launch_silu_mul(r->gate + (size_t)R * ff_l, r->up, r->gate + (size_t)R * ff_l, ff_l, s, &st.n, pdl));
         }
         if (!folded(l, 2)) gather(r->gate, r->x_gate, ff_l, l, 2);
         // during down-proj: the next layer's Q and K/V (or the output matrix after the last layer)
@@ -464,7 +558,14 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
             TpFuse td;
             if (folded(l, 3)) td = push_of(r->x_pair_hidden, dim_l, l, 3);
             if (folded(l, 2)) add_wait(td, r->x_pair_gate, l, 2);
-            if (!(skip & 32)) st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l, nullptr, &td);
+            if (L.ffn_post_norm_f32) {
+                // post-FFN norm (Gemma2, model_runner.rs:985-999)
+                st.qmv(L.ffn_down, r->gate, r->ffn_out, dim, ff);
+                st.ok(launch_rms_norm(r->ffn_out, L.ffn_post_norm_f32, r->attn_proj, dim, c.norm_eps, s, &st.n, pdl));
+                st.ok(launch_elementwise(kElemAddVec, r->hidden, r->attn_proj, r->hidden, dim, 0.f, s, &st.n, pdl));
+            } else if (!(skip & 32)) {
+                st.qmv(L.ffn_down, r->gate, hidden_l, dim_l, ff, hidden_l, nullptr, &td);
+            }
         }
         if (!folded(l, 3)) gather(r->hidden, r->x_hidden, dim_l, l, 3);
     }
@@ -482,6 +583,9 @@ cudaError_t enqueue_forward_graph(yule_cuda_runner *r, uint64_t *launches) {
         st.qmv(out_w, r->normed, r->logits + (size_t)R * vocab_l, vocab_l, dim);
     }
     gather(r->logits, r->x_logits, vocab_l, 0, 4);
+    // final logit softcap (Gemma2, model_runner.rs:1027-1032)
+    if (c.logit_softcap != 0.f)
+        st.ok(launch_elementwise(kElemSoftcap, r->logits, nullptr, r->logits, c.vocab_size, c.logit_softcap, s, &st.n, pdl));
     if (!(skip & 128)) st.ok(launch_argmax(r->logits, c.vocab_size, r->d_state, r->d_history, s, &st.n, pdl));
     *launches += st.n;
     return st.err;
@@ -498,6 +602,8 @@ int32_t finalize(yule_cuda_runner *r) {
     int32_t rc;
     if (N > 1 && !r->output.set)
         return fail(YULE_ERR_MISSING_TENSOR, "tensor parallelism needs output.weight (a tied embedding cannot be row-sharded)");
+    if (N > 1 && has_post_norms(r))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "tensor parallelism does not cover the post-attention / post-FFN norms (they need the whole projected vector)");
     if (!r->token_embd.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: token_embd.weight");
     {
         uint32_t bs = block_size(r->token_embd.type);
@@ -515,6 +621,11 @@ int32_t finalize(yule_cuda_runner *r) {
         Layer &L = r->layers[l];
         if ((rc = norm_as_f32(r, L.attn_norm, "attn_norm.weight", l, &L.attn_norm_f32))) return rc;
         if ((rc = norm_as_f32(r, L.ffn_norm, "ffn_norm.weight", l, &L.ffn_norm_f32))) return rc;
+        if (L.attn_post_norm.set && (rc = norm_as_f32(r, L.attn_post_norm, "attn_post_norm.weight", l, &L.attn_post_norm_f32))) return rc;
+        if (L.ffn_post_norm.set && (rc = norm_as_f32(r, L.ffn_post_norm, "ffn_post_norm.weight", l, &L.ffn_post_norm_f32))) return rc;
+        if (L.q_bias.set && (rc = vector_as_f32(r, L.q_bias, "attn_q.bias", l, qdim_in, 0.f, &L.q_bias_f32))) return rc;
+        if (L.k_bias.set && (rc = vector_as_f32(r, L.k_bias, "attn_k.bias", l, c.n_kv_heads * hd, 0.f, &L.k_bias_f32))) return rc;
+        if (L.v_bias.set && (rc = vector_as_f32(r, L.v_bias, "attn_v.bias", l, c.n_kv_heads * hd, 0.f, &L.v_bias_f32))) return rc;
         if ((rc = check_matrix(L.attn_q, "attn_q.weight", l, qdim, dim))) return rc;
         if ((rc = check_matrix(L.attn_k, "attn_k.weight", l, kvdim, dim))) return rc;
         if ((rc = check_matrix(L.attn_v, "attn_v.weight", l, kvdim, dim))) return rc;
@@ -604,6 +715,7 @@ bool prefill_batched_ok(const yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
     if (knob("YULE_CUDA_BATCH_PREFILL") && atoi(knob("YULE_CUDA_BATCH_PREFILL")) == 0) return false;
     if (!r->fused || r->ctx->tp_world > 1 || !r->attn_gqa) return false;
+    if (is_variant(r)) return false;  // the chunked path implements the Llama op sequence only
     if (!qgemm_supported(YULE_DTYPE_Q4_K, c.dim, 8) || !qgemm_supported(YULE_DTYPE_Q4_K, c.ff_dim, 8) ||
         !qgemm_supported(YULE_DTYPE_Q4_K, c.n_heads * c.head_dim, 8))
         return false;
@@ -615,12 +727,10 @@ bool prefill_batched_ok(const yule_cuda_runner *r) {
     return score_bytes <= 96 * 1024;
 }
 
-int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n) {
+// Row buffers of the GEMM-driven paths (chunked prefill, batched decode), allocated on first use.
+int32_t ensure_chunk_buffers(yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
-    yule_cuda_ctx *ctx = r->ctx;
-    cudaStream_t s = ctx->stream;
     const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
-    const int sms = ctx->prop.multiProcessorCount;
     int32_t rc;
     if (!r->pf_chunk) {
         const uint32_t C = prefill_chunk_size(r);
@@ -639,8 +749,19 @@ int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n)
     }
     const uint32_t C = r->pf_chunk;
     const uint32_t widest = ff > qdim ? (ff > dim ? ff : dim) : (qdim > dim ? qdim : dim);
-    if ((rc = ensure_gemm_scratch(ctx, qgemm_scratch_bytes(C, widest)))) return rc;
-    if ((rc = ensure_pinned(r, C))) return rc;
+    if ((rc = ensure_gemm_scratch(r->ctx, qgemm_scratch_bytes(C, widest)))) return rc;
+    return ensure_pinned(r, C);
+}
+
+int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n) {
+    const yule_runner_config &c = r->cfg;
+    yule_cuda_ctx *ctx = r->ctx;
+    cudaStream_t s = ctx->stream;
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    const int sms = ctx->prop.multiProcessorCount;
+    int32_t rc;
+    if ((rc = ensure_chunk_buffers(r))) return rc;
+    const uint32_t C = r->pf_chunk;
     uint64_t launches = 0;
     struct Guard {
         yule_cuda_ctx *ctx;
@@ -733,6 +854,157 @@ int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n)
     return YULE_OK;
 }
 
+// ── batched decode ──────────────────────────────────────────────────────────────────────────
+// `batch` independent sequences, one new token each per step.  The reference decodes one sequence at a time
+// (yule-infer/src/lib.rs:169-216 drives ModelRunner::decode_step); per sequence the arithmetic here is the
+// chunked prefill's — every linear one tensor-core GEMM over the rows, so the weights cross HBM once per step
+// instead of once per sequence — with row b at its own position of its own KV caches.
+
+bool batch_decode_ok(const yule_cuda_runner *r) { return prefill_batched_ok(r); }
+
+// Enqueues one step: tokens in bd_tokens, positions in bd_pos (device).  Leaves the logits in bd_logits, the greedy
+// picks in bd_tokens / bd_history, and moves positions and step counter on.
+cudaError_t enqueue_batch_step(yule_cuda_runner *r, uint64_t *launches) {
+    const yule_runner_config &c = r->cfg;
+    yule_cuda_ctx *ctx = r->ctx;
+    cudaStream_t s = ctx->stream;
+    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    const uint32_t B = r->bd_batch, m = r->bd_rows;
+    const int sms = ctx->prop.multiProcessorCount;
+    const size_t cache_stride = (size_t)c.max_seq_len * kvdim;
+    cudaError_t err = cudaSuccess;
+    auto ok = [&](cudaError_t e) {
+        if (err == cudaSuccess && e != cudaSuccess) err = e;
+    };
+    auto xprep = [&](const float *x, uint32_t cols, const float *norm_w, const float *gate) {
+        QGemm g;
+        g.type = YULE_DTYPE_Q4_K;
+        g.x = x;
+        g.gate = gate;
+        g.norm_w = norm_w;
+        g.eps = c.norm_eps;
+        g.x_stride = cols;
+        g.n_cols = cols;
+        g.n_tokens = m;
+        g.scratch = ctx->gemm_scratch;
+        ok(launch_qgemm_xprep(g, s, launches));
+    };
+    auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, float *out, const float *residual) {
+        QGemm g;
+        g.w = (const uint8_t *)t.buf.ptr;
+        g.type = t.type;
+        g.out = out;
+        g.residual = residual;
+        g.n_rows = rows;
+        g.n_cols = cols;
+        g.n_tokens = m;
+        g.out_stride = rows;
+        g.scratch = ctx->gemm_scratch;
+        g.status = ctx->device_status;
+        ok(launch_qgemm_mm(g, sms, s, launches));
+    };
+    ok(launch_embed_gather_batch((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, r->bd_tokens, B, r->pf_x, s, launches));
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        Layer &L = r->layers[l];
+        xprep(r->pf_x, dim, L.attn_norm_f32, nullptr);
+        mm(L.attn_q, qdim, dim, r->pf_q, nullptr);
+        mm(L.attn_k, kvdim, dim, r->pf_k, nullptr);
+        mm(L.attn_v, kvdim, dim, r->pf_v, nullptr);
+        ok(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, r->bd_k[l], r->bd_v[l], r->rope_cos, r->rope_sin, 0, B, hd, c.n_heads,
+                                      c.n_kv_heads, s, launches, r->bd_pos, cache_stride));
+        AttnDecode a;
+        a.q = r->pf_q;
+        a.k_cache = r->bd_k[l];
+        a.v_cache = r->bd_v[l];
+        a.pos_ptr = r->bd_pos;
+        a.pos_per_query = true;
+        a.kv_batch_stride = cache_stride;
+        a.out = r->pf_att;
+        a.scratch = r->pf_attn_scratch;
+        a.tickets = r->pf_tickets;
+        a.hd = hd;
+        a.n_heads = c.n_heads;
+        a.n_kv_heads = c.n_kv_heads;
+        a.kv_stride = kvdim;
+        a.n_splits = r->pf_splits;
+        a.max_seq_len = c.max_seq_len;
+        a.min_chunk = kPrefillMinChunk;
+        a.gqa = true;
+        a.n_tokens = B;
+        a.q_stride = qdim;
+        a.out_stride = qdim;
+        ok(launch_attn_decode(a, s, launches));
+        xprep(r->pf_att, qdim, nullptr, nullptr);
+        mm(L.attn_output, dim, qdim, r->pf_x, r->pf_x);
+        xprep(r->pf_x, dim, L.ffn_norm_f32, nullptr);
+        mm(L.ffn_gate, ff, dim, r->pf_gate, nullptr);
+        mm(L.ffn_up, ff, dim, r->pf_up, nullptr);
+        xprep(r->pf_up, ff, nullptr, r->pf_gate);
+        mm(L.ffn_down, dim, ff, r->pf_x, r->pf_x);
+    }
+    const Tensor &out_w = r->output.set ? r->output : r->token_embd;
+    xprep(r->pf_x, dim, r->output_norm_f32, nullptr);
+    mm(out_w, c.vocab_size, dim, r->bd_logits, nullptr);
+    ok(launch_argmax_rows(r->bd_logits, c.vocab_size, B, r->bd_tokens, r->bd_pos, r->bd_step, r->bd_history, c.max_seq_len + 1, s, launches));
+    ok(launch_advance_rows(r->bd_pos, r->bd_step, B, s, launches));
+    return err;
+}
+
+int32_t ensure_batch_state(yule_cuda_runner *r, uint32_t batch) {
+    const yule_runner_config &c = r->cfg;
+    if (!batch_decode_ok(r))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "batched decode needs a single-GPU runner created with fused = 1, block-quantised "
+                                               "linears with column counts in multiples of 256 and the Llama op sequence");
+    int32_t rc = ensure_chunk_buffers(r);
+    if (rc) return rc;
+    if (batch == 0 || batch > r->pf_chunk) return fail(YULE_ERR_INVALID_ARGUMENT, "batch %u outside 1..%u", batch, r->pf_chunk);
+    if (r->bd_batch == batch) return YULE_OK;
+    if (r->bd_batch) return fail(YULE_ERR_INVALID_ARGUMENT, "this runner decodes batches of %u sequences; %u asked for", r->bd_batch, batch);
+    const uint32_t kvdim = c.n_kv_heads * c.head_dim;
+    const uint32_t rows = batch < 8 ? 8 : batch;  // the GEMM works on at least eight rows; the extra ones stay unused
+    r->bd_k.assign(c.n_layers, nullptr);
+    r->bd_v.assign(c.n_layers, nullptr);
+    for (uint32_t l = 0; l < c.n_layers; l++)
+        if ((rc = alloc_f32(r, (size_t)batch * c.max_seq_len * kvdim, &r->bd_k[l])) ||
+            (rc = alloc_f32(r, (size_t)batch * c.max_seq_len * kvdim, &r->bd_v[l])))
+            return rc;
+    float *tok = nullptr, *pos = nullptr, *step = nullptr, *hist = nullptr;
+    if ((rc = alloc_f32(r, (size_t)rows * c.vocab_size, &r->bd_logits)) || (rc = alloc_f32(r, rows, &tok)) ||
+        (rc = alloc_f32(r, rows, &pos)) || (rc = alloc_f32(r, 4, &step)) ||
+        (rc = alloc_f32(r, (size_t)batch * (c.max_seq_len + 1), &hist)))
+        return rc;
+    r->bd_tokens = (uint32_t *)tok;
+    r->bd_pos = (uint32_t *)pos;
+    r->bd_step = (uint32_t *)step;
+    r->bd_history = (uint32_t *)hist;
+    r->bd_host_pos.assign(batch, 0);
+    r->bd_host_step = 0;
+    r->bd_batch = batch;
+    r->bd_rows = rows;
+    return YULE_OK;
+}
+
+int32_t ensure_batch_graph(yule_cuda_runner *r) {
+    if (r->bd_graph) return YULE_OK;
+    cudaStream_t s = r->ctx->stream;
+    cudaGraph_t graph = nullptr;
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    YULE_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
+    uint64_t n = 0;
+    cudaError_t e = enqueue_batch_step(r, &n);
+    cudaError_t e2 = cudaStreamEndCapture(s, &graph);
+    if (e != cudaSuccess || e2 != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return fail_cuda(e != cudaSuccess ? e : e2, "graph capture of the batched decode step");
+    }
+    e = cudaGraphInstantiate(&r->bd_graph, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGraphInstantiate");
+    r->bd_graph_kernels = (uint32_t)n;
+    return YULE_OK;
+}
+
 // One token through the model; logits stay on the device.
 int32_t step(yule_cuda_runner *r, uint32_t token, bool token_from_device) {
     const yule_runner_config &c = r->cfg;
@@ -786,6 +1058,8 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         return fail(YULE_ERR_INVALID_ARGUMENT, "runner config has a zero field");
     if (c.n_heads % c.n_kv_heads) return fail(YULE_ERR_INVALID_ARGUMENT, "n_heads must be a multiple of n_kv_heads");
     if (c.head_dim % 2 || c.head_dim > 256) return fail(YULE_ERR_INVALID_ARGUMENT, "head_dim must be even and <= 256");
+    if (c.rotary_dim % 2) return fail(YULE_ERR_INVALID_ARGUMENT, "rotary_dim must be even");
+    if (c.attn_logit_softcap < 0.f || c.logit_softcap < 0.f) return fail(YULE_ERR_INVALID_ARGUMENT, "softcaps must be positive (0 = none)");
     if (c.dim % 32 || c.ff_dim % 32 || (c.n_heads * c.head_dim) % 32)
         return fail(YULE_ERR_INVALID_ARGUMENT, "dim, ff_dim and n_heads*head_dim must be multiples of 32");
     const uint32_t tpw = ctx->tp_world ? ctx->tp_world : 1;
@@ -864,12 +1138,20 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         // RoPE table with the CPU runner's recipe (model_runner.rs:78-99): f32 powf / sin / cos of
         // the host libm, so rotations match it bit for bit.
         std::vector<float> hc((size_t)c.max_seq_len * half), hs((size_t)c.max_seq_len * half);
+        // partial RoPE (model_runner.rs:430-434, :502): only the first rotary_dim/2 pairs of a head turn, with
+        // frequencies formed over rotary_dim; the other pairs get the identity rotation (x·1 − y·0 is x exactly)
+        const size_t rot = (c.rotary_dim && c.rotary_dim < hd) ? c.rotary_dim : hd;
         for (size_t p = 0; p < c.max_seq_len; p++)
             for (size_t i = 0; i < half; i++) {
-                float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)hd);
-                float theta = (float)p * freq;
-                hc[p * half + i] = cosf(theta);
-                hs[p * half + i] = sinf(theta);
+                if (i < rot / 2) {
+                    float freq = 1.0f / powf(c.rope_freq_base, 2.0f * (float)i / (float)rot);
+                    float theta = (float)p * freq;
+                    hc[p * half + i] = cosf(theta);
+                    hs[p * half + i] = sinf(theta);
+                } else {
+                    hc[p * half + i] = 1.0f;
+                    hs[p * half + i] = 0.0f;
+                }
             }
         cudaError_t e = cudaMemcpyAsync(r->rope_cos, hc.data(), hc.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess)
@@ -890,6 +1172,7 @@ int32_t yule_cuda_runner_destroy(yule_cuda_runner *r) {
     cudaSetDevice(r->ctx->device);
     cudaStreamSynchronize(r->ctx->stream);
     if (r->graph_exec) cudaGraphExecDestroy(r->graph_exec);
+    if (r->bd_graph) cudaGraphExecDestroy(r->bd_graph);
     if (r->h_pinned) cudaFreeHost(r->h_pinned);
     for (yule_buffer h : r->owned) yule_cuda_free(r->ctx, h);
     delete r;
@@ -911,6 +1194,10 @@ int32_t yule_cuda_runner_set_tensor(yule_cuda_runner *r, const char *name, yule_
     if (r->graph_exec) {  // pointers are baked into the graph
         cudaGraphExecDestroy(r->graph_exec);
         r->graph_exec = nullptr;
+    }
+    if (r->bd_graph) {
+        cudaGraphExecDestroy(r->bd_graph);
+        r->bd_graph = nullptr;
     }
     return YULE_OK;
 }
@@ -1012,6 +1299,95 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *pr
     }
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
     return r->xchg ? yule_cuda_synchronize(r->ctx) : YULE_OK;  // reports a peer that never arrived
+}
+
+int32_t yule_cuda_runner_reset_batch(yule_cuda_runner *r) {
+    if (!r) return fail(YULE_ERR_INVALID_ARGUMENT, "null runner");
+    for (auto &p : r->bd_host_pos) p = 0;
+    r->bd_host_step = 0;
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_decode_batch(yule_cuda_runner *r, const uint32_t *tokens, uint32_t batch, float *logits_out) {
+    if (!r || !tokens) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    if ((rc = ensure_batch_state(r, batch))) return rc;
+    const yule_runner_config &c = r->cfg;
+    for (uint32_t b = 0; b < batch; b++) {
+        if (tokens[b] >= c.vocab_size) return fail(YULE_ERR_INVALID_ARGUMENT, "token %u outside the vocabulary (%u)", tokens[b], c.vocab_size);
+        if (r->bd_host_pos[b] >= c.max_seq_len) return fail(YULE_ERR_CONTEXT_LENGTH, "context length exceeded");
+    }
+    if ((rc = ensure_batch_graph(r))) return rc;
+    cudaStream_t s = r->ctx->stream;
+    if ((rc = ensure_pinned(r, 2 * (size_t)batch + 1))) return rc;
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));  // staging words may still be in flight
+    // tokens, positions and the step are rewritten from the host's copy, so a reset or a failed step cannot
+    // leave the device counters out of step with it
+    for (uint32_t b = 0; b < batch; b++) {
+        r->h_pinned[b] = tokens[b];
+        r->h_pinned[batch + b] = r->bd_host_pos[b];
+    }
+    r->h_pinned[2 * batch] = r->bd_host_step;
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_tokens, r->h_pinned, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_pos, r->h_pinned + batch, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_step, r->h_pinned + 2 * batch, 4, cudaMemcpyHostToDevice, s));
+    YULE_CUDA_TRY(cudaGraphLaunch(r->bd_graph, s));
+    r->ctx->launches.fetch_add(r->bd_graph_kernels);
+    for (auto &p : r->bd_host_pos) p += 1;
+    r->bd_host_step += 1;
+    if (logits_out) YULE_CUDA_TRY(cudaMemcpyAsync(logits_out, r->bd_logits, (size_t)batch * c.vocab_size * 4, cudaMemcpyDeviceToHost, s));
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    return yule_cuda_synchronize(r->ctx);
+}
+
+int32_t yule_cuda_runner_generate_greedy_batch(yule_cuda_runner *r, const uint32_t *prompts, uint32_t batch, uint32_t n_prompt,
+                                               uint32_t n_generate, uint32_t *out_tokens) {
+    if (!r || !prompts || (n_generate && !out_tokens)) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    if (n_prompt == 0) return fail(YULE_ERR_INVALID_ARGUMENT, "every sequence needs at least one prompt token");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    if ((rc = ensure_batch_state(r, batch))) return rc;
+    const yule_runner_config &c = r->cfg;
+    if ((uint64_t)n_prompt + n_generate > c.max_seq_len) return fail(YULE_ERR_CONTEXT_LENGTH, "context length exceeded");
+    for (size_t i = 0; i < (size_t)batch * n_prompt; i++)
+        if (prompts[i] >= c.vocab_size) return fail(YULE_ERR_INVALID_ARGUMENT, "token %u outside the vocabulary", prompts[i]);
+    if ((rc = ensure_batch_graph(r))) return rc;
+    cudaStream_t s = r->ctx->stream;
+    // prompts to the device, position-major, so that step i takes its tokens with one small device copy
+    const size_t n_words = (size_t)batch * n_prompt;
+    if (r->bd_prompts_cap < n_words) {
+        float *pw = nullptr;
+        if ((rc = alloc_f32(r, n_words, &pw))) return rc;
+        r->bd_prompts = (uint32_t *)pw;
+        r->bd_prompts_cap = n_words;
+    }
+    if ((rc = ensure_pinned(r, n_words + batch + 1))) return rc;
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    for (uint32_t i = 0; i < n_prompt; i++)
+        for (uint32_t b = 0; b < batch; b++) r->h_pinned[(size_t)i * batch + b] = prompts[(size_t)b * n_prompt + i];
+    for (uint32_t b = 0; b <= batch; b++) r->h_pinned[n_words + b] = 0;  // positions and step start at zero
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_prompts, r->h_pinned, n_words * 4, cudaMemcpyHostToDevice, s));
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_pos, r->h_pinned + n_words, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_step, r->h_pinned + n_words + batch, 4, cudaMemcpyHostToDevice, s));
+    for (uint32_t i = 0; i < n_prompt + n_generate; i++) {
+        // prompt steps take their tokens from the prompt; afterwards each step consumes the previous step's picks
+        if (i < n_prompt)
+            YULE_CUDA_TRY(cudaMemcpyAsync(r->bd_tokens, r->bd_prompts + (size_t)i * batch, (size_t)batch * 4, cudaMemcpyDeviceToDevice, s));
+        YULE_CUDA_TRY(cudaGraphLaunch(r->bd_graph, s));
+    }
+    r->ctx->launches.fetch_add((uint64_t)r->bd_graph_kernels * (n_prompt + n_generate));
+    // token g of sequence b is the pick made after position n_prompt − 1 + g
+    const size_t hist_stride = (size_t)c.max_seq_len + 1;
+    for (uint32_t b = 0; b < batch && n_generate; b++)
+        YULE_CUDA_TRY(cudaMemcpyAsync(out_tokens + (size_t)b * n_generate, r->bd_history + b * hist_stride + n_prompt - 1,
+                                      (size_t)n_generate * 4, cudaMemcpyDeviceToHost, s));
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    for (auto &p : r->bd_host_pos) p = n_prompt + n_generate;
+    r->bd_host_step = n_prompt + n_generate;
+    return yule_cuda_synchronize(r->ctx);
 }
 
 int32_t yule_cuda_runner_buffer(yule_cuda_runner *r, uint32_t which, uint32_t layer, yule_buffer *out_handle) {

@@ -333,18 +333,24 @@ int ys_quantize(int type, const float *x, uint64_t n, uint8_t *out, int n_thread
     return 0;
 }
 
-// N(0, std) weights generated and quantised block by block without an f32 copy of the tensor.
-int ys_random_quantized(int type, uint64_t seed, float std_, uint8_t *out, uint64_t n_weights, int n_threads) {
+// N(0, std) weights generated and quantised block by block without an f32 copy of the tensor.  The weights
+// are those at positions [first_weight, first_weight + n_weights) of the tensor's stream (a function of seed
+// and position only), so a row shard can be generated on its own and equals the same rows of the whole tensor.
+int ys_random_quantized_at(int type, uint64_t seed, float std_, uint8_t *out, uint64_t first_weight, uint64_t n_weights,
+                           int n_threads) {
     const int bs = block_size(type), bb = block_bytes(type);
-    if (!bs || !has_quantizer(type) || n_weights % (uint64_t)bs) return -1;
+    if (!bs || !has_quantizer(type) || n_weights % (uint64_t)bs || first_weight % (uint64_t)bs) return -1;
     parallel_for(n_weights / bs, n_threads, [=](uint64_t b, uint64_t e) {
         float tmp[256];
         for (uint64_t i = b; i < e; i++) {
-            for (int k = 0; k < bs; k++) tmp[k] = std_ * normal(seed, i * (uint64_t)bs + k);
+            for (int k = 0; k < bs; k++) tmp[k] = std_ * normal(seed, first_weight + i * (uint64_t)bs + k);
             quantize_block(type, tmp, out + i * (uint64_t)bb);
         }
     });
     return 0;
+}
+int ys_random_quantized(int type, uint64_t seed, float std_, uint8_t *out, uint64_t n_weights, int n_threads) {
+    return ys_random_quantized_at(type, seed, std_, out, 0, n_weights, n_threads);
 }
 
 uint16_t ys_f32_to_f16(float f) { return f32_to_f16(f); }

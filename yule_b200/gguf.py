@@ -97,7 +97,10 @@ class GgufFile:
         _check(self._lib.yule_gguf_runner_config(self._g, max_seq_len, C.byref(cfg)))
         return ModelConfig(dim=cfg.dim, n_layers=cfg.n_layers, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
                            head_dim=cfg.head_dim, vocab_size=cfg.vocab_size, ff_dim=cfg.ff_dim,
-                           max_seq_len=cfg.max_seq_len, norm_eps=cfg.norm_eps, rope_freq_base=cfg.rope_freq_base)
+                           max_seq_len=cfg.max_seq_len, norm_eps=cfg.norm_eps, rope_freq_base=cfg.rope_freq_base,
+                           rotary_dim=cfg.rotary_dim, sliding_window=cfg.sliding_window,
+                           attn_logit_softcap=cfg.attn_logit_softcap, logit_softcap=cfg.logit_softcap,
+                           norm_weight_offset=cfg.norm_weight_offset, geglu=bool(cfg.geglu))
 
 
 def load_runner(backend: CudaB200Backend, gguf: GgufFile, max_seq_len: int = 0, fused: bool = True) -> CudaTransformerRunner:

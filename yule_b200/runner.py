@@ -31,6 +31,13 @@ class ModelConfig:
     max_seq_len: int = 4096
     norm_eps: float = 1e-5
     rope_freq_base: float = 10000.0
+    # architecture variants of the CPU runner's dense path (yule-infer/src/model_runner.rs:417-460); zero = Llama
+    rotary_dim: int = 0
+    sliding_window: int = 0
+    attn_logit_softcap: float = 0.0
+    logit_softcap: float = 0.0
+    norm_weight_offset: float = 0.0
+    geglu: bool = False
 
     def tensor_shapes(self) -> dict[str, tuple[int, int]]:
         """GGUF tensor name → (rows, cols) for every matrix the runner reads (gpu_runner.rs:213-222)."""
@@ -67,7 +74,9 @@ class CudaTransformerRunner:
         self._lib = _lib.cuda_lib()
         cfg = _lib.RunnerConfig(config.dim, config.n_layers, config.n_heads, config.n_kv_heads, config.head_dim,
                                 config.vocab_size, config.ff_dim, config.max_seq_len, config.norm_eps,
-                                config.rope_freq_base, 1 if fused else 0)
+                                config.rope_freq_base, 1 if fused else 0, config.rotary_dim, config.sliding_window,
+                                config.attn_logit_softcap, config.logit_softcap, config.norm_weight_offset,
+                                1 if config.geglu else 0)
         r = C.c_void_p()
         _check(self._lib.yule_cuda_runner_create(backend._ctx, C.byref(cfg), C.byref(r)))
         self._r = r
@@ -127,6 +136,30 @@ class CudaTransformerRunner:
             self._r, toks.ctypes.data_as(C.POINTER(C.c_uint32)), toks.size, n_generate,
             out.ctypes.data_as(C.POINTER(C.c_uint32))))
         return out[:n_generate]
+
+    # ── batched decode: independent sequences advancing together ───────────────────────────
+    def decode_batch(self, tokens) -> np.ndarray:
+        """One new token for each of ``len(tokens)`` sequences (each with its own KV caches and position);
+        returns the logits ``[batch][vocab_size]``.  The first call fixes the batch size."""
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        logits = np.empty((toks.size, self.config.vocab_size), np.float32)
+        _check(self._lib.yule_cuda_runner_decode_batch(self._r, toks.ctypes.data_as(C.POINTER(C.c_uint32)), toks.size,
+                                                       logits.ctypes.data_as(C.POINTER(C.c_float))))
+        return logits
+
+    def reset_batch(self) -> None:
+        _check(self._lib.yule_cuda_runner_reset_batch(self._r))
+
+    def generate_greedy_batch(self, prompts, n_generate: int) -> np.ndarray:
+        """``prompts`` is ``[batch][n_prompt]`` (equal lengths); returns ``[batch][n_generate]`` greedy tokens,
+        picked on the device."""
+        p = np.ascontiguousarray(prompts, dtype=np.uint32)
+        assert p.ndim == 2
+        out = np.empty((p.shape[0], max(n_generate, 1)), np.uint32)
+        _check(self._lib.yule_cuda_runner_generate_greedy_batch(
+            self._r, p.ctypes.data_as(C.POINTER(C.c_uint32)), p.shape[0], p.shape[1], n_generate,
+            out.ctypes.data_as(C.POINTER(C.c_uint32))))
+        return out[:, :n_generate] if n_generate else out[:, :0]
 
     def buffer(self, which: str, layer: int = 0) -> BufferHandle:
         sel = {"hidden": 0, "k_cache": 1, "v_cache": 2, "logits": 3}[which]

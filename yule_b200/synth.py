@@ -61,21 +61,31 @@ def quantize(dtype: DType, x: np.ndarray, n_threads: int = 0) -> np.ndarray:
     return out
 
 
-def random_quantized(dtype: DType, seed: int, n_weights: int, std: float = 0.02, n_threads: int = 0) -> np.ndarray:
-    """N(0, std) weights quantised to ``dtype`` (generated block by block, no f32 copy kept)."""
-    assert n_weights % dtype.block_size == 0
+def random_quantized(dtype: DType, seed: int, n_weights: int, std: float = 0.02, n_threads: int = 0,
+                     first_weight: int = 0) -> np.ndarray:
+    """N(0, std) weights quantised to ``dtype`` (generated block by block, no f32 copy kept): the weights at
+    positions ``[first_weight, first_weight + n_weights)`` of the stream that ``seed`` defines, so a row shard
+    generated on its own equals those rows of the whole tensor."""
+    assert n_weights % dtype.block_size == 0 and first_weight % dtype.block_size == 0
     out = np.empty(n_weights // dtype.block_size * dtype.size_of_block, np.uint8)
-    rc = _lib.synth_lib().ys_random_quantized(int(dtype), seed, std, out.ctypes.data_as(_u8p), n_weights, n_threads)
+    rc = _lib.synth_lib().ys_random_quantized_at(int(dtype), seed, std, out.ctypes.data_as(_u8p), first_weight,
+                                                  n_weights, n_threads)
     assert rc == 0
     return out
 
 
+ROW_SHARDED = ("attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight", "ffn_gate.weight",
+               "ffn_up.weight", "ffn_down.weight", "output.weight")
+
+
 def synthetic_model(cfg: ModelConfig, seed: int = 0, linear: DType = DType.Q4_K, ffn_down: DType | None = None,
                     output: DType | None = None, token_embd: DType | None = None, std: float = 0.02,
-                    norm_dtype: DType = DType.F32) -> dict:
+                    norm_dtype: DType = DType.F32, rank: int = 0, world: int = 1) -> dict:
     """Random-init N(0, std) Llama-architecture weights as a GGUF-name → (bytes, DType) map.
 
-    Norm weights are 1.0.  ``ffn_down`` / ``output`` / ``token_embd`` default to ``linear``.
+    Norm weights are 1.0.  ``ffn_down`` / ``output`` / ``token_embd`` default to ``linear``.  With ``world`` > 1
+    only this rank's output rows of every linear are generated (the same bytes as those rows of the
+    ``world`` = 1 model); the embedding table and the norms are whole.
     """
     ffn_down = ffn_down or linear
     output = output or linear
@@ -90,7 +100,12 @@ def synthetic_model(cfg: ModelConfig, seed: int = 0, linear: DType = DType.Q4_K,
             dt = ffn_down
         else:
             dt = linear
-        weights[name] = (random_quantized(dt, tensor_seed(seed, name), rows * cols, std), dt)
+        if world > 1 and name.endswith(ROW_SHARDED):
+            assert rows % world == 0
+            local = rows // world
+            weights[name] = (random_quantized(dt, tensor_seed(seed, name), local * cols, std, first_weight=rank * local * cols), dt)
+        else:
+            weights[name] = (random_quantized(dt, tensor_seed(seed, name), rows * cols, std), dt)
     for name in cfg.norm_names():
         ones = np.ones(cfg.dim, np.float32)
         if norm_dtype == DType.F16:
