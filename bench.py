@@ -218,6 +218,28 @@ def matvec_ring_roofline(backend, peaks, peak_kind, iters: int = 1000) -> dict:
             "traffic": RING_TRAFFIC_BYTES, "traffic_source": RING_TRAFFIC_SOURCE}
 
 
+def reference_cuda_kernel_leg(peaks) -> dict:
+    """The reference's own CUDA kernel for the same matvec (yule-gpu/kernels/cuda/qmv_q4_k.cu, compiled unmodified
+    for sm_100a into oracle/_ref/ and launched with its launch shape, yule-gpu/src/cuda/kernels.rs:236-243: one
+    256-thread block per row) on the same 5632x2048 ring: what a recompile of the reference gives on this GPU."""
+    try:
+        from oracle import ref_cuda
+        from yule_b200 import DType, matvec_bytes, synth
+        if not ref_cuda.available(int(DType.Q4_K)):
+            return {"unavailable": "oracle/_ref holds no compiled reference kernel (no Yule checkout was reachable at build time)"}
+        n_rows, n_cols, dt = 5632, 2048, DType.Q4_K
+        per, copies = dt.tensor_bytes(n_rows, n_cols), 80
+        ring = np.concatenate([synth.random_blocks(dt, 1000 + c, n_rows * n_cols // 256) for c in range(8)])
+        ring = np.tile(ring, copies // 8)
+        us = ref_cuda.time_ring(int(dt), ring, per, copies, synth.normal(7, n_cols), n_rows, n_cols, launches=200)
+        nbytes = matvec_bytes(dt, n_rows, n_cols)
+        gbs = nbytes / us / 1e3
+        return {"kernel": "qmv_q4_k_kernel (reference, one block per row)", "workload": "Q4_K 5632x2048 matvec x200 over the same 80-copy ring",
+                "us_per_launch": round(us, 3), "achieved": round(gbs, 1), "unit": "GB/s", "frac": round(gbs / float(peaks["hbm_gbs"]), 4)}
+    except Exception as e:  # a missing driver binding or module must not take the bench line down
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+
+
 def large_shape_rooflines(backend, peaks) -> dict:
     """The same matvec kernels on shapes large enough to be bandwidth-bound (BASELINE.json configs[2]'s 128256x4096,
     Q4_K and Q6_K, batch 1) and the tcgen05 GEMM on a prefill-sized problem: what the kernels do when launch
@@ -509,6 +531,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
     if rank == 0:
         roof = matvec_ring_roofline(backend, peaks, peak_kind, iters=20 if args.small else 1000)
         roof_large = None if (args.small or world > 1 or args.workload != "c1") else large_shape_rooflines(backend, peaks)
+        ref_kernel = None if (args.small or world > 1 or args.workload != "c1") else reference_cuda_kernel_leg(peaks)
         mid_pos = N_PROMPT + N_GEN // 2
         bpt = decode_bytes_per_token(cfg, weights, mid_pos, tp_world=world if tp else 1)
         per_gpu_tok_s = N_GEN * args.steps / (decode_ms * 1e-3)
@@ -541,7 +564,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": 8 * N_GEN,
                     "d2h_bytes_per_step": 4 * cfg.vocab_size * N_GEN,
                     "path": "ModelRunner prefill/decode_step over the C ABI, host logits + host argmax"},
-            "gpu_launches": int(launches), "roofline": roof, "roofline_large_shapes": roof_large, "cpu_baseline": cpu,
+            "gpu_launches": int(launches), "roofline": roof, "roofline_large_shapes": roof_large, "reference_cuda_kernel": ref_kernel,
+            "cpu_baseline": cpu,
             "clocks": clocks, "tp": tp_obj,
         }
         print(json.dumps(line), flush=True)

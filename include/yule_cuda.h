@@ -158,6 +158,22 @@ int32_t yule_cuda_quantized_matmul(yule_cuda_ctx *ctx, yule_buffer weights, yule
                                    yule_buffer output, uint32_t n_rows, uint32_t n_cols,
                                    uint32_t gguf_type);
 
+/* ── sampling: Sampler::sample_with_history (yule-infer/src/sampler.rs:17-136) on the device ── */
+typedef struct yule_sampling_params { /* SamplingParams, yule-infer/src/lib.rs:65-84 */
+    float temperature;        /* <= 0 or 1: no scaling (sampler.rs:41) */
+    float top_p;              /* >= 1: off */
+    uint32_t top_k;           /* 0 or >= n: off; keeps the probabilities >= sorted[k] of the descending order */
+    float repetition_penalty; /* 1: off; applied once per earlier occurrence of a token */
+    float min_p;              /* <= 0: off */
+} yule_sampling_params;
+/* One pick from `n` logits held in a device buffer.  previous_tokens (n_previous words, device buffer; ignored
+ * when n_previous is 0) is the token list the repetition penalty looks at.  random_value in [0, 1) takes the
+ * place of the reference's CSPRNG draw (sampler.rs:212-220), so a call is reproducible.  The steps and their
+ * order are the reference's; sums are formed as trees instead of left to right, which can move a pick only when
+ * random_value lies within rounding distance of a boundary of the cumulative distribution. */
+int32_t yule_cuda_sample(yule_cuda_ctx *ctx, yule_buffer logits, uint32_t n, const yule_sampling_params *params,
+                         yule_buffer previous_tokens, uint32_t n_previous, float random_value, uint32_t *out_token);
+
 /* ── additive entry points (not trait methods; each equals a sequence of
  *    trait calls, so the plain trait stays sufficient) ──────────────────── */
 
@@ -306,6 +322,11 @@ int32_t yule_cuda_runner_position(yule_cuda_runner *runner, uint32_t *out_pos);
 int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *runner, const uint32_t *prompt,
                                          uint32_t n_prompt, uint32_t n_generate,
                                          uint32_t *out_tokens);
+/* Layout of a rank's exchange region under tensor parallelism, in floats: out_offsets[0..3] the gathered
+ * attention output / hidden / gate / logits vectors, [4..6] the (value, epoch) pair copies of hidden / gate /
+ * attention output, [7] the total.  Host arithmetic only (no device needed).  No counterpart in the reference,
+ * which has no multi-device path. */
+int32_t yule_cuda_tp_exchange_layout(const yule_runner_config *cfg, uint64_t out_offsets[8]);
 /* Batched decode: `batch` independent sequences, one new token each per call, every sequence with its own
  * KV caches and position (all start at 0; reset_batch rewinds them).  Per sequence the result is that of
  * decode_step on a runner of its own (the reference serves one sequence per ModelRunner,
@@ -319,6 +340,15 @@ int32_t yule_cuda_runner_reset_batch(yule_cuda_runner *runner);
  * n_prompt - 1 + g (ties to the highest index, sampler.rs:150-163). */
 int32_t yule_cuda_runner_generate_greedy_batch(yule_cuda_runner *runner, const uint32_t *prompts, uint32_t batch,
                                                uint32_t n_prompt, uint32_t n_generate, uint32_t *out_tokens);
+/* Sampled generation: as generate_greedy, but every pick after the prompt is made by the device sampler
+ * (yule_cuda_sample's arithmetic) over all tokens so far, prompt included (yule-infer/src/lib.rs:194-204), and fed
+ * back without leaving the device.  The random values come from a counter-based generator seeded with `seed`
+ * (pick g uses value g of the stream), so equal seeds give equal streams. */
+int32_t yule_cuda_runner_generate_sampled(yule_cuda_runner *runner, const uint32_t *prompt, uint32_t n_prompt,
+                                          uint32_t n_generate, const yule_sampling_params *params, uint64_t seed,
+                                          uint32_t *out_tokens);
+/* The random value pick g of a sampled generation uses: a function of (seed, g) only, in [0, 1). */
+float yule_cuda_sampling_random_value(uint64_t seed, uint32_t index);
 /* Device buffers of the runner for layer-by-layer checks: which = 0 hidden,
  * 1 K cache of `layer`, 2 V cache of `layer`, 3 logits. */
 int32_t yule_cuda_runner_buffer(yule_cuda_runner *runner, uint32_t which, uint32_t layer,

@@ -66,6 +66,13 @@ def _load() -> C.CDLL:
     lib.yo_attention.restype = None
     lib.yo_attention_ex.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p] + [C.c_size_t] * 5 + [C.c_float]
     lib.yo_attention_ex.restype = None
+    lib.yo_ct_gte.argtypes = [C.c_float, C.c_float]
+    lib.yo_ct_gte.restype = C.c_float
+    lib.yo_sample_ct.argtypes = [_f32p, C.c_size_t, C.c_float]
+    lib.yo_sample_ct.restype = C.c_uint32
+    lib.yo_sample.argtypes = [_f32p, C.c_size_t, C.c_float, C.c_float, C.c_uint32, C.c_float, C.c_float,
+                              C.POINTER(C.c_uint32), C.c_size_t, C.c_float]
+    lib.yo_sample.restype = C.c_int64
     lib.yo_gelu.argtypes = [C.c_float]
     lib.yo_gelu.restype = C.c_float
     lib.yo_swiglu.argtypes = [_f32p, _f32p, C.c_size_t]
@@ -223,6 +230,25 @@ def attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len, slidi
     lib.yo_attention_ex(_f32(q), _f32(k_cache), _f32(v_cache), _f32(out), _f32(scratch), n_heads,
                         n_kv_heads, head_dim, seq_len, sliding_window, softcap)
     return out
+
+
+def ct_gte(a: float, b: float) -> float:
+    return float(lib.yo_ct_gte(a, b))
+
+
+def sample_ct(probs: np.ndarray, r: float) -> int:
+    probs = np.ascontiguousarray(probs, np.float32)
+    return int(lib.yo_sample_ct(_f32(probs), probs.size, r))
+
+
+def sample(logits: np.ndarray, r: float, temperature: float = 0.7, top_p: float = 0.9, top_k: int = 40,
+           min_p: float = 0.05, repetition_penalty: float = 1.1, previous=()) -> int:
+    """Sampler::sample_with_history with the random value ``r`` given (defaults: SamplingParams::default,
+    yule-infer/src/lib.rs:74-84)."""
+    logits = np.ascontiguousarray(logits, np.float32)
+    prev = np.ascontiguousarray(previous, np.uint32)
+    return int(lib.yo_sample(_f32(logits), logits.size, temperature, top_p, top_k, min_p, repetition_penalty,
+                             prev.ctypes.data_as(C.POINTER(C.c_uint32)), prev.size, r))
 
 
 def gelu(x: float) -> float:

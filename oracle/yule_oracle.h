@@ -134,6 +134,13 @@ float yo_gelu(float x);
  * highest index. */
 uint32_t yo_argmax(const float *v, size_t n);
 
+/* ── sampler (yule-infer/src/sampler.rs), yule_oracle_sampler.c ── */
+float yo_ct_gte(float a, float b);                                  /* sampler.rs:141-147 */
+uint32_t yo_sample_ct(const float *probs, size_t n, float r);      /* sampler.rs:166-183 */
+/* sampler.rs:17-136 with the random value supplied by the caller; -1 on empty logits. */
+int64_t yo_sample(const float *logits, size_t n, float temperature, float top_p, uint32_t top_k, float min_p,
+                  float repetition_penalty, const uint32_t *previous, size_t n_previous, float r);
+
 /* ── whole forward pass: TransformerRunner (model_runner.rs:533-1036) ── */
 typedef struct {
     uint32_t dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, ff_dim, max_seq_len;

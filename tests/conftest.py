@@ -31,6 +31,7 @@ def native_libs():
     build.build_cuda()
     build_oracle.build_oracle()
     build_oracle.build_ref()
+    build_oracle.build_ref_cuda()
     return True
 
 

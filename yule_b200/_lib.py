@@ -24,6 +24,11 @@ class RunnerConfig(C.Structure):
                 ("attn_logit_softcap", f32), ("logit_softcap", f32), ("norm_weight_offset", f32), ("geglu", u32)]
 
 
+class SamplingParams(C.Structure):
+    """``yule_sampling_params`` of include/yule_cuda.h (SamplingParams, yule-infer/src/lib.rs:65-84)."""
+    _fields_ = [("temperature", f32), ("top_p", f32), ("top_k", u32), ("repetition_penalty", f32), ("min_p", f32)]
+
+
 class GgufTensorInfo(C.Structure):
     """``yule_gguf_tensor_info`` of include/yule_cuda.h."""
     _fields_ = [("name", C.c_char_p), ("n_dims", u32), ("shape", u64 * 8), ("gguf_type", u32), ("offset", u64),
@@ -74,6 +79,7 @@ _SIGNATURES = {
     "yule_cuda_tp_unique_id": [C.POINTER(C.c_uint8)],
     "yule_cuda_tp_init": [vp, u32, u32, C.POINTER(C.c_uint8)],
     "yule_cuda_tp_all_gather": [vp, u64, size_t],
+    "yule_cuda_tp_exchange_layout": [C.POINTER(RunnerConfig), C.POINTER(u64)],
     "yule_cuda_runner_create": [vp, C.POINTER(RunnerConfig), C.POINTER(vp)],
     "yule_cuda_runner_destroy": [vp],
     "yule_cuda_runner_set_tensor": [vp, C.c_char_p, u64, u32],
@@ -83,6 +89,8 @@ _SIGNATURES = {
     "yule_cuda_runner_position": [vp, C.POINTER(u32)],
     "yule_cuda_runner_generate_greedy": [vp, C.POINTER(u32), u32, u32, C.POINTER(u32)],
     "yule_cuda_runner_buffer": [vp, u32, u32, C.POINTER(u64)],
+    "yule_cuda_sample": [vp, u64, u32, C.POINTER(SamplingParams), u64, u32, f32, C.POINTER(u32)],
+    "yule_cuda_runner_generate_sampled": [vp, C.POINTER(u32), u32, u32, C.POINTER(SamplingParams), u64, C.POINTER(u32)],
     "yule_cuda_runner_decode_batch": [vp, C.POINTER(u32), u32, C.POINTER(f32)],
     "yule_cuda_runner_reset_batch": [vp],
     "yule_cuda_runner_generate_greedy_batch": [vp, C.POINTER(u32), u32, u32, u32, C.POINTER(u32)],
@@ -98,7 +106,7 @@ _SIGNATURES = {
     "yule_gguf_runner_config": [vp, u32, C.POINTER(RunnerConfig)],
     "yule_cuda_runner_load_gguf": [vp, vp, u32, u32, C.POINTER(vp)],
 }
-_RESTYPES = {"yule_cuda_last_error": C.c_char_p}
+_RESTYPES = {"yule_cuda_last_error": C.c_char_p, "yule_cuda_sampling_random_value": f32}
 
 EXPORTS = tuple(sorted(list(_SIGNATURES) + list(_RESTYPES)))
 
@@ -117,6 +125,8 @@ def cuda_lib() -> C.CDLL:
             fn.restype = i32
         lib.yule_cuda_last_error.argtypes = []
         lib.yule_cuda_last_error.restype = C.c_char_p
+        lib.yule_cuda_sampling_random_value.argtypes = [u64, u32]
+        lib.yule_cuda_sampling_random_value.restype = f32
         _cuda = lib
     return _cuda
 

@@ -156,6 +156,17 @@ class CudaB200Backend:
         give-up path works, which is the expected outcome."""
         _check(self._lib.yule_cuda_selftest_bounded_wait(self._ctx, which, budget_cycles))
 
+    def sample(self, logits: BufferHandle, n: int, random_value: float, *, temperature: float = 0.7, top_p: float = 0.9,
+               top_k: int = 40, repetition_penalty: float = 1.1, min_p: float = 0.05,
+               previous: BufferHandle | None = None, n_previous: int = 0) -> int:
+        """``Sampler::sample_with_history`` (yule-infer/src/sampler.rs:17-136) on the device; defaults are
+        ``SamplingParams::default`` (yule-infer/src/lib.rs:74-84)."""
+        params = _lib.SamplingParams(temperature, top_p, top_k, repetition_penalty, min_p)
+        out = C.c_uint32()
+        _check(self._lib.yule_cuda_sample(self._ctx, logits.id, n, C.byref(params), previous.id if previous else 0,
+                                          n_previous, random_value, C.byref(out)))
+        return out.value
+
     def attn_score(self, q: BufferHandle, k_cache: BufferHandle, scores: BufferHandle, head_dim: int, seq_len: int,
                    head_offset: int, kv_offset: int, kv_stride: int) -> None:
         _check(self._lib.yule_cuda_attn_score(self._ctx, q.id, k_cache.id, scores.id, head_dim, seq_len,

@@ -57,6 +57,21 @@ int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes) {
     return YULE_OK;
 }
 
+int32_t ensure_sampler_scratch(yule_cuda_ctx *ctx, size_t n_floats) {
+    if (ctx->sampler_scratch_floats >= n_floats) return YULE_OK;
+    if (ctx->capturing) return fail(YULE_ERR_INVALID_ARGUMENT, "the sampler scratch cannot grow during graph capture");
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if (ctx->sampler_scratch) ctx->retired_scratch.push_back(ctx->sampler_scratch);
+    ctx->sampler_scratch = nullptr;
+    ctx->sampler_scratch_floats = 0;
+    if (cudaMalloc((void **)&ctx->sampler_scratch, n_floats * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(YULE_ERR_OUT_OF_MEMORY, "cuda allocation of %zu bytes of sampler scratch failed", n_floats * sizeof(float));
+    }
+    ctx->sampler_scratch_floats = n_floats;
+    return YULE_OK;
+}
+
 }  // namespace yule
 
 using namespace yule;
@@ -165,6 +180,7 @@ int32_t yule_cuda_destroy(yule_cuda_ctx *ctx) {
     if (ctx->device_status) cudaFree(ctx->device_status);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     for (void *p : ctx->retired_scratch) cudaFree(p);
+    if (ctx->sampler_scratch) cudaFree(ctx->sampler_scratch);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return YULE_OK;
@@ -778,6 +794,42 @@ int32_t yule_cuda_graph_destroy(yule_cuda_ctx *ctx, uint32_t graph_id) {
         return fail(YULE_ERR_INVALID_ARGUMENT, "unknown graph %u", graph_id);
     cudaGraphExecDestroy(ctx->graphs[graph_id].exec);
     ctx->graphs[graph_id].exec = nullptr;
+    return YULE_OK;
+}
+
+// Sampler::sample_with_history (yule-infer/src/sampler.rs:17-136) on the device.
+int32_t yule_cuda_sample(yule_cuda_ctx *ctx, yule_buffer logits, uint32_t n, const yule_sampling_params *params,
+                         yule_buffer previous_tokens, uint32_t n_previous, float random_value, uint32_t *out_token) {
+    CTX_GUARD(ctx);
+    if (!params || !out_token) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    if (n == 0) return fail(YULE_ERR_INVALID_ARGUMENT, "empty logits");  // sampler.rs:19-21
+    if (!(random_value >= 0.0f && random_value < 1.0f)) return fail(YULE_ERR_INVALID_ARGUMENT, "the random value must lie in [0, 1)");
+    FIND(ctx, logits, L);
+    NEED_BYTES(L, (size_t)n * 4, "sample logits");
+    const uint32_t *prev = nullptr;
+    if (n_previous) {
+        FIND(ctx, previous_tokens, P);
+        NEED_BYTES(P, (size_t)n_previous * 4, "sample previous tokens");
+        prev = (const uint32_t *)P.ptr;
+    }
+    int32_t rc = ensure_sampler_scratch(ctx, 2 * (size_t)n + 4);
+    if (rc) return rc;
+    SampleArgs a;
+    a.logits = (const float *)L.ptr;
+    a.n = n;
+    a.temperature = params->temperature;
+    a.top_p = params->top_p;
+    a.top_k = params->top_k;
+    a.min_p = params->min_p;
+    a.repetition_penalty = params->repetition_penalty;
+    a.previous = prev;
+    a.n_previous = n_previous;
+    a.r = random_value;
+    a.scratch = ctx->sampler_scratch;
+    a.out_token = reinterpret_cast<uint32_t *>(ctx->sampler_scratch + 2 * (size_t)n);
+    LAUNCHED(ctx, launch_sample(a, ctx->stream, &_n));
+    YULE_CUDA_TRY(cudaMemcpyAsync(out_token, a.out_token, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    YULE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     return YULE_OK;
 }
 

@@ -109,6 +109,9 @@ struct yule_cuda_ctx {
     // activation tiles of the tensor-core GEMM (qgemm_tc.cu), grown on demand
     void *gemm_scratch = nullptr;
     size_t gemm_scratch_bytes = 0;
+    // scratch of the device sampler (sampler.cu): probabilities and occurrence counts, plus one word for the pick
+    float *sampler_scratch = nullptr;
+    size_t sampler_scratch_floats = 0;
     // Scratch blocks that were outgrown.  A CUDA graph captured earlier (the runner's steps, a caller's batch)
     // may still replay into them, so they are kept until the context is destroyed instead of being freed.
     std::vector<void *> retired_scratch;
@@ -223,6 +226,10 @@ struct QmvArgs {
     long long wait_cycles = kDefaultWaitCycles;
 };
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
+// Q8_0 / Q4_0 on the tensor pipe from a shared-memory ring (qmv_q8q4_ring.cu): n_cols a multiple of 256, weights and
+// activations 16-byte aligned, one activation vector.
+bool q8q4_ring_supported(const QmvArgs &a);
+cudaError_t launch_q8q4_ring(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches);
 
 // Quantised GEMM on tcgen05 for eight or more activation rows (qgemm_tc.cu): an activation
 // re-layout kernel followed by the persistent GEMM.  `scratch` holds qgemm_scratch_bytes().
@@ -316,6 +323,7 @@ void tp_destroy(yule_cuda_ctx *ctx);
 // Peer-memory exchange: the same all-gather as stores into every peer's mapped buffer plus epoch flags.
 int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base);
 bool tp_has_exchange(const yule_cuda_ctx *ctx);
+int32_t tp_release_exchange(yule_cuda_ctx *ctx);  // collective over the ranks; called when a tensor-parallel runner is destroyed
 // Fill the producer / consumer half of a TpFuse for exchange `index` of a gathered vector whose pair buffer
 // starts at pair_offset_floats inside the exchange region (2 floats per element, rank r's slice at element
 // r·per_rank).
@@ -440,5 +448,22 @@ cudaError_t launch_rope_kv_write(float *q, const float *k_tmp, const float *v_tm
 cudaError_t launch_argmax(const float *v, uint32_t n, uint32_t *state, uint32_t *history, cudaStream_t s,
                           uint64_t *launches, bool pdl = false);
 cudaError_t launch_fill_bytes(void *p, size_t n, int value, cudaStream_t s, uint64_t *launches);
+
+// Token sampler on the device (sampler.cu; yule-infer/src/sampler.rs:17-136).
+struct SampleArgs {
+    const float *logits = nullptr;
+    uint32_t n = 0;
+    float temperature = 0.7f, top_p = 0.9f, min_p = 0.05f, repetition_penalty = 1.1f;  // SamplingParams::default
+    uint32_t top_k = 40;
+    const uint32_t *previous = nullptr;  // tokens seen so far, device memory
+    uint32_t n_previous = 0;
+    float r = 0.f;                       // uniform random value in [0, 1)
+    float *scratch = nullptr;            // 2 * n floats
+    uint32_t *out_token = nullptr;       // device word that receives the pick
+    uint32_t *append_to = nullptr;       // optional: the pick also goes to append_to[n_previous]
+    uint32_t *feed_state = nullptr;      // optional: the pick also goes to feed_state[0]
+};
+cudaError_t launch_sample(const SampleArgs &a, cudaStream_t s, uint64_t *launches);
+int32_t ensure_sampler_scratch(yule_cuda_ctx *ctx, size_t n_floats);
 
 }  // namespace yule

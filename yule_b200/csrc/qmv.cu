@@ -603,6 +603,9 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         if (const char *k = knob("YULE_QMV_RING")) ring = atoi(k) != 0;
         return ring ? launch_q6k_mma(f, sm_count, s, launches) : launch_q6k_stream(f, sm_count, s, launches);
     }
+    // Q8_0 / Q4_0, one vector, 256-column multiples: the tensor-pipe ring kernel (YULE_QMV_Q8Q4_RING=0: the SIMT kernel)
+    if (q8q4_ring_supported(a) && !(knob("YULE_QMV_Q8Q4_RING") && atoi(knob("YULE_QMV_Q8Q4_RING")) == 0))
+        return launch_q8q4_ring(a, sm_count, s, launches);
     if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;
     uint32_t done = 0;
     while (done < a.batch) {

@@ -87,11 +87,14 @@ struct yule_cuda_runner {
     cudaGraphExec_t bd_graph = nullptr;
     uint32_t bd_graph_kernels = 0;
 
+    uint32_t *d_seq = nullptr;  // sampled generation: every token of the sequence so far (prompt and picks)
+
     uint32_t pos = 0;
     bool fused = false;
     bool pdl = true;  // programmatic dependent launch between the kernels of the graph
     uint32_t graph_kernels = 0;  // kernels replayed per graph launch
     bool finalized = false;
+    bool created = false;  // yule_cuda_runner_create ran to its end
     bool have_next_token = false;  // d_state[0] holds the greedy continuation
     cudaGraphExec_t graph_exec = nullptr;
 };
@@ -1048,6 +1051,24 @@ int32_t read_logits(yule_cuda_runner *r, float *logits_out) {
 
 extern "C" {
 
+// Offsets (in floats) inside a rank's exchange region of the tensor-parallel runner: the four gathered
+// activation vectors, then their (value, epoch) pair copies (two floats per element, 16-byte aligned), then the
+// total.  Rank r's slice of a gathered vector of n elements is [r·n/world, (r+1)·n/world) of it, of a pair copy
+// twice that; the layout itself does not depend on the world size.
+int32_t yule_cuda_tp_exchange_layout(const yule_runner_config *cfg, uint64_t out_offsets[8]) {
+    if (!cfg || !out_offsets) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    const uint64_t qdim = (uint64_t)cfg->n_heads * cfg->head_dim;
+    out_offsets[0] = 0;                                                   // attention output, qdim
+    out_offsets[1] = out_offsets[0] + qdim;                               // hidden, dim
+    out_offsets[2] = out_offsets[1] + cfg->dim;                           // gate (SwiGLU output), ff_dim
+    out_offsets[3] = out_offsets[2] + cfg->ff_dim;                        // logits, vocab_size
+    out_offsets[4] = (out_offsets[3] + cfg->vocab_size + 3) & ~(uint64_t)3;  // pairs of hidden, 2·dim
+    out_offsets[5] = out_offsets[4] + 2 * (uint64_t)cfg->dim;             // pairs of gate, 2·ff_dim
+    out_offsets[6] = out_offsets[5] + 2 * (uint64_t)cfg->ff_dim;          // pairs of the attention output, 2·qdim
+    out_offsets[7] = out_offsets[6] + 2 * qdim;                           // floats in all
+    return YULE_OK;
+}
+
 int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cfg, yule_cuda_runner **out_runner) {
     if (!ctx || !cfg || !out_runner) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
     *out_runner = nullptr;
@@ -1083,15 +1104,17 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     const bool use_xchg = tpw > 1 && !(knob("YULE_TP_NCCL") && atoi(knob("YULE_TP_NCCL")) != 0);
     if (use_xchg) {
         // gathered activations live in one region that every peer maps
-        r->x_attn_out = 0;
-        r->x_hidden = r->x_attn_out + qdim;
-        r->x_gate = r->x_hidden + c.dim;
-        r->x_logits = r->x_gate + c.ff_dim;
-        r->x_pair_hidden = (r->x_logits + c.vocab_size + 3) & ~(size_t)3;  // 16-byte aligned
-        r->x_pair_gate = r->x_pair_hidden + 2 * (size_t)c.dim;
-        r->x_pair_attn = r->x_pair_gate + 2 * (size_t)c.ff_dim;
+        uint64_t lay[8];
+        yule_cuda_tp_exchange_layout(&c, lay);
+        r->x_attn_out = lay[0];
+        r->x_hidden = lay[1];
+        r->x_gate = lay[2];
+        r->x_logits = lay[3];
+        r->x_pair_hidden = lay[4];
+        r->x_pair_gate = lay[5];
+        r->x_pair_attn = lay[6];
         float *base = nullptr;
-        rc = tp_setup_exchange(ctx, r->x_pair_attn + 2 * (size_t)qdim, &base);
+        rc = tp_setup_exchange(ctx, (size_t)lay[7], &base);
         if (rc == YULE_OK) {
             r->xchg = true;
             r->attn_out = base + r->x_attn_out;
@@ -1163,6 +1186,7 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         yule_cuda_runner_destroy(r);
         return rc;
     }
+    r->created = true;
     *out_runner = r;
     return YULE_OK;
 }
@@ -1175,6 +1199,9 @@ int32_t yule_cuda_runner_destroy(yule_cuda_runner *r) {
     if (r->bd_graph) cudaGraphExecDestroy(r->bd_graph);
     if (r->h_pinned) cudaFreeHost(r->h_pinned);
     for (yule_buffer h : r->owned) yule_cuda_free(r->ctx, h);
+    // collective: every rank destroys its runner at the same point (a runner whose creation failed half-way leaves
+    // the region to the context, which frees it without a rendezvous)
+    if (r->xchg && r->created) tp_release_exchange(r->ctx);
     delete r;
     return YULE_OK;
 }
@@ -1299,6 +1326,69 @@ int32_t yule_cuda_runner_generate_greedy(yule_cuda_runner *r, const uint32_t *pr
     }
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
     return r->xchg ? yule_cuda_synchronize(r->ctx) : YULE_OK;  // reports a peer that never arrived
+}
+
+float yule_cuda_sampling_random_value(uint64_t seed, uint32_t index) {
+    // SplitMix64 of (seed, index); the top 24 bits over 2^24, the mapping of the reference's csprng_f32
+    // (yule-infer/src/sampler.rs:212-220)
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull * ((uint64_t)index + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (float)(uint32_t)(z >> 40) / 16777216.0f;
+}
+
+int32_t yule_cuda_runner_generate_sampled(yule_cuda_runner *r, const uint32_t *prompt, uint32_t n_prompt, uint32_t n_generate,
+                                          const yule_sampling_params *params, uint64_t seed, uint32_t *out_tokens) {
+    if (!r || !prompt || !params || (n_generate && !out_tokens)) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    if (n_prompt == 0) return fail(YULE_ERR_INVALID_ARGUMENT, "sampled generation needs a prompt");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    if (!is_fused(r)) return fail(YULE_ERR_INVALID_ARGUMENT, "generate_sampled needs a runner created with fused = 1");
+    if (r->pos != 0) return fail(YULE_ERR_INVALID_ARGUMENT, "generate_sampled starts a sequence: reset the runner first");
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    if ((rc = ensure_graph(r))) return rc;
+    const yule_runner_config &c = r->cfg;
+    if ((uint64_t)n_prompt + n_generate > c.max_seq_len) return fail(YULE_ERR_CONTEXT_LENGTH, "context length exceeded");
+    if ((rc = ensure_sampler_scratch(r->ctx, 2 * (size_t)c.vocab_size + 4))) return rc;
+    if (!r->d_seq) {
+        float *p = nullptr;
+        if ((rc = alloc_f32(r, (size_t)c.max_seq_len + 1, &p))) return rc;
+        r->d_seq = (uint32_t *)p;
+    }
+    cudaStream_t s = r->ctx->stream;
+    // the prompt: KV caches and the logits after its last token, exactly as generate_greedy feeds it
+    uint32_t dummy = 0;
+    if ((rc = yule_cuda_runner_generate_greedy(r, prompt, n_prompt, 0, &dummy))) return rc;
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->d_seq, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s));
+    uint64_t launches = 0;
+    cudaError_t e = cudaSuccess;
+    for (uint32_t g = 0; g < n_generate && e == cudaSuccess; g++) {
+        SampleArgs a;
+        a.logits = r->logits;
+        a.n = c.vocab_size;
+        a.temperature = params->temperature;
+        a.top_p = params->top_p;
+        a.top_k = params->top_k;
+        a.min_p = params->min_p;
+        a.repetition_penalty = params->repetition_penalty;
+        a.previous = r->d_seq;
+        a.n_previous = n_prompt + g;
+        a.r = yule_cuda_sampling_random_value(seed, g);
+        a.scratch = r->ctx->sampler_scratch;
+        a.out_token = reinterpret_cast<uint32_t *>(r->ctx->sampler_scratch + 2 * (size_t)c.vocab_size);
+        a.append_to = r->d_seq;
+        a.feed_state = r->d_state;  // the token step reads its input token here
+        e = launch_sample(a, s, &launches);
+        if (e == cudaSuccess) e = cudaGraphLaunch(r->graph_exec, s);
+    }
+    r->ctx->launches.fetch_add(launches + (uint64_t)graph_kernels(r) * n_generate);
+    if (e != cudaSuccess) return fail_cuda(e, "sampled generation");
+    r->pos += n_generate;
+    if (n_generate)
+        YULE_CUDA_TRY(cudaMemcpyAsync(out_tokens, r->d_seq + n_prompt, (size_t)n_generate * 4, cudaMemcpyDeviceToHost, s));
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    return r->xchg ? yule_cuda_synchronize(r->ctx) : YULE_OK;
 }
 
 int32_t yule_cuda_runner_reset_batch(yule_cuda_runner *r) {

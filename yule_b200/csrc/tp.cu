@@ -190,6 +190,28 @@ int32_t tp_setup_exchange(yule_cuda_ctx *ctx, size_t n_floats, float **out_base)
     return YULE_OK;
 }
 
+// Gives the exchange region back when the runner that used it goes away, so that another runner can be created on
+// the same context.  Collective: every rank unmaps its peers' regions, all ranks meet (a one-byte all-gather on
+// the communicator), and only then does each free its own — a region must not be freed while a peer still has it
+// mapped.  The caller has synchronised its stream, so nothing of this rank still touches the regions.
+int32_t tp_release_exchange(yule_cuda_ctx *ctx) {
+    if (!tp_has_exchange(ctx)) return YULE_OK;
+    float *mine = ctx->tp_peer_base[ctx->tp_rank];
+    for (uint32_t p = 0; p < (uint32_t)kMaxRanks; p++) {
+        if (ctx->tp_peer_base[p] && p != ctx->tp_rank) cudaIpcCloseMemHandle(ctx->tp_peer_base[p]);
+        ctx->tp_peer_base[p] = nullptr;
+    }
+    unsigned char *d = nullptr;
+    if (ctx->tp_comm && cudaMalloc((void **)&d, ctx->tp_world) == cudaSuccess) {
+        g_nccl.AllGather(d + ctx->tp_rank, d, 1, /*ncclChar*/ 0, ctx->tp_comm, ctx->stream);
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(d);
+    }
+    cudaFree(mine);
+    ctx->tp_flag_offset = ctx->tp_xchg_floats = 0;
+    return YULE_OK;
+}
+
 void tp_fuse_push(const yule_cuda_ctx *ctx, size_t pair_offset_floats, uint32_t per_rank, const uint32_t *tick,
                   uint32_t epochs_per_tick, uint32_t index, TpFuse *f) {
     f->world = ctx->tp_world;

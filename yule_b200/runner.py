@@ -137,6 +137,22 @@ class CudaTransformerRunner:
             out.ctypes.data_as(C.POINTER(C.c_uint32))))
         return out[:n_generate]
 
+    def generate_sampled(self, prompt, n_generate: int, seed: int, *, temperature: float = 0.7, top_p: float = 0.9,
+                         top_k: int = 40, repetition_penalty: float = 1.1, min_p: float = 0.05) -> np.ndarray:
+        """Feed ``prompt`` (the runner must be at position 0), then emit ``n_generate`` tokens picked by the
+        device sampler; pick ``g`` uses ``random_value(seed, g)``."""
+        toks = np.ascontiguousarray(prompt, dtype=np.uint32)
+        out = np.empty(max(n_generate, 1), np.uint32)
+        params = _lib.SamplingParams(temperature, top_p, top_k, repetition_penalty, min_p)
+        _check(self._lib.yule_cuda_runner_generate_sampled(
+            self._r, toks.ctypes.data_as(C.POINTER(C.c_uint32)), toks.size, n_generate, C.byref(params), seed,
+            out.ctypes.data_as(C.POINTER(C.c_uint32))))
+        return out[:n_generate]
+
+    @staticmethod
+    def random_value(seed: int, index: int) -> float:
+        return float(_lib.cuda_lib().yule_cuda_sampling_random_value(seed, index))
+
     # ── batched decode: independent sequences advancing together ───────────────────────────
     def decode_batch(self, tokens) -> np.ndarray:
         """One new token for each of ``len(tokens)`` sequences (each with its own KV caches and position);
