@@ -374,7 +374,8 @@ def measure_tp(args, rank: int, world: int, local_rank: int, dist, peaks) -> dic
             out["tp_check"] = {"world": 1, "note": "the one-GPU run is the reference of the check"}
         del w_loc
         # ── timing: the 80-layer model ────────────────────────────────────────────────────────────
-        cfg = full if not args.small else dataclasses.replace(full, n_layers=4)
+        # 1024 positions suffice for the prompt + generated tokens and bound the KV caches of the 32-sequence batch
+        cfg = dataclasses.replace(full, max_seq_len=1024) if not args.small else dataclasses.replace(full, n_layers=4, max_seq_len=256)
         one_layer = synth.synthetic_model(dataclasses.replace(cfg, n_layers=1), seed=70, linear=DType.Q4_K, rank=rank, world=world)
         weights = {}
         for name, val in one_layer.items():
@@ -422,6 +423,28 @@ def measure_tp(args, rank: int, world: int, local_rank: int, dist, peaks) -> dic
                     "frac_of_peak_per_gpu": round(gbs / float(peaks["hbm_gbs"]), 4),
                     "dominant_kernel": "qmv_q4k_mma_kernel (Q4_K matvec, about 95 % of the token step; attention and the "
                                        "logits exchange are the rest)"})
+        # ── configs[4] batch 32: 32 independent sequences decoded together, every linear one GEMM per step ──
+        nb, bp, bg = (8, 4, 4) if args.small else (32, args.tp_prompt, args.tp_gen // 2)
+        prompts = synth.tokens(17, nb * bp, cfg.vocab_size).reshape(nb, bp)
+        run.generate_greedy_batch(prompts, bg)  # warm-up: allocations, graph capture
+        tpb.synchronize()
+        tpb.event_reset()
+        if dist is not None:
+            dist.barrier()
+        e0 = tpb.event_record()
+        run.generate_greedy_batch(prompts, bg)
+        e1 = tpb.event_record()
+        b_ms = gather_max(tpb.event_elapsed_ms(e0, e1))
+        steps = bp + bg
+        step_ms = b_ms / steps
+        kv_bytes = 2 * cfg.n_layers * nb * (bp + bg // 2) * (cfg.n_kv_heads // world) * cfg.head_dim * 4
+        wbytes = decode_bytes_per_token(cfg, weights, 0, tp_world=world)
+        out["batch32"] = {"sequences": nb, "prompt_tokens": bp, "generated_tokens": bg, "ms_per_step": round(step_ms, 4),
+                          "tokens_per_s": round(nb * 1e3 / step_ms, 1),
+                          "weight_bytes_per_step_per_gpu": wbytes,
+                          "achieved_gbs_per_gpu": round((wbytes + kv_bytes) / (step_ms * 1e-3) / 1e9, 1),
+                          "frac_of_peak_per_gpu": round((wbytes + kv_bytes) / (step_ms * 1e-3) / 1e9 / float(peaks["hbm_gbs"]), 4),
+                          "path": "tcgen05 GEMM per linear over the 32 rows (prompt positions are steps of the same kind)"}
         run.close()
     except YuleGpuError as e:
         out["error"] = f"{e.code}: {e.message}"

@@ -34,7 +34,17 @@ prompt = synth.tokens(5, 7, cfg.vocab_size)
 logits = run.prefill(prompt)
 run.reset()
 toks = run.generate_greedy(prompt, 24)
-pickle.dump((logits, toks), open(os.path.join(os.environ["OUT"], f"rank{rank}.pkl"), "wb"))
+extra = None
+if os.environ.get("EXTRA") == "1":
+    # a prompt long enough for the chunked tensor-core prefill, then a batch of sequences decoded together:
+    # both run every linear as one GEMM per rank over its rows and exchange row matrices
+    run.reset()
+    long_prompt = synth.tokens(9, 40, cfg.vocab_size)
+    long_logits = run.prefill(long_prompt)
+    batch_toks = synth.tokens(11, 8 * 3, cfg.vocab_size).reshape(8, 3)
+    batch_logits = [run.decode_batch(batch_toks[:, i]) for i in range(3)]
+    extra = (long_logits, batch_logits)
+pickle.dump((logits, toks, extra), open(os.path.join(os.environ["OUT"], f"rank{rank}.pkl"), "wb"))
 dist.barrier()
 run.close(); b.close()
 dist.destroy_process_group()
@@ -67,6 +77,12 @@ def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path, collecti
     want_logits = single.prefill(prompt)
     single.reset()
     want_toks = single.generate_greedy(prompt, 24)
+    extra = collective == "peer_exchange" and mix in ("q4k", "q4k_q6k")
+    if extra:
+        single.reset()
+        want_long = single.prefill(synth.tokens(9, 40, cfg.vocab_size))
+        batch_toks = synth.tokens(11, 8 * 3, cfg.vocab_size).reshape(8, 3)
+        want_batch = [single.decode_batch(batch_toks[:, i]) for i in range(3)]
     single.close()
 
     with socket.socket() as s:
@@ -78,13 +94,26 @@ def test_two_rank_tensor_parallel_matches_single_gpu(backend, tmp_path, collecti
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", PORT=str(port), OUT=str(tmp_path), YULE_ROOT=ROOT,
                    NCCL_NVLS_ENABLE="0", YULE_TP_NCCL="1" if collective == "nccl" else "0", MIX=mix,
-                   YULE_TP_FUSE="0" if collective == "peer_exchange_unfolded" else "1")
+                   YULE_TP_FUSE="0" if collective == "peer_exchange_unfolded" else "1", EXTRA="1" if extra else "0")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env))
-    for p in procs:
-        assert p.wait(timeout=600) == 0
+    try:
+        for p in procs:
+            assert p.wait(timeout=600) == 0
+    finally:
+        for p in procs:  # a rank that failed leaves its peer waiting: end it
+            if p.poll() is None:
+                p.kill()
     import pickle
     for rank in range(2):
-        logits, toks = pickle.load(open(tmp_path / f"rank{rank}.pkl", "rb"))
+        logits, toks, got_extra = pickle.load(open(tmp_path / f"rank{rank}.pkl", "rb"))
+        if extra:
+            from conftest import REL_TOL
+            from test_gpu_runner import guarded_rel_err as scale_rel_err
+            long_logits, batch_logits = got_extra
+            # same GEMM kernels on row slices: the per-row sums are those of the one-GPU run
+            assert scale_rel_err(long_logits, want_long) <= REL_TOL
+            for got_b, want_b in zip(batch_logits, want_batch):
+                assert scale_rel_err(got_b, want_b) <= REL_TOL
         if mix == "q5k":
             # one GPU folds RMSNorm and SwiGLU into the Q5_K launches, the sharded run uses the separate
             # kernels: same math, different rounding

@@ -575,7 +575,7 @@ cudaError_t launch_argmax_rows(const float *v, uint32_t n, uint32_t batch, uint3
     return cudaGetLastError();
 }
 cudaError_t launch_advance_rows(uint32_t *pos, uint32_t *step, uint32_t batch, cudaStream_t s, uint64_t *launches) {
-    advance_rows_kernel<<<(batch + 255) / 256, 256, 0, s>>>(pos, step, batch);
+    advance_rows_kernel<<<batch ? (batch + 255) / 256 : 1, 256, 0, s>>>(pos, step, batch);  // batch 0: only the counter moves
     *launches += 1;
     return cudaGetLastError();
 }

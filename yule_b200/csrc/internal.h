@@ -331,8 +331,10 @@ void tp_fuse_push(const yule_cuda_ctx *ctx, size_t pair_offset_floats, uint32_t 
                   uint32_t epochs_per_tick, uint32_t index, TpFuse *f);
 void tp_fuse_wait(const yule_cuda_ctx *ctx, size_t pair_offset_floats, const uint32_t *tick, uint32_t epochs_per_tick,
                   uint32_t index, TpFuse *f);
+// n_rows > 1: the buffer is a matrix [n_rows][row_stride] (floats) and each rank owns a column block of every row.
 cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot,
-                        const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches);
+                        const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches,
+                        uint32_t n_rows = 1, size_t row_stride = 0);
 
 // Launch helper shared by every kernel: optional programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>

@@ -19,7 +19,7 @@
 //   d and the power-of-two factors are applied in fp32.  Only the order of fp32 additions differs from the CPU.
 //
 // Schedule: that of qmv_q4k_ring.cu — two groups of 8 warps per CTA, 16-row tiles dealt round-robin, a stage is
-// 16 rows × eight 128-column groups (one per warp), slots refilled by the warp that releases them last, every
+// 16 rows × eight (Q8_0) or sixteen (Q4_0) 128-column groups (one or two per warp), slots refilled by the warp that releases them last, every
 // wait bounded.  Activation staging is per group (each warp converts the columns it multiplies).
 
 #include <cuda_fp16.h>
@@ -34,7 +34,8 @@ constexpr int kWarps = 8;
 constexpr int kGroups = 2;
 constexpr int kThreadsCta = kGroups * kWarps * 32;
 constexpr int kStageRows = 16;
-constexpr int kStageSgs = kWarps;  // 128-column groups per row in a stage
+// 128-column groups per warp and stage: one of Q8_0 (136 bytes per row), two of Q4_0 (72 bytes per row), so that a
+// stage row is about 1.1 KB in both formats and the per-stage bookkeeping is spread over the same amount of work
 constexpr int kMaxStages = 6;      // per group
 constexpr size_t kHalfSmSmem = 115712;
 constexpr size_t kFullSmSmem = 227 * 1024;
@@ -43,8 +44,10 @@ template <bool Q8>
 struct Fmt {
     static constexpr uint32_t kBlockBytes = Q8 ? 34 : 18;
     static constexpr uint32_t kSgBytes = 4 * kBlockBytes;                  // 136 / 72
-    static constexpr uint32_t kRowPitch = kStageSgs * kSgBytes + 16;       // 1104 / 592
-    static constexpr uint32_t kStageBytes = kStageRows * kRowPitch;        // 17 664 / 9 472
+    static constexpr int kSgsPerWarp = Q8 ? 1 : 2;
+    static constexpr uint32_t kStageSgs = kWarps * kSgsPerWarp;            // 8 / 16 groups per stage row
+    static constexpr uint32_t kRowPitch = kStageSgs * kSgBytes + 16;       // 1104 / 1168
+    static constexpr uint32_t kStageBytes = kStageRows * kRowPitch;        // 17 664 / 18 688
     static constexpr int kWords = Q8 ? 8 : 4;                              // 32-bit words of quants per block
 };
 
@@ -259,8 +262,8 @@ __device__ __forceinline__ void issue_stage(const RingParams &p, uint32_t tile, 
     const uint32_t row0 = tile * kStageRows;
     const uint32_t left = p.n_rows - row0;
     const uint32_t rows = left < (uint32_t)kStageRows ? left : (uint32_t)kStageRows;
-    const uint32_t sg0 = chunk * kStageSgs;
-    const uint32_t nsg = n_sg - sg0 < (uint32_t)kStageSgs ? n_sg - sg0 : (uint32_t)kStageSgs;
+    const uint32_t sg0 = chunk * F::kStageSgs;
+    const uint32_t nsg = n_sg - sg0 < F::kStageSgs ? n_sg - sg0 : F::kStageSgs;
     const uint32_t bytes = nsg * F::kSgBytes;  // a multiple of 16: the group count of a chunk is even
     if (lane == 0) mbar_arrive_expect_tx(bar, rows * bytes);
     __syncwarp();
@@ -395,12 +398,16 @@ qmv_q8q4_ring_kernel(const __grid_constant__ RingParams p) {
     for (uint32_t n = 0; n < total; n++) {
         const uint32_t bar = bar0 + 8 * slot;
         if (!ring_wait(bar, phase, p.status, p.wait_cycles)) return;  // all eight warps of the group wait on the same copy
-        const uint32_t sg0 = cc * kStageSgs;
-        const uint32_t nsg = n_sg - sg0 < (uint32_t)kStageSgs ? n_sg - sg0 : (uint32_t)kStageSgs;
-        if ((uint32_t)wid < nsg) {
-            const uint32_t s = sg0 + wid;
-            const unsigned char *r0 = ring + (size_t)slot * F::kStageBytes + (uint32_t)g * F::kRowPitch + (uint32_t)wid * F::kSgBytes;
-            consume_sg<Q8>(r0, t, b_base + (size_t)s * b_sg, b_run, sf_base + (size_t)s * sf_sg, u, acc0, acc1);
+        const uint32_t sg0 = cc * F::kStageSgs;
+        const uint32_t nsg = n_sg - sg0 < F::kStageSgs ? n_sg - sg0 : F::kStageSgs;
+#pragma unroll
+        for (int j = 0; j < F::kSgsPerWarp; j++) {
+            const uint32_t local = (uint32_t)wid + (uint32_t)kWarps * j;  // groups ≡ wid (mod 8): the ones this warp staged x for
+            if (local < nsg) {
+                const uint32_t s = sg0 + local;
+                const unsigned char *r0 = ring + (size_t)slot * F::kStageBytes + (uint32_t)g * F::kRowPitch + local * F::kSgBytes;
+                consume_sg<Q8>(r0, t, b_base + (size_t)s * b_sg, b_run, sf_base + (size_t)s * sf_sg, u, acc0, acc1);
+            }
         }
         if (n + S < total) {
             __syncwarp();
@@ -474,7 +481,7 @@ cudaError_t launch_variant(const QmvArgs &a, int sm_count, cudaStream_t s) {
     p.wait_cycles = a.wait_cycles;
     p.late_wait = (a.pdl && a.late_wait) ? 1u : 0u;
     const uint32_t n_sg = a.n_cols / 128;
-    p.chunks = (n_sg + kStageSgs - 1) / kStageSgs;
+    p.chunks = (n_sg + F::kStageSgs - 1) / F::kStageSgs;
     uint32_t max_ctas = 2u * (uint32_t)sm_count;
     if (const char *k = knob("YULE_QMV_RING_CTAS")) max_ctas = (uint32_t)atoi(k) > 0 ? (uint32_t)atoi(k) : max_ctas;
     uint32_t grid = (p.n_tiles + kGroups - 1) / kGroups;

@@ -87,6 +87,11 @@ struct yule_cuda_runner {
     cudaGraphExec_t bd_graph = nullptr;
     uint32_t bd_graph_kernels = 0;
 
+    // tensor parallelism of the GEMM-driven paths (chunked prefill, batched decode): the row matrices that are
+    // gathered live in the exchange region (offsets in floats), their exchanges count epochs on a device word
+    size_t xb_x = 0, xb_att = 0, xb_gate = 0, xb_up = 0, xb_logits = 0;
+    uint32_t xb_rows = 0, xb_logit_rows = 0;  // rows those regions were sized for
+    uint32_t *d_btick = nullptr;
     uint32_t *d_seq = nullptr;  // sampled generation: every token of the sequence so far (prompt and picks)
 
     uint32_t pos = 0;
@@ -717,7 +722,8 @@ uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
 bool prefill_batched_ok(const yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
     if (knob("YULE_CUDA_BATCH_PREFILL") && atoi(knob("YULE_CUDA_BATCH_PREFILL")) == 0) return false;
-    if (!r->fused || r->ctx->tp_world > 1 || !r->attn_gqa) return false;
+    if (!r->fused || !r->attn_gqa) return false;
+    if (r->ctx->tp_world > 1 && (!r->xchg || !r->xb_rows)) return false;  // needs the peer exchange with its row matrices
     if (is_variant(r)) return false;  // the chunked path implements the Llama op sequence only
     if (!qgemm_supported(YULE_DTYPE_Q4_K, c.dim, 8) || !qgemm_supported(YULE_DTYPE_Q4_K, c.ff_dim, 8) ||
         !qgemm_supported(YULE_DTYPE_Q4_K, c.n_heads * c.head_dim, 8))
@@ -730,21 +736,35 @@ bool prefill_batched_ok(const yule_cuda_runner *r) {
     return score_bytes <= 96 * 1024;
 }
 
-// Row buffers of the GEMM-driven paths (chunked prefill, batched decode), allocated on first use.
+// Row buffers of the GEMM-driven paths (chunked prefill, batched decode), allocated on first use.  Under tensor
+// parallelism the matrices that are gathered (x, attention output, gate, up) live in the exchange region, which
+// every peer maps; q / k / v hold this rank's heads only.
 int32_t ensure_chunk_buffers(yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
+    const uint32_t N = r->ctx->tp_world > 1 ? r->ctx->tp_world : 1;
     const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
     int32_t rc;
     if (!r->pf_chunk) {
-        const uint32_t C = prefill_chunk_size(r);
+        uint32_t C = prefill_chunk_size(r);
+        if (N > 1 && C > r->xb_rows) C = r->xb_rows;
         r->pf_splits = c.max_seq_len / 1024 < 1 ? 1 : (c.max_seq_len / 1024 > 8 ? 8 : c.max_seq_len / 1024);
-        float *tok_f = nullptr, *tick_f = nullptr;
-        if ((rc = alloc_f32(r, (size_t)C * dim, &r->pf_x)) || (rc = alloc_f32(r, (size_t)C * qdim, &r->pf_q)) ||
-            (rc = alloc_f32(r, (size_t)C * kvdim, &r->pf_k)) || (rc = alloc_f32(r, (size_t)C * kvdim, &r->pf_v)) ||
-            (rc = alloc_f32(r, (size_t)C * qdim, &r->pf_att)) || (rc = alloc_f32(r, (size_t)C * ff, &r->pf_gate)) ||
-            (rc = alloc_f32(r, (size_t)C * ff, &r->pf_up)) || (rc = alloc_f32(r, C, &tok_f)) ||
+        float *tok_f = nullptr, *tick_f = nullptr, *bt = nullptr;
+        if (N > 1) {
+            float *base = r->ctx->tp_peer_base[r->ctx->tp_rank];
+            r->pf_x = base + r->xb_x;
+            r->pf_att = base + r->xb_att;
+            r->pf_gate = base + r->xb_gate;
+            r->pf_up = base + r->xb_up;
+            if ((rc = alloc_f32(r, 4, &bt))) return rc;
+            r->d_btick = (uint32_t *)bt;
+        } else if ((rc = alloc_f32(r, (size_t)C * dim, &r->pf_x)) || (rc = alloc_f32(r, (size_t)C * qdim, &r->pf_att)) ||
+                   (rc = alloc_f32(r, (size_t)C * ff, &r->pf_gate)) || (rc = alloc_f32(r, (size_t)C * ff, &r->pf_up))) {
+            return rc;
+        }
+        if ((rc = alloc_f32(r, (size_t)C * (qdim / N), &r->pf_q)) || (rc = alloc_f32(r, (size_t)C * (kvdim / N), &r->pf_k)) ||
+            (rc = alloc_f32(r, (size_t)C * (kvdim / N), &r->pf_v)) || (rc = alloc_f32(r, C, &tok_f)) ||
             (rc = alloc_f32(r, (size_t)C * c.n_heads, &tick_f)) ||
-            (rc = alloc_f32(r, (size_t)C * attn_scratch_floats(c.n_heads, r->pf_splits, hd) + 4, &r->pf_attn_scratch)))
+            (rc = alloc_f32(r, (size_t)C * attn_scratch_floats(c.n_heads / N, r->pf_splits, hd) + 4, &r->pf_attn_scratch)))
             return rc;
         r->pf_tokens = (uint32_t *)tok_f;
         r->pf_tickets = (uint32_t *)tick_f;  // zero-filled by the allocator; the kernel leaves them at zero
@@ -756,125 +776,29 @@ int32_t ensure_chunk_buffers(yule_cuda_runner *r) {
     return ensure_pinned(r, C);
 }
 
-int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n) {
+// One pass of `m` rows through every layer with one GEMM per linear: the body shared by the chunked prefill
+// (rows = consecutive positions of one sequence) and the batched decode step (rows = the current tokens of
+// `n_live` sequences, each at its own position of its own caches).  Tensor parallelism: every GEMM computes this
+// rank's output rows into its column block of the full-width matrix, which is then exchanged with the peers
+// (row-matrix form of the peer-store exchange; epochs count on d_btick, flag slots 5..7).
+struct RowsPass {
+    uint32_t m = 0;            // rows the GEMMs run over
+    uint32_t n_live = 0;       // rows that carry a token (RoPE, KV write and attention touch only these)
+    const uint32_t *tokens = nullptr;
+    bool batch = false;        // false: prefill at positions pos0 .. pos0 + n_live − 1 of the runner's caches
+    uint32_t pos0 = 0;
+};
+
+cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t *launches) {
     const yule_runner_config &c = r->cfg;
     yule_cuda_ctx *ctx = r->ctx;
     cudaStream_t s = ctx->stream;
+    const uint32_t N = ctx->tp_world > 1 ? ctx->tp_world : 1, R = N > 1 ? ctx->tp_rank : 0;
     const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
+    const uint32_t qdim_l = qdim / N, kvdim_l = kvdim / N, ff_l = ff / N, dim_l = dim / N, vocab_l = c.vocab_size / N;
+    const uint32_t m = ps.m;
     const int sms = ctx->prop.multiProcessorCount;
-    int32_t rc;
-    if ((rc = ensure_chunk_buffers(r))) return rc;
-    const uint32_t C = r->pf_chunk;
-    uint64_t launches = 0;
-    struct Guard {
-        yule_cuda_ctx *ctx;
-        uint64_t *n;
-        ~Guard() { ctx->launches.fetch_add(*n); }
-    } guard{ctx, &launches};
-
-    auto xprep = [&](const float *x, uint32_t cols, uint32_t m, const float *norm_w, const float *gate) {
-        QGemm g;
-        g.type = YULE_DTYPE_Q4_K;
-        g.x = x;
-        g.gate = gate;
-        g.norm_w = norm_w;
-        g.eps = c.norm_eps;
-        g.x_stride = cols;
-        g.n_cols = cols;
-        g.n_tokens = m;
-        g.scratch = ctx->gemm_scratch;
-        return launch_qgemm_xprep(g, s, &launches);
-    };
-    auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, uint32_t m, float *out, const float *residual) {
-        QGemm g;
-        g.w = (const uint8_t *)t.buf.ptr;
-        g.type = t.type;
-        g.out = out;
-        g.residual = residual;
-        g.n_rows = rows;
-        g.n_cols = cols;
-        g.n_tokens = m;
-        g.out_stride = rows;
-        g.scratch = ctx->gemm_scratch;
-        g.status = ctx->device_status;
-        return launch_qgemm_mm(g, sms, s, &launches);
-    };
-#define PF_TRY(expr)                                              \
-    do {                                                          \
-        cudaError_t _e = (expr);                                  \
-        if (_e != cudaSuccess) return fail_cuda(_e, "batched prefill: " #expr); \
-    } while (0)
-
-    for (uint32_t c0 = 0; c0 < n; c0 += C) {
-        const uint32_t m = n - c0 < C ? n - c0 : C, pos0 = r->pos + c0;
-        YULE_CUDA_TRY(cudaStreamSynchronize(s));  // the staging words of the previous chunk may still be in flight
-        for (uint32_t i = 0; i < m; i++) r->h_pinned[i] = tokens[c0 + i];
-        YULE_CUDA_TRY(cudaMemcpyAsync(r->pf_tokens, r->h_pinned, (size_t)m * 4, cudaMemcpyHostToDevice, s));
-        PF_TRY(launch_embed_gather_batch((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, r->pf_tokens, m, r->pf_x,
-                                         s, &launches));
-        for (uint32_t l = 0; l < c.n_layers; l++) {
-            Layer &L = r->layers[l];
-            // attention block: RMSNorm folded into the re-layout, Q/K/V share it
-            PF_TRY(xprep(r->pf_x, dim, m, L.attn_norm_f32, nullptr));
-            PF_TRY(mm(L.attn_q, qdim, dim, m, r->pf_q, nullptr));
-            PF_TRY(mm(L.attn_k, kvdim, dim, m, r->pf_k, nullptr));
-            PF_TRY(mm(L.attn_v, kvdim, dim, m, r->pf_v, nullptr));
-            PF_TRY(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin, pos0, m, hd,
-                                              c.n_heads, c.n_kv_heads, s, &launches));
-            AttnDecode a;
-            a.q = r->pf_q;
-            a.k_cache = L.k_cache;
-            a.v_cache = L.v_cache;
-            a.seq_len = pos0 + 1;  // query z attends to positions [0, pos0 + z]
-            a.out = r->pf_att;
-            a.scratch = r->pf_attn_scratch;
-            a.tickets = r->pf_tickets;
-            a.hd = hd;
-            a.n_heads = c.n_heads;
-            a.n_kv_heads = c.n_kv_heads;
-            a.kv_stride = kvdim;
-            a.n_splits = r->pf_splits;
-            a.max_seq_len = c.max_seq_len;
-            a.min_chunk = kPrefillMinChunk;
-            a.gqa = true;
-            a.n_tokens = m;
-            a.q_stride = qdim;
-            a.out_stride = qdim;
-            PF_TRY(launch_attn_decode(a, s, &launches));
-            PF_TRY(xprep(r->pf_att, qdim, m, nullptr, nullptr));
-            PF_TRY(mm(L.attn_output, dim, qdim, m, r->pf_x, r->pf_x));  // x += Wo · attention
-            // feed-forward block: RMSNorm folded in, gate/up share the re-layout, SwiGLU folded into the next one
-            PF_TRY(xprep(r->pf_x, dim, m, L.ffn_norm_f32, nullptr));
-            PF_TRY(mm(L.ffn_gate, ff, dim, m, r->pf_gate, nullptr));
-            PF_TRY(mm(L.ffn_up, ff, dim, m, r->pf_up, nullptr));
-            PF_TRY(xprep(r->pf_up, ff, m, nullptr, r->pf_gate));
-            PF_TRY(mm(L.ffn_down, dim, ff, m, r->pf_x, r->pf_x));  // x += Wdown · (silu(gate) · up)
-        }
-    }
-#undef PF_TRY
-    r->pos += n;
-    r->have_next_token = false;
-    return YULE_OK;
-}
-
-// ── batched decode ──────────────────────────────────────────────────────────────────────────
-// `batch` independent sequences, one new token each per step.  The reference decodes one sequence at a time
-// (yule-infer/src/lib.rs:169-216 drives ModelRunner::decode_step); per sequence the arithmetic here is the
-// chunked prefill's — every linear one tensor-core GEMM over the rows, so the weights cross HBM once per step
-// instead of once per sequence — with row b at its own position of its own KV caches.
-
-bool batch_decode_ok(const yule_cuda_runner *r) { return prefill_batched_ok(r); }
-
-// Enqueues one step: tokens in bd_tokens, positions in bd_pos (device).  Leaves the logits in bd_logits, the greedy
-// picks in bd_tokens / bd_history, and moves positions and step counter on.
-cudaError_t enqueue_batch_step(yule_cuda_runner *r, uint64_t *launches) {
-    const yule_runner_config &c = r->cfg;
-    yule_cuda_ctx *ctx = r->ctx;
-    cudaStream_t s = ctx->stream;
-    const uint32_t dim = c.dim, hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd, ff = c.ff_dim;
-    const uint32_t B = r->bd_batch, m = r->bd_rows;
-    const int sms = ctx->prop.multiProcessorCount;
-    const size_t cache_stride = (size_t)c.max_seq_len * kvdim;
+    const size_t cache_stride = (size_t)c.max_seq_len * kvdim_l;
     cudaError_t err = cudaSuccess;
     auto ok = [&](cudaError_t e) {
         if (err == cudaSuccess && e != cudaSuccess) err = e;
@@ -892,7 +816,8 @@ cudaError_t enqueue_batch_step(yule_cuda_runner *r, uint64_t *launches) {
         g.scratch = ctx->gemm_scratch;
         ok(launch_qgemm_xprep(g, s, launches));
     };
-    auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, float *out, const float *residual) {
+    // `rows` output rows of this rank, written at `out` with `stride` floats between the rows of the result
+    auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, float *out, uint32_t stride, const float *residual) {
         QGemm g;
         g.w = (const uint8_t *)t.buf.ptr;
         g.type = t.type;
@@ -901,70 +826,150 @@ cudaError_t enqueue_batch_step(yule_cuda_runner *r, uint64_t *launches) {
         g.n_rows = rows;
         g.n_cols = cols;
         g.n_tokens = m;
-        g.out_stride = rows;
+        g.out_stride = stride;
         g.scratch = ctx->gemm_scratch;
         g.status = ctx->device_status;
         ok(launch_qgemm_mm(g, sms, s, launches));
     };
-    ok(launch_embed_gather_batch((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, r->bd_tokens, B, r->pf_x, s, launches));
+    const uint32_t epochs_per_tick = 5 * c.n_layers + 1;
+    uint32_t xchg_index = 0;
+    auto exchange = [&](size_t offset, uint32_t per_rank, uint32_t stride) {
+        if (N > 1) ok(tp_exchange(ctx, offset, per_rank, 5 + xchg_index % 3, r->d_btick, epochs_per_tick, xchg_index, false, launches, m, stride));
+        xchg_index++;
+    };
+    if (N > 1) ok(launch_advance_rows(nullptr, r->d_btick, 0, s, launches));  // a new tick for this pass's exchanges
+    ok(launch_embed_gather_batch((const uint8_t *)r->token_embd.buf.ptr, r->token_embd.type, dim, ps.tokens, ps.n_live, r->pf_x, s, launches));
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
+        // attention block: RMSNorm folded into the re-layout, Q/K/V share it; this rank's heads only
         xprep(r->pf_x, dim, L.attn_norm_f32, nullptr);
-        mm(L.attn_q, qdim, dim, r->pf_q, nullptr);
-        mm(L.attn_k, kvdim, dim, r->pf_k, nullptr);
-        mm(L.attn_v, kvdim, dim, r->pf_v, nullptr);
-        ok(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, r->bd_k[l], r->bd_v[l], r->rope_cos, r->rope_sin, 0, B, hd, c.n_heads,
-                                      c.n_kv_heads, s, launches, r->bd_pos, cache_stride));
+        mm(L.attn_q, qdim_l, dim, r->pf_q, qdim_l, nullptr);
+        mm(L.attn_k, kvdim_l, dim, r->pf_k, kvdim_l, nullptr);
+        mm(L.attn_v, kvdim_l, dim, r->pf_v, kvdim_l, nullptr);
         AttnDecode a;
+        if (ps.batch) {
+            ok(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, r->bd_k[l], r->bd_v[l], r->rope_cos, r->rope_sin, 0, ps.n_live, hd,
+                                          c.n_heads / N, c.n_kv_heads / N, s, launches, r->bd_pos, cache_stride));
+            a.k_cache = r->bd_k[l];
+            a.v_cache = r->bd_v[l];
+            a.pos_ptr = r->bd_pos;
+            a.pos_per_query = true;
+            a.kv_batch_stride = cache_stride;
+        } else {
+            ok(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, L.k_cache, L.v_cache, r->rope_cos, r->rope_sin, ps.pos0, ps.n_live, hd,
+                                          c.n_heads / N, c.n_kv_heads / N, s, launches));
+            a.k_cache = L.k_cache;
+            a.v_cache = L.v_cache;
+            a.seq_len = ps.pos0 + 1;  // query z attends to positions [0, pos0 + z]
+        }
         a.q = r->pf_q;
-        a.k_cache = r->bd_k[l];
-        a.v_cache = r->bd_v[l];
-        a.pos_ptr = r->bd_pos;
-        a.pos_per_query = true;
-        a.kv_batch_stride = cache_stride;
-        a.out = r->pf_att;
+        a.out = r->pf_att + (size_t)R * qdim_l;
         a.scratch = r->pf_attn_scratch;
         a.tickets = r->pf_tickets;
         a.hd = hd;
-        a.n_heads = c.n_heads;
-        a.n_kv_heads = c.n_kv_heads;
-        a.kv_stride = kvdim;
+        a.n_heads = c.n_heads / N;
+        a.n_kv_heads = c.n_kv_heads / N;
+        a.kv_stride = kvdim_l;
         a.n_splits = r->pf_splits;
         a.max_seq_len = c.max_seq_len;
         a.min_chunk = kPrefillMinChunk;
         a.gqa = true;
-        a.n_tokens = B;
-        a.q_stride = qdim;
+        a.n_tokens = ps.n_live;
+        a.q_stride = qdim_l;
         a.out_stride = qdim;
         ok(launch_attn_decode(a, s, launches));
+        exchange(r->xb_att, qdim_l, qdim);
         xprep(r->pf_att, qdim, nullptr, nullptr);
-        mm(L.attn_output, dim, qdim, r->pf_x, r->pf_x);
+        mm(L.attn_output, dim_l, qdim, r->pf_x + (size_t)R * dim_l, dim, r->pf_x + (size_t)R * dim_l);  // x += Wo · attention
+        exchange(r->xb_x, dim_l, dim);
+        // feed-forward block: RMSNorm folded in, gate/up share the re-layout, SwiGLU folded into the next one
         xprep(r->pf_x, dim, L.ffn_norm_f32, nullptr);
-        mm(L.ffn_gate, ff, dim, r->pf_gate, nullptr);
-        mm(L.ffn_up, ff, dim, r->pf_up, nullptr);
+        mm(L.ffn_gate, ff_l, dim, r->pf_gate + (size_t)R * ff_l, ff, nullptr);
+        mm(L.ffn_up, ff_l, dim, r->pf_up + (size_t)R * ff_l, ff, nullptr);
+        exchange(r->xb_gate, ff_l, ff);
+        exchange(r->xb_up, ff_l, ff);
         xprep(r->pf_up, ff, nullptr, r->pf_gate);
-        mm(L.ffn_down, dim, ff, r->pf_x, r->pf_x);
+        mm(L.ffn_down, dim_l, ff, r->pf_x + (size_t)R * dim_l, dim, r->pf_x + (size_t)R * dim_l);  // x += Wdown · (silu(gate) · up)
+        exchange(r->xb_x, dim_l, dim);
     }
-    const Tensor &out_w = r->output.set ? r->output : r->token_embd;
-    xprep(r->pf_x, dim, r->output_norm_f32, nullptr);
-    mm(out_w, c.vocab_size, dim, r->bd_logits, nullptr);
-    ok(launch_argmax_rows(r->bd_logits, c.vocab_size, B, r->bd_tokens, r->bd_pos, r->bd_step, r->bd_history, c.max_seq_len + 1, s, launches));
-    ok(launch_advance_rows(r->bd_pos, r->bd_step, B, s, launches));
+    if (ps.batch) {
+        const Tensor &out_w = r->output.set ? r->output : r->token_embd;
+        xprep(r->pf_x, dim, r->output_norm_f32, nullptr);
+        mm(out_w, vocab_l, dim, r->bd_logits + (size_t)R * vocab_l, c.vocab_size, nullptr);
+        exchange(r->xb_logits, vocab_l, c.vocab_size);
+        ok(launch_argmax_rows(r->bd_logits, c.vocab_size, ps.n_live, r->bd_tokens, r->bd_pos, r->bd_step, r->bd_history, c.max_seq_len + 1, s, launches));
+        ok(launch_advance_rows(r->bd_pos, r->bd_step, ps.n_live, s, launches));
+    }
     return err;
+}
+
+int32_t prefill_batched(yule_cuda_runner *r, const uint32_t *tokens, uint32_t n) {
+    yule_cuda_ctx *ctx = r->ctx;
+    cudaStream_t s = ctx->stream;
+    int32_t rc;
+    if ((rc = ensure_chunk_buffers(r))) return rc;
+    const uint32_t C = r->pf_chunk;
+    uint64_t launches = 0;
+    struct Guard {
+        yule_cuda_ctx *ctx;
+        uint64_t *n;
+        ~Guard() { ctx->launches.fetch_add(*n); }
+    } guard{ctx, &launches};
+    for (uint32_t c0 = 0; c0 < n; c0 += C) {
+        const uint32_t m = n - c0 < C ? n - c0 : C;
+        YULE_CUDA_TRY(cudaStreamSynchronize(s));  // the staging words of the previous chunk may still be in flight
+        for (uint32_t i = 0; i < m; i++) r->h_pinned[i] = tokens[c0 + i];
+        YULE_CUDA_TRY(cudaMemcpyAsync(r->pf_tokens, r->h_pinned, (size_t)m * 4, cudaMemcpyHostToDevice, s));
+        RowsPass ps;
+        ps.m = m;
+        ps.n_live = m;
+        ps.tokens = r->pf_tokens;
+        ps.pos0 = r->pos + c0;
+        cudaError_t e = enqueue_rows_pass(r, ps, &launches);
+        if (e != cudaSuccess) return fail_cuda(e, "batched prefill");
+        // tensor parallelism: a peer that stopped answering is noticed per chunk
+        if (r->xchg && (rc = yule_cuda_synchronize(ctx))) return rc;
+    }
+    r->pos += n;
+    r->have_next_token = false;
+    return YULE_OK;
+}
+
+// ── batched decode ──────────────────────────────────────────────────────────────────────────
+// `batch` independent sequences, one new token each per step.  The reference decodes one sequence at a time
+// (yule-infer/src/lib.rs:169-216 drives ModelRunner::decode_step); per sequence the arithmetic here is the
+// chunked prefill's — every linear one tensor-core GEMM over the rows, so the weights cross HBM once per step
+// instead of once per sequence — with row b at its own position of its own KV caches.
+
+bool batch_decode_ok(const yule_cuda_runner *r) { return prefill_batched_ok(r); }
+
+// Enqueues one step: tokens in bd_tokens, positions in bd_pos (device).  Leaves the logits in bd_logits, the greedy
+// picks in bd_tokens / bd_history, and moves positions and step counter on.
+cudaError_t enqueue_batch_step(yule_cuda_runner *r, uint64_t *launches) {
+    RowsPass ps;
+    ps.m = r->bd_rows;
+    ps.n_live = r->bd_batch;
+    ps.tokens = r->bd_tokens;
+    ps.batch = true;
+    return enqueue_rows_pass(r, ps, launches);
 }
 
 int32_t ensure_batch_state(yule_cuda_runner *r, uint32_t batch) {
     const yule_runner_config &c = r->cfg;
     if (!batch_decode_ok(r))
-        return fail(YULE_ERR_INVALID_ARGUMENT, "batched decode needs a single-GPU runner created with fused = 1, block-quantised "
-                                               "linears with column counts in multiples of 256 and the Llama op sequence");
+        return fail(YULE_ERR_INVALID_ARGUMENT, "batched decode needs a runner created with fused = 1 (under tensor parallelism: with "
+                                               "the peer exchange), block-quantised linears with column counts in multiples of 256 "
+                                               "and the Llama op sequence");
     int32_t rc = ensure_chunk_buffers(r);
     if (rc) return rc;
     if (batch == 0 || batch > r->pf_chunk) return fail(YULE_ERR_INVALID_ARGUMENT, "batch %u outside 1..%u", batch, r->pf_chunk);
     if (r->bd_batch == batch) return YULE_OK;
     if (r->bd_batch) return fail(YULE_ERR_INVALID_ARGUMENT, "this runner decodes batches of %u sequences; %u asked for", r->bd_batch, batch);
-    const uint32_t kvdim = c.n_kv_heads * c.head_dim;
+    const uint32_t tpw = r->ctx->tp_world > 1 ? r->ctx->tp_world : 1;
+    const uint32_t kvdim = c.n_kv_heads * c.head_dim / tpw;  // this rank's KV heads
     const uint32_t rows = batch < 8 ? 8 : batch;  // the GEMM works on at least eight rows; the extra ones stay unused
+    if (tpw > 1 && rows > r->xb_logit_rows)
+        return fail(YULE_ERR_INVALID_ARGUMENT, "tensor-parallel batched decode takes at most %u sequences", r->xb_logit_rows);
     r->bd_k.assign(c.n_layers, nullptr);
     r->bd_v.assign(c.n_layers, nullptr);
     for (uint32_t l = 0; l < c.n_layers; l++)
@@ -972,7 +977,11 @@ int32_t ensure_batch_state(yule_cuda_runner *r, uint32_t batch) {
             (rc = alloc_f32(r, (size_t)batch * c.max_seq_len * kvdim, &r->bd_v[l])))
             return rc;
     float *tok = nullptr, *pos = nullptr, *step = nullptr, *hist = nullptr;
-    if ((rc = alloc_f32(r, (size_t)rows * c.vocab_size, &r->bd_logits)) || (rc = alloc_f32(r, rows, &tok)) ||
+    if (tpw > 1)
+        r->bd_logits = r->ctx->tp_peer_base[r->ctx->tp_rank] + r->xb_logits;  // gathered: lives in the exchange region
+    else if ((rc = alloc_f32(r, (size_t)rows * c.vocab_size, &r->bd_logits)))
+        return rc;
+    if ((rc = alloc_f32(r, rows, &tok)) ||
         (rc = alloc_f32(r, rows, &pos)) || (rc = alloc_f32(r, 4, &step)) ||
         (rc = alloc_f32(r, (size_t)batch * (c.max_seq_len + 1), &hist)))
         return rc;
@@ -1114,7 +1123,24 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         r->x_pair_gate = lay[5];
         r->x_pair_attn = lay[6];
         float *base = nullptr;
-        rc = tp_setup_exchange(ctx, (size_t)lay[7], &base);
+        // behind the vectors of the token step: the row matrices of the GEMM-driven paths (chunked prefill, batched
+        // decode) — x, attention output, gate and up for a chunk of rows, and the logits of a decode batch
+        const uint32_t pf_rows = prefill_chunk_size(r) < 8 ? 8 : prefill_chunk_size(r);
+        const uint32_t logit_rows = 64;
+        size_t at = ((size_t)lay[7] + 3) & ~(size_t)3;
+        r->xb_x = at;
+        at += (size_t)pf_rows * c.dim;
+        r->xb_att = at;
+        at += (size_t)pf_rows * qdim;
+        r->xb_gate = at;
+        at += (size_t)pf_rows * c.ff_dim;
+        r->xb_up = at;
+        at += (size_t)pf_rows * c.ff_dim;
+        r->xb_logits = at;
+        at += (size_t)logit_rows * c.vocab_size;
+        r->xb_rows = pf_rows;
+        r->xb_logit_rows = logit_rows;
+        rc = tp_setup_exchange(ctx, at, &base);
         if (rc == YULE_OK) {
             r->xchg = true;
             r->attn_out = base + r->x_attn_out;

@@ -88,20 +88,24 @@ __device__ __forceinline__ uint32_t *flags_of(float *base, size_t flag_offset_fl
 __global__ void __launch_bounds__(kXchgThreads)
 tp_exchange_kernel(PeerTable peers, size_t buf_offset, uint32_t per_rank, uint32_t rank, uint32_t world,
                    size_t flag_offset, uint32_t slot, const uint32_t *__restrict__ tick, uint32_t epochs_per_tick,
-                   uint32_t epoch_index, int *__restrict__ status, long long wait_cycles) {
+                   uint32_t epoch_index, int *__restrict__ status, long long wait_cycles, uint32_t n_rows, size_t row_stride) {
     yule_pdl_launch_dependents();
     yule_pdl_wait();
     // One epoch per (token, exchange): the token counter only changes in another kernel, so every
     // CTA of every rank computes the same number.
     const uint32_t epoch = *tick * epochs_per_tick + epoch_index + 1u;
     float *mine = peers.base[rank] + buf_offset + (size_t)rank * per_rank;
-    // push this rank's slice into every peer's copy of the buffer
+    // push this rank's slice into every peer's copy of the buffer; with n_rows > 1 the buffer is a matrix
+    // [n_rows][row_stride] and the slice the column block [rank·per_rank, (rank+1)·per_rank) of every row
     const uint32_t n4 = per_rank / 4;
+    const size_t total4 = (size_t)n4 * n_rows;
     for (uint32_t p = 0; p < world; p++) {
         if (p == rank) continue;
-        float4 *dst = reinterpret_cast<float4 *>(peers.base[p] + buf_offset + (size_t)rank * per_rank);
-        const float4 *src = reinterpret_cast<const float4 *>(mine);
-        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+        float *dst_base = peers.base[p] + buf_offset + (size_t)rank * per_rank;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+            const size_t row = i / n4, c4 = i - row * n4;
+            reinterpret_cast<float4 *>(dst_base + row * row_stride)[c4] = reinterpret_cast<const float4 *>(mine + row * row_stride)[c4];
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -137,16 +141,19 @@ tp_exchange_kernel(PeerTable peers, size_t buf_offset, uint32_t per_rank, uint32
 }  // namespace
 
 cudaError_t tp_exchange(yule_cuda_ctx *ctx, size_t buf_offset_floats, uint32_t per_rank, uint32_t slot,
-                        const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches) {
+                        const uint32_t *tick, uint32_t epochs_per_tick, uint32_t epoch_index, bool pdl, uint64_t *launches,
+                        uint32_t n_rows, size_t row_stride) {
     PeerTable pt;
     for (int i = 0; i < kMaxRanks; i++) pt.base[i] = ctx->tp_peer_base[i];
-    uint32_t grid = (per_rank / 4 + kXchgThreads - 1) / kXchgThreads;
-    grid = grid < 1 ? 1 : (grid > 8 ? 8 : grid);
+    // a few CTAs for a vector; a matrix of rows gets one CTA per 16 KB of payload, up to one per SM
+    const size_t total4 = (size_t)(per_rank / 4) * n_rows;
+    size_t want = (total4 + kXchgThreads * 4 - 1) / (kXchgThreads * 4);
+    uint32_t grid = (uint32_t)(want < 1 ? 1 : (n_rows <= 1 ? (want > 8 ? 8 : want) : (want > 148 ? 148 : want)));
     const long long wait_cycles = ctx->wait_cycles;
     *launches += 1;
     return launch_kernel(tp_exchange_kernel, dim3(grid), dim3(kXchgThreads), 0, ctx->stream, pdl, pt, buf_offset_floats,
                          per_rank, ctx->tp_rank, ctx->tp_world, ctx->tp_flag_offset, slot, tick, epochs_per_tick,
-                         epoch_index, ctx->device_status, wait_cycles);
+                         epoch_index, ctx->device_status, wait_cycles, n_rows, row_stride);
 }
 
 // Allocates this rank's exchange region (n_floats of payload + flags), maps every peer's, and
@@ -367,7 +374,7 @@ int32_t yule_cuda_selftest_bounded_wait(yule_cuda_ctx *ctx, uint32_t which, uint
         ctx->tp_world = 2;
         ctx->tp_flag_offset = payload;
         ctx->wait_cycles = budget;
-        e = tp_exchange(ctx, 0, per_rank, 0, tick, 1, 0, false, &launches);
+        e = tp_exchange(ctx, 0, per_rank, 0, tick, 1, 0, false, &launches, 1, 0);
         ctx->tp_peer_base[0] = ctx->tp_peer_base[1] = nullptr;
         ctx->tp_world = 1;
         ctx->tp_flag_offset = 0;
