@@ -487,7 +487,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         cfg, weights, prompt = build_model_70b(rank, world, args.workload)
     else:
         cfg, weights, prompt = build_model(rank, args.linear)
-    runner = CudaTransformerRunner(backend, cfg, weights, fused=True)
+    runner = CudaTransformerRunner(backend, cfg, weights, fused=1 if (tp or args.step == "graph") else 2)
+    step_kind = runner.step_kind
 
     def job():
         """One configs[1] job on the device; returns (prefill ms, decode ms, tokens)."""
@@ -579,7 +580,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
                        {"workload": WORKLOAD_C1.format(linear=args.linear, n_prompt=N_PROMPT, n_gen=N_GEN),
                         "parallelism": f"{world} independent replica(s), one sequence per GPU",
                         "l2": f"weights read per token ({bpt / 1e6:.0f} MB) exceed the 126 MB L2; no flush needed"}),
-            "decode": {"ms_per_token": round(decode_ms / (N_GEN * args.steps), 4),
+            "decode": {"token_step": {1: "fused kernels replayed from a CUDA graph", 2: "one persistent kernel per token"}[step_kind],
+                       "ms_per_token": round(decode_ms / (N_GEN * args.steps), 4),
                        "prefill_tokens_per_s": round(N_PROMPT * args.steps / (prefill_ms * 1e-3), 1),
                        "hbm_bytes_per_token": bpt, "achieved_gbs": round(decode_gbs, 1),
                        "frac_of_peak": round(decode_gbs / float(peaks["hbm_gbs"]), 4),
@@ -611,6 +613,8 @@ def main() -> int:
                          "prompt + 256 tokens.  c4: Llama-3-70B-arch decode (512-token prompt + "
                          "256 tokens).  c3/c4 shard the output rows of every linear over the GPUs (tensor parallelism)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--step", choices=["persistent", "graph"], default="persistent",
+                    help="token step of the configs[1] runner: one persistent kernel (default) or the multi-kernel CUDA graph")
     ap.add_argument("--no-tp", action="store_true", help="leave out the `tp` object (the 70B-arch tensor-parallel decode)")
     ap.add_argument("--tp-prompt", type=int, default=64, help="prompt tokens of the `tp` measurement")
     ap.add_argument("--tp-gen", type=int, default=128, help="generated tokens of the `tp` measurement")

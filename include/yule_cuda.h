@@ -284,7 +284,11 @@ typedef struct {
     float norm_eps, rope_freq_base;
     /* 0: one kernel per reference dispatch (RmsNorm, Qmv, Rope, KV copy,
      *    MultiheadAttn, Add, SiluMul), launched one by one.
-     * 1: fused kernels replayed from a CUDA graph (same arithmetic per row). */
+     * 1: fused kernels replayed from a CUDA graph (same arithmetic per row).
+     * 2: as 1, with the token step as ONE persistent kernel where the model allows it (one GPU, the Llama op
+     *    sequence, Q4_K attn_q/k/v and ffn_gate/up, Q4_K or Q6_K attn_output / ffn_down / output matrix,
+     *    grouped-query head shapes 64 or 128 wide); any other model runs as with 1.
+     *    yule_cuda_runner_step_kind tells which one a runner uses. */
     uint32_t fused;
     /* Architecture variants of the dense path, as RunnerConfig derives them from the file
      * (yule-infer/src/model_runner.rs:417-460); all zero = the Llama default.  The reference's GPU runner drops
@@ -316,6 +320,15 @@ int32_t yule_cuda_runner_decode_step(yule_cuda_runner *runner, uint32_t token, f
 /* ModelRunner::reset (gpu_runner.rs:715-719). */
 int32_t yule_cuda_runner_reset(yule_cuda_runner *runner);
 int32_t yule_cuda_runner_position(yule_cuda_runner *runner, uint32_t *out_pos);
+/* How this runner executes a token step: 0 one kernel per dispatch, 1 fused kernels in a CUDA graph, 2 one
+ * persistent kernel.  Builds the step (weights must be set) so that the answer is final. */
+int32_t yule_cuda_runner_step_kind(yule_cuda_runner *runner, uint32_t *out_kind);
+/* Self-test of the persistent kernel's bounded waits (step kind 2 only): runs the token kernel once with every
+ * consumer expecting epochs that no producer writes, with a budget of budget_cycles (0: the context's).  The
+ * kernel returns normally; the call returns YULE_ERR_DEVICE_STATUS, which is the expected result.  Token and
+ * position are left as they were; the activations and the KV rows of the current position hold garbage
+ * afterwards, so reset the runner before using it again. */
+int32_t yule_cuda_runner_selftest_bounded_wait(yule_cuda_runner *runner, uint64_t budget_cycles);
 /* Greedy generation with the argmax on the device (ties resolve to the highest
  * index, yule-infer/src/sampler.rs:150-163): feeds `prompt`, then emits
  * n_generate tokens into out_tokens.  Only token ids cross the bus. */

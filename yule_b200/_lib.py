@@ -87,6 +87,8 @@ _SIGNATURES = {
     "yule_cuda_runner_decode_step": [vp, u32, C.POINTER(f32)],
     "yule_cuda_runner_reset": [vp],
     "yule_cuda_runner_position": [vp, C.POINTER(u32)],
+    "yule_cuda_runner_step_kind": [vp, C.POINTER(u32)],
+    "yule_cuda_runner_selftest_bounded_wait": [vp, C.c_uint64],
     "yule_cuda_runner_generate_greedy": [vp, C.POINTER(u32), u32, u32, C.POINTER(u32)],
     "yule_cuda_runner_buffer": [vp, u32, u32, C.POINTER(u64)],
     "yule_cuda_sample": [vp, u64, u32, C.POINTER(SamplingParams), u64, u32, f32, C.POINTER(u32)],

@@ -468,4 +468,45 @@ struct SampleArgs {
 cudaError_t launch_sample(const SampleArgs &a, cudaStream_t s, uint64_t *launches);
 int32_t ensure_sampler_scratch(yule_cuda_ctx *ctx, size_t n_floats);
 
+// Tiled 2-D tensor map (qgemm_tc.cu); `out` points to a CUtensorMap (128 bytes, 64-byte aligned).
+cudaError_t encode_tensor_map_2d(const void *base, uint32_t elem_bytes, uint64_t inner, uint64_t n_rows, uint64_t row_stride_bytes,
+                                 uint32_t box_inner, uint32_t box_rows, void *out);
+
+// Persistent decode kernel (decode_mega.cu): the whole token step of a dense Llama-family model in one cooperative
+// launch.  Covers: one GPU, no architecture variant, Q4_K attn_q/k/v and ffn_gate/up, Q4_K or Q6_K (row-planar copy)
+// attn_output / ffn_down / output matrix, grouped-query head shapes that were instantiated.
+struct MegaTensor {
+    const uint8_t *ptr = nullptr;  // raw Q4_K rows, or the row-planar copy of a Q6_K tensor
+    uint32_t type = 0;
+};
+struct MegaLayer {
+    MegaTensor q, k, v, o, gate, up, down;
+    const float *attn_norm = nullptr, *ffn_norm = nullptr;
+    float *k_cache = nullptr, *v_cache = nullptr;
+};
+struct MegaModel {
+    uint32_t dim = 0, head_dim = 0, n_heads = 0, n_kv_heads = 0, ff_dim = 0, vocab = 0, n_layers = 0, max_seq_len = 0;
+    float eps = 0.f;
+    const uint8_t *embd = nullptr;  // token_embd, any block format
+    uint32_t embd_type = 0;
+    MegaTensor output;
+    const float *output_norm = nullptr;
+    std::vector<MegaLayer> layers;
+    const float *rope_cos = nullptr, *rope_sin = nullptr;
+    uint32_t *state = nullptr, *history = nullptr;  // {token, position, tokens so far}; picks by position
+    float *logits = nullptr;
+    int *status = nullptr;
+    long long wait_cycles = kDefaultWaitCycles;
+    int sm_count = 0;
+};
+struct MegaHandle;
+// Bytes of zero-filled device memory the kernel needs for this model, or 0 with the reason when it does not cover it.
+size_t mega_workspace_bytes(const MegaModel &m, std::string *why);
+cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, MegaHandle **out);
+void mega_set_cooperative(MegaHandle *h, bool on);
+void mega_set_wait_cycles(MegaHandle *h, long long cycles);
+cudaError_t mega_launch(const MegaHandle *h, cudaStream_t s, uint64_t *launches);
+cudaError_t mega_launch_selftest(const MegaHandle *h, long long budget, cudaStream_t s, uint64_t *launches);
+void mega_destroy(MegaHandle *h);
+
 }  // namespace yule

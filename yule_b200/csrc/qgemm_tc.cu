@@ -897,6 +897,19 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
 // 2-D view of a Q4_K matrix for the TMA engine: bytes along a row, rows; box = one super-block
 // (144 bytes) of 128 rows.  Rows past the end read as zeros (a block of zeros dequantises to 0).
 cudaError_t encode_weight_map(const uint8_t *w, uint32_t n_rows, uint32_t n_cols, CUtensorMap *out) {
+    const uint64_t row_bytes = (uint64_t)(n_cols / 256) * 144;
+    return encode_tensor_map_2d(w, 1, row_bytes, n_rows, row_bytes, 144, kBM, out);
+}
+
+uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 64 ? 64 : 128); }
+
+}  // namespace
+
+// Tiled 2-D tensor map over rows of `elem_bytes`-sized elements (1 or 8): `inner` elements per row, `n_rows` rows
+// `row_stride_bytes` apart (a multiple of 16; base 16-byte aligned), box of box_inner x box_rows elements, no
+// swizzle, out-of-range elements read as zeros.  `out` is a CUtensorMap.
+cudaError_t encode_tensor_map_2d(const void *base, uint32_t elem_bytes, uint64_t inner, uint64_t n_rows, uint64_t row_stride_bytes,
+                                 uint32_t box_inner, uint32_t box_rows, void *out) {
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -913,20 +926,16 @@ cudaError_t encode_weight_map(const uint8_t *w, uint32_t n_rows, uint32_t n_cols
             encode = reinterpret_cast<EncodeFn>(fn);
         }
     }
-    const cuuint64_t row_bytes = (cuuint64_t)(n_cols / 256) * 144;
-    const cuuint64_t dims[2] = {row_bytes, n_rows};
-    const cuuint64_t strides[1] = {row_bytes};  // bytes between rows (a multiple of 16)
-    const cuuint32_t box[2] = {144, kBM};
+    if (elem_bytes != 1 && elem_bytes != 8) return cudaErrorInvalidValue;
+    const cuuint64_t dims[2] = {inner, n_rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode(static_cast<CUtensorMap *>(out), elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT64, 2,
+                        const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
-
-uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 64 ? 64 : 128); }
-
-}  // namespace
 
 // Q4_K runs on the exact-integer kernel; Q6_K, Q8_0 and Q4_0 on the generic one (YULE_GEMM_GENERIC=1
 // sends Q4_K there too, for comparison).  The activation tiles are laid out per 256 columns.

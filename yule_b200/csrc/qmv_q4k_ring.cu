@@ -35,11 +35,9 @@ namespace yule {
 namespace {
 
 #include "q4k_mma_common.cuh"
+#include "q4k_ring_common.cuh"
+#include "ring_common.cuh"
 
-constexpr int kStageRows = 16;
-constexpr int kStageBlocks = kWarps;                                // super-blocks per row in a stage
-constexpr uint32_t kRowPitch = kStageBlocks * 144 + 16;             // ≡ 16 (mod 128)
-constexpr uint32_t kStageBytes = kStageRows * kRowPitch;            // 18 688
 constexpr int kMaxStages = 6;                                       // per group
 constexpr size_t kHalfSmSmem = 115712;                              // (228 KB − 2 × 1 KB reserved) / 2
 constexpr size_t kFullSmSmem = 227 * 1024;
@@ -114,44 +112,6 @@ __device__ __forceinline__ RingSmem carve_ring(unsigned char *base, uint32_t n_c
     return s;
 }
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait for a stage.  False: the copy did not complete within the budget (status recorded).
-__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, int *status, long long budget) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t it = 1;; it++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 0u && clock64() - t0 > budget) {
-            if (status) atomicCAS(status, 0, kStatusRingTimeout);
-            return false;
-        }
-    }
-}
-// 1-D bulk copy global → shared memory of this CTA, completion counted in bytes on `bar`.
-// src and dst 16-byte aligned, bytes a multiple of 16; the source is this GPU's own memory.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
 // Position in a group's stage sequence: job k (tile first_tile + k·tile_stride), matrix q, chunk c.
 struct Cur {
     uint32_t k, q, c;
@@ -195,54 +155,6 @@ __device__ __forceinline__ void issue_stage(const Q4kRingParams &p, const Cur &u
     __syncwarp();
     if ((uint32_t)lane < rows)
         bulk_g2s(dst + (uint32_t)lane * kRowPitch, p.w[seg] + ((size_t)(row0 + lane) * bpr + blk0) * 144u, bytes, bar);
-}
-
-__device__ __forceinline__ uint32_t word4(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-
-// One super-block of rows g and g+8 (r0, r1: the block's bytes in the ring) times this lane's 64-column
-// group, in the sub-block-per-column formulation of consume_block_subcol — same MMA order, so the same
-// bits — with the nibbles fetched from shared memory 16 bytes at a time, just before they are used.
-__device__ __forceinline__ void consume_block_smem(const unsigned char *r0, const unsigned char *r1, const uint4 *bp,
-                                                   const float *sfp, int u, int t, bool charge_mins, float &acc0, float &acc1) {
-    float dl[4] = {0.f, 0.f, 0.f, 0.f}, dh[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int half = 0; half < 2; half++) {
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(r0 + 16 + 32 * t + 16 * half);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(r1 + 16 + 32 * t + 16 * half);
-#pragma unroll
-        for (int w2 = 0; w2 < 2; w2++) {
-            const int wp = 2 * half + w2;
-            const uint4 bl = bp[wp * 8], bh = bp[32 + wp * 8];
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const uint32_t a = word4(q0, 2 * w2 + e), b = word4(q1, 2 * w2 + e);
-                const uint32_t a8 = a >> 8, b8 = b >> 8;
-                mma_16816(dl, a & 0x000F000Fu, b & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, e ? bl.z : bl.x,
-                          e ? bl.w : bl.y);
-                mma_16816(dh, a & 0x00F000F0u, b & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, e ? bh.z : bh.x,
-                          e ? bh.w : bh.y);
-            }
-        }
-    }
-    const float4 sx = *reinterpret_cast<const float4 *>(sfp);  // Σx of sub-blocks 4u..4u+3
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(r ? r1 : r0);
-        const RowScalesF rs = unpack_scales_f<false>(hdr, u, charge_mins);
-        float a = r ? acc1 : acc0;
-        a = fmaf(rs.sc[0], dl[2 * r + 0], a);
-        a = fmaf(rs.sc[1], dh[2 * r + 0], a);
-        a = fmaf(rs.sc[2], dl[2 * r + 1], a);
-        a = fmaf(rs.sc[3], dh[2 * r + 1], a);
-        float m = rs.mn[0] * sx.x;
-        m = fmaf(rs.mn[1], sx.y, m);
-        m = fmaf(rs.mn[2], sx.z, m);
-        m = fmaf(rs.mn[3], sx.w, m);
-        if (r)
-            acc1 = a - m;
-        else
-            acc0 = a - m;
-    }
 }
 
 __device__ __forceinline__ void ring_group_barrier(int group) {

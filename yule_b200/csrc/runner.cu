@@ -102,6 +102,10 @@ struct yule_cuda_runner {
     bool created = false;  // yule_cuda_runner_create ran to its end
     bool have_next_token = false;  // d_state[0] holds the greedy continuation
     cudaGraphExec_t graph_exec = nullptr;
+    // fused = 2: the token step as one persistent kernel (decode_mega.cu) where the model allows it
+    bool mega_wanted = false, mega_tried = false;
+    MegaHandle *mega = nullptr;
+    std::string mega_why;  // why the persistent kernel does not cover this model (empty when it does)
 };
 
 namespace yule {
@@ -663,24 +667,110 @@ int32_t finalize(yule_cuda_runner *r) {
     return YULE_OK;
 }
 
+// fused = 2: describes the model to the persistent decode kernel.  A model it does not cover keeps the
+// multi-kernel graph (the reason is kept for yule_cuda_runner_token_step_kind).
+int32_t setup_mega(yule_cuda_runner *r) {
+    const yule_runner_config &c = r->cfg;
+    if (is_variant(r)) {
+        r->mega_why = "architecture variant";
+        return YULE_OK;
+    }
+    MegaModel m;
+    m.dim = c.dim;
+    m.head_dim = c.head_dim;
+    m.n_heads = c.n_heads;
+    m.n_kv_heads = c.n_kv_heads;
+    m.ff_dim = c.ff_dim;
+    m.vocab = c.vocab_size;
+    m.n_layers = c.n_layers;
+    m.max_seq_len = c.max_seq_len;
+    m.eps = c.norm_eps;
+    auto tensor = [](const Tensor &t, uint32_t cols) {
+        MegaTensor o;
+        o.type = t.type;
+        // Q6_K travels as its row-planar copy (finalize() built it); a Q6_K tensor without one is not covered
+        o.ptr = t.type == YULE_DTYPE_Q6_K ? (t.buf.planar && t.buf.planar_cols == cols ? (const uint8_t *)t.buf.planar : nullptr)
+                                          : (const uint8_t *)t.buf.ptr;
+        return o;
+    };
+    const uint32_t qdim = c.n_heads * c.head_dim;
+    m.embd = (const uint8_t *)r->token_embd.buf.ptr;
+    m.embd_type = r->token_embd.type;
+    m.output = tensor(r->output.set ? r->output : r->token_embd, c.dim);
+    m.output_norm = r->output_norm_f32;
+    m.layers.resize(c.n_layers);
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        const Layer &L = r->layers[l];
+        MegaLayer &M = m.layers[l];
+        M.q = tensor(L.attn_q, c.dim);
+        M.k = tensor(L.attn_k, c.dim);
+        M.v = tensor(L.attn_v, c.dim);
+        M.o = tensor(L.attn_output, qdim);
+        M.gate = tensor(L.ffn_gate, c.dim);
+        M.up = tensor(L.ffn_up, c.dim);
+        M.down = tensor(L.ffn_down, c.ff_dim);
+        M.attn_norm = L.attn_norm_f32;
+        M.ffn_norm = L.ffn_norm_f32;
+        M.k_cache = L.k_cache;
+        M.v_cache = L.v_cache;
+    }
+    m.rope_cos = r->rope_cos;
+    m.rope_sin = r->rope_sin;
+    m.state = r->d_state;
+    m.history = r->d_history;
+    m.logits = r->logits;
+    m.status = r->ctx->device_status;
+    m.wait_cycles = r->ctx->wait_cycles;
+    m.sm_count = r->ctx->prop.multiProcessorCount;
+    const size_t bytes = mega_workspace_bytes(m, &r->mega_why);
+    if (!bytes) return YULE_OK;
+    float *ws = nullptr;
+    int32_t rc = alloc_f32(r, (bytes + 3) / 4, &ws);  // zero-filled
+    if (rc) return rc;
+    cudaError_t e = mega_setup(m, ws, r->ctx->stream, &r->mega);
+    if (e != cudaSuccess) {
+        r->mega = nullptr;
+        return fail_cuda(e, "persistent decode kernel set-up");
+    }
+    r->mega_why.clear();
+    return YULE_OK;
+}
+
 int32_t ensure_graph(yule_cuda_runner *r) {
     if (r->graph_exec) return YULE_OK;
     cudaStream_t s = r->ctx->stream;
-    cudaGraph_t graph = nullptr;
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
-    YULE_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
-    uint64_t n = 0;
-    cudaError_t e = enqueue_forward_graph(r, &n);
-    cudaError_t e2 = cudaStreamEndCapture(s, &graph);
-    if (e != cudaSuccess || e2 != cudaSuccess) {
+    if (r->mega_wanted && !r->mega_tried) {
+        r->mega_tried = true;
+        int32_t rc = setup_mega(r);
+        if (rc) return rc;
+    }
+    // With the persistent kernel the graph is that one launch: cooperative first, and if the capture or the
+    // instantiation refuses the attribute, an ordinary launch of the same grid (one CTA per SM; its waits are bounded).
+    for (int attempt = 0; attempt < (r->mega ? 2 : 1); attempt++) {
+        cudaGraph_t graph = nullptr;
+        if (r->mega) mega_set_cooperative(r->mega, attempt == 0);
+        YULE_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
+        uint64_t n = 0;
+        cudaError_t e = r->mega ? mega_launch(r->mega, s, &n) : enqueue_forward_graph(r, &n);
+        cudaError_t e2 = cudaStreamEndCapture(s, &graph);
+        if (e == cudaSuccess && e2 == cudaSuccess) {
+            e = cudaGraphInstantiate(&r->graph_exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e == cudaSuccess) {
+                r->graph_kernels = (uint32_t)n;
+                return YULE_OK;
+            }
+            r->graph_exec = nullptr;
+            cudaGetLastError();
+            if (r->mega && attempt == 0) continue;
+            return fail_cuda(e, "cudaGraphInstantiate");
+        }
         if (graph) cudaGraphDestroy(graph);
         cudaGetLastError();
+        if (r->mega && attempt == 0) continue;
         return fail_cuda(e != cudaSuccess ? e : e2, "graph capture of the token step");
     }
-    e = cudaGraphInstantiate(&r->graph_exec, graph, 0);
-    cudaGraphDestroy(graph);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaGraphInstantiate");
-    r->graph_kernels = (uint32_t)n;
     return YULE_OK;
 }
 
@@ -1103,6 +1193,7 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
     r->ctx = ctx;
     r->cfg = c;
     r->fused = c.fused != 0;
+    r->mega_wanted = c.fused == 2 && tpw <= 1 && !(knob("YULE_CUDA_MEGA") && atoi(knob("YULE_CUDA_MEGA")) == 0);
     if (const char *e = knob("YULE_CUDA_PDL")) r->pdl = atoi(e) != 0;
     r->layers.resize(c.n_layers);
     const uint32_t hd = c.head_dim, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd;
@@ -1223,6 +1314,7 @@ int32_t yule_cuda_runner_destroy(yule_cuda_runner *r) {
     cudaStreamSynchronize(r->ctx->stream);
     if (r->graph_exec) cudaGraphExecDestroy(r->graph_exec);
     if (r->bd_graph) cudaGraphExecDestroy(r->bd_graph);
+    if (r->mega) mega_destroy(r->mega);
     if (r->h_pinned) cudaFreeHost(r->h_pinned);
     for (yule_buffer h : r->owned) yule_cuda_free(r->ctx, h);
     // collective: every rank destroys its runner at the same point (a runner whose creation failed half-way leaves
@@ -1248,6 +1340,11 @@ int32_t yule_cuda_runner_set_tensor(yule_cuda_runner *r, const char *name, yule_
         cudaGraphExecDestroy(r->graph_exec);
         r->graph_exec = nullptr;
     }
+    if (r->mega) {
+        mega_destroy(r->mega);
+        r->mega = nullptr;
+    }
+    r->mega_tried = false;
     if (r->bd_graph) {
         cudaGraphExecDestroy(r->bd_graph);
         r->bd_graph = nullptr;
@@ -1289,6 +1386,36 @@ int32_t yule_cuda_runner_reset(yule_cuda_runner *r) {
     r->pos = 0;
     r->have_next_token = false;
     return YULE_OK;
+}
+
+int32_t yule_cuda_runner_step_kind(yule_cuda_runner *r, uint32_t *out_kind) {
+    if (!r || !out_kind) return fail(YULE_ERR_INVALID_ARGUMENT, "null argument");
+    YULE_CUDA_TRY(cudaSetDevice(r->ctx->device));
+    int32_t rc = finalize(r);
+    if (rc) return rc;
+    if (is_fused(r) && (rc = ensure_graph(r))) return rc;
+    *out_kind = !is_fused(r) ? 0u : (r->mega ? 2u : 1u);
+    return YULE_OK;
+}
+
+int32_t yule_cuda_runner_selftest_bounded_wait(yule_cuda_runner *r, uint64_t budget_cycles) {
+    if (!r) return fail(YULE_ERR_INVALID_ARGUMENT, "null runner");
+    uint32_t kind = 0;
+    int32_t rc = yule_cuda_runner_step_kind(r, &kind);
+    if (rc) return rc;
+    if (kind != 2) return fail(YULE_ERR_INVALID_ARGUMENT, "the self-test needs a runner whose token step is the persistent kernel");
+    cudaStream_t s = r->ctx->stream;
+    YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    // a valid token and position for the garbage step
+    r->h_pinned[0] = 0;
+    r->h_pinned[1] = 0;
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->d_state, r->h_pinned, 8, cudaMemcpyHostToDevice, s));
+    uint64_t n = 0;
+    cudaError_t e = mega_launch_selftest(r->mega, budget_cycles ? (long long)budget_cycles : r->ctx->wait_cycles, s, &n);
+    r->ctx->launches.fetch_add(n);
+    r->pos = 0;
+    r->have_next_token = false;
+    return e == cudaSuccess ? yule_cuda_synchronize(r->ctx) : fail_cuda(e, "bounded-wait self-test launch");
 }
 
 int32_t yule_cuda_runner_position(yule_cuda_runner *r, uint32_t *out_pos) {

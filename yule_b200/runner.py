@@ -65,7 +65,8 @@ class CudaTransformerRunner:
     """``ModelRunner`` over the CUDA backend.
 
     ``weights`` maps GGUF tensor names to ``(bytes-like or uint8/float array, DType)``.  ``fused=False``
-    issues one kernel per reference dispatch; ``fused=True`` replays fused kernels from a CUDA graph.
+    issues one kernel per reference dispatch; ``fused=True`` replays fused kernels from a CUDA graph; ``fused=2``
+    additionally runs the token step as one persistent kernel where the model allows it (``step_kind`` tells).
     """
 
     def __init__(self, backend: CudaB200Backend, config: ModelConfig, weights: dict, fused: bool = True):
@@ -74,7 +75,7 @@ class CudaTransformerRunner:
         self._lib = _lib.cuda_lib()
         cfg = _lib.RunnerConfig(config.dim, config.n_layers, config.n_heads, config.n_kv_heads, config.head_dim,
                                 config.vocab_size, config.ff_dim, config.max_seq_len, config.norm_eps,
-                                config.rope_freq_base, 1 if fused else 0, config.rotary_dim, config.sliding_window,
+                                config.rope_freq_base, int(fused), config.rotary_dim, config.sliding_window,
                                 config.attn_logit_softcap, config.logit_softcap, config.norm_weight_offset,
                                 1 if config.geglu else 0)
         r = C.c_void_p()
@@ -127,6 +128,18 @@ class CudaTransformerRunner:
         p = C.c_uint32()
         _check(self._lib.yule_cuda_runner_position(self._r, C.byref(p)))
         return p.value
+
+    @property
+    def step_kind(self) -> int:
+        """0: one kernel per dispatch; 1: fused kernels in a CUDA graph; 2: one persistent kernel per token."""
+        k = C.c_uint32()
+        _check(self._lib.yule_cuda_runner_step_kind(self._r, C.byref(k)))
+        return k.value
+
+    def selftest_bounded_wait(self, budget_cycles: int = 0) -> int:
+        """Runs the persistent token kernel once with waits that cannot be satisfied; returns the error code
+        (``YULE_ERR_DEVICE_STATUS`` is the expected one).  Reset the runner afterwards."""
+        return int(self._lib.yule_cuda_runner_selftest_bounded_wait(self._r, int(budget_cycles)))
 
     def generate_greedy(self, prompt, n_generate: int) -> np.ndarray:
         """Feed ``prompt`` (may be empty to continue), then emit ``n_generate`` greedy tokens on the device."""
