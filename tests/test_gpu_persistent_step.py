@@ -57,7 +57,7 @@ def test_head_shapes(backend, oracle, heads, kv_heads, head_dim):
     weights = synth.synthetic_model(cfg, seed=13, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
     ref = make_oracle_model(oracle, cfg, weights)
     run = persistent_runner(backend, cfg, weights)
-    prompt = synth.tokens(5, 7, cfg.vocab_size)
+    prompt = synth.tokens(5, 40, cfg.vocab_size)  # head_dim 128: the attention unit needs two passes from position 32 on
     assert guarded_rel_err(run.prefill(prompt), ref.prefill(prompt)) <= REL_TOL
     for tok in (1, 2, 3):
         assert guarded_rel_err(run.decode_step(tok), ref.decode_step(tok)) <= REL_TOL
@@ -79,15 +79,22 @@ def test_greedy_stream_identical(backend, oracle):
     run.close()
 
 
-def test_long_context_uses_several_splits(backend, oracle):
-    """Past 32 positions the attention of a KV head is split over several CTAs and merged by the last one to finish;
-    the prompt is long enough for the chunked prefill, which shares the KV caches with the persistent kernel."""
-    weights = synth.synthetic_model(SMALL, seed=21, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
-    ref = make_oracle_model(oracle, SMALL, weights)
-    run = persistent_runner(backend, SMALL, weights)
-    prompt = synth.tokens(9, 130, SMALL.vocab_size)
+def test_long_context_uses_several_passes_and_splits(backend, oracle):
+    """A unit of the attention phase takes its positions 64 at a time (head_dim 64) with a running soft-max, and past
+    256 positions a KV head is split over several CTAs whose partial results the last one to finish merges.  The
+    prompt goes through the chunked prefill, which shares the KV caches with the persistent kernel."""
+    cfg = ModelConfig(dim=512, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, vocab_size=1000, ff_dim=1024, max_seq_len=640)
+    weights = synth.synthetic_model(cfg, seed=21, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
+    ref = make_oracle_model(oracle, cfg, weights)
+    run = persistent_runner(backend, cfg, weights)
+    prompt = synth.tokens(9, 130, cfg.vocab_size)  # positions 129..: three passes of one unit
     assert guarded_rel_err(run.prefill(prompt), ref.prefill(prompt)) <= REL_TOL
-    for tok in (7, 8, 9, 10):
+    for tok in (7, 8):
+        assert guarded_rel_err(run.decode_step(tok), ref.decode_step(tok)) <= REL_TOL
+    more = synth.tokens(10, 400, cfg.vocab_size)  # on to position 532: three splits of three passes each, merged
+    got, want = run.prefill(more), ref.prefill(more)
+    assert guarded_rel_err(got, want) <= REL_TOL
+    for tok in (9, 10, 11):
         assert guarded_rel_err(run.decode_step(tok), ref.decode_step(tok)) <= REL_TOL
     run.close()
 

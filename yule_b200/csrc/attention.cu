@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_gqa_kernel(const __grid_
     au.tickets = p.tickets + (size_t)z * p.n_heads;
     au.q_pairs = au.k_pairs = au.v_pairs = nullptr;
     au.in_epoch = 0;
+    au.prof = nullptr;
     float *out_z = p.out + (size_t)z * p.out_stride;
     attn_gqa_unit<GROUP, HD, false>(
         p, au, blockIdx.x, blockIdx.y, threadIdx.x, sm, &s_last, [] { __syncthreads(); },

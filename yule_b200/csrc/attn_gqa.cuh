@@ -52,6 +52,7 @@ struct AttnUnit {
     const uint2 *q_pairs, *k_pairs, *v_pairs;
     uint32_t in_epoch;
     uint32_t pos;
+    unsigned long long *prof;  // timing aid of the persistent kernel (three stamps), or null
 };
 
 // ── grouped-query variant ───────────────────────────────────────────────────────────────────
@@ -62,6 +63,136 @@ struct AttnUnit {
 // CTA of a KV head (ticket) merges the splits of its GROUP heads.
 constexpr int kGqaMaxSplits = 64;
 
+// The end of a unit: `o` holds this split's unnormalised output sums (element tid + k·kThreads of the
+// [GROUP][HD] block of this KV head), `ml` (shared memory) its (max, Σexp) per head.  One split: normalise and store.
+// Several: publish (sums, max, Σexp), take a ticket; the last unit of the KV head merges all splits and stores.
+//   work  shared memory: max(GROUP·HD/4, kThreads) float4 for the merge, then 2·GROUP·kGqaMaxSplits floats
+template <int GROUP, int HD, class Sync, class Store>
+__device__ __forceinline__ void attn_gqa_finish(const AttnParams &p, float *scratch_z, uint32_t *tickets_z, uint32_t kvh, uint32_t split,
+                                                uint32_t eff, bool nonempty, uint32_t tid, const float (&o)[(GROUP * HD + kThreads - 1) / kThreads],
+                                                float *ml, float *work, uint32_t *s_last, Sync sync, Store store) {
+    constexpr int HD4 = HD / 4;
+    constexpr int NOUT = (GROUP * HD + kThreads - 1) / kThreads;
+    const uint32_t head0 = kvh * GROUP;
+    float *partial = work;
+    float *mrg = work + 4 * (GROUP * HD4 > kThreads ? GROUP * HD4 : kThreads);
+    if (eff == 1) {
+#pragma unroll
+        for (int k = 0; k < NOUT; k++) {
+            const uint32_t idx = tid + k * kThreads;
+            if (idx < GROUP * HD) {
+                const float val = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
+                store((uint32_t)(head0 * HD + idx), val);
+            }
+        }
+        return;
+    }
+
+    // publish (m, l, acc) per head, take a ticket; the last CTA of this KV head merges.
+    // Scratch: accumulators [head][split][HD], then the (m, l) pairs [head][split][2].
+    float *stats = scratch_z + (size_t)p.n_heads * p.n_splits * HD;
+#pragma unroll
+    for (int k = 0; k < NOUT; k++) {
+        const uint32_t idx = tid + k * kThreads;
+        if (idx < GROUP * HD) {
+            const uint32_t h = idx / HD, dd = idx % HD;
+            scratch_z[((size_t)(head0 + h) * p.n_splits + split) * HD + dd] = o[k];
+        }
+    }
+    if (tid < GROUP) {
+        float *mine = stats + ((size_t)(head0 + tid) * p.n_splits + split) * 2;
+        mine[0] = nonempty ? ml[2 * tid] : -FLT_MAX;
+        mine[1] = nonempty ? ml[2 * tid + 1] : 0.f;
+    }
+    __threadfence();
+    sync();
+    if (tid == 0) *s_last = (atomicAdd(&tickets_z[kvh], 1u) == eff - 1) ? 1u : 0u;
+    sync();
+    if (!*s_last) return;
+    __threadfence();
+    // (m, l) of every (head, split): one load per thread, then the weights exp(m - M) in shared memory
+    float *mm = mrg, *ww = mrg + GROUP * kGqaMaxSplits;
+    for (uint32_t i = tid; i < GROUP * eff; i += kThreads) {
+        const uint32_t h = i / eff, s2 = i % eff;
+        const float2 st = __ldcg(reinterpret_cast<const float2 *>(stats + ((size_t)(head0 + h) * p.n_splits + s2) * 2));
+        mm[h * kGqaMaxSplits + s2] = st.x;
+        ww[h * kGqaMaxSplits + s2] = st.y;
+    }
+    sync();
+    if (tid < GROUP) {
+        const uint32_t h = tid;
+        float M = -FLT_MAX;
+        for (uint32_t s2 = 0; s2 < eff; s2++) M = fmaxf(M, mm[h * kGqaMaxSplits + s2]);
+        float L = 0.f;
+        for (uint32_t s2 = 0; s2 < eff; s2++) {
+            const float l = ww[h * kGqaMaxSplits + s2];
+            const float w = l > 0.f ? expf(mm[h * kGqaMaxSplits + s2] - M) : 0.f;  // empty split: no weight
+            L = fmaf(l, w, L);
+            ww[h * kGqaMaxSplits + s2] = w;
+        }
+        ml[2 * h + 1] = L;
+    }
+    sync();
+    // Weighted sum of the splits' accumulators: thread (slice, head, d4) takes splits slice,
+    // slice + MS, … as 16-byte loads, sixteen in flight; the slices meet in shared memory.
+    constexpr int NV = GROUP * HD4;                         // float4 outputs of this KV head
+    constexpr int MS = NV >= kThreads ? 1 : kThreads / NV;  // split slices
+    constexpr int NVT = (NV + kThreads - 1) / kThreads;     // outputs per thread when MS == 1
+    float4 *red4 = reinterpret_cast<float4 *>(partial);     // MS × NV float4 (fits: MS·NV ≤ max(NV, 256))
+#pragma unroll
+    for (int k = 0; k < NVT; k++) {
+        const uint32_t vi = (tid % (MS > 1 ? NV : kThreads)) + k * kThreads;
+        const uint32_t msl = MS > 1 ? tid / NV : 0;
+        if (vi < (uint32_t)NV) {
+            const uint32_t h = vi / HD4, c4 = vi % HD4;
+            const float4 *src = reinterpret_cast<const float4 *>(scratch_z + (size_t)(head0 + h) * p.n_splits * HD) + c4;
+            const float *wh = ww + h * kGqaMaxSplits;
+            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+            uint32_t s2 = msl;
+            for (; s2 + 15 * MS < eff; s2 += 16 * MS) {
+                float4 v[16];
+#pragma unroll
+                for (int u = 0; u < 16; u++) v[u] = __ldcg(src + (size_t)(s2 + u * MS) * HD4);
+#pragma unroll
+                for (int u = 0; u < 16; u++) {
+                    const float w = wh[s2 + u * MS];
+                    O.x = fmaf(v[u].x, w, O.x);
+                    O.y = fmaf(v[u].y, w, O.y);
+                    O.z = fmaf(v[u].z, w, O.z);
+                    O.w = fmaf(v[u].w, w, O.w);
+                }
+            }
+            for (; s2 < eff; s2 += MS) {
+                const float4 v = __ldcg(src + (size_t)s2 * HD4);
+                const float w = wh[s2];
+                O.x = fmaf(v.x, w, O.x);
+                O.y = fmaf(v.y, w, O.y);
+                O.z = fmaf(v.z, w, O.z);
+                O.w = fmaf(v.w, w, O.w);
+            }
+            red4[(size_t)msl * NV + vi] = O;
+        }
+    }
+    sync();
+    for (uint32_t vi = tid; vi < (uint32_t)NV; vi += kThreads) {
+        float4 O = red4[vi];
+        for (int m2 = 1; m2 < MS; m2++) {
+            const float4 v = red4[(size_t)m2 * NV + vi];
+            O.x += v.x;
+            O.y += v.y;
+            O.z += v.z;
+            O.w += v.w;
+        }
+        const float inv = 1.0f / ml[2 * (vi / HD4) + 1];
+        const float4 res = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+        const uint32_t o0 = head0 * HD + 4 * vi;
+        store(o0, res.x);
+        store(o0 + 1, res.y);
+        store(o0 + 2, res.z);
+        store(o0 + 3, res.w);
+    }
+    if (tid == 0) tickets_z[kvh] = 0;  // ready for the next launch on this stream
+}
 // One (KV head, split) unit of work, by 256 threads (`tid` 0..255) that can meet at `sync()`.
 //   PAIRS  the query and the new K / V rows arrive as (value, epoch) pairs that are polled (persistent decode
 //          kernel); otherwise they are plain floats written by an earlier kernel.
@@ -108,7 +239,7 @@ __device__ __forceinline__ void attn_gqa_unit(const AttnParams &p, const AttnUni
     float *ml = vcur + HD;                        // (max, sum) per head, 16 floats
     float *scores = ml + 16;                      // GROUP × max_chunk
     float *partial = scores + (size_t)GROUP * p.max_chunk;  // NSL × GROUP × HD
-    float *mrg = partial + (size_t)NSL * GROUP * HD;        // merge: 2 × GROUP × kGqaMaxSplits
+    // (the merge of attn_gqa_finish works in `partial` and the 2 × GROUP × kGqaMaxSplits floats behind it)
 
     // The first K tile does not depend on the query: its loads go out before the RoPE prologue.
     const int qtr = lane >> 3, l8 = lane & 7;
@@ -331,120 +462,233 @@ __device__ __forceinline__ void attn_gqa_unit(const AttnParams &p, const AttnUni
         }
     }
 
-    if (eff == 1) {
-#pragma unroll
-        for (int k = 0; k < NOUT; k++) {
-            const uint32_t idx = tid + k * kThreads;
-            if (idx < GROUP * HD) {
-                const float val = o[k] * (1.0f / ml[2 * (idx / HD) + 1]);
-                store((uint32_t)(head0 * HD + idx), val);
-            }
+    attn_gqa_finish<GROUP, HD>(p, scratch_z, tickets_z, kvh, split, eff, lo < hi, tid, o, ml, partial, s_last, sync, store);
+}
+
+// ── the same unit with its keys and values staged in shared memory ──────────────────────────────────────────────
+// For the persistent decode kernel, where a phase costs latency rather than bandwidth and registers are scarce.
+// The K and V rows of the unit's positions are brought into shared memory by 16-byte asynchronous copies, all in
+// flight at once and issued before the unit waits for its query (they do not depend on it); scores, soft-max and
+// the weighted sum then run out of shared memory, C positions per pass, with a running (max, Σexp) across passes.
+// Inputs are (value, epoch) pairs; plain Llama attention (no window, no soft-cap).  Splits, tickets, merge and
+// output are those of attn_gqa_unit.
+constexpr size_t attn_staged_smem_floats(int group, int hd) {
+    const int c = 4096 / hd;
+    const size_t front = (size_t)group * hd + 2 * hd + 32 + (size_t)group * c;
+    const size_t kv = (size_t)c * (hd + 4) + (size_t)c * hd;
+    const size_t nv = (size_t)group * hd / 4;
+    const size_t work = 4 * (nv > (size_t)kThreads ? nv : (size_t)kThreads) + 2 * (size_t)group * kGqaMaxSplits;
+    return front + (kv > work ? kv : work);
+}
+
+template <int GROUP, int HD, int NT, class SyncAll, class Sync, class Store>
+__device__ __forceinline__ void attn_unit_staged(const AttnParams &p, const AttnUnit &au, uint32_t kvh, uint32_t split, uint32_t tid,
+                                                 float *sm, uint32_t *s_last, SyncAll sync_all, Sync sync, Store store) {
+    // NT threads (tid 0..NT-1, meeting at sync_all) run the passes; the first kThreads of them (meeting at sync)
+    // publish / merge / store.
+    constexpr int C = 4096 / HD;  // positions per pass
+    constexpr int KP = HD + 4;    // row pitch of K in shared memory (floats): rows 16 bytes apart in bank terms
+    constexpr int HD4 = HD / 4;
+    constexpr int LP = NT / C;    // lanes per position in the score step, 8 dimensions each
+    static_assert(LP * 8 == HD && LP <= 32, "eight dimensions per lane");
+    constexpr int NOUT = (GROUP * HD + kThreads - 1) / kThreads;
+    constexpr int NACC = (GROUP * HD + NT - 1) / NT;
+    constexpr int QIT = (GROUP * (HD / 2) + NT - 1) / NT;
+    const uint32_t head0 = kvh * GROUP, pos = au.pos, seq = pos + 1;
+    uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
+    eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
+    if (split >= eff) return;
+    const uint32_t chunk = (seq + eff - 1) / eff;
+    const uint32_t lo = split * chunk < seq ? split * chunk : seq;
+    const uint32_t hi = lo + chunk < seq ? lo + chunk : seq;
+    const int lane = tid & 31, wid = tid >> 5;
+
+    float *qs = sm;                  // GROUP × HD rotated queries
+    float *kcur = qs + GROUP * HD;   // rotated K row of the current token
+    float *vcur = kcur + HD;         // V row of the current token
+    float *ml = vcur + HD;           // running (max, Σexp) per head
+    float *alpha = ml + 16;          // rescale factor of the pass, per head
+    float *sc = alpha + 16;          // GROUP × C scores, then weights
+    float *Ks = sc + GROUP * C;      // C × KP
+    float *Vs = Ks + C * KP;         // C × HD
+    float *k_cache = au.k_cache, *v_cache = au.v_cache;
+
+    // the rows of positions [p0, p0 + n) except the current one (which never comes from the cache)
+    auto stage_rows = [&](uint32_t p0, uint32_t n) {
+        for (uint32_t idx = tid; idx < n * HD4; idx += NT) {
+            const uint32_t t = idx / HD4, j = idx % HD4;
+            if (p0 + t == pos) continue;
+            const size_t src = (size_t)(p0 + t) * p.kv_stride + (size_t)kvh * HD + 4 * j;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(Ks + t * KP + 4 * j)),
+                         "l"(k_cache + src)
+                         : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(Vs + t * HD + 4 * j)),
+                         "l"(v_cache + src)
+                         : "memory");
         }
-        return;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (lo < hi) stage_rows(lo, hi - lo < (uint32_t)C ? hi - lo : (uint32_t)C);
+
+    // query and new K / V rows: rotation factors first (plain loads), then every pair load, then the checks
+    float rot_c[QIT], rot_s[QIT];
+    uint2 pq[QIT][2] = {}, pk[2] = {}, pv = {};
+#pragma unroll
+    for (int it = 0; it < QIT; it++) {
+        const uint32_t idx = tid + it * NT;
+        rot_c[it] = 1.f;
+        rot_s[it] = 0.f;
+        if (p.cos_table && idx < GROUP * (HD / 2)) {
+            rot_c[it] = p.cos_table[(size_t)pos * (HD / 2) + idx % (HD / 2)];
+            rot_s[it] = p.sin_table[(size_t)pos * (HD / 2) + idx % (HD / 2)];
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < QIT; it++) {
+        const uint32_t idx = tid + it * NT;
+        if (idx < GROUP * (HD / 2)) {
+            pq[it][0] = pair_peek(au.q_pairs + (size_t)head0 * HD + 2 * idx);
+            pq[it][1] = pair_peek(au.q_pairs + (size_t)head0 * HD + 2 * idx + 1);
+        }
+    }
+    if (tid < HD / 2) {
+        pk[0] = pair_peek(au.k_pairs + (size_t)kvh * HD + 2 * tid);
+        pk[1] = pair_peek(au.k_pairs + (size_t)kvh * HD + 2 * tid + 1);
+    }
+    // the V row is fetched by the threads at the far end, which have no query pair to fetch
+    const uint32_t vt = NT - 1 - tid;
+    if (vt < HD) pv = pair_peek(au.v_pairs + (size_t)kvh * HD + vt);
+    // RoPE as in apply_rope (model_runner.rs:277-293): products and sums rounded separately
+#pragma unroll
+    for (int it = 0; it < QIT; it++) {
+        const uint32_t idx = tid + it * NT;
+        if (idx >= GROUP * (HD / 2)) break;
+        const size_t qi = (size_t)head0 * HD + 2 * idx;
+        const float q0 = pair_settle(pq[it][0], au.q_pairs + qi, au.in_epoch, p.status, p.wait_cycles);
+        const float q1 = pair_settle(pq[it][1], au.q_pairs + qi + 1, au.in_epoch, p.status, p.wait_cycles);
+        const float c = rot_c[it], sn = rot_s[it];
+        qs[2 * idx] = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, sn));
+        qs[2 * idx + 1] = __fadd_rn(__fmul_rn(q0, sn), __fmul_rn(q1, c));
+        if (idx < HD / 2) {  // head 0 of the group: this thread also rotates the new K row
+            const size_t ki = (size_t)kvh * HD + 2 * idx;
+            const float k0 = pair_settle(pk[0], au.k_pairs + ki, au.in_epoch, p.status, p.wait_cycles);
+            const float k1 = pair_settle(pk[1], au.k_pairs + ki + 1, au.in_epoch, p.status, p.wait_cycles);
+            kcur[2 * idx] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, sn));
+            kcur[2 * idx + 1] = __fadd_rn(__fmul_rn(k0, sn), __fmul_rn(k1, c));
+        }
+    }
+    if (vt < HD) vcur[vt] = pair_settle(pv, au.v_pairs + (size_t)kvh * HD + vt, au.in_epoch, p.status, p.wait_cycles);
+    if (tid < GROUP) {
+        ml[2 * tid] = -FLT_MAX;
+        ml[2 * tid + 1] = 0.f;
+    }
+    sync_all();
+    if (au.prof && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(au.prof[1]));  // inputs settled
+    // the split that owns the current position appends the new K and V rows
+    if (pos >= lo && pos < hi) {
+        for (uint32_t d = tid; d < HD; d += NT) {
+            k_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = kcur[d];
+            v_cache[(size_t)pos * p.kv_stride + (size_t)kvh * HD + d] = vcur[d];
+        }
     }
 
-    // publish (m, l, acc) per head, take a ticket; the last CTA of this KV head merges.
-    // Scratch: accumulators [head][split][HD], then the (m, l) pairs [head][split][2].
-    float *stats = scratch_z + (size_t)p.n_heads * p.n_splits * HD;
+    const float scale = 1.0f / sqrtf((float)HD);
+    float acc[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) acc[k] = 0.f;
+    for (uint32_t p0 = lo; p0 < hi; p0 += C) {
+        const uint32_t n = hi - p0 < (uint32_t)C ? hi - p0 : (uint32_t)C;
+        if (p0 != lo) stage_rows(p0, n);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (pos >= p0 && pos < p0 + n)
+            for (uint32_t d = tid; d < HD; d += NT) {
+                Ks[(pos - p0) * KP + d] = kcur[d];
+                Vs[(pos - p0) * HD + d] = vcur[d];
+            }
+        sync_all();
+        // scores: LP lanes per position, eight dimensions each
+        {
+            const uint32_t tp = tid / LP, part = tid % LP;
+            const float *kr = Ks + (tp < n ? tp : 0u) * KP + part * 8;
+            const float4 k0 = *reinterpret_cast<const float4 *>(kr), k1 = *reinterpret_cast<const float4 *>(kr + 4);
+#pragma unroll
+            for (int h = 0; h < GROUP; h++) {
+                const float *qr = qs + h * HD + part * 8;
+                const float4 q0 = *reinterpret_cast<const float4 *>(qr), q1 = *reinterpret_cast<const float4 *>(qr + 4);
+                float a0 = q0.x * k0.x, a1 = q0.y * k0.y;
+                a0 = fmaf(q0.z, k0.z, a0);
+                a1 = fmaf(q0.w, k0.w, a1);
+                a0 = fmaf(q1.x, k1.x, a0);
+                a1 = fmaf(q1.y, k1.y, a1);
+                a0 = fmaf(q1.z, k1.z, a0);
+                a1 = fmaf(q1.w, k1.w, a1);
+                float dsum = a0 + a1;
+#pragma unroll
+                for (int o = 1; o < LP; o <<= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
+                if (part == 0 && tp < n) sc[h * C + tp] = dsum * scale;
+            }
+        }
+        sync_all();
+        // running soft-max: one warp per head
+        for (int h = wid; h < GROUP; h += NT / 32) {
+            float *s = sc + h * C;
+            float mx = -FLT_MAX;
+            for (uint32_t i = lane; i < n; i += 32) mx = fmaxf(mx, s[i]);
+            mx = warp_max(mx);
+            const float m_old = ml[2 * h], m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (uint32_t i = lane; i < n; i += 32) {
+                const float e = expf(s[i] - m_new);
+                s[i] = e;
+                sum += e;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                const float a = expf(m_old - m_new);  // 0 on the first pass
+                alpha[h] = a;
+                ml[2 * h] = m_new;
+                ml[2 * h + 1] = fmaf(ml[2 * h + 1], a, sum);
+            }
+        }
+        sync_all();
+        // Σ_t weight_t · V[t]: every thread owns NACC (head, dimension) outputs; two chains per output
+#pragma unroll
+        for (int k = 0; k < NACC; k++) {
+            const uint32_t idx = tid + k * NT;
+            if (idx < GROUP * HD) {
+                const uint32_t h = idx / HD, d = idx % HD;
+                const float *w = sc + h * C;
+                const float *v = Vs + d;
+                float a = acc[k] * alpha[h], b = 0.f;
+                uint32_t t = 0;
+                for (; t + 4 <= n; t += 4) {
+                    const float4 w4 = *reinterpret_cast<const float4 *>(w + t);
+                    a = fmaf(w4.x, v[(size_t)t * HD], a);
+                    b = fmaf(w4.y, v[(size_t)(t + 1) * HD], b);
+                    a = fmaf(w4.z, v[(size_t)(t + 2) * HD], a);
+                    b = fmaf(w4.w, v[(size_t)(t + 3) * HD], b);
+                }
+                for (; t < n; t++) a = fmaf(w[t], v[(size_t)t * HD], a);
+                acc[k] = a + b;
+            }
+        }
+        sync_all();  // before the next pass (or the hand-over) reuses the rows and the scores
+        if (au.prof && tid == 0 && p0 == lo) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(au.prof[2]));  // first pass done
+    }
+    if (au.prof && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(au.prof[3]));  // all passes done
+    // hand the sums to the first kThreads threads, which finish the unit
+#pragma unroll
+    for (int k = 0; k < NACC; k++) {
+        const uint32_t idx = tid + k * NT;
+        if (idx < GROUP * HD) Vs[idx] = acc[k];
+    }
+    sync_all();
+    if (tid >= (uint32_t)kThreads) return;
+    float o[NOUT];
 #pragma unroll
     for (int k = 0; k < NOUT; k++) {
         const uint32_t idx = tid + k * kThreads;
-        if (idx < GROUP * HD) {
-            const uint32_t h = idx / HD, dd = idx % HD;
-            scratch_z[((size_t)(head0 + h) * p.n_splits + split) * HD + dd] = o[k];
-        }
+        o[k] = idx < GROUP * HD ? Vs[idx] : 0.f;
     }
-    if (tid < GROUP) {
-        float *mine = stats + ((size_t)(head0 + tid) * p.n_splits + split) * 2;
-        mine[0] = lo < hi ? ml[2 * tid] : -FLT_MAX;
-        mine[1] = lo < hi ? ml[2 * tid + 1] : 0.f;
-    }
-    __threadfence();
-    sync();
-    if (tid == 0) *s_last = (atomicAdd(&tickets_z[kvh], 1u) == eff - 1) ? 1u : 0u;
-    sync();
-    if (!*s_last) return;
-    __threadfence();
-    // (m, l) of every (head, split): one load per thread, then the weights exp(m - M) in shared memory
-    float *mm = mrg, *ww = mrg + GROUP * kGqaMaxSplits;
-    for (uint32_t i = tid; i < GROUP * eff; i += kThreads) {
-        const uint32_t h = i / eff, s2 = i % eff;
-        const float2 st = __ldcg(reinterpret_cast<const float2 *>(stats + ((size_t)(head0 + h) * p.n_splits + s2) * 2));
-        mm[h * kGqaMaxSplits + s2] = st.x;
-        ww[h * kGqaMaxSplits + s2] = st.y;
-    }
-    sync();
-    if (tid < GROUP) {
-        const uint32_t h = tid;
-        float M = -FLT_MAX;
-        for (uint32_t s2 = 0; s2 < eff; s2++) M = fmaxf(M, mm[h * kGqaMaxSplits + s2]);
-        float L = 0.f;
-        for (uint32_t s2 = 0; s2 < eff; s2++) {
-            const float l = ww[h * kGqaMaxSplits + s2];
-            const float w = l > 0.f ? expf(mm[h * kGqaMaxSplits + s2] - M) : 0.f;  // empty split: no weight
-            L = fmaf(l, w, L);
-            ww[h * kGqaMaxSplits + s2] = w;
-        }
-        ml[2 * h + 1] = L;
-    }
-    sync();
-    // Weighted sum of the splits' accumulators: thread (slice, head, d4) takes splits slice,
-    // slice + MS, … as 16-byte loads, sixteen in flight; the slices meet in shared memory.
-    constexpr int NV = GROUP * HD4;                         // float4 outputs of this KV head
-    constexpr int MS = NV >= kThreads ? 1 : kThreads / NV;  // split slices
-    constexpr int NVT = (NV + kThreads - 1) / kThreads;     // outputs per thread when MS == 1
-    float4 *red4 = reinterpret_cast<float4 *>(partial);     // MS × NV float4 (fits: MS·NV ≤ max(NV, 256))
-#pragma unroll
-    for (int k = 0; k < NVT; k++) {
-        const uint32_t vi = (tid % (MS > 1 ? NV : kThreads)) + k * kThreads;
-        const uint32_t msl = MS > 1 ? tid / NV : 0;
-        if (vi < (uint32_t)NV) {
-            const uint32_t h = vi / HD4, c4 = vi % HD4;
-            const float4 *src = reinterpret_cast<const float4 *>(scratch_z + (size_t)(head0 + h) * p.n_splits * HD) + c4;
-            const float *wh = ww + h * kGqaMaxSplits;
-            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-            uint32_t s2 = msl;
-            for (; s2 + 15 * MS < eff; s2 += 16 * MS) {
-                float4 v[16];
-#pragma unroll
-                for (int u = 0; u < 16; u++) v[u] = __ldcg(src + (size_t)(s2 + u * MS) * HD4);
-#pragma unroll
-                for (int u = 0; u < 16; u++) {
-                    const float w = wh[s2 + u * MS];
-                    O.x = fmaf(v[u].x, w, O.x);
-                    O.y = fmaf(v[u].y, w, O.y);
-                    O.z = fmaf(v[u].z, w, O.z);
-                    O.w = fmaf(v[u].w, w, O.w);
-                }
-            }
-            for (; s2 < eff; s2 += MS) {
-                const float4 v = __ldcg(src + (size_t)s2 * HD4);
-                const float w = wh[s2];
-                O.x = fmaf(v.x, w, O.x);
-                O.y = fmaf(v.y, w, O.y);
-                O.z = fmaf(v.z, w, O.z);
-                O.w = fmaf(v.w, w, O.w);
-            }
-            red4[(size_t)msl * NV + vi] = O;
-        }
-    }
-    sync();
-    for (uint32_t vi = tid; vi < (uint32_t)NV; vi += kThreads) {
-        float4 O = red4[vi];
-        for (int m2 = 1; m2 < MS; m2++) {
-            const float4 v = red4[(size_t)m2 * NV + vi];
-            O.x += v.x;
-            O.y += v.y;
-            O.z += v.z;
-            O.w += v.w;
-        }
-        const float inv = 1.0f / ml[2 * (vi / HD4) + 1];
-        const float4 res = make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
-        const uint32_t o0 = head0 * HD + 4 * vi;
-        store(o0, res.x);
-        store(o0 + 1, res.y);
-        store(o0 + 2, res.z);
-        store(o0 + 3, res.w);
-    }
-    if (tid == 0) tickets_z[kvh] = 0;  // ready for the next launch on this stream
+    attn_gqa_finish<GROUP, HD>(p, au.scratch, au.tickets, kvh, split, eff, lo < hi, tid, o, ml, Ks, s_last, sync, store);
 }

@@ -58,6 +58,7 @@ namespace q6 {
 constexpr int kMegaThreads = 512;
 constexpr uint32_t kSlotBytes = 28672;  // a ring slot holds one stage of either format
 constexpr int kMegaMaxSlots = 3;
+constexpr uint32_t kMegaMinChunk = 256;  // positions per attention split
 static_assert(q4::kStageBytes <= kSlotBytes && q6::kStageBytes <= kSlotBytes, "slot holds a stage of either format");
 static_assert(q4::kThreadsCta == kMegaThreads && q6::kThreadsCta == kMegaThreads, "staging code assumes this CTA size");
 constexpr size_t kMegaSmemMax = 227 * 1024;
@@ -120,7 +121,7 @@ struct MegaParams {
 
 // fixed part of the shared memory, after ring, phase scratch and the phase table
 constexpr uint32_t kFxZero = 0, kFxInvScale = 1024, kFxRed = 1040, kFxPartial = 1296, kFxBest = 5392, kFxBars = 5648,
-                   kFxCnt = 5696, kFxLast = 5720, kFxPick = 5728, kFxCur = 5856, kFxBytes = 5888;
+                   kFxCnt = 5696, kFxLast = 5720, kFxPick = 5728, kFxPairBuf = 5888, kFxBytes = 6016;
 
 __device__ __forceinline__ void pair_store(uint2 *p, uint32_t v, uint32_t epoch) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v), "r"(epoch) : "memory");
@@ -150,8 +151,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-__device__ __forceinline__ uint32_t my_tiles_of(const Phase &P, uint32_t gi, uint32_t stride) {
-    return (ph_matvec(P) && P.n_tiles > gi) ? (P.n_tiles - gi + stride - 1) / stride : 0u;
+// Jobs of a group in a phase.  Tiles are dealt round-robin to the groups of the grid, except in a pair phase
+// (SiLU(gate)·up), where they are dealt to the CTAs: group 0 multiplies the gate tile, group 1 the up tile of the same
+// rows, and they meet in shared memory (352 tiles over 148 CTAs is three rounds of one stage; over 296 groups as
+// gate+up jobs it was two rounds of two).
+__device__ __forceinline__ uint32_t my_tiles_of(const Phase &P, uint32_t group) {
+    if (!ph_matvec(P)) return 0u;
+    const uint32_t G = gridDim.x;
+    const uint32_t first = ph_pair(P) ? blockIdx.x : blockIdx.x + group * G, stride = ph_pair(P) ? G : 2u * G;
+    return P.n_tiles > first ? (P.n_tiles - first + stride - 1) / stride : 0u;
 }
 // A group's stage sequence over the whole token is a list built on the host (it depends on the model and the
 // grid only) and copied into shared memory: entry = phase | matrix << 10 | chunk << 12 | tile within the matrix << 18.
@@ -246,28 +254,32 @@ __device__ __forceinline__ void mega_stage(const bool Q6, unsigned char *scratch
             mx = fmaxf(mx, fabsf(norm_w ? v[i] * w[i] : v[i]));
         }
     };
-    if (c0 < n_cols) {
+    // eight columns from the pairs of the vector: the four loads go out together, then they are checked
+    auto load_x = [&](uint32_t c, float(&v)[8]) {
         uint4 q[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) q[i] = ld_pairs2(xp + c0 + 2 * i);
+        for (int i = 0; i < 4; i++) q[i] = ld_pairs2(xp + c + 2 * i);
         bool ok = true;
 #pragma unroll
         for (int i = 0; i < 4; i++) ok = ok && q[i].y == x_epoch && q[i].w == x_epoch;
         if (ok) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                a[2 * i] = __uint_as_float(q[i].x);
-                a[2 * i + 1] = __uint_as_float(q[i].z);
+                v[2 * i] = __uint_as_float(q[i].x);
+                v[2 * i + 1] = __uint_as_float(q[i].z);
             }
         } else {
-            q4::tp_load8(xp + c0, x_epoch, status, budget, a);
+            q4::tp_load8(xp + c, x_epoch, status, budget, v);
         }
+    };
+    if (c0 < n_cols) {
+        load_x(c0, a);
         reduce8(a, gw);
     }
     if (prof && tid == 0) prof[1] = global_ns();  // this thread's part of x has arrived
     for (uint32_t c = c0 + kMegaThreads * 8u; c < n_cols; c += kMegaThreads * 8u) {
         float v[8], w[8];
-        q4::tp_load8(xp + c, x_epoch, status, budget, v);
+        load_x(c, v);
         if (norm_w) {
             *reinterpret_cast<float4 *>(w) = *reinterpret_cast<const float4 *>(norm_w + c);
             *reinterpret_cast<float4 *>(w + 4) = *reinterpret_cast<const float4 *>(norm_w + c + 4);
@@ -357,6 +369,27 @@ __device__ __forceinline__ void mega_stage(const bool Q6, unsigned char *scratch
     if (prof && tid == 0) prof[2] = global_ns();  // image complete
 }
 
+// The dynamic shared memory of the kernel: fixed part (constant offsets), phase table with the per-group job counts
+// and stage lists, phase scratch, the two rings.  Pointers into it are derived where they are used instead of being
+// carried through the phase loop: registers are what this kernel is short of.
+extern __shared__ __align__(128) unsigned char mega_smem[];
+__device__ __forceinline__ Phase *sm_hot() { return reinterpret_cast<Phase *>(mega_smem + kFxBytes); }
+__device__ __forceinline__ unsigned short *sm_mt(const MegaParams &p, int group) {
+    return reinterpret_cast<unsigned short *>(mega_smem + kFxBytes + (size_t)p.n_phases * sizeof(Phase)) + group * p.n_phases;
+}
+__device__ __forceinline__ uint32_t *sm_list(const MegaParams &p, int group) {
+    return reinterpret_cast<uint32_t *>(mega_smem + kFxBytes + (size_t)p.n_phases * (sizeof(Phase) + 4)) + group * p.list_stride;
+}
+__device__ __forceinline__ unsigned char *sm_scratch(const MegaParams &p) { return mega_smem + kFxBytes + p.hot_bytes; }
+__device__ __forceinline__ unsigned char *sm_ring(const MegaParams &p, int group) {
+    return mega_smem + kFxBytes + p.hot_bytes + p.scratch_bytes + (size_t)group * p.slots * kSlotBytes;
+}
+__device__ __forceinline__ uint4 *sm_zero() { return reinterpret_cast<uint4 *>(mega_smem + kFxZero); }
+__device__ __forceinline__ float *sm_partial(int group) { return reinterpret_cast<float *>(mega_smem + kFxPartial) + group * 512; }
+__device__ __forceinline__ float *sm_bestv(int group) { return reinterpret_cast<float *>(mega_smem + kFxBest) + group * 32; }
+__device__ __forceinline__ uint32_t *sm_cnt(int group) { return reinterpret_cast<uint32_t *>(mega_smem + kFxCnt) + group * kMegaMaxSlots; }
+__device__ __forceinline__ uint32_t sm_bar0(int group) { return smem_u32(mega_smem + kFxBars) + (uint32_t)group * kMegaMaxSlots * 8u; }
+
 // What the consume loop of a phase keeps across iterations: where the group is in its ring.
 struct RingPos {
     uint32_t slot, parity, n;  // n: stages of the token consumed so far
@@ -366,17 +399,28 @@ struct RingPos {
 // (cross-warp sum, scale, SiLU·up or residual, pair store or logits + running arg-max) and refills the ring.
 // Separate instantiations per format keep the lane constants of the other format out of the loop.
 template <bool Q6>
-__device__ __forceinline__ void mega_consume(const MegaParams &p, const Phase *hot, const unsigned short *mt, const uint32_t *list, uint32_t ph,
-                                             uint32_t gi, uint32_t stride, uint32_t S, uint32_t total, RingPos &rp, unsigned char *ring,
-                                             uint32_t ring_u32, uint32_t bar0, uint32_t *cnt, const unsigned char *scratch, const uint4 *zero,
-                                             float *partial, float *bestv, float invs, uint32_t epoch0, uint32_t epoch, uint2 res_pre) {
+__device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, RingPos &rp, uint32_t tick, uint2 res_pre) {
     const uint32_t tid = threadIdx.x, gt = tid & 255u;
     const int lane = tid & 31, group = tid >> 8, wid = (tid >> 5) & 7;
     const int g = lane >> 2, t = lane & 3;
+    const uint32_t gi = blockIdx.x + (uint32_t)group * gridDim.x, stride = 2u * gridDim.x;
+    const uint32_t S = p.slots, total = p.list_len[gi];
+    const Phase *hot = sm_hot();
+    const unsigned short *mt = sm_mt(p, group);
+    const uint32_t *list = sm_list(p, group);
+    unsigned char *ring = sm_ring(p, group);
+    const uint32_t ring_u32 = smem_u32(ring), bar0 = sm_bar0(group);
+    uint32_t *cnt = sm_cnt(group);
+    const unsigned char *scratch = sm_scratch(p);
+    const uint4 *zero = sm_zero();
+    float *partial = sm_partial(group), *bestv = sm_bestv(group);
+    const float invs = reinterpret_cast<const float *>(mega_smem + kFxInvScale)[0];
+    const uint32_t epoch0 = tick * (p.n_phases + 1u), epoch = epoch0 + ph + 1u;
     const Phase &P = hot[ph];
     const uint32_t bpr = P.n_cols >> 8, chunks = ph_chunks(P);
-    const uint32_t nq = ph_pair(P) ? 2u : 1u;
+    const bool pair = ph_pair(P);
     const uint32_t my_tiles = mt[ph];
+    const uint32_t tile0 = pair ? blockIdx.x : gi, tile_step = pair ? gridDim.x : stride;
     const bool has_res = P.res_phase != kNoPhase;
     // lane constants (B column n = g is live only for g = t (hi part) and g = t + 4 (lo part))
     const bool feeds = (g & 3) == t;
@@ -395,66 +439,59 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, const Phase *h
     for (uint32_t k = 0; k < my_tiles; k++) {
         if (k > 0 && has_res && gt < 128u && (gt & 7u) == 0u) {
             // the hidden-state value this lane will add to its row: requested now, settled in the epilogue
-            const uint32_t row = (gi + k * stride) * 16u + (gt >> 3);
+            const uint32_t row = (tile0 + k * tile_step) * 16u + (gt >> 3);
             if (row < P.rows[0]) res_pre = pair_peek(p.vec[kVecHidden] + row);
         }
-        for (uint32_t q = 0; q < nq; q++) {
-            for (uint32_t c = 0; c < chunks; c++) {
-                const uint32_t bar = bar0 + 8 * rp.slot;
-                unsigned long long *sprof = (p.prof && blockIdx.x == 0 && tid == 0 && rp.n < 256u) ? p.prof + (size_t)gridDim.x * (p.n_phases + 1u) * 4 : nullptr;
-                if (sprof) sprof[256 + rp.n] = global_ns();
-                if (!(p.dbg & 2u)) ring_wait(bar, rp.parity, p.status, p.wait_cycles);  // a wait that gave up has recorded it; go on with what is there
-                if (sprof) sprof[512 + rp.n] = global_ns();
-                const uint32_t blk0 = c * 8u;
-                const uint32_t nblk = bpr - blk0 < 8u ? bpr - blk0 : 8u;
-                if ((uint32_t)wid < nblk && !(p.dbg & 1u)) {
-                    const unsigned char *st = ring + (size_t)rp.slot * kSlotBytes;
-                    const uint32_t blk = blk0 + wid;
-                    if (!Q6) {
-                        const unsigned char *r0 = st + (uint32_t)g * q4::kRowPitch + (uint32_t)wid * 144u;
-                        q4::consume_block_smem(r0, r0 + 8 * q4::kRowPitch, reinterpret_cast<const uint4 *>(bsrc + (size_t)blk * bstride),
-                                               reinterpret_cast<const float *>(ssrc + (size_t)blk * sstride), u, t, first_half, acc0, acc1);
-                    } else {
-                        const int h6 = t >> 1;
-                        q6::consume_block_smem(st + q6::kQlOff + (uint32_t)g * q6::kQlPitch + (uint32_t)wid * 128u + 64u * h6 + 16u * u,
-                                               st + q6::kQhOff + (uint32_t)g * q6::kQhPitch + (uint32_t)wid * 64u + 32u * h6 + 16u * u,
-                                               st + q6::kScOff + (uint32_t)g * q6::kScPitch + (uint32_t)wid * 16u,
-                                               st + q6::kDOff + (uint32_t)g * q6::kDPitch + (uint32_t)wid * 2u,
-                                               reinterpret_cast<const __half *>(bsrc + (size_t)blk * bstride), feeds ? 32u : 0u,
-                                               reinterpret_cast<const float *>(ssrc + (size_t)blk * sstride), u, acc0, acc1);
-                    }
-                }
-                // release the slot when some later stage of the token will reuse it; the warp that releases it last refills it
-                if (rp.n + S < total) {
-                    __syncwarp();
-                    uint32_t last = 0;
-                    if (lane == 0) {
-                        __threadfence_block();
-                        last = ((atomicAdd(&cnt[rp.slot], 1u) & 7u) == 7u) ? 1u : 0u;
-                    }
-                    last = __shfl_sync(0xffffffffu, last, 0);
-                    if (last && !(p.dbg & 2u)) {
-                        const bool sp = p.prof && blockIdx.x == 0 && group == 0 && lane == 0 && rp.n + S < 256u;
-                        if (sp) p.prof[(size_t)gridDim.x * (p.n_phases + 1u) * 4 + 768 + rp.n + S] = global_ns();
-                        if (lane == 0) mega_issue(hot, list[rp.n + S], ring_u32 + rp.slot * kSlotBytes, bar);
-                        __syncwarp();
-                        if (p.prof && blockIdx.x == 0 && group == 0 && lane == 0 && rp.n + S < 256u)
-                            p.prof[(size_t)gridDim.x * (p.n_phases + 1u) * 4 + rp.n + S] = global_ns();
-                    }
-                }
-                rp.n++;
-                if (++rp.slot == S) {
-                    rp.slot = 0;
-                    rp.parity ^= 1u;
+        for (uint32_t c = 0; c < chunks; c++) {
+            const uint32_t bar = bar0 + 8 * rp.slot;
+            unsigned long long *sprof = (p.prof && blockIdx.x == 0 && tid == 0 && rp.n < 256u) ? p.prof + (size_t)gridDim.x * (p.n_phases + 1u) * 4 : nullptr;
+            if (sprof) sprof[256 + rp.n] = global_ns();
+            if (!(p.dbg & 2u)) ring_wait(bar, rp.parity, p.status, p.wait_cycles);  // a wait that gave up has recorded it; go on with what is there
+            if (sprof) sprof[512 + rp.n] = global_ns();
+            const uint32_t blk0 = c * 8u;
+            const uint32_t nblk = bpr - blk0 < 8u ? bpr - blk0 : 8u;
+            if ((uint32_t)wid < nblk && !(p.dbg & 1u)) {
+                const unsigned char *st = ring + (size_t)rp.slot * kSlotBytes;
+                const uint32_t blk = blk0 + wid;
+                if (!Q6) {
+                    const unsigned char *r0 = st + (uint32_t)g * q4::kRowPitch + (uint32_t)wid * 144u;
+                    q4::consume_block_smem(r0, r0 + 8 * q4::kRowPitch, reinterpret_cast<const uint4 *>(bsrc + (size_t)blk * bstride),
+                                           reinterpret_cast<const float *>(ssrc + (size_t)blk * sstride), u, t, first_half, acc0, acc1);
+                } else {
+                    const int h6 = t >> 1;
+                    q6::consume_block_smem(st + q6::kQlOff + (uint32_t)g * q6::kQlPitch + (uint32_t)wid * 128u + 64u * h6 + 16u * u,
+                                           st + q6::kQhOff + (uint32_t)g * q6::kQhPitch + (uint32_t)wid * 64u + 32u * h6 + 16u * u,
+                                           st + q6::kScOff + (uint32_t)g * q6::kScPitch + (uint32_t)wid * 16u,
+                                           st + q6::kDOff + (uint32_t)g * q6::kDPitch + (uint32_t)wid * 2u,
+                                           reinterpret_cast<const __half *>(bsrc + (size_t)blk * bstride), feeds ? 32u : 0u,
+                                           reinterpret_cast<const float *>(ssrc + (size_t)blk * sstride), u, acc0, acc1);
                 }
             }
-            // this matrix's rows are complete in this warp: sum the four column groups, park the 16 row sums
+            // release the slot when some later stage of the token will reuse it; the warp that releases it last refills it
+            if (rp.n + S < total) {
+                __syncwarp();
+                uint32_t last = 0;
+                if (lane == 0) {
+                    __threadfence_block();
+                    last = ((atomicAdd(&cnt[rp.slot], 1u) & 7u) == 7u) ? 1u : 0u;
+                    if (last && !(p.dbg & 2u)) mega_issue(hot, list[rp.n + S], ring_u32 + rp.slot * kSlotBytes, bar);
+                }
+                __syncwarp();
+            }
+            rp.n++;
+            if (++rp.slot == S) {
+                rp.slot = 0;
+                rp.parity ^= 1u;
+            }
+        }
+        // the tile's rows are complete in this warp: sum the four column groups, park the 16 row sums
+        {
             float v0 = acc0, v1 = acc1;
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
-            float *part = partial + (size_t)(k & 1u) * 256 + (size_t)q * 128;
+            float *part = partial + (size_t)(k & 1u) * 256;
             if (t == 0) {
                 part[wid * 16 + g] = v0;
                 part[wid * 16 + g + 8] = v1;
@@ -465,43 +502,45 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, const Phase *h
         // sums in a fixed tree).  The two partial buffers alternate between jobs, so the next job's sums cannot overtake
         // these reads (a warp passes the next barrier only after the first four warps have finished here).
         mega_group_barrier(group);
+        float s0 = 0.f;
+        uint32_t seg = pair ? (uint32_t)group : 0u, tile = tile0 + k * tile_step;
+        const uint32_t rr = gt >> 3, w2 = gt & 7u;
         if (gt < 128u) {
-            const uint32_t rr = gt >> 3, w2 = gt & 7u;
             const uint32_t nwu = bpr < 8u ? bpr : 8u;
-            const float *pb = partial + (size_t)(k & 1u) * 256;
-            float s0 = w2 < nwu ? pb[w2 * 16 + rr] : 0.f;
-            float s1 = (nq == 2u && w2 < nwu) ? pb[128 + w2 * 16 + rr] : 0.f;
+            s0 = w2 < nwu ? partial[(size_t)(k & 1u) * 256 + w2 * 16 + rr] : 0.f;
 #pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            uint32_t seg = 0, tile = gi + k * stride;
-            if (nq == 1u)
+            for (int o = 1; o < 8; o <<= 1) s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s0 *= invs;
+            if (!pair)
                 while (seg + 1 < P.n_seg && tile >= (P.rows[seg] + 15u) / 16u) {
                     tile -= (P.rows[seg] + 15u) / 16u;
                     seg++;
                 }
-            const uint32_t row = tile * 16u + rr;
-            if (w2 == 0 && row < P.rows[seg]) {
-                s0 *= invs;
-                if (nq == 2u) {
-                    s1 *= invs;
-                    s0 = (s0 / (1.0f + expf(-s0))) * s1;  // silu_mul.cu: x / (1 + exp(−x)) * up
-                } else if (has_res) {
-                    s0 += pair_settle(res_pre, p.vec[kVecHidden] + row, epoch0 + P.res_phase + 1u + p.epoch_skew, p.status, p.wait_cycles);
+        }
+        const uint32_t row = tile * 16u + rr;
+        const bool mine = gt < 128u && w2 == 0 && row < P.rows[seg];
+        if (pair) {
+            // group 1 hands its up sums to group 0 through shared memory (both run the same number of jobs here)
+            float *pairbuf = reinterpret_cast<float *>(mega_smem + kFxPairBuf) + (k & 1u) * 16;
+            if (group == 1 && mine) pairbuf[rr] = s0;
+            __syncthreads();
+            if (group == 0 && mine) {
+                const float up = pairbuf[rr];
+                s0 = (s0 / (1.0f + expf(-s0))) * up;  // silu_mul.cu: x / (1 + exp(−x)) * up
+                pair_store(p.vec[(P.vecs >> 8) & 0xFFu] + row, __float_as_uint(s0), epoch);
+            }
+        } else if (mine) {
+            if (has_res) s0 += pair_settle(res_pre, p.vec[kVecHidden] + row, epoch0 + P.res_phase + 1u + p.epoch_skew, p.status, p.wait_cycles);
+            const uint32_t ov = (P.vecs >> (8 + 8 * seg)) & 0xFFu;
+            if (ov == kVecLogits) {
+                p.logits[row] = s0;
+                // running arg-max of the rows this lane finishes; rows come in rising order: ties go to the highest index
+                if (s0 >= bestv[rr]) {
+                    bestv[rr] = s0;
+                    reinterpret_cast<uint32_t *>(bestv)[16 + rr] = row;
                 }
-                const uint32_t ov = (P.vecs >> (8 + 8 * seg)) & 0xFFu;
-                if (ov == kVecLogits) {
-                    p.logits[row] = s0;
-                    // running arg-max of the rows this lane finishes; rows come in rising order: ties go to the highest index
-                    if (s0 >= bestv[rr]) {
-                        bestv[rr] = s0;
-                        reinterpret_cast<uint32_t *>(bestv)[16 + rr] = row;
-                    }
-                } else {
-                    pair_store(p.vec[ov] + row, __float_as_uint(s0), epoch);
-                }
+            } else {
+                pair_store(p.vec[ov] + row, __float_as_uint(s0), epoch);
             }
         }
     }
@@ -509,70 +548,58 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, const Phase *h
 
 template <int GROUP, int HD>
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __grid_constant__ MegaParams p) {
-    extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t tid = threadIdx.x;
-    const int lane = tid & 31, group = tid >> 8, wid = (tid >> 5) & 7;
+    const int lane = tid & 31, group = tid >> 8;
     const uint32_t gt = tid & 255u;  // thread within the group
-    const uint32_t G = gridDim.x, gi = blockIdx.x + (uint32_t)group * G, stride = 2u * G;
-    const uint32_t S = p.slots, NP = p.n_phases;
-
-    // shared memory: fixed part (constant offsets), phase table, phase scratch, the two rings
-    unsigned char *fixed = smem;
-    Phase *hot = reinterpret_cast<Phase *>(smem + kFxBytes);
-    unsigned char *scratch = smem + kFxBytes + p.hot_bytes;
-    unsigned char *ring = scratch + p.scratch_bytes + (size_t)group * S * kSlotBytes;
-    uint4 *zero = reinterpret_cast<uint4 *>(fixed + kFxZero);
-    float *inv_scale = reinterpret_cast<float *>(fixed + kFxInvScale);
-    float *red = reinterpret_cast<float *>(fixed + kFxRed);
-    float *partial = reinterpret_cast<float *>(fixed + kFxPartial) + group * 512;  // [buffer 2][matrix 2][warp 8][row 16]
-    float *bestv = reinterpret_cast<float *>(fixed + kFxBest) + group * 32;        // 16 values, 16 indices
-    uint32_t *cnt = reinterpret_cast<uint32_t *>(fixed + kFxCnt) + group * kMegaMaxSlots;
-    uint32_t *s_last = reinterpret_cast<uint32_t *>(fixed + kFxLast);
-    const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t bar0 = smem_u32(fixed + kFxBars) + (uint32_t)group * kMegaMaxSlots * 8u;
-
+    const uint32_t NP = p.n_phases;
     const uint32_t pos = p.state[1], tick = *p.tick;
-    const uint32_t epoch0 = tick * (NP + 1u);  // phase ph writes with epoch0 + ph + 1
 
     // the phase table, the zero region, the arg-max slots and the ring barriers; one CTA barrier before anybody uses them
     {
         const uint4 *src = reinterpret_cast<const uint4 *>(p.phases);
-        uint4 *dst = reinterpret_cast<uint4 *>(hot);
+        uint4 *dst = reinterpret_cast<uint4 *>(sm_hot());
         for (uint32_t i = tid; i < NP * (uint32_t)(sizeof(Phase) / 16); i += kMegaThreads) dst[i] = src[i];
     }
-    if (tid < 64) zero[tid] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < 64) sm_zero()[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (gt < 16) {
-        bestv[gt] = -FLT_MAX;
-        reinterpret_cast<uint32_t *>(bestv)[16 + gt] = 0u;
+        sm_bestv(group)[gt] = -FLT_MAX;
+        reinterpret_cast<uint32_t *>(sm_bestv(group))[16 + gt] = 0u;
     }
     if (gt == 0) {
         for (int i = 0; i < kMegaMaxSlots; i++) {
-            mbar_init(bar0 + 8 * i, 1);
-            cnt[i] = 0;
+            mbar_init(sm_bar0(group) + 8 * i, 1);
+            sm_cnt(group)[i] = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
 
-    // this group's job count per phase, the length of its stage sequence, and its first copies
-    unsigned short *mt = reinterpret_cast<unsigned short *>(reinterpret_cast<unsigned char *>(hot) + (size_t)NP * sizeof(Phase)) + group * NP;
-    uint32_t *list = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(hot) + (size_t)NP * (sizeof(Phase) + 4)) + group * p.list_stride;
-    const uint32_t total = p.list_len[gi];
-    for (uint32_t i = gt; i < NP; i += 256u) mt[i] = (unsigned short)my_tiles_of(hot[i], gi, stride);
-    for (uint32_t i = gt; i < total; i += 256u) list[i] = p.lists[(size_t)gi * p.list_stride + i];
-    mega_group_barrier(group);
-    if (gt == 0)
-        for (uint32_t n = 0; n < S && n < total; n++) mega_issue(hot, list[n], ring_u32 + n * kSlotBytes, bar0 + 8 * n);
+    // this group's job count per phase, its stage list, and its first copies
+    {
+        const uint32_t gi = blockIdx.x + (uint32_t)group * gridDim.x;
+        const uint32_t total = p.list_len[gi];
+        const Phase *hot = sm_hot();
+        unsigned short *mt = sm_mt(p, group);
+        uint32_t *list = sm_list(p, group);
+        for (uint32_t i = gt; i < NP; i += 256u) mt[i] = (unsigned short)my_tiles_of(hot[i], (uint32_t)group);
+        for (uint32_t i = gt; i < total; i += 256u) list[i] = p.lists[(size_t)gi * p.list_stride + i];
+        mega_group_barrier(group);
+        if (gt == 0)
+            for (uint32_t n = 0; n < p.slots && n < total; n++)
+                mega_issue(hot, list[n], smem_u32(sm_ring(p, group)) + n * kSlotBytes, sm_bar0(group) + 8 * n);
+    }
 
     RingPos rp = {0u, 0u, 0u};
-    const uint32_t *hints = p.use_hints ? p.hint : nullptr;
 
     for (uint32_t ph = 0; ph < NP; ph++) {
+        const Phase *hot = sm_hot();
         const uint32_t kind = ph_kind(hot[ph]);
+        const uint32_t epoch0 = tick * (NP + 1u);  // phase ph writes with epoch0 + ph + 1
         const uint32_t epoch = epoch0 + ph + 1u;
         const uint32_t x_phase = hot[ph].x_phase;
         const uint32_t x_epoch = epoch0 + x_phase + 1u + p.epoch_skew;
+        const uint32_t *hints = p.use_hints ? p.hint : nullptr;
         if (p.prof && tid == 0) p.prof[((size_t)blockIdx.x * (NP + 1u) + ph) * 4] = global_ns();  // entering phase ph
 
         if (kind == kPhEmbed) {
@@ -591,8 +618,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         if (kind == kPhAttn) {
             if (blockIdx.x >= p.attn_units) continue;
             if (hints && tid == 0) hint_wait(hints + x_phase, (tick + 1u) * hot[x_phase].n_prod, p.status, p.wait_cycles);
-            __syncthreads();  // Q/K/V are there; and the other group has left the image of x that this scratch overlays
-            if (group == 0) {
+            __syncthreads();  // Q/K/V are there; and both groups have left the image of x that this scratch overlays
+            {
+                // all sixteen warps run the passes of the unit; group 0 then publishes / merges / stores
                 bool stored = false;
                 const uint32_t n_splits = p.attn.n_splits;
                 AttnUnit au;
@@ -606,15 +634,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
                 au.v_pairs = p.vec[kVecV];
                 au.in_epoch = x_epoch;
                 au.pos = pos;
+                au.prof = p.prof ? p.prof + ((size_t)blockIdx.x * (NP + 1u) + ph) * 4 : nullptr;
                 uint2 *outp = p.vec[kVecAtt];
-                attn_gqa_unit<GROUP, HD, true>(
-                    p.attn, au, blockIdx.x / n_splits, blockIdx.x % n_splits, gt, reinterpret_cast<float *>(scratch), s_last,
-                    [] { mega_group_barrier(0); },
+                attn_unit_staged<GROUP, HD, kMegaThreads>(
+                    p.attn, au, blockIdx.x / n_splits, blockIdx.x % n_splits, tid, reinterpret_cast<float *>(sm_scratch(p)),
+                    reinterpret_cast<uint32_t *>(mega_smem + kFxLast), [] { __syncthreads(); }, [] { mega_group_barrier(0); },
                     [&](uint32_t idx, float v) {
                         pair_store(outp + idx, __float_as_uint(v), epoch);
                         stored = true;
                     });
-                if (hints) {
+                if (hints && group == 0) {
                     // the unit that wrote this KV head's output (thread 0 takes part in those stores) announces it
                     mega_group_barrier(0);
                     if (gt == 0 && stored) atomicAdd(p.hint + ph, 1u);
@@ -627,8 +656,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             // by CTA 0: arg-max over the groups' records (ties to the highest index), then what argmax_kernel does at the
             // end of the multi-kernel token step
             if (blockIdx.x != 0) continue;
-            float *pickv = reinterpret_cast<float *>(fixed + kFxPick);
-            uint32_t *picki = reinterpret_cast<uint32_t *>(fixed + kFxPick + 64);
+            float *pickv = reinterpret_cast<float *>(mega_smem + kFxPick);
+            uint32_t *picki = reinterpret_cast<uint32_t *>(mega_smem + kFxPick + 64);
             if (hints && tid == 0) hint_wait(hints + x_phase, (tick + 1u) * hot[x_phase].n_prod, p.status, p.wait_cycles);
             __syncthreads();
             float bv = -FLT_MAX;
@@ -679,6 +708,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
 
         // ── matvec phase ─────────────────────────────────────────────────────────────────────────
         if (hot[ph].n_tiles <= blockIdx.x) continue;  // neither group of this CTA has a job here
+        const uint32_t gi = blockIdx.x + (uint32_t)group * gridDim.x;
         // the hidden-state value this lane will add to the row of its first job: requested before anything else (it was
         // complete long ago), settled in the epilogue
         uint2 res_pre = make_uint2(0u, 0u);
@@ -690,32 +720,32 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             const uint32_t *hw = hints ? hints + x_phase : nullptr;
             const uint32_t target = (tick + 1u) * hot[x_phase].n_prod;
             const uint2 *xp = p.vec[hot[ph].vecs & 0xFFu];
-            mega_stage(kind == kPhQ6K, scratch, xp, x_epoch, hot[ph].n_cols, hot[ph].norm_w, p.eps, red, inv_scale, hw, target, p.status,
+            mega_stage(kind == kPhQ6K, sm_scratch(p), xp, x_epoch, hot[ph].n_cols, hot[ph].norm_w, p.eps,
+                       reinterpret_cast<float *>(mega_smem + kFxRed), reinterpret_cast<float *>(mega_smem + kFxInvScale), hw, target, p.status,
                        p.wait_cycles, p.prof ? p.prof + ((size_t)blockIdx.x * (NP + 1u) + ph) * 4 : nullptr);
         }
-        if (hot[ph].n_tiles <= gi) continue;  // this group has no job in the phase (it only helped with the staging)
+        if (!ph_pair(hot[ph]) && hot[ph].n_tiles <= gi) continue;  // this group has no job in the phase (it only helped with the staging)
         if (kind == kPhQ4K)
-            mega_consume<false>(p, hot, mt, list, ph, gi, stride, S, total, rp, ring, ring_u32, bar0, cnt, scratch, zero, partial, bestv,
-                                inv_scale[0], epoch0, epoch, res_pre);
+            mega_consume<false>(p, ph, rp, tick, res_pre);
         else
-            mega_consume<true>(p, hot, mt, list, ph, gi, stride, S, total, rp, ring, ring_u32, bar0, cnt, scratch, zero, partial, bestv,
-                               inv_scale[0], epoch0, epoch, res_pre);
+            mega_consume<true>(p, ph, rp, tick, res_pre);
         if (p.prof && tid == 0) p.prof[((size_t)blockIdx.x * (NP + 1u) + ph) * 4 + 3] = global_ns();  // group 0's jobs done
         const bool to_logits = ((hot[ph].vecs >> 8) & 0xFFu) == kVecLogits;
-        if (hints && !to_logits) {
+        if (hints && !to_logits && !(ph_pair(hot[ph]) && group == 1)) {
             // every store of this group in this phase has been issued: announce it
             mega_group_barrier(group);
             if (gt == 0) atomicAdd(p.hint + ph, 1u);
         }
         if (to_logits) {
             // this group's arg-max over the rows it produced, as two pairs for the pick phase
+            const float *bestv = sm_bestv(group);
             mega_group_barrier(group);
             if (gt == 0) {
                 float bv = bestv[0];
-                uint32_t bi = reinterpret_cast<uint32_t *>(bestv)[16];
+                uint32_t bi = reinterpret_cast<const uint32_t *>(bestv)[16];
                 for (int i = 1; i < 16; i++) {
                     const float v = bestv[i];
-                    const uint32_t vi = reinterpret_cast<uint32_t *>(bestv)[16 + i];
+                    const uint32_t vi = reinterpret_cast<const uint32_t *>(bestv)[16 + i];
                     if (better(v, vi, bv, bi)) {
                         bv = v;
                         bi = vi;
@@ -790,17 +820,17 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     const uint32_t G = (uint32_t)m.sm_count;
     d->grid = G;
     uint32_t ns = G / m.n_kv_heads;
-    const uint32_t by_len = (m.max_seq_len + 31) / 32;
+    // A split is at least kMegaMinChunk positions: below that one unit per KV head is faster than several plus the
+    // merge (a ticket, a fence and two more L2 round trips), since a phase here costs latency, not bandwidth.
+    const uint32_t by_len = (m.max_seq_len + kMegaMinChunk - 1) / kMegaMinChunk;
     if (by_len < ns) ns = by_len;
     if (ns > (uint32_t)kGqaMaxSplits) ns = kGqaMaxSplits;
     if (ns < 1) return no("more KV heads than SMs");
     d->n_splits = ns;
     uint32_t mc = (m.max_seq_len + ns - 1) / ns;
-    if (mc < 32) mc = 32;
+    if (mc < kMegaMinChunk) mc = kMegaMinChunk;
     d->max_chunk = ((mc + 3) / 4) * 4;
-    const uint32_t nsl = 256 / (hd / 4);
-    const size_t attn_bytes = ((size_t)group * hd + 2 * hd + 16 + (size_t)group * d->max_chunk + (size_t)nsl * group * hd +
-                               2 * (size_t)group * kGqaMaxSplits) * sizeof(float);
+    const size_t attn_bytes = attn_staged_smem_floats((int)group, (int)hd) * sizeof(float);
     size_t scratch = attn_bytes;
     auto image = [&](const MegaTensor &t, uint32_t cols) {
         const size_t b = t.type == YULE_DTYPE_Q4_K ? q4_image_bytes(cols) : q6_image_bytes(cols);
@@ -823,8 +853,9 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
         auto tiles = [](uint32_t rows) { return (rows + 15) / 16; };
         auto chunks = [](uint32_t cols) { return (cols / 256 + 7) / 8; };
         auto mine = [&](uint32_t n_tiles) { return (n_tiles + 2 * G - 1) / (2 * G); };
+        auto mine_cta = [&](uint32_t n_tiles) { return (n_tiles + G - 1) / G; };  // pair phases: a CTA's groups share the tile
         const uint32_t per_layer = mine(tiles(qdim) + 2 * tiles(kvdim)) * chunks(dim) + mine(tiles(dim)) * chunks(qdim) +
-                                   mine(tiles(ff)) * 2 * chunks(dim) + mine(tiles(dim)) * chunks(ff);
+                                   mine_cta(tiles(ff)) * chunks(dim) + mine(tiles(dim)) * chunks(ff);
         const uint32_t longest = per_layer * m.n_layers + mine(tiles(m.vocab)) * chunks(dim);
         d->list_stride = (longest + 3) & ~3u;
         if (chunks(dim) > 64 || chunks(ff) > 64 || chunks(qdim) > 64 || tiles(m.vocab) >= (1u << 14) || tiles(ff) >= (1u << 14) ||
@@ -965,7 +996,7 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
         P.x_phase = x_phase;
         P.norm_w = norm_w;
         P.res_phase = res_phase;
-        P.n_prod = tiles < 2 * G ? tiles : 2 * G;
+        P.n_prod = pair ? (tiles < G ? tiles : G) : (tiles < 2 * G ? tiles : 2 * G);
         h->phases.push_back(P);
         return (uint32_t)h->phases.size() - 1;
     };
@@ -1012,24 +1043,22 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
             const uint32_t kind = P.kind & 0xFFu;
             if (kind != kPhQ4K && kind != kPhQ6K) continue;
             const bool pair = (P.kind & 0x100u) != 0;
-            for (uint32_t tile = gi; tile < P.n_tiles; tile += 2 * G)
-                for (uint32_t q = 0; q < (pair ? 2u : 1u); q++) {
-                    uint32_t seg = q, t = tile;
-                    if (!pair) {
-                        seg = 0;
-                        while (seg + 1 < P.n_seg && t >= (P.rows[seg] + 15) / 16) {
-                            t -= (P.rows[seg] + 15) / 16;
-                            seg++;
-                        }
+            // pair phase: tiles go to the CTAs, group 0 takes the gate tile and group 1 the up tile of the same rows
+            for (uint32_t tile = pair ? gi % G : gi; tile < P.n_tiles; tile += pair ? G : 2 * G) {
+                uint32_t seg = pair ? gi / G : 0, t = tile;
+                if (!pair)
+                    while (seg + 1 < P.n_seg && t >= (P.rows[seg] + 15) / 16) {
+                        t -= (P.rows[seg] + 15) / 16;
+                        seg++;
                     }
-                    for (uint32_t c = 0; c < (P.kind >> 16); c++) {
-                        if (n >= d.list_stride) {
-                            delete h;
-                            return cudaErrorInvalidValue;
-                        }
-                        lists[(size_t)gi * d.list_stride + n++] = stage_entry(ph, seg, c, t);
+                for (uint32_t c = 0; c < (P.kind >> 16); c++) {
+                    if (n >= d.list_stride) {
+                        delete h;
+                        return cudaErrorInvalidValue;
                     }
+                    lists[(size_t)gi * d.list_stride + n++] = stage_entry(ph, seg, c, t);
                 }
+            }
         }
         list_len[gi] = n;
     }
@@ -1082,7 +1111,7 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
     a.kv_stride = kvdim;
     a.n_splits = d.n_splits;
     a.max_chunk = d.max_chunk;
-    a.min_chunk = 32;
+    a.min_chunk = kMegaMinChunk;
     a.status = m.status;
     a.wait_cycles = m.wait_cycles;
     p.attn_units = m.n_kv_heads * d.n_splits;

@@ -747,7 +747,8 @@ int32_t ensure_graph(yule_cuda_runner *r) {
     }
     // With the persistent kernel the graph is that one launch: cooperative first, and if the capture or the
     // instantiation refuses the attribute, an ordinary launch of the same grid (one CTA per SM; its waits are bounded).
-    for (int attempt = 0; attempt < (r->mega ? 2 : 1); attempt++) {
+    const bool plain_first = knob("YULE_MEGA_COOP") && atoi(knob("YULE_MEGA_COOP")) == 0;  // timing aid: skip the cooperative attempt
+    for (int attempt = plain_first ? 1 : 0; attempt < (r->mega ? 2 : 1); attempt++) {
         cudaGraph_t graph = nullptr;
         if (r->mega) mega_set_cooperative(r->mega, attempt == 0);
         YULE_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
