@@ -472,6 +472,9 @@ int32_t ensure_sampler_scratch(yule_cuda_ctx *ctx, size_t n_floats);
 cudaError_t encode_tensor_map_2d(const void *base, uint32_t elem_bytes, uint64_t inner, uint64_t n_rows, uint64_t row_stride_bytes,
                                  uint32_t box_inner, uint32_t box_rows, void *out);
 
+cudaError_t cached_tensor_map_2d(const void *base, uint32_t elem_bytes, uint64_t inner, uint64_t n_rows, uint64_t row_stride_bytes,
+                                 uint32_t box_inner, uint32_t box_rows, void *out);
+
 // Persistent decode kernel (decode_mega.cu): the whole token step of a dense Llama-family model in one cooperative
 // launch.  Covers: one GPU, no architecture variant, Q4_K attn_q/k/v and ffn_gate/up, Q4_K or Q6_K (row-planar copy)
 // attn_output / ffn_down / output matrix, grouped-query head shapes that were instantiated.

@@ -44,6 +44,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
+#include <unordered_map>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -904,6 +906,43 @@ cudaError_t encode_weight_map(const uint8_t *w, uint32_t n_rows, uint32_t n_cols
 uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 64 ? 64 : 128); }
 
 }  // namespace
+
+// The same through a per-process cache: a map depends on the address and the shape only, and encoding one costs a
+// driver call, which the matvec entry points would otherwise pay on every launch.
+cudaError_t cached_tensor_map_2d(const void *base, uint32_t elem_bytes, uint64_t inner, uint64_t n_rows, uint64_t row_stride_bytes,
+                                 uint32_t box_inner, uint32_t box_rows, void *out) {
+    struct Key {
+        const void *base;
+        uint64_t inner, n_rows, stride;
+        uint32_t elem, box_inner, box_rows;
+        bool operator==(const Key &o) const {
+            return base == o.base && inner == o.inner && n_rows == o.n_rows && stride == o.stride && elem == o.elem &&
+                   box_inner == o.box_inner && box_rows == o.box_rows;
+        }
+    };
+    struct Hash {
+        size_t operator()(const Key &k) const {
+            size_t h = std::hash<const void *>()(k.base);
+            for (uint64_t v : {k.inner, k.n_rows, k.stride, (uint64_t)k.elem, (uint64_t)k.box_inner, (uint64_t)k.box_rows})
+                h = h * 0x9E3779B97F4A7C15ull + std::hash<uint64_t>()(v);
+            return h;
+        }
+    };
+    static std::unordered_map<Key, CUtensorMap, Hash> cache;
+    static std::mutex mu;
+    const Key key{base, inner, n_rows, row_stride_bytes, elem_bytes, box_inner, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        cudaError_t e = encode_tensor_map_2d(base, elem_bytes, inner, n_rows, row_stride_bytes, box_inner, box_rows, &m);
+        if (e != cudaSuccess) return e;
+        if (cache.size() >= 16384) cache.clear();
+        it = cache.emplace(key, m).first;
+    }
+    memcpy(out, &it->second, sizeof(CUtensorMap));
+    return cudaSuccess;
+}
 
 // Tiled 2-D tensor map over rows of `elem_bytes`-sized elements (1 or 8): `inner` elements per row, `n_rows` rows
 // `row_stride_bytes` apart (a multiple of 16; base 16-byte aligned), box of box_inner x box_rows elements, no

@@ -598,9 +598,9 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         f.late_wait = a.late_wait;
         f.status = a.status;
         f.wait_cycles = a.wait_cycles;
-        // independent call on a short matrix → ring kernel (overlaps with its predecessor; measured 2.3 against 5.4 µs at
-        // 1024x4096, level at 4096x4096, behind from 14336 rows on); dependent chain or longer matrix → streaming kernel
-        bool ring = a.pdl && a.late_wait && (a.n_rows + 15) / 16 <= 2u * (uint32_t)sm_count;
+        // independent call → ring kernel (overlaps with its predecessor; measured against the streaming kernel: 5.1 / 6.7 µs at
+        // 4096x4096, 12.7 / 14.5 at 14336x4096, 93 / 91 at 128256x4096); dependent chain or very long matrix → streaming kernel
+        bool ring = a.pdl && a.late_wait && (a.n_rows + 15) / 16 <= 8u * (uint32_t)sm_count;
         if (const char *k = knob("YULE_QMV_RING")) ring = atoi(k) != 0;
         return ring ? launch_q6k_mma(f, sm_count, s, launches) : launch_q6k_stream(f, sm_count, s, launches);
     }

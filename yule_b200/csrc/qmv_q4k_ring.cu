@@ -26,6 +26,7 @@
 
 #include <cstdlib>
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -44,6 +45,9 @@ constexpr size_t kFullSmSmem = 227 * 1024;
 constexpr size_t kRingPartialBytes = (size_t)kGroups * 2 * 2 * kWarps * 16 * sizeof(float);  // [group][buffer][matrix][warp][row]
 
 struct Q4kRingParams {
+    // One tiled view per matrix (8-byte elements, box = 16 rows x the shared-memory row pitch): a stage is ONE copy
+    // instruction.  A copy per row (16 per stage) cost the issuing warp about 0.7 µs, on the critical path of its group.
+    CUtensorMap map[3];
     const uint8_t *w[3];
     float *out[3];
     uint32_t seg_tiles[3];
@@ -140,21 +144,21 @@ __device__ __forceinline__ void locate_job(const Q4kRingParams &p, uint32_t tile
     seg_tile = tile;
 }
 
-// Issues the copies of one stage; called by a whole (converged) warp.
+// Issues the copy of one stage; called by a whole (converged) warp, done by its first lane.  The box is as wide as the
+// shared-memory row pitch, so the padding between rows comes with the copy (what lies beyond the eight super-blocks of
+// the chunk — the next block, the next row or zeros — is never read); rows past the end of the matrix arrive as zeros.
 __device__ __forceinline__ void issue_stage(const Q4kRingParams &p, const Cur &u, uint32_t first_tile, uint32_t tile_stride,
                                             uint32_t bpr, uint32_t dst, uint32_t bar, int lane) {
-    uint32_t seg, tile;
-    locate_job(p, first_tile + u.k * tile_stride, u.q, seg, tile);
-    const uint32_t row0 = tile * kStageRows;
-    const uint32_t left = p.seg_rows[seg] - row0;
-    const uint32_t rows = left < (uint32_t)kStageRows ? left : (uint32_t)kStageRows;
-    const uint32_t blk0 = u.c * kStageBlocks;
-    const uint32_t nblk = bpr - blk0 < (uint32_t)kStageBlocks ? bpr - blk0 : (uint32_t)kStageBlocks;
-    const uint32_t bytes = nblk * 144u;
-    if (lane == 0) mbar_arrive_expect_tx(bar, rows * bytes);
+    (void)bpr;
+    if (lane == 0) {
+        uint32_t seg, tile;
+        locate_job(p, first_tile + u.k * tile_stride, u.q, seg, tile);
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                     "l"(reinterpret_cast<uint64_t>(&p.map[seg])), "r"(bar), "r"(u.c * kStageBlocks * 18u), "r"(tile * kStageRows)
+                     : "memory");
+    }
     __syncwarp();
-    if ((uint32_t)lane < rows)
-        bulk_g2s(dst + (uint32_t)lane * kRowPitch, p.w[seg] + ((size_t)(row0 + lane) * bpr + blk0) * 144u, bytes, bar);
 }
 
 __device__ __forceinline__ void ring_group_barrier(int group) {
@@ -496,6 +500,11 @@ bool q4k_ring_supported(const Q4kFused &f) {
 
 cudaError_t launch_q4k_ring(const Q4kFused &f, int sm_count, cudaStream_t s, uint64_t *launches) {
     Q4kRingParams p = {};
+    for (uint32_t i = 0; i < f.n_seg; i++) {
+        const uint32_t bpr_i = f.n_cols / 256;
+        cudaError_t me = cached_tensor_map_2d(f.w[i], 8, (uint64_t)bpr_i * 18, f.rows[i], (uint64_t)bpr_i * 144, kRowPitch / 8, kStageRows, &p.map[i]);
+        if (me != cudaSuccess) return me;
+    }
     const bool pair = f.swiglu_pair;
     uint32_t n_tiles = 0;
     for (uint32_t i = 0; i < f.n_seg; i++) {

@@ -22,6 +22,7 @@
 // 16 rows × eight (Q8_0) or sixteen (Q4_0) 128-column groups (one or two per warp), slots refilled by the warp that releases them last, every
 // wait bounded.  Activation staging is per group (each warp converts the columns it multiplies).
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -244,6 +245,7 @@ __device__ __forceinline__ float stage_x_group(const XImage &sm, const float *__
 }
 
 struct RingParams {
+    CUtensorMap map;  // tiled view of the matrix (8-byte elements, box = 16 rows x the shared-memory row pitch): one copy per stage
     const uint8_t *w;
     float *out;
     uint32_t n_rows, n_cols, n_tiles;
@@ -258,17 +260,18 @@ struct RingParams {
 template <bool Q8>
 __device__ __forceinline__ void issue_stage(const RingParams &p, uint32_t tile, uint32_t chunk, uint32_t n_sg, uint32_t dst,
                                             uint32_t bar, int lane) {
+    // One tiled copy per stage, by the first lane (a copy per row, 16 per stage, cost the issuing warp about 0.7 µs on
+    // the critical path of its group).  The box is as wide as the shared-memory row pitch; what lies beyond the chunk's
+    // groups is never read, rows past the end of the matrix arrive as zeros.
     using F = Fmt<Q8>;
-    const uint32_t row0 = tile * kStageRows;
-    const uint32_t left = p.n_rows - row0;
-    const uint32_t rows = left < (uint32_t)kStageRows ? left : (uint32_t)kStageRows;
-    const uint32_t sg0 = chunk * F::kStageSgs;
-    const uint32_t nsg = n_sg - sg0 < F::kStageSgs ? n_sg - sg0 : F::kStageSgs;
-    const uint32_t bytes = nsg * F::kSgBytes;  // a multiple of 16: the group count of a chunk is even
-    if (lane == 0) mbar_arrive_expect_tx(bar, rows * bytes);
+    (void)n_sg;
+    if (lane == 0) {
+        mbar_arrive_expect_tx(bar, F::kStageBytes);
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                     "l"(reinterpret_cast<uint64_t>(&p.map)), "r"(bar), "r"(chunk * F::kStageSgs * (F::kSgBytes / 8u)), "r"(tile * kStageRows)
+                     : "memory");
+    }
     __syncwarp();
-    if ((uint32_t)lane < rows)
-        bulk_g2s(dst + (uint32_t)lane * F::kRowPitch, p.w + ((size_t)(row0 + lane) * n_sg + sg0) * F::kSgBytes, bytes, bar);
 }
 
 // The 32-bit word `i` of the quants of a block whose bytes start at `qs` (2-byte aligned) in shared memory.
@@ -470,6 +473,11 @@ template <bool Q8>
 cudaError_t launch_variant(const QmvArgs &a, int sm_count, cudaStream_t s) {
     using F = Fmt<Q8>;
     RingParams p = {};
+    {
+        const uint64_t row_bytes = (uint64_t)(a.n_cols / 128) * F::kSgBytes;
+        cudaError_t me = cached_tensor_map_2d(a.w, 8, row_bytes / 8, a.n_rows, row_bytes, F::kRowPitch / 8, kStageRows, &p.map);
+        if (me != cudaSuccess) return me;
+    }
     p.w = a.w;
     p.out = a.out;
     p.n_rows = a.n_rows;
