@@ -53,8 +53,8 @@ if ROOT not in sys.path:
 
 N_PROMPT, N_GEN = 32, 128
 # DRAM bytes of one 5632x2048 launch of the ring kernel, from the ncu capture summarised in the named file
-RING_TRAFFIC_BYTES = None
-RING_TRAFFIC_SOURCE = "profiles/qmv_q4k_ring_5632x2048.md (ncu capture of one launch; null until captured for this kernel)"
+RING_TRAFFIC_BYTES = 6534144
+RING_TRAFFIC_SOURCE = "profiles/qmv_q4k_ring_5632x2048.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture)"
 METRIC = "batch-1 decode tokens/s; Q4_K matvec achieved HBM GB/s vs B200 peak"
 UNIT = "tokens/s"
 

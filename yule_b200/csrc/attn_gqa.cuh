@@ -472,18 +472,21 @@ __device__ __forceinline__ void attn_gqa_unit(const AttnParams &p, const AttnUni
 // the weighted sum then run out of shared memory, C positions per pass, with a running (max, Σexp) across passes.
 // Inputs are (value, epoch) pairs; plain Llama attention (no window, no soft-cap).  Splits, tickets, merge and
 // output are those of attn_gqa_unit.
-constexpr size_t attn_staged_smem_floats(int group, int hd) {
+constexpr size_t attn_staged_smem_floats(int hpu, int hd) {
     const int c = 4096 / hd;
-    const size_t front = (size_t)group * hd + 2 * hd + 32 + (size_t)group * c;
+    const size_t front = (size_t)hpu * hd + 2 * hd + 32 + (size_t)hpu * c;
     const size_t kv = (size_t)c * (hd + 4) + (size_t)c * hd;
-    const size_t nv = (size_t)group * hd / 4;
-    const size_t work = 4 * (nv > (size_t)kThreads ? nv : (size_t)kThreads) + 2 * (size_t)group * kGqaMaxSplits;
+    const size_t nv = (size_t)hpu * hd / 4;
+    const size_t work = 4 * (nv > (size_t)kThreads ? nv : (size_t)kThreads) + 2 * (size_t)hpu * kGqaMaxSplits;
     return front + (kv > work ? kv : work);
 }
 
+// A unit serves GROUP consecutive query heads (unit index `uh`: heads uh·GROUP …) that share KV head `kvh`; the
+// persistent kernel uses GROUP = 1 (a unit per query head: at the contexts where a phase is latency-bound the
+// passes of eight heads in one CTA cost more than reading the K / V rows, which sit in L2, eight times).
 template <int GROUP, int HD, int NT, class SyncAll, class Sync, class Store>
-__device__ __forceinline__ void attn_unit_staged(const AttnParams &p, const AttnUnit &au, uint32_t kvh, uint32_t split, uint32_t tid,
-                                                 float *sm, uint32_t *s_last, SyncAll sync_all, Sync sync, Store store) {
+__device__ __forceinline__ void attn_unit_staged(const AttnParams &p, const AttnUnit &au, uint32_t uh, uint32_t kvh, uint32_t split,
+                                                 uint32_t tid, float *sm, uint32_t *s_last, SyncAll sync_all, Sync sync, Store store) {
     // NT threads (tid 0..NT-1, meeting at sync_all) run the passes; the first kThreads of them (meeting at sync)
     // publish / merge / store.
     constexpr int C = 4096 / HD;  // positions per pass
@@ -494,7 +497,7 @@ __device__ __forceinline__ void attn_unit_staged(const AttnParams &p, const Attn
     constexpr int NOUT = (GROUP * HD + kThreads - 1) / kThreads;
     constexpr int NACC = (GROUP * HD + NT - 1) / NT;
     constexpr int QIT = (GROUP * (HD / 2) + NT - 1) / NT;
-    const uint32_t head0 = kvh * GROUP, pos = au.pos, seq = pos + 1;
+    const uint32_t head0 = uh * GROUP, pos = au.pos, seq = pos + 1;
     uint32_t eff = (seq + p.min_chunk - 1) / p.min_chunk;
     eff = eff < 1 ? 1 : (eff > p.n_splits ? p.n_splits : eff);
     if (split >= eff) return;
@@ -651,25 +654,42 @@ __device__ __forceinline__ void attn_unit_staged(const AttnParams &p, const Attn
             }
         }
         sync_all();
-        // Σ_t weight_t · V[t]: every thread owns NACC (head, dimension) outputs; two chains per output
+        // Σ_t weight_t · V[t].  With at least NT outputs every thread owns NACC (head, dimension) outputs; with fewer, PG
+        // threads share an output (positions pg, pg + PG, …) and meet in shared memory (the K rows are done with).
+        if (GROUP * HD >= NT) {
 #pragma unroll
-        for (int k = 0; k < NACC; k++) {
-            const uint32_t idx = tid + k * NT;
-            if (idx < GROUP * HD) {
-                const uint32_t h = idx / HD, d = idx % HD;
-                const float *w = sc + h * C;
-                const float *v = Vs + d;
-                float a = acc[k] * alpha[h], b = 0.f;
-                uint32_t t = 0;
-                for (; t + 4 <= n; t += 4) {
-                    const float4 w4 = *reinterpret_cast<const float4 *>(w + t);
-                    a = fmaf(w4.x, v[(size_t)t * HD], a);
-                    b = fmaf(w4.y, v[(size_t)(t + 1) * HD], b);
-                    a = fmaf(w4.z, v[(size_t)(t + 2) * HD], a);
-                    b = fmaf(w4.w, v[(size_t)(t + 3) * HD], b);
+            for (int k = 0; k < NACC; k++) {
+                const uint32_t idx = tid + k * NT;
+                if (idx < GROUP * HD) {
+                    const uint32_t h = idx / HD, d = idx % HD;
+                    const float *w = sc + h * C;
+                    const float *v = Vs + d;
+                    float a = acc[k] * alpha[h], b = 0.f;
+                    uint32_t t = 0;
+                    for (; t + 4 <= n; t += 4) {
+                        const float4 w4 = *reinterpret_cast<const float4 *>(w + t);
+                        a = fmaf(w4.x, v[(size_t)t * HD], a);
+                        b = fmaf(w4.y, v[(size_t)(t + 1) * HD], b);
+                        a = fmaf(w4.z, v[(size_t)(t + 2) * HD], a);
+                        b = fmaf(w4.w, v[(size_t)(t + 3) * HD], b);
+                    }
+                    for (; t < n; t++) a = fmaf(w[t], v[(size_t)t * HD], a);
+                    acc[k] = a + b;
                 }
-                for (; t < n; t++) a = fmaf(w[t], v[(size_t)t * HD], a);
-                acc[k] = a + b;
+            }
+        } else {
+            constexpr int NVO = GROUP * HD, PG = NT / (NVO > NT ? NT : NVO);
+            const uint32_t idx = tid % NVO, pg = tid / NVO;
+            const uint32_t h = idx / HD, d = idx % HD;
+            float a = 0.f;
+            for (uint32_t t = pg; t < n; t += PG) a = fmaf(sc[h * C + t], Vs[(size_t)t * HD + d], a);
+            Ks[pg * NVO + idx] = a;
+            sync_all();
+            if (tid < (uint32_t)NVO) {
+                float sum = 0.f;
+#pragma unroll
+                for (int g2 = 0; g2 < PG; g2++) sum += Ks[g2 * NVO + tid];
+                acc[0] = fmaf(acc[0], alpha[h], sum);
             }
         }
         sync_all();  // before the next pass (or the hand-over) reuses the rows and the scores
@@ -690,5 +710,5 @@ __device__ __forceinline__ void attn_unit_staged(const AttnParams &p, const Attn
         const uint32_t idx = tid + k * kThreads;
         o[k] = idx < GROUP * HD ? Vs[idx] : 0.f;
     }
-    attn_gqa_finish<GROUP, HD>(p, au.scratch, au.tickets, kvh, split, eff, lo < hi, tid, o, ml, Ks, s_last, sync, store);
+    attn_gqa_finish<GROUP, HD>(p, au.scratch, au.tickets, uh, split, eff, lo < hi, tid, o, ml, Ks, s_last, sync, store);
 }
