@@ -546,7 +546,7 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
     }
 }
 
-template <int GROUP, int HD>
+template <int HD>
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __grid_constant__ MegaParams p) {
     const uint32_t tid = threadIdx.x;
     const int lane = tid & 31, group = tid >> 8;
@@ -620,9 +620,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             if (hints && tid == 0) hint_wait(hints + x_phase, (tick + 1u) * hot[x_phase].n_prod, p.status, p.wait_cycles);
             __syncthreads();  // Q/K/V are there; and both groups have left the image of x that this scratch overlays
             {
-                // all sixteen warps run the passes of the unit; group 0 then publishes / merges / stores
+                // a unit per (query head, split); all sixteen warps run its passes, group 0 then publishes / merges / stores
                 bool stored = false;
                 const uint32_t n_splits = p.attn.n_splits;
+                const uint32_t head = blockIdx.x / n_splits;
                 AttnUnit au;
                 au.k_cache = reinterpret_cast<float *>(hot[ph].ptr[0]);
                 au.v_cache = reinterpret_cast<float *>(hot[ph].ptr[1]);
@@ -636,9 +637,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
                 au.pos = pos;
                 au.prof = p.prof ? p.prof + ((size_t)blockIdx.x * (NP + 1u) + ph) * 4 : nullptr;
                 uint2 *outp = p.vec[kVecAtt];
-                attn_unit_staged<GROUP, HD, kMegaThreads>(
-                    p.attn, au, blockIdx.x / n_splits, blockIdx.x % n_splits, tid, reinterpret_cast<float *>(sm_scratch(p)),
-                    reinterpret_cast<uint32_t *>(mega_smem + kFxLast), [] { __syncthreads(); }, [] { mega_group_barrier(0); },
+                attn_unit_staged<1, HD, kMegaThreads>(
+                    p.attn, au, head, head / (p.attn.n_heads / p.attn.n_kv_heads), blockIdx.x % n_splits, tid,
+                    reinterpret_cast<float *>(sm_scratch(p)), reinterpret_cast<uint32_t *>(mega_smem + kFxLast), [] { __syncthreads(); },
+                    [] { mega_group_barrier(0); },
                     [&](uint32_t idx, float v) {
                         pair_store(outp + idx, __float_as_uint(v), epoch);
                         stored = true;
@@ -787,13 +789,7 @@ bool tensor_ok(const MegaTensor &t, bool allow_q6) {
     return t.type == YULE_DTYPE_Q4_K || (allow_q6 && t.type == YULE_DTYPE_Q6_K);
 }
 
-bool variant_built(uint32_t group, uint32_t hd) {
-#ifdef YULE_MEGA_ONE_VARIANT
-    return group == 8 && hd == 64;
-#else
-    return (hd == 64 && (group == 1 || group == 4 || group == 8)) || (hd == 128 && (group == 1 || group == 4 || group == 8));
-#endif
-}
+bool variant_built(uint32_t hd) { return hd == 64 || hd == 128; }
 
 size_t q4_image_bytes(uint32_t n_cols) { return (size_t)4 * n_cols + 2 * (size_t)(n_cols / 8); }
 size_t q6_image_bytes(uint32_t n_cols) { return 2 * (q6::x_plane_bytes(n_cols) + 64) + (size_t)(n_cols / 16) * 4; }
@@ -805,8 +801,8 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     };
     if (!m.n_layers || m.layers.size() != m.n_layers) return no("no layers");
     if (!m.n_kv_heads || m.n_heads % m.n_kv_heads) return no("head counts");
-    const uint32_t group = m.n_heads / m.n_kv_heads, hd = m.head_dim;
-    if (!variant_built(group, hd)) return no("no instantiation for this head shape");
+    const uint32_t hd = m.head_dim;
+    if (!variant_built(hd)) return no("no instantiation for this head dimension");
     const uint32_t dim = m.dim, qdim = m.n_heads * hd, kvdim = m.n_kv_heads * hd, ff = m.ff_dim;
     if (dim % 256 || qdim % 256 || ff % 256) return no("row lengths must be multiples of 256");
     if (m.sm_count < 1 || 2 * m.sm_count > kMegaThreads) return no("SM count");
@@ -819,18 +815,18 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     if (!tensor_ok(m.output, true) || !m.output_norm || !m.embd) return no("output matrix must be Q4_K or Q6_K");
     const uint32_t G = (uint32_t)m.sm_count;
     d->grid = G;
-    uint32_t ns = G / m.n_kv_heads;
+    uint32_t ns = G / m.n_heads;  // a unit per (query head, split)
     // A split is at least kMegaMinChunk positions: below that one unit per KV head is faster than several plus the
     // merge (a ticket, a fence and two more L2 round trips), since a phase here costs latency, not bandwidth.
     const uint32_t by_len = (m.max_seq_len + kMegaMinChunk - 1) / kMegaMinChunk;
     if (by_len < ns) ns = by_len;
     if (ns > (uint32_t)kGqaMaxSplits) ns = kGqaMaxSplits;
-    if (ns < 1) return no("more KV heads than SMs");
+    if (ns < 1) return no("more query heads than SMs");
     d->n_splits = ns;
     uint32_t mc = (m.max_seq_len + ns - 1) / ns;
     if (mc < kMegaMinChunk) mc = kMegaMinChunk;
     d->max_chunk = ((mc + 3) / 4) * 4;
-    const size_t attn_bytes = attn_staged_smem_floats((int)group, (int)hd) * sizeof(float);
+    const size_t attn_bytes = attn_staged_smem_floats(1, (int)hd) * sizeof(float);
     size_t scratch = attn_bytes;
     auto image = [&](const MegaTensor &t, uint32_t cols) {
         const size_t b = t.type == YULE_DTYPE_Q4_K ? q4_image_bytes(cols) : q6_image_bytes(cols);
@@ -882,7 +878,7 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     for (uint32_t i = 0; i < kVecCount; i++) d->off_vec[i] = take((size_t)vlen[i] * sizeof(uint2));
     d->off_best = take((size_t)2 * G * 2 * sizeof(uint2));
     d->off_scratch = take(((size_t)m.n_heads * ns * (hd + 2) + 4) * sizeof(float));
-    d->off_tickets = take((size_t)m.n_layers * m.n_kv_heads * sizeof(uint32_t));
+    d->off_tickets = take((size_t)m.n_layers * m.n_heads * sizeof(uint32_t));
     d->off_hint = take((size_t)d->n_phases * sizeof(uint32_t));
     d->off_tick = take(sizeof(uint32_t));
     auto maps_of = [](const MegaTensor &t) { return t.type == YULE_DTYPE_Q4_K ? 1u : 4u; };
@@ -897,9 +893,9 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     return true;
 }
 
-template <int GROUP, int HD>
+template <int HD>
 cudaError_t launch_variant(const MegaHandle &h, cudaStream_t s) {
-    auto kern = decode_token_kernel<GROUP, HD>;
+    auto kern = decode_token_kernel<HD>;
     static bool attr_done[64] = {};
     static std::mutex mu;
     {
@@ -1013,9 +1009,9 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
         Phase A = blank(kPhAttn);
         A.ptr[0] = reinterpret_cast<uint64_t>(L.k_cache);
         A.ptr[1] = reinterpret_cast<uint64_t>(L.v_cache);
-        A.ptr[2] = reinterpret_cast<uint64_t>(tickets + (size_t)l * m.n_kv_heads);
+        A.ptr[2] = reinterpret_cast<uint64_t>(tickets + (size_t)l * m.n_heads);
         A.x_phase = ph_qkv;
-        A.n_prod = m.n_kv_heads;
+        A.n_prod = m.n_heads;
         h->phases.push_back(A);
         const uint32_t ph_att = (uint32_t)h->phases.size() - 1;
         const uint32_t ph_o = matvec({L.o}, {dim}, qdim, false, kVecAtt, ph_att, nullptr, {kVecHidden}, last_hidden);
@@ -1114,7 +1110,7 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
     a.min_chunk = kMegaMinChunk;
     a.status = m.status;
     a.wait_cycles = m.wait_cycles;
-    p.attn_units = m.n_kv_heads * d.n_splits;
+    p.attn_units = m.n_heads * d.n_splits;
     p.slots = d.slots;
     p.scratch_bytes = d.scratch_bytes;
     p.hot_bytes = d.hot_bytes;
@@ -1142,17 +1138,8 @@ void mega_set_wait_cycles(MegaHandle *h, long long cycles) {
 
 cudaError_t mega_launch(const MegaHandle *h, cudaStream_t s, uint64_t *launches) {
     cudaError_t e = cudaErrorInvalidValue;
-#define YULE_MEGA_CASE(G_, H_) \
-    if (h->group == G_ && h->hd == H_) e = launch_variant<G_, H_>(*h, s)
-    YULE_MEGA_CASE(8, 64);
-#ifndef YULE_MEGA_ONE_VARIANT
-    YULE_MEGA_CASE(4, 64);
-    YULE_MEGA_CASE(1, 64);
-    YULE_MEGA_CASE(8, 128);
-    YULE_MEGA_CASE(4, 128);
-    YULE_MEGA_CASE(1, 128);
-#endif
-#undef YULE_MEGA_CASE
+    if (h->hd == 64) e = launch_variant<64>(*h, s);
+    if (h->hd == 128) e = launch_variant<128>(*h, s);
     if (e == cudaSuccess) *launches += 1;
     return e;
 }
