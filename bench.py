@@ -487,7 +487,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
         cfg, weights, prompt = build_model_70b(rank, world, args.workload)
     else:
         cfg, weights, prompt = build_model(rank, args.linear)
-    runner = CudaTransformerRunner(backend, cfg, weights, fused=1 if (tp or args.step == "graph") else 2)
+    runner = CudaTransformerRunner(backend, cfg, weights, fused=1 if ((tp and world > 1) or args.step == "graph") else 2)
     step_kind = runner.step_kind
 
     def job():

@@ -436,12 +436,33 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
     const uint32_t sstride = Q6 ? (first_half ? 64u : 0u) : 32u;  // bytes per super-block
 
     float acc0 = 0.f, acc1 = 0.f;
-    for (uint32_t k = 0; k < my_tiles; k++) {
-        if (k > 0 && has_res && gt < 128u && (gt & 7u) == 0u) {
-            // the hidden-state value this lane will add to its row: requested now, settled in the epilogue
-            const uint32_t row = (tile0 + k * tile_step) * 16u + (gt >> 3);
-            if (row < P.rows[0]) res_pre = pair_peek(p.vec[kVecHidden] + row);
+    const uint32_t rr = gt >> 3, w2 = gt & 7u;  // finishing threads (gt < 128): row of the tile, lane of the eight that add up a row
+    // Releases the slot just consumed when some later stage of the token will reuse it; the warp that releases it last
+    // refills it (one thread: a stage is one tiled copy per plane).
+    auto release = [&](uint32_t n_stage, uint32_t slot_used) {
+        if (n_stage + S < total) {
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_block();
+                const bool last = (atomicAdd(&cnt[slot_used], 1u) & 7u) == 7u;
+                if (last && !(p.dbg & 2u)) mega_issue(hot, list[n_stage + S], ring_u32 + slot_used * kSlotBytes, bar0 + 8 * slot_used);
+            }
+            __syncwarp();
         }
+    };
+    for (uint32_t k = 0; k < my_tiles; k++) {
+        // where this job's rows go: worked out before the multiplications, off the path from the last one to the stores
+        uint32_t seg = pair ? (uint32_t)group : 0u, tile = tile0 + k * tile_step;
+        if (!pair)
+            while (seg + 1 < P.n_seg && tile >= (P.rows[seg] + 15u) / 16u) {
+                tile -= (P.rows[seg] + 15u) / 16u;
+                seg++;
+            }
+        const uint32_t row = tile * 16u + rr;
+        const bool mine = gt < 128u && w2 == 0 && row < P.rows[seg];
+        const uint32_t ov = (P.vecs >> (8 + 8 * (pair ? 0u : seg))) & 0xFFu;
+        if (k > 0 && has_res && mine) res_pre = pair_peek(p.vec[kVecHidden] + row);  // settled in the epilogue
+        uint32_t last_n = 0, last_slot = 0;
         for (uint32_t c = 0; c < chunks; c++) {
             const uint32_t bar = bar0 + 8 * rp.slot;
             unsigned long long *sprof = (p.prof && blockIdx.x == 0 && tid == 0 && rp.n < 256u) ? p.prof + (size_t)gridDim.x * (p.n_phases + 1u) * 4 : nullptr;
@@ -467,16 +488,12 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
                                            reinterpret_cast<const float *>(ssrc + (size_t)blk * sstride), u, acc0, acc1);
                 }
             }
-            // release the slot when some later stage of the token will reuse it; the warp that releases it last refills it
-            if (rp.n + S < total) {
-                __syncwarp();
-                uint32_t last = 0;
-                if (lane == 0) {
-                    __threadfence_block();
-                    last = ((atomicAdd(&cnt[rp.slot], 1u) & 7u) == 7u) ? 1u : 0u;
-                    if (last && !(p.dbg & 2u)) mega_issue(hot, list[rp.n + S], ring_u32 + rp.slot * kSlotBytes, bar);
-                }
-                __syncwarp();
+            // the last stage of a job is released after the job's rows are on their way (below)
+            if (c + 1 < chunks) {
+                release(rp.n, rp.slot);
+            } else {
+                last_n = rp.n;
+                last_slot = rp.slot;
             }
             rp.n++;
             if (++rp.slot == S) {
@@ -502,47 +519,39 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
         // sums in a fixed tree).  The two partial buffers alternate between jobs, so the next job's sums cannot overtake
         // these reads (a warp passes the next barrier only after the first four warps have finished here).
         mega_group_barrier(group);
-        float s0 = 0.f;
-        uint32_t seg = pair ? (uint32_t)group : 0u, tile = tile0 + k * tile_step;
-        const uint32_t rr = gt >> 3, w2 = gt & 7u;
         if (gt < 128u) {
             const uint32_t nwu = bpr < 8u ? bpr : 8u;
-            s0 = w2 < nwu ? partial[(size_t)(k & 1u) * 256 + w2 * 16 + rr] : 0.f;
+            float s0 = w2 < nwu ? partial[(size_t)(k & 1u) * 256 + w2 * 16 + rr] : 0.f;
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) s0 += __shfl_xor_sync(0xffffffffu, s0, o);
             s0 *= invs;
-            if (!pair)
-                while (seg + 1 < P.n_seg && tile >= (P.rows[seg] + 15u) / 16u) {
-                    tile -= (P.rows[seg] + 15u) / 16u;
-                    seg++;
+            if (pair) {
+                // group 1 hands its up sums to group 0 through shared memory: the finishing warps of the two groups (256
+                // threads; both groups run the same number of jobs here) meet at a barrier of their own, the other warps
+                // go on with the next job
+                float *pairbuf = reinterpret_cast<float *>(mega_smem + kFxPairBuf) + (k & 1u) * 16;
+                if (group == 1 && mine) pairbuf[rr] = s0;
+                asm volatile("bar.sync 3, 256;" ::: "memory");
+                if (group == 0 && mine) {
+                    const float up = pairbuf[rr];
+                    s0 = (s0 / (1.0f + expf(-s0))) * up;  // silu_mul.cu: x / (1 + exp(−x)) * up
+                    pair_store(p.vec[ov] + row, __float_as_uint(s0), epoch);
                 }
-        }
-        const uint32_t row = tile * 16u + rr;
-        const bool mine = gt < 128u && w2 == 0 && row < P.rows[seg];
-        if (pair) {
-            // group 1 hands its up sums to group 0 through shared memory (both run the same number of jobs here)
-            float *pairbuf = reinterpret_cast<float *>(mega_smem + kFxPairBuf) + (k & 1u) * 16;
-            if (group == 1 && mine) pairbuf[rr] = s0;
-            __syncthreads();
-            if (group == 0 && mine) {
-                const float up = pairbuf[rr];
-                s0 = (s0 / (1.0f + expf(-s0))) * up;  // silu_mul.cu: x / (1 + exp(−x)) * up
-                pair_store(p.vec[(P.vecs >> 8) & 0xFFu] + row, __float_as_uint(s0), epoch);
-            }
-        } else if (mine) {
-            if (has_res) s0 += pair_settle(res_pre, p.vec[kVecHidden] + row, epoch0 + P.res_phase + 1u + p.epoch_skew, p.status, p.wait_cycles);
-            const uint32_t ov = (P.vecs >> (8 + 8 * seg)) & 0xFFu;
-            if (ov == kVecLogits) {
-                p.logits[row] = s0;
-                // running arg-max of the rows this lane finishes; rows come in rising order: ties go to the highest index
-                if (s0 >= bestv[rr]) {
-                    bestv[rr] = s0;
-                    reinterpret_cast<uint32_t *>(bestv)[16 + rr] = row;
+            } else if (mine) {
+                if (has_res) s0 += pair_settle(res_pre, p.vec[kVecHidden] + row, epoch0 + P.res_phase + 1u + p.epoch_skew, p.status, p.wait_cycles);
+                if (ov == kVecLogits) {
+                    p.logits[row] = s0;
+                    // running arg-max of the rows this lane finishes; rows come in rising order: ties go to the highest index
+                    if (s0 >= bestv[rr]) {
+                        bestv[rr] = s0;
+                        reinterpret_cast<uint32_t *>(bestv)[16 + rr] = row;
+                    }
+                } else {
+                    pair_store(p.vec[ov] + row, __float_as_uint(s0), epoch);
                 }
-            } else {
-                pair_store(p.vec[ov] + row, __float_as_uint(s0), epoch);
             }
         }
+        release(last_n, last_slot);
     }
 }
 
