@@ -873,6 +873,11 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     if (scratch + hot + kFxBytes + 2 * 2 * (size_t)kSlotBytes > kMegaSmemMax) return no("activation image too large for two ring slots per group");
     uint32_t slots = (uint32_t)((kMegaSmemMax - scratch - hot - kFxBytes) / (2 * (size_t)kSlotBytes));
     if (slots > (uint32_t)kMegaMaxSlots) slots = kMegaMaxSlots;
+    // Where it pays off.  The kernel wins where a token is a chain of short, latency-bound steps (TinyLlama class:
+    // 0.65 against 0.76 ms per token); where the steps are long enough to be bound by the weight stream (8B class:
+    // rows of 4096 / 14336 columns, whose image of x leaves room for two ring slots only) the multi-kernel graph with
+    // the streaming kernels is faster (2.2 against 3.0 ms per token), so such models keep it.
+    if (slots < (uint32_t)kMegaMaxSlots) return no("model too wide for the persistent kernel to pay off");
     d->slots = slots;
     d->smem = (size_t)2 * slots * kSlotBytes + scratch + hot + kFxBytes;
     // workspace layout

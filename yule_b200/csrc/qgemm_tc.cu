@@ -900,7 +900,7 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
 // (144 bytes) of 128 rows.  Rows past the end read as zeros (a block of zeros dequantises to 0).
 cudaError_t encode_weight_map(const uint8_t *w, uint32_t n_rows, uint32_t n_cols, CUtensorMap *out) {
     const uint64_t row_bytes = (uint64_t)(n_cols / 256) * 144;
-    return encode_tensor_map_2d(w, 1, row_bytes, n_rows, row_bytes, 144, kBM, out);
+    return cached_tensor_map_2d(w, 1, row_bytes, n_rows, row_bytes, 144, kBM, out);  // one driver call per (tensor, shape), not per launch
 }
 
 uint32_t pick_bn(uint32_t n_tokens) { return n_tokens <= 32 ? 32 : (n_tokens <= 64 ? 64 : 128); }

@@ -68,6 +68,7 @@ struct yule_cuda_runner {
     uint32_t *d_history = nullptr;  // greedy pick made after each position
     uint32_t *h_pinned = nullptr;   // staging for token ids (pinned)
     size_t h_pinned_cap = 0;
+    float *h_logits = nullptr;      // pinned landing buffer of the logits read-back (a copy into pageable memory is staged by the driver, slower)
 
     // Batched prefill on the tensor-core GEMM: chunk buffers, allocated on first use
     uint32_t pf_chunk = 0, pf_splits = 1;
@@ -1142,8 +1143,11 @@ int32_t step(yule_cuda_runner *r, uint32_t token, bool token_from_device) {
 int32_t read_logits(yule_cuda_runner *r, float *logits_out) {
     if (!logits_out) return YULE_OK;
     cudaStream_t s = r->ctx->stream;
-    YULE_CUDA_TRY(cudaMemcpyAsync(logits_out, r->logits, (size_t)r->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, s));
+    const size_t bytes = (size_t)r->cfg.vocab_size * 4;
+    if (!r->h_logits) YULE_CUDA_TRY(cudaMallocHost((void **)&r->h_logits, bytes));
+    YULE_CUDA_TRY(cudaMemcpyAsync(r->h_logits, r->logits, bytes, cudaMemcpyDeviceToHost, s));
     YULE_CUDA_TRY(cudaStreamSynchronize(s));
+    memcpy(logits_out, r->h_logits, bytes);
     return r->xchg ? yule_cuda_synchronize(r->ctx) : YULE_OK;  // reports a peer that never arrived
 }
 
@@ -1316,6 +1320,7 @@ int32_t yule_cuda_runner_destroy(yule_cuda_runner *r) {
     if (r->graph_exec) cudaGraphExecDestroy(r->graph_exec);
     if (r->bd_graph) cudaGraphExecDestroy(r->bd_graph);
     if (r->mega) mega_destroy(r->mega);
+    if (r->h_logits) cudaFreeHost(r->h_logits);
     if (r->h_pinned) cudaFreeHost(r->h_pinned);
     for (yule_buffer h : r->owned) yule_cuda_free(r->ctx, h);
     // collective: every rank destroys its runner at the same point (a runner whose creation failed half-way leaves
