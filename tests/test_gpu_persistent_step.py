@@ -64,6 +64,21 @@ def test_head_shapes(backend, oracle, heads, kv_heads, head_dim):
     run.close()
 
 
+@pytest.mark.parametrize("ff_dim,down", [(4608, DType.Q6_K), (4096, DType.Q4_K)], ids=["three_chunks_q6k", "two_chunks_q4k"])
+def test_rows_wider_than_a_stage(backend, oracle, ff_dim, down):
+    """A down projection with more than 2048 columns is several stages per tile; with few tiles the two groups of a CTA
+    share a tile, take half of the stages each and add their partial sums in shared memory."""
+    cfg = ModelConfig(dim=512, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, vocab_size=1000, ff_dim=ff_dim, max_seq_len=64)
+    weights = synth.synthetic_model(cfg, seed=17, std=0.05, linear=DType.Q4_K, ffn_down=down, output=DType.Q6_K)
+    ref = make_oracle_model(oracle, cfg, weights)
+    run = persistent_runner(backend, cfg, weights)
+    prompt = synth.tokens(4, 6, cfg.vocab_size)
+    assert guarded_rel_err(run.prefill(prompt), ref.prefill(prompt)) <= REL_TOL
+    for tok in (11, 12, 13):
+        assert guarded_rel_err(run.decode_step(tok), ref.decode_step(tok)) <= REL_TOL
+    run.close()
+
+
 def test_greedy_stream_identical(backend, oracle):
     weights = synth.synthetic_model(SMALL, seed=5, std=0.05, linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K)
     ref = make_oracle_model(oracle, SMALL, weights)

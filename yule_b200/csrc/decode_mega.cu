@@ -73,7 +73,7 @@ constexpr uint32_t kNoPhase = 0xFFFFFFFFu;
 struct Phase {
     uint64_t ptr[3];      // matvec: the matrices sharing x (raw Q4_K rows / row-planar Q6_K records); attention: K cache, V cache, tickets
     const float *norm_w;  // RMSNorm weights folded into the staging of x, or null
-    uint32_t kind;        // kind | pair << 8 | chunks << 16   (chunks: stages per (job, matrix))
+    uint32_t kind;        // kind | pair << 8 | k-split << 9 | chunks << 16   (chunks: stages per (job, matrix))
     uint32_t n_tiles;     // 16-row jobs (pair: of one matrix); pick: records to read
     uint32_t x_phase;     // the phase that wrote the input vector
     uint32_t res_phase;   // the phase that wrote the hidden state added to the rows, or kNoPhase
@@ -87,7 +87,11 @@ struct Phase {
 static_assert(sizeof(Phase) == 80, "copied to shared memory 16 bytes at a time");
 __device__ __forceinline__ uint32_t ph_kind(const Phase &P) { return P.kind & 0xFFu; }
 __device__ __forceinline__ bool ph_pair(const Phase &P) { return (P.kind & 0x100u) != 0; }
+__device__ __forceinline__ bool ph_ksplit(const Phase &P) { return (P.kind & 0x200u) != 0; }
+__device__ __forceinline__ bool ph_cta_jobs(const Phase &P) { return (P.kind & 0x300u) != 0; }  // tiles dealt to CTAs, the two groups share a tile
 __device__ __forceinline__ uint32_t ph_chunks(const Phase &P) { return P.kind >> 16; }
+// k-split phase: chunks [0, ph_split_at) go to group 0, the rest to group 1
+__device__ __forceinline__ uint32_t ph_split_at(const Phase &P) { return (ph_chunks(P) + 1u) / 2u; }
 __device__ __forceinline__ bool ph_matvec(const Phase &P) { return ph_kind(P) == kPhQ4K || ph_kind(P) == kPhQ6K; }
 
 struct MegaParams {
@@ -151,14 +155,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-// Jobs of a group in a phase.  Tiles are dealt round-robin to the groups of the grid, except in a pair phase
-// (SiLU(gate)·up), where they are dealt to the CTAs: group 0 multiplies the gate tile, group 1 the up tile of the same
-// rows, and they meet in shared memory (352 tiles over 148 CTAs is three rounds of one stage; over 296 groups as
-// gate+up jobs it was two rounds of two).
+// Jobs of a group in a phase.  Tiles are dealt round-robin to the groups of the grid, except where the two groups of
+// a CTA share a tile and meet in shared memory: a pair phase (SiLU(gate)·up: group 0 multiplies the gate tile, group 1
+// the up tile of the same rows; 352 tiles over 148 CTAs is three rounds of one stage, over 296 groups as gate+up jobs
+// it was two rounds of two) and a k-split phase (a matrix with few tiles and several chunks of columns, like the
+// down projection: the groups take half of the chunks each and group 0 adds the two partial sums).
 __device__ __forceinline__ uint32_t my_tiles_of(const Phase &P, uint32_t group) {
     if (!ph_matvec(P)) return 0u;
     const uint32_t G = gridDim.x;
-    const uint32_t first = ph_pair(P) ? blockIdx.x : blockIdx.x + group * G, stride = ph_pair(P) ? G : 2u * G;
+    const uint32_t first = ph_cta_jobs(P) ? blockIdx.x : blockIdx.x + group * G, stride = ph_cta_jobs(P) ? G : 2u * G;
     return P.n_tiles > first ? (P.n_tiles - first + stride - 1) / stride : 0u;
 }
 // A group's stage sequence over the whole token is a list built on the host (it depends on the model and the
@@ -418,9 +423,10 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
     const uint32_t epoch0 = tick * (p.n_phases + 1u), epoch = epoch0 + ph + 1u;
     const Phase &P = hot[ph];
     const uint32_t bpr = P.n_cols >> 8, chunks = ph_chunks(P);
-    const bool pair = ph_pair(P);
+    const bool pair = ph_pair(P), ksplit = ph_ksplit(P), shared_tile = pair || ksplit;
     const uint32_t my_tiles = mt[ph];
-    const uint32_t tile0 = pair ? blockIdx.x : gi, tile_step = pair ? gridDim.x : stride;
+    const uint32_t tile0 = shared_tile ? blockIdx.x : gi, tile_step = shared_tile ? gridDim.x : stride;
+    const uint32_t c_begin = (ksplit && group == 1) ? ph_split_at(P) : 0u, c_end = (ksplit && group == 0) ? ph_split_at(P) : chunks;
     const bool has_res = P.res_phase != kNoPhase;
     // lane constants (B column n = g is live only for g = t (hi part) and g = t + 4 (lo part))
     const bool feeds = (g & 3) == t;
@@ -463,7 +469,7 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
         const uint32_t ov = (P.vecs >> (8 + 8 * (pair ? 0u : seg))) & 0xFFu;
         if (k > 0 && has_res && mine) res_pre = pair_peek(p.vec[kVecHidden] + row);  // settled in the epilogue
         uint32_t last_n = 0, last_slot = 0;
-        for (uint32_t c = 0; c < chunks; c++) {
+        for (uint32_t c = c_begin; c < c_end; c++) {
             const uint32_t bar = bar0 + 8 * rp.slot;
             unsigned long long *sprof = (p.prof && blockIdx.x == 0 && tid == 0 && rp.n < 256u) ? p.prof + (size_t)gridDim.x * (p.n_phases + 1u) * 4 : nullptr;
             if (sprof) sprof[256 + rp.n] = global_ns();
@@ -489,7 +495,7 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
                 }
             }
             // the last stage of a job is released after the job's rows are on their way (below)
-            if (c + 1 < chunks) {
+            if (c + 1 < c_end) {
                 release(rp.n, rp.slot);
             } else {
                 last_n = rp.n;
@@ -525,16 +531,22 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) s0 += __shfl_xor_sync(0xffffffffu, s0, o);
             s0 *= invs;
-            if (pair) {
-                // group 1 hands its up sums to group 0 through shared memory: the finishing warps of the two groups (256
+            if (shared_tile) {
+                // group 1 hands its sums to group 0 through shared memory: the finishing warps of the two groups (256
                 // threads; both groups run the same number of jobs here) meet at a barrier of their own, the other warps
                 // go on with the next job
                 float *pairbuf = reinterpret_cast<float *>(mega_smem + kFxPairBuf) + (k & 1u) * 16;
                 if (group == 1 && mine) pairbuf[rr] = s0;
                 asm volatile("bar.sync 3, 256;" ::: "memory");
                 if (group == 0 && mine) {
-                    const float up = pairbuf[rr];
-                    s0 = (s0 / (1.0f + expf(-s0))) * up;  // silu_mul.cu: x / (1 + exp(−x)) * up
+                    const float other = pairbuf[rr];
+                    if (pair) {
+                        s0 = (s0 / (1.0f + expf(-s0))) * other;  // silu_mul.cu: x / (1 + exp(−x)) * up
+                    } else {
+                        s0 += other;
+                        if (has_res)
+                            s0 += pair_settle(res_pre, p.vec[kVecHidden] + row, epoch0 + P.res_phase + 1u + p.epoch_skew, p.status, p.wait_cycles);
+                    }
                     pair_store(p.vec[ov] + row, __float_as_uint(s0), epoch);
                 }
             } else if (mine) {
@@ -724,7 +736,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         // complete long ago), settled in the epilogue
         uint2 res_pre = make_uint2(0u, 0u);
         if (hot[ph].res_phase != kNoPhase && gt < 128u && (gt & 7u) == 0u) {
-            const uint32_t row = gi * 16u + (gt >> 3);
+            const uint32_t row = (ph_cta_jobs(hot[ph]) ? blockIdx.x : gi) * 16u + (gt >> 3);
             if (row < hot[ph].rows[0]) res_pre = pair_peek(p.vec[kVecHidden] + row);
         }
         {
@@ -735,14 +747,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
                        reinterpret_cast<float *>(mega_smem + kFxRed), reinterpret_cast<float *>(mega_smem + kFxInvScale), hw, target, p.status,
                        p.wait_cycles, p.prof ? p.prof + ((size_t)blockIdx.x * (NP + 1u) + ph) * 4 : nullptr);
         }
-        if (!ph_pair(hot[ph]) && hot[ph].n_tiles <= gi) continue;  // this group has no job in the phase (it only helped with the staging)
+        if (!ph_cta_jobs(hot[ph]) && hot[ph].n_tiles <= gi) continue;  // this group has no job in the phase (it only helped with the staging)
         if (kind == kPhQ4K)
             mega_consume<false>(p, ph, rp, tick, res_pre);
         else
             mega_consume<true>(p, ph, rp, tick, res_pre);
         if (p.prof && tid == 0) p.prof[((size_t)blockIdx.x * (NP + 1u) + ph) * 4 + 3] = global_ns();  // group 0's jobs done
         const bool to_logits = ((hot[ph].vecs >> 8) & 0xFFu) == kVecLogits;
-        if (hints && !to_logits && !(ph_pair(hot[ph]) && group == 1)) {
+        if (hints && !to_logits && !(ph_cta_jobs(hot[ph]) && group == 1)) {
             // every store of this group in this phase has been issued: announce it
             mega_group_barrier(group);
             if (gt == 0) atomicAdd(p.hint + ph, 1u);
@@ -1000,13 +1012,16 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
         P.vecs = x_vec;
         i = 0;
         for (uint32_t o : outs) P.vecs |= o << (8 + 8 * i++);
-        P.kind |= (pair ? 0x100u : 0u) | (((cols / 256 + 7) / 8) << 16);
+        const uint32_t n_chunks = (cols / 256 + 7) / 8;
+        // few tiles and several chunks of columns: the two groups of a CTA split the chunks of a tile between them
+        const bool ksplit = !pair && P.n_seg == 1 && n_chunks >= 2 && tiles <= G && *outs.begin() != kVecLogits;
+        P.kind |= (pair ? 0x100u : 0u) | (ksplit ? 0x200u : 0u) | (n_chunks << 16);
         P.n_cols = cols;
         P.n_tiles = tiles;
         P.x_phase = x_phase;
         P.norm_w = norm_w;
         P.res_phase = res_phase;
-        P.n_prod = pair ? (tiles < G ? tiles : G) : (tiles < 2 * G ? tiles : 2 * G);
+        P.n_prod = (pair || ksplit) ? (tiles < G ? tiles : G) : (tiles < 2 * G ? tiles : 2 * G);
         h->phases.push_back(P);
         return (uint32_t)h->phases.size() - 1;
     };
@@ -1052,16 +1067,19 @@ cudaError_t mega_setup(const MegaModel &m, void *workspace, cudaStream_t s, Mega
             const Phase &P = h->phases[ph];
             const uint32_t kind = P.kind & 0xFFu;
             if (kind != kPhQ4K && kind != kPhQ6K) continue;
-            const bool pair = (P.kind & 0x100u) != 0;
-            // pair phase: tiles go to the CTAs, group 0 takes the gate tile and group 1 the up tile of the same rows
-            for (uint32_t tile = pair ? gi % G : gi; tile < P.n_tiles; tile += pair ? G : 2 * G) {
-                uint32_t seg = pair ? gi / G : 0, t = tile;
-                if (!pair)
+            const bool pair = (P.kind & 0x100u) != 0, ksplit = (P.kind & 0x200u) != 0, shared_tile = pair || ksplit;
+            const uint32_t n_chunks = P.kind >> 16, split_at = (n_chunks + 1) / 2, grp = gi / G;
+            // pair / k-split phase: tiles go to the CTAs; group 0 takes the gate tile (or the first half of the chunks),
+            // group 1 the up tile of the same rows (or the second half)
+            const uint32_t c_begin = (ksplit && grp == 1) ? split_at : 0, c_end = (ksplit && grp == 0) ? split_at : n_chunks;
+            for (uint32_t tile = shared_tile ? gi % G : gi; tile < P.n_tiles; tile += shared_tile ? G : 2 * G) {
+                uint32_t seg = pair ? grp : 0, t = tile;
+                if (!shared_tile)
                     while (seg + 1 < P.n_seg && t >= (P.rows[seg] + 15) / 16) {
                         t -= (P.rows[seg] + 15) / 16;
                         seg++;
                     }
-                for (uint32_t c = 0; c < (P.kind >> 16); c++) {
+                for (uint32_t c = c_begin; c < c_end; c++) {
                     if (n >= d.list_stride) {
                         delete h;
                         return cudaErrorInvalidValue;
