@@ -2,31 +2,36 @@
 //
 // The token step of GpuTransformerRunner::forward (yule-infer/src/gpu_runner.rs:296-695) is a chain of
 // about five dependent matvec-sized dispatches per layer.  As separate kernels each link of that chain
-// pays a launch boundary, a cold start of its weight stream and a drain; at the TinyLlama shape those
-// fixed costs are several times the time HBM needs for the bytes.  This kernel runs the whole chain in
-// one cooperative launch of one CTA per SM:
+// pays a launch boundary and a cold start of its weight stream; at the TinyLlama shape those fixed costs are
+// several times the time HBM needs for the bytes.  This kernel runs the whole chain in one cooperative launch of
+// one 512-thread CTA per SM (two groups of eight warps):
 //
-//   * Weights.  Every 8-warp group owns a ring of shared-memory slots filled by 1-D bulk copies
-//     (raw Q4_K rows, or the row-planar Q6_K records).  The sequence of stages a group will consume —
-//     over every matvec of the token — is known up front, so the warp that releases a slot last
-//     refills it with the stage `slots` ahead, whatever phase that stage belongs to: the weight stream
-//     never stops at a phase boundary.
+//   * Weights.  Every group owns a ring of shared-memory slots, each filled by one tiled TMA copy per plane of a
+//     stage (16 rows × 8 super-blocks of raw Q4_K rows, or of the row-planar Q6_K records).  The sequence of stages
+//     a group will consume — over every matvec of the token — is a list built on the host, so the warp that
+//     releases a slot last refills it with the stage `slots` ahead, whatever phase that stage belongs to: the weight
+//     stream never stops at a phase boundary, and a phase's first weights are in shared memory before its input is.
 //   * Activations.  A vector that one phase produces and the next consumes lives in global memory as
-//     (value, epoch) pairs.  A producer stores each finished row as one 8-byte pair; a consumer polls the
-//     pairs while it builds its shared-memory image of x, so "the data has arrived" and "the data" are
-//     the same load.  The epoch is token counter × (phases + 1) + phase + 1: no flag is ever reset.
-//     A pair buffer is overwritten only by a phase whose CTAs have, through the vectors they polled,
-//     transitively waited for every reader of the previous contents.
-//   * Phases.  embedding row → per layer { RMSNorm + Q/K/V, RoPE + KV append + attention,
-//     o-proj + residual, RMSNorm + gate/up + SiLU·mul, down + residual } → RMSNorm + output matrix with a
-//     running arg-max → pick (ties to the highest index, yule-infer/src/sampler.rs:150-163), history
-//     and position advance.
+//     (value, epoch) pairs.  A producer stores each finished row as one 8-byte pair; a consumer polls the pairs while
+//     it builds its shared-memory image of x, so "the data has arrived" and "the data" are the same load.  The epoch
+//     is token counter × (phases + 1) + phase + 1: no flag is ever reset, and there is no grid barrier.
+//     A pair buffer is overwritten only by a phase whose CTAs have, through the vectors they polled, transitively
+//     waited for every reader of the previous contents.
+//   * Phases.  embedding row → per layer { RMSNorm + Q/K/V, RoPE + KV append + attention (a unit per query head and
+//     split, K / V rows staged in shared memory), o-proj + residual, RMSNorm + gate/up + SiLU·mul (a CTA's two groups
+//     take the gate and the up tile of the same rows), down + residual (the groups split the column chunks of a
+//     tile) } → RMSNorm + output matrix with a running arg-max → pick (ties to the highest index,
+//     yule-infer/src/sampler.rs:150-163), history and position advance.
 //   * Arithmetic is that of the tensor-pipe matvec kernels (qmv_q4k_ring.cu, qmv_q6k_ring.cu) and of the
 //     grouped-query attention kernel (attention.cu), whose device code this file includes.
+//   * Registers and L1.  With 224 KB of the SM given to shared memory L1 is tiny: a register spill, or a descriptor
+//     read from global memory, is an L2 round trip.  The kernel compiles without spills (128 registers per thread)
+//     and keeps its phase table, job counts and stage lists in shared memory; pointers into shared memory are
+//     derived where they are used rather than carried through the phase loop.
 //
-// Every wait (bulk copy, pair) is bounded; the first one that runs out records a status word and every
-// later wait returns at once, so a failed step ends in microseconds and the host reads the status.
-// No thread leaves the kernel early: all CTA- and group-wide barriers are reached whatever happened.
+// Every wait (copy, pair) is bounded; the first one that runs out records a status word and every later wait
+// returns at once, so a failed step ends in microseconds and the host reads the status.  No thread leaves the
+// kernel early: all CTA- and group-wide barriers are reached whatever happened.
 
 #include <cfloat>
 #include <cstring>
@@ -471,10 +476,7 @@ __device__ __forceinline__ void mega_consume(const MegaParams &p, uint32_t ph, R
         uint32_t last_n = 0, last_slot = 0;
         for (uint32_t c = c_begin; c < c_end; c++) {
             const uint32_t bar = bar0 + 8 * rp.slot;
-            unsigned long long *sprof = (p.prof && blockIdx.x == 0 && tid == 0 && rp.n < 256u) ? p.prof + (size_t)gridDim.x * (p.n_phases + 1u) * 4 : nullptr;
-            if (sprof) sprof[256 + rp.n] = global_ns();
             if (!(p.dbg & 2u)) ring_wait(bar, rp.parity, p.status, p.wait_cycles);  // a wait that gave up has recorded it; go on with what is there
-            if (sprof) sprof[512 + rp.n] = global_ns();
             const uint32_t blk0 = c * 8u;
             const uint32_t nblk = bpr - blk0 < 8u ? bpr - blk0 : 8u;
             if ((uint32_t)wid < nblk && !(p.dbg & 1u)) {
@@ -913,7 +915,7 @@ bool mega_dims(const MegaModel &m, MegaDims *d, std::string *why) {
     d->off_maps = take((size_t)d->n_maps * sizeof(CUtensorMap));
     d->off_lists = take((size_t)2 * G * d->list_stride * sizeof(uint32_t));
     d->off_list_len = take((size_t)2 * G * sizeof(uint32_t));
-    d->off_prof = take(((size_t)G * (d->n_phases + 1) * 4 + 1024) * sizeof(unsigned long long));
+    d->off_prof = take((size_t)G * (d->n_phases + 1) * 4 * sizeof(unsigned long long));
     d->total = off;
     (void)kvdim;
     return true;
@@ -1190,7 +1192,7 @@ void mega_destroy(MegaHandle *h) {
     // timing aid (YULE_MEGA_PROF=<file> in a debug process): the stamps of the last token, with the phase kinds
     const char *path = knob("YULE_MEGA_PROF");
     if (h && h->params.prof && path) {
-        const size_t n = (size_t)h->grid * (h->params.n_phases + 1) * 4 + 1024;
+        const size_t n = (size_t)h->grid * (h->params.n_phases + 1) * 4;
         std::vector<unsigned long long> stamps(n);
         if (cudaMemcpy(stamps.data(), h->params.prof, n * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
             if (FILE *f = fopen(path, "wb")) {
