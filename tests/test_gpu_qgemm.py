@@ -114,3 +114,30 @@ def test_generic_format_gemm(backend, oracle, monkeypatch, dtype, n_rows, n_cols
     for b in range(0, batch, max(1, batch // 8)):
         ref = oracle.qmv(int(dtype), w, x[b * n_cols:(b + 1) * n_cols], n_rows, n_cols)
         assert guarded_rel_err(y[b], ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("dtype", [DType.Q4_K, DType.Q8_0, DType.Q6_K])
+@pytest.mark.parametrize("n_rows,n_cols,batch,forced", [
+    (256, 4096, 32, None),    # two tiles, sixteen super-blocks: four parts of four
+    (200, 2816, 16, None),    # eleven super-blocks: parts of six and five, ragged rows
+    (1280, 8192, 32, None),   # the Q/K/V slice of a 70B-class layer on eight GPUs
+    (2560, 2048, 24, 8),      # 160 work items: some CTAs take two
+])
+def test_column_split(backend, oracle, monkeypatch, dtype, n_rows, n_cols, batch, forced):
+    """With few row tiles and long rows the columns of a tile are split over several CTAs; the warp that stores its
+    part last adds the parts in their order.  Same result as the unsplit kernel to fp32 rounding, the same bits on
+    every launch (the tickets return to zero), parity with the scalar reference."""
+    w = synth.random_blocks(dtype, 700 + n_rows, n_rows * (n_cols // dtype.block_size))
+    x = synth.normal(701 + batch, batch * n_cols)
+    if forced:
+        monkeypatch.setenv("YULE_GEMM_KSPLIT", str(forced))
+    y = run(backend, w, x, n_rows, n_cols, batch, dtype=dtype)
+    again = run(backend, w, x, n_rows, n_cols, batch, dtype=dtype)
+    assert np.array_equal(y, again)
+    monkeypatch.setenv("YULE_GEMM_KSPLIT", "1")
+    whole = run(backend, w, x, n_rows, n_cols, batch, dtype=dtype)
+    assert not np.array_equal(y, whole), "the split did not take place"
+    assert np.abs(y - whole).max() <= 4e-6 * np.abs(whole).max()
+    for b in (0, batch // 2, batch - 1):
+        ref = oracle.qmv(int(dtype), w, x[b * n_cols:(b + 1) * n_cols], n_rows, n_cols)
+        assert guarded_rel_err(y[b], ref) <= REL_TOL

@@ -53,6 +53,9 @@ int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes) {
         cudaGetLastError();
         return fail(YULE_ERR_OUT_OF_MEMORY, "cuda allocation of %zu bytes of GEMM scratch failed", bytes);
     }
+    // the scratch opens with the split-column tickets of the GEMM, which the kernels expect (and leave) at zero
+    e = cudaMemset(ctx->gemm_scratch, 0, bytes < kGemmTicketBytes ? bytes : kGemmTicketBytes);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemset of the GEMM tickets");
     ctx->gemm_scratch_bytes = bytes;
     return YULE_OK;
 }

@@ -247,6 +247,11 @@ struct QGemm {
     int *status = nullptr;  // the context's device status word
     bool pdl = false;
 };
+// The scratch opens with the work area of the GEMM's column split: tickets (zero between launches), then one block of
+// partial results per work item; the activation tiles follow.
+constexpr size_t kGemmTicketBytes = 8192;
+constexpr uint32_t kGemmSplitMaxItems = 160;
+constexpr size_t kGemmSplitBytes = kGemmTicketBytes + (size_t)kGemmSplitMaxItems * 128 * 128 * sizeof(float);
 int32_t ensure_gemm_scratch(yule_cuda_ctx *ctx, size_t bytes);
 // Adds a buffer to the set the runner frees when it is destroyed (runner.cu).
 void runner_adopt_buffer(yule_cuda_runner *r, yule_buffer h);

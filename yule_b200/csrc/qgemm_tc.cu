@@ -86,6 +86,9 @@ struct GemmParams {
     uint32_t n_rows, n_cols, n_tokens, out_stride;
     uint32_t bn;           // activation rows per tile: 32, 64 or 128
     uint32_t n_mtiles, n_ntiles, stages;
+    uint32_t ksplit, sb_per;  // split of the columns: `ksplit` work items per tile, `sb_per` super-blocks each (the last may be shorter)
+    float *split_part;        // ksplit > 1: per work item a [bn][128] block of partial results
+    uint32_t *split_tickets;  // ksplit > 1: per (tile, drain warp) the number of items that have stored theirs; left at zero
     uint32_t type;         // GGUF type id of the weights (generic kernel)
     uint64_t w_row_bytes;  // bytes of one row of the weight tensor
     uint32_t unit_bytes;   // generic kernel: bytes of 256 columns of one row
@@ -120,12 +123,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__constant__ int c_gemm_spin;  // timing aid: poll with test_wait instead of try_wait
 // Bounded wait.  False: the CTA is giving up (this thread ran out of time, or another did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    const bool spin = c_gemm_spin != 0;
     for (uint32_t it = 1;; it++) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitCycles) {
@@ -309,6 +325,45 @@ struct RingPos {
     }
 };
 
+// A work item: tile (row tile x activation tile) and the range of super-blocks [sb0, sb1) of its columns.
+struct Item {
+    uint32_t tile, ks, mt, nt, sb0, sb1;
+};
+__device__ __forceinline__ Item decode_item(const GemmParams &p, uint32_t item, uint32_t bpr) {
+    Item r;
+    r.tile = item / p.ksplit;
+    r.ks = item - r.tile * p.ksplit;
+    r.mt = r.tile / p.n_ntiles;
+    r.nt = r.tile - r.mt * p.n_ntiles;
+    r.sb0 = r.ks * p.sb_per;
+    r.sb1 = r.sb0 + p.sb_per < bpr ? r.sb0 + p.sb_per : bpr;
+    return r;
+}
+// The (work item, super-block) pairs of this CTA in the order every role goes through them.
+struct UnitWalk {
+    uint32_t item, sb, sb1, mt;
+    bool live;
+    __device__ __forceinline__ void load(const GemmParams &p, uint32_t n_items, uint32_t bpr) {
+        live = item < n_items;
+        if (live) {
+            const Item it = decode_item(p, item, bpr);
+            sb = it.sb0;
+            sb1 = it.sb1;
+            mt = it.mt;
+        }
+    }
+    __device__ __forceinline__ void start(const GemmParams &p, uint32_t n_items, uint32_t bpr) {
+        item = blockIdx.x;
+        load(p, n_items, bpr);
+    }
+    __device__ __forceinline__ void next(const GemmParams &p, uint32_t n_items, uint32_t bpr) {
+        if (++sb == sb1) {
+            item += gridDim.x;
+            load(p, n_items, bpr);
+        }
+    }
+};
+
 // One row's share of a super-block: the 16-byte header (d, dmin, packed scales) and this thread's
 // 16 of the 32 quant bytes of each of the four 64-column groups.
 struct RowBlock {
@@ -380,8 +435,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t n_tiles = p.n_mtiles * p.n_ntiles;
-    const uint32_t n_kb = p.n_cols / kBK;
+    const uint32_t n_items = p.n_mtiles * p.n_ntiles * p.ksplit;
     const uint32_t bpr = p.n_cols / 256;  // super-blocks per row
 
     if (warp == kLoaderWarp) {
@@ -390,10 +444,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             uint32_t it = 0;
             RingPos ring;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const uint32_t nt = tile % p.n_ntiles;
-                const unsigned char *src = reinterpret_cast<const unsigned char *>(p.xb) + (size_t)nt * bpr * T::kSuperBytes;
-                for (uint32_t kb = 0; kb < n_kb; kb++, it++, ring.advance(p.stages)) {
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const Item wi = decode_item(p, item, bpr);
+                const unsigned char *src = reinterpret_cast<const unsigned char *>(p.xb) + (size_t)wi.nt * bpr * T::kSuperBytes;
+                for (uint32_t kb = 4 * wi.sb0; kb < 4 * wi.sb1; kb++, it++, ring.advance(p.stages)) {
                     const uint32_t s = ring.s, ph = ring.ph;
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                         ok = false;
@@ -425,8 +479,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             RingPos ring;
             long long tw0 = 0, tw1 = 0, ti = 0, tc = 0;
             const long long tstart = p.prof ? clock64() : 0;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                for (uint32_t kb = 0; kb < n_kb; kb++, it++, ring.advance(p.stages)) {
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const Item wi = decode_item(p, item, bpr);
+                for (uint32_t kb = 4 * wi.sb0; kb < 4 * wi.sb1; kb++, it++, ring.advance(p.stages)) {
                     const bool mine = (it & 1u) == parity_of_mine;  // the threads alternate stages
                     const uint32_t s = ring.s, ph = ring.ph;
                     const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
@@ -495,13 +550,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         }
     } else if (warp == kRawWarp) {
         if (!GENERIC && lane == 0) {
-            const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-            const uint32_t n_units = my_tiles * bpr;
-            for (uint32_t u = 0; u < n_units; u++) {
+            UnitWalk walk;
+            walk.start(p, n_items, bpr);
+            for (uint32_t u = 0; walk.live; u++, walk.next(p, n_items, bpr)) {
                 const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
                 if (!mbar_wait(bar_raw_empty + 8 * slot, ph ^ 1u, abort_flag, p.status)) break;
-                const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x, sb = u % bpr;
-                const uint32_t x = sb * 144u, y = (tile / p.n_ntiles) * kBM;  // byte column (a multiple of 16), first row
+                const uint32_t x = walk.sb * 144u, y = walk.mt * kBM;  // byte column (a multiple of 16), first row
+                if (p.skip & 64u) {  // timing aid: no raw bytes
+                    mbar_arrive(bar_raw_full + 8 * slot);
+                    continue;
+                }
                 mbar_arrive_expect_tx(bar_raw_full + 8 * slot, kRawBytes);
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -523,16 +581,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             const uint32_t in_core = (r >> 3) * 128 + (r & 7u) * 16;
             const uint32_t ub = p.unit_bytes, rstride = p.raw_stride, c16 = p.raw_chunks;
             const uint32_t slot_bytes = kBM * rstride;
-            const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-            const uint32_t n_units = my_tiles * bpr;
-            auto unit_start = [&](uint32_t u, uint32_t tile_row) {  // address of row `tile_row`'s bytes of unit u
-                const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x, sb = u % bpr;
-                uint32_t grow = (tile / p.n_ntiles) * kBM + tile_row;
+            auto unit_start = [&](const UnitWalk &w, uint32_t tile_row) {  // address of row `tile_row`'s bytes of the unit
+                uint32_t grow = w.mt * kBM + tile_row;
                 grow = grow < p.n_rows ? grow : p.n_rows - 1;
-                return reinterpret_cast<uintptr_t>(p.w) + (size_t)grow * p.w_row_bytes + (size_t)sb * ub;
+                return reinterpret_cast<uintptr_t>(p.w) + (size_t)grow * p.w_row_bytes + (size_t)w.sb * ub;
             };
-            auto copy_unit = [&](uint32_t u) {
-                if (u < n_units) {
+            auto copy_unit = [&](const UnitWalk &w, uint32_t u) {
+                if (w.live) {
                     const uint32_t dst0 = smem_u32(raw + (size_t)(u & 1u) * slot_bytes);
                     uint32_t row = 0, c = ptid;
                     while (c >= c16) {
@@ -540,7 +595,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                         row++;
                     }
                     for (uint32_t e = ptid; e < kBM * c16; e += 256) {
-                        const uintptr_t src = (unit_start(u, row) & ~(uintptr_t)15) + (size_t)c * 16;
+                        const uintptr_t src = (unit_start(w, row) & ~(uintptr_t)15) + (size_t)c * 16;
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + row * rstride + c * 16), "l"(src) : "memory");
                         c += 256;
                         while (c >= c16) {
@@ -553,14 +608,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             };
             RingPos ring;
             bool ok = true;
-            copy_unit(0);
-            for (uint32_t u = 0; u < n_units && ok; u++) {
-                copy_unit(u + 1);
+            UnitWalk cur, ahead;  // the unit being unpacked and the one being copied
+            cur.start(p, n_items, bpr);
+            ahead = cur;
+            copy_unit(ahead, 0);
+            for (uint32_t u = 0; cur.live && ok; u++, cur = ahead) {
+                ahead.next(p, n_items, bpr);
+                copy_unit(ahead, u + 1);
                 asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of unit u have landed
                 asm volatile("bar.sync 2, 256;" ::: "memory");         // and everyone else's
-                const uint32_t tile = blockIdx.x + (u / bpr) * gridDim.x;
-                const bool live = (tile / p.n_ntiles) * kBM + r < p.n_rows;
-                const unsigned char *rawrow = raw + (size_t)(u & 1u) * slot_bytes + (size_t)r * rstride + (unit_start(u, r) & 15u);
+                const bool live = cur.mt * kBM + r < p.n_rows;
+                const unsigned char *rawrow = raw + (size_t)(u & 1u) * slot_bytes + (size_t)r * rstride + (unit_start(cur, r) & 15u);
                 for (uint32_t g = 0; g < 4 && ok; g++, ring.advance(p.stages)) {
                     if (!mbar_wait(bar_empty + 8 * ring.s, ring.ph ^ 1u, abort_flag, p.status)) {
                         ok = false;
@@ -596,8 +654,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         } else {
-        const uint32_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const uint32_t n_units = my_tiles * bpr;  // (tile, super-block) pairs of this CTA, in order
         uint32_t it = 0;
         bool ok = true;
         const uint32_t in_core = (r >> 3) * 128 + (r & 7u) * 16;
@@ -665,7 +721,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 pf += c3 - c2;
             }
         };
-        for (uint32_t u = 0; u < n_units && ok; u++) {
+        UnitWalk walk;
+        walk.start(p, n_items, bpr);
+        for (uint32_t u = 0; walk.live && ok; u++, walk.next(p, n_items, bpr)) {
             const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
             if (!mbar_wait(bar_raw_full + 8 * slot, ph, abort_flag, p.status)) break;
             // row r of the box: 144 bytes; rows are 36 words apart, so eight lanes cover all 32 banks
@@ -693,20 +751,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         bool ok = true;
         long long dw = 0;
         const long long dstart = p.prof ? clock64() : 0;
-        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const uint32_t mt = tile / p.n_ntiles, nt = tile % p.n_ntiles;
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const Item wi = decode_item(p, item, bpr);
+            const uint32_t mt = wi.mt, nt = wi.nt;
             const uint32_t row = mt * kBM + lane_base + lane;
             const uint8_t *rowp = p.w + (size_t)(row < p.n_rows ? row : p.n_rows - 1) * bpr * 144;
             float acc[CW];
 #pragma unroll
             for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
-            uint32_t dd_cur = 0, dd_next = GENERIC ? 0u : __ldg(reinterpret_cast<const uint32_t *>(rowp));  // (d, dmin) of super-block 0
-            for (uint32_t kb = 0; kb < n_kb; kb++, it++) {
+            uint32_t dd_cur = 0, dd_next = GENERIC ? 0u : __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)wi.sb0 * 144));  // (d, dmin) of the first super-block
+            const uint32_t kb_end = 4 * wi.sb1;
+            for (uint32_t kb = 4 * wi.sb0; kb < kb_end; kb++, it++) {
                 if (p.skip & 32u) break;
                 const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
                 if (!GENERIC && (kb & 3u) == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
                     dd_cur = dd_next;
-                    if (kb + 4 < n_kb) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)((kb >> 2) + 1) * 144));
+                    if (kb + 4 < kb_end) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)((kb >> 2) + 1) * 144));
                 }
                 const float2 dd = GENERIC ? make_float2(1.f, 0.f) : __half22float2(as_half2(dd_cur));
                 const long long c0 = p.prof ? clock64() : 0;
@@ -740,6 +800,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             }
             if (!ok) break;
             const uint32_t n0 = nt * BN + col_base;
+            if (p.ksplit > 1) {
+                // This item covers a part of the columns.  Every drain warp stores its block of scaled partial sums, then
+                // takes a ticket of its (tile, warp); the warp that finds all the other parts stored adds them in the
+                // order of the parts (its own included, so the sum does not depend on who came last) and writes the result.
+                float *mine = p.split_part + (size_t)item * (BN * kBM) + lane_base + lane;
+#pragma unroll
+                for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
+                    const float osc = lane < 16 ? p.oscale[n0 + c0 + lane] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const float sc = __shfl_sync(0xffffffffu, osc, j);
+                        __stcg(mine + (size_t)(col_base + c0 + j) * kBM, acc[c0 + j] * sc * p.out_scale);
+                    }
+                }
+                __threadfence();
+                __syncwarp();
+                uint32_t ticket = 0;
+                uint32_t *tk = p.split_tickets + (size_t)wi.tile * kEpiWarps + warp;
+                if (lane == 0) {
+                    ticket = atomicAdd(tk, 1u);
+                    if (ticket == p.ksplit - 1) *tk = 0;  // left at zero for the next launch
+                }
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket != p.ksplit - 1) continue;
+                __threadfence();
+                const float *parts = p.split_part + (size_t)(wi.tile * p.ksplit) * (BN * kBM) + lane_base + lane;
+#pragma unroll 1
+                for (uint32_t j = 0; j < CW; j++) {
+                    const uint32_t n = n0 + j;
+                    if (row < p.n_rows && n < p.n_tokens) {
+                        float val = 0.f;
+                        for (uint32_t ks = 0; ks < p.ksplit; ks++) val += __ldcg(parts + (size_t)ks * (BN * kBM) + (size_t)(col_base + j) * kBM);
+                        const size_t o = (size_t)n * p.out_stride + row;
+                        if (p.residual) val += p.residual[o];
+                        p.out[o] = val;
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                 const float osc = lane < 16 ? p.oscale[n0 + c0 + lane] : 0.f;  // padded to whole tiles
@@ -985,14 +1084,14 @@ bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens) {
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols) {
     const uint32_t bn = pick_bn(n_tokens);
     const size_t padded = (size_t)((n_tokens + bn - 1) / bn) * bn;
-    return padded * n_cols * 4 + padded * (n_cols / 256) * 32 + padded * sizeof(float) + 512;
+    return kGemmSplitBytes + padded * n_cols * 4 + padded * (n_cols / 256) * 32 + padded * sizeof(float) + 512;
 }
 
 cudaError_t launch_qgemm_xprep(const QGemm &g, cudaStream_t s, uint64_t *launches) {
     if (!qgemm_supported(g.type, g.n_cols, g.n_tokens)) return cudaErrorInvalidValue;
     const uint32_t bn = pick_bn(g.n_tokens);
     const uint32_t n_ntiles = (g.n_tokens + bn - 1) / bn, padded = n_ntiles * bn;
-    unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch);
+    unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch) + kGemmSplitBytes;
     const size_t tiles_bytes = (size_t)padded * g.n_cols * 4 + (size_t)padded * (g.n_cols / 256) * 32;
     float *oscale = reinterpret_cast<float *>(xb + ((tiles_bytes + 255) & ~(size_t)255));
 
@@ -1017,7 +1116,7 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     if (!qgemm_supported(g.type, g.n_cols, g.n_tokens) || g.n_rows == 0) return cudaErrorInvalidValue;
     const uint32_t bn = pick_bn(g.n_tokens);
     const uint32_t n_ntiles = (g.n_tokens + bn - 1) / bn, padded = n_ntiles * bn;
-    unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch);
+    unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch) + kGemmSplitBytes;
     const size_t tiles_bytes = (size_t)padded * g.n_cols * 4 + (size_t)padded * (g.n_cols / 256) * 32;
     float *oscale = reinterpret_cast<float *>(xb + ((tiles_bytes + 255) & ~(size_t)255));
     cudaError_t e;
@@ -1034,6 +1133,28 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.bn = bn;
     p.n_mtiles = (g.n_rows + kBM - 1) / kBM;
     p.n_ntiles = n_ntiles;
+    // Few tiles and long rows: the columns of a tile are split over several CTAs (whole super-blocks, at least four
+    // per part), whose partial results the last one to finish adds up in a fixed order.
+    p.ksplit = 1;
+    p.sb_per = g.n_cols / 256;
+    {
+        const uint32_t base = p.n_mtiles * p.n_ntiles, bpr = g.n_cols / 256;
+        uint32_t want = 1;
+        if (base * 2 <= (uint32_t)sm_count && bpr >= 8) {
+            want = (uint32_t)sm_count / base;
+            if (want > bpr / 4) want = bpr / 4;
+            if (want > 16) want = 16;
+        }
+        if (const char *k = knob("YULE_GEMM_KSPLIT")) want = (uint32_t)atoi(k) > 0 ? (uint32_t)atoi(k) : want;
+        if (want > bpr) want = bpr;
+        while (want > 1 && base * want > kGemmSplitMaxItems) want--;
+        if (want > 1) {
+            p.sb_per = (bpr + want - 1) / want;
+            p.ksplit = (bpr + p.sb_per - 1) / p.sb_per;
+        }
+        p.split_tickets = reinterpret_cast<uint32_t *>(g.scratch);
+        p.split_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(g.scratch) + kGemmTicketBytes);
+    }
     const bool generic = g.type != YULE_DTYPE_Q4_K || (knob("YULE_GEMM_GENERIC") && atoi(knob("YULE_GEMM_GENERIC")));
     const uint32_t stage_bytes = generic ? 2 * kABytes + 2 * bn * kBK * 2 : kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
     p.unit_bytes = 256 / block_size(g.type) * block_bytes(g.type);
@@ -1050,6 +1171,10 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.status = g.status;
     p.prof = knob("YULE_GEMM_PROF") ? 1u : 0u;
     p.skip = knob("YULE_GEMM_SKIP") ? (uint32_t)atoi(knob("YULE_GEMM_SKIP")) : 0u;
+    if (knob("YULE_GEMM_SPIN")) {
+        const int v = atoi(knob("YULE_GEMM_SPIN"));
+        cudaMemcpyToSymbolAsync(c_gemm_spin, &v, sizeof(v), 0, cudaMemcpyHostToDevice, s);
+    }
     const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 32;
     const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
     CUtensorMap w_map;
@@ -1058,7 +1183,7 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
         e = encode_weight_map(g.w, g.n_rows, g.n_cols, &w_map);
         if (e != cudaSuccess) return e;
     }
-    uint32_t grid = p.n_mtiles * p.n_ntiles;
+    uint32_t grid = p.n_mtiles * p.n_ntiles * p.ksplit;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
     auto launch = [&](auto kern) {
         cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024);
