@@ -178,6 +178,17 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// The same load without the wait: the registers hold the values only after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -376,8 +387,14 @@ struct RowBlock {
 // into fp16 hi + lo; three MMAs per 16 columns (W_hi·x_hi, W_hi·x_lo, W_lo·x_hi); no raw-block ring.
 template <int BN, bool GENERIC>
 struct Tile {
-    static constexpr uint32_t NBUF = BN <= 64 ? 4 : 2;       // TMEM accumulator pairs in flight
-    static constexpr uint32_t kTmemCols = NBUF * 2 * BN;     // 256 or 512: main + min accumulator each
+    // Up to 64 activation rows the hi and lo terms of the activations sit side by side as one operand of 2·BN rows:
+    // one MMA per 16 columns instead of two (an MMA reads its 4 KB of W from shared memory whatever its width, which
+    // is what a narrow MMA costs), the two products land in neighbouring accumulator columns and the drain adds them.
+    static constexpr bool MERGED = BN <= 64;
+    static constexpr uint32_t NBUF = BN == 32 ? 4 : 2;       // TMEM accumulator sets in flight
+    static constexpr uint32_t kMainCols = MERGED ? 2 * BN : BN;
+    static constexpr uint32_t kBufCols = kMainCols + BN;     // main + min accumulator
+    static constexpr uint32_t kTmemCols = 512;               // NBUF · kBufCols = 384 or 512, allocated as a power of two
     static constexpr uint32_t CW = BN / 2;                   // columns per drain warp
     static constexpr uint32_t kXHalfBytes = BN * kBK * 2;    // one fp16 term of the activation slab
     static constexpr uint32_t kBmBytes = BN * 16 * 2;        // sub-block sums of x: BN rows × (8 hi + 8 lo)
@@ -396,6 +413,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
     constexpr uint32_t NBUF = T::NBUF, CW = T::CW, kXHalfBytes = T::kXHalfBytes, kStageBytes = T::kStageBytes;
     extern __shared__ __align__(128) unsigned char smem[];
     yule_pdl_launch_dependents();
+    const long long t_entry = p.prof ? clock64() : 0;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *tail = smem + (size_t)p.stages * kStageBytes;
     unsigned char *raw = tail;                               // kRawSlots boxes of raw Q4_K bytes
@@ -473,7 +491,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             const uint32_t parity_of_mine = warp == kMmaWarp ? 0u : 1u;  // this thread issues the stages with it % 2 == parity
             // fp16 × fp16 → fp32, both operands K-major, M = 128, N = BN
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-            constexpr uint32_t x_lbo = BN * 16;  // bytes of one 8-column step of an activation slab
+            [[maybe_unused]] constexpr uint32_t idesc2 = (1u << 4) | ((uint32_t)((2 * BN) >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);  // N = 2·BN
+            constexpr uint32_t x_lbo = BN * 16;  // bytes of one 8-column step of an activation slab (of its hi or lo rows)
             uint32_t it = 0;
             bool ok = true;
             RingPos ring;
@@ -516,24 +535,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     tw0 += c1 - c0;
                     tw1 += c2 - c1;
                     tc_fence_after();
-                    const uint32_t d_main = tmem_base + buf * 2 * BN;
-                    [[maybe_unused]] const uint32_t d_min = d_main + BN;
+                    const uint32_t d_main = tmem_base + buf * T::kBufCols;
+                    [[maybe_unused]] const uint32_t d_min = d_main + T::kMainCols;
                     const uint32_t a = smem_u32(smem + (size_t)s * kStageBytes);
                     const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
 #pragma unroll
                     for (uint32_t k16 = 0; k16 < kBK / 16; k16++) {
                         if (p.skip & 2u) break;
                         const uint64_t da = smem_desc(a + k16 * 4096, 2048, 128);
-                        umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // every stage starts a fresh accumulator
-                        umma_f16(d_main, da, smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
-                        if (GENERIC)  // the lo term of the weights against the hi term of the activations
-                            umma_f16(d_main, smem_desc(a + kABytes + k16 * 4096, 2048, 128), smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
+                        if constexpr (T::MERGED) {
+                            // rows [0, BN) of an 8-column step are the hi terms, rows [BN, 2·BN) the lo terms
+                            const uint64_t db = smem_desc(x_hi + k16 * 4 * x_lbo, 2 * x_lbo, 128);
+                            umma_f16(d_main, da, db, idesc2, k16 != 0u);  // every stage starts a fresh accumulator
+                            if (GENERIC)  // the lo term of the weights against the hi term of the activations: the first BN rows
+                                umma_f16(d_main, smem_desc(a + kABytes + k16 * 4096, 2048, 128), db, idesc, 1u);
+                        } else {
+                            umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // every stage starts a fresh accumulator
+                            umma_f16(d_main, da, smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
+                            if (GENERIC)  // the lo term of the weights against the hi term of the activations
+                                umma_f16(d_main, smem_desc(a + kABytes + k16 * 4096, 2048, 128), smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
+                        }
                     }
                     if (!GENERIC && (kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
                         umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(x_lo + kXHalfBytes, x_lbo, 128), idesc, 0u);
                     const long long c3 = p.prof ? clock64() : 0;
                     umma_commit(bar_empty + 8 * s);       // the slabs may be overwritten once these MMAs are done
                     if (!(p.skip & 32u)) umma_commit(bar_acc_full + 8 * buf);  // and the accumulators may be drained
+                    if (p.skip & 256u) mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status);  // timing aid: the commit's own latency, charged to `commit`
                     const long long c4 = p.prof ? clock64() : 0;
                     ti += c3 - c2;
                     tc += c4 - c3;
@@ -745,11 +773,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         }  // exact Q4_K producer
     } else {
         // drain warp: TMEM lanes [32·(warp % 4), +32) = rows of the tile, columns [CW·(warp / 4), +CW)
+        const long long t_ready = p.prof ? clock64() : 0;
         yule_pdl_wait();
         const uint32_t lane_base = (warp & 3u) * 32u, col_base = (warp >> 2) * CW;
         uint32_t it = 0;
         bool ok = true;
-        long long dw = 0;
+        long long dw = 0, t_loop_end = 0;
         const long long dstart = p.prof ? clock64() : 0;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const Item wi = decode_item(p, item, bpr);
@@ -776,20 +805,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 }
                 if (p.prof) dw += clock64() - c0;
                 tc_fence_after();
-                const uint32_t t_main = tmem_base + (lane_base << 16) + buf * 2 * BN + col_base;
+                const uint32_t t_main = tmem_base + (lane_base << 16) + buf * T::kBufCols + col_base;
+                if constexpr (T::MERGED) {
+                    // all the loads of the stage in flight together, one wait
+                    uint32_t v[CW], vl[CW];
+                    if (!(p.skip & 4u)) {
 #pragma unroll
-                for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
-                    if (p.skip & 4u) break;
-                    uint32_t v[16];
-                    tmem_ld16(t_main + c0, v);
+                        for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
+                            tmem_ld16_issue(t_main + c0, v + c0);
+                            tmem_ld16_issue(t_main + BN + c0, vl + c0);  // the products with the lo terms
+                        }
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(dd.x, __uint_as_float(v[j]), acc[c0 + j]);
+                        for (uint32_t j = 0; j < CW; j++) acc[j] = fmaf(dd.x, __uint_as_float(v[j]) + __uint_as_float(vl[j]), acc[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
+                        if (p.skip & 4u) break;
+                        uint32_t v[16];
+                        tmem_ld16(t_main + c0, v);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(dd.x, __uint_as_float(v[j]), acc[c0 + j]);
+                    }
                 }
                 if (!GENERIC && (kb & 3u) == 3u) {  // the stage that ends a super-block carries the min term
 #pragma unroll
                     for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                         uint32_t v[16];
-                        tmem_ld16(t_main + BN + c0, v);
+                        tmem_ld16(t_main + T::kMainCols + c0, v);
 #pragma unroll
                         for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(-dd.y * (1.0f / kSumScale), __uint_as_float(v[j]), acc[c0 + j]);
                     }
@@ -799,6 +843,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
             }
             if (!ok) break;
+            if (p.prof) t_loop_end = clock64();
             const uint32_t n0 = nt * BN + col_base;
             if (p.ksplit > 1) {
                 // This item covers a part of the columns.  Every drain warp stores its block of scaled partial sums, then
@@ -825,16 +870,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 ticket = __shfl_sync(0xffffffffu, ticket, 0);
                 if (ticket != p.ksplit - 1) continue;
                 __threadfence();
-                const float *parts = p.split_part + (size_t)(wi.tile * p.ksplit) * (BN * kBM) + lane_base + lane;
+                const float *parts = p.split_part + (size_t)(wi.tile * p.ksplit) * (BN * kBM) + (size_t)col_base * kBM + lane_base + lane;
+#pragma unroll
+                for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
 #pragma unroll 1
+                for (uint32_t ks = 0; ks < p.ksplit; ks++, parts += BN * kBM) {  // the loads of a part are independent of one another
+                    float v[CW];
+#pragma unroll
+                    for (uint32_t j = 0; j < CW; j++) v[j] = __ldcg(parts + (size_t)j * kBM);
+#pragma unroll
+                    for (uint32_t j = 0; j < CW; j++) acc[j] += v[j];
+                }
+#pragma unroll
                 for (uint32_t j = 0; j < CW; j++) {
                     const uint32_t n = n0 + j;
                     if (row < p.n_rows && n < p.n_tokens) {
-                        float val = 0.f;
-                        for (uint32_t ks = 0; ks < p.ksplit; ks++) val += __ldcg(parts + (size_t)ks * (BN * kBM) + (size_t)(col_base + j) * kBM);
                         const size_t o = (size_t)n * p.out_stride + row;
-                        if (p.residual) val += p.residual[o];
-                        p.out[o] = val;
+                        p.out[o] = p.residual ? acc[j] + p.residual[o] : acc[j];
                     }
                 }
                 continue;
@@ -858,10 +910,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
             g_gemm_prof[10] = clock64() - dstart;
             g_gemm_prof[11] = dw;
+            g_gemm_prof[12] = t_ready - t_entry;
+            g_gemm_prof[13] = dstart - t_ready;
+            g_gemm_prof[14] = clock64() - t_loop_end;
         }
     }
 
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) g_gemm_prof[15] = 1;
     // common exit: nothing of this CTA may still be in flight when its TMEM and shared memory go
     tc_fence_before();
     __syncthreads();
@@ -876,6 +930,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T::kTmemCols) : "memory");
     }
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) g_gemm_prof[15] = clock64() - t_entry;
 }
 
 // Activation rows → the GEMM's operand tiles, one CTA per (padded) row: power-of-two row scale,
@@ -892,7 +947,12 @@ struct XprepParams {
     float *oscale;
 };
 
-__global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
+// One CTA of 1024 threads per row; a thread keeps its 8·CHUNKS columns in registers from the single read of the row
+// to the stores, so a row of up to 8192·CHUNKS columns costs one round trip to memory and two block reductions
+// whatever its length.
+constexpr int kXprepThreads = 1024;
+template <int CHUNKS>
+__global__ void __launch_bounds__(kXprepThreads) gemm_xprep_kernel(const XprepParams p) {
     yule_pdl_launch_dependents();
     yule_pdl_wait();
     __shared__ float red[32];
@@ -903,6 +963,8 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
     // 16 bytes of columns [k0, k0 + 8): term 0 = hi, 1 = lo
     auto slab16 = [&](uint32_t k0, uint32_t term) {
         const uint32_t sb = k0 >> 8, g = (k0 >> 6) & 3u, kc = (k0 >> 3) & 7u;
+        if (p.bn <= 64)  // hi and lo rows of an 8-column step side by side (one operand of 2·bn rows)
+            return p.xb + ((size_t)nt * bpr + sb) * super_bytes + (size_t)(2 * g) * x_half_bytes + (2 * kc + term) * (p.bn * 16) + core;
         return p.xb + ((size_t)nt * bpr + sb) * super_bytes + (size_t)(2 * g + term) * x_half_bytes + kc * (p.bn * 16) + core;
     };
     // the two bytes of sub-block s (of super-block sb) in the sums slab: column s (hi) or 8 + s (lo)
@@ -911,7 +973,7 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
                                           term * (p.bn * 16) + core) + s;
     };
     if (n >= p.n_tokens) {  // padding row of the last tile
-        for (uint32_t k0 = threadIdx.x * 8; k0 < p.n_cols; k0 += 256 * 8) {
+        for (uint32_t k0 = threadIdx.x * 8; k0 < p.n_cols; k0 += kXprepThreads * 8) {
             *reinterpret_cast<uint4 *>(slab16(k0, 0)) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4 *>(slab16(k0, 1)) = make_uint4(0, 0, 0, 0);
             if ((k0 & 31u) == 0) {
@@ -933,27 +995,63 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
         if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
         __syncthreads();
         v = red[0];
-        for (int i = 1; i < 8; i++) v = is_max ? fmaxf(v, red[i]) : v + red[i];
+        for (int i = 1; i < kXprepThreads / 32; i++) v = is_max ? fmaxf(v, red[i]) : v + red[i];
         return v;
     };
-    float inv = 1.f;
+    // rows start on a 16-byte boundary when the stride is a multiple of four floats; otherwise scalar loads
+    const bool vec = ((reinterpret_cast<uintptr_t>(x) | (gate ? reinterpret_cast<uintptr_t>(gate) : 0)) & 15u) == 0;
+    float v[CHUNKS][8];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c++) {
+        const uint32_t k0 = ((uint32_t)c * kXprepThreads + threadIdx.x) * 8;
+        if (k0 < p.n_cols) {
+            if (vec) {
+                const float4 a = *reinterpret_cast<const float4 *>(x + k0), b = *reinterpret_cast<const float4 *>(x + k0 + 4);
+                v[c][0] = a.x, v[c][1] = a.y, v[c][2] = a.z, v[c][3] = a.w, v[c][4] = b.x, v[c][5] = b.y, v[c][6] = b.z, v[c][7] = b.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[c][i] = x[k0 + i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[c][i] = 0.f;
+        }
+    }
     if (p.norm_w) {
         float ss = 0.f;
-        for (uint32_t i = threadIdx.x; i < p.n_cols; i += 256) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; c++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) ss = fmaf(v[c][i], v[c][i], ss);
         ss = block_reduce(ss, false);
-        inv = 1.0f / sqrtf(ss / (float)p.n_cols + p.eps);
-    }
-    auto value = [&](uint32_t i) {
-        float v = x[i];
-        if (p.norm_w) v = v * inv * p.norm_w[i];
-        if (gate) {
-            const float gt = gate[i];
-            v = (gt / (1.0f + expf(-gt))) * v;
+        const float inv = 1.0f / sqrtf(ss / (float)p.n_cols + p.eps);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; c++) {
+            const uint32_t k0 = ((uint32_t)c * kXprepThreads + threadIdx.x) * 8;
+            if (k0 < p.n_cols) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[c][i] = v[c][i] * inv * p.norm_w[k0 + i];
+            }
         }
-        return v;
-    };
+    }
+    if (gate) {
+#pragma unroll
+        for (int c = 0; c < CHUNKS; c++) {
+            const uint32_t k0 = ((uint32_t)c * kXprepThreads + threadIdx.x) * 8;
+            if (k0 < p.n_cols) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float gt = gate[k0 + i];
+                    v[c][i] = (gt / (1.0f + expf(-gt))) * v[c][i];
+                }
+            }
+        }
+    }
     float amax = 0.f;
-    for (uint32_t i = threadIdx.x; i < p.n_cols; i += 256) amax = fmaxf(amax, fabsf(value(i)));
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[c][i]));
     amax = block_reduce(amax, true);
     // power of two that puts the largest element in [2^13, 2^14)
     float scale = 1.f;
@@ -963,16 +1061,18 @@ __global__ void __launch_bounds__(256) gemm_xprep_kernel(const XprepParams p) {
         scale = ldexpf(1.f, 14 - ex);
     }
     if (threadIdx.x == 0) p.oscale[n] = 1.0f / scale;
-    for (uint32_t k0 = threadIdx.x * 8; k0 < p.n_cols; k0 += 256 * 8) {
-        float v[8];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c++) {
+        const uint32_t k0 = ((uint32_t)c * kXprepThreads + threadIdx.x) * 8;
+        if (k0 >= p.n_cols) break;  // whole groups of four threads (32 columns) leave together
         float sum = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            v[i] = value(k0 + i) * scale;
-            sum += v[i];
+            v[c][i] *= scale;
+            sum += v[c][i];
         }
         // positions 0..7 of the 16 bytes hold columns 0,2,1,3,4,6,5,7
-        const float o[8] = {v[0], v[2], v[1], v[3], v[4], v[6], v[5], v[7]};
+        const float o[8] = {v[c][0], v[c][2], v[c][1], v[c][3], v[c][4], v[c][6], v[c][5], v[c][7]};
         uint32_t h[4], l[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -1078,7 +1178,7 @@ cudaError_t encode_tensor_map_2d(const void *base, uint32_t elem_bytes, uint64_t
 // Q4_K runs on the exact-integer kernel; Q6_K, Q8_0 and Q4_0 on the generic one (YULE_GEMM_GENERIC=1
 // sends Q4_K there too, for comparison).  The activation tiles are laid out per 256 columns.
 bool qgemm_supported(uint32_t type, uint32_t n_cols, uint32_t n_tokens) {
-    return is_quantized(type) && n_cols % 256 == 0 && n_cols > 0 && n_tokens >= 1;
+    return is_quantized(type) && n_cols % 256 == 0 && n_cols > 0 && n_cols <= 65536 && n_tokens >= 1;
 }
 
 size_t qgemm_scratch_bytes(uint32_t n_tokens, uint32_t n_cols) {
@@ -1106,7 +1206,17 @@ cudaError_t launch_qgemm_xprep(const QGemm &g, cudaStream_t s, uint64_t *launche
     xp.bn = bn;
     xp.xb = xb;
     xp.oscale = oscale;
-    cudaError_t e = launch_kernel(gemm_xprep_kernel, dim3(padded), dim3(256), 0, s, g.pdl, xp);
+    cudaError_t e;
+    if (g.n_cols <= 8192)
+        e = launch_kernel(gemm_xprep_kernel<1>, dim3(padded), dim3(kXprepThreads), 0, s, g.pdl, xp);
+    else if (g.n_cols <= 16384)
+        e = launch_kernel(gemm_xprep_kernel<2>, dim3(padded), dim3(kXprepThreads), 0, s, g.pdl, xp);
+    else if (g.n_cols <= 32768)
+        e = launch_kernel(gemm_xprep_kernel<4>, dim3(padded), dim3(kXprepThreads), 0, s, g.pdl, xp);
+    else if (g.n_cols <= 65536)
+        e = launch_kernel(gemm_xprep_kernel<8>, dim3(padded), dim3(kXprepThreads), 0, s, g.pdl, xp);
+    else
+        return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;
     *launches += 1;
     return cudaSuccess;
@@ -1204,8 +1314,9 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
             if (cudaMemcpyFromSymbol(h, g_gemm_prof, sizeof(h)) == cudaSuccess)
                 fprintf(stderr,
                         "[qgemm prof, CTA 0, cycles] mma: total %lld wait_acc_empty %lld wait_full %lld issue %lld commit %lld stages %lld | "
-                        "producer: total %lld wait_empty %lld unpack %lld fence+arrive %lld | drain: total %lld wait_acc_full %lld\n",
-                        h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], h[10], h[11]);
+                        "producer: total %lld wait_empty %lld unpack %lld fence+arrive %lld | drain: total %lld wait_acc_full %lld | "
+                        "set-up %lld wait for the re-layout %lld epilogue %lld kernel %lld\n",
+                        h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], h[10], h[11], h[12], h[13], h[14], h[15]);
         }
     }
     return cudaSuccess;
@@ -1215,7 +1326,9 @@ cudaError_t launch_qgemm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t 
     if (g.n_rows == 0) return cudaErrorInvalidValue;
     cudaError_t e = launch_qgemm_xprep(g, s, launches);
     if (e != cudaSuccess) return e;
-    return launch_qgemm_mm(g, sm_count, s, launches);
+    QGemm mm = g;
+    mm.pdl = true;  // behind the re-layout of its own activations: only the weight copies run ahead of it
+    return launch_qgemm_mm(mm, sm_count, s, launches);
 }
 
 }  // namespace yule

@@ -906,6 +906,7 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         g.n_cols = cols;
         g.n_tokens = m;
         g.scratch = ctx->gemm_scratch;
+        g.pdl = true;  // starts under the tail of its predecessor; reads and writes only after the dependency wait
         ok(launch_qgemm_xprep(g, s, launches));
     };
     // `rows` output rows of this rank, written at `out` with `stride` floats between the rows of the result
@@ -921,6 +922,7 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         g.out_stride = stride;
         g.scratch = ctx->gemm_scratch;
         g.status = ctx->device_status;
+        g.pdl = true;  // barrier set-up, TMEM allocation and the first weight copies overlap with the re-layout before it
         ok(launch_qgemm_mm(g, sms, s, launches));
     };
     const uint32_t epochs_per_tick = 5 * c.n_layers + 1;
