@@ -64,6 +64,36 @@ def test_batched_equals_per_vector(backend, oracle, dtype, batch):
         assert guarded_rel_err(y[b], ref) <= REL_TOL
 
 
+@pytest.mark.parametrize("dtype,n_rows,n_cols,batch", [
+    (DType.Q8_0, 16, 256, 2),        # one tile, one group of columns
+    (DType.Q8_0, 1000, 4096, 3),     # three vectors, ragged last tile, four stages per tile
+    (DType.Q4_0, 1000, 4096, 4),
+    (DType.Q8_0, 300, 8192, 7),      # three vectors per pass fit beside the ring: 3 + 3 + 1
+    (DType.Q4_0, 129, 14336, 4),     # two vectors per pass
+    (DType.Q4_0, 40, 512, 6),
+    (DType.Q8_0, 4096, 4096, 4),
+])
+def test_q8_0_q4_0_several_vectors_per_pass(backend, oracle, dtype, n_rows, n_cols, batch):
+    """Q8_0 / Q4_0 with two to four activation vectors per pass of the ring kernel (one MMA column pair per vector),
+    vectors of very different magnitudes (each has its own power-of-two scale), strides wider than the data."""
+    w = synth.random_blocks(dtype, 400 + n_rows, n_rows * (n_cols // 32))
+    x = synth.normal(401 + batch, batch * n_cols).reshape(batch, n_cols)
+    x *= np.float32(10.0) ** np.arange(-3, -3 + batch, dtype=np.float32)[:, None]
+    x_stride, out_stride = n_cols + 64, n_rows + 5
+    xs = np.zeros((batch, x_stride), np.float32)
+    xs[:, :n_cols] = x
+    wh, xh = backend.upload(w), backend.upload(xs.reshape(-1))
+    oh = backend.upload(np.full(batch * out_stride, 7.0, np.float32))
+    backend.quantized_matmul_batched(wh, xh, oh, n_rows, n_cols, dtype, batch, x_stride, out_stride)
+    y = backend.download(oh, batch * out_stride).reshape(batch, out_stride)
+    for h in (wh, xh, oh):
+        backend.free(h)
+    assert np.all(y[:, n_rows:] == 7.0)
+    for b in range(batch):
+        ref = oracle.qmv(int(dtype), w, x[b], n_rows, n_cols)
+        assert guarded_rel_err(y[b, :n_rows], ref) <= REL_TOL, f"vector {b}"
+
+
 def test_config0_shape_quantised_gaussian(backend, oracle):
     """The TinyLlama FFN-up shape of the headline matvec: 5632 x 2048 Q4_K."""
     n_rows, n_cols = 5632, 2048

@@ -607,6 +607,37 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
     // Q8_0 / Q4_0, one vector, 256-column multiples: the tensor-pipe ring kernel (YULE_QMV_Q8Q4_RING=0: the SIMT kernel)
     if (q8q4_ring_supported(a) && !(knob("YULE_QMV_Q8Q4_RING") && atoi(knob("YULE_QMV_Q8Q4_RING")) == 0))
         return launch_q8q4_ring(a, sm_count, s, launches);
+    // Q8_0 / Q4_0, several vectors: two to four per pass of the batched ring kernel, a single left-over vector on the
+    // one-vector kernel
+    if (q8q4_ring_batch_width(a) >= 2 && !(knob("YULE_QMV_Q8Q4_RING") && atoi(knob("YULE_QMV_Q8Q4_RING")) == 0)) {
+        uint32_t done = 0;
+        while (done < a.batch) {
+            QmvArgs part = a;
+            part.x = a.x + (size_t)done * a.x_stride;
+            part.out = a.out + (size_t)done * a.out_stride;
+            part.residual = a.residual ? a.residual + (size_t)done * a.out_stride : nullptr;
+            part.batch = a.batch - done;
+            const uint32_t nb = q8q4_ring_batch_width(part);
+            cudaError_t e;
+            if (nb >= 2) {
+                e = launch_q8q4_ring_batch(part, nb, sm_count, s, launches);
+                done += nb;
+            } else {
+                part.batch = 1;
+                if (!q8q4_ring_supported(part)) break;  // the SIMT kernels below take the rest
+                e = launch_q8q4_ring(part, sm_count, s, launches);
+                done += 1;
+            }
+            if (e != cudaSuccess) return e;
+        }
+        if (done == a.batch) return cudaSuccess;
+        QmvArgs rest = a;
+        rest.x = a.x + (size_t)done * a.x_stride;
+        rest.out = a.out + (size_t)done * a.out_stride;
+        rest.residual = a.residual ? a.residual + (size_t)done * a.out_stride : nullptr;
+        rest.batch = a.batch - done;
+        return launch_qmv(rest, sm_count, s, launches);
+    }
     if (qmv_smem_bytes(a.type, a.n_cols, 1) > kMaxSmem) return cudaErrorInvalidValue;
     uint32_t done = 0;
     while (done < a.batch) {

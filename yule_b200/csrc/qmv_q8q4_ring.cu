@@ -469,6 +469,362 @@ qmv_q8q4_ring_kernel(const __grid_constant__ RingParams p) {
     }
 }
 
+// ── two to four activation vectors per pass ──────────────────────────────────────────────────────────────────
+//
+// Same ring, same stages, another use of the MMA's eight B columns: column 2v is the hi term of vector v, column
+// 2v + 1 its lo term, and one MMA covers 16 weights of ONE block (its k slots are permuted so that lane t owns four
+// consecutive quant bytes: one 32-bit word per row and MMA).  D[row][2v], D[row][2v+1] of the two MMAs of a block
+// are the Σ q·x of that block for vector v; lane (g, t) holds them for rows g, g + 8 and vector t, adds the offset
+// term (−128 or −8 times the block's Σx, staged with the activations) and multiplies by the row's d in fp32.  The
+// tensor pipe does the same number of MMAs per weight as for one vector, so up to four vectors cost about the time
+// of one.  Each vector has its own power-of-two scale.
+//
+// Shared-memory image of the activations: per 16-weight chunk (block b of group s, MMA j: chunk (4s + b)·2 + j)
+// and B column n = 2v + part, four entries t of 8 bytes = the four halves lane t multiplies:
+//   Q8_0  chunk j of a block = its weights 8t + 4j .. 8t + 4j + 3 for t = 0..3
+//   Q4_0  word t of a block holds its weights 8t..8t+7 (byte j: weight 2j low, 2j+1 high); chunk 0 = the low
+//         nibbles, entry t = weights 8t, 8t+4, 8t+2, 8t+6; chunk 1 = the high nibbles, entry t = 8t+1, 8t+5, 8t+3,
+//         8t+7 (the order in which the nibbles of a word fall into the A registers)
+// A chunk is nb·64 bytes; the 8 x nb lanes that feed an MMA read it as one contiguous run.  sfb[(4s + b)·4 + v]
+// is c·2^-24·Σx of block b for vector v (c = −128 or −8).
+struct BatchParams {
+    RingParams r;
+    uint32_t nb, x_stride, out_stride;
+};
+
+struct BatchSmem {
+    unsigned char *ring;
+    unsigned char *xb;  // n_cols/16 chunks of nb·64 bytes
+    float *sfb;         // n_cols/32 blocks x 4
+    unsigned char *zb;  // 256 bytes of zeros
+    float *red;         // [group][warp][4]
+    float *partial;     // [group][buffer][warp][16 rows][4 vectors]
+    uint64_t *bars;
+    uint32_t *cnt;
+};
+constexpr size_t kBatchPartialBytes = (size_t)kGroups * 2 * kWarps * 64 * sizeof(float);
+__host__ __device__ inline size_t batch_fixed_bytes(uint32_t n_cols, uint32_t nb) {
+    size_t off = (size_t)n_cols * 4 * nb + (size_t)(n_cols / 32) * 16;
+    off += 256 + (size_t)kGroups * kWarps * 4 * sizeof(float) + kBatchPartialBytes + (size_t)kGroups * kMaxStages * (8 + 4);
+    return (off + 127) & ~(size_t)127;
+}
+__device__ __forceinline__ BatchSmem batch_carve(unsigned char *base, uint32_t n_cols, uint32_t nb, size_t ring_bytes) {
+    BatchSmem s;
+    s.ring = base;
+    size_t off = ring_bytes;
+    s.xb = base + off;
+    off += (size_t)n_cols * 4 * nb;
+    s.sfb = reinterpret_cast<float *>(base + off);
+    off += (size_t)(n_cols / 32) * 16;
+    s.zb = base + off;
+    off += 256;
+    s.red = reinterpret_cast<float *>(base + off);
+    off += (size_t)kGroups * kWarps * 4 * sizeof(float);
+    s.partial = reinterpret_cast<float *>(base + off);
+    off += kBatchPartialBytes;
+    s.bars = reinterpret_cast<uint64_t *>(base + off);
+    off += (size_t)kGroups * kMaxStages * 8;
+    s.cnt = reinterpret_cast<uint32_t *>(base + off);
+    return s;
+}
+
+__device__ __forceinline__ void mma_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// Activation staging by one 8-warp group for `nb` vectors: warp w converts the 128-column groups w, w+8, … of every
+// vector, lane l the four columns 4l..4l+3.  Returns 2^-e of vector `want` (the one this thread stores at the end
+// of a tile).
+template <bool Q8>
+__device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float *__restrict__ x, uint32_t x_stride, uint32_t nb,
+                                               uint32_t n_sg, int group, int wid, int lane, uint32_t want) {
+    constexpr int KC = 2;  // groups per vector kept in registers between the two passes
+    const uint32_t tid = threadIdx.x & (kWarps * 32 - 1);
+    if (tid < 64) reinterpret_cast<uint32_t *>(sm.zb)[tid] = 0u;
+    float4 cache[4][KC];
+    float mx[4] = {0.f, 0.f, 0.f, 0.f};
+    auto amax4 = [](float4 a) { return fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))); };
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        if ((uint32_t)v < nb) {
+            const float *xv = x + (size_t)v * x_stride;
+#pragma unroll
+            for (int i = 0; i < KC; i++) {
+                const uint32_t s = (uint32_t)wid + 8u * i;
+                if (s < n_sg) {
+                    cache[v][i] = *reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u);
+                    mx[v] = fmaxf(mx[v], amax4(cache[v][i]));
+                }
+            }
+            for (uint32_t s = (uint32_t)wid + 8u * KC; s < n_sg; s += 8u)
+                mx[v] = fmaxf(mx[v], amax4(*reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u)));
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; v++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], o));
+    float4 *red = reinterpret_cast<float4 *>(sm.red) + group * kWarps;
+    if (lane == 0) red[wid] = make_float4(mx[0], mx[1], mx[2], mx[3]);
+    ring_group_barrier(group);
+    {
+        float4 m = red[0];
+#pragma unroll
+        for (int w = 1; w < kWarps; w++) {
+            const float4 o = red[w];
+            m.x = fmaxf(m.x, o.x), m.y = fmaxf(m.y, o.y), m.z = fmaxf(m.z, o.z), m.w = fmaxf(m.w, o.w);
+        }
+        mx[0] = m.x, mx[1] = m.y, mx[2] = m.z, mx[3] = m.w;
+    }
+    float scale[4], inv_want = 1.f;
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        // 2^e with max|x|·2^e in [2^13, 2^14); exponent clamped so both 2^e and 2^-e stay finite normals
+        int eb = (int)((__float_as_uint(mx[v]) >> 23) & 0xFFu);
+        if (mx[v] == 0.f || eb == 0xFF) eb = 127 + 13;
+        int se = 127 + 13 - (eb - 127);
+        se = se < 1 ? 1 : (se > 253 ? 253 : se);
+        scale[v] = __uint_as_float((uint32_t)se << 23);
+        if ((uint32_t)v == want) inv_want = __uint_as_float((uint32_t)(254 - se) << 23);
+    }
+    const uint32_t chunk_bytes = nb * 64u;
+    const float off = (Q8 ? -128.0f : -8.0f) * 5.9604644775390625e-08f;  // c · 2^-24
+    auto convert = [&](uint32_t s, uint32_t v, float4 a, float sc) {
+        a.x *= sc;  // exact (power of two)
+        a.y *= sc;
+        a.z *= sc;
+        a.w *= sc;
+        const __half h0 = __float2half_rn(a.x), h1 = __float2half_rn(a.y), h2 = __float2half_rn(a.z), h3 = __float2half_rn(a.w);
+        const __half l0 = __float2half_rn(a.x - __half2float(h0)), l1 = __float2half_rn(a.y - __half2float(h1)),
+                     l2 = __float2half_rn(a.z - __half2float(h2)), l3 = __float2half_rn(a.w - __half2float(h3));
+        const uint32_t b = (uint32_t)lane >> 3, m = (uint32_t)lane & 7u;
+        uint32_t chunk, t;
+        uint2 hi, lo;
+        if (Q8) {
+            chunk = (s * 4 + b) * 2 + (m & 1u);
+            t = m >> 1;
+            hi = make_uint2(h2_as_u32(__halves2half2(h0, h1)), h2_as_u32(__halves2half2(h2, h3)));
+            lo = make_uint2(h2_as_u32(__halves2half2(l0, l1)), h2_as_u32(__halves2half2(l2, l3)));
+        } else {
+            // two neighbouring lanes hold the eight weights of a word: the even lane builds the entry of the low nibbles
+            // {x0,x4} {x2,x6}, the odd lane that of the high nibbles {x1,x5} {x3,x7}
+            const uint32_t mine_h02 = h2_as_u32(__halves2half2(h0, h2)), mine_h13 = h2_as_u32(__halves2half2(h1, h3));
+            const uint32_t mine_l02 = h2_as_u32(__halves2half2(l0, l2)), mine_l13 = h2_as_u32(__halves2half2(l1, l3));
+            const uint32_t oth_h02 = __shfl_xor_sync(0xffffffffu, mine_h02, 1), oth_h13 = __shfl_xor_sync(0xffffffffu, mine_h13, 1);
+            const uint32_t oth_l02 = __shfl_xor_sync(0xffffffffu, mine_l02, 1), oth_l13 = __shfl_xor_sync(0xffffffffu, mine_l13, 1);
+            chunk = (s * 4 + b) * 2 + (m & 1u);
+            t = m >> 1;
+            if ((m & 1u) == 0) {
+                hi = make_uint2(__byte_perm(mine_h02, oth_h02, 0x5410), __byte_perm(mine_h02, oth_h02, 0x7632));
+                lo = make_uint2(__byte_perm(mine_l02, oth_l02, 0x5410), __byte_perm(mine_l02, oth_l02, 0x7632));
+            } else {
+                hi = make_uint2(__byte_perm(oth_h13, mine_h13, 0x5410), __byte_perm(oth_h13, mine_h13, 0x7632));
+                lo = make_uint2(__byte_perm(oth_l13, mine_l13, 0x5410), __byte_perm(oth_l13, mine_l13, 0x7632));
+            }
+        }
+        unsigned char *dst = sm.xb + (size_t)chunk * chunk_bytes + (2 * v) * 32u + t * 8u;
+        *reinterpret_cast<uint2 *>(dst) = hi;
+        *reinterpret_cast<uint2 *>(dst + 32) = lo;
+        // Σ over the 32 columns of a block: eight consecutive lanes
+        float s4 = (a.x + a.y) + (a.z + a.w);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 2);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 4);
+        if (m == 0) sm.sfb[(s * 4 + b) * 4 + v] = s4 * off;
+    };
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        if ((uint32_t)v < nb) {
+            const float *xv = x + (size_t)v * x_stride;
+#pragma unroll
+            for (int i = 0; i < KC; i++) {
+                const uint32_t s = (uint32_t)wid + 8u * i;
+                if (s < n_sg) convert(s, v, cache[v][i], scale[v]);
+            }
+            for (uint32_t s = (uint32_t)wid + 8u * KC; s < n_sg; s += 8u)
+                convert(s, v, *reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u), scale[v]);
+        } else {
+            for (uint32_t s = (uint32_t)wid; s < n_sg; s += 8u)
+                if ((lane & 7) == 0) sm.sfb[(s * 4 + ((uint32_t)lane >> 3)) * 4 + v] = 0.f;
+        }
+    }
+    __syncwarp();
+    return inv_want;
+}
+
+// Block B (0..3, a compile-time constant: it fixes the alignment of the quants) of one 128-column group, rows g and g+8.
+template <bool Q8, int B>
+__device__ __forceinline__ void consume_block_batch(const unsigned char *r0, int t, const unsigned char *bp, uint32_t chunk_stride,
+                                                    const float *sfp, float &acc0, float &acc1) {
+    using F = Fmt<Q8>;
+    const unsigned char *blk0 = r0 + B * F::kBlockBytes, *blk1 = blk0 + 8 * F::kRowPitch;
+    // the quants start 2 bytes into the block: 4-byte aligned for odd B, 2 bytes past a word for even B
+    constexpr bool kShift = (B & 1) == 0;
+    const uint32_t lane_off = Q8 ? 8u * t : 4u * t;
+    const unsigned char *q0 = blk0 + (kShift ? 0 : 2) + lane_off, *q1 = blk1 + (kShift ? 0 : 2) + lane_off;
+    auto word = [&](const unsigned char *q, int i) {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(q);
+        return kShift ? __funnelshift_r(w[i], w[i + 1], 16) : w[i];
+    };
+    float d[4];
+    if (Q8) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const uint32_t w0 = word(q0, j) ^ 0x80808080u, w1 = word(q1, j) ^ 0x80808080u;
+            const uint2 b = *reinterpret_cast<const uint2 *>(bp + j * chunk_stride);
+            const uint32_t a0 = __byte_perm(w0, 0u, 0x4140), a1 = __byte_perm(w1, 0u, 0x4140), a2 = __byte_perm(w0, 0u, 0x4342),
+                           a3 = __byte_perm(w1, 0u, 0x4342);
+            if (j == 0)
+                mma_16816_z(d, a0, a1, a2, a3, b.x, b.y);
+            else
+                mma_16816(d, a0, a1, a2, a3, b.x, b.y);
+        }
+    } else {
+        const uint32_t w0 = word(q0, 0), w1 = word(q1, 0);
+        const uint2 blo = *reinterpret_cast<const uint2 *>(bp), bhi = *reinterpret_cast<const uint2 *>(bp + chunk_stride);
+        mma_16816_z(d, w0 & 0x000F000Fu, w1 & 0x000F000Fu, (w0 >> 8) & 0x000F000Fu, (w1 >> 8) & 0x000F000Fu, blo.x, blo.y);
+        mma_16816(d, (w0 >> 4) & 0x000F000Fu, (w1 >> 4) & 0x000F000Fu, (w0 >> 12) & 0x000F000Fu, (w1 >> 12) & 0x000F000Fu, bhi.x, bhi.y);
+    }
+    const float sx = *sfp;
+    const float d0 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blk0)));
+    const float d1 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blk1)));
+    acc0 = fmaf(d0, (d[0] + d[1]) + sx, acc0);
+    acc1 = fmaf(d1, (d[2] + d[3]) + sx, acc1);
+}
+
+template <bool Q8>
+__global__ void __launch_bounds__(kThreadsCta, 1)
+qmv_q8q4_ring_batch_kernel(const __grid_constant__ BatchParams bpm) {
+    using F = Fmt<Q8>;
+    const RingParams &p = bpm.r;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    yule_pdl_launch_dependents();
+
+    const int lane = threadIdx.x & 31;
+    const int group = threadIdx.x >> 8, wid = (threadIdx.x >> 5) & (kWarps - 1);
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t nb = bpm.nb;
+    const uint32_t n_sg = p.n_cols / 128;
+    const uint32_t G = gridDim.x;
+    const uint32_t first_tile = blockIdx.x + group * G, tile_stride = kGroups * G;
+    const uint32_t my_tiles = p.n_tiles > first_tile ? (p.n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+    const uint32_t S = p.stages, chunks = p.chunks;
+    const uint32_t total = my_tiles * chunks;
+    if (total == 0) return;  // a group without tiles takes no part in anything below
+
+    const BatchSmem sm = batch_carve(smem_raw, p.n_cols, nb, (size_t)kGroups * S * F::kStageBytes);
+    unsigned char *ring = sm.ring + (size_t)group * S * F::kStageBytes;
+    const uint32_t ring_u32 = smem_u32(ring);
+    const uint32_t bar0 = smem_u32(sm.bars + group * kMaxStages);
+    uint32_t *cnt = sm.cnt + group * kMaxStages;
+
+    if (wid == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < kMaxStages; i++) {
+                mbar_init(bar0 + 8 * i, 1);
+                cnt[i] = 0;
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        uint32_t k = 0, c = 0;
+        for (uint32_t n = 0; n < S && n < total; n++) {
+            issue_stage<Q8>(p, first_tile + k * tile_stride, c, n_sg, ring_u32 + n * F::kStageBytes, bar0 + 8 * n, lane);
+            if (++c == chunks) {
+                c = 0;
+                k++;
+            }
+        }
+    }
+
+    if (!p.late_wait) yule_pdl_wait();  // the activations (and the residual) come from the previous kernel
+    const uint32_t tid = threadIdx.x & (kWarps * 32 - 1);
+    const float inv_scale = stage_x_batch<Q8>(sm, p.x, bpm.x_stride, nb, n_sg, group, wid, lane, tid >> 4);
+
+    // B column n = g carries vector g / 2 (hi for even g, lo for odd); columns past 2·nb read zeros
+    const bool feeds = (uint32_t)g < 2 * nb;
+    const unsigned char *b_base = feeds ? sm.xb + g * 32 + t * 8 : sm.zb;
+    const uint32_t chunk_stride = feeds ? nb * 64u : 0u;
+    const bool charge = (uint32_t)t < nb;  // this lane's D columns belong to vector t
+    const float *sf_base = charge ? sm.sfb + t : reinterpret_cast<const float *>(sm.zb);
+    const uint32_t sf_blk = charge ? 4u : 0u;
+    const uint32_t n_warps_used = n_sg < (uint32_t)kWarps ? n_sg : (uint32_t)kWarps;
+    float *part_base = sm.partial + (size_t)group * (2 * kWarps * 64);
+
+    uint32_t ck = 0, cc = 0;
+    float acc0 = 0.f, acc1 = 0.f;
+    uint32_t slot = 0, phase = 0;
+    for (uint32_t n = 0; n < total; n++) {
+        const uint32_t bar = bar0 + 8 * slot;
+        if (!ring_wait(bar, phase, p.status, p.wait_cycles)) return;
+        const uint32_t sg0 = cc * F::kStageSgs;
+        const uint32_t nsg = n_sg - sg0 < F::kStageSgs ? n_sg - sg0 : F::kStageSgs;
+#pragma unroll
+        for (int j = 0; j < F::kSgsPerWarp; j++) {
+            const uint32_t local = (uint32_t)wid + (uint32_t)kWarps * j;
+            if (local < nsg) {
+                const uint32_t s = sg0 + local;
+                const unsigned char *r0 = ring + (size_t)slot * F::kStageBytes + (uint32_t)g * F::kRowPitch + local * F::kSgBytes;
+                const unsigned char *bp = b_base + (size_t)(s * 8) * chunk_stride;
+                const float *sfp = sf_base + (size_t)(s * 4) * sf_blk;
+                consume_block_batch<Q8, 0>(r0, t, bp, chunk_stride, sfp, acc0, acc1);
+                consume_block_batch<Q8, 1>(r0, t, bp + 2 * chunk_stride, chunk_stride, sfp + sf_blk, acc0, acc1);
+                consume_block_batch<Q8, 2>(r0, t, bp + 4 * chunk_stride, chunk_stride, sfp + 2 * sf_blk, acc0, acc1);
+                consume_block_batch<Q8, 3>(r0, t, bp + 6 * chunk_stride, chunk_stride, sfp + 3 * sf_blk, acc0, acc1);
+            }
+        }
+        if (n + S < total) {
+            __syncwarp();
+            uint32_t last = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                last = ((atomicAdd(&cnt[slot], 1u) & (kWarps - 1)) == kWarps - 1) ? 1u : 0u;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                uint32_t nk = ck, nc = cc + S;
+                while (nc >= chunks) {
+                    nc -= chunks;
+                    nk++;
+                }
+                issue_stage<Q8>(p, first_tile + nk * tile_stride, nc, n_sg, ring_u32 + slot * F::kStageBytes, bar, lane);
+            }
+        }
+        if (cc + 1 == chunks) {
+            float *part = part_base + (size_t)(ck & 1u) * (kWarps * 64);
+            part[wid * 64 + g * 4 + t] = acc0;
+            part[wid * 64 + (g + 8) * 4 + t] = acc1;
+            acc0 = acc1 = 0.f;
+            if (p.late_wait) yule_pdl_wait();  // the previous kernel is settled before our stores
+            ring_group_barrier(group);
+            if (tid < 16u * nb) {
+                // thread (vector v, row r): the eight warps' sums in a fixed order
+                const uint32_t v = tid >> 4, rr = tid & 15u;
+                float sacc = 0.f;
+                for (uint32_t w2 = 0; w2 < n_warps_used; w2++) sacc += part[w2 * 64 + rr * 4 + v];
+                const uint32_t row = (first_tile + ck * tile_stride) * kStageRows + rr;
+                if (row < p.n_rows) {
+                    sacc = (sacc * 16777216.0f) * inv_scale;
+                    const size_t o = (size_t)v * bpm.out_stride + row;
+                    if (p.residual) sacc += p.residual[o];
+                    p.out[o] = sacc;
+                }
+            }
+            cc = 0;
+            ck++;
+        } else {
+            cc++;
+        }
+        if (++slot == S) {
+            slot = 0;
+            phase ^= 1u;
+        }
+    }
+}
+
 template <bool Q8>
 cudaError_t launch_variant(const QmvArgs &a, int sm_count, cudaStream_t s) {
     using F = Fmt<Q8>;
@@ -522,7 +878,84 @@ cudaError_t launch_variant(const QmvArgs &a, int sm_count, cudaStream_t s) {
     return launch_kernel(kern, dim3(grid), dim3(kThreadsCta), smem, s, a.pdl, p);
 }
 
+template <bool Q8>
+cudaError_t launch_batch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, int sm_count, cudaStream_t s) {
+    using F = Fmt<Q8>;
+    BatchParams bp = {};
+    RingParams &p = bp.r;
+    {
+        const uint64_t row_bytes = (uint64_t)(a.n_cols / 128) * F::kSgBytes;
+        cudaError_t me = cached_tensor_map_2d(a.w, 8, row_bytes / 8, a.n_rows, row_bytes, F::kRowPitch / 8, kStageRows, &p.map);
+        if (me != cudaSuccess) return me;
+    }
+    p.w = a.w;
+    p.out = a.out;
+    p.n_rows = a.n_rows;
+    p.n_cols = a.n_cols;
+    p.n_tiles = (a.n_rows + kStageRows - 1) / kStageRows;
+    p.x = a.x;
+    p.residual = a.residual;
+    p.status = a.status;
+    p.wait_cycles = a.wait_cycles;
+    p.late_wait = (a.pdl && a.late_wait) ? 1u : 0u;
+    bp.nb = nb;
+    bp.x_stride = a.x_stride;
+    bp.out_stride = a.out_stride;
+    const uint32_t n_sg = a.n_cols / 128;
+    p.chunks = (n_sg + F::kStageSgs - 1) / F::kStageSgs;
+    uint32_t grid = (p.n_tiles + kGroups - 1) / kGroups;
+    if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
+    const uint32_t jobs_per_group = (p.n_tiles + kGroups * grid - 1) / (kGroups * grid);
+    const uint32_t need = jobs_per_group * p.chunks;
+    if (stages > need) stages = need;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * kGroups * F::kStageBytes + batch_fixed_bytes(a.n_cols, nb);
+    auto kern = qmv_q8q4_ring_batch_kernel<Q8>;
+    static bool attr_done[64] = {};  // the opt-in for large dynamic shared memory is a per-device attribute
+    static std::mutex mu;
+    {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFullSmSmem);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
+    return launch_kernel(kern, dim3(grid), dim3(kThreadsCta), smem, s, a.pdl, bp);
+}
+
+// Ring slots per group that fit beside the activation image of `nb` vectors.
+uint32_t batch_stages(uint32_t type, uint32_t n_cols, uint32_t nb) {
+    const size_t stage = type == YULE_DTYPE_Q8_0 ? Fmt<true>::kStageBytes : Fmt<false>::kStageBytes;
+    const size_t fixed = batch_fixed_bytes(n_cols, nb);
+    if (fixed + (size_t)kGroups * stage > kFullSmSmem) return 0;
+    const size_t st = (kFullSmSmem - fixed) / ((size_t)kGroups * stage);
+    return st > (size_t)kMaxStages ? (uint32_t)kMaxStages : (uint32_t)st;
+}
+
 }  // namespace
+
+uint32_t q8q4_ring_batch_width(const QmvArgs &a) {
+    if (a.type != YULE_DTYPE_Q8_0 && a.type != YULE_DTYPE_Q4_0) return 0;
+    if (a.batch < 2 || a.n_cols == 0 || a.n_cols % 256 || a.n_rows == 0 || a.x_stride % 4) return 0;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return 0;
+    // the widest pass that leaves at least three ring slots per group (two for very long rows)
+    for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
+        if (batch_stages(a.type, a.n_cols, nb) >= 3) return nb;
+    return batch_stages(a.type, a.n_cols, 2) >= 2 ? 2 : 0;
+}
+
+cudaError_t launch_q8q4_ring_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches) {
+    const uint32_t stages = batch_stages(a.type, a.n_cols, nb);
+    if (nb < 2 || nb > 4 || stages < 2) return cudaErrorInvalidValue;
+    cudaError_t e = a.type == YULE_DTYPE_Q8_0 ? launch_batch_variant<true>(a, nb, stages, sm_count, s)
+                                               : launch_batch_variant<false>(a, nb, stages, sm_count, s);
+    if (e == cudaSuccess) *launches += 1;
+    return e;
+}
 
 bool q8q4_ring_supported(const QmvArgs &a) {
     if (a.type != YULE_DTYPE_Q8_0 && a.type != YULE_DTYPE_Q4_0) return false;
