@@ -535,15 +535,16 @@ __device__ __forceinline__ void mma_16816_z(float (&d)[4], uint32_t a0, uint32_t
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-// Activation staging by one 8-warp group for `nb` vectors: warp w converts the 128-column groups w, w+8, … of every
-// vector, lane l the four columns 4l..4l+3.  Returns 2^-e of vector `want` (the one this thread stores at the end
-// of a tile).
+// Activation staging by the whole CTA for `nb` vectors: warp W (0..15) converts the 128-column groups W, W+16, … of
+// every vector, lane l the four columns 4l..4l+3; two CTA barriers (the per-vector power-of-two scales, then the
+// finished image).  Returns 2^-e of vector `want` (the one this thread stores at the end of a tile).
 template <bool Q8>
 __device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float *__restrict__ x, uint32_t x_stride, uint32_t nb,
-                                               uint32_t n_sg, int group, int wid, int lane, uint32_t want) {
-    constexpr int KC = 2;  // groups per vector kept in registers between the two passes
-    const uint32_t tid = threadIdx.x & (kWarps * 32 - 1);
-    if (tid < 64) reinterpret_cast<uint32_t *>(sm.zb)[tid] = 0u;
+                                               uint32_t n_sg, int lane, uint32_t want) {
+    constexpr int KC = 2;  // groups per vector kept in registers between the two passes (all of them up to 4096 columns)
+    constexpr uint32_t kAllWarps = kGroups * kWarps;
+    const uint32_t W = threadIdx.x >> 5;
+    if (threadIdx.x < 64) reinterpret_cast<uint32_t *>(sm.zb)[threadIdx.x] = 0u;
     float4 cache[4][KC];
     float mx[4] = {0.f, 0.f, 0.f, 0.f};
     auto amax4 = [](float4 a) { return fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))); };
@@ -553,13 +554,19 @@ __device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float 
             const float *xv = x + (size_t)v * x_stride;
 #pragma unroll
             for (int i = 0; i < KC; i++) {
-                const uint32_t s = (uint32_t)wid + 8u * i;
-                if (s < n_sg) {
-                    cache[v][i] = *reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u);
-                    mx[v] = fmaxf(mx[v], amax4(cache[v][i]));
-                }
+                const uint32_t s = W + kAllWarps * i;
+                if (s < n_sg) cache[v][i] = *reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u);
             }
-            for (uint32_t s = (uint32_t)wid + 8u * KC; s < n_sg; s += 8u)
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        if ((uint32_t)v < nb) {
+            const float *xv = x + (size_t)v * x_stride;
+#pragma unroll
+            for (int i = 0; i < KC; i++)
+                if (W + kAllWarps * i < n_sg) mx[v] = fmaxf(mx[v], amax4(cache[v][i]));
+            for (uint32_t s = W + kAllWarps * KC; s < n_sg; s += kAllWarps)
                 mx[v] = fmaxf(mx[v], amax4(*reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u)));
         }
     }
@@ -567,13 +574,13 @@ __device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float 
     for (int v = 0; v < 4; v++)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], o));
-    float4 *red = reinterpret_cast<float4 *>(sm.red) + group * kWarps;
-    if (lane == 0) red[wid] = make_float4(mx[0], mx[1], mx[2], mx[3]);
-    ring_group_barrier(group);
+    float4 *red = reinterpret_cast<float4 *>(sm.red);
+    if (lane == 0) red[W] = make_float4(mx[0], mx[1], mx[2], mx[3]);
+    __syncthreads();
     {
         float4 m = red[0];
 #pragma unroll
-        for (int w = 1; w < kWarps; w++) {
+        for (uint32_t w = 1; w < kAllWarps; w++) {
             const float4 o = red[w];
             m.x = fmaxf(m.x, o.x), m.y = fmaxf(m.y, o.y), m.z = fmaxf(m.z, o.z), m.w = fmaxf(m.w, o.w);
         }
@@ -592,39 +599,39 @@ __device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float 
     }
     const uint32_t chunk_bytes = nb * 64u;
     const float off = (Q8 ? -128.0f : -8.0f) * 5.9604644775390625e-08f;  // c · 2^-24
+    const uint32_t b = (uint32_t)lane >> 3, m = (uint32_t)lane & 7u;
     auto convert = [&](uint32_t s, uint32_t v, float4 a, float sc) {
         a.x *= sc;  // exact (power of two)
         a.y *= sc;
         a.z *= sc;
         a.w *= sc;
-        const __half h0 = __float2half_rn(a.x), h1 = __float2half_rn(a.y), h2 = __float2half_rn(a.z), h3 = __float2half_rn(a.w);
-        const __half l0 = __float2half_rn(a.x - __half2float(h0)), l1 = __float2half_rn(a.y - __half2float(h1)),
-                     l2 = __float2half_rn(a.z - __half2float(h2)), l3 = __float2half_rn(a.w - __half2float(h3));
-        const uint32_t b = (uint32_t)lane >> 3, m = (uint32_t)lane & 7u;
-        uint32_t chunk, t;
         uint2 hi, lo;
         if (Q8) {
-            chunk = (s * 4 + b) * 2 + (m & 1u);
-            t = m >> 1;
-            hi = make_uint2(h2_as_u32(__halves2half2(h0, h1)), h2_as_u32(__halves2half2(h2, h3)));
-            lo = make_uint2(h2_as_u32(__halves2half2(l0, l1)), h2_as_u32(__halves2half2(l2, l3)));
+            const __half2 h01 = __floats2half2_rn(a.x, a.y), h23 = __floats2half2_rn(a.z, a.w);
+            const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+            hi = make_uint2(h2_as_u32(h01), h2_as_u32(h23));
+            lo = make_uint2(h2_as_u32(__floats2half2_rn(a.x - b01.x, a.y - b01.y)), h2_as_u32(__floats2half2_rn(a.z - b23.x, a.w - b23.y)));
         } else {
             // two neighbouring lanes hold the eight weights of a word: the even lane builds the entry of the low nibbles
             // {x0,x4} {x2,x6}, the odd lane that of the high nibbles {x1,x5} {x3,x7}
-            const uint32_t mine_h02 = h2_as_u32(__halves2half2(h0, h2)), mine_h13 = h2_as_u32(__halves2half2(h1, h3));
-            const uint32_t mine_l02 = h2_as_u32(__halves2half2(l0, l2)), mine_l13 = h2_as_u32(__halves2half2(l1, l3));
-            const uint32_t oth_h02 = __shfl_xor_sync(0xffffffffu, mine_h02, 1), oth_h13 = __shfl_xor_sync(0xffffffffu, mine_h13, 1);
-            const uint32_t oth_l02 = __shfl_xor_sync(0xffffffffu, mine_l02, 1), oth_l13 = __shfl_xor_sync(0xffffffffu, mine_l13, 1);
-            chunk = (s * 4 + b) * 2 + (m & 1u);
-            t = m >> 1;
-            if ((m & 1u) == 0) {
-                hi = make_uint2(__byte_perm(mine_h02, oth_h02, 0x5410), __byte_perm(mine_h02, oth_h02, 0x7632));
-                lo = make_uint2(__byte_perm(mine_l02, oth_l02, 0x5410), __byte_perm(mine_l02, oth_l02, 0x7632));
+            const __half2 h02 = __floats2half2_rn(a.x, a.z), h13 = __floats2half2_rn(a.y, a.w);
+            const float2 b02 = __half22float2(h02), b13 = __half22float2(h13);
+            const uint32_t mine_h02 = h2_as_u32(h02), mine_h13 = h2_as_u32(h13);
+            const uint32_t mine_l02 = h2_as_u32(__floats2half2_rn(a.x - b02.x, a.z - b02.y)),
+                           mine_l13 = h2_as_u32(__floats2half2_rn(a.y - b13.x, a.w - b13.y));
+            const bool even = (m & 1u) == 0;
+            // each lane needs one pair of the other: the even lane the other's {x4,x6}, the odd lane the other's {x1,x3}
+            const uint32_t oth_h = __shfl_xor_sync(0xffffffffu, even ? mine_h13 : mine_h02, 1);
+            const uint32_t oth_l = __shfl_xor_sync(0xffffffffu, even ? mine_l13 : mine_l02, 1);
+            if (even) {
+                hi = make_uint2(__byte_perm(mine_h02, oth_h, 0x5410), __byte_perm(mine_h02, oth_h, 0x7632));
+                lo = make_uint2(__byte_perm(mine_l02, oth_l, 0x5410), __byte_perm(mine_l02, oth_l, 0x7632));
             } else {
-                hi = make_uint2(__byte_perm(oth_h13, mine_h13, 0x5410), __byte_perm(oth_h13, mine_h13, 0x7632));
-                lo = make_uint2(__byte_perm(oth_l13, mine_l13, 0x5410), __byte_perm(oth_l13, mine_l13, 0x7632));
+                hi = make_uint2(__byte_perm(oth_h, mine_h13, 0x5410), __byte_perm(oth_h, mine_h13, 0x7632));
+                lo = make_uint2(__byte_perm(oth_l, mine_l13, 0x5410), __byte_perm(oth_l, mine_l13, 0x7632));
             }
         }
+        const uint32_t chunk = (s * 4 + b) * 2 + (m & 1u), t = m >> 1;
         unsigned char *dst = sm.xb + (size_t)chunk * chunk_bytes + (2 * v) * 32u + t * 8u;
         *reinterpret_cast<uint2 *>(dst) = hi;
         *reinterpret_cast<uint2 *>(dst + 32) = lo;
@@ -641,17 +648,17 @@ __device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float 
             const float *xv = x + (size_t)v * x_stride;
 #pragma unroll
             for (int i = 0; i < KC; i++) {
-                const uint32_t s = (uint32_t)wid + 8u * i;
+                const uint32_t s = W + kAllWarps * i;
                 if (s < n_sg) convert(s, v, cache[v][i], scale[v]);
             }
-            for (uint32_t s = (uint32_t)wid + 8u * KC; s < n_sg; s += 8u)
+            for (uint32_t s = W + kAllWarps * KC; s < n_sg; s += kAllWarps)
                 convert(s, v, *reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u), scale[v]);
         } else {
-            for (uint32_t s = (uint32_t)wid; s < n_sg; s += 8u)
-                if ((lane & 7) == 0) sm.sfb[(s * 4 + ((uint32_t)lane >> 3)) * 4 + v] = 0.f;
+            for (uint32_t s = W; s < n_sg; s += kAllWarps)
+                if (m == 0) sm.sfb[(s * 4 + b) * 4 + v] = 0.f;
         }
     }
-    __syncwarp();
+    __syncthreads();
     return inv_want;
 }
 
@@ -712,8 +719,7 @@ qmv_q8q4_ring_batch_kernel(const __grid_constant__ BatchParams bpm) {
     const uint32_t first_tile = blockIdx.x + group * G, tile_stride = kGroups * G;
     const uint32_t my_tiles = p.n_tiles > first_tile ? (p.n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
     const uint32_t S = p.stages, chunks = p.chunks;
-    const uint32_t total = my_tiles * chunks;
-    if (total == 0) return;  // a group without tiles takes no part in anything below
+    const uint32_t total = my_tiles * chunks;  // 0: this group only helps with the activations
 
     const BatchSmem sm = batch_carve(smem_raw, p.n_cols, nb, (size_t)kGroups * S * F::kStageBytes);
     unsigned char *ring = sm.ring + (size_t)group * S * F::kStageBytes;
@@ -721,7 +727,7 @@ qmv_q8q4_ring_batch_kernel(const __grid_constant__ BatchParams bpm) {
     const uint32_t bar0 = smem_u32(sm.bars + group * kMaxStages);
     uint32_t *cnt = sm.cnt + group * kMaxStages;
 
-    if (wid == 0) {
+    if (wid == 0 && total != 0) {
         if (lane == 0) {
             for (int i = 0; i < kMaxStages; i++) {
                 mbar_init(bar0 + 8 * i, 1);
@@ -742,7 +748,8 @@ qmv_q8q4_ring_batch_kernel(const __grid_constant__ BatchParams bpm) {
 
     if (!p.late_wait) yule_pdl_wait();  // the activations (and the residual) come from the previous kernel
     const uint32_t tid = threadIdx.x & (kWarps * 32 - 1);
-    const float inv_scale = stage_x_batch<Q8>(sm, p.x, bpm.x_stride, nb, n_sg, group, wid, lane, tid >> 4);
+    const float inv_scale = stage_x_batch<Q8>(sm, p.x, bpm.x_stride, nb, n_sg, lane, tid >> 4);
+    if (total == 0) return;
 
     // B column n = g carries vector g / 2 (hi for even g, lo for odd); columns past 2·nb read zeros
     const bool feeds = (uint32_t)g < 2 * nb;
