@@ -94,6 +94,40 @@ def test_q8_0_q4_0_several_vectors_per_pass(backend, oracle, dtype, n_rows, n_co
         assert guarded_rel_err(y[b, :n_rows], ref) <= REL_TOL, f"vector {b}"
 
 
+@pytest.mark.parametrize("dtype,n_rows,n_cols,batch", [
+    (DType.Q4_K, 16, 256, 2),        # one tile, one super-block
+    (DType.Q6_K, 16, 256, 2),
+    (DType.Q4_K, 1000, 4096, 3),     # three vectors, ragged last tile, two stages per tile
+    (DType.Q6_K, 1000, 4096, 4),
+    (DType.Q4_K, 300, 8192, 7),
+    (DType.Q6_K, 300, 8192, 5),      # two or three vectors per pass fit beside the ring
+    (DType.Q4_K, 129, 14336, 4),     # two vectors per pass
+    (DType.Q6_K, 40, 768, 6),        # three super-blocks: five of a stage's eight warps idle
+    (DType.Q4_K, 5632, 2048, 4),
+    (DType.Q6_K, 4096, 4096, 4),
+])
+def test_q4_k_q6_k_several_vectors_per_pass(backend, oracle, dtype, n_rows, n_cols, batch):
+    """Q4_K and Q6_K (prepared: row-planar copy) with two to four activation vectors per pass of the batched ring
+    kernel, vectors of very different magnitudes, strides wider than the data."""
+    w = synth.random_blocks(dtype, 600 + n_rows, n_rows * (n_cols // 256))
+    x = synth.normal(601 + batch, batch * n_cols).reshape(batch, n_cols)
+    x *= np.float32(10.0) ** np.arange(-3, -3 + batch, dtype=np.float32)[:, None]
+    x_stride, out_stride = n_cols + 64, n_rows + 5
+    xs = np.zeros((batch, x_stride), np.float32)
+    xs[:, :n_cols] = x
+    wh, xh = backend.upload(w), backend.upload(xs.reshape(-1))
+    backend.prepare_weights(wh, dtype, n_rows, n_cols)
+    oh = backend.upload(np.full(batch * out_stride, 7.0, np.float32))
+    backend.quantized_matmul_batched(wh, xh, oh, n_rows, n_cols, dtype, batch, x_stride, out_stride)
+    y = backend.download(oh, batch * out_stride).reshape(batch, out_stride)
+    for h in (wh, xh, oh):
+        backend.free(h)
+    assert np.all(y[:, n_rows:] == 7.0)
+    for b in range(batch):
+        ref = oracle.qmv(int(dtype), w, x[b], n_rows, n_cols)
+        assert guarded_rel_err(y[b, :n_rows], ref) <= REL_TOL, f"vector {b}"
+
+
 def test_config0_shape_quantised_gaussian(backend, oracle):
     """The TinyLlama FFN-up shape of the headline matvec: 5632 x 2048 Q4_K."""
     n_rows, n_cols = 5632, 2048

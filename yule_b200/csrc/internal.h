@@ -235,6 +235,11 @@ cudaError_t launch_q8q4_ring(const QmvArgs &a, int sm_count, cudaStream_t s, uin
 uint32_t q8q4_ring_batch_width(const QmvArgs &a);
 cudaError_t launch_q8q4_ring_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches);
 
+// Q4_K and Q6_K (row-planar copy) over two to four activation vectors per pass (qmv_kquant_batch.cu): the number of
+// vectors one pass can take for this call (0: not supported), and one pass over the first `nb` vectors of `a`.
+uint32_t kquant_batch_width(const QmvArgs &a);
+cudaError_t launch_kquant_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches);
+
 // Quantised GEMM on tcgen05 for eight or more activation rows (qgemm_tc.cu): an activation
 // re-layout kernel followed by the persistent GEMM.  `scratch` holds qgemm_scratch_bytes().
 struct QGemm {

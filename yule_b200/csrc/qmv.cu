@@ -548,6 +548,24 @@ constexpr size_t kMaxSmem = 200 * 1024;
 }  // namespace
 
 cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t *launches) {
+    // Q4_K / Q6_K, several vectors: two to four per pass of the batched ring kernel (YULE_QMV_KBATCH=0: the older paths);
+    // a single left-over vector goes through the one-vector routing below
+    if (a.batch >= 2 && kquant_batch_width(a) >= 2 && !(knob("YULE_QMV_KBATCH") && atoi(knob("YULE_QMV_KBATCH")) == 0)) {
+        uint32_t done = 0;
+        while (done < a.batch) {
+            QmvArgs part = a;
+            part.x = a.x + (size_t)done * a.x_stride;
+            part.out = a.out + (size_t)done * a.out_stride;
+            part.residual = a.residual ? a.residual + (size_t)done * a.out_stride : nullptr;
+            part.batch = a.batch - done;
+            const uint32_t nb = kquant_batch_width(part);
+            if (nb < 2) return launch_qmv(part, sm_count, s, launches);  // one vector left
+            cudaError_t e = launch_kquant_batch(part, nb, sm_count, s, launches);
+            if (e != cudaSuccess) return e;
+            done += nb;
+        }
+        return cudaSuccess;
+    }
     const bool q5_mma = a.type == YULE_DTYPE_Q5_K && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0 && !a.tp.push && !a.tp.wait;
     if ((a.type == YULE_DTYPE_Q4_K || q5_mma) && q4k_mma_supported(a.n_cols, 1)) {
         // tensor-pipe path, up to four activation vectors per pass over the weights
