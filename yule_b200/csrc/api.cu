@@ -480,15 +480,20 @@ int32_t yule_cuda_attn_value(yule_cuda_ctx *ctx, yule_buffer weights, yule_buffe
 }
 
 // From how many activation rows the tcgen05 GEMM beats ceil(batch / 4) passes of the matvec kernels
-// (measured on 4096x4096 .. 128256x4096): the exact Q4_K kernel from 16, the generic kernel of the
-// other formats from 32, except Q5_K (tensor-pipe matvec at 3.5 us per row against a 195 us GEMM) from 64.
-// YULE_GEMM_MIN_BATCH overrides all three (at least 8).
-static uint32_t gemm_min_batch(uint32_t type) {
+// (measured on 1024x4096 .. 128256x4096): the exact Q4_K kernel from 16 (from 32 on matrices of up to 8M weights,
+// where four passes of the batched matvec cost less than the GEMM's fixed part), the generic kernel of the other
+// formats from 32, except Q5_K (tensor-pipe matvec at 3.5 us per row against a 195 us GEMM) from 64; from 8 where the
+// rows are too long for a batched matvec kernel to hold its activation image.  YULE_GEMM_MIN_BATCH overrides all of
+// them (at least 8).
+static uint32_t gemm_min_batch(const QmvArgs &a) {
     if (const char *e = knob("YULE_GEMM_MIN_BATCH")) {
         const int v = atoi(e);
         return v < 8 ? 8u : (uint32_t)v;
     }
-    return type == YULE_DTYPE_Q4_K ? 16u : type == YULE_DTYPE_Q5_K ? 64u : 32u;
+    const bool tuned = a.type == YULE_DTYPE_Q4_K || a.type == YULE_DTYPE_Q6_K || a.type == YULE_DTYPE_Q8_0 || a.type == YULE_DTYPE_Q4_0;
+    if (tuned && a.batch >= 8 && kquant_batch_width(a) < 2 && q8q4_ring_batch_width(a) < 2) return 8u;
+    if (a.type == YULE_DTYPE_Q4_K) return (uint64_t)a.n_rows * a.n_cols <= (8ull << 20) ? 32u : 16u;
+    return a.type == YULE_DTYPE_Q5_K ? 64u : 32u;
 }
 
 static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight_offset, yule_buffer input,
@@ -529,7 +534,7 @@ static int32_t qmv_common(yule_cuda_ctx *ctx, yule_buffer weights, size_t weight
     if (type == YULE_DTYPE_Q6_K && W.planar && weight_offset == 0 && W.planar_cols == n_cols &&
         W.planar_blocks == (uint64_t)n_rows * (n_cols / 256))
         a.planar = W.planar;
-    if (batch >= gemm_min_batch(type) && qgemm_supported(type, n_cols, batch)) {
+    if (batch >= 8 && batch >= gemm_min_batch(a) && qgemm_supported(type, n_cols, batch)) {
         // enough activation rows: one pass over the weights on the tcgen05 GEMM
         int32_t rc = ensure_gemm_scratch(ctx, qgemm_scratch_bytes(batch, n_cols));
         if (rc) return rc;

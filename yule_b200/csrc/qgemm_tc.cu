@@ -74,7 +74,13 @@ constexpr float kGenericWScale = 1024.f;      // generic kernel: weights are sca
 constexpr uint32_t kAmBytes = kBM * 16 * 2;  // the m slab of a super-block: 128 rows × 16 columns, 4 KB
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any real stall
 
-// Cycle counters of CTA 0's roles (YULE_GEMM_PROF=1 prints them after the launch): a timing aid.
+// Cycle counters of CTA 0's roles (YULE_GEMM_PROF=1 prints them after the launch): a timing aid, compiled in only
+// with -DYULE_GEMM_PROFILE (its counters cost the drain warps registers they do not have to spare).
+#ifdef YULE_GEMM_PROFILE
+constexpr bool kProfile = true;
+#else
+constexpr bool kProfile = false;
+#endif
 __device__ long long g_gemm_prof[16];
 
 struct GemmParams {
@@ -97,7 +103,8 @@ struct GemmParams {
     uint32_t raw_ring_bytes;  // generic kernel: two slots of 128 rows
     float out_scale;       // generic kernel: 1 / kGenericWScale; exact kernel: 1
     uint32_t prof;         // timing aid: record cycle counters of CTA 0
-    uint32_t skip;         // timing aid (YULE_GEMM_SKIP): 1 no unpacking, 2 no MMAs, 4 no draining; results meaningless
+    uint32_t skip;         // timing aid (YULE_GEMM_SKIP, bits): 1 no unpacking, 2 no MMAs, 4 no draining, 8 no activation copies,
+                           // 64 no weight copies, 256 the MMA threads wait for their own commits; results meaningless
     int *status;
 };
 
@@ -123,25 +130,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__constant__ int c_gemm_spin;  // timing aid: poll with test_wait instead of try_wait
 // Bounded wait.  False: the CTA is giving up (this thread ran out of time, or another did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    const bool spin = c_gemm_spin != 0;
     for (uint32_t it = 1;; it++) {
-        if (spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitCycles) {
@@ -413,7 +407,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
     constexpr uint32_t NBUF = T::NBUF, CW = T::CW, kXHalfBytes = T::kXHalfBytes, kStageBytes = T::kStageBytes;
     extern __shared__ __align__(128) unsigned char smem[];
     yule_pdl_launch_dependents();
-    const long long t_entry = p.prof ? clock64() : 0;
+    const uint32_t skip = kProfile ? p.skip : 0u;  // the timing aids exist only in profiling builds
+    const long long t_entry = (kProfile && p.prof) ? clock64() : 0;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *tail = smem + (size_t)p.stages * kStageBytes;
     unsigned char *raw = tail;                               // kRawSlots boxes of raw Q4_K bytes
@@ -474,7 +469,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     const uint32_t g = kb & 3u;
                     const uint32_t bytes = 2 * kXHalfBytes + ((!GENERIC && g == 3) ? T::kBmBytes : 0u);  // the sums ride with the last stage
                     const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes + T::kOffX);
-                    if (p.skip & 8u) {
+                    if (skip & 8u) {
                         mbar_arrive(bar_full + 8 * s);
                         continue;
                     }
@@ -497,20 +492,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             bool ok = true;
             RingPos ring;
             long long tw0 = 0, tw1 = 0, ti = 0, tc = 0;
-            const long long tstart = p.prof ? clock64() : 0;
+            const long long tstart = (kProfile && p.prof) ? clock64() : 0;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const Item wi = decode_item(p, item, bpr);
                 for (uint32_t kb = 4 * wi.sb0; kb < 4 * wi.sb1; kb++, it++, ring.advance(p.stages)) {
                     const bool mine = (it & 1u) == parity_of_mine;  // the threads alternate stages
                     const uint32_t s = ring.s, ph = ring.ph;
                     const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
-                    const long long c0 = p.prof ? clock64() : 0;
-                    if (mine && !(p.skip & 16u) && !mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status)) {
+                    const long long c0 = (kProfile && p.prof) ? clock64() : 0;
+                    if (mine && !(skip & 16u) && !mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
                     if (!mine) continue;
-                    const long long c1 = p.prof ? clock64() : 0;
+                    const long long c1 = (kProfile && p.prof) ? clock64() : 0;
                     // A parity wait only tells phase k of a barrier from phase k - 1.  The previous use of this
                     // stage may belong to the other thread: wait until it has seen that phase complete, so that
                     // this thread never asks for a phase two ahead of the barrier's.
@@ -531,7 +526,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                         break;
                     }
                     mma_progress[parity_of_mine] = it + 1;
-                    const long long c2 = p.prof ? clock64() : 0;
+                    const long long c2 = (kProfile && p.prof) ? clock64() : 0;
                     tw0 += c1 - c0;
                     tw1 += c2 - c1;
                     tc_fence_after();
@@ -541,7 +536,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
 #pragma unroll
                     for (uint32_t k16 = 0; k16 < kBK / 16; k16++) {
-                        if (p.skip & 2u) break;
+                        if (skip & 2u) break;
                         const uint64_t da = smem_desc(a + k16 * 4096, 2048, 128);
                         if constexpr (T::MERGED) {
                             // rows [0, BN) of an 8-column step are the hi terms, rows [BN, 2·BN) the lo terms
@@ -558,16 +553,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     }
                     if (!GENERIC && (kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
                         umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(x_lo + kXHalfBytes, x_lbo, 128), idesc, 0u);
-                    const long long c3 = p.prof ? clock64() : 0;
+                    const long long c3 = (kProfile && p.prof) ? clock64() : 0;
                     umma_commit(bar_empty + 8 * s);       // the slabs may be overwritten once these MMAs are done
-                    if (!(p.skip & 32u)) umma_commit(bar_acc_full + 8 * buf);  // and the accumulators may be drained
-                    if (p.skip & 256u) mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status);  // timing aid: the commit's own latency, charged to `commit`
-                    const long long c4 = p.prof ? clock64() : 0;
+                    if (!(skip & 32u)) umma_commit(bar_acc_full + 8 * buf);  // and the accumulators may be drained
+                    if (skip & 256u) mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status);  // timing aid: the commit's own latency, charged to `commit`
+                    const long long c4 = (kProfile && p.prof) ? clock64() : 0;
                     ti += c3 - c2;
                     tc += c4 - c3;
                 }
             }
-            if (p.prof && blockIdx.x == 0 && warp == kMmaWarp) {
+            if ((kProfile && p.prof) && blockIdx.x == 0 && warp == kMmaWarp) {
                 g_gemm_prof[0] = clock64() - tstart;
                 g_gemm_prof[1] = tw0;
                 g_gemm_prof[2] = tw1;
@@ -584,7 +579,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
                 if (!mbar_wait(bar_raw_empty + 8 * slot, ph ^ 1u, abort_flag, p.status)) break;
                 const uint32_t x = walk.sb * 144u, y = walk.mt * kBM;  // byte column (a multiple of 16), first row
-                if (p.skip & 64u) {  // timing aid: no raw bytes
+                if (skip & 64u) {  // timing aid: no raw bytes
                     mbar_arrive(bar_raw_full + 8 * slot);
                     continue;
                 }
@@ -688,7 +683,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         const __half2 k1024 = __half2half2(__ushort_as_half(0x6400)), kneg1024 = __half2half2(__ushort_as_half(0xE400));
         RingPos ring;
         long long pw = 0, pk = 0, pf = 0;
-        const long long pstart = p.prof ? clock64() : 0;
+        const long long pstart = (kProfile && p.prof) ? clock64() : 0;
         // the four stages of one super-block
         auto unpack_block = [&](const RowBlock &cur) {
             const ScalesMins sm = q4k_scales_mins(cur.hdr.y, cur.hdr.z, cur.hdr.w);
@@ -700,19 +695,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 const __half2 sc0 = __hsub2(as_half2(biased_pair(scw, 0x4040u + j0 * 0x0101u)), k1024);
                 const __half2 sc1 = __hsub2(as_half2(biased_pair(scw, 0x4040u + (j0 + 1) * 0x0101u)), k1024);
                 const __half2 nb0 = __hmul2(sc0, kneg1024), nb1 = __hmul2(sc1, kneg1024);  // −1024·sc ≥ −64512: exact
-                const long long c0 = p.prof ? clock64() : 0;
+                const long long c0 = (kProfile && p.prof) ? clock64() : 0;
                 if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                     ok = false;
                     return;
                 }
-                const long long c1 = p.prof ? clock64() : 0;
+                const long long c1 = (kProfile && p.prof) ? clock64() : 0;
                 pw += c1 - c0;
                 unsigned char *a = smem + (size_t)s * kStageBytes;
                 // byte b of the 32 holds column b (low nibble, sub-block 2g) and column 32 + b (high nibble)
                 const uint32_t qw[4] = {cur.q[g].x, cur.q[g].y, cur.q[g].z, cur.q[g].w};
 #pragma unroll
                 for (int half8 = 0; half8 < 2; half8++) {
-                    if (p.skip & 1u) break;
+                    if (skip & 1u) break;
                     const uint32_t w0 = qw[2 * half8], w1 = qw[2 * half8 + 1];
                     const uint32_t kc_lo = hf * 2 + half8;  // 8-column step of the low-nibble columns
                     // (1024 + q)·sc − 1024·sc = q·sc, exact; pairs are bytes (0, 2) and (1, 3) of a word
@@ -740,11 +735,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     m.w = as_u32(__hsub2(as_half2(biased_pair(sm.m_hi, 0x5342u)), k1024));
                     *reinterpret_cast<uint4 *>(a + T::kOffAm + hf * 2048 + in_core) = m;
                 }
-                const long long c2 = p.prof ? clock64() : 0;
+                const long long c2 = (kProfile && p.prof) ? clock64() : 0;
                 fence_async_smem();  // generic-proxy stores → visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);
-                const long long c3 = p.prof ? clock64() : 0;
+                const long long c3 = (kProfile && p.prof) ? clock64() : 0;
                 pk += c2 - c1;
                 pf += c3 - c2;
             }
@@ -764,7 +759,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_raw_empty + 8 * slot);  // this warp is done with the box
         }
-        if (p.prof && blockIdx.x == 0 && ptid == 0) {
+        if ((kProfile && p.prof) && blockIdx.x == 0 && ptid == 0) {
             g_gemm_prof[6] = clock64() - pstart;
             g_gemm_prof[7] = pw;
             g_gemm_prof[8] = pk;
@@ -773,13 +768,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         }  // exact Q4_K producer
     } else {
         // drain warp: TMEM lanes [32·(warp % 4), +32) = rows of the tile, columns [CW·(warp / 4), +CW)
-        const long long t_ready = p.prof ? clock64() : 0;
+        const long long t_ready = (kProfile && p.prof) ? clock64() : 0;
         yule_pdl_wait();
         const uint32_t lane_base = (warp & 3u) * 32u, col_base = (warp >> 2) * CW;
         uint32_t it = 0;
         bool ok = true;
         long long dw = 0, t_loop_end = 0;
-        const long long dstart = p.prof ? clock64() : 0;
+        const long long dstart = (kProfile && p.prof) ? clock64() : 0;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const Item wi = decode_item(p, item, bpr);
             const uint32_t mt = wi.mt, nt = wi.nt;
@@ -791,25 +786,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             uint32_t dd_cur = 0, dd_next = GENERIC ? 0u : __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)wi.sb0 * 144));  // (d, dmin) of the first super-block
             const uint32_t kb_end = 4 * wi.sb1;
             for (uint32_t kb = 4 * wi.sb0; kb < kb_end; kb++, it++) {
-                if (p.skip & 32u) break;
+                if (skip & 32u) break;
                 const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
                 if (!GENERIC && (kb & 3u) == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
                     dd_cur = dd_next;
                     if (kb + 4 < kb_end) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)((kb >> 2) + 1) * 144));
                 }
                 const float2 dd = GENERIC ? make_float2(1.f, 0.f) : __half22float2(as_half2(dd_cur));
-                const long long c0 = p.prof ? clock64() : 0;
+                const long long c0 = (kProfile && p.prof) ? clock64() : 0;
                 if (!mbar_wait(bar_acc_full + 8 * buf, aph, abort_flag, p.status)) {
                     ok = false;
                     break;
                 }
-                if (p.prof) dw += clock64() - c0;
+                if ((kProfile && p.prof)) dw += clock64() - c0;
                 tc_fence_after();
                 const uint32_t t_main = tmem_base + (lane_base << 16) + buf * T::kBufCols + col_base;
                 if constexpr (T::MERGED) {
                     // all the loads of the stage in flight together, one wait
                     uint32_t v[CW], vl[CW];
-                    if (!(p.skip & 4u)) {
+                    if (!(skip & 4u)) {
 #pragma unroll
                         for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                             tmem_ld16_issue(t_main + c0, v + c0);
@@ -822,7 +817,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 } else {
 #pragma unroll
                     for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
-                        if (p.skip & 4u) break;
+                        if (skip & 4u) break;
                         uint32_t v[16];
                         tmem_ld16(t_main + c0, v);
 #pragma unroll
@@ -843,7 +838,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
             }
             if (!ok) break;
-            if (p.prof) t_loop_end = clock64();
+            if ((kProfile && p.prof)) t_loop_end = clock64();
             const uint32_t n0 = nt * BN + col_base;
             if (p.ksplit > 1) {
                 // This item covers a part of the columns.  Every drain warp stores its block of scaled partial sums, then
@@ -907,7 +902,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 }
             }
         }
-        if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
+        if ((kProfile && p.prof) && blockIdx.x == 0 && threadIdx.x == 0) {
             g_gemm_prof[10] = clock64() - dstart;
             g_gemm_prof[11] = dw;
             g_gemm_prof[12] = t_ready - t_entry;
@@ -930,7 +925,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T::kTmemCols) : "memory");
     }
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) g_gemm_prof[15] = clock64() - t_entry;
+    if ((kProfile && p.prof) && blockIdx.x == 0 && threadIdx.x == 0) g_gemm_prof[15] = clock64() - t_entry;
 }
 
 // Activation rows → the GEMM's operand tiles, one CTA per (padded) row: power-of-two row scale,
@@ -1279,12 +1274,8 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.w_row_bytes = (uint64_t)(g.n_cols / block_size(g.type)) * block_bytes(g.type);
     p.out_scale = generic ? 1.0f / kGenericWScale : 1.0f;
     p.status = g.status;
-    p.prof = knob("YULE_GEMM_PROF") ? 1u : 0u;
-    p.skip = knob("YULE_GEMM_SKIP") ? (uint32_t)atoi(knob("YULE_GEMM_SKIP")) : 0u;
-    if (knob("YULE_GEMM_SPIN")) {
-        const int v = atoi(knob("YULE_GEMM_SPIN"));
-        cudaMemcpyToSymbolAsync(c_gemm_spin, &v, sizeof(v), 0, cudaMemcpyHostToDevice, s);
-    }
+    p.prof = (kProfile && knob("YULE_GEMM_PROF")) ? 1u : 0u;
+    p.skip = (kProfile && knob("YULE_GEMM_SKIP")) ? (uint32_t)atoi(knob("YULE_GEMM_SKIP")) : 0u;
     const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 32;
     const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
     CUtensorMap w_map;

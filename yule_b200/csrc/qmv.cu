@@ -602,6 +602,19 @@ cudaError_t launch_qmv(const QmvArgs &a, int sm_count, cudaStream_t s, uint64_t 
         }
         return cudaSuccess;
     }
+    if (a.type == YULE_DTYPE_Q6_K && a.planar && a.batch > 1 && a.batch <= 8 && q6k_mma_supported(a.n_cols) && q6k_stream_supported(a.n_cols)) {
+        // rows too long for the batched kernel's activation image: one pass of the one-vector kernel per vector
+        for (uint32_t b = 0; b < a.batch; b++) {
+            QmvArgs one = a;
+            one.x = a.x + (size_t)b * a.x_stride;
+            one.out = a.out + (size_t)b * a.out_stride;
+            one.residual = a.residual ? a.residual + (size_t)b * a.out_stride : nullptr;
+            one.batch = 1;
+            cudaError_t e = launch_qmv(one, sm_count, s, launches);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
     if (a.type == YULE_DTYPE_Q6_K && a.planar && a.batch == 1 && q6k_mma_supported(a.n_cols) && q6k_stream_supported(a.n_cols)) {
         Q6kPlanar f;
         f.planar = a.planar;
