@@ -12,7 +12,8 @@ from yule_b200 import CudaTransformerRunner, DType, YuleGpuError, synth
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("batch,mix", [(12, "q4k"), (3, "q4k"), (32, "q4k_q6k"), (9, "q8_0")])
+@pytest.mark.parametrize("batch,mix", [(12, "q4k"), (3, "q4k"), (32, "q4k_q6k"), (9, "q8_0"),
+                                       (4, "q4k_q6k"), (7, "q4k_q6k"), (2, "q8_0")])  # up to eight rows: the batched matvec kernels
 def test_batch_matches_independent_sequences(backend, oracle, batch, mix):
     kw = {"q4k": dict(linear=DType.Q4_K), "q4k_q6k": dict(linear=DType.Q4_K, ffn_down=DType.Q6_K, output=DType.Q6_K),
           "q8_0": dict(linear=DType.Q8_0)}[mix]

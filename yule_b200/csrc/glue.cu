@@ -81,6 +81,8 @@ __global__ void rms_norm_kernel(const float *__restrict__ in, const float *__res
     yule_pdl_launch_dependents();
     yule_pdl_wait();
     __shared__ float red[32];
+    in += (size_t)blockIdx.x * n;  // one CTA per row
+    out += (size_t)blockIdx.x * n;
     float ss = 0.f;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
     ss = block_sum(ss, red);
@@ -480,6 +482,12 @@ cudaError_t launch_rms_norm(const float *in, const float *w, float *out, uint32_
                             uint64_t *launches, bool pdl) {
     *launches += 1;
     return launch_kernel(rms_norm_kernel, dim3(1), dim3(1024), 0, s, pdl, in, w, out, n, eps);
+}
+cudaError_t launch_rms_norm_rows(const float *in, const float *w, float *out, uint32_t n, uint32_t rows, float eps, cudaStream_t s,
+                                 uint64_t *launches) {
+    if (rows == 0) return cudaSuccess;
+    *launches += 1;
+    return launch_kernel(rms_norm_kernel, dim3(rows), dim3(1024), 0, s, true, in, w, out, n, eps);
 }
 cudaError_t launch_rope_angles(float *q, float *k, uint32_t head_dim, uint32_t n_heads_q, uint32_t n_heads_k,
                                const RopeAngles &ang, cudaStream_t s, uint64_t *launches) {

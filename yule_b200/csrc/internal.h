@@ -389,6 +389,9 @@ cudaError_t launch_advance_rows(uint32_t *pos, uint32_t *step, uint32_t batch, c
 cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k,
                               cudaStream_t s, uint64_t *launches);
 cudaError_t launch_softmax(const float *in, float *out, uint32_t n, cudaStream_t s, uint64_t *launches);
+// `rows` contiguous rows of n elements, one CTA each.
+cudaError_t launch_rms_norm_rows(const float *in, const float *w, float *out, uint32_t n, uint32_t rows, float eps, cudaStream_t s,
+                                 uint64_t *launches);
 cudaError_t launch_rms_norm(const float *in, const float *w, float *out, uint32_t n, float eps,
                             cudaStream_t s, uint64_t *launches, bool pdl = false);
 // cos/sin hold head_dim/2 entries for this position (host-computed), passed by value.

@@ -73,7 +73,7 @@ struct yule_cuda_runner {
     // Batched prefill on the tensor-core GEMM: chunk buffers, allocated on first use
     uint32_t pf_chunk = 0, pf_splits = 1;
     float *pf_x = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_att = nullptr, *pf_gate = nullptr,
-          *pf_up = nullptr, *pf_attn_scratch = nullptr;
+          *pf_up = nullptr, *pf_attn_scratch = nullptr, *pf_norm = nullptr;
     uint32_t *pf_tokens = nullptr, *pf_tickets = nullptr;
 
     // Batched decode: `bd_batch` independent sequences advancing one token per step, each with its own KV
@@ -801,6 +801,10 @@ int32_t ensure_pinned(yule_cuda_runner *r, size_t n_words) {
 // wait has given up (the waits themselves return at once after the first failure).
 constexpr uint32_t kStatusCheckTokens = 32;
 constexpr uint32_t kPrefillChunk = 512, kPrefillMinTokens = 16, kPrefillMinChunk = 256;
+// Up to this many live rows a pass over the layers runs its linears on the batched matvec kernels (two to four rows
+// per pass over the weights, about the time of one) instead of the GEMM, whose fixed cost per launch is several
+// matvec passes.
+constexpr uint32_t kRowsMatvecMax = 8;
 
 uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
     uint32_t c = knob("YULE_CUDA_PREFILL_CHUNK") ? (uint32_t)atoi(knob("YULE_CUDA_PREFILL_CHUNK")) : kPrefillChunk;
@@ -856,7 +860,8 @@ int32_t ensure_chunk_buffers(yule_cuda_runner *r) {
         if ((rc = alloc_f32(r, (size_t)C * (qdim / N), &r->pf_q)) || (rc = alloc_f32(r, (size_t)C * (kvdim / N), &r->pf_k)) ||
             (rc = alloc_f32(r, (size_t)C * (kvdim / N), &r->pf_v)) || (rc = alloc_f32(r, C, &tok_f)) ||
             (rc = alloc_f32(r, (size_t)C * c.n_heads, &tick_f)) ||
-            (rc = alloc_f32(r, (size_t)C * attn_scratch_floats(c.n_heads / N, r->pf_splits, hd) + 4, &r->pf_attn_scratch)))
+            (rc = alloc_f32(r, (size_t)C * attn_scratch_floats(c.n_heads / N, r->pf_splits, hd) + 4, &r->pf_attn_scratch)) ||
+            (rc = alloc_f32(r, (size_t)kRowsMatvecMax * dim, &r->pf_norm)))
             return rc;
         r->pf_tokens = (uint32_t *)tok_f;
         r->pf_tickets = (uint32_t *)tick_f;  // zero-filled by the allocator; the kernel leaves them at zero
@@ -925,6 +930,46 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         g.pdl = true;  // barrier set-up, TMEM allocation and the first weight copies overlap with the re-layout before it
         ok(launch_qgemm_mm(g, sms, s, launches));
     };
+    // Few live rows: the same sequence of linears on the matvec kernels.  `prep` leaves the rows the next linears read
+    // in `act`: normed rows in a buffer of their own, SwiGLU in place, anything else where it is.
+    bool mv = ps.n_live <= kRowsMatvecMax;
+    if (const char *k = knob("YULE_ROWS_MATVEC")) mv = mv && atoi(k) != 0;
+    const float *act = nullptr;
+    auto prep = [&](float *x, uint32_t cols, const float *norm_w, const float *gate) {
+        if (!mv) {
+            xprep(x, cols, norm_w, gate);
+        } else if (norm_w) {
+            ok(launch_rms_norm_rows(x, norm_w, r->pf_norm, cols, ps.n_live, c.norm_eps, s, launches));
+            act = r->pf_norm;
+        } else if (gate) {
+            ok(launch_silu_mul(gate, x, x, ps.n_live * cols, s, launches, true));
+            act = x;
+        } else {
+            act = x;
+        }
+    };
+    auto lin = [&](const Tensor &t, uint32_t rows, uint32_t cols, float *out, uint32_t stride, const float *residual) {
+        if (!mv) {
+            mm(t, rows, cols, out, stride, residual);
+            return;
+        }
+        QmvArgs a = {};
+        a.w = (const uint8_t *)t.buf.ptr;
+        a.x = act;
+        a.out = out;
+        a.n_rows = rows;
+        a.n_cols = cols;
+        a.type = t.type;
+        a.batch = ps.n_live;
+        a.x_stride = cols;
+        a.out_stride = stride;
+        a.residual = residual;
+        if (t.type == YULE_DTYPE_Q6_K && t.buf.planar && t.buf.planar_cols == cols) a.planar = t.buf.planar;
+        a.status = ctx->device_status;
+        a.wait_cycles = ctx->wait_cycles;
+        a.pdl = true;  // set-up and the first weight copies run under the tail of the kernel before; the rows are read after the wait
+        ok(launch_qmv(a, sms, s, launches));
+    };
     const uint32_t epochs_per_tick = 5 * c.n_layers + 1;
     uint32_t xchg_index = 0;
     auto exchange = [&](size_t offset, uint32_t per_rank, uint32_t stride) {
@@ -936,10 +981,10 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
     for (uint32_t l = 0; l < c.n_layers; l++) {
         Layer &L = r->layers[l];
         // attention block: RMSNorm folded into the re-layout, Q/K/V share it; this rank's heads only
-        xprep(r->pf_x, dim, L.attn_norm_f32, nullptr);
-        mm(L.attn_q, qdim_l, dim, r->pf_q, qdim_l, nullptr);
-        mm(L.attn_k, kvdim_l, dim, r->pf_k, kvdim_l, nullptr);
-        mm(L.attn_v, kvdim_l, dim, r->pf_v, kvdim_l, nullptr);
+        prep(r->pf_x, dim, L.attn_norm_f32, nullptr);
+        lin(L.attn_q, qdim_l, dim, r->pf_q, qdim_l, nullptr);
+        lin(L.attn_k, kvdim_l, dim, r->pf_k, kvdim_l, nullptr);
+        lin(L.attn_v, kvdim_l, dim, r->pf_v, kvdim_l, nullptr);
         AttnDecode a;
         if (ps.batch) {
             ok(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, r->bd_k[l], r->bd_v[l], r->rope_cos, r->rope_sin, 0, ps.n_live, hd,
@@ -973,23 +1018,23 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         a.out_stride = qdim;
         ok(launch_attn_decode(a, s, launches));
         exchange(r->xb_att, qdim_l, qdim);
-        xprep(r->pf_att, qdim, nullptr, nullptr);
-        mm(L.attn_output, dim_l, qdim, r->pf_x + (size_t)R * dim_l, dim, r->pf_x + (size_t)R * dim_l);  // x += Wo · attention
+        prep(r->pf_att, qdim, nullptr, nullptr);
+        lin(L.attn_output, dim_l, qdim, r->pf_x + (size_t)R * dim_l, dim, r->pf_x + (size_t)R * dim_l);  // x += Wo · attention
         exchange(r->xb_x, dim_l, dim);
         // feed-forward block: RMSNorm folded in, gate/up share the re-layout, SwiGLU folded into the next one
-        xprep(r->pf_x, dim, L.ffn_norm_f32, nullptr);
-        mm(L.ffn_gate, ff_l, dim, r->pf_gate + (size_t)R * ff_l, ff, nullptr);
-        mm(L.ffn_up, ff_l, dim, r->pf_up + (size_t)R * ff_l, ff, nullptr);
+        prep(r->pf_x, dim, L.ffn_norm_f32, nullptr);
+        lin(L.ffn_gate, ff_l, dim, r->pf_gate + (size_t)R * ff_l, ff, nullptr);
+        lin(L.ffn_up, ff_l, dim, r->pf_up + (size_t)R * ff_l, ff, nullptr);
         exchange(r->xb_gate, ff_l, ff);
         exchange(r->xb_up, ff_l, ff);
-        xprep(r->pf_up, ff, nullptr, r->pf_gate);
-        mm(L.ffn_down, dim_l, ff, r->pf_x + (size_t)R * dim_l, dim, r->pf_x + (size_t)R * dim_l);  // x += Wdown · (silu(gate) · up)
+        prep(r->pf_up, ff, nullptr, r->pf_gate);
+        lin(L.ffn_down, dim_l, ff, r->pf_x + (size_t)R * dim_l, dim, r->pf_x + (size_t)R * dim_l);  // x += Wdown · (silu(gate) · up)
         exchange(r->xb_x, dim_l, dim);
     }
     if (ps.batch) {
         const Tensor &out_w = r->output.set ? r->output : r->token_embd;
-        xprep(r->pf_x, dim, r->output_norm_f32, nullptr);
-        mm(out_w, vocab_l, dim, r->bd_logits + (size_t)R * vocab_l, c.vocab_size, nullptr);
+        prep(r->pf_x, dim, r->output_norm_f32, nullptr);
+        lin(out_w, vocab_l, dim, r->bd_logits + (size_t)R * vocab_l, c.vocab_size, nullptr);
         exchange(r->xb_logits, vocab_l, c.vocab_size);
         ok(launch_argmax_rows(r->bd_logits, c.vocab_size, ps.n_live, r->bd_tokens, r->bd_pos, r->bd_step, r->bd_history, c.max_seq_len + 1, s, launches));
         ok(launch_advance_rows(r->bd_pos, r->bd_step, ps.n_live, s, launches));
