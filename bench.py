@@ -161,6 +161,31 @@ def build_model(rank: int, linear: str = "Q4_K"):
     return cfg, weights, prompt
 
 
+def small_batch_decode(backend, cfg, weights, n_prompt: int = 8, n_gen: int = 64):
+    """The same model serving a few independent sequences per step (own KV caches and positions, device picks):
+    every linear reads its weights once per step for up to four sequences (batched matvec kernels) or for all of
+    them (GEMM, from nine sequences).  Device time per step over `n_prompt + n_gen` steps, tokens/s over all sequences."""
+    from yule_b200 import CudaTransformerRunner, synth
+    out = {}
+    for batch in (4, 8, 16):
+        run = CudaTransformerRunner(backend, cfg, weights, fused=1)
+        prompts = synth.tokens(7 + batch, batch * n_prompt, cfg.vocab_size).reshape(batch, n_prompt)
+        run.generate_greedy_batch(prompts, 4)  # warm-up: buffers, graph
+        run.reset_batch()
+        backend.synchronize()
+        backend.event_reset()
+        e0 = backend.event_record()
+        run.generate_greedy_batch(prompts, n_gen)  # the prompt tokens are steps of the same kind
+        e1 = backend.event_record()
+        ms = backend.event_elapsed_ms(e0, e1)
+        steps = n_prompt + n_gen
+        out[f"batch_{batch}"] = {"steps": steps, "ms_per_step": round(ms / steps, 4),
+                                 "tokens_per_s": round(batch * steps / (ms * 1e-3), 1),
+                                 "linears": "batched matvec kernels" if batch <= 8 else "tcgen05 GEMM"}
+        run.close()
+    return out
+
+
 def decode_bytes_per_token(cfg, weights, pos: int, tp_world: int = 1) -> int:
     """Algorithmic HBM bytes one GPU reads per decode token: every matrix (shard) once, the embedding row,
     and this GPU's KV rows of positions [0, pos] for every layer (K and V)."""
@@ -552,6 +577,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
     if not tp and not args.no_tp:
         tp_obj = measure_tp(args, rank, world, local_rank, dist, peaks)
 
+    small_batch = None
+    if rank == 0 and not tp and not args.small:
+        small_batch = small_batch_decode(backend, cfg, weights)
+
     if rank == 0:
         roof = matvec_ring_roofline(backend, peaks, peak_kind, iters=20 if args.small else 1000)
         roof_large = None if (args.small or world > 1 or args.workload != "c1") else large_shape_rooflines(backend, peaks)
@@ -585,7 +614,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
                        "prefill_tokens_per_s": round(N_PROMPT * args.steps / (prefill_ms * 1e-3), 1),
                        "hbm_bytes_per_token": bpt, "achieved_gbs": round(decode_gbs, 1),
                        "frac_of_peak": round(decode_gbs / float(peaks["hbm_gbs"]), 4),
-                       "greedy_stream_matches_host_argmax_path": e2e_tokens_match},
+                       "greedy_stream_matches_host_argmax_path": e2e_tokens_match,
+                       "several_sequences": small_batch},
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": 8 * N_GEN,
                     "d2h_bytes_per_step": 4 * cfg.vocab_size * N_GEN,
                     "path": "ModelRunner prefill/decode_step over the C ABI, host logits + host argmax"},

@@ -481,7 +481,9 @@ qmv_q8q4_ring_kernel(const __grid_constant__ RingParams p) {
 //
 // Shared-memory image of the activations: per 16-weight chunk (block b of group s, MMA j: chunk (4s + b)·2 + j)
 // and B column n = 2v + part, four entries t of 8 bytes = the four halves lane t multiplies:
-//   Q8_0  chunk j of a block = its weights 8t + 4j .. 8t + 4j + 3 for t = 0..3
+//   Q8_0  chunk j of a block = its weights 16j + 4t .. 16j + 4t + 3 for t = 0..3 (the four lanes of a quad read 16
+//         contiguous bytes of a row, and the eight rows of an MMA sit at distinct multiples of 16 bytes mod 128:
+//         no bank conflicts; lane t at byte 8t, the first version, had them two ways)
 //   Q4_0  word t of a block holds its weights 8t..8t+7 (byte j: weight 2j low, 2j+1 high); chunk 0 = the low
 //         nibbles, entry t = weights 8t, 8t+4, 8t+2, 8t+6; chunk 1 = the high nibbles, entry t = 8t+1, 8t+5, 8t+3,
 //         8t+7 (the order in which the nibbles of a word fall into the A registers)
@@ -631,7 +633,9 @@ __device__ __forceinline__ float stage_x_batch(const BatchSmem &sm, const float 
                 lo = make_uint2(__byte_perm(oth_l, mine_l13, 0x5410), __byte_perm(oth_l, mine_l13, 0x7632));
             }
         }
-        const uint32_t chunk = (s * 4 + b) * 2 + (m & 1u), t = m >> 1;
+        // Q8_0: chunk j of a block = its weights 16j..16j+15, lane m % 4 of it; Q4_0: the lane pair m / 2 built entry m / 2
+        // of chunk 0 (even lane) and of chunk 1 (odd lane)
+        const uint32_t chunk = (s * 4 + b) * 2 + (Q8 ? (m >> 2) : (m & 1u)), t = Q8 ? (m & 3u) : (m >> 1);
         unsigned char *dst = sm.xb + (size_t)chunk * chunk_bytes + (2 * v) * 32u + t * 8u;
         *reinterpret_cast<uint2 *>(dst) = hi;
         *reinterpret_cast<uint2 *>(dst + 32) = lo;
@@ -670,7 +674,7 @@ __device__ __forceinline__ void consume_block_batch(const unsigned char *r0, int
     const unsigned char *blk0 = r0 + B * F::kBlockBytes, *blk1 = blk0 + 8 * F::kRowPitch;
     // the quants start 2 bytes into the block: 4-byte aligned for odd B, 2 bytes past a word for even B
     constexpr bool kShift = (B & 1) == 0;
-    const uint32_t lane_off = Q8 ? 8u * t : 4u * t;
+    const uint32_t lane_off = 4u * t;
     const unsigned char *q0 = blk0 + (kShift ? 0 : 2) + lane_off, *q1 = blk1 + (kShift ? 0 : 2) + lane_off;
     auto word = [&](const unsigned char *q, int i) {
         const uint32_t *w = reinterpret_cast<const uint32_t *>(q);
@@ -680,7 +684,7 @@ __device__ __forceinline__ void consume_block_batch(const unsigned char *r0, int
     if (Q8) {
 #pragma unroll
         for (int j = 0; j < 2; j++) {
-            const uint32_t w0 = word(q0, j) ^ 0x80808080u, w1 = word(q1, j) ^ 0x80808080u;
+            const uint32_t w0 = word(q0, 4 * j) ^ 0x80808080u, w1 = word(q1, 4 * j) ^ 0x80808080u;
             const uint2 b = *reinterpret_cast<const uint2 *>(bp + j * chunk_stride);
             const uint32_t a0 = __byte_perm(w0, 0u, 0x4140), a1 = __byte_perm(w1, 0u, 0x4140), a2 = __byte_perm(w0, 0u, 0x4342),
                            a3 = __byte_perm(w1, 0u, 0x4342);
