@@ -69,7 +69,9 @@ def test_batched_equals_per_vector(backend, oracle, dtype, batch):
     (DType.Q8_0, 1000, 4096, 3),     # three vectors, ragged last tile, four stages per tile
     (DType.Q4_0, 1000, 4096, 4),
     (DType.Q8_0, 300, 8192, 7),      # three vectors per pass fit beside the ring: 3 + 3 + 1
-    (DType.Q4_0, 129, 14336, 4),     # two vectors per pass
+    (DType.Q4_0, 129, 14336, 4),     # rows longer than one launch's image: three launches over a part of the columns each
+    (DType.Q8_0, 200, 14336, 3),
+    (DType.Q8_0, 64, 28672, 2),
     (DType.Q4_0, 40, 512, 6),
     (DType.Q8_0, 4096, 4096, 4),
 ])
@@ -101,7 +103,9 @@ def test_q8_0_q4_0_several_vectors_per_pass(backend, oracle, dtype, n_rows, n_co
     (DType.Q6_K, 1000, 4096, 4),
     (DType.Q4_K, 300, 8192, 7),
     (DType.Q6_K, 300, 8192, 5),      # two or three vectors per pass fit beside the ring
-    (DType.Q4_K, 129, 14336, 4),     # two vectors per pass
+    (DType.Q4_K, 129, 14336, 4),     # rows longer than one launch's image: three launches over a part of the columns each
+    (DType.Q6_K, 129, 14336, 4),
+    (DType.Q4_K, 64, 28672, 3),
     (DType.Q6_K, 40, 768, 6),        # three super-blocks: five of a stage's eight warps idle
     (DType.Q4_K, 5632, 2048, 4),
     (DType.Q6_K, 4096, 4096, 4),

@@ -83,6 +83,7 @@ struct KBatchParams {
     const float *residual;
     uint32_t n_rows, n_cols, n_tiles, stages, chunks;
     uint32_t nb, x_stride, out_stride, late_wait;
+    uint32_t blk_off;  // first super-block of the rows this launch covers (a launch takes a range of the columns)
     int *status;
     long long wait_cycles;
 };
@@ -129,7 +130,7 @@ __device__ __forceinline__ void issue_stage(const KBatchParams &p, uint32_t tile
     // Tiled copies by the first lane; every box is as wide as its plane's shared-memory row pitch (what lies beyond the
     // eight super-blocks is never read), rows past the end of the matrix arrive as zeros.
     if (lane == 0) {
-        const uint32_t row0 = tile * kStageRows, blk0 = chunk * kStageBlocks;
+        const uint32_t row0 = tile * kStageRows, blk0 = p.blk_off + chunk * kStageBlocks;
         mbar_arrive_expect_tx(bar, stage_bytes<Q6>());
         auto box = [&](uint32_t off, const CUtensorMap *m, uint32_t x) {
             asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -491,8 +492,10 @@ uint32_t batch_stages(bool q6, uint32_t n_cols, uint32_t nb) {
     return st > (size_t)kMaxStages ? (uint32_t)kMaxStages : (uint32_t)st;
 }
 
+// One launch over the columns [256·blk_off, 256·blk_off + part_cols) of every row; `residual` is added to its results.
 template <bool Q6>
-cudaError_t launch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, int sm_count, cudaStream_t s) {
+cudaError_t launch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, uint32_t blk_off, uint32_t part_cols, const float *residual,
+                           int sm_count, cudaStream_t s) {
     KBatchParams p = {};
     const uint32_t bpr = a.n_cols / 256;
     if (Q6) {
@@ -510,12 +513,13 @@ cudaError_t launch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, int s
         if (me != cudaSuccess) return me;
     }
     p.out = a.out;
-    p.x = a.x;
-    p.residual = a.residual;
+    p.x = a.x + (size_t)blk_off * 256;
+    p.residual = residual;
     p.n_rows = a.n_rows;
-    p.n_cols = a.n_cols;
+    p.n_cols = part_cols;
+    p.blk_off = blk_off;
     p.n_tiles = (a.n_rows + kStageRows - 1) / kStageRows;
-    p.chunks = (bpr + kStageBlocks - 1) / kStageBlocks;
+    p.chunks = (part_cols / 256 + kStageBlocks - 1) / kStageBlocks;
     p.nb = nb;
     p.x_stride = a.x_stride;
     p.out_stride = a.out_stride;
@@ -528,7 +532,7 @@ cudaError_t launch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, int s
     const uint32_t need = jobs_per_group * p.chunks;
     if (stages > need) stages = need;
     p.stages = stages;
-    const size_t smem = (size_t)stages * kGroups * stage_bytes<Q6>() + fixed_bytes(a.n_cols, nb);
+    const size_t smem = (size_t)stages * kGroups * stage_bytes<Q6>() + fixed_bytes(part_cols, nb);
     auto kern = qmv_kquant_batch_kernel<Q6>;
     static bool attr_done[64] = {};  // the opt-in for large dynamic shared memory is a per-device attribute
     static std::mutex mu;
@@ -546,6 +550,19 @@ cudaError_t launch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, int s
     return launch_kernel(kern, dim3(grid), dim3(kThreadsCta), smem, s, a.pdl, p);
 }
 
+// Columns one launch covers for `nb` vectors: all of them if their activation image leaves room for enough ring slots
+// (three per group for Q4_K, two for Q6_K), else the largest multiple of a stage's 2048 columns that does; rows longer
+// than that take several launches, each adding its columns' share to the result of the one before.  0: nothing fits.
+uint32_t part_cols_for(bool q6, uint32_t n_cols, uint32_t nb) {
+    const uint32_t want = q6 ? 2u : 3u;
+    if (batch_stages(q6, n_cols, nb) >= want) return n_cols;
+    const uint32_t step = kStageBlocks * 256;
+    uint32_t best = 0;
+    for (uint32_t c = step; c < n_cols; c += step)
+        if (batch_stages(q6, c, nb) >= want) best = c;
+    return best >= 2 * step ? best : 0;  // shorter parts would be mostly launch overhead
+}
+
 }  // namespace
 
 uint32_t kquant_batch_width(const QmvArgs &a) {
@@ -555,23 +572,37 @@ uint32_t kquant_batch_width(const QmvArgs &a) {
     if (a.batch < 2 || a.n_cols == 0 || a.n_cols % 256 || a.n_rows == 0 || a.x_stride % 4) return 0;
     if (a.norm_w || a.tp.push || a.tp.wait) return 0;  // fused prologues and exchanges stay with the one-pass kernels
     if ((reinterpret_cast<uintptr_t>(q6 ? (const void *)a.planar : (const void *)a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return 0;
-    // Q4_K: the widest pass that leaves three ring slots per group, else the widest with two; Q6_K (stages half as
-    // large again): the widest with two
-    if (!q6)
-        for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
-            if (batch_stages(q6, a.n_cols, nb) >= 3) return nb;
+    // the widest pass whose image fits whole; for longer rows the widest that fits in parts of at least two stages
     for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
-        if (batch_stages(q6, a.n_cols, nb) >= 2) return nb;
+        if (part_cols_for(q6, a.n_cols, nb) == a.n_cols) return nb;
+    for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
+        if (part_cols_for(q6, a.n_cols, nb) != 0) return nb;
     return 0;
 }
 
 cudaError_t launch_kquant_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches) {
     const bool q6 = a.type == YULE_DTYPE_Q6_K;
-    const uint32_t stages = batch_stages(q6, a.n_cols, nb);
-    if (nb < 2 || nb > 4 || stages < 2) return cudaErrorInvalidValue;
-    cudaError_t e = q6 ? launch_variant<true>(a, nb, stages, sm_count, s) : launch_variant<false>(a, nb, stages, sm_count, s);
-    if (e == cudaSuccess) *launches += 1;
-    return e;
+    if (nb < 2 || nb > 4) return cudaErrorInvalidValue;
+    const uint32_t part = part_cols_for(q6, a.n_cols, nb);
+    if (part == 0) return cudaErrorInvalidValue;
+    // parts of equal length (in stages) rather than full parts and a short tail
+    const uint32_t step = kStageBlocks * 256;
+    const uint32_t n_parts = (a.n_cols + part - 1) / part;
+    const uint32_t stages_total = (a.n_cols + step - 1) / step;
+    uint32_t col = 0;
+    for (uint32_t i = 0; i < n_parts; i++) {
+        const uint32_t st = stages_total / n_parts + (i < stages_total % n_parts ? 1u : 0u);
+        uint32_t cols = st * step;
+        if (col + cols > a.n_cols) cols = a.n_cols - col;
+        const uint32_t stages = batch_stages(q6, cols, nb);
+        const float *residual = i == 0 ? a.residual : a.out;  // later parts add to what the earlier ones stored
+        cudaError_t e = q6 ? launch_variant<true>(a, nb, stages, col / 256, cols, residual, sm_count, s)
+                           : launch_variant<false>(a, nb, stages, col / 256, cols, residual, sm_count, s);
+        if (e != cudaSuccess) return e;
+        *launches += 1;
+        col += cols;
+    }
+    return cudaSuccess;
 }
 
 }  // namespace yule

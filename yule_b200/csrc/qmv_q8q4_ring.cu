@@ -255,6 +255,7 @@ struct RingParams {
     int *status;
     long long wait_cycles;
     uint32_t late_wait;
+    uint32_t sg_off;  // first 128-column group of the rows this launch covers (the batched kernel may take a range of the columns)
 };
 
 template <bool Q8>
@@ -268,7 +269,7 @@ __device__ __forceinline__ void issue_stage(const RingParams &p, uint32_t tile, 
     if (lane == 0) {
         mbar_arrive_expect_tx(bar, F::kStageBytes);
         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-                     "l"(reinterpret_cast<uint64_t>(&p.map)), "r"(bar), "r"(chunk * F::kStageSgs * (F::kSgBytes / 8u)), "r"(tile * kStageRows)
+                     "l"(reinterpret_cast<uint64_t>(&p.map)), "r"(bar), "r"((p.sg_off + chunk * F::kStageSgs) * (F::kSgBytes / 8u)), "r"(tile * kStageRows)
                      : "memory");
     }
     __syncwarp();
@@ -889,8 +890,10 @@ cudaError_t launch_variant(const QmvArgs &a, int sm_count, cudaStream_t s) {
     return launch_kernel(kern, dim3(grid), dim3(kThreadsCta), smem, s, a.pdl, p);
 }
 
+// One launch over the columns [128·sg_off, 128·sg_off + part_cols) of every row; `residual` is added to its results.
 template <bool Q8>
-cudaError_t launch_batch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, int sm_count, cudaStream_t s) {
+cudaError_t launch_batch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, uint32_t sg_off, uint32_t part_cols, const float *residual,
+                                 int sm_count, cudaStream_t s) {
     using F = Fmt<Q8>;
     BatchParams bp = {};
     RingParams &p = bp.r;
@@ -902,17 +905,18 @@ cudaError_t launch_batch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages,
     p.w = a.w;
     p.out = a.out;
     p.n_rows = a.n_rows;
-    p.n_cols = a.n_cols;
+    p.n_cols = part_cols;
+    p.sg_off = sg_off;
     p.n_tiles = (a.n_rows + kStageRows - 1) / kStageRows;
-    p.x = a.x;
-    p.residual = a.residual;
+    p.x = a.x + (size_t)sg_off * 128;
+    p.residual = residual;
     p.status = a.status;
     p.wait_cycles = a.wait_cycles;
     p.late_wait = (a.pdl && a.late_wait) ? 1u : 0u;
     bp.nb = nb;
     bp.x_stride = a.x_stride;
     bp.out_stride = a.out_stride;
-    const uint32_t n_sg = a.n_cols / 128;
+    const uint32_t n_sg = part_cols / 128;
     p.chunks = (n_sg + F::kStageSgs - 1) / F::kStageSgs;
     uint32_t grid = (p.n_tiles + kGroups - 1) / kGroups;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
@@ -920,7 +924,7 @@ cudaError_t launch_batch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages,
     const uint32_t need = jobs_per_group * p.chunks;
     if (stages > need) stages = need;
     p.stages = stages;
-    const size_t smem = (size_t)stages * kGroups * F::kStageBytes + batch_fixed_bytes(a.n_cols, nb);
+    const size_t smem = (size_t)stages * kGroups * F::kStageBytes + batch_fixed_bytes(part_cols, nb);
     auto kern = qmv_q8q4_ring_batch_kernel<Q8>;
     static bool attr_done[64] = {};  // the opt-in for large dynamic shared memory is a per-device attribute
     static std::mutex mu;
@@ -947,25 +951,54 @@ uint32_t batch_stages(uint32_t type, uint32_t n_cols, uint32_t nb) {
     return st > (size_t)kMaxStages ? (uint32_t)kMaxStages : (uint32_t)st;
 }
 
+// Columns one launch covers for `nb` vectors: all of them if their activation image leaves room for three ring slots
+// per group, else the largest multiple of a stage's columns that does; rows longer than that take several launches,
+// each adding its columns' share to the result of the one before.  0: nothing fits.
+uint32_t batch_part_cols(uint32_t type, uint32_t n_cols, uint32_t nb) {
+    if (batch_stages(type, n_cols, nb) >= 3) return n_cols;
+    const uint32_t step = 128u * (type == YULE_DTYPE_Q8_0 ? Fmt<true>::kStageSgs : Fmt<false>::kStageSgs);
+    uint32_t best = 0;
+    for (uint32_t c = step; c < n_cols; c += step)
+        if (batch_stages(type, c, nb) >= 3) best = c;
+    return best >= 4096 ? best : 0;  // shorter parts would be mostly launch overhead
+}
+
 }  // namespace
 
 uint32_t q8q4_ring_batch_width(const QmvArgs &a) {
     if (a.type != YULE_DTYPE_Q8_0 && a.type != YULE_DTYPE_Q4_0) return 0;
     if (a.batch < 2 || a.n_cols == 0 || a.n_cols % 256 || a.n_rows == 0 || a.x_stride % 4) return 0;
     if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return 0;
-    // the widest pass that leaves at least three ring slots per group (two for very long rows)
+    // the widest pass whose image fits whole; for longer rows the widest that fits in parts
     for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
-        if (batch_stages(a.type, a.n_cols, nb) >= 3) return nb;
-    return batch_stages(a.type, a.n_cols, 2) >= 2 ? 2 : 0;
+        if (batch_part_cols(a.type, a.n_cols, nb) == a.n_cols) return nb;
+    for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
+        if (batch_part_cols(a.type, a.n_cols, nb) != 0) return nb;
+    return 0;
 }
 
 cudaError_t launch_q8q4_ring_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches) {
-    const uint32_t stages = batch_stages(a.type, a.n_cols, nb);
-    if (nb < 2 || nb > 4 || stages < 2) return cudaErrorInvalidValue;
-    cudaError_t e = a.type == YULE_DTYPE_Q8_0 ? launch_batch_variant<true>(a, nb, stages, sm_count, s)
-                                               : launch_batch_variant<false>(a, nb, stages, sm_count, s);
-    if (e == cudaSuccess) *launches += 1;
-    return e;
+    if (nb < 2 || nb > 4) return cudaErrorInvalidValue;
+    const uint32_t part = batch_part_cols(a.type, a.n_cols, nb);
+    if (part == 0) return cudaErrorInvalidValue;
+    const bool q8 = a.type == YULE_DTYPE_Q8_0;
+    const uint32_t step = 128u * (q8 ? Fmt<true>::kStageSgs : Fmt<false>::kStageSgs);
+    const uint32_t n_parts = (a.n_cols + part - 1) / part;
+    const uint32_t stages_total = (a.n_cols + step - 1) / step;
+    uint32_t col = 0;
+    for (uint32_t i = 0; i < n_parts; i++) {  // parts of equal length (in stages)
+        const uint32_t st = stages_total / n_parts + (i < stages_total % n_parts ? 1u : 0u);
+        uint32_t cols = st * step;
+        if (col + cols > a.n_cols) cols = a.n_cols - col;
+        const uint32_t stages = batch_stages(a.type, cols, nb);
+        const float *residual = i == 0 ? a.residual : a.out;  // later parts add to what the earlier ones stored
+        cudaError_t e = q8 ? launch_batch_variant<true>(a, nb, stages, col / 128, cols, residual, sm_count, s)
+                           : launch_batch_variant<false>(a, nb, stages, col / 128, cols, residual, sm_count, s);
+        if (e != cudaSuccess) return e;
+        *launches += 1;
+        col += cols;
+    }
+    return cudaSuccess;
 }
 
 bool q8q4_ring_supported(const QmvArgs &a) {
