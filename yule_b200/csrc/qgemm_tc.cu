@@ -14,12 +14,18 @@
 // more MMA per super-block, (m of the 8 sub-blocks) × (per-sub-block sums of x), drained with −dmin.
 // Activations are fp32, which tcgen05 cannot take: each row is scaled by a power of two that puts
 // its largest element in [2¹³, 2¹⁴) and split into fp16 hi + lo (22 significant bits); two MMAs per
-// 16 columns, W·x_hi and W·x_lo.  The tensor core adds into its fp32 accumulator with truncation, a
+// 16 columns, W·x_hi and W·x_lo (up to 64 activation rows one MMA against both terms side by side as
+// one operand of twice the rows).  The tensor core adds into its fp32 accumulator with truncation, a
 // bias that grows with the chain length; draining after every stage keeps a chain at 8 MMAs and
 // leaves the long sum to ordinary round-to-nearest fp32.  The result matches the fp32 matvec to
 // fp32 rounding.
 //
-// One CTA per SM, 20 warps, persistent over (row tile, activation tile) pairs:
+// Work items: (row tile, activation tile) pairs; when these are few (small matrices, tensor-parallel
+// shards, few activation rows) the super-blocks of a row are split into up to 16 parts, one item each,
+// whose scaled partial sums the last drain warp of a (tile, warp) to finish adds up in the order of
+// the parts.
+//
+// One CTA per SM, 20 warps, persistent over the work items:
 //   warps 0-7   drain warps: tcgen05.ld of their 32 TMEM lanes × half of the columns after every
 //               stage, FMA by d (and −dmin) into registers; at the end of a tile scale, residual, store
 //   warp  8     one thread: bulk copies (TMA engine) of the pre-arranged activation tiles
