@@ -180,9 +180,11 @@ int32_t yule_cuda_sample(yule_cuda_ctx *ctx, yule_buffer logits, uint32_t n, con
 /* `batch` activation vectors against one weight read: input is
  * [batch][x_stride] floats, output [batch][out_stride] floats.  Same per-row
  * arithmetic as quantized_matmul.  Small batches go through the matvec kernels
- * four vectors at a time; from 16 vectors of Q4_K, 64 of Q5_K, or 32 of the
- * other block formats (n_cols a multiple of 256), the tcgen05 GEMM takes one
- * pass over the weights.
+ * four vectors at a time (Q4_K, Q6_K, Q8_0, Q4_0: four vectors share the
+ * tensor-core instructions of one, so a pass costs about one vector's time);
+ * from 16 vectors of Q4_K (32 on matrices of up to 8M weights), 64 of Q5_K, or
+ * 32 of the other block formats (n_cols a multiple of 256), the tcgen05 GEMM
+ * takes one pass over the weights.
  * The GEMM keeps its activation tiles in a scratch owned by the context, grown
  * on demand; growing is not possible while a graph is being captured, so run
  * one call of the largest batch before yule_cuda_graph_begin. */
