@@ -303,6 +303,13 @@ typedef struct {
     float logit_softcap;         /* the same on the final logits (:1027-1032); 0 = none */
     float norm_weight_offset;    /* Gemma: norms use (w + offset), embeddings are scaled by sqrt(dim) (:246-275, :568-574) */
     uint32_t geglu;              /* Gemma: gelu(gate) * up instead of SiLU(gate) * up (:974-978) */
+    /* Mixture of experts (:395-397, :813-958): n_experts > 0 replaces the dense FFN of every layer by a router
+     * ("blk.N.ffn_gate_inp.weight", [n_experts][dim], F32 / F16 or a block format), a softmax over its logits, the
+     * n_experts_used most probable experts (ties: lower index first) with their probabilities renormalised, and the
+     * weighted sum of those experts' SwiGLU FFNs.  Expert weights: packed, "blk.N.ffn_{gate,up,down}_exps.weight"
+     * (expert e = the e-th of n_experts equal slices), or one tensor per expert, "blk.N.ffn_{gate,up,down}.E.weight".
+     * Such a runner works in mode 0 (one kernel per dispatch, the chosen expert indices read back once per layer). */
+    uint32_t n_experts, n_experts_used;
 } yule_runner_config;
 
 int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cfg,

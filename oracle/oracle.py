@@ -30,6 +30,7 @@ class ModelConfig(C.Structure):
         ("mod_enabled", C.c_int32), ("simd", C.c_int32), ("n_threads", C.c_int32),
         ("rotary_dim", C.c_uint32), ("sliding_window", C.c_uint32), ("attn_logit_softcap", C.c_float),
         ("logit_softcap", C.c_float), ("norm_weight_offset", C.c_float), ("geglu", C.c_int32),
+        ("n_experts", C.c_uint32), ("n_experts_used", C.c_uint32),
     ]
 
 
@@ -75,6 +76,8 @@ def _load() -> C.CDLL:
     lib.yo_sample.restype = C.c_int64
     lib.yo_gelu.argtypes = [C.c_float]
     lib.yo_gelu.restype = C.c_float
+    lib.yo_moe_route.argtypes = [_f32p, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint32), _f32p]
+    lib.yo_moe_route.restype = None
     lib.yo_swiglu.argtypes = [_f32p, _f32p, C.c_size_t]
     lib.yo_swiglu.restype = None
     lib.yo_argmax.argtypes = [_f32p, C.c_size_t]
@@ -255,6 +258,16 @@ def gelu(x: float) -> float:
     return float(lib.yo_gelu(x))
 
 
+def moe_route(logits, n_used: int):
+    """Router of the mixture-of-experts FFN (model_runner.rs:827-854): returns (probabilities, selected experts in
+    order of decreasing probability, their renormalised weights)."""
+    probs = np.ascontiguousarray(logits, dtype=np.float32).copy()
+    sel = np.empty(n_used, np.uint32)
+    w = np.empty(n_used, np.float32)
+    lib.yo_moe_route(_f32(probs), probs.size, n_used, sel.ctypes.data_as(C.POINTER(C.c_uint32)), _f32(w))
+    return probs, sel, w
+
+
 def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     out = np.array(gate, dtype=np.float32, copy=True)
     up = np.ascontiguousarray(up, np.float32)
@@ -273,14 +286,14 @@ class Model:
     def __init__(self, *, dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, ff_dim,
                  max_seq_len, norm_eps=1e-5, rope_freq_base=10000.0, mod_enabled=-1, simd=SCALAR,
                  n_threads=0, rotary_dim=0, sliding_window=0, attn_logit_softcap=0.0, logit_softcap=0.0,
-                 norm_weight_offset=0.0, geglu=False):
+                 norm_weight_offset=0.0, geglu=False, n_experts=0, n_experts_used=0):
         if simd == AVX2_ASM and not load_reference_asm():
             simd = AVX2
         self.simd = simd
         self.cfg = ModelConfig(dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, ff_dim,
                                max_seq_len, norm_eps, rope_freq_base, mod_enabled, simd, n_threads,
                                rotary_dim, sliding_window, attn_logit_softcap, logit_softcap, norm_weight_offset,
-                               1 if geglu else 0)
+                               1 if geglu else 0, n_experts, n_experts_used)
         self._m = lib.yo_model_create(C.byref(self.cfg))
         self._keep = {}
 

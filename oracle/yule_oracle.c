@@ -578,6 +578,10 @@ typedef struct {
     yo_tensor attn_norm, attn_q, attn_k, attn_v, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down;
     /* optional (weight_loader.rs:203-218): Qwen2 Q/K/V biases, Gemma2 post-norms */
     yo_tensor attn_q_bias, attn_k_bias, attn_v_bias, attn_post_norm, ffn_post_norm;
+    /* mixture of experts (weight_loader.rs:222-260): the router, the experts packed in one tensor per projection
+     * or one tensor per expert ("ffn_gate.E.weight") */
+    yo_tensor ffn_gate_inp, ffn_gate_exps, ffn_up_exps, ffn_down_exps;
+    yo_tensor *gate_e, *up_e, *down_e; /* n_experts each, or NULL */
 } yo_layer;
 
 struct yo_model {
@@ -587,7 +591,7 @@ struct yo_model {
     yo_layer *layers;
     float **k_cache, **v_cache;
     float *hidden, *residual, *normed, *q, *k, *v, *attn_out, *attn_proj, *scores, *gate, *up,
-        *ffn_out, *normw, *post_tmp;
+        *ffn_out, *normw, *post_tmp, *router, *expert_out;
     float *rope_cos, *rope_sin;
     uint32_t pos;
     /* Mixture-of-Depths bookkeeping (mixture_of_depths.rs:28-67) */
@@ -625,6 +629,14 @@ yo_model *yo_model_create(const yo_model_config *cfg) {
     m->gate = falloc(cfg->ff_dim);
     m->up = falloc(cfg->ff_dim);
     m->ffn_out = falloc(dim);
+    m->router = falloc(cfg->n_experts);
+    m->expert_out = falloc(dim);
+    if (cfg->n_experts)
+        for (size_t l = 0; l < L; l++) {
+            m->layers[l].gate_e = (yo_tensor *)calloc(cfg->n_experts, sizeof(yo_tensor));
+            m->layers[l].up_e = (yo_tensor *)calloc(cfg->n_experts, sizeof(yo_tensor));
+            m->layers[l].down_e = (yo_tensor *)calloc(cfg->n_experts, sizeof(yo_tensor));
+        }
     /* model_runner.rs:430-434: a rotary dimension below head_dim rotates only that prefix of every head */
     size_t rot = (cfg->rotary_dim && cfg->rotary_dim < hd) ? cfg->rotary_dim : hd;
     size_t half = rot / 2;
@@ -645,6 +657,13 @@ void yo_model_destroy(yo_model *m) {
     }
     free(m->k_cache);
     free(m->v_cache);
+    for (size_t l = 0; l < m->cfg.n_layers; l++) {
+        free(m->layers[l].gate_e);
+        free(m->layers[l].up_e);
+        free(m->layers[l].down_e);
+    }
+    free(m->router);
+    free(m->expert_out);
     free(m->layers);
     free(m->hidden);
     free(m->residual);
@@ -695,12 +714,27 @@ int yo_model_set_tensor(yo_model *m, const char *name, const uint8_t *data, size
                      {"ffn_down.weight", &l->ffn_down},       {"attn_q.bias", &l->attn_q_bias},
                      {"attn_k.bias", &l->attn_k_bias},        {"attn_v.bias", &l->attn_v_bias},
                      {"attn_post_norm.weight", &l->attn_post_norm},
-                     {"ffn_post_norm.weight", &l->ffn_post_norm}};
+                     {"ffn_post_norm.weight", &l->ffn_post_norm},
+                     {"ffn_gate_inp.weight", &l->ffn_gate_inp},
+                     {"ffn_gate_exps.weight", &l->ffn_gate_exps},
+                     {"ffn_up_exps.weight", &l->ffn_up_exps},
+                     {"ffn_down_exps.weight", &l->ffn_down_exps}};
         for (size_t i = 0; i < sizeof(slots) / sizeof(slots[0]); i++)
             if (!strcmp(rest, slots[i].n)) {
                 *slots[i].t = t;
                 return 0;
             }
+        /* one tensor per expert: "ffn_gate.E.weight" (weight_loader.rs:228-244) */
+        unsigned e = 0;
+        char which[16], tail[16];
+        if (l->gate_e && sscanf(rest, "ffn_%15[a-z].%u.%15s", which, &e, tail) == 3 && !strcmp(tail, "weight") &&
+            e < m->cfg.n_experts) {
+            yo_tensor *arr = !strcmp(which, "gate") ? l->gate_e : !strcmp(which, "up") ? l->up_e : !strcmp(which, "down") ? l->down_e : NULL;
+            if (arr) {
+                arr[e] = t;
+                return 0;
+            }
+        }
     }
     return -1;
 }
@@ -722,6 +756,65 @@ static int model_qmv(const yo_model *m, const yo_tensor *t, const float *x, size
     if (!t->data)
         return -1;
     return yo_qmv(t->type, t->data, x, out, n_rows, n_cols, m->cfg.n_threads, m->cfg.simd);
+}
+
+/* The router's matvec (model_runner.rs:819-825 through qmv, :152-244): block formats as everywhere; F32 / F16 are
+ * "blocks" of one weight, i.e. a plain left-to-right fp32 sum of w * x. */
+static int router_mv(const yo_model *m, const yo_tensor *t, const float *x, size_t n_cols, float *out, size_t n_rows) {
+    if (!t->data)
+        return -1;
+    if (t->type != YO_F32 && t->type != YO_F16)
+        return model_qmv(m, t, x, n_cols, out, n_rows);
+    for (size_t r = 0; r < n_rows; r++) {
+        float sum = 0.0f;
+        for (size_t i = 0; i < n_cols; i++) {
+            float w;
+            if (t->type == YO_F32)
+                memcpy(&w, t->data + 4 * (r * n_cols + i), 4);
+            else
+                w = rd_f16(t->data, 2 * (r * n_cols + i));
+            sum += w * x[i];
+        }
+        out[r] = sum;
+    }
+    return 0;
+}
+
+/* model_runner.rs:827-854 (and its test :1138-1186): softmax over the router logits, experts ordered by probability
+ * (stable sort, descending: equal probabilities keep index order), the first n_used renormalised to sum 1.
+ * `probs` holds the logits on entry and the probabilities on return. */
+void yo_moe_route(float *probs, size_t n_exp, size_t n_used, uint32_t *selected, float *weights) {
+    float max_r = -INFINITY;
+    for (size_t i = 0; i < n_exp; i++)
+        max_r = probs[i] > max_r ? probs[i] : max_r;
+    float sum_r = 0.0f;
+    for (size_t i = 0; i < n_exp; i++) {
+        probs[i] = expf(probs[i] - max_r);
+        sum_r += probs[i];
+    }
+    float inv_r = 1.0f / sum_r;
+    for (size_t i = 0; i < n_exp; i++)
+        probs[i] *= inv_r;
+    /* stable insertion sort of the indices by descending probability */
+    uint32_t order[256];
+    if (n_exp > 256)
+        n_exp = 256;
+    for (size_t i = 0; i < n_exp; i++) {
+        size_t j = i;
+        while (j > 0 && probs[order[j - 1]] < probs[i]) {
+            order[j] = order[j - 1];
+            j--;
+        }
+        order[j] = (uint32_t)i;
+    }
+    float selected_sum = 0.0f;
+    for (size_t k = 0; k < n_used; k++)
+        selected_sum += probs[order[k]];
+    float inv_sel = 1.0f / selected_sum;
+    for (size_t k = 0; k < n_used; k++) {
+        selected[k] = order[k];
+        weights[k] = probs[order[k]] * inv_sel;
+    }
 }
 
 /* model_runner.rs:295-310: F32 or F16 bias added element by element. */
@@ -765,8 +858,9 @@ static int should_skip_layer(const float *hidden, size_t dim, size_t layer, size
     return activation_norm(hidden, dim) < skip_threshold;
 }
 
-/* model_runner.rs:533-1036, dense path with its architecture variants (Q/K/V bias, partial RoPE, sliding
- * window, Gemma norm offset / embedding scale / GeGLU / post-norms / softcaps); no MoE, flat KV cache. */
+/* model_runner.rs:533-1036: the dense path with its architecture variants (Q/K/V bias, partial RoPE, sliding
+ * window, Gemma norm offset / embedding scale / GeGLU / post-norms / softcaps) and the mixture-of-experts FFN;
+ * flat KV cache. */
 int yo_model_forward(yo_model *m, uint32_t token, float *logits) {
     const yo_model_config *c = &m->cfg;
     size_t dim = c->dim, hd = c->head_dim, n_heads = c->n_heads, n_kv = c->n_kv_heads;
@@ -861,6 +955,50 @@ int yo_model_forward(yo_model *m, uint32_t token, float *logits) {
             return -1;
         yo_rms_norm(m->hidden, m->normw, dim, c->norm_eps, norm_off, m->normed);
 
+        if (c->n_experts > 0) {
+            /* mixture of experts (:813-958): router, top-k, the selected experts' SwiGLU FFNs weighted and summed */
+            size_t n_exp = c->n_experts, n_used = c->n_experts_used;
+            if (n_used == 0 || n_used > n_exp || n_exp > 256)
+                return -1;
+            if (router_mv(m, &L->ffn_gate_inp, m->normed, dim, m->router, n_exp))
+                return -1;
+            uint32_t sel[256];
+            float wsel[256];
+            yo_moe_route(m->router, n_exp, n_used, sel, wsel);
+            memset(m->ffn_out, 0, dim * 4);
+            for (size_t k = 0; k < n_used; k++) {
+                size_t e = sel[k];
+                yo_tensor g, u, d;
+                if (L->gate_e && L->gate_e[e].data) {
+                    g = L->gate_e[e];
+                    u = L->up_e[e];
+                    d = L->down_e[e];
+                    if (!u.data || !d.data)
+                        return -1;
+                } else if (L->ffn_gate_exps.data) {
+                    /* packed: expert e is the e-th of n_exp equal slices of each tensor (:890-918) */
+                    if (!L->ffn_up_exps.data || !L->ffn_down_exps.data)
+                        return -1;
+                    size_t gb = L->ffn_gate_exps.n_bytes / n_exp, ub = L->ffn_up_exps.n_bytes / n_exp, db = L->ffn_down_exps.n_bytes / n_exp;
+                    g = (yo_tensor){L->ffn_gate_exps.data + e * gb, gb, L->ffn_gate_exps.type};
+                    u = (yo_tensor){L->ffn_up_exps.data + e * ub, ub, L->ffn_up_exps.type};
+                    d = (yo_tensor){L->ffn_down_exps.data + e * db, db, L->ffn_down_exps.type};
+                } else {
+                    return -1;
+                }
+                if (model_qmv(m, &g, m->normed, dim, m->gate, ff) || model_qmv(m, &u, m->normed, dim, m->up, ff))
+                    return -1;
+                /* always SwiGLU here (:876-881), written as gate * sigmoid(gate) * up */
+                for (size_t i = 0; i < ff; i++) {
+                    float sigmoid = 1.0f / (1.0f + expf(-m->gate[i]));
+                    m->gate[i] = m->gate[i] * sigmoid * m->up[i];
+                }
+                if (model_qmv(m, &d, m->gate, ff, m->expert_out, dim))
+                    return -1;
+                for (size_t i = 0; i < dim; i++)
+                    m->ffn_out[i] += wsel[k] * m->expert_out[i];
+            }
+        } else {
         if (model_qmv(m, &L->ffn_gate, m->normed, dim, m->gate, ff) ||
             model_qmv(m, &L->ffn_up, m->normed, dim, m->up, ff))
             return -1;
@@ -872,6 +1010,7 @@ int yo_model_forward(yo_model *m, uint32_t token, float *logits) {
         }
         if (model_qmv(m, &L->ffn_down, m->gate, ff, m->ffn_out, dim))
             return -1;
+        }
         /* post-FFN norm (Gemma2, :985-999) */
         if (L->ffn_post_norm.data) {
             memcpy(m->post_tmp, m->ffn_out, dim * 4);

@@ -155,9 +155,16 @@ typedef struct {
     float logit_softcap;       /* the same on the final logits (:1027-1032); 0 = none */
     float norm_weight_offset;  /* Gemma: norm weights are (w + 1) and embeddings are scaled by sqrt(dim) (:246-275, :568-574) */
     int32_t geglu;             /* Gemma: gelu(gate) * up instead of SiLU (:312-314, :974-978) */
+    uint32_t n_experts;        /* mixture of experts (:395-397, :813-958): experts per layer, 0 = dense FFN */
+    uint32_t n_experts_used;   /* experts evaluated per token */
 } yo_model_config;
 
 typedef struct yo_model yo_model;
+
+/* Router of the mixture-of-experts FFN (model_runner.rs:827-854): `probs` holds n_exp logits on entry, their softmax
+ * on return; selected[k], weights[k] (k < n_used) are the chosen experts in order of decreasing probability and their
+ * renormalised weights. */
+void yo_moe_route(float *probs, size_t n_exp, size_t n_used, uint32_t *selected, float *weights);
 
 yo_model *yo_model_create(const yo_model_config *cfg);
 void yo_model_destroy(yo_model *m);

@@ -55,7 +55,8 @@ def build(metadata: dict, tensors: dict, alignment: int = 32, version: int = 3) 
 
 
 def llama_metadata(cfg, arch: str = "llama") -> dict:
-    return {"general.architecture": arch, "general.name": "synthetic", f"{arch}.context_length": cfg.max_seq_len,
+    moe = {f"{arch}.expert_count": cfg.n_experts, f"{arch}.expert_used_count": cfg.n_experts_used} if cfg.n_experts else {}
+    return {**moe, "general.architecture": arch, "general.name": "synthetic", f"{arch}.context_length": cfg.max_seq_len,
             f"{arch}.embedding_length": cfg.dim, f"{arch}.block_count": cfg.n_layers,
             f"{arch}.attention.head_count": cfg.n_heads, f"{arch}.attention.head_count_kv": cfg.n_kv_heads,
             f"{arch}.attention.layer_norm_rms_epsilon": float(cfg.norm_eps), f"{arch}.rope.freq_base": float(cfg.rope_freq_base),
@@ -64,7 +65,7 @@ def llama_metadata(cfg, arch: str = "llama") -> dict:
 
 def model_file(cfg, weights: dict, arch: str = "llama") -> bytes:
     """A GGUF image of a synthetic model: ``weights`` as produced by ``synth.synthetic_model``."""
-    shapes = cfg.tensor_shapes()
+    shapes = {**cfg.tensor_shapes(True), **cfg.tensor_shapes(False)} if cfg.n_experts else cfg.tensor_shapes()
     tensors = {}
     for name, (data, dt) in weights.items():
         if name in shapes:

@@ -164,9 +164,13 @@ def test_architecture_variants_from_metadata(native_libs):
     assert parsed("phi3", {"phi3.rope.dimension_count": 32}).rotary_dim == 0  # the whole head: no partial rotation
     got = parsed("gemma2", {"gemma2.attn_logit_softcapping": (gw.F64, 30.0), "gemma2.attention.attn_logit_softcapping": (gw.F64, 50.0)})
     assert got.geglu and got.norm_weight_offset == 1.0 and got.logit_softcap == 30.0 and got.attn_logit_softcap == 50.0
-    # mixture of experts: refused (expert routing, model_runner.rs:813-958, is not computed by this backend)
+    # mixture of experts (model_runner.rs:395-407): the counts come from the metadata; a nonsensical pair is refused
+    got = parsed("llama", {"llama.expert_count": 8, "llama.expert_used_count": 2})
+    assert got.n_experts == 8 and got.n_experts_used == 2
     with pytest.raises(YuleGpuError, match="experts"):
-        parsed("llama", {"llama.expert_count": 8, "llama.expert_used_count": 2})
+        parsed("llama", {"llama.expert_count": 8, "llama.expert_used_count": 9})
+    with pytest.raises(YuleGpuError, match="experts"):
+        parsed("llama", {"llama.expert_count": 4})
     # default epsilon of Qwen / Phi / Gemma files that carry none: 1e-6 (model_runner.rs:414-417)
     shapes = cfg.tensor_shapes()
     tensors = {n: (d, int(t), (shapes[n][1], shapes[n][0]) if n in shapes else (cfg.dim,)) for n, (d, t) in weights.items()}

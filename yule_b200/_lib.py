@@ -21,7 +21,8 @@ class RunnerConfig(C.Structure):
     _fields_ = [("dim", u32), ("n_layers", u32), ("n_heads", u32), ("n_kv_heads", u32), ("head_dim", u32),
                 ("vocab_size", u32), ("ff_dim", u32), ("max_seq_len", u32), ("norm_eps", f32),
                 ("rope_freq_base", f32), ("fused", u32), ("rotary_dim", u32), ("sliding_window", u32),
-                ("attn_logit_softcap", f32), ("logit_softcap", f32), ("norm_weight_offset", f32), ("geglu", u32)]
+                ("attn_logit_softcap", f32), ("logit_softcap", f32), ("norm_weight_offset", f32), ("geglu", u32),
+                ("n_experts", u32), ("n_experts_used", u32)]
 
 
 class SamplingParams(C.Structure):

@@ -383,18 +383,21 @@ int32_t yule_gguf_runner_config(const yule_gguf *g, uint32_t max_seq_len_cap, yu
     const std::string prefix = arch ? arch : "unknown";
     // The dense transformer path of yule-infer/src/model_runner.rs with its variants: Llama / Mistral (sliding
     // window), Phi (partial RoPE), Qwen (Q/K/V bias), Gemma (norm offset, embedding scale, GeGLU, post-norms,
-    // softcaps).  Mixture-of-experts files (model_runner.rs:813-958) and the non-transformer architectures are
+    // softcaps), and the mixture-of-experts FFN (model_runner.rs:813-958).  The non-transformer architectures are
     // refused rather than mis-computed.
     const bool is_gemma = prefix == "gemma" || prefix == "gemma2";
     const bool is_phi = prefix == "phi" || prefix == "phi2" || prefix == "phi3";
     const bool is_qwen = prefix == "qwen" || prefix == "qwen2";
     if (prefix != "llama" && prefix != "mistral" && !is_qwen && !is_gemma && !is_phi)
         return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: architecture '%s' is outside the dense decode path of this backend", prefix.c_str());
-    uint32_t experts = 0;
-    if (g->get_u32(prefix + ".expert_count", &experts) && experts > 0)
-        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: mixture-of-experts model (%u experts): expert routing is not implemented in this backend", experts);
-    if (g->find_tensor("blk.0.ffn_gate_exps.weight") || g->find_tensor("blk.0.ffn_gate.0.weight"))
-        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: mixture-of-experts tensors present: expert routing is not implemented in this backend");
+    // mixture of experts (model_runner.rs:395-397): expert_count > 0 switches every layer's FFN to the routed form
+    uint32_t experts = 0, experts_used = 0;
+    g->get_u32(prefix + ".expert_count", &experts);
+    g->get_u32(prefix + ".expert_used_count", &experts_used);
+    if (experts == 0 && (g->find_tensor("blk.0.ffn_gate_exps.weight") || g->find_tensor("blk.0.ffn_gate.0.weight")))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: mixture-of-experts tensors present but no %s.expert_count", prefix.c_str());
+    if (experts > 0 && (experts > 256 || experts_used == 0 || experts_used > experts))
+        return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: mixture of experts with %u experts, %u used per token", experts, experts_used);
     if (is_phi && !g->find_tensor("blk.0.attn_q.weight"))
         return fail(YULE_ERR_INVALID_ARGUMENT, "gguf: this file has a packed attn_qkv tensor; the runner reads separate attn_q / attn_k / attn_v");
     memset(cfg, 0, sizeof(*cfg));
@@ -421,6 +424,16 @@ int32_t yule_gguf_runner_config(const yule_gguf *g, uint32_t max_seq_len_cap, yu
     cfg->head_dim = cfg->dim / heads;
     const TensorEntry *gate = g->find_tensor("blk.0.ffn_gate.weight");
     cfg->ff_dim = (gate && gate->n_dims == 2) ? (uint32_t)gate->shape[1] : (uint32_t)(std::ceil(cfg->dim * 8.0 / 3.0 / 256.0) * 256);
+    if (experts > 0) {
+        // model_runner.rs:399-407: the packed tensor holds all experts' rows, a per-expert tensor one expert's
+        cfg->n_experts = experts;
+        cfg->n_experts_used = experts_used;
+        const TensorEntry *packed = g->find_tensor("blk.0.ffn_gate_exps.weight"), *one = g->find_tensor("blk.0.ffn_gate.0.weight");
+        if (packed && packed->n_dims == 2)
+            cfg->ff_dim = (uint32_t)(packed->shape[1] / experts);
+        else if (one && one->n_dims == 2)
+            cfg->ff_dim = (uint32_t)one->shape[1];
+    }
     // model_runner.rs:414-417: 1e-6 for Phi / Qwen / Gemma, 1e-5 otherwise, when the file has no epsilon
     double eps = (is_phi || is_qwen || is_gemma) ? 1e-6 : 1e-5, theta = 10000.0;
     g->get_f64(prefix + ".attention.layer_norm_rms_epsilon", &eps);
@@ -503,7 +516,8 @@ int32_t yule_cuda_runner_load_gguf(yule_cuda_ctx *ctx, const yule_gguf *g, uint3
     if ((rc = upload("token_embd.weight", true)) || (rc = upload("output_norm.weight", true)) || (rc = upload("output.weight", false)))
         return cleanup(rc);
     static const char *per_layer[] = {"attn_norm.weight", "attn_q.weight",   "attn_k.weight",  "attn_v.weight",   "attn_output.weight",
-                                      "ffn_norm.weight",  "ffn_gate.weight", "ffn_up.weight",  "ffn_down.weight"};
+                                      "ffn_norm.weight"};
+    static const char *dense_ffn[] = {"ffn_gate.weight", "ffn_up.weight", "ffn_down.weight"};
     // optional tensors of the variants (weight_loader.rs:203-218)
     static const char *per_layer_optional[] = {"attn_q.bias", "attn_k.bias", "attn_v.bias", "attn_post_norm.weight", "ffn_post_norm.weight"};
     for (uint32_t l = 0; l < cfg.n_layers; l++) {
@@ -515,6 +529,30 @@ int32_t yule_cuda_runner_load_gguf(yule_cuda_ctx *ctx, const yule_gguf *g, uint3
         for (const char *suffix : per_layer_optional) {
             snprintf(name, sizeof(name), "blk.%u.%s", l, suffix);
             if ((rc = upload(name, false))) return cleanup(rc);
+        }
+        if (cfg.n_experts == 0) {
+            for (const char *suffix : dense_ffn) {
+                snprintf(name, sizeof(name), "blk.%u.%s", l, suffix);
+                if ((rc = upload(name, true))) return cleanup(rc);
+            }
+        } else {
+            // the router, then the experts: packed tensors if the file has them, else one tensor per expert
+            // (weight_loader.rs:222-260)
+            snprintf(name, sizeof(name), "blk.%u.ffn_gate_inp.weight", l);
+            if ((rc = upload(name, true))) return cleanup(rc);
+            snprintf(name, sizeof(name), "blk.%u.ffn_gate_exps.weight", l);
+            if (g->find_tensor(name)) {
+                for (const char *proj : {"gate", "up", "down"}) {
+                    snprintf(name, sizeof(name), "blk.%u.ffn_%s_exps.weight", l, proj);
+                    if ((rc = upload(name, true))) return cleanup(rc);
+                }
+            } else {
+                for (uint32_t e = 0; e < cfg.n_experts; e++)
+                    for (const char *proj : {"gate", "up", "down"}) {
+                        snprintf(name, sizeof(name), "blk.%u.ffn_%s.%u.weight", l, proj, e);
+                        if ((rc = upload(name, true))) return cleanup(rc);
+                    }
+            }
         }
     }
     rc = cleanup(YULE_OK);

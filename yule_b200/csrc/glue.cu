@@ -57,6 +57,45 @@ __global__ void matvec_f32_kernel(const float *__restrict__ a, const float *__re
     if (lane == 0) out[warp] = acc;
 }
 
+// Router of a mixture-of-experts layer (yule-infer/src/model_runner.rs:827-854): softmax over the n_exp router logits
+// (left in `probs`), the n_used most probable experts in order of decreasing probability (equal probabilities: lower
+// index first, as the CPU runner's stable sort leaves them) and their probabilities renormalised to sum 1.  A handful
+// of values: one thread.
+__global__ void moe_route_kernel(float *__restrict__ probs, uint32_t n_exp, uint32_t n_used, uint32_t *__restrict__ sel,
+                                 float *__restrict__ w) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float mx = -INFINITY;
+    for (uint32_t i = 0; i < n_exp; i++) mx = fmaxf(mx, probs[i]);
+    float sum = 0.f;
+    for (uint32_t i = 0; i < n_exp; i++) {
+        const float e = expf(probs[i] - mx);
+        probs[i] = e;
+        sum += e;
+    }
+    const float inv = 1.0f / sum;
+    for (uint32_t i = 0; i < n_exp; i++) probs[i] *= inv;
+    uint32_t picked[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // n_exp <= 256
+    float sel_sum = 0.f;
+    for (uint32_t k = 0; k < n_used; k++) {
+        int best = -1;
+        for (uint32_t i = 0; i < n_exp; i++) {
+            if ((picked[i >> 5] >> (i & 31)) & 1u) continue;
+            if (best < 0 || probs[i] > probs[best]) best = (int)i;
+        }
+        picked[best >> 5] |= 1u << (best & 31);
+        sel[k] = (uint32_t)best;
+        sel_sum += probs[best];
+    }
+    const float inv_sel = 1.0f / sel_sum;
+    for (uint32_t k = 0; k < n_used; k++) w[k] = probs[sel[k]] * inv_sel;
+}
+
+// out[i] += (*w) · x[i], the product and the sum rounded separately (model_runner.rs:950-952).
+__global__ void axpy_dev_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ out, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __fadd_rn(out[i], __fmul_rn(*w, x[i]));
+}
+
 // kernels/cuda/softmax.cu:3-45 — single CTA, max-subtracted.
 __global__ void softmax_kernel(const float *__restrict__ in, float *__restrict__ out, uint32_t n) {
     __shared__ float red[32];
@@ -470,6 +509,17 @@ __global__ void fill_bytes_kernel(uint4 *__restrict__ p, size_t n16, uint32_t v)
 cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k, cudaStream_t s,
                               uint64_t *launches) {
     matvec_f32_kernel<<<(m + 7) / 8, 256, 0, s>>>(a, b, out, m, k);
+    *launches += 1;
+    return cudaGetLastError();
+}
+cudaError_t launch_moe_route(float *probs, uint32_t n_exp, uint32_t n_used, uint32_t *sel, float *w, cudaStream_t s, uint64_t *launches) {
+    if (n_exp == 0 || n_exp > 256 || n_used == 0 || n_used > n_exp) return cudaErrorInvalidValue;
+    moe_route_kernel<<<1, 32, 0, s>>>(probs, n_exp, n_used, sel, w);
+    *launches += 1;
+    return cudaGetLastError();
+}
+cudaError_t launch_axpy_dev(const float *w, const float *x, float *out, uint32_t n, cudaStream_t s, uint64_t *launches) {
+    axpy_dev_kernel<<<(n + 255) / 256, 256, 0, s>>>(w, x, out, n);
     *launches += 1;
     return cudaGetLastError();
 }

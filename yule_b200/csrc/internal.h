@@ -389,6 +389,10 @@ cudaError_t launch_advance_rows(uint32_t *pos, uint32_t *step, uint32_t batch, c
 cudaError_t launch_matvec_f32(const float *a, const float *b, float *out, uint32_t m, uint32_t k,
                               cudaStream_t s, uint64_t *launches);
 cudaError_t launch_softmax(const float *in, float *out, uint32_t n, cudaStream_t s, uint64_t *launches);
+// Mixture-of-experts router: softmax of the n_exp logits in `probs` (in place), the n_used most probable experts and
+// their renormalised weights.  out[i] += (*w) · x[i] with the weight read on the device.
+cudaError_t launch_moe_route(float *probs, uint32_t n_exp, uint32_t n_used, uint32_t *sel, float *w, cudaStream_t s, uint64_t *launches);
+cudaError_t launch_axpy_dev(const float *w, const float *x, float *out, uint32_t n, cudaStream_t s, uint64_t *launches);
 // `rows` contiguous rows of n elements, one CTA each.
 cudaError_t launch_rms_norm_rows(const float *in, const float *w, float *out, uint32_t n, uint32_t rows, float eps, cudaStream_t s,
                                  uint64_t *launches);

@@ -38,6 +38,11 @@ struct Layer {
     const float *attn_post_norm_f32 = nullptr, *ffn_post_norm_f32 = nullptr;
     yule_buffer k_cache_h = 0, v_cache_h = 0;
     float *k_cache = nullptr, *v_cache = nullptr;
+    // mixture of experts (weight_loader.rs:222-260): the router, then the experts packed in one tensor per projection
+    // or one tensor per expert
+    Tensor ffn_gate_inp, ffn_gate_exps, ffn_up_exps, ffn_down_exps;
+    std::vector<Tensor> gate_e, up_e, down_e;
+    const float *router_f32 = nullptr;  // the router as fp32 when the file holds it as F32 / F16
 };
 
 }  // namespace
@@ -54,6 +59,8 @@ struct yule_cuda_runner {
     float *hidden = nullptr, *residual = nullptr, *normed = nullptr, *q = nullptr, *k_tmp = nullptr,
           *v_tmp = nullptr, *attn_out = nullptr, *attn_proj = nullptr, *gate = nullptr, *up = nullptr,
           *ffn_out = nullptr, *logits = nullptr;
+    float *moe_logits = nullptr, *moe_w = nullptr;  // mixture of experts: router logits / probabilities, weights of the chosen experts
+    uint32_t *moe_sel = nullptr, *h_moe_sel = nullptr;  // the chosen experts (device, pinned host)
     float *rope_cos = nullptr, *rope_sin = nullptr;  // [max_seq_len][head_dim/2], device
     float *attn_scratch = nullptr;  // partial results of the split-KV attention
     uint32_t *attn_tickets = nullptr;
@@ -147,6 +154,25 @@ Tensor *slot_for(yule_cuda_runner *r, const char *name) {
                  {"attn_post_norm.weight", &L.attn_post_norm}, {"ffn_post_norm.weight", &L.ffn_post_norm}};
     for (auto &s : slots)
         if (!strcmp(rest, s.n)) return s.t;
+    if (r->cfg.n_experts) {
+        struct {
+            const char *n;
+            Tensor *t;
+        } moe[] = {{"ffn_gate_inp.weight", &L.ffn_gate_inp}, {"ffn_gate_exps.weight", &L.ffn_gate_exps},
+                   {"ffn_up_exps.weight", &L.ffn_up_exps}, {"ffn_down_exps.weight", &L.ffn_down_exps}};
+        for (auto &s : moe)
+            if (!strcmp(rest, s.n)) return s.t;
+        // one tensor per expert: "ffn_gate.E.weight" (weight_loader.rs:228-244)
+        unsigned e = 0;
+        char which[16], tail[16];
+        if (sscanf(rest, "ffn_%15[a-z].%u.%15s", which, &e, tail) == 3 && !strcmp(tail, "weight") && e < r->cfg.n_experts) {
+            std::vector<Tensor> *arr = !strcmp(which, "gate") ? &L.gate_e : !strcmp(which, "up") ? &L.up_e : !strcmp(which, "down") ? &L.down_e : nullptr;
+            if (arr) {
+                if (arr->size() < r->cfg.n_experts) arr->resize(r->cfg.n_experts);
+                return &(*arr)[e];
+            }
+        }
+    }
     return nullptr;
 }
 
@@ -210,7 +236,7 @@ bool has_post_norms(const yule_cuda_runner *r) {
 bool is_variant(const yule_cuda_runner *r) {
     const yule_runner_config &c = r->cfg;
     return c.sliding_window || c.attn_logit_softcap != 0.f || c.logit_softcap != 0.f || c.norm_weight_offset != 0.f || c.geglu ||
-           has_bias(r) || has_post_norms(r);
+           c.n_experts != 0 || has_bias(r) || has_post_norms(r);
 }
 
 struct Step {
@@ -320,6 +346,47 @@ cudaError_t enqueue_forward_by_value(yule_cuda_runner *r, uint32_t token, uint32
         }
         st.ok(cudaMemcpyAsync(r->residual, r->hidden, (size_t)dim * 4, cudaMemcpyDeviceToDevice, s));
         st.ok(launch_rms_norm(r->hidden, L.ffn_norm_f32, r->normed, dim, c.norm_eps, s, &st.n));
+        if (c.n_experts) {
+            // Mixture of experts (model_runner.rs:813-958).  Router, softmax, the n_experts_used most probable
+            // experts and their renormalised weights on the device; the chosen indices come back to the host (a few
+            // bytes per layer), which picks the experts' weights; their SwiGLU FFNs are summed with the device-side
+            // weights in the order of decreasing probability, as the CPU runner does.
+            if (L.router_f32)
+                st.ok(launch_matvec_f32(L.router_f32, r->normed, r->moe_logits, c.n_experts, dim, s, &st.n));
+            else
+                st.qmv(L.ffn_gate_inp, r->normed, r->moe_logits, c.n_experts, dim);
+            st.ok(launch_moe_route(r->moe_logits, c.n_experts, c.n_experts_used, r->moe_sel, r->moe_w, s, &st.n));
+            st.ok(cudaMemcpyAsync(r->h_moe_sel, r->moe_sel, (size_t)c.n_experts_used * 4, cudaMemcpyDeviceToHost, s));
+            st.ok(cudaMemsetAsync(r->ffn_out, 0, (size_t)dim * 4, s));
+            if (st.err == cudaSuccess) st.ok(cudaStreamSynchronize(s));
+            for (uint32_t k = 0; k < c.n_experts_used && st.err == cudaSuccess; k++) {
+                const uint32_t e = r->h_moe_sel[k] < c.n_experts ? r->h_moe_sel[k] : 0;
+                Tensor g, u, d;
+                if (!L.gate_e.empty() && L.gate_e[e].set) {
+                    g = L.gate_e[e];
+                    u = L.up_e[e];
+                    d = L.down_e[e];
+                } else {
+                    // packed: expert e is the e-th of n_experts equal slices of each tensor (:890-918)
+                    auto slice = [&](const Tensor &t, uint64_t rows, uint64_t cols) {
+                        Tensor o = t;
+                        const size_t bytes = tensor_bytes(t.type, rows, cols);
+                        o.buf.ptr = (char *)t.buf.ptr + (size_t)e * bytes;
+                        o.buf.size = bytes;
+                        o.buf.planar = nullptr;  // a planar copy, if any, belongs to the whole tensor
+                        return o;
+                    };
+                    g = slice(L.ffn_gate_exps, ff, dim);
+                    u = slice(L.ffn_up_exps, ff, dim);
+                    d = slice(L.ffn_down_exps, dim, ff);
+                }
+                st.qmv(g, r->normed, r->gate, ff, dim);
+                st.qmv(u, r->normed, r->up, ff, dim);
+                st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n));  // always SwiGLU here (:876-881)
+                st.qmv(d, r->gate, r->attn_proj, dim, ff);
+                st.ok(launch_axpy_dev(r->moe_w + k, r->attn_proj, r->ffn_out, dim, s, &st.n));  // ffn_out += w_k · expert_out
+            }
+        } else {
         st.qmv(L.ffn_gate, r->normed, r->gate, ff, dim);
         st.qmv(L.ffn_up, r->normed, r->up, ff, dim);
         if (c.geglu)  // model_runner.rs:974-978
@@ -327,6 +394,7 @@ cudaError_t enqueue_forward_by_value(yule_cuda_runner *r, uint32_t token, uint32
         else
             st.ok(launch_silu_mul(r->gate, r->up, r->gate, ff, s, &st.n));
         st.qmv(L.ffn_down, r->gate, r->ffn_out, dim, ff);
+        }
         // post-FFN norm (Gemma2, model_runner.rs:985-999)
         if (L.ffn_post_norm_f32) {
             st.ok(launch_rms_norm(r->ffn_out, L.ffn_post_norm_f32, r->attn_proj, dim, c.norm_eps, s, &st.n));
@@ -643,6 +711,29 @@ int32_t finalize(yule_cuda_runner *r) {
         if ((rc = check_matrix(L.attn_k, "attn_k.weight", l, kvdim, dim))) return rc;
         if ((rc = check_matrix(L.attn_v, "attn_v.weight", l, kvdim, dim))) return rc;
         if ((rc = check_matrix(L.attn_output, "attn_output.weight", l, dim_rows, qdim_in))) return rc;
+        if (c.n_experts) {
+            // router: F32 / F16 (expanded to fp32 once) or a block format; experts: per expert or packed
+            if (!L.ffn_gate_inp.set) return fail(YULE_ERR_MISSING_TENSOR, "tensor not found: ffn_gate_inp.weight (layer %u)", l);
+            if (L.ffn_gate_inp.type == YULE_DTYPE_F32 || L.ffn_gate_inp.type == YULE_DTYPE_F16) {
+                if ((rc = vector_as_f32(r, L.ffn_gate_inp, "ffn_gate_inp.weight", l, c.n_experts * dim, 0.f, &L.router_f32))) return rc;
+            } else if ((rc = check_matrix(L.ffn_gate_inp, "ffn_gate_inp.weight", l, c.n_experts, dim))) {
+                return rc;
+            }
+            const bool per_expert = !L.gate_e.empty();
+            if (per_expert) {
+                if (L.up_e.size() < c.n_experts || L.down_e.size() < c.n_experts || L.gate_e.size() < c.n_experts)
+                    return fail(YULE_ERR_MISSING_TENSOR, "layer %u: expert tensors missing", l);
+                for (uint32_t e = 0; e < c.n_experts; e++)
+                    if ((rc = check_matrix(L.gate_e[e], "ffn_gate.E.weight", l, ff, dim)) || (rc = check_matrix(L.up_e[e], "ffn_up.E.weight", l, ff, dim)) ||
+                        (rc = check_matrix(L.down_e[e], "ffn_down.E.weight", l, dim, ff)))
+                        return rc;
+            } else if ((rc = check_matrix(L.ffn_gate_exps, "ffn_gate_exps.weight", l, (uint64_t)c.n_experts * ff, dim)) ||
+                       (rc = check_matrix(L.ffn_up_exps, "ffn_up_exps.weight", l, (uint64_t)c.n_experts * ff, dim)) ||
+                       (rc = check_matrix(L.ffn_down_exps, "ffn_down_exps.weight", l, (uint64_t)c.n_experts * dim, ff))) {
+                return rc;
+            }
+            continue;
+        }
         if ((rc = check_matrix(L.ffn_gate, "ffn_gate.weight", l, ff, dim))) return rc;
         if ((rc = check_matrix(L.ffn_up, "ffn_up.weight", l, ff, dim))) return rc;
         if ((rc = check_matrix(L.ffn_down, "ffn_down.weight", l, dim_rows, ff_in))) return rc;
@@ -1241,10 +1332,16 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
             (c.dim / tpw) % 8 || (c.ff_dim / tpw) % 8 || (c.vocab_size / tpw) % 8)
             return fail(YULE_ERR_INVALID_ARGUMENT, "model dimensions do not split evenly over %u ranks", tpw);
     }
+    if (c.n_experts) {
+        if (c.n_experts > 256 || c.n_experts_used == 0 || c.n_experts_used > c.n_experts)
+            return fail(YULE_ERR_INVALID_ARGUMENT, "mixture of experts: %u experts, %u used per token", c.n_experts, c.n_experts_used);
+        if (tpw > 1) return fail(YULE_ERR_INVALID_ARGUMENT, "tensor parallelism does not cover mixture-of-experts models");
+    }
     auto *r = new yule_cuda_runner();
     r->ctx = ctx;
     r->cfg = c;
-    r->fused = c.fused != 0;
+    // a mixture-of-experts model runs one kernel per dispatch: its expert choice passes through the host
+    r->fused = c.fused != 0 && c.n_experts == 0;
     r->mega_wanted = c.fused == 2 && tpw <= 1 && !(knob("YULE_CUDA_MEGA") && atoi(knob("YULE_CUDA_MEGA")) == 0);
     if (const char *e = knob("YULE_CUDA_PDL")) r->pdl = atoi(e) != 0;
     r->layers.resize(c.n_layers);
@@ -1295,6 +1392,17 @@ int32_t yule_cuda_runner_create(yule_cuda_ctx *ctx, const yule_runner_config *cf
         A(c.dim, &r->hidden, &r->hidden_h);
     }
     A(c.dim, &r->residual);
+    if (c.n_experts) {
+        float *sel_f = nullptr;
+        A(c.n_experts, &r->moe_logits);
+        A(c.n_experts_used, &r->moe_w);
+        A(c.n_experts_used, &sel_f);
+        r->moe_sel = (uint32_t *)sel_f;
+        if (rc == YULE_OK && cudaMallocHost((void **)&r->h_moe_sel, (size_t)c.n_experts_used * 4) != cudaSuccess) {
+            cudaGetLastError();
+            rc = fail(YULE_ERR_OUT_OF_MEMORY, "pinned host allocation for the expert choice failed");
+        }
+    }
     A(c.dim, &r->normed);
     const uint32_t kvdim_l = kvdim / tpw;  // this rank's KV heads
     A(qdim / tpw, &r->q);
@@ -1368,6 +1476,7 @@ int32_t yule_cuda_runner_destroy(yule_cuda_runner *r) {
     if (r->bd_graph) cudaGraphExecDestroy(r->bd_graph);
     if (r->mega) mega_destroy(r->mega);
     if (r->h_logits) cudaFreeHost(r->h_logits);
+    if (r->h_moe_sel) cudaFreeHost(r->h_moe_sel);
     if (r->h_pinned) cudaFreeHost(r->h_pinned);
     for (yule_buffer h : r->owned) yule_cuda_free(r->ctx, h);
     // collective: every rank destroys its runner at the same point (a runner whose creation failed half-way leaves

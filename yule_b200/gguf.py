@@ -100,7 +100,8 @@ class GgufFile:
                            max_seq_len=cfg.max_seq_len, norm_eps=cfg.norm_eps, rope_freq_base=cfg.rope_freq_base,
                            rotary_dim=cfg.rotary_dim, sliding_window=cfg.sliding_window,
                            attn_logit_softcap=cfg.attn_logit_softcap, logit_softcap=cfg.logit_softcap,
-                           norm_weight_offset=cfg.norm_weight_offset, geglu=bool(cfg.geglu))
+                           norm_weight_offset=cfg.norm_weight_offset, geglu=bool(cfg.geglu),
+                           n_experts=cfg.n_experts, n_experts_used=cfg.n_experts_used)
 
 
 def load_runner(backend: CudaB200Backend, gguf: GgufFile, max_seq_len: int = 0, fused: bool = True) -> CudaTransformerRunner:

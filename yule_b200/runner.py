@@ -38,9 +38,14 @@ class ModelConfig:
     logit_softcap: float = 0.0
     norm_weight_offset: float = 0.0
     geglu: bool = False
+    # mixture of experts (model_runner.rs:395-397, 813-958): experts per layer (0 = dense FFN), experts used per token
+    n_experts: int = 0
+    n_experts_used: int = 0
 
-    def tensor_shapes(self) -> dict[str, tuple[int, int]]:
-        """GGUF tensor name → (rows, cols) for every matrix the runner reads (gpu_runner.rs:213-222)."""
+    def tensor_shapes(self, packed_experts: bool = True) -> dict[str, tuple[int, int]]:
+        """GGUF tensor name → (rows, cols) for every matrix the runner reads (gpu_runner.rs:213-222); for a
+        mixture-of-experts model the router and the experts, packed (one tensor per projection holding all experts'
+        rows) or one tensor per expert (weight_loader.rs:222-260)."""
         q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
         shapes = {"token_embd.weight": (self.vocab_size, self.dim), "output.weight": (self.vocab_size, self.dim)}
         for l in range(self.n_layers):
@@ -49,9 +54,21 @@ class ModelConfig:
             shapes[p + "attn_k.weight"] = (kv, self.dim)
             shapes[p + "attn_v.weight"] = (kv, self.dim)
             shapes[p + "attn_output.weight"] = (self.dim, q)
-            shapes[p + "ffn_gate.weight"] = (self.ff_dim, self.dim)
-            shapes[p + "ffn_up.weight"] = (self.ff_dim, self.dim)
-            shapes[p + "ffn_down.weight"] = (self.dim, self.ff_dim)
+            if self.n_experts == 0:
+                shapes[p + "ffn_gate.weight"] = (self.ff_dim, self.dim)
+                shapes[p + "ffn_up.weight"] = (self.ff_dim, self.dim)
+                shapes[p + "ffn_down.weight"] = (self.dim, self.ff_dim)
+            else:
+                shapes[p + "ffn_gate_inp.weight"] = (self.n_experts, self.dim)
+                if packed_experts:
+                    shapes[p + "ffn_gate_exps.weight"] = (self.n_experts * self.ff_dim, self.dim)
+                    shapes[p + "ffn_up_exps.weight"] = (self.n_experts * self.ff_dim, self.dim)
+                    shapes[p + "ffn_down_exps.weight"] = (self.n_experts * self.dim, self.ff_dim)
+                else:
+                    for e in range(self.n_experts):
+                        shapes[p + f"ffn_gate.{e}.weight"] = (self.ff_dim, self.dim)
+                        shapes[p + f"ffn_up.{e}.weight"] = (self.ff_dim, self.dim)
+                        shapes[p + f"ffn_down.{e}.weight"] = (self.dim, self.ff_dim)
         return shapes
 
     def norm_names(self) -> list[str]:
@@ -77,7 +94,7 @@ class CudaTransformerRunner:
                                 config.vocab_size, config.ff_dim, config.max_seq_len, config.norm_eps,
                                 config.rope_freq_base, int(fused), config.rotary_dim, config.sliding_window,
                                 config.attn_logit_softcap, config.logit_softcap, config.norm_weight_offset,
-                                1 if config.geglu else 0)
+                                1 if config.geglu else 0, config.n_experts, config.n_experts_used)
         r = C.c_void_p()
         _check(self._lib.yule_cuda_runner_create(backend._ctx, C.byref(cfg), C.byref(r)))
         self._r = r

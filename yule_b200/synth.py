@@ -80,7 +80,8 @@ ROW_SHARDED = ("attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.w
 
 def synthetic_model(cfg: ModelConfig, seed: int = 0, linear: DType = DType.Q4_K, ffn_down: DType | None = None,
                     output: DType | None = None, token_embd: DType | None = None, std: float = 0.02,
-                    norm_dtype: DType = DType.F32, rank: int = 0, world: int = 1) -> dict:
+                    norm_dtype: DType = DType.F32, rank: int = 0, world: int = 1, packed_experts: bool = True,
+                    router: DType = DType.F32) -> dict:
     """Random-init N(0, std) Llama-architecture weights as a GGUF-name → (bytes, DType) map.
 
     Norm weights are 1.0.  ``ffn_down`` / ``output`` / ``token_embd`` default to ``linear``.  With ``world`` > 1
@@ -91,12 +92,22 @@ def synthetic_model(cfg: ModelConfig, seed: int = 0, linear: DType = DType.Q4_K,
     output = output or linear
     token_embd = token_embd or linear
     weights = {}
-    for name, (rows, cols) in cfg.tensor_shapes().items():
+    for name, (rows, cols) in cfg.tensor_shapes(packed_experts).items():
+        if name.endswith("ffn_gate_inp.weight"):
+            # the router of a mixture-of-experts layer: F32 / F16 in model files (or any block format); a larger
+            # spread than the linears so that the expert probabilities differ
+            if router in (DType.F32, DType.F16):
+                vals = normal(tensor_seed(seed, name), rows * cols) * np.float32(0.5)
+                data = vals.view(np.uint8) if router == DType.F32 else vals.astype(np.float16).view(np.uint8)
+                weights[name] = (data, router)
+            else:
+                weights[name] = (random_quantized(router, tensor_seed(seed, name), rows * cols, 0.5), router)
+            continue
         if name == "token_embd.weight":
             dt = token_embd
         elif name == "output.weight":
             dt = output
-        elif name.endswith("ffn_down.weight"):
+        elif name.endswith("ffn_down.weight") or name.endswith("ffn_down_exps.weight") or ".ffn_down." in name:
             dt = ffn_down
         else:
             dt = linear
