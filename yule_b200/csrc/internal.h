@@ -239,6 +239,10 @@ cudaError_t launch_q8q4_ring_batch(const QmvArgs &a, uint32_t nb, int sm_count, 
 // vectors one pass can take for this call (0: not supported), and one pass over the first `nb` vectors of `a`.
 uint32_t kquant_batch_width(const QmvArgs &a);
 cudaError_t launch_kquant_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches);
+// Up to three matrices that read the same activation rows (Q/K/V; gate/up) as ONE launch per pass of four vectors, with
+// the optional RMSNorm prologue (norm_w / eps of the arguments): whether the arguments allow it, and the launch.
+bool kquant_batch_can_share(const QmvArgs *segs, uint32_t n_seg);
+cudaError_t launch_kquant_batch_shared(const QmvArgs *segs, uint32_t n_seg, int sm_count, cudaStream_t s, uint64_t *launches);
 
 // Quantised GEMM on tcgen05 for eight or more activation rows (qgemm_tc.cu): an activation
 // re-layout kernel followed by the persistent GEMM.  `scratch` holds qgemm_scratch_bytes().

@@ -76,13 +76,19 @@ __device__ __forceinline__ float byte_to_float(uint32_t w) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 + I)) - 8388608.0f;
 }
 
+constexpr int kMaxSegs = 3;  // matrices that share their activations (Q/K/V; gate/up) in one launch
 struct KBatchParams {
-    CUtensorMap map[4];  // Q4_K: map[0] = the raw tensor; Q6_K: the four planes of the row-planar copy
-    float *out;
+    CUtensorMap map[kMaxSegs][4];  // per matrix — Q4_K: [0] = the raw tensor; Q6_K: the four planes of the row-planar copy
+    float *out[kMaxSegs];
+    uint32_t n_rows[kMaxSegs], out_stride[kMaxSegs];
+    uint32_t tile0[kMaxSegs + 1];  // first 16-row tile of each matrix in the launch's tile numbering; [n_seg] = n_tiles
+    uint32_t n_seg;
     const float *x;
-    const float *residual;
-    uint32_t n_rows, n_cols, n_tiles, stages, chunks;
-    uint32_t nb, x_stride, out_stride, late_wait;
+    const float *residual;  // added to the results of matrix 0 (single-matrix launches only)
+    const float *norm_w;    // RMSNorm prologue: the rows are x · inv_rms · norm_w (yule-infer/src/model_runner.rs:254-263), or null
+    float eps;
+    uint32_t n_cols, n_tiles, stages, chunks;
+    uint32_t nb, x_stride, late_wait;
     uint32_t blk_off;  // first super-block of the rows this launch covers (a launch takes a range of the columns)
     int *status;
     long long wait_cycles;
@@ -102,7 +108,7 @@ struct KBatchSmem {
 constexpr size_t kPartialBytes = (size_t)kGroups * 2 * kWarps * 64 * sizeof(float);
 __host__ __device__ inline size_t fixed_bytes(uint32_t n_cols, uint32_t nb) {
     size_t off = (size_t)n_cols * 4 * nb + (size_t)(n_cols / 16) * 16;
-    off += 256 + (size_t)kGroups * kWarps * 4 * sizeof(float) + kPartialBytes + (size_t)kGroups * kMaxStages * (8 + 4);
+    off += 256 + 2 * (size_t)kGroups * kWarps * 4 * sizeof(float) + kPartialBytes + (size_t)kGroups * kMaxStages * (8 + 4);
     return (off + 127) & ~(size_t)127;
 }
 __device__ __forceinline__ KBatchSmem carve(unsigned char *base, uint32_t n_cols, uint32_t nb, size_t ring_bytes) {
@@ -116,7 +122,7 @@ __device__ __forceinline__ KBatchSmem carve(unsigned char *base, uint32_t n_cols
     s.zb = base + off;
     off += 256;
     s.red = reinterpret_cast<float *>(base + off);
-    off += (size_t)kGroups * kWarps * 4 * sizeof(float);
+    off += 2 * (size_t)kGroups * kWarps * 4 * sizeof(float);
     s.partial = reinterpret_cast<float *>(base + off);
     off += kPartialBytes;
     s.bars = reinterpret_cast<uint64_t *>(base + off);
@@ -130,7 +136,9 @@ __device__ __forceinline__ void issue_stage(const KBatchParams &p, uint32_t tile
     // Tiled copies by the first lane; every box is as wide as its plane's shared-memory row pitch (what lies beyond the
     // eight super-blocks is never read), rows past the end of the matrix arrive as zeros.
     if (lane == 0) {
-        const uint32_t row0 = tile * kStageRows, blk0 = p.blk_off + chunk * kStageBlocks;
+        uint32_t seg = 0;
+        while (seg + 1 < p.n_seg && tile >= p.tile0[seg + 1]) seg++;
+        const uint32_t row0 = (tile - p.tile0[seg]) * kStageRows, blk0 = p.blk_off + chunk * kStageBlocks;
         mbar_arrive_expect_tx(bar, stage_bytes<Q6>());
         auto box = [&](uint32_t off, const CUtensorMap *m, uint32_t x) {
             asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -139,12 +147,12 @@ __device__ __forceinline__ void issue_stage(const KBatchParams &p, uint32_t tile
                          : "memory");
         };
         if (Q6) {
-            box(kQlOff, &p.map[0], blk0 * 16u);
-            box(kQhOff, &p.map[1], blk0 * 8u);
-            box(kScOff, &p.map[2], blk0 * 2u);
-            box(kDOff, &p.map[3], blk0 / 4u);
+            box(kQlOff, &p.map[seg][0], blk0 * 16u);
+            box(kQhOff, &p.map[seg][1], blk0 * 8u);
+            box(kScOff, &p.map[seg][2], blk0 * 2u);
+            box(kDOff, &p.map[seg][3], blk0 / 4u);
         } else {
-            box(0, &p.map[0], blk0 * 18u);
+            box(0, &p.map[seg][0], blk0 * 18u);
         }
     }
     __syncwarp();
@@ -154,14 +162,18 @@ __device__ __forceinline__ void issue_stage(const KBatchParams &p, uint32_t tile
 // l the four columns 4l..4l+3; two CTA barriers (the per-vector power-of-two scales, then the finished image).
 // Returns 2^-e of vector `want`.
 __device__ __forceinline__ float stage_x(const KBatchSmem &sm, const float *__restrict__ x, uint32_t x_stride, uint32_t nb, uint32_t n_sg,
-                                         int lane, uint32_t want) {
+                                         int lane, uint32_t want, const float *__restrict__ norm_w, float eps) {
     constexpr int KC = 2;  // groups per vector kept in registers between the two passes (all of them up to 4096 columns)
     constexpr uint32_t kAllWarps = kGroups * kWarps;
     const uint32_t W = threadIdx.x >> 5;
     if (threadIdx.x < 64) reinterpret_cast<uint32_t *>(sm.zb)[threadIdx.x] = 0u;
     float4 cache[4][KC];
-    float mx[4] = {0.f, 0.f, 0.f, 0.f};
-    auto amax4 = [](float4 a) { return fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))); };
+    float mx[4] = {0.f, 0.f, 0.f, 0.f}, ss[4] = {0.f, 0.f, 0.f, 0.f};
+    // With the RMSNorm prologue the image holds x · inv_rms · w: max |x · w| and Σx² are reduced together, the
+    // vector's 1/rms enters the maximum afterwards.
+    auto wts = [&](uint32_t s) { return norm_w ? *reinterpret_cast<const float4 *>(norm_w + s * 128u + lane * 4u) : make_float4(1.f, 1.f, 1.f, 1.f); };
+    auto amax4 = [](float4 a, float4 g) { return fmaxf(fmaxf(fabsf(a.x * g.x), fabsf(a.y * g.y)), fmaxf(fabsf(a.z * g.z), fabsf(a.w * g.w))); };
+    auto sq4 = [](float4 a, float acc) { return fmaf(a.w, a.w, fmaf(a.z, a.z, fmaf(a.y, a.y, fmaf(a.x, a.x, acc)))); };
 #pragma unroll
     for (int v = 0; v < 4; v++) {
         if ((uint32_t)v < nb) {
@@ -179,26 +191,48 @@ __device__ __forceinline__ float stage_x(const KBatchSmem &sm, const float *__re
             const float *xv = x + (size_t)v * x_stride;
 #pragma unroll
             for (int i = 0; i < KC; i++)
-                if (W + kAllWarps * i < n_sg) mx[v] = fmaxf(mx[v], amax4(cache[v][i]));
-            for (uint32_t s = W + kAllWarps * KC; s < n_sg; s += kAllWarps)
-                mx[v] = fmaxf(mx[v], amax4(*reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u)));
+                if (W + kAllWarps * i < n_sg) {
+                    mx[v] = fmaxf(mx[v], amax4(cache[v][i], wts(W + kAllWarps * i)));
+                    ss[v] = sq4(cache[v][i], ss[v]);
+                }
+            for (uint32_t s = W + kAllWarps * KC; s < n_sg; s += kAllWarps) {
+                const float4 a = *reinterpret_cast<const float4 *>(xv + s * 128u + lane * 4u);
+                mx[v] = fmaxf(mx[v], amax4(a, wts(s)));
+                ss[v] = sq4(a, ss[v]);
+            }
         }
     }
 #pragma unroll
     for (int v = 0; v < 4; v++)
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], o));
+        for (int o = 16; o > 0; o >>= 1) {
+            mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], o));
+            ss[v] += __shfl_xor_sync(0xffffffffu, ss[v], o);
+        }
     float4 *red = reinterpret_cast<float4 *>(sm.red);
-    if (lane == 0) red[W] = make_float4(mx[0], mx[1], mx[2], mx[3]);
+    if (lane == 0) {
+        red[W] = make_float4(mx[0], mx[1], mx[2], mx[3]);
+        red[kAllWarps + W] = make_float4(ss[0], ss[1], ss[2], ss[3]);
+    }
     __syncthreads();
+    float inv_rms[4] = {1.f, 1.f, 1.f, 1.f};
     {
-        float4 m = red[0];
+        float4 m = red[0], q = red[kAllWarps];
 #pragma unroll
         for (uint32_t w = 1; w < kAllWarps; w++) {
-            const float4 o = red[w];
+            const float4 o = red[w], o2 = red[kAllWarps + w];
             m.x = fmaxf(m.x, o.x), m.y = fmaxf(m.y, o.y), m.z = fmaxf(m.z, o.z), m.w = fmaxf(m.w, o.w);
+            q.x += o2.x, q.y += o2.y, q.z += o2.z, q.w += o2.w;
         }
         mx[0] = m.x, mx[1] = m.y, mx[2] = m.z, mx[3] = m.w;
+        if (norm_w) {
+            // 1 / sqrt(Σx² / n + eps), as the CPU runner forms it (model_runner.rs:254-258)
+            const float n = (float)(n_sg * 128u);
+            inv_rms[0] = 1.0f / sqrtf(q.x / n + eps), inv_rms[1] = 1.0f / sqrtf(q.y / n + eps);
+            inv_rms[2] = 1.0f / sqrtf(q.z / n + eps), inv_rms[3] = 1.0f / sqrtf(q.w / n + eps);
+#pragma unroll
+            for (int v = 0; v < 4; v++) mx[v] *= inv_rms[v];
+        }
     }
     float scale[4], inv_want = 1.f;
 #pragma unroll
@@ -213,6 +247,11 @@ __device__ __forceinline__ float stage_x(const KBatchSmem &sm, const float *__re
     }
     const uint32_t chunk_bytes = nb * 64u;
     auto convert = [&](uint32_t s, uint32_t v, float4 a, float sc) {
+        if (norm_w) {
+            const float4 g = wts(s);
+            const float ir = inv_rms[v];
+            a.x = a.x * ir * g.x, a.y = a.y * ir * g.y, a.z = a.z * ir * g.z, a.w = a.w * ir * g.w;
+        }
         a.x *= sc;  // exact (power of two)
         a.y *= sc;
         a.z *= sc;
@@ -405,7 +444,7 @@ qmv_kquant_batch_kernel(const __grid_constant__ KBatchParams p) {
 
     if (!p.late_wait) yule_pdl_wait();  // the activations (and the residual) come from the previous kernel
     const uint32_t tid = threadIdx.x & (kWarps * 32 - 1);
-    const float inv_scale = stage_x(sm, p.x, p.x_stride, nb, p.n_cols / 128, lane, tid >> 4);
+    const float inv_scale = stage_x(sm, p.x, p.x_stride, nb, p.n_cols / 128, lane, tid >> 4, p.norm_w, p.eps);
     if (total == 0) return;
 
     // B column n = g carries vector g / 2 (hi for even g, lo for odd); columns past 2·nb read zeros
@@ -463,12 +502,15 @@ qmv_kquant_batch_kernel(const __grid_constant__ KBatchParams p) {
                 const uint32_t v = tid >> 4, rr = tid & 15u;
                 float sacc = 0.f;
                 for (uint32_t w2 = 0; w2 < n_warps_used; w2++) sacc += part[w2 * 64 + rr * 4 + v];
-                const uint32_t row = (first_tile + ck * tile_stride) * kStageRows + rr;
-                if (row < p.n_rows) {
+                const uint32_t tile = first_tile + ck * tile_stride;
+                uint32_t seg = 0;
+                while (seg + 1 < p.n_seg && tile >= p.tile0[seg + 1]) seg++;
+                const uint32_t row = (tile - p.tile0[seg]) * kStageRows + rr;
+                if (row < p.n_rows[seg]) {
                     sacc = (sacc * 16777216.0f) * inv_scale;
-                    const size_t o = (size_t)v * p.out_stride + row;
+                    const size_t o = (size_t)v * p.out_stride[seg] + row;
                     if (p.residual) sacc += p.residual[o];
-                    p.out[o] = sacc;
+                    p.out[seg][o] = sacc;
                 }
             }
             cc = 0;
@@ -492,37 +534,49 @@ uint32_t batch_stages(bool q6, uint32_t n_cols, uint32_t nb) {
     return st > (size_t)kMaxStages ? (uint32_t)kMaxStages : (uint32_t)st;
 }
 
-// One launch over the columns [256·blk_off, 256·blk_off + part_cols) of every row; `residual` is added to its results.
+// One launch over the columns [256·blk_off, 256·blk_off + part_cols) of every row of `n_seg` matrices that share their
+// activations (same type, columns, vectors); `residual` is added to the results (single matrix only).
 template <bool Q6>
-cudaError_t launch_variant(const QmvArgs &a, uint32_t nb, uint32_t stages, uint32_t blk_off, uint32_t part_cols, const float *residual,
-                           int sm_count, cudaStream_t s) {
+cudaError_t launch_variant(const QmvArgs *segs, uint32_t n_seg, uint32_t nb, uint32_t stages, uint32_t blk_off, uint32_t part_cols,
+                           const float *residual, int sm_count, cudaStream_t s) {
+    const QmvArgs &a = segs[0];
     KBatchParams p = {};
     const uint32_t bpr = a.n_cols / 256;
-    if (Q6) {
-        const uint64_t rec = row_record_bytes(bpr);
-        const uint64_t off[4] = {0, (uint64_t)bpr * 128, (uint64_t)bpr * 192, (uint64_t)bpr * 208};
-        const uint64_t len[4] = {(uint64_t)bpr * 128, (uint64_t)bpr * 64, (uint64_t)bpr * 16, d_section_bytes(bpr)};
-        const uint32_t pitch[4] = {kQlPitch, kQhPitch, kScPitch, kDPitch};
-        for (int pl = 0; pl < 4; pl++) {
-            cudaError_t me = cached_tensor_map_2d(a.planar + off[pl], 8, len[pl] / 8, a.n_rows, rec, pitch[pl] / 8, kStageRows, &p.map[pl]);
+    p.n_seg = n_seg;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < n_seg; i++) {
+        const QmvArgs &g = segs[i];
+        if (Q6) {
+            const uint64_t rec = row_record_bytes(bpr);
+            const uint64_t off[4] = {0, (uint64_t)bpr * 128, (uint64_t)bpr * 192, (uint64_t)bpr * 208};
+            const uint64_t len[4] = {(uint64_t)bpr * 128, (uint64_t)bpr * 64, (uint64_t)bpr * 16, d_section_bytes(bpr)};
+            const uint32_t pitch[4] = {kQlPitch, kQhPitch, kScPitch, kDPitch};
+            for (int pl = 0; pl < 4; pl++) {
+                cudaError_t me = cached_tensor_map_2d(g.planar + off[pl], 8, len[pl] / 8, g.n_rows, rec, pitch[pl] / 8, kStageRows, &p.map[i][pl]);
+                if (me != cudaSuccess) return me;
+            }
+        } else {
+            const uint64_t row_bytes = (uint64_t)bpr * 144;
+            cudaError_t me = cached_tensor_map_2d(g.w, 8, row_bytes / 8, g.n_rows, row_bytes, kQ4RowPitch / 8, kStageRows, &p.map[i][0]);
             if (me != cudaSuccess) return me;
         }
-    } else {
-        const uint64_t row_bytes = (uint64_t)bpr * 144;
-        cudaError_t me = cached_tensor_map_2d(a.w, 8, row_bytes / 8, a.n_rows, row_bytes, kQ4RowPitch / 8, kStageRows, &p.map[0]);
-        if (me != cudaSuccess) return me;
+        p.out[i] = g.out;
+        p.n_rows[i] = g.n_rows;
+        p.out_stride[i] = g.out_stride;
+        p.tile0[i] = tiles;
+        tiles += (g.n_rows + kStageRows - 1) / kStageRows;
     }
-    p.out = a.out;
+    for (uint32_t i = n_seg; i <= (uint32_t)kMaxSegs; i++) p.tile0[i] = tiles;
     p.x = a.x + (size_t)blk_off * 256;
     p.residual = residual;
-    p.n_rows = a.n_rows;
+    p.norm_w = a.norm_w;
+    p.eps = a.eps;
     p.n_cols = part_cols;
     p.blk_off = blk_off;
-    p.n_tiles = (a.n_rows + kStageRows - 1) / kStageRows;
+    p.n_tiles = tiles;
     p.chunks = (part_cols / 256 + kStageBlocks - 1) / kStageBlocks;
     p.nb = nb;
     p.x_stride = a.x_stride;
-    p.out_stride = a.out_stride;
     p.late_wait = (a.pdl && a.late_wait) ? 1u : 0u;
     p.status = a.status;
     p.wait_cycles = a.wait_cycles;
@@ -570,14 +624,64 @@ uint32_t kquant_batch_width(const QmvArgs &a) {
     if (!q6 && a.type != YULE_DTYPE_Q4_K) return 0;
     if (q6 && !a.planar) return 0;
     if (a.batch < 2 || a.n_cols == 0 || a.n_cols % 256 || a.n_rows == 0 || a.x_stride % 4) return 0;
-    if (a.norm_w || a.tp.push || a.tp.wait) return 0;  // fused prologues and exchanges stay with the one-pass kernels
+    if (a.tp.push || a.tp.wait) return 0;  // fused exchanges stay with the one-vector kernels
     if ((reinterpret_cast<uintptr_t>(q6 ? (const void *)a.planar : (const void *)a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return 0;
     // the widest pass whose image fits whole; for longer rows the widest that fits in parts of at least two stages
     for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
         if (part_cols_for(q6, a.n_cols, nb) == a.n_cols) return nb;
+    if (a.norm_w) return 0;  // the RMSNorm prologue needs the whole row in one launch
     for (uint32_t nb = a.batch < 4 ? a.batch : 4; nb >= 2; nb--)
         if (part_cols_for(q6, a.n_cols, nb) != 0) return nb;
     return 0;
+}
+
+// Matrices that share their activations (Q/K/V, gate/up) as one launch: same format, columns, vectors, prologue.
+bool kquant_batch_can_share(const QmvArgs *segs, uint32_t n_seg) {
+    if (n_seg < 1 || n_seg > (uint32_t)kMaxSegs) return false;
+    const QmvArgs &a = segs[0];
+    const uint32_t nb = kquant_batch_width(a);
+    if (nb < 2) return false;
+    if (part_cols_for(a.type == YULE_DTYPE_Q6_K, a.n_cols, nb) != a.n_cols) return false;  // rows that need several launches: one matrix at a time
+    for (uint32_t i = 1; i < n_seg; i++) {
+        const QmvArgs &g = segs[i];
+        if (g.type != a.type || g.n_cols != a.n_cols || g.x != a.x || g.batch != a.batch || g.x_stride != a.x_stride || g.norm_w != a.norm_w ||
+            g.residual || a.residual || kquant_batch_width(g) != nb)
+            return false;
+    }
+    return true;
+}
+
+cudaError_t launch_kquant_batch_shared(const QmvArgs *segs, uint32_t n_seg, int sm_count, cudaStream_t s, uint64_t *launches) {
+    if (!kquant_batch_can_share(segs, n_seg)) return cudaErrorInvalidValue;
+    // passes of up to four vectors over all the matrices
+    const QmvArgs &a = segs[0];
+    const bool q6 = a.type == YULE_DTYPE_Q6_K;
+    uint32_t done = 0;
+    while (done < a.batch) {
+        QmvArgs part[kMaxSegs];
+        for (uint32_t i = 0; i < n_seg; i++) {
+            part[i] = segs[i];
+            part[i].x = segs[i].x + (size_t)done * segs[i].x_stride;
+            part[i].out = segs[i].out + (size_t)done * segs[i].out_stride;
+            part[i].residual = segs[i].residual ? segs[i].residual + (size_t)done * segs[i].out_stride : nullptr;
+            part[i].batch = a.batch - done;
+        }
+        const uint32_t nb = kquant_batch_width(part[0]);
+        if (nb < 2) {  // one vector left: the one-vector kernels, matrix by matrix
+            for (uint32_t i = 0; i < n_seg; i++) {
+                cudaError_t e = launch_qmv(part[i], sm_count, s, launches);
+                if (e != cudaSuccess) return e;
+            }
+            return cudaSuccess;
+        }
+        const uint32_t stages = batch_stages(q6, a.n_cols, nb);
+        cudaError_t e = q6 ? launch_variant<true>(part, n_seg, nb, stages, 0, a.n_cols, part[0].residual, sm_count, s)
+                           : launch_variant<false>(part, n_seg, nb, stages, 0, a.n_cols, part[0].residual, sm_count, s);
+        if (e != cudaSuccess) return e;
+        *launches += 1;
+        done += nb;
+    }
+    return cudaSuccess;
 }
 
 cudaError_t launch_kquant_batch(const QmvArgs &a, uint32_t nb, int sm_count, cudaStream_t s, uint64_t *launches) {
@@ -596,8 +700,8 @@ cudaError_t launch_kquant_batch(const QmvArgs &a, uint32_t nb, int sm_count, cud
         if (col + cols > a.n_cols) cols = a.n_cols - col;
         const uint32_t stages = batch_stages(q6, cols, nb);
         const float *residual = i == 0 ? a.residual : a.out;  // later parts add to what the earlier ones stored
-        cudaError_t e = q6 ? launch_variant<true>(a, nb, stages, col / 256, cols, residual, sm_count, s)
-                           : launch_variant<false>(a, nb, stages, col / 256, cols, residual, sm_count, s);
+        cudaError_t e = q6 ? launch_variant<true>(&a, 1, nb, stages, col / 256, cols, residual, sm_count, s)
+                           : launch_variant<false>(&a, 1, nb, stages, col / 256, cols, residual, sm_count, s);
         if (e != cudaSuccess) return e;
         *launches += 1;
         col += cols;

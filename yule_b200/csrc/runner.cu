@@ -1025,25 +1025,44 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
     // in `act`: normed rows in a buffer of their own, SwiGLU in place, anything else where it is.
     bool mv = ps.n_live <= kRowsMatvecMax;
     if (const char *k = knob("YULE_ROWS_MATVEC")) mv = mv && atoi(k) != 0;
-    const float *act = nullptr;
+    // The matrices that read the same rows (Q/K/V; gate/up) are collected and launched together by `flush`: as one
+    // launch with the RMSNorm folded into its staging where the batched kernel allows it, else one by one behind a
+    // separate RMSNorm kernel.
+    const float *act = nullptr, *act_norm = nullptr;
+    QmvArgs pending[3];
+    uint32_t n_pending = 0;
+    auto flush = [&]() {
+        if (n_pending == 0) return;
+        for (uint32_t i = 0; i < n_pending; i++) pending[i].norm_w = act_norm;
+        if (act_norm && !kquant_batch_can_share(pending, n_pending)) {
+            ok(launch_rms_norm_rows(act, act_norm, r->pf_norm, pending[0].n_cols, ps.n_live, c.norm_eps, s, launches));
+            for (uint32_t i = 0; i < n_pending; i++) {
+                pending[i].x = r->pf_norm;
+                pending[i].norm_w = nullptr;
+            }
+        }
+        if (kquant_batch_can_share(pending, n_pending))
+            ok(launch_kquant_batch_shared(pending, n_pending, sms, s, launches));
+        else
+            for (uint32_t i = 0; i < n_pending; i++) ok(launch_qmv(pending[i], sms, s, launches));
+        n_pending = 0;
+    };
     auto prep = [&](float *x, uint32_t cols, const float *norm_w, const float *gate) {
         if (!mv) {
             xprep(x, cols, norm_w, gate);
-        } else if (norm_w) {
-            ok(launch_rms_norm_rows(x, norm_w, r->pf_norm, cols, ps.n_live, c.norm_eps, s, launches));
-            act = r->pf_norm;
-        } else if (gate) {
-            ok(launch_silu_mul(gate, x, x, ps.n_live * cols, s, launches, true));
-            act = x;
-        } else {
-            act = x;
+            return;
         }
+        flush();
+        if (gate) ok(launch_silu_mul(gate, x, x, ps.n_live * cols, s, launches, true));  // SwiGLU in place
+        act = x;
+        act_norm = norm_w;
     };
     auto lin = [&](const Tensor &t, uint32_t rows, uint32_t cols, float *out, uint32_t stride, const float *residual) {
         if (!mv) {
             mm(t, rows, cols, out, stride, residual);
             return;
         }
+        if (n_pending == 3) flush();
         QmvArgs a = {};
         a.w = (const uint8_t *)t.buf.ptr;
         a.x = act;
@@ -1055,15 +1074,17 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         a.x_stride = cols;
         a.out_stride = stride;
         a.residual = residual;
+        a.eps = c.norm_eps;
         if (t.type == YULE_DTYPE_Q6_K && t.buf.planar && t.buf.planar_cols == cols) a.planar = t.buf.planar;
         a.status = ctx->device_status;
         a.wait_cycles = ctx->wait_cycles;
         a.pdl = true;  // set-up and the first weight copies run under the tail of the kernel before; the rows are read after the wait
-        ok(launch_qmv(a, sms, s, launches));
+        pending[n_pending++] = a;
     };
     const uint32_t epochs_per_tick = 5 * c.n_layers + 1;
     uint32_t xchg_index = 0;
     auto exchange = [&](size_t offset, uint32_t per_rank, uint32_t stride) {
+        flush();
         if (N > 1) ok(tp_exchange(ctx, offset, per_rank, 5 + xchg_index % 3, r->d_btick, epochs_per_tick, xchg_index, false, launches, m, stride));
         xchg_index++;
     };
@@ -1076,6 +1097,7 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         lin(L.attn_q, qdim_l, dim, r->pf_q, qdim_l, nullptr);
         lin(L.attn_k, kvdim_l, dim, r->pf_k, kvdim_l, nullptr);
         lin(L.attn_v, kvdim_l, dim, r->pf_v, kvdim_l, nullptr);
+        flush();
         AttnDecode a;
         if (ps.batch) {
             ok(launch_rope_kv_write_batch(r->pf_q, r->pf_k, r->pf_v, r->bd_k[l], r->bd_v[l], r->rope_cos, r->rope_sin, 0, ps.n_live, hd,
@@ -1127,6 +1149,7 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         prep(r->pf_x, dim, r->output_norm_f32, nullptr);
         lin(out_w, vocab_l, dim, r->bd_logits + (size_t)R * vocab_l, c.vocab_size, nullptr);
         exchange(r->xb_logits, vocab_l, c.vocab_size);
+        flush();
         ok(launch_argmax_rows(r->bd_logits, c.vocab_size, ps.n_live, r->bd_tokens, r->bd_pos, r->bd_step, r->bd_history, c.max_seq_len + 1, s, launches));
         ok(launch_advance_rows(r->bd_pos, r->bd_step, ps.n_live, s, launches));
     }
