@@ -164,10 +164,10 @@ def build_model(rank: int, linear: str = "Q4_K"):
 def small_batch_decode(backend, cfg, weights, n_prompt: int = 8, n_gen: int = 64):
     """The same model serving a few independent sequences per step (own KV caches and positions, device picks):
     every linear reads its weights once per step for up to four sequences (batched matvec kernels) or for all of
-    them (GEMM, from nine sequences).  Device time per step over `n_prompt + n_gen` steps, tokens/s over all sequences."""
+    them (GEMM, from thirteen sequences).  Device time per step over `n_prompt + n_gen` steps, tokens/s over all sequences."""
     from yule_b200 import CudaTransformerRunner, synth
     out = {}
-    for batch in (4, 8, 16):
+    for batch in (4, 8, 12, 16):
         run = CudaTransformerRunner(backend, cfg, weights, fused=1)
         prompts = synth.tokens(7 + batch, batch * n_prompt, cfg.vocab_size).reshape(batch, n_prompt)
         run.generate_greedy_batch(prompts, 4)  # warm-up: buffers, graph
@@ -181,7 +181,7 @@ def small_batch_decode(backend, cfg, weights, n_prompt: int = 8, n_gen: int = 64
         steps = n_prompt + n_gen
         out[f"batch_{batch}"] = {"steps": steps, "ms_per_step": round(ms / steps, 4),
                                  "tokens_per_s": round(batch * steps / (ms * 1e-3), 1),
-                                 "linears": "batched matvec kernels" if batch <= 8 else "tcgen05 GEMM"}
+                                 "linears": "batched matvec kernels" if batch <= 12 else "tcgen05 GEMM"}
         run.close()
     return out
 

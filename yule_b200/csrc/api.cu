@@ -325,6 +325,8 @@ int32_t yule_cuda_synchronize(yule_cuda_ctx *ctx) {
     YULE_CUDA_TRY(cudaMemcpy(&status, ctx->device_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (status != 0) {
         cudaMemset(ctx->device_status, 0, sizeof(int));
+        // a GEMM that gave up may have left tickets of its column split behind: the next launch expects zeros
+        if (ctx->gemm_scratch) cudaMemset(ctx->gemm_scratch, 0, ctx->gemm_scratch_bytes < kGemmTicketBytes ? ctx->gemm_scratch_bytes : kGemmTicketBytes);
         return fail(YULE_ERR_DEVICE_STATUS, "a device-side bounded wait gave up (status word %d)", status);
     }
     return YULE_OK;

@@ -895,7 +895,7 @@ constexpr uint32_t kPrefillChunk = 512, kPrefillMinTokens = 16, kPrefillMinChunk
 // Up to this many live rows a pass over the layers runs its linears on the batched matvec kernels (two to four rows
 // per pass over the weights, about the time of one) instead of the GEMM, whose fixed cost per launch is several
 // matvec passes.
-constexpr uint32_t kRowsMatvecMax = 8;
+constexpr uint32_t kRowsMatvecMax = 12;
 
 uint32_t prefill_chunk_size(const yule_cuda_runner *r) {
     uint32_t c = knob("YULE_CUDA_PREFILL_CHUNK") ? (uint32_t)atoi(knob("YULE_CUDA_PREFILL_CHUNK")) : kPrefillChunk;
