@@ -72,7 +72,10 @@ constexpr int kMaxStages = 6;
 #ifndef YULE_GEMM_RAW_SLOTS
 #define YULE_GEMM_RAW_SLOTS 4
 #endif
-constexpr int kRawSlots = YULE_GEMM_RAW_SLOTS;                       // super-blocks of raw Q4_K bytes in flight per CTA
+constexpr int kRawSlots = YULE_GEMM_RAW_SLOTS;                       // super-blocks of raw Q4_K bytes in flight per CTA (at most)
+// At 128 activation rows a stage is 56 KB: two raw slots instead of four make room for a third stage, which together
+// with the third accumulator set lets the unpacking, MMA-issuing and drain roles overlap.
+__host__ __device__ constexpr uint32_t raw_slots_for(uint32_t bn) { return bn >= 128 ? 2u : (uint32_t)kRawSlots; }
 constexpr uint32_t kRawBytes = kBM * 144;          // one super-block of 128 rows: 18 KB
 constexpr uint32_t kABytes = kBM * kBK * 2;  // the W slab of a stage: 16 KB
 constexpr float kSumScale = 1.0f / 32.0f;     // the sub-block sums of x are stored divided by 32
@@ -391,10 +394,17 @@ struct Tile {
     // one MMA per 16 columns instead of two (an MMA reads its 4 KB of W from shared memory whatever its width, which
     // is what a narrow MMA costs), the two products land in neighbouring accumulator columns and the drain adds them.
     static constexpr bool MERGED = BN <= 64;
-    static constexpr uint32_t NBUF = BN == 32 ? 4 : 2;       // TMEM accumulator sets in flight
+    // TMEM accumulator sets in flight.  Up to 64 rows every set has its own min accumulator.  At 128 rows the min
+    // accumulator (written by one MMA per super-block, read by the drain of that stage) is shared by all sets, which
+    // leaves room for three main accumulators instead of two: the MMA of stage i + 3 waits for the drain of stage i,
+    // which is after the drain of any earlier min term.  With two sets the issue-then-drain cycle of a set (about
+    // 600 cycles each at 128 rows) bounded a stage at 750 cycles whatever the other buffers.
+    static constexpr bool SHARED_MIN = BN == 128;
+    static constexpr uint32_t NBUF = BN == 32 ? 4 : (SHARED_MIN ? (GENERIC ? 4 : 3) : 2);
     static constexpr uint32_t kMainCols = MERGED ? 2 * BN : BN;
-    static constexpr uint32_t kBufCols = kMainCols + BN;     // main + min accumulator
-    static constexpr uint32_t kTmemCols = 512;               // NBUF · kBufCols = 384 or 512, allocated as a power of two
+    static constexpr uint32_t kBufCols = SHARED_MIN ? kMainCols : kMainCols + BN;  // main (+ min) accumulator of a set
+    static constexpr uint32_t kMinBase = SHARED_MIN ? 3 * kMainCols : kMainCols;   // shared: column 384; else behind the set's main
+    static constexpr uint32_t kTmemCols = 512;               // allocated as a power of two
     static constexpr uint32_t CW = BN / 2;                   // columns per drain warp
     static constexpr uint32_t kXHalfBytes = BN * kBK * 2;    // one fp16 term of the activation slab
     static constexpr uint32_t kBmBytes = BN * 16 * 2;        // sub-block sums of x: BN rows × (8 hi + 8 lo)
@@ -402,7 +412,8 @@ struct Tile {
     // stage (generic): W_hi | W_lo | x_hi | x_lo
     static constexpr uint32_t kOffAm = kABytes, kOffX = GENERIC ? 2 * kABytes : kABytes + kAmBytes;
     static constexpr uint32_t kStageBytes = kOffX + 2 * kXHalfBytes + (GENERIC ? 0u : kBmBytes);
-    static constexpr uint32_t kRawRingBytes = GENERIC ? 0u : kRawSlots * kRawBytes;  // generic: sized at launch
+    static constexpr uint32_t kRaw = raw_slots_for(BN);
+    static constexpr uint32_t kRawRingBytes = GENERIC ? 0u : kRaw * kRawBytes;  // generic: sized at launch
     // activation tiles in global memory, per (activation tile, super-block): four (hi, lo) slabs, then the sums
     static constexpr uint32_t kSuperBytes = 8 * kXHalfBytes + kBmBytes;
 };
@@ -435,7 +446,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             mbar_init(bar_acc_full + 8 * b, 1);
             mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
         }
-        for (uint32_t b = 0; b < (uint32_t)kRawSlots; b++) {
+        for (uint32_t b = 0; b < T::kRaw; b++) {
             mbar_init(bar_raw_full + 8 * b, 1);            // the loader's expect_tx
             mbar_init(bar_raw_empty + 8 * b, kProdWarps);  // every producer warp is done with the box
         }
@@ -537,7 +548,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     tw1 += c2 - c1;
                     tc_fence_after();
                     const uint32_t d_main = tmem_base + buf * T::kBufCols;
-                    [[maybe_unused]] const uint32_t d_min = d_main + T::kMainCols;
+                    [[maybe_unused]] const uint32_t d_min = T::SHARED_MIN ? tmem_base + T::kMinBase : d_main + T::kMinBase;
                     const uint32_t a = smem_u32(smem + (size_t)s * kStageBytes);
                     const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
 #pragma unroll
@@ -582,7 +593,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             UnitWalk walk;
             walk.start(p, n_items, bpr);
             for (uint32_t u = 0; walk.live; u++, walk.next(p, n_items, bpr)) {
-                const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
+                const uint32_t slot = u % T::kRaw, ph = (u / T::kRaw) & 1u;
                 if (!mbar_wait(bar_raw_empty + 8 * slot, ph ^ 1u, abort_flag, p.status)) break;
                 const uint32_t x = walk.sb * 144u, y = walk.mt * kBM;  // byte column (a multiple of 16), first row
                 if (skip & 64u) {  // timing aid: no raw bytes
@@ -753,7 +764,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
         UnitWalk walk;
         walk.start(p, n_items, bpr);
         for (uint32_t u = 0; walk.live && ok; u++, walk.next(p, n_items, bpr)) {
-            const uint32_t slot = u % kRawSlots, ph = (u / kRawSlots) & 1u;
+            const uint32_t slot = u % T::kRaw, ph = (u / T::kRaw) & 1u;
             if (!mbar_wait(bar_raw_full + 8 * slot, ph, abort_flag, p.status)) break;
             // row r of the box: 144 bytes; rows are 36 words apart, so eight lanes cover all 32 banks
             const unsigned char *bp = raw + (size_t)slot * kRawBytes + r * 144u;
@@ -834,7 +845,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
 #pragma unroll
                     for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                         uint32_t v[16];
-                        tmem_ld16(t_main + T::kMainCols + c0, v);
+                        tmem_ld16((T::SHARED_MIN ? tmem_base + (lane_base << 16) + col_base : t_main) + T::kMinBase + c0, v);
 #pragma unroll
                         for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(-dd.y * (1.0f / kSumScale), __uint_as_float(v[j]), acc[c0 + j]);
                     }
@@ -1272,7 +1283,7 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.raw_chunks = (p.unit_bytes + 14 + 15) / 16;      // covers the unit from any 2-byte-aligned start
     p.raw_stride = (p.raw_chunks | 1u) * 16;            // an odd multiple of 16 bytes
     p.raw_ring_bytes = (2 * kBM * p.raw_stride + 127u) & ~127u;
-    const size_t raw_ring = generic ? p.raw_ring_bytes : (size_t)kRawSlots * kRawBytes;
+    const size_t raw_ring = generic ? p.raw_ring_bytes : (size_t)raw_slots_for(bn) * kRawBytes;
     uint32_t stages = (uint32_t)((220u * 1024u - (raw_ring + 512u)) / stage_bytes);
     if (stages < 2) return cudaErrorInvalidValue;
     p.stages = stages > (uint32_t)kMaxStages ? (uint32_t)kMaxStages : stages;
