@@ -33,8 +33,9 @@
 //               (a single thread issues about one MMA per 63 cycles, less than the tensor core
 //               takes); warp 9 also owns the TMEM allocation
 //   warp  10    one thread: tiled TMA loads (cp.async.bulk.tensor.2d) of the raw Q4_K bytes, one
-//               128-row × 144-byte box per super-block, four boxes in flight; rows past the end of
-//               the matrix arrive as zeros
+//               128-row × 144-byte box per super-block, four boxes in flight (two at 128 activation
+//               rows, where the room goes to a third operand stage); rows past the end of the matrix
+//               arrive as zeros
 //   warps 12-19 unpack Q4_K from that shared-memory copy → fp16 sc·q in the operand layout (about
 //               1.4 instructions per weight)
 // A stage is a 128-row × 64-column slab of W (16 KB) plus the matching hi and lo slabs of x; the last
@@ -51,6 +52,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <functional>
+#include <type_traits>
 #include <unordered_map>
 
 #include <cuda.h>
@@ -174,6 +176,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same with the accumulate flag known at compile time (an immediate: no register, a predicate ptxas can fold).
+template <int ACC>
+__device__ __forceinline__ void umma_f16_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC)
         : "memory");
 }
 // The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
@@ -551,22 +563,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                     [[maybe_unused]] const uint32_t d_min = T::SHARED_MIN ? tmem_base + T::kMinBase : d_main + T::kMinBase;
                     const uint32_t a = smem_u32(smem + (size_t)s * kStageBytes);
                     const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
-#pragma unroll
-                    for (uint32_t k16 = 0; k16 < kBK / 16; k16++) {
-                        if (skip & 2u) break;
-                        const uint64_t da = smem_desc(a + k16 * 4096, 2048, 128);
+                    // One descriptor per operand and stage; the 16-column steps are constants added to its address field (the
+                    // issuing thread's own instruction stream, not the tensor pipe, bounded the MMA rate).
+                    const uint64_t da0 = smem_desc(a, 2048, 128);
+                    const uint64_t db0 = T::MERGED ? smem_desc(x_hi, 2 * x_lbo, 128) : smem_desc(x_hi, x_lbo, 128);
+                    auto step = [&](auto k16c) {
+                        constexpr uint32_t k16 = decltype(k16c)::value;
+                        const uint64_t da = da0 + (uint64_t)((k16 * 4096u) >> 4);
                         if constexpr (T::MERGED) {
                             // rows [0, BN) of an 8-column step are the hi terms, rows [BN, 2·BN) the lo terms
-                            const uint64_t db = smem_desc(x_hi + k16 * 4 * x_lbo, 2 * x_lbo, 128);
-                            umma_f16(d_main, da, db, idesc2, k16 != 0u);  // every stage starts a fresh accumulator
+                            const uint64_t db = db0 + (uint64_t)((k16 * 4u * x_lbo) >> 4);
+                            umma_f16_c<(k16 != 0)>(d_main, da, db, idesc2);  // every stage starts a fresh accumulator
                             if (GENERIC)  // the lo term of the weights against the hi term of the activations: the first BN rows
-                                umma_f16(d_main, smem_desc(a + kABytes + k16 * 4096, 2048, 128), db, idesc, 1u);
+                                umma_f16_c<1>(d_main, da + (uint64_t)(kABytes >> 4), db, idesc);
                         } else {
-                            umma_f16(d_main, da, smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, k16 != 0u);  // every stage starts a fresh accumulator
-                            umma_f16(d_main, da, smem_desc(x_lo + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
+                            const uint64_t dbh = db0 + (uint64_t)((k16 * 2u * x_lbo) >> 4);
+                            umma_f16_c<(k16 != 0)>(d_main, da, dbh, idesc);  // every stage starts a fresh accumulator
+                            umma_f16_c<1>(d_main, da, dbh + (uint64_t)(kXHalfBytes >> 4), idesc);
                             if (GENERIC)  // the lo term of the weights against the hi term of the activations
-                                umma_f16(d_main, smem_desc(a + kABytes + k16 * 4096, 2048, 128), smem_desc(x_hi + k16 * 2 * x_lbo, x_lbo, 128), idesc, 1u);
+                                umma_f16_c<1>(d_main, da + (uint64_t)(kABytes >> 4), dbh, idesc);
                         }
+                    };
+                    if (!(skip & 2u)) {
+                        step(std::integral_constant<uint32_t, 0>{});
+                        step(std::integral_constant<uint32_t, 1>{});
+                        step(std::integral_constant<uint32_t, 2>{});
+                        step(std::integral_constant<uint32_t, 3>{});
                     }
                     if (!GENERIC && (kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
                         umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(x_lo + kXHalfBytes, x_lbo, 128), idesc, 0u);
