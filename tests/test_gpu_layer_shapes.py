@@ -62,12 +62,13 @@ def test_chunked_prefill_logits_and_greedy(backend, oracle, shaped_model):
     run.close()
 
 
-@pytest.mark.parametrize("dtype", [DType.Q4_K, DType.Q6_K])
-@pytest.mark.parametrize("batch", [1, 4])
+@pytest.mark.parametrize("dtype", [DType.Q4_K, DType.Q6_K, DType.Q8_0, DType.Q4_0])
+@pytest.mark.parametrize("batch", [1, 4, 7])
 def test_vocabulary_matvec_against_threaded_qmv(backend, oracle, dtype, batch):
-    """128256 x 4096 (the Llama-3 output matrix): the matvec's shared-memory ring wraps many times per CTA."""
+    """128256 x 4096 (the Llama-3 output matrix): the matvec's shared-memory ring wraps many times per CTA; one
+    vector, four vectors in one pass of the batched kernels, seven as a pass of four and one of three."""
     n_rows, n_cols = 128256, 4096
-    w = synth.random_blocks(dtype, 7, n_rows * n_cols // 256)
+    w = synth.random_blocks(dtype, 7, n_rows * n_cols // dtype.block_size)
     x = synth.normal(8, batch * n_cols)
     wh, xh, oh = backend.upload(w), backend.upload(x), backend.allocate(batch * n_rows * 4)
     backend.prepare_weights(wh, dtype, n_rows, n_cols)
