@@ -109,6 +109,11 @@ def test_q8_0_q4_0_several_vectors_per_pass(backend, oracle, dtype, n_rows, n_co
     (DType.Q6_K, 40, 768, 6),        # three super-blocks: five of a stage's eight warps idle
     (DType.Q4_K, 5632, 2048, 4),
     (DType.Q6_K, 4096, 4096, 4),
+    (DType.Q4_K, 1000, 2048, 8),     # two passes of four
+    (DType.Q6_K, 300, 2048, 8),
+    (DType.Q4_K, 64, 4096, 8),
+    (DType.Q6_K, 2048, 5632, 6),
+    (DType.Q4_K, 5632, 2048, 9),     # two passes of four, and one vector through the one-vector kernel
 ])
 def test_q4_k_q6_k_several_vectors_per_pass(backend, oracle, dtype, n_rows, n_cols, batch):
     """Q4_K and Q6_K (prepared: row-planar copy) with two to four activation vectors per pass of the batched ring
