@@ -1,14 +1,14 @@
-// qmv_q8q4_ring.cu — Q8_0 and Q4_0 fused dequantise + matvec (one activation vector) on the tensor pipe, raw
-// blocks staged through a shared-memory ring by bulk copies.
+// qmv_q8q4_ring.cu — Q8_0 and Q4_0 fused dequantise + matvec on the tensor pipe, raw blocks staged through a
+// shared-memory ring by tiled TMA copies: a kernel for one activation vector and one for two to four per pass.
 //
 // Contract: yule-core/src/dequant.rs:902-926 — per 32-weight block, sum += d · Σ q·x with q the signed byte
 // (Q8_0) or nibble − 8 (Q4_0, byte j of a block holding weights 2j in its low and 2j+1 in its high nibble).
 //
 // The blocks are 34 and 18 bytes long and only 2-byte aligned in the GGUF stream, which rules out wide global
 // loads.  A row, however, is 16-byte aligned whenever n_cols is a multiple of 256 (8 blocks = 272 or 144 bytes),
-// and so is every run of eight 128-column groups of it: such runs go HBM → shared memory with 1-D bulk copies
-// (cp.async.bulk + mbarrier, issued before `griddepcontrol.wait`), and the odd alignment is dealt with there —
-// aligned 32-bit shared-memory loads and a funnel shift by 0 or 16 bits.
+// and so is every run of eight 128-column groups of it: 16 rows of such runs go HBM → shared memory as one tiled
+// copy (cp.async.bulk.tensor.2d + mbarrier, issued before `griddepcontrol.wait`), and the odd alignment is dealt
+// with there — aligned 32-bit shared-memory loads and a funnel shift by 0 or 16 bits.
 //
 // Tensor-core formulation (the same ideas as qmv_q4k_mma.cu):
 //   A  the quant as an fp16 subnormal, exact: the byte + 128 (Q8_0: one XOR, two PRMT per four weights) or the
@@ -49,7 +49,6 @@ struct Fmt {
     static constexpr uint32_t kStageSgs = kWarps * kSgsPerWarp;            // 8 / 16 groups per stage row
     static constexpr uint32_t kRowPitch = kStageSgs * kSgBytes + 16;       // 1104 / 1168
     static constexpr uint32_t kStageBytes = kStageRows * kRowPitch;        // 17 664 / 18 688
-    static constexpr int kWords = Q8 ? 8 : 4;                              // 32-bit words of quants per block
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -88,12 +87,6 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, int *st
             return false;
         }
     }
-}
-// 1-D bulk copy global → shared memory of this CTA (16-byte aligned, this GPU's own memory).
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
 }
 __device__ __forceinline__ void ring_group_barrier(int group) {
     asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(kWarps * 32) : "memory");
