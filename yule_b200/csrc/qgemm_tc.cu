@@ -907,13 +907,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 const float *parts = p.split_part + (size_t)(wi.tile * p.ksplit) * (BN * kBM) + (size_t)col_base * kBM + lane_base + lane;
 #pragma unroll
                 for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
+                // the loads of up to KS parts are in flight together; the additions keep the order of the parts
+                constexpr uint32_t KS = CW <= 16 ? 4 : (CW <= 32 ? 2 : 1);
 #pragma unroll 1
-                for (uint32_t ks = 0; ks < p.ksplit; ks++, parts += BN * kBM) {  // the loads of a part are independent of one another
-                    float v[CW];
+                for (uint32_t ks0 = 0; ks0 < p.ksplit; ks0 += KS, parts += KS * BN * kBM) {
+                    float v[KS][CW];
 #pragma unroll
-                    for (uint32_t j = 0; j < CW; j++) v[j] = __ldcg(parts + (size_t)j * kBM);
+                    for (uint32_t q = 0; q < KS; q++)
 #pragma unroll
-                    for (uint32_t j = 0; j < CW; j++) acc[j] += v[j];
+                        for (uint32_t j = 0; j < CW; j++)
+                            v[q][j] = ks0 + q < p.ksplit ? __ldcg(parts + (size_t)q * (BN * kBM) + (size_t)j * kBM) : 0.f;
+#pragma unroll
+                    for (uint32_t q = 0; q < KS; q++)
+#pragma unroll
+                        for (uint32_t j = 0; j < CW; j++) acc[j] += v[q][j];
                 }
 #pragma unroll
                 for (uint32_t j = 0; j < CW; j++) {
