@@ -256,6 +256,12 @@ struct QGemm {
     float *out = nullptr;           // [n_tokens][out_stride]
     const float *residual = nullptr;  // added to out (same layout), or null
     uint32_t n_rows = 0, n_cols = 0, n_tokens = 0, x_stride = 0, out_stride = 0;
+    // Further matrices of the same type and row length applied to the same activations in the same launch (Q/K/V,
+    // gate/up); residual must then be null.
+    uint32_t n_more = 0;
+    const uint8_t *w_more[2] = {nullptr, nullptr};
+    float *out_more[2] = {nullptr, nullptr};
+    uint32_t n_rows_more[2] = {0, 0}, out_stride_more[2] = {0, 0};
     void *scratch = nullptr;
     int *status = nullptr;  // the context's device status word
     bool pdl = false;

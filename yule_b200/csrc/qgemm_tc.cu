@@ -94,13 +94,20 @@ constexpr bool kProfile = false;
 #endif
 __device__ long long g_gemm_prof[16];
 
+constexpr int kGemmSegs = 3;  // matrices that share their activation tiles (Q/K/V; gate/up) in one launch
+struct GemmMaps {
+    CUtensorMap m[kGemmSegs];  // exact kernel: tiled view of each weight matrix
+};
 struct GemmParams {
-    const uint8_t *w;      // Q4_K blocks, row-major
+    const uint8_t *w[kGemmSegs];  // blocks, row-major, per matrix
     const __half *xb;      // activation tiles written by gemm_xprep_kernel
     const float *oscale;   // per (padded) activation row: 1 / row scale
-    float *out;            // [n_tokens][out_stride]
-    const float *residual; // added to out (same layout) or null
-    uint32_t n_rows, n_cols, n_tokens, out_stride;
+    float *out[kGemmSegs]; // [n_tokens][out_stride] per matrix
+    const float *residual; // added to the results of matrix 0 (same layout; single-matrix launches only) or null
+    uint32_t n_rows[kGemmSegs], out_stride[kGemmSegs];
+    uint32_t mt0[kGemmSegs + 1];  // first row tile of each matrix in the launch's numbering; [n_seg] = n_mtiles
+    uint32_t n_seg;
+    uint32_t n_cols, n_tokens;
     uint32_t bn;           // activation rows per tile: 32, 64 or 128
     uint32_t n_mtiles, n_ntiles, stages;
     uint32_t ksplit, sb_per;  // split of the columns: `ksplit` work items per tile, `sb_per` super-blocks each (the last may be shorter)
@@ -353,7 +360,7 @@ struct RingPos {
 
 // A work item: tile (row tile x activation tile) and the range of super-blocks [sb0, sb1) of its columns.
 struct Item {
-    uint32_t tile, ks, mt, nt, sb0, sb1;
+    uint32_t tile, ks, mt, nt, sb0, sb1, seg;  // mt: row tile inside matrix `seg`
 };
 __device__ __forceinline__ Item decode_item(const GemmParams &p, uint32_t item, uint32_t bpr) {
     Item r;
@@ -361,13 +368,16 @@ __device__ __forceinline__ Item decode_item(const GemmParams &p, uint32_t item, 
     r.ks = item - r.tile * p.ksplit;
     r.mt = r.tile / p.n_ntiles;
     r.nt = r.tile - r.mt * p.n_ntiles;
+    r.seg = 0;
+    while (r.seg + 1 < p.n_seg && r.mt >= p.mt0[r.seg + 1]) r.seg++;
+    r.mt -= p.mt0[r.seg];
     r.sb0 = r.ks * p.sb_per;
     r.sb1 = r.sb0 + p.sb_per < bpr ? r.sb0 + p.sb_per : bpr;
     return r;
 }
 // The (work item, super-block) pairs of this CTA in the order every role goes through them.
 struct UnitWalk {
-    uint32_t item, sb, sb1, mt;
+    uint32_t item, sb, sb1, mt, seg;
     bool live;
     __device__ __forceinline__ void load(const GemmParams &p, uint32_t n_items, uint32_t bpr) {
         live = item < n_items;
@@ -376,6 +386,7 @@ struct UnitWalk {
             sb = it.sb0;
             sb1 = it.sb1;
             mt = it.mt;
+            seg = it.seg;
         }
     }
     __device__ __forceinline__ void start(const GemmParams &p, uint32_t n_items, uint32_t bpr) {
@@ -431,7 +442,7 @@ struct Tile {
 };
 
 template <int BN, bool GENERIC>
-__global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap w_map) {
+__global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps w_maps) {
     using T = Tile<BN, GENERIC>;
     constexpr uint32_t NBUF = T::NBUF, CW = T::CW, kXHalfBytes = T::kXHalfBytes, kStageBytes = T::kStageBytes;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -626,7 +637,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
                         smem_u32(raw + (size_t)slot * kRawBytes)),
-                    "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar_raw_full + 8 * slot), "r"(x), "r"(y)
+                    "l"(reinterpret_cast<uint64_t>(&w_maps.m[walk.seg])), "r"(bar_raw_full + 8 * slot), "r"(x), "r"(y)
                     : "memory");
             }
         }
@@ -645,8 +656,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             const uint32_t slot_bytes = kBM * rstride;
             auto unit_start = [&](const UnitWalk &w, uint32_t tile_row) {  // address of row `tile_row`'s bytes of the unit
                 uint32_t grow = w.mt * kBM + tile_row;
-                grow = grow < p.n_rows ? grow : p.n_rows - 1;
-                return reinterpret_cast<uintptr_t>(p.w) + (size_t)grow * p.w_row_bytes + (size_t)w.sb * ub;
+                grow = grow < p.n_rows[w.seg] ? grow : p.n_rows[w.seg] - 1;
+                return reinterpret_cast<uintptr_t>(p.w[w.seg]) + (size_t)grow * p.w_row_bytes + (size_t)w.sb * ub;
             };
             auto copy_unit = [&](const UnitWalk &w, uint32_t u) {
                 if (w.live) {
@@ -679,7 +690,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 copy_unit(ahead, u + 1);
                 asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of unit u have landed
                 asm volatile("bar.sync 2, 256;" ::: "memory");         // and everyone else's
-                const bool live = cur.mt * kBM + r < p.n_rows;
+                const bool live = cur.mt * kBM + r < p.n_rows[cur.seg];
                 const unsigned char *rawrow = raw + (size_t)(u & 1u) * slot_bytes + (size_t)r * rstride + (unit_start(cur, r) & 15u);
                 for (uint32_t g = 0; g < 4 && ok; g++, ring.advance(p.stages)) {
                     if (!mbar_wait(bar_empty + 8 * ring.s, ring.ph ^ 1u, abort_flag, p.status)) {
@@ -818,7 +829,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
             const Item wi = decode_item(p, item, bpr);
             const uint32_t mt = wi.mt, nt = wi.nt;
             const uint32_t row = mt * kBM + lane_base + lane;
-            const uint8_t *rowp = p.w + (size_t)(row < p.n_rows ? row : p.n_rows - 1) * bpr * 144;
+            const uint8_t *rowp = p.w[wi.seg] + (size_t)(row < p.n_rows[wi.seg] ? row : p.n_rows[wi.seg] - 1) * bpr * 144;
             float acc[CW];
 #pragma unroll
             for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
@@ -925,9 +936,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
 #pragma unroll
                 for (uint32_t j = 0; j < CW; j++) {
                     const uint32_t n = n0 + j;
-                    if (row < p.n_rows && n < p.n_tokens) {
-                        const size_t o = (size_t)n * p.out_stride + row;
-                        p.out[o] = p.residual ? acc[j] + p.residual[o] : acc[j];
+                    if (row < p.n_rows[wi.seg] && n < p.n_tokens) {
+                        const size_t o = (size_t)n * p.out_stride[wi.seg] + row;
+                        p.out[wi.seg][o] = p.residual ? acc[j] + p.residual[o] : acc[j];
                     }
                 }
                 continue;
@@ -939,11 +950,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const GemmPar
                 for (int j = 0; j < 16; j++) {
                     const float sc = __shfl_sync(0xffffffffu, osc, j);
                     const uint32_t n = n0 + c0 + j;
-                    if (row < p.n_rows && n < p.n_tokens) {
+                    if (row < p.n_rows[wi.seg] && n < p.n_tokens) {
                         float val = acc[c0 + j] * sc * p.out_scale;
-                        const size_t o = (size_t)n * p.out_stride + row;
+                        const size_t o = (size_t)n * p.out_stride[wi.seg] + row;
                         if (p.residual) val += p.residual[o];
-                        p.out[o] = val;
+                        p.out[wi.seg][o] = val;
                     }
                 }
             }
@@ -1265,6 +1276,7 @@ cudaError_t launch_qgemm_xprep(const QGemm &g, cudaStream_t s, uint64_t *launche
 
 cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64_t *launches) {
     if (!qgemm_supported(g.type, g.n_cols, g.n_tokens) || g.n_rows == 0) return cudaErrorInvalidValue;
+    if (g.n_more > (uint32_t)kGemmSegs - 1 || (g.n_more && g.residual)) return cudaErrorInvalidValue;
     const uint32_t bn = pick_bn(g.n_tokens);
     const uint32_t n_ntiles = (g.n_tokens + bn - 1) / bn, padded = n_ntiles * bn;
     unsigned char *xb = reinterpret_cast<unsigned char *>(g.scratch) + kGemmSplitBytes;
@@ -1272,17 +1284,23 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     float *oscale = reinterpret_cast<float *>(xb + ((tiles_bytes + 255) & ~(size_t)255));
     cudaError_t e;
     GemmParams p = {};
-    p.w = g.w;
     p.xb = reinterpret_cast<const __half *>(xb);
     p.oscale = oscale;
-    p.out = g.out;
     p.residual = g.residual;
-    p.n_rows = g.n_rows;
     p.n_cols = g.n_cols;
     p.n_tokens = g.n_tokens;
-    p.out_stride = g.out_stride;
     p.bn = bn;
-    p.n_mtiles = (g.n_rows + kBM - 1) / kBM;
+    p.n_seg = 1 + g.n_more;
+    for (uint32_t i = 0; i < p.n_seg; i++) {
+        p.w[i] = i ? g.w_more[i - 1] : g.w;
+        p.out[i] = i ? g.out_more[i - 1] : g.out;
+        p.n_rows[i] = i ? g.n_rows_more[i - 1] : g.n_rows;
+        p.out_stride[i] = i ? g.out_stride_more[i - 1] : g.out_stride;
+        if (!p.w[i] || !p.out[i] || p.n_rows[i] == 0) return cudaErrorInvalidValue;
+        p.mt0[i + 1] = p.mt0[i] + (p.n_rows[i] + kBM - 1) / kBM;
+    }
+    for (uint32_t i = p.n_seg; i < (uint32_t)kGemmSegs; i++) p.mt0[i + 1] = p.mt0[p.n_seg];
+    p.n_mtiles = p.mt0[p.n_seg];
     p.n_ntiles = n_ntiles;
     // Few tiles and long rows: the columns of a tile are split over several CTAs (whole super-blocks, at least four
     // per part), whose partial results the last one to finish adds up in a fixed order.
@@ -1324,18 +1342,20 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
     p.skip = (kProfile && knob("YULE_GEMM_SKIP")) ? (uint32_t)atoi(knob("YULE_GEMM_SKIP")) : 0u;
     const size_t tail_bytes = raw_ring + (2 * kMaxStages + 8 + 2 * kRawSlots) * 8 + 32;
     const size_t smem = (size_t)p.stages * stage_bytes + tail_bytes;
-    CUtensorMap w_map;
-    memset(&w_map, 0, sizeof(w_map));
+    GemmMaps w_maps;
+    memset(&w_maps, 0, sizeof(w_maps));
     if (!generic) {
-        e = encode_weight_map(g.w, g.n_rows, g.n_cols, &w_map);
-        if (e != cudaSuccess) return e;
+        for (uint32_t i = 0; i < p.n_seg; i++) {
+            e = encode_weight_map(p.w[i], p.n_rows[i], g.n_cols, &w_maps.m[i]);
+            if (e != cudaSuccess) return e;
+        }
     }
     uint32_t grid = p.n_mtiles * p.n_ntiles * p.ksplit;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
     auto launch = [&](auto kern) {
         cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024);
         if (e2 != cudaSuccess) return e2;
-        return launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, s, g.pdl, p, w_map);
+        return launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, s, g.pdl, p, w_maps);
     };
     if (generic)
         e = bn == 32 ? launch(qgemm_tc_kernel<32, true>) : (bn == 64 ? launch(qgemm_tc_kernel<64, true>) : launch(qgemm_tc_kernel<128, true>));

@@ -1005,21 +1005,42 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         g.pdl = true;  // starts under the tail of its predecessor; reads and writes only after the dependency wait
         ok(launch_qgemm_xprep(g, s, launches));
     };
-    // `rows` output rows of this rank, written at `out` with `stride` floats between the rows of the result
+    // `rows` output rows of this rank, written at `out` with `stride` floats between the rows of the result.  Matrices
+    // of one format that read the same re-laid-out rows and add no residual (Q/K/V; gate/up) wait in `gq` and go out
+    // as one launch, whose row tiles run over all of them.
+    QGemm gq;
+    bool gq_open = false;
+    bool share_mm = true;
+    if (const char *k = knob("YULE_GEMM_SHARE")) share_mm = atoi(k) != 0;
+    auto mm_flush = [&]() {
+        if (!gq_open) return;
+        ok(launch_qgemm_mm(gq, sms, s, launches));
+        gq_open = false;
+    };
     auto mm = [&](const Tensor &t, uint32_t rows, uint32_t cols, float *out, uint32_t stride, const float *residual) {
-        QGemm g;
-        g.w = (const uint8_t *)t.buf.ptr;
-        g.type = t.type;
-        g.out = out;
-        g.residual = residual;
-        g.n_rows = rows;
-        g.n_cols = cols;
-        g.n_tokens = m;
-        g.out_stride = stride;
-        g.scratch = ctx->gemm_scratch;
-        g.status = ctx->device_status;
-        g.pdl = true;  // barrier set-up, TMEM allocation and the first weight copies overlap with the re-layout before it
-        ok(launch_qgemm_mm(g, sms, s, launches));
+        if (gq_open && share_mm && !residual && gq.type == t.type && gq.n_cols == cols && gq.n_more < 2) {
+            const uint32_t i = gq.n_more++;
+            gq.w_more[i] = (const uint8_t *)t.buf.ptr;
+            gq.out_more[i] = out;
+            gq.n_rows_more[i] = rows;
+            gq.out_stride_more[i] = stride;
+            return;
+        }
+        mm_flush();
+        gq = QGemm();
+        gq.w = (const uint8_t *)t.buf.ptr;
+        gq.type = t.type;
+        gq.out = out;
+        gq.residual = residual;
+        gq.n_rows = rows;
+        gq.n_cols = cols;
+        gq.n_tokens = m;
+        gq.out_stride = stride;
+        gq.scratch = ctx->gemm_scratch;
+        gq.status = ctx->device_status;
+        gq.pdl = true;  // barrier set-up, TMEM allocation and the first weight copies overlap with the re-layout before it
+        gq_open = true;
+        if (residual) mm_flush();
     };
     // Few live rows: the same sequence of linears on the matvec kernels.  `prep` leaves the rows the next linears read
     // in `act`: normed rows in a buffer of their own, SwiGLU in place, anything else where it is.
@@ -1032,6 +1053,7 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
     QmvArgs pending[3];
     uint32_t n_pending = 0;
     auto flush = [&]() {
+        mm_flush();
         if (n_pending == 0) return;
         for (uint32_t i = 0; i < n_pending; i++) pending[i].norm_w = act_norm;
         if (act_norm && !kquant_batch_can_share(pending, n_pending)) {
@@ -1048,11 +1070,11 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         n_pending = 0;
     };
     auto prep = [&](float *x, uint32_t cols, const float *norm_w, const float *gate) {
+        flush();
         if (!mv) {
             xprep(x, cols, norm_w, gate);
             return;
         }
-        flush();
         if (gate) ok(launch_silu_mul(gate, x, x, ps.n_live * cols, s, launches, true));  // SwiGLU in place
         act = x;
         act_norm = norm_w;
@@ -1153,6 +1175,7 @@ cudaError_t enqueue_rows_pass(yule_cuda_runner *r, const RowsPass &ps, uint64_t 
         ok(launch_argmax_rows(r->bd_logits, c.vocab_size, ps.n_live, r->bd_tokens, r->bd_pos, r->bd_step, r->bd_history, c.max_seq_len + 1, s, launches));
         ok(launch_advance_rows(r->bd_pos, r->bd_step, ps.n_live, s, launches));
     }
+    flush();
     return err;
 }
 
