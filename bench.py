@@ -37,6 +37,7 @@ exchange step — and `value` is the sum over ranks divided by the slowest rank'
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import json
 import os
 import statistics
@@ -633,6 +634,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> int:
 
 
 def main() -> int:
+    faulthandler.enable()  # a crash in native code leaves the Python stack on stderr
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)

@@ -9,6 +9,7 @@ or numpy arrays.  All compute runs in ``libyule_cuda.so``; nothing here computes
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass
 
 import numpy as np
@@ -70,9 +71,14 @@ class CudaB200Backend:
         ctx = C.c_void_p()
         _check(self._lib.yule_cuda_create(device, C.byref(ctx)))
         self._ctx = ctx
+        self._runners = weakref.WeakSet()  # runners created on this context: destroyed before it
 
     def close(self) -> None:
         if getattr(self, "_ctx", None):
+            # A runner holds a pointer to the context: one left open (an exception between its creation and its
+            # close) must not outlive it.
+            for run in list(self._runners):
+                run.close()
             self._lib.yule_cuda_destroy(self._ctx)
             self._ctx = None
 

@@ -34,12 +34,16 @@
 //               takes); warp 9 also owns the TMEM allocation
 //   warp  10    one thread: tiled TMA loads (cp.async.bulk.tensor.2d) of the raw Q4_K bytes, one
 //               128-row × 144-byte box per super-block, four boxes in flight (two at 128 activation
-//               rows, where the room goes to a third operand stage); rows past the end of the matrix
-//               arrive as zeros
+//               rows, where the room goes to a third operand stage; three at 32); rows past the end of
+//               the matrix arrive as zeros
 //   warps 12-19 unpack Q4_K from that shared-memory copy → fp16 sc·q in the operand layout (about
 //               1.4 instructions per weight)
 // A stage is a 128-row × 64-column slab of W (16 KB) plus the matching hi and lo slabs of x; the last
-// stage of a super-block also carries the 4 KB m slab and the sub-block sums of x.
+// stage of a super-block also carries the 4 KB m slab and the sub-block sums of x.  At 32 activation rows
+// a stage is two such column groups (a chain of eight MMAs, as at 128 rows, and half the hand-offs per
+// column), and three raw boxes are in flight.
+// One launch can run over up to three matrices that read the same activations (Q/K/V; gate/up): their row
+// tiles are numbered one after the other.
 // Operands use the no-swizzle K-major core-matrix layout: 8 rows × 16 bytes per core matrix,
 // core matrices of one 8-column step contiguous along the rows.  Inside a core-matrix row the eight
 // columns sit in the order 0,2,1,3,4,6,5,7 (the order in which nibble pairs fall out of a 32-bit
@@ -77,7 +81,23 @@ constexpr int kMaxStages = 6;
 constexpr int kRawSlots = YULE_GEMM_RAW_SLOTS;                       // super-blocks of raw Q4_K bytes in flight per CTA (at most)
 // At 128 activation rows a stage is 56 KB: two raw slots instead of four make room for a third stage, which together
 // with the third accumulator set lets the unpacking, MMA-issuing and drain roles overlap.
-__host__ __device__ constexpr uint32_t raw_slots_for(uint32_t bn) { return bn >= 128 ? 2u : (uint32_t)kRawSlots; }
+// At 32 rows a stage is two column groups wide (53 KB): three raw slots leave room for three of them.
+#ifndef YULE_GEMM_WIDE_32
+#define YULE_GEMM_WIDE_32 1   // two column groups per stage at 32 activation rows
+#endif
+#ifndef YULE_GEMM_RAW_SLOTS_32
+#define YULE_GEMM_RAW_SLOTS_32 (YULE_GEMM_WIDE_32 ? 3 : 4)
+#endif
+__host__ __device__ constexpr uint32_t raw_slots_for(uint32_t bn) {
+    return bn >= 128 ? 2u : (bn <= 32 ? (uint32_t)YULE_GEMM_RAW_SLOTS_32 : (uint32_t)(kRawSlots < 4 ? kRawSlots : 4));
+}
+// 64-column groups of W per stage.  The exact kernel at 32 activation rows takes two: its MMAs are narrow and its
+// drains short, so the waits, fences and barrier arrivals of a stage, not its work, set the pace, and a stage of
+// twice the columns halves them.  A chain is then eight MMAs (one per 16 columns against hi | lo), the same length as
+// at 128 rows.
+__host__ __device__ constexpr uint32_t groups_per_stage(uint32_t bn, bool generic) {
+    return (YULE_GEMM_WIDE_32 && !generic && bn <= 32) ? 2u : 1u;
+}
 constexpr uint32_t kRawBytes = kBM * 144;          // one super-block of 128 rows: 18 KB
 constexpr uint32_t kABytes = kBM * kBK * 2;  // the W slab of a stage: 16 KB
 constexpr float kSumScale = 1.0f / 32.0f;     // the sub-block sums of x are stored divided by 32
@@ -431,10 +451,13 @@ struct Tile {
     static constexpr uint32_t CW = BN / 2;                   // columns per drain warp
     static constexpr uint32_t kXHalfBytes = BN * kBK * 2;    // one fp16 term of the activation slab
     static constexpr uint32_t kBmBytes = BN * 16 * 2;        // sub-block sums of x: BN rows × (8 hi + 8 lo)
-    // stage (exact):   W | m | x_hi | x_lo | sums   (the last three arrive in one bulk copy)
+    static constexpr uint32_t KG = groups_per_stage(BN, GENERIC);  // 64-column groups per stage
+    static constexpr uint32_t SPB = 4 / KG;                        // stages per super-block
+    // stage (exact):   W (KG groups) | m | KG × (x_hi | x_lo) | sums   (everything after m arrives in one bulk copy)
     // stage (generic): W_hi | W_lo | x_hi | x_lo
-    static constexpr uint32_t kOffAm = kABytes, kOffX = GENERIC ? 2 * kABytes : kABytes + kAmBytes;
-    static constexpr uint32_t kStageBytes = kOffX + 2 * kXHalfBytes + (GENERIC ? 0u : kBmBytes);
+    static constexpr uint32_t kOffAm = KG * kABytes, kOffX = GENERIC ? 2 * kABytes : KG * kABytes + kAmBytes;
+    static constexpr uint32_t kOffSums = kOffX + KG * 2 * kXHalfBytes;
+    static constexpr uint32_t kStageBytes = kOffSums + (GENERIC ? 0u : kBmBytes);
     static constexpr uint32_t kRaw = raw_slots_for(BN);
     static constexpr uint32_t kRawRingBytes = GENERIC ? 0u : kRaw * kRawBytes;  // generic: sized at launch
     // activation tiles in global memory, per (activation tile, super-block): four (hi, lo) slabs, then the sums
@@ -500,14 +523,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const Item wi = decode_item(p, item, bpr);
                 const unsigned char *src = reinterpret_cast<const unsigned char *>(p.xb) + (size_t)wi.nt * bpr * T::kSuperBytes;
-                for (uint32_t kb = 4 * wi.sb0; kb < 4 * wi.sb1; kb++, it++, ring.advance(p.stages)) {
+                for (uint32_t kb = T::SPB * wi.sb0; kb < T::SPB * wi.sb1; kb++, it++, ring.advance(p.stages)) {
                     const uint32_t s = ring.s, ph = ring.ph;
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t g = kb & 3u;
-                    const uint32_t bytes = 2 * kXHalfBytes + ((!GENERIC && g == 3) ? T::kBmBytes : 0u);  // the sums ride with the last stage
+                    const uint32_t g = kb % T::SPB;
+                    const uint32_t bytes = T::KG * 2 * kXHalfBytes + ((!GENERIC && g == T::SPB - 1) ? T::kBmBytes : 0u);  // the sums ride with the last stage
                     const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes + T::kOffX);
                     if (skip & 8u) {
                         mbar_arrive(bar_full + 8 * s);
@@ -515,7 +538,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
                     }
                     mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                                 "l"(src + (size_t)(kb >> 2) * T::kSuperBytes + (size_t)g * 2 * kXHalfBytes), "r"(bytes),
+                                 "l"(src + (size_t)(kb / T::SPB) * T::kSuperBytes + (size_t)g * T::KG * 2 * kXHalfBytes), "r"(bytes),
                                  "r"(bar_full + 8 * s)
                                  : "memory");
                 }
@@ -535,7 +558,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
             const long long tstart = (kProfile && p.prof) ? clock64() : 0;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const Item wi = decode_item(p, item, bpr);
-                for (uint32_t kb = 4 * wi.sb0; kb < 4 * wi.sb1; kb++, it++, ring.advance(p.stages)) {
+                for (uint32_t kb = T::SPB * wi.sb0; kb < T::SPB * wi.sb1; kb++, it++, ring.advance(p.stages)) {
                     const bool mine = (it & 1u) == parity_of_mine;  // the threads alternate stages
                     const uint32_t s = ring.s, ph = ring.ph;
                     const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
@@ -573,7 +596,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
                     const uint32_t d_main = tmem_base + buf * T::kBufCols;
                     [[maybe_unused]] const uint32_t d_min = T::SHARED_MIN ? tmem_base + T::kMinBase : d_main + T::kMinBase;
                     const uint32_t a = smem_u32(smem + (size_t)s * kStageBytes);
-                    const uint32_t x_hi = a + T::kOffX, x_lo = x_hi + kXHalfBytes;
+                    const uint32_t x_hi = a + T::kOffX;
                     // One descriptor per operand and stage; the 16-column steps are constants added to its address field (the
                     // issuing thread's own instruction stream, not the tensor pipe, bounded the MMA rate).
                     const uint64_t da0 = smem_desc(a, 2048, 128);
@@ -600,9 +623,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
                         step(std::integral_constant<uint32_t, 1>{});
                         step(std::integral_constant<uint32_t, 2>{});
                         step(std::integral_constant<uint32_t, 3>{});
+                        if constexpr (T::KG == 2) {  // the second group's slabs follow the first's in both operands
+                            step(std::integral_constant<uint32_t, 4>{});
+                            step(std::integral_constant<uint32_t, 5>{});
+                            step(std::integral_constant<uint32_t, 6>{});
+                            step(std::integral_constant<uint32_t, 7>{});
+                        }
                     }
-                    if (!GENERIC && (kb & 3u) == 3u)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
-                        umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(x_lo + kXHalfBytes, x_lbo, 128), idesc, 0u);
+                    if (!GENERIC && kb % T::SPB == T::SPB - 1)  // Σ_s m_s · (sum of x over sub-block s), hi and lo sums side by side
+                        umma_f16(d_min, smem_desc(a + T::kOffAm, 2048, 128), smem_desc(a + T::kOffSums, x_lbo, 128), idesc, 0u);
                     const long long c3 = (kProfile && p.prof) ? clock64() : 0;
                     umma_commit(bar_empty + 8 * s);       // the slabs may be overwritten once these MMAs are done
                     if (!(skip & 32u)) umma_commit(bar_acc_full + 8 * buf);  // and the accumulators may be drained
@@ -738,21 +767,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
         auto unpack_block = [&](const RowBlock &cur) {
             const ScalesMins sm = q4k_scales_mins(cur.hdr.y, cur.hdr.z, cur.hdr.w);
 #pragma unroll
-            for (uint32_t g = 0; g < 4; g++, it++, ring.advance(p.stages)) {
+            for (uint32_t g = 0; g < 4; g++, it++) {
                 const uint32_t s = ring.s, ph = ring.ph;
+                const bool opens = g % T::KG == 0, closes = g % T::KG == T::KG - 1;  // first / last group of its stage
                 // scales of sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles) as fp16 pairs (sc, sc)
                 const uint32_t scw = g < 2 ? sm.sc_lo : sm.sc_hi, j0 = (2 * g) & 3u;
                 const __half2 sc0 = __hsub2(as_half2(biased_pair(scw, 0x4040u + j0 * 0x0101u)), k1024);
                 const __half2 sc1 = __hsub2(as_half2(biased_pair(scw, 0x4040u + (j0 + 1) * 0x0101u)), k1024);
                 const __half2 nb0 = __hmul2(sc0, kneg1024), nb1 = __hmul2(sc1, kneg1024);  // −1024·sc ≥ −64512: exact
                 const long long c0 = (kProfile && p.prof) ? clock64() : 0;
-                if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
+                if (opens && !mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) {
                     ok = false;
                     return;
                 }
                 const long long c1 = (kProfile && p.prof) ? clock64() : 0;
                 pw += c1 - c0;
-                unsigned char *a = smem + (size_t)s * kStageBytes;
+                unsigned char *stage = smem + (size_t)s * kStageBytes, *a = stage + (g % T::KG) * kABytes;
                 // byte b of the 32 holds column b (low nibble, sub-block 2g) and column 32 + b (high nibble)
                 const uint32_t qw[4] = {cur.q[g].x, cur.q[g].y, cur.q[g].z, cur.q[g].w};
 #pragma unroll
@@ -783,12 +813,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
                     m.y = as_u32(__hsub2(as_half2(biased_pair(sm.m_lo, 0x5342u)), k1024));
                     m.z = as_u32(__hsub2(as_half2(biased_pair(sm.m_hi, 0x5140u)), k1024));
                     m.w = as_u32(__hsub2(as_half2(biased_pair(sm.m_hi, 0x5342u)), k1024));
-                    *reinterpret_cast<uint4 *>(a + T::kOffAm + hf * 2048 + in_core) = m;
+                    *reinterpret_cast<uint4 *>(stage + T::kOffAm + hf * 2048 + in_core) = m;
                 }
                 const long long c2 = (kProfile && p.prof) ? clock64() : 0;
-                fence_async_smem();  // generic-proxy stores → visible to the tensor core's reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                if (closes) {
+                    fence_async_smem();  // generic-proxy stores → visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                    ring.advance(p.stages);
+                }
                 const long long c3 = (kProfile && p.prof) ? clock64() : 0;
                 pk += c2 - c1;
                 pf += c3 - c2;
@@ -834,13 +867,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
 #pragma unroll
             for (uint32_t j = 0; j < CW; j++) acc[j] = 0.f;
             uint32_t dd_cur = 0, dd_next = GENERIC ? 0u : __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)wi.sb0 * 144));  // (d, dmin) of the first super-block
-            const uint32_t kb_end = 4 * wi.sb1;
-            for (uint32_t kb = 4 * wi.sb0; kb < kb_end; kb++, it++) {
+            const uint32_t kb_end = T::SPB * wi.sb1;
+            for (uint32_t kb = T::SPB * wi.sb0; kb < kb_end; kb++, it++) {
                 if (skip & 32u) break;
                 const uint32_t buf = it % NBUF, aph = (it / NBUF) & 1u;
-                if (!GENERIC && (kb & 3u) == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
+                if (!GENERIC && kb % T::SPB == 0u) {  // new super-block: take its (d, dmin), ask for the next one's
                     dd_cur = dd_next;
-                    if (kb + 4 < kb_end) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)((kb >> 2) + 1) * 144));
+                    if (kb + T::SPB < kb_end) dd_next = __ldg(reinterpret_cast<const uint32_t *>(rowp + (size_t)(kb / T::SPB + 1) * 144));
                 }
                 const float2 dd = GENERIC ? make_float2(1.f, 0.f) : __half22float2(as_half2(dd_cur));
                 const long long c0 = (kProfile && p.prof) ? clock64() : 0;
@@ -874,7 +907,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) qgemm_tc_kernel(const __grid_
                         for (int j = 0; j < 16; j++) acc[c0 + j] = fmaf(dd.x, __uint_as_float(v[j]), acc[c0 + j]);
                     }
                 }
-                if (!GENERIC && (kb & 3u) == 3u) {  // the stage that ends a super-block carries the min term
+                if (!GENERIC && kb % T::SPB == T::SPB - 1) {  // the stage that ends a super-block carries the min term
 #pragma unroll
                     for (uint32_t c0 = 0; c0 < CW; c0 += 16) {
                         uint32_t v[16];
@@ -1325,7 +1358,8 @@ cudaError_t launch_qgemm_mm(const QGemm &g, int sm_count, cudaStream_t s, uint64
         p.split_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(g.scratch) + kGemmTicketBytes);
     }
     const bool generic = g.type != YULE_DTYPE_Q4_K || (knob("YULE_GEMM_GENERIC") && atoi(knob("YULE_GEMM_GENERIC")));
-    const uint32_t stage_bytes = generic ? 2 * kABytes + 2 * bn * kBK * 2 : kABytes + kAmBytes + 2 * bn * kBK * 2 + bn * 32;
+    const uint32_t kg = groups_per_stage(bn, generic);
+    const uint32_t stage_bytes = generic ? 2 * kABytes + 2 * bn * kBK * 2 : kg * kABytes + kAmBytes + kg * 2 * bn * kBK * 2 + bn * 32;
     p.unit_bytes = 256 / block_size(g.type) * block_bytes(g.type);
     p.raw_chunks = (p.unit_bytes + 14 + 15) / 16;      // covers the unit from any 2-byte-aligned start
     p.raw_stride = (p.raw_chunks | 1u) * 16;            // an odd multiple of 16 bytes

@@ -98,6 +98,7 @@ class CudaTransformerRunner:
         r = C.c_void_p()
         _check(self._lib.yule_cuda_runner_create(backend._ctx, C.byref(cfg), C.byref(r)))
         self._r = r
+        backend._runners.add(self)
         self._handles: dict[str, BufferHandle] = {}
         self.weight_bytes = 0
         for name, (data, dtype) in weights.items():
@@ -110,12 +111,13 @@ class CudaTransformerRunner:
         backend.synchronize()
 
     def close(self) -> None:
-        if getattr(self, "_r", None):
-            self._lib.yule_cuda_runner_destroy(self._r)
-            self._r = None
-            for h in self._handles.values():
-                self.backend.free(h)
-            self._handles.clear()
+        r, self._r = getattr(self, "_r", None), None  # at most one destroy, whatever the frees below raise
+        if r:
+            handles, self._handles = self._handles, {}
+            if getattr(self.backend, "_ctx", None):  # the context takes its runners with it (backend.close)
+                self._lib.yule_cuda_runner_destroy(r)
+                for h in handles.values():
+                    self.backend.free(h)
 
     def __del__(self):
         try:
